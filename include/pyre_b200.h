@@ -1,0 +1,197 @@
+/* pyre_b200 -- C ABI of the B200-native Qwen-Next decode engine.
+ *
+ * Drop-in boundary for the model surface that the reference's engine loop calls
+ * (Lyamc/pyre: src/engine_qn.rs, src/spec.rs, src/qn_cli.rs).  The reference has no FFI
+ * today; each entry point below names the Rust item it replaces (file:line inside the
+ * reference project).  Plain pointers and sizes only; no C++ or torch types.
+ *
+ * Conventions
+ *   - Every function returns a pb_status (0 = PB_OK).  Nothing aborts, traps or unwinds
+ *     across this boundary; pb_last_error(ctx) gives the text of the last failure.
+ *     (The reference panics on impossible states and its worker turns the panic into an
+ *     error event, src/engine_qn.rs:56-59.)
+ *   - A context is thread-affine: create it and make every call on one OS thread, as
+ *     the reference's single "qn-worker" thread does (src/engine_qn.rs:13-17).
+ *   - Pointers named *_host are caller-owned host memory; *_dev are device pointers on
+ *     the context's GPU.  Weights are copied at upload; handles are freed by the caller.
+ *   - Activations are token-major: x [t][cols], y [t][rows] (QMat::matmul, gguf_q.rs:217).
+ *   - There is no CPU fallback: every compute entry point runs CUDA kernels or fails.
+ */
+#ifndef PYRE_B200_H
+#define PYRE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum pb_status {
+    PB_OK = 0,
+    PB_ERR_ARG = 1,        /* bad argument (shape, type id, null pointer, range) */
+    PB_ERR_CUDA = 2,       /* a CUDA runtime call failed */
+    PB_ERR_OOM = 3,        /* device allocation failed */
+    PB_UNSUPPORTED = 4,    /* valid request that this build does not implement */
+    PB_ERR_DEVICE = 5,     /* a kernel reported a failure in the device status word */
+    PB_ERR_STATE = 6       /* call not valid in the handle's current state */
+} pb_status;
+
+typedef struct pb_ctx pb_ctx;
+typedef struct pb_qmat pb_qmat;
+typedef struct pb_model pb_model;
+typedef struct pb_state pb_state;
+
+/* ggml type ids accepted for matrices (QType::from_id, src/model/gguf_q.rs:23-29) */
+enum { PB_TYPE_F32 = 0, PB_TYPE_F16 = 1, PB_TYPE_Q8_0 = 8, PB_TYPE_Q4_K = 12, PB_TYPE_IQ2_XS = 17, PB_TYPE_IQ3_S = 21, PB_TYPE_BF16 = 30 };
+
+/* ---------------------------------------------------------------- context */
+
+/* One context per GPU and worker thread (replaces the reference's Cube / device handle,
+ * src/model/qn_cube.rs:6237-6250). */
+int pb_ctx_create(int device, pb_ctx** out);
+int pb_ctx_destroy(pb_ctx* ctx);
+const char* pb_last_error(const pb_ctx* ctx);
+/* Launch on a caller-provided cudaStream_t (passed as void*; NULL is the legacy default stream).
+ * pb_ctx_own_stream returns to the context's own non-blocking stream. */
+int pb_ctx_set_stream(pb_ctx* ctx, void* cuda_stream);
+int pb_ctx_own_stream(pb_ctx* ctx);
+int pb_ctx_sync(pb_ctx* ctx);
+/* Reads and clears the device status word (0 = no kernel reported a failure). */
+int pb_ctx_device_status(pb_ctx* ctx, int* status);
+
+/* (elements per block, bytes per block) -- QType::geom, src/model/gguf_q.rs:33-41 */
+int pb_type_geom(int ggml_type, int* elems, int* bytes);
+
+/* ---------------------------------------------------------------- quantized matrices */
+
+/* Copy a rows x cols matrix of GGUF blocks to the GPU, kept in its native block format.
+ * Replaces QMat views over the mmapped file: Gguf::mat src/model/gguf_q.rs:326-331,
+ * QMat::bytes/raw_rows :209-214. */
+int pb_qmat_upload(pb_ctx* ctx, int ggml_type, int64_t rows, int64_t cols, const void* bytes_host, size_t nbytes, pb_qmat** out);
+/* Seeded synthetic matrix generated on the GPU (benchmark weights; no counterpart in the
+ * reference, whose tests patch LCG-random block bytes the same way, src/model/qdot.rs:1033-1047). */
+int pb_qmat_synth(pb_ctx* ctx, int ggml_type, int64_t rows, int64_t cols, uint64_t seed, uint64_t tensor_id, pb_qmat** out);
+int pb_qmat_free(pb_qmat* m);
+int pb_qmat_info(const pb_qmat* m, int* ggml_type, int64_t* rows, int64_t* cols, size_t* nbytes);
+/* Raw block bytes of rows [r0, r0+nrows) back to the host (QMat::raw_rows :214). */
+int pb_qmat_read(pb_ctx* ctx, const pb_qmat* m, int64_t r0, int64_t nrows, void* bytes_host);
+/* Dequantize rows [r0, r0+nrows) to f32, bit-identical to dequant(), src/model/gguf_q.rs:67-166
+ * (QMat::row :210, QMat::to_f32 :211). */
+int pb_qmat_dequant(pb_ctx* ctx, const pb_qmat* m, int64_t r0, int64_t nrows, float* out_host);
+int pb_qmat_dequant_dev(pb_ctx* ctx, const pb_qmat* m, int64_t r0, int64_t nrows, float* out_dev);
+/* y[ti*rows + r] = sum_c W[r,c] * x[ti*cols + c], f32 accumulate -- QMat::matmul,
+ * src/model/gguf_q.rs:217-242.  Host-buffer form (what the reference's callers hold) and
+ * device-buffer form. */
+int pb_gemv(pb_ctx* ctx, const pb_qmat* m, const float* x_host, int t, float* y_host);
+int pb_gemv_dev(pb_ctx* ctx, const pb_qmat* m, const float* x_dev, int t, float* y_dev);
+
+/* ---------------------------------------------------------------- model */
+
+/* Cfg, src/model/qwen4exp_gguf.rs:18-26 (fields of the decode path only). */
+typedef struct pb_cfg {
+    int32_t n_layers, d, hc, hc_lr, n_head, n_kv, hd, n_rot;
+    float rope_base, eps;
+    int32_t n_exp, top_k, ff_exp, ff_sh;
+    int32_t lin_nk, lin_nv, lin_dk, lin_dv, conv_k, full_every;
+    int32_t vocab, max_ctx;
+    int32_t kv_bits;    /* 0: f32 KV; 4: positions older than the recent window are 4-bit (src/model/kv4.rs) */
+    int32_t kv_recent;  /* f32 window in front of the packed region (reference default 1024, kv_push :1517-1534) */
+} pb_cfg;
+
+/* Tensor roles: the fields of Layer / Mixer / Hc, src/model/qwen4exp_gguf.rs:28-34, and the
+ * GGUF names they are loaded from (:494-511). */
+typedef enum pb_role {
+    PB_R_TOKEN_EMBD = 0, PB_R_OUTPUT, PB_R_OUT_NORM,
+    PB_R_ATTN_NORM, PB_R_FFN_NORM,
+    PB_R_ATTN_Q, PB_R_ATTN_K, PB_R_ATTN_V, PB_R_ATTN_O, PB_R_ATTN_Q_NORM, PB_R_ATTN_K_NORM,
+    PB_R_LIN_QKV, PB_R_LIN_Z, PB_R_LIN_BETA, PB_R_LIN_ALPHA, PB_R_LIN_OUT,
+    PB_R_LIN_A, PB_R_LIN_DT, PB_R_LIN_CONV, PB_R_LIN_NORM,
+    PB_R_ROUTER, PB_R_EXP_GATE, PB_R_EXP_UP, PB_R_EXP_DOWN,
+    PB_R_SH_GATE, PB_R_SH_UP, PB_R_SH_DOWN, PB_R_SH_GATE_INP,
+    PB_R_HCA_NORM, PB_R_HCA_DOWN, PB_R_HCA_UP, PB_R_HCA_INJECT,
+    PB_R_HCF_NORM, PB_R_HCF_DOWN, PB_R_HCF_UP, PB_R_HCF_INJECT,
+    PB_R_OUT_HC_NORM, PB_R_OUT_HC_DOWN, PB_R_OUT_HC_UP,
+    PB_R_COUNT
+} pb_role;
+
+/* Model::load, src/model/qwen4exp_gguf.rs:462-524, split into create / set / finalize so the
+ * Rust side keeps owning the GGUF mmap.  layer = -1 for global tensors. */
+int pb_model_create(pb_ctx* ctx, const pb_cfg* cfg, pb_model** out);
+int pb_model_set_tensor(pb_model* m, int layer, int role, pb_qmat* mat);   /* the model takes ownership */
+int pb_model_set_vec(pb_model* m, int layer, int role, const float* v_host, int64_t n);
+/* attach_gpu :555-657.  ep_rank/ep_world: this GPU holds routed experts
+ * [ep_rank*n_exp/ep_world, (ep_rank+1)*n_exp/ep_world) of every layer; dense tensors are replicated. */
+int pb_model_finalize(pb_model* m, int ep_rank, int ep_world);
+int pb_model_destroy(pb_model* m);
+
+/* new_state :1345-1353; `batch` independent sequences decode together. */
+int pb_state_create(pb_model* m, int batch, pb_state** out);
+int pb_state_destroy(pb_state* s);
+/* Pre-fill attention layer `attn_index` of sequence `b` with n positions of already normed and
+ * roped K and V rows [n][n_kv*hd] (f32, host); packs per cfg.kv_bits.  Benchmark set-up for a
+ * long context without running a prefill. */
+int pb_state_fill_kv(pb_state* s, int b, int attn_index, const float* k_host, const float* v_host, int64_t n);
+/* Same with seeded synthetic N(0,1) rows generated on the GPU. */
+int pb_state_fill_kv_synth(pb_state* s, int attn_index, int64_t n, uint64_t seed);
+int pb_state_set_pos(pb_state* s, int64_t pos);
+int pb_state_pos(const pb_state* s, int64_t* pos);
+
+/* Model::forward(ids, st) -> logits, src/model/qwen4exp_gguf.rs:2050-2157 (= spec::Target::step,
+ * src/spec.rs:106-120, QnTarget::step src/engine_qn.rs:247).  ids_host [batch][t]; the logits of
+ * the last fed token of each sequence go to logits_host [batch][vocab]. */
+int pb_forward(pb_state* s, const uint32_t* ids_host, int t, float* logits_host);
+/* forward + sampler::argmax (src/sampler.rs:142-148) on the device: next_host [batch]. */
+int pb_step_greedy(pb_state* s, const uint32_t* tok_host, uint32_t* next_host);
+/* Decode n greedy tokens per sequence without leaving the device between steps;
+ * out_host [batch][n].  Same arithmetic as n calls of pb_step_greedy. */
+int pb_decode_greedy(pb_state* s, const uint32_t* tok_host, int n, uint32_t* out_host);
+
+/* Model::forward_multi :2365-2480 (= Target::verify): logits for every fed position,
+ * logits_host [t][vocab]; records per-position rollback checkpoints.  batch must be 1. */
+int pb_verify(pb_state* s, const uint32_t* ids_host, int t, float* logits_host);
+/* Model::spec_keep :2495-2515 (= Target::keep): keep the first `keep` of the last t verified tokens. */
+int pb_keep(pb_state* s, int t, int keep);
+/* Model::mtp_draft :2177 (= Target::draft).  Returns PB_UNSUPPORTED: the caller's n-gram drafter
+ * then takes over (src/spec.rs:207). */
+int pb_draft(pb_state* s, int max_draft, uint32_t* ids_host, int* n);
+
+/* Model::snapshot / restore, Snap :3277-3298.  size query: pass buf_host = NULL. */
+int pb_state_snapshot(pb_state* s, void* buf_host, size_t* nbytes);
+int pb_state_restore(pb_state* s, const void* buf_host, size_t nbytes);
+
+/* multi_ok :2352, spec_max_window :2486, max_ctx :526 */
+typedef struct pb_caps { int32_t multi_ok, max_window, max_ctx, max_batch, ep_world; } pb_caps;
+int pb_caps_get(const pb_model* m, pb_caps* caps);
+
+/* Counters for the reference's metrics hooks (src/metrics.rs:6-7). */
+typedef struct pb_stats {
+    uint64_t steps, kernels_launched, weight_bytes_per_step, kv_bytes_per_step, state_bytes_per_step;
+} pb_stats;
+int pb_stats_get(const pb_state* s, pb_stats* out);
+
+/* ---------------------------------------------------------------- layer-level entry points
+ * The blocks of the token loop, callable alone on device buffers (parity tests, benchmarks). */
+
+/* MoE block: ffn :1675-1684 + routed :1721-1795.  x_host [t][d] -> y_host [t][d];
+ * sel_host (optional) [t][top_k] expert ids in the order they are accumulated. */
+int pb_moe_forward(pb_state* s, int layer, const float* x_host, int t, float* y_host, int32_t* sel_host);
+/* Gated DeltaNet layer step: linear :1617-1621 + linear_core :1624-1673 for one token per
+ * sequence.  x_host [batch][d] -> y_host [batch][d]; advances the layer's conv and ssm state. */
+int pb_deltanet_step(pb_state* s, int layer, const float* x_host, float* y_host);
+/* Gated attention layer step: attn :1441-1446 + attn_core :1558-1615 at the state's position. */
+int pb_attn_step(pb_state* s, int layer, const float* x_host, float* y_host);
+/* Copies of a DeltaNet layer's recurrent state for inspection / set-up: ssm [batch][nv][dk][dv],
+ * conv [batch][conv_k-1][ch]. */
+int pb_state_get_lin(pb_state* s, int layer, float* conv_host, float* ssm_host);
+int pb_state_set_lin(pb_state* s, int layer, const float* conv_host, const float* ssm_host);
+
+/* 4-bit KV packing on the device: kv4::pack / kv4::get, src/model/kv4.rs:12-42.
+ * x_host [n] f32 (n a multiple of 32) -> words_host [n/8], scales_host [n/32]. */
+int pb_kv4_pack(pb_ctx* ctx, const float* x_host, int64_t n, uint32_t* words_host, float* scales_host);
+int pb_kv4_unpack(pb_ctx* ctx, const uint32_t* words_host, const float* scales_host, int64_t n, float* x_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PYRE_B200_H */

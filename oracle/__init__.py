@@ -1,0 +1,283 @@
+"""ctypes front end of the CPU oracle (oracle/pyre_oracle.c) -- TEST INFRASTRUCTURE ONLY.
+
+Only tests, the smoke check and the CPU-baseline / reference arm of the benchmark import
+this module.  The product package never does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+_HERE = Path(__file__).resolve().parent
+_SO = _HERE / "_ref" / "libpyre_oracle.so"
+
+F32, F16, Q8_0, Q4_K, IQ2_XS, IQ3_S, BF16 = 0, 1, 8, 12, 17, 21, 30
+QUANT_TYPES = {"Q8_0": Q8_0, "Q4_K": Q4_K, "IQ2_XS": IQ2_XS, "IQ3_S": IQ3_S}
+
+ROLES = [
+    "TOKEN_EMBD", "OUTPUT", "OUT_NORM", "ATTN_NORM", "FFN_NORM",
+    "ATTN_Q", "ATTN_K", "ATTN_V", "ATTN_O", "ATTN_Q_NORM", "ATTN_K_NORM",
+    "LIN_QKV", "LIN_Z", "LIN_BETA", "LIN_ALPHA", "LIN_OUT", "LIN_A", "LIN_DT", "LIN_CONV", "LIN_NORM",
+    "ROUTER", "EXP_GATE", "EXP_UP", "EXP_DOWN", "SH_GATE", "SH_UP", "SH_DOWN", "SH_GATE_INP",
+    "HCA_NORM", "HCA_DOWN", "HCA_UP", "HCA_INJECT", "HCF_NORM", "HCF_DOWN", "HCF_UP", "HCF_INJECT",
+    "OUT_HC_NORM", "OUT_HC_DOWN", "OUT_HC_UP",
+]
+ROLE = {n: i for i, n in enumerate(ROLES)}
+
+
+def build(force: bool = False) -> Path:
+    """Compile the oracle with the Makefile beside it (gcc, a second or two)."""
+    src = [_HERE / "pyre_oracle.c", _HERE / "pyre_oracle.h", _HERE / "iq_tables.h"]
+    if force or not _SO.exists() or any(s.stat().st_mtime > _SO.stat().st_mtime for s in src):
+        subprocess.run(["make", "-C", str(_HERE)] + (["-B"] if force else []), check=True, capture_output=True)
+    return _SO
+
+
+class Mat(C.Structure):
+    _fields_ = [("type", C.c_int32), ("rows", C.c_int64), ("cols", C.c_int64), ("data", C.c_void_p),
+                ("seed", C.c_uint64), ("tid", C.c_uint64)]
+
+
+class Cfg(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_layers", "d", "hc", "hc_lr", "n_head", "n_kv", "hd", "n_rot")] + \
+               [("rope_base", C.c_float), ("eps", C.c_float)] + \
+               [(n, C.c_int32) for n in ("n_exp", "top_k", "ff_exp", "ff_sh", "lin_nk", "lin_nv", "lin_dk", "lin_dv",
+                                         "conv_k", "full_every", "vocab", "max_ctx", "kv_bits", "kv_recent")]
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        L = C.CDLL(str(_SO))
+        L.orc_row_bytes.restype = C.c_int64
+        L.orc_row_bytes.argtypes = [C.c_int, C.c_int64]
+        L.orc_dot.restype = C.c_float
+        L.orc_kv4_get.restype = C.c_float
+        L.orc_argmax.restype = C.c_uint32
+        L.orc_model_new.restype = C.c_void_p
+        L.orc_state_new.restype = C.c_void_p
+        L.orc_threads.restype = C.c_int
+        _lib = L
+    return _lib
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def threads() -> int:
+    return lib().orc_threads()
+
+
+def geom(t: int):
+    e, b = C.c_int(), C.c_int()
+    if lib().orc_type_geom(t, C.byref(e), C.byref(b)):
+        raise ValueError(f"unsupported ggml type {t}")
+    return e.value, b.value
+
+
+def row_bytes(t: int, cols: int) -> int:
+    return lib().orc_row_bytes(t, cols)
+
+
+def dequant(t: int, raw: np.ndarray, n: int) -> np.ndarray:
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    y = np.empty(n, dtype=np.float32)
+    if lib().orc_dequant(t, _p(raw), C.c_int64(n), _p(y)):
+        raise ValueError(f"unsupported ggml type {t}")
+    return y
+
+
+def synth_rows(t: int, seed: int, tid: int, cols: int, r0: int, nrows: int) -> np.ndarray:
+    out = np.empty(nrows * row_bytes(t, cols), dtype=np.uint8)
+    lib().orc_synth_rows(t, C.c_uint64(seed), C.c_uint64(tid), C.c_int64(cols), C.c_int64(r0), C.c_int64(nrows), _p(out))
+    return out
+
+
+def synth_normal(seed: int, tid: int, i0: int, n: int, sigma: float) -> np.ndarray:
+    out = np.empty(n, dtype=np.float32)
+    lib().orc_synth_normal(C.c_uint64(seed), C.c_uint64(tid), C.c_int64(i0), C.c_int64(n), C.c_float(sigma), _p(out))
+    return out
+
+
+class QMat:
+    """Quantized matrix view: explicit bytes (kept alive here) or a synthetic (seed, tid) tensor."""
+
+    def __init__(self, t: int, rows: int, cols: int, data: np.ndarray | None = None, seed: int = 0, tid: int = 0):
+        self.type, self.rows, self.cols, self.seed, self.tid = t, rows, cols, seed, tid
+        self.data = None if data is None else np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        if self.data is not None:
+            assert self.data.size == rows * row_bytes(t, cols), (self.data.size, rows, cols, t)
+        self.c = Mat(t, rows, cols, None if self.data is None else self.data.ctypes.data, seed, tid)
+
+    @classmethod
+    def synth(cls, t, rows, cols, seed, tid):
+        return cls(t, rows, cols, None, seed, tid)
+
+    def raw(self) -> np.ndarray:
+        if self.data is not None:
+            return self.data
+        return synth_rows(self.type, self.seed, self.tid, self.cols, 0, self.rows)
+
+    def to_f32(self) -> np.ndarray:
+        return dequant(self.type, self.raw(), self.rows * self.cols).reshape(self.rows, self.cols)
+
+    def matmul(self, x: np.ndarray) -> np.ndarray:
+        """x [t][cols] -> y [t][rows] (QMat::matmul, token-major)."""
+        x = _f32(x).reshape(-1, self.cols)
+        y = np.empty((x.shape[0], self.rows), dtype=np.float32)
+        lib().orc_matmul(C.byref(self.c), _p(x), C.c_int(x.shape[0]), _p(y))
+        return y
+
+
+def top_k(r: np.ndarray, k: int):
+    r = _f32(r)
+    idx = np.empty(k, dtype=np.int32)
+    w = np.empty(k, dtype=np.float32)
+    lib().orc_top_k(_p(r), C.c_int(r.size), C.c_int(k), _p(idx), _p(w))
+    return idx, w
+
+
+def argmax(v: np.ndarray) -> int:
+    v = _f32(v)
+    return lib().orc_argmax(_p(v), C.c_int64(v.size))
+
+
+def kv4_pack(x: np.ndarray):
+    x = _f32(x).reshape(-1)
+    w = np.empty(x.size // 8, dtype=np.uint32)
+    sc = np.empty(x.size // 32, dtype=np.float32)
+    lib().orc_kv4_pack(_p(x), C.c_int64(x.size), _p(w), _p(sc))
+    return w, sc
+
+
+def kv4_unpack(w: np.ndarray, sc: np.ndarray, n: int) -> np.ndarray:
+    w = np.ascontiguousarray(w, dtype=np.uint32)
+    sc = _f32(sc)
+    L = lib()
+    return np.array([L.orc_kv4_get(_p(w), _p(sc), C.c_int64(i)) for i in range(n)], dtype=np.float32)
+
+
+def rope_inv(n_rot: int, base: float) -> np.ndarray:
+    inv = np.empty(n_rot // 2, dtype=np.float32)
+    lib().orc_rope_inv(C.c_int(n_rot), C.c_float(base), _p(inv))
+    return inv
+
+
+def make_cfg(**kw) -> Cfg:
+    c = Cfg()
+    defaults = dict(n_layers=4, d=2048, hc=0, hc_lr=0, n_head=16, n_kv=2, hd=256, n_rot=64, rope_base=1e7, eps=1e-6,
+                    n_exp=512, top_k=10, ff_exp=512, ff_sh=512, lin_nk=16, lin_nv=32, lin_dk=128, lin_dv=128,
+                    conv_k=4, full_every=4, vocab=151936, max_ctx=4096, kv_bits=0, kv_recent=1024)
+    defaults.update(kw)
+    for k, v in defaults.items():
+        setattr(c, k, v)
+    return c
+
+
+def moe(cfg: Cfg, router: QMat, gate_e: QMat, up_e: QMat, down_e: QMat, sh_gate: QMat, sh_up: QMat, sh_down: QMat,
+        sh_gate_inp: np.ndarray, x: np.ndarray):
+    x = _f32(x).reshape(-1, cfg.d)
+    t = x.shape[0]
+    y = np.empty((t, cfg.d), dtype=np.float32)
+    sel = np.empty((t, cfg.top_k), dtype=np.int32)
+    selw = np.empty((t, cfg.top_k), dtype=np.float32)
+    sgi = _f32(sh_gate_inp)
+    lib().orc_moe(C.byref(cfg), C.byref(router.c), C.byref(gate_e.c), C.byref(up_e.c), C.byref(down_e.c),
+                  C.byref(sh_gate.c), C.byref(sh_up.c), C.byref(sh_down.c), _p(sgi), _p(x), C.c_int(t), _p(y), _p(sel), _p(selw))
+    return y, sel, selw
+
+
+def linear_core(cfg: Cfg, qkv, z, beta, alpha, a, dt, conv_w, norm_w, conv_state, ssm):
+    """One sequence, t tokens.  conv_state and ssm are updated in place (float32, C-contiguous)."""
+    qkv, z, beta, alpha = _f32(qkv), _f32(z), _f32(beta), _f32(alpha)
+    a, dt, conv_w, norm_w = _f32(a), _f32(dt), _f32(conv_w), _f32(norm_w)
+    assert conv_state.dtype == np.float32 and ssm.dtype == np.float32 and conv_state.flags.c_contiguous and ssm.flags.c_contiguous
+    ch = 2 * cfg.lin_nk * cfg.lin_dk + cfg.lin_nv * cfg.lin_dv
+    t = qkv.size // ch
+    out = np.empty((t, cfg.lin_nv * cfg.lin_dv), dtype=np.float32)
+    lib().orc_linear_core(C.byref(cfg), _p(qkv), _p(z), _p(beta), _p(alpha), _p(a), _p(dt), _p(conv_w), _p(norm_w),
+                          _p(conv_state), _p(ssm), C.c_int(t), _p(out))
+    return out
+
+
+def attn_core(cfg: Cfg, qf, kf, vf, qn, kn, inv, kc, vc, pos, packed=None, q4n=0):
+    """One new token at position pos.  kc/vc [>=pos+1][n_kv*hd] f32, updated in place at row pos."""
+    qf, kf, vf, qn, kn, inv = _f32(qf), _f32(kf), _f32(vf), _f32(qn), _f32(kn), _f32(inv)
+    att = np.empty(cfg.n_head * cfg.hd, dtype=np.float32)
+    if packed is None:
+        kw = ks = vw = vs = None
+    else:
+        kw, ks, vw, vs = (_p(a) for a in packed)
+    lib().orc_attn_core(C.byref(cfg), _p(qf), _p(kf), _p(vf), _p(qn), _p(kn), _p(inv), _p(kc), _p(vc), C.c_int64(pos),
+                        kw, ks, vw, vs, C.c_int64(q4n), _p(att))
+    return att
+
+
+class Model:
+    def __init__(self, cfg: Cfg):
+        self.cfg = cfg
+        self._keep = []
+        self.h = C.c_void_p(lib().orc_model_new(C.byref(cfg)))
+
+    def set_mat(self, layer: int, role: str, m: QMat):
+        self._keep.append(m)
+        assert lib().orc_model_set_mat(self.h, C.c_int(layer), C.c_int(ROLE[role]), C.byref(m.c)) == 0
+
+    def set_vec(self, layer: int, role: str, v: np.ndarray):
+        v = _f32(v).reshape(-1)
+        assert lib().orc_model_set_vec(self.h, C.c_int(layer), C.c_int(ROLE[role]), _p(v), C.c_int64(v.size)) == 0
+
+    def new_state(self) -> "State":
+        return State(self)
+
+    def __del__(self):
+        try:
+            lib().orc_model_free(self.h)
+        except Exception:
+            pass
+
+
+class State:
+    def __init__(self, model: Model):
+        self.model = model
+        self.h = C.c_void_p(lib().orc_state_new(model.h))
+
+    def fill_kv(self, ai: int, k: np.ndarray, v: np.ndarray):
+        k, v = _f32(k), _f32(v)
+        row = self.model.cfg.n_kv * self.model.cfg.hd
+        assert lib().orc_state_fill_kv(self.h, C.c_int(ai), _p(k), _p(v), C.c_int64(k.size // row)) == 0
+
+    def set_pos(self, pos: int):
+        lib().orc_state_set_pos(self.h, C.c_int64(pos))
+
+    def forward(self, ids) -> np.ndarray:
+        ids = np.ascontiguousarray(ids, dtype=np.uint32).reshape(-1)
+        logits = np.empty(self.model.cfg.vocab, dtype=np.float32)
+        rc = lib().orc_forward(self.model.h, self.h, _p(ids), C.c_int(ids.size), _p(logits))
+        if rc:
+            raise RuntimeError(f"orc_forward failed: {rc}")
+        return logits
+
+    def margins(self):
+        a, b = C.c_float(), C.c_float()
+        lib().orc_last_margins(self.h, C.byref(a), C.byref(b))
+        return a.value, b.value
+
+    def __del__(self):
+        try:
+            lib().orc_state_free(self.h)
+        except Exception:
+            pass

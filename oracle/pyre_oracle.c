@@ -1,0 +1,579 @@
+/* CPU oracle for the Qwen-Next decode path -- TEST INFRASTRUCTURE ONLY (see pyre_oracle.h).
+ *
+ * Build:  make -C oracle      (gcc -O2 -ffp-contract=off -fopenmp; no reference sources are copied)
+ * File/line citations name files of the reference project (Lyamc/pyre) by their path in it.
+ */
+#include "pyre_oracle.h"
+#include "iq_tables.h"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* ------------------------------------------------------------------ scalars */
+
+/* f16 -> f32, exact (the reference uses half::f16::to_f32, gguf_q.rs:60) */
+static float h2f(uint16_t h) {
+    uint32_t s = (uint32_t)(h >> 15) << 31, e = (h >> 10) & 31, m = h & 1023, u;
+    if (e == 0) {
+        if (m == 0) u = s;
+        else { int sh = 0; while (!(m & 1024)) { m <<= 1; sh++; } m &= 1023; u = s | ((uint32_t)(113 - sh) << 23) | (m << 13); }
+    } else if (e == 31) u = s | 0x7F800000u | (m << 13);
+    else u = s | ((e + 112) << 23) | (m << 13);
+    float f; memcpy(&f, &u, 4); return f;
+}
+/* f32 -> f16 round-to-nearest-even (used only by the synthetic generator) */
+static uint16_t f2h(float f) {
+    uint32_t u; memcpy(&u, &f, 4);
+    uint32_t s = (u >> 16) & 0x8000u; int32_t e = (int32_t)((u >> 23) & 255) - 127 + 15; uint32_t m = u & 0x7FFFFFu;
+    if (((u >> 23) & 255) == 255) return (uint16_t)(s | 0x7C00u | (m ? 0x200u : 0));
+    if (e >= 31) return (uint16_t)(s | 0x7C00u);
+    if (e <= 0) {
+        if (e < -10) return (uint16_t)s;
+        m |= 0x800000u; int sh = 14 - e; uint32_t r = m >> sh, rem = m & ((1u << sh) - 1), half = 1u << (sh - 1);
+        if (rem > half || (rem == half && (r & 1))) r++;
+        return (uint16_t)(s | r);
+    }
+    uint32_t r = ((uint32_t)e << 10) | (m >> 13), rem = m & 0x1FFFu;
+    if (rem > 0x1000u || (rem == 0x1000u && (r & 1))) r++;
+    return (uint16_t)(s | r);
+}
+static inline uint16_t rd16(const uint8_t* p) { return (uint16_t)(p[0] | (p[1] << 8)); }
+
+static inline float sigm(float x) { return 1.0f / (1.0f + expf(-x)); }            /* qwen4exp_gguf.rs:457 */
+static inline float silu(float x) { return x * sigm(x); }                          /* :458 */
+static inline float softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }  /* :459 */
+
+/* rms :209 -- y = x * s * w ; rms_inplace :210 -- x *= s * w */
+static void rms(const float* x, const float* w, float eps, float* y, int n) {
+    float ss = 0.0f; for (int i = 0; i < n; i++) ss += x[i] * x[i];
+    float s = 1.0f / sqrtf(ss / (float)n + eps);
+    for (int i = 0; i < n; i++) y[i] = x[i] * s * w[i];
+}
+static void rms_inplace(float* x, const float* w, float eps, int n) {
+    float ss = 0.0f; for (int i = 0; i < n; i++) ss += x[i] * x[i];
+    float s = 1.0f / sqrtf(ss / (float)n + eps);
+    for (int i = 0; i < n; i++) x[i] *= s * w[i];
+}
+
+int orc_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+/* ------------------------------------------------------------------ block formats */
+
+int orc_type_geom(int type, int* el, int* by) {  /* gguf_q.rs:33-41 */
+    int e, b;
+    switch (type) {
+        case ORC_F32: e = 1; b = 4; break;
+        case ORC_F16: case ORC_BF16: e = 1; b = 2; break;
+        case ORC_Q8_0: e = 32; b = 34; break;
+        case ORC_Q4_K: e = 256; b = 144; break;
+        case ORC_IQ2_XS: e = 256; b = 74; break;
+        case ORC_IQ3_S: e = 256; b = 110; break;
+        default: return -1;
+    }
+    if (el) *el = e;
+    if (by) *by = b;
+    return 0;
+}
+int64_t orc_row_bytes(int type, int64_t cols) { int e, b; if (orc_type_geom(type, &e, &b)) return -1; return cols / e * b; }
+
+static void scale_min_k4(int j, const uint8_t* q, uint8_t* d, uint8_t* m) {  /* gguf_q.rs:62-64 */
+    if (j < 4) { *d = q[j] & 63; *m = q[j + 4] & 63; }
+    else { *d = (uint8_t)((q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4)); *m = (uint8_t)((q[j + 4] >> 4) | ((q[j] >> 6) << 4)); }
+}
+
+/* put8, gguf_q.rs:58: y[j] = d * g[j] * s[j], evaluated left to right */
+static inline void put8(float* y, float d, const uint8_t* g, uint8_t signs) {
+    for (int j = 0; j < 8; j++) { float s = (signs >> j) & 1 ? -1.0f : 1.0f; float t = d * (float)g[j]; y[j] = t * s; }
+}
+
+int orc_dequant(int type, const uint8_t* x, int64_t n, float* y) {  /* gguf_q.rs:67-166 */
+    int qk, bs; if (orc_type_geom(type, &qk, &bs)) return -1;
+    int64_t nb = n / qk;
+    switch (type) {
+    case ORC_F32: memcpy(y, x, (size_t)n * 4); break;                                         /* :71 */
+    case ORC_F16: for (int64_t i = 0; i < n; i++) y[i] = h2f(rd16(x + 2 * i)); break;          /* :72 */
+    case ORC_BF16: for (int64_t i = 0; i < n; i++) { uint32_t u = (uint32_t)rd16(x + 2 * i) << 16; memcpy(&y[i], &u, 4); } break;  /* :73 */
+    case ORC_Q8_0:                                                                             /* :79 */
+        for (int64_t i = 0; i < nb; i++) { const uint8_t* b = x + i * bs; float d = h2f(rd16(b));
+            for (int j = 0; j < 32; j++) y[i * 32 + j] = (float)(int8_t)b[2 + j] * d; }
+        break;
+    case ORC_Q4_K:                                                                             /* :103-107 */
+        for (int64_t i = 0; i < nb; i++) {
+            const uint8_t* b = x + i * bs; float d = h2f(rd16(b)), mn = h2f(rd16(b + 2)); const uint8_t* sc = b + 4; const uint8_t* q = b + 16; float* yy = y + i * 256;
+            for (int j = 0; j < 4; j++) {
+                uint8_t s1, m1, s2, m2; scale_min_k4(2 * j, sc, &s1, &m1); scale_min_k4(2 * j + 1, sc, &s2, &m2);
+                float d1 = d * (float)s1, mm1 = mn * (float)m1, d2 = d * (float)s2, mm2 = mn * (float)m2;
+                for (int l = 0; l < 32; l++) { yy[l] = d1 * (float)(q[l] & 0xF) - mm1; yy[l + 32] = d2 * (float)(q[l] >> 4) - mm2; }
+                yy += 64; q += 32;
+            }
+        }
+        break;
+    case ORC_IQ2_XS:                                                                           /* :126-129 */
+        for (int64_t i = 0; i < nb; i++) {
+            const uint8_t* b = x + i * bs; float d = h2f(rd16(b)); const uint8_t* qs = b + 2; const uint8_t* sc = b + 66; float* yy = y + i * 256;
+            for (int ib = 0; ib < 8; ib++) {
+                float db[2]; db[0] = d * (0.5f + (float)(sc[ib] & 0xF)) * 0.25f; db[1] = d * (0.5f + (float)(sc[ib] >> 4)) * 0.25f;
+                for (int l = 0; l < 4; l++) {
+                    uint16_t q = rd16(qs + 2 * (4 * ib + l));
+                    uint64_t g = PB_IQ2XS_GRID[q & 511]; uint8_t gb[8]; for (int j = 0; j < 8; j++) gb[j] = (uint8_t)(g >> (8 * j));
+                    put8(yy, db[l / 2], gb, PB_KSIGNS_IQ2XS[q >> 9]); yy += 8;
+                }
+            }
+        }
+        break;
+    case ORC_IQ3_S:                                                                            /* :141-151 */
+        for (int64_t i = 0; i < nb; i++) {
+            const uint8_t* b = x + i * bs; float d = h2f(rd16(b)); const uint8_t* qs = b + 2; const uint8_t* qh = b + 66; const uint8_t* signs = b + 74; const uint8_t* sc = b + 106; float* yy = y + i * 256;
+            for (int ib = 0; ib < 8; ib += 2) {
+                for (int half = 0; half < 2; half++) {
+                    uint8_t s = sc[ib / 2]; float db = d * (float)(1 + 2 * (half == 0 ? (s & 0xF) : (s >> 4)));
+                    for (int l = 0; l < 4; l++) {
+                        uint32_t g1 = PB_IQ3S_GRID[qs[2 * l] | (((uint32_t)qh[half] << (8 - 2 * l)) & 256)];
+                        uint32_t g2 = PB_IQ3S_GRID[qs[2 * l + 1] | (((uint32_t)qh[half] << (7 - 2 * l)) & 256)];
+                        uint8_t gb[8]; for (int j = 0; j < 4; j++) { gb[j] = (uint8_t)(g1 >> (8 * j)); gb[4 + j] = (uint8_t)(g2 >> (8 * j)); }
+                        put8(yy, db, gb, signs[l]); yy += 8;
+                    }
+                    qs += 8; signs += 4;
+                }
+                qh += 2;
+            }
+        }
+        break;
+    default: return -1;
+    }
+    return 0;
+}
+
+/* dot_avx2, gguf_q.rs:176-197: four 8-lane FMA accumulators over 32-element strides, an
+ * 8-element tail on accumulator 0, (s0+s1)+(s2+s3) per lane, lanes summed in order, scalar tail. */
+float orc_dot(const float* a, const float* b, int64_t n) {
+    float s[4][8]; memset(s, 0, sizeof s);
+    int64_t i = 0;
+    for (; i + 32 <= n; i += 32)
+        for (int k = 0; k < 4; k++) for (int l = 0; l < 8; l++) s[k][l] = fmaf(a[i + 8 * k + l], b[i + 8 * k + l], s[k][l]);
+    for (; i + 8 <= n; i += 8) for (int l = 0; l < 8; l++) s[0][l] = fmaf(a[i + l], b[i + l], s[0][l]);
+    float r = 0.0f;
+    for (int l = 0; l < 8; l++) r += (s[0][l] + s[1][l]) + (s[2][l] + s[3][l]);
+    for (; i < n; i++) r += a[i] * b[i];
+    return r;
+}
+
+/* ------------------------------------------------------------------ seeded synthetic tensors
+ *
+ * Specification (mirrored by the CUDA generator; both must produce identical bytes):
+ *   sm64(x)      = splitmix64 finaliser of x + 0x9E3779B97F4A7C15
+ *   tkey         = sm64(sm64(seed) ^ tid)
+ *   bkey(b)      = sm64(tkey ^ (b * 0xD1342543DE82EF95))         b = global block (or element) index
+ *   word(b, j)   = sm64(bkey(b) + j)
+ *   normal(w0..w2) = (sum of the twelve 16-bit fields of three words - 393210) / 65536   (Irwin-Hall, ~N(0,1))
+ *   scale        = f16_rne(|normal| * 0.02f)
+ * Q8_0 : d = scale(words 0-2); q[j] = (byte j of words 3-6) % 255 - 127
+ * Q4_K : d = scale(0-2), dmin = scale(3-5), 140 payload bytes = words 6..
+ * IQ2_XS: d = scale(0-2), 72 payload bytes = words 3..   IQ3_S: d = scale(0-2), 108 payload bytes = words 3..
+ * F32  : element i = normal(words 0-2 of bkey(i)) * sigma      (orc_synth_normal)
+ * All payload fields of the k-/i-quants are uniform bit fields, so uniform bytes give uniform
+ * sub-scales, grid indices and signs.
+ */
+static inline uint64_t sm64(uint64_t x) {
+    x += 0x9E3779B97F4A7C15ull; x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull; x = (x ^ (x >> 27)) * 0x94D049BB133111EBull; return x ^ (x >> 31);
+}
+static inline uint64_t synth_tkey(uint64_t seed, uint64_t tid) { return sm64(sm64(seed) ^ tid); }
+static inline uint64_t synth_bkey(uint64_t tkey, uint64_t b) { return sm64(tkey ^ (b * 0xD1342543DE82EF95ull)); }
+static inline float synth_normal(uint64_t bkey, int j0) {
+    int32_t s = 0;
+    for (int j = 0; j < 3; j++) { uint64_t w = sm64(bkey + (uint64_t)(j0 + j)); s += (int32_t)(w & 0xFFFF) + (int32_t)((w >> 16) & 0xFFFF) + (int32_t)((w >> 32) & 0xFFFF) + (int32_t)(w >> 48); }
+    return (float)(s - 393210) * (1.0f / 65536.0f);
+}
+static inline uint16_t synth_scale(uint64_t bkey, int j0) { return f2h(fabsf(synth_normal(bkey, j0)) * 0.02f); }
+static void synth_payload(uint64_t bkey, int j0, uint8_t* out, int nbytes) {
+    for (int o = 0; o < nbytes; o += 8) { uint64_t w = sm64(bkey + (uint64_t)(j0 + o / 8)); for (int k = 0; k < 8 && o + k < nbytes; k++) out[o + k] = (uint8_t)(w >> (8 * k)); }
+}
+static void synth_block(int type, uint64_t tkey, uint64_t b, uint8_t* out) {
+    uint64_t k = synth_bkey(tkey, b);
+    uint16_t d = synth_scale(k, 0); out[0] = (uint8_t)d; out[1] = (uint8_t)(d >> 8);
+    switch (type) {
+    case ORC_Q8_0: { uint8_t raw[32]; synth_payload(k, 3, raw, 32); for (int j = 0; j < 32; j++) out[2 + j] = (uint8_t)(int8_t)((int)(raw[j] % 255) - 127); } break;
+    case ORC_Q4_K: { uint16_t m = synth_scale(k, 3); out[2] = (uint8_t)m; out[3] = (uint8_t)(m >> 8); synth_payload(k, 6, out + 4, 140); } break;
+    case ORC_IQ2_XS: synth_payload(k, 3, out + 2, 72); break;
+    case ORC_IQ3_S: synth_payload(k, 3, out + 2, 108); break;
+    }
+}
+void orc_synth_rows(int type, uint64_t seed, uint64_t tid, int64_t cols, int64_t r0, int64_t nrows, uint8_t* out) {
+    int el, bs; if (orc_type_geom(type, &el, &bs)) return;
+    uint64_t tkey = synth_tkey(seed, tid); int64_t bpr = cols / el;
+    if (type == ORC_F32) { orc_synth_normal(seed, tid, r0 * cols, nrows * cols, 0.02f, (float*)out); return; }
+    #pragma omp parallel for schedule(static) if (nrows * bpr > 4096)
+    for (int64_t i = 0; i < nrows * bpr; i++) synth_block(type, tkey, (uint64_t)(r0 * bpr + i), out + i * bs);
+}
+void orc_synth_normal(uint64_t seed, uint64_t tid, int64_t i0, int64_t n, float sigma, float* out) {
+    uint64_t tkey = synth_tkey(seed, tid);
+    #pragma omp parallel for schedule(static) if (n > 65536)
+    for (int64_t i = 0; i < n; i++) out[i] = synth_normal(synth_bkey(tkey, (uint64_t)(i0 + i)), 0) * sigma;
+}
+
+/* ------------------------------------------------------------------ QMat */
+
+void orc_mat_row_raw(const orc_mat* m, int64_t r, uint8_t* out) {
+    int64_t rb = orc_row_bytes(m->type, m->cols);
+    if (m->data) memcpy(out, m->data + r * rb, (size_t)rb);
+    else orc_synth_rows(m->type, m->seed, m->tid, m->cols, r, 1, out);
+}
+void orc_mat_row(const orc_mat* m, int64_t r, float* y) {  /* QMat::row :210 */
+    int64_t rb = orc_row_bytes(m->type, m->cols);
+    if (m->data) { orc_dequant(m->type, m->data + r * rb, m->cols, y); return; }
+    uint8_t stackbuf[4096]; uint8_t* raw = rb <= (int64_t)sizeof stackbuf ? stackbuf : (uint8_t*)malloc((size_t)rb);
+    orc_synth_rows(m->type, m->seed, m->tid, m->cols, r, 1, raw);
+    orc_dequant(m->type, raw, m->cols, y);
+    if (raw != stackbuf) free(raw);
+}
+/* QMat::matmul :217-242, the t < 16 branch (row dequantized once, dotted against every token);
+ * rows are split over threads like the rayon chunks; every output element is produced by one
+ * thread so the result does not depend on the thread count.  The t >= 16 branch of the
+ * reference uses a blocked SGEMM whose summation order is not reproduced here. */
+void orc_matmul(const orc_mat* m, const float* x, int t, float* y) {
+    int64_t rows = m->rows, cols = m->cols;
+    #pragma omp parallel
+    {
+        float* buf = (float*)malloc((size_t)cols * 4);
+        #pragma omp for schedule(static)
+        for (int64_t r = 0; r < rows; r++) { orc_mat_row(m, r, buf); for (int ti = 0; ti < t; ti++) y[(int64_t)ti * rows + r] = orc_dot(buf, x + (int64_t)ti * cols, cols); }
+        free(buf);
+    }
+}
+/* ------------------------------------------------------------------ router / sampler / kv4 / rope */
+
+/* top_k qwen4exp_gguf.rs:3132-3139: the k largest raw logits, weights = softmax over them
+ * (max-subtracted).  The reference selects with select_nth_unstable_by, whose order inside
+ * the selection is unspecified; the canonical order here is descending logit, ties to the
+ * lower index, and the softmax denominator is summed in that order.  NaN logits are treated
+ * as -inf (nan_clean :3121-3125); if the best selected logit is not finite the weights are uniform
+ * (soft_top :3128). */
+void orc_top_k(const float* r, int n, int k, int32_t* idx, float* w) {
+    char* used = (char*)calloc((size_t)n, 1);
+    for (int j = 0; j < k; j++) {
+        int best = -1; float bv = 0;
+        for (int i = 0; i < n; i++) { if (used[i]) continue; float v = isnan(r[i]) ? -INFINITY : r[i]; if (best < 0 || v > bv) { best = i; bv = v; } }
+        used[best] = 1; idx[j] = best; w[j] = bv;
+    }
+    free(used);
+    float mx = -INFINITY; for (int j = 0; j < k; j++) mx = fmaxf(mx, w[j]);
+    if (!isfinite(mx)) { for (int j = 0; j < k; j++) w[j] = 1.0f / (float)(k > 0 ? k : 1); return; }
+    float sum = 0.0f; for (int j = 0; j < k; j++) { w[j] = expf(w[j] - mx); sum += w[j]; }
+    for (int j = 0; j < k; j++) w[j] = w[j] / sum;
+}
+
+uint32_t orc_argmax(const float* v, int64_t n) {  /* sampler.rs:142-148 */
+    int64_t best = 0; for (int64_t i = 1; i < n; i++) if (v[i] > v[best]) best = i; return (uint32_t)best;
+}
+
+void orc_kv4_pack(const float* x, int64_t n, uint32_t* w, float* sc) {  /* kv4.rs:12-32 */
+    for (int64_t b = 0; b < n / 32; b++) {
+        const float* p = x + b * 32; float m = 0.0f; for (int j = 0; j < 32; j++) m = fmaxf(m, fabsf(p[j]));
+        float s = (m > 0.0f && isfinite(m)) ? m / 7.0f : 0.0f; sc[b] = s;
+        for (int c = 0; c < 4; c++) { uint32_t u = 0;
+            for (int j = 0; j < 8; j++) { int q = 0; if (s > 0.0f) { float v = roundf(p[c * 8 + j] / s); v = v < -7.0f ? -7.0f : (v > 7.0f ? 7.0f : v); q = (int)v; }
+                u |= ((uint32_t)(uint8_t)(int8_t)q & 0xF) << (4 * j); }
+            w[b * 4 + c] = u; }
+    }
+}
+float orc_kv4_get(const uint32_t* w, const float* sc, int64_t i) {  /* kv4.rs:35-40 */
+    uint32_t nib = (w[i / 8] >> (4 * (i % 8))) & 0xF; int q = (int)nib - (nib >= 8 ? 16 : 0); return (float)q * sc[i / 32];
+}
+void orc_rope_inv(int n_rot, float base, float* inv) {  /* qn_ctx.rs:168 */
+    for (int i = 0; i < n_rot / 2; i++) inv[i] = powf(base, -(2.0f * (float)i) / (float)n_rot);
+}
+/* rope :1436-1439 with rope_cs :529-533 (mscale 1) */
+static void rope(float* v, int64_t pos, const float* inv, int n_rot) {
+    int half = n_rot / 2;
+    for (int i = 0; i < half; i++) { float a = (float)pos * inv[i]; float s = sinf(a), co = cosf(a); float x0 = v[i], x1 = v[i + half]; v[i] = x0 * co - x1 * s; v[i + half] = x1 * co + x0 * s; }
+}
+
+/* ------------------------------------------------------------------ MoE block */
+
+/* expert e of a fused [n_exp*rows_per][cols] tensor: QMat::slice_rows(e*rows_per, rows_per) :1756,1786 */
+static void expert_row(const orc_mat* m, int64_t e, int64_t rows_per, int64_t r, float* y) { orc_mat_row(m, e * rows_per + r, y); }
+
+void orc_moe(const orc_cfg* c, const orc_mat* router, const orc_mat* gate_e, const orc_mat* up_e, const orc_mat* down_e,
+             const orc_mat* sh_gate, const orc_mat* sh_up, const orc_mat* sh_down, const float* sh_gate_inp,
+             const float* x, int t, float* y, int32_t* sel, float* selw) {
+    int d = c->d, ff = c->ff_exp, sf = (int)sh_gate->rows, ne = c->n_exp, k = c->top_k;
+    /* ffn :1675-1684 */
+    float* lg = (float*)malloc((size_t)t * ne * 4); float* g = (float*)malloc((size_t)t * sf * 4); float* u = (float*)malloc((size_t)t * sf * 4);
+    orc_matmul(router, x, t, lg); orc_matmul(sh_gate, x, t, g); orc_matmul(sh_up, x, t, u);
+    for (int64_t i = 0; i < (int64_t)t * sf; i++) g[i] = silu(g[i]) * u[i];
+    orc_matmul(sh_down, g, t, y);
+    /* routed :1723 shared gate */
+    for (int ti = 0; ti < t; ti++) { float sg = sigm(orc_dot(sh_gate_inp, x + (int64_t)ti * d, d)); for (int i = 0; i < d; i++) y[(int64_t)ti * d + i] *= sg; }
+    /* routing :1725-1731 */
+    int32_t* ids = (int32_t*)malloc((size_t)t * k * 4); float* ws = (float*)malloc((size_t)t * k * 4);
+    for (int ti = 0; ti < t; ti++) orc_top_k(lg + (int64_t)ti * ne, ne, k, ids + ti * k, ws + ti * k);
+    if (sel) memcpy(sel, ids, (size_t)t * k * 4);
+    if (selw) memcpy(selw, ws, (size_t)t * k * 4);
+    /* f32 branch :1769-1793: per (expert, token) hidden = silu(gate.x) * (up.x); the down projections
+     * accumulate w * (down_row . hidden) into o over experts in ascending expert id, then y += o. */
+    float* o = (float*)calloc((size_t)t * d, 4);
+    float* hid = (float*)malloc((size_t)t * ff * 4);
+    for (int e = 0; e < ne; e++) {
+        int nt = 0; int toks[1024]; float tw[1024];
+        for (int ti = 0; ti < t && nt < 1024; ti++) for (int j = 0; j < k; j++) if (ids[ti * k + j] == e) { toks[nt] = ti; tw[nt] = ws[ti * k + j]; nt++; }
+        if (!nt) continue;
+        #pragma omp parallel
+        {
+            float* buf = (float*)malloc((size_t)(d > ff ? d : ff) * 4); float* gv = (float*)malloc((size_t)nt * 4);
+            #pragma omp for schedule(static)
+            for (int r = 0; r < ff; r++) {
+                expert_row(gate_e, e, ff, r, buf); for (int j = 0; j < nt; j++) gv[j] = orc_dot(buf, x + (int64_t)toks[j] * d, d);
+                expert_row(up_e, e, ff, r, buf); for (int j = 0; j < nt; j++) hid[(int64_t)j * ff + r] = silu(gv[j]) * orc_dot(buf, x + (int64_t)toks[j] * d, d);
+            }
+            #pragma omp for schedule(static)
+            for (int r = 0; r < d; r++) { expert_row(down_e, e, d, r, buf); for (int j = 0; j < nt; j++) o[(int64_t)toks[j] * d + r] += tw[j] * orc_dot(buf, hid + (int64_t)j * ff, ff); }
+            free(buf); free(gv);
+        }
+    }
+    for (int64_t i = 0; i < (int64_t)t * d; i++) y[i] += o[i];
+    free(o); free(hid); free(ids); free(ws); free(lg); free(g); free(u);
+}
+
+/* ------------------------------------------------------------------ Gated DeltaNet */
+
+void orc_linear_core(const orc_cfg* c, const float* m, const float* zz, const float* bb, const float* aa,
+                     const float* a, const float* dt, const float* conv, const float* norm,
+                     float* cs, float* s, int t, float* o_all) {  /* linear_core :1624-1673 */
+    int nk = c->lin_nk, nv = c->lin_nv, dk = c->lin_dk, dv = c->lin_dv, kk = c->conv_k; int ch = 2 * nk * dk + nv * dv; int w = nv * dv;
+    float* co_all = (float*)malloc((size_t)t * ch * 4);
+    /* 1) causal depthwise conv + SiLU, state shifts (:1643-1647) */
+    for (int ti = 0; ti < t; ti++) {
+        const float* cur = m + (int64_t)ti * ch; float* co = co_all + (int64_t)ti * ch;
+        for (int cc = 0; cc < ch; cc++) { float o = conv[cc * kk + kk - 1] * cur[cc]; for (int k = 0; k < kk - 1; k++) o += conv[cc * kk + k] * cs[k * ch + cc]; co[cc] = silu(o); }
+        memmove(cs, cs + ch, (size_t)(kk - 2) * ch * 4); memcpy(cs + (kk - 2) * ch, cur, (size_t)ch * 4);
+    }
+    /* 2) L2-normalise q (scaled by 1/sqrt(dk)) and k per head (:1649-1651) */
+    for (int ti = 0; ti < t; ti++) { float* co = co_all + (int64_t)ti * ch;
+        for (int h = 0; h < nk; h++) for (int which = 0; which < 2; which++) {
+            float* buf = co + which * nk * dk + h * dk; float sc = which == 0 ? 1.0f / sqrtf((float)dk) : 1.0f;
+            float ss = 0.0f; for (int i = 0; i < dk; i++) ss += buf[i] * buf[i];
+            float n = 1.0f / sqrtf(ss + 1e-6f) * sc; for (int i = 0; i < dk; i++) buf[i] *= n; } }
+    /* 3) delta-rule recurrence per V head (:1654-1669) */
+    #pragma omp parallel for schedule(static)
+    for (int h = 0; h < nv; h++) {
+        float* sh = s + (int64_t)h * dk * dv; int kh = h % nk; float mem[1024], delta[1024];
+        for (int ti = 0; ti < t; ti++) {
+            const float* co = co_all + (int64_t)ti * ch; const float* qv = co + kh * dk; const float* kv = co + nk * dk + kh * dk; const float* vv = co + 2 * nk * dk + h * dv;
+            float g = expf(softplus(aa[ti * nv + h] + dt[h]) * a[h]); float b = sigm(bb[ti * nv + h]);
+            for (int i = 0; i < dk * dv; i++) sh[i] *= g;
+            for (int j = 0; j < dv; j++) mem[j] = 0.0f;
+            for (int i = 0; i < dk; i++) { float ki = kv[i]; const float* row = sh + i * dv; for (int j = 0; j < dv; j++) mem[j] += row[j] * ki; }
+            for (int j = 0; j < dv; j++) delta[j] = (vv[j] - mem[j]) * b;
+            float* oh = o_all + (int64_t)ti * w + h * dv; for (int j = 0; j < dv; j++) oh[j] = 0.0f;
+            for (int i = 0; i < dk; i++) { float ki = kv[i], qi = qv[i]; float* row = sh + i * dv; for (int j = 0; j < dv; j++) { row[j] += ki * delta[j]; oh[j] += row[j] * qi; } }
+            rms_inplace(oh, norm, c->eps, dv); const float* zh = zz + (int64_t)ti * w + h * dv; for (int j = 0; j < dv; j++) oh[j] *= sigm(zh[j]);
+        }
+    }
+    free(co_all);
+}
+
+/* ------------------------------------------------------------------ gated attention */
+
+void orc_attn_core(const orc_cfg* c, const float* qf, const float* kf_in, const float* vf,
+                   const float* qn, const float* kn, const float* inv,
+                   float* kc, float* vc, int64_t pos,
+                   const uint32_t* kw, const float* ks, const uint32_t* vw, const float* vs, int64_t q4n,
+                   float* att) {  /* attn_core :1558-1615, dense branch, one token */
+    int nh = c->n_head, nkv = c->n_kv, hd = c->hd; int row = nkv * hd; int grp = nh / nkv;
+    /* k: RMSNorm * kn, rope, append (:1563-1564) */
+    float* kf = kc + pos * row; memcpy(kf, kf_in, (size_t)row * 4);
+    for (int h = 0; h < nkv; h++) { rms_inplace(kf + h * hd, kn, c->eps, hd); rope(kf + h * hd, pos, inv, c->n_rot); }
+    memcpy(vc + pos * row, vf, (size_t)row * 4);
+    float scale = 1.0f / sqrtf((float)hd); int64_t n = pos + 1;
+    #pragma omp parallel for schedule(static)
+    for (int h = 0; h < nh; h++) {
+        float* out = att + h * hd; for (int i = 0; i < hd; i++) out[i] = 0.0f;
+        int base = h * 2 * hd; float qh[1024]; memcpy(qh, qf + base, (size_t)hd * 4); rms_inplace(qh, qn, c->eps, hd); rope(qh, pos, inv, c->n_rot);  /* :1603-1604 */
+        int kvh = h / grp; float* sc = (float*)malloc((size_t)n * 4); float krow[1024];
+        for (int64_t p = 0; p < n; p++) {
+            const float* kp;
+            if (kw && p < q4n) { for (int i = 0; i < hd; i++) krow[i] = orc_kv4_get(kw, ks, p * row + kvh * hd + i); kp = krow; } else kp = kc + p * row + kvh * hd;
+            sc[p] = orc_dot(qh, kp, hd) * scale;
+        }
+        float mx = -INFINITY; for (int64_t p = 0; p < n; p++) mx = fmaxf(mx, sc[p]);
+        float sum = 0.0f; for (int64_t p = 0; p < n; p++) { sc[p] = expf(sc[p] - mx); sum += sc[p]; }
+        float invs = 1.0f / sum;
+        for (int64_t p = 0; p < n; p++) { float wgt = sc[p] * invs;
+            if (vw && p < q4n) { for (int i = 0; i < hd; i++) out[i] += wgt * orc_kv4_get(vw, vs, p * row + kvh * hd + i); }
+            else { const float* vv = vc + p * row + kvh * hd; for (int i = 0; i < hd; i++) out[i] += wgt * vv[i]; } }
+        const float* gate = qf + base + hd; for (int i = 0; i < hd; i++) out[i] *= sigm(gate[i]);  /* :1610 */
+        free(sc);
+    }
+}
+
+/* ------------------------------------------------------------------ model / token loop */
+
+typedef struct { orc_mat mat; int has_mat; float* vec; int64_t nvec; } orc_slot;
+
+struct orc_model {
+    orc_cfg cfg;
+    orc_slot* slots;   /* [(n_layers + 1)][ORC_R_COUNT], index 0 = global */
+    float* rope_inv;
+};
+struct orc_state {
+    const orc_model* m;
+    int64_t pos;
+    float** conv; float** ssm;           /* per linear layer */
+    float** k; float** v;                /* per attention layer, f32 [max_ctx][row] (rows < q4n are stale) */
+    uint32_t** kw; float** ks; uint32_t** vw; float** vs; int64_t* q4n;
+    int n_lin, n_attn;
+    float logit_margin, router_margin;
+};
+
+static orc_slot* slot(const orc_model* m, int layer, int role) { return &m->slots[(size_t)(layer + 1) * ORC_R_COUNT + role]; }
+static const orc_mat* M(const orc_model* m, int layer, int role) { orc_slot* s = slot(m, layer, role); return s->has_mat ? &s->mat : NULL; }
+static const float* V(const orc_model* m, int layer, int role) { return slot(m, layer, role)->vec; }
+static int is_full(const orc_cfg* c, int il) { return c->full_every > 0 && (il + 1) % c->full_every == 0; }  /* :498 */
+
+orc_model* orc_model_new(const orc_cfg* cfg) {
+    orc_model* m = (orc_model*)calloc(1, sizeof *m); m->cfg = *cfg;
+    m->slots = (orc_slot*)calloc((size_t)(cfg->n_layers + 1) * ORC_R_COUNT, sizeof(orc_slot));
+    m->rope_inv = (float*)malloc((size_t)(cfg->n_rot / 2 + 1) * 4); orc_rope_inv(cfg->n_rot, cfg->rope_base, m->rope_inv);
+    return m;
+}
+void orc_model_free(orc_model* m) {
+    if (!m) return;
+    for (size_t i = 0; i < (size_t)(m->cfg.n_layers + 1) * ORC_R_COUNT; i++) free(m->slots[i].vec);
+    free(m->slots); free(m->rope_inv); free(m);
+}
+int orc_model_set_mat(orc_model* m, int layer, int role, const orc_mat* mat) {
+    if (layer < -1 || layer >= m->cfg.n_layers || role < 0 || role >= ORC_R_COUNT) return -1;
+    orc_slot* s = slot(m, layer, role); s->mat = *mat; s->has_mat = 1; return 0;
+}
+int orc_model_set_vec(orc_model* m, int layer, int role, const float* v, int64_t n) {
+    if (layer < -1 || layer >= m->cfg.n_layers || role < 0 || role >= ORC_R_COUNT) return -1;
+    orc_slot* s = slot(m, layer, role); free(s->vec); s->vec = (float*)malloc((size_t)n * 4); memcpy(s->vec, v, (size_t)n * 4); s->nvec = n; return 0;
+}
+
+orc_state* orc_state_new(const orc_model* m) {  /* new_state :1345-1353 */
+    const orc_cfg* c = &m->cfg; orc_state* s = (orc_state*)calloc(1, sizeof *s); s->m = m;
+    int ch = 2 * c->lin_nk * c->lin_dk + c->lin_nv * c->lin_dv; int row = c->n_kv * c->hd;
+    for (int il = 0; il < c->n_layers; il++) { if (is_full(c, il)) s->n_attn++; else s->n_lin++; }
+    s->conv = (float**)calloc((size_t)s->n_lin + 1, sizeof(float*)); s->ssm = (float**)calloc((size_t)s->n_lin + 1, sizeof(float*));
+    for (int i = 0; i < s->n_lin; i++) { s->conv[i] = (float*)calloc((size_t)(c->conv_k - 1) * ch, 4); s->ssm[i] = (float*)calloc((size_t)c->lin_nv * c->lin_dk * c->lin_dv, 4); }
+    int na = s->n_attn + 1;
+    s->k = (float**)calloc((size_t)na, sizeof(float*)); s->v = (float**)calloc((size_t)na, sizeof(float*));
+    s->kw = (uint32_t**)calloc((size_t)na, sizeof(void*)); s->vw = (uint32_t**)calloc((size_t)na, sizeof(void*));
+    s->ks = (float**)calloc((size_t)na, sizeof(void*)); s->vs = (float**)calloc((size_t)na, sizeof(void*)); s->q4n = (int64_t*)calloc((size_t)na, 8);
+    for (int i = 0; i < s->n_attn; i++) {
+        s->k[i] = (float*)calloc((size_t)c->max_ctx * row, 4); s->v[i] = (float*)calloc((size_t)c->max_ctx * row, 4);
+        if (c->kv_bits == 4) { s->kw[i] = (uint32_t*)calloc((size_t)c->max_ctx * row / 8, 4); s->vw[i] = (uint32_t*)calloc((size_t)c->max_ctx * row / 8, 4);
+            s->ks[i] = (float*)calloc((size_t)c->max_ctx * row / 32, 4); s->vs[i] = (float*)calloc((size_t)c->max_ctx * row / 32, 4); }
+    }
+    return s;
+}
+void orc_state_free(orc_state* s) {
+    if (!s) return;
+    for (int i = 0; i < s->n_lin; i++) { free(s->conv[i]); free(s->ssm[i]); }
+    for (int i = 0; i < s->n_attn; i++) { free(s->k[i]); free(s->v[i]); free(s->kw[i]); free(s->vw[i]); free(s->ks[i]); free(s->vs[i]); }
+    free(s->conv); free(s->ssm); free(s->k); free(s->v); free(s->kw); free(s->vw); free(s->ks); free(s->vs); free(s->q4n); free(s);
+}
+/* Layout rule of the packed region (kv_push :1517-1534): with len positions held, the first
+ * q4n = ((len - recent) / 64) * 64 are 4-bit (whole multiples of 64 positions), the rest f32. */
+static void kv_repack(orc_state* s, int ai, int64_t len) {
+    const orc_cfg* c = &s->m->cfg; if (c->kv_bits != 4 || len <= c->kv_recent) return;
+    int row = c->n_kv * c->hd; int64_t want = ((len - c->kv_recent) / 64) * 64;
+    if (want <= s->q4n[ai]) return;
+    int64_t a = s->q4n[ai], n = (want - a) * row;
+    orc_kv4_pack(s->k[ai] + a * row, n, s->kw[ai] + a * row / 8, s->ks[ai] + a * row / 32);
+    orc_kv4_pack(s->v[ai] + a * row, n, s->vw[ai] + a * row / 8, s->vs[ai] + a * row / 32);
+    s->q4n[ai] = want;
+}
+int orc_state_fill_kv(orc_state* s, int ai, const float* k, const float* v, int64_t n) {
+    const orc_cfg* c = &s->m->cfg; int row = c->n_kv * c->hd; if (ai < 0 || ai >= s->n_attn || n > c->max_ctx) return -1;
+    memcpy(s->k[ai], k, (size_t)n * row * 4); memcpy(s->v[ai], v, (size_t)n * row * 4); s->q4n[ai] = 0; kv_repack(s, ai, n); return 0;
+}
+int orc_state_set_pos(orc_state* s, int64_t pos) { s->pos = pos; return 0; }
+void orc_last_margins(const orc_state* s, float* a, float* b) { if (a) *a = s->logit_margin; if (b) *b = s->router_margin; }
+
+/* hc_mix :1357-1382 (f32 branch).  x [t][hc*d] -> mixed [t][d], inj [t][hc] */
+static void hc_mix(const orc_model* m, int layer, int r_norm, int r_down, int r_up, int r_inj, const float* x, int t, float* mixed, float* inj) {
+    const orc_cfg* c = &m->cfg; int d = c->d, hc = c->hc, w = hc * d, lr = c->hc_lr;
+    const float* norm = V(m, layer, r_norm); const orc_mat* down = M(m, layer, r_down); const orc_mat* up = M(m, layer, r_up); const orc_mat* injm = r_inj >= 0 ? M(m, layer, r_inj) : NULL;
+    float* xn = (float*)malloc((size_t)t * w * 4); float* lo = (float*)malloc((size_t)t * lr * 4); float* gate = (float*)malloc((size_t)t * w * 4);
+    for (int i = 0; i < t * hc; i++) { int s = i % hc; rms(x + (int64_t)i * d, norm + s * d, c->eps, xn + (int64_t)i * d, d); }
+    orc_matmul(down, xn, t, lo); for (int i = 0; i < t * lr; i++) lo[i] = silu(lo[i] / (float)hc);
+    if (injm) { orc_matmul(injm, xn, t, inj); for (int i = 0; i < t * hc; i++) inj[i] /= (float)hc; } else for (int i = 0; i < t * hc; i++) inj[i] = 0.0f;
+    orc_matmul(up, lo, t, gate);
+    for (int ti = 0; ti < t; ti++) { float* mr = mixed + (int64_t)ti * d; for (int i = 0; i < d; i++) mr[i] = 0.0f;
+        for (int s = 0; s < hc; s++) for (int i = 0; i < d; i++) { int64_t k = (int64_t)ti * w + s * d + i; mr[i] += xn[k] * sigm(gate[k]); }
+        for (int i = 0; i < d; i++) mr[i] /= (float)hc; }
+    free(xn); free(lo); free(gate);
+}
+/* hc_combine :1384-1388 */
+static void hc_combine(const orc_cfg* c, float* x, const float* out, const float* inj, int t) {
+    int d = c->d, hc = c->hc;
+    for (int ti = 0; ti < t; ti++) for (int s = 0; s < hc; s++) { float w = 2.0f * sigm(inj[ti * hc + s]); float* r = x + ((int64_t)ti * hc + s) * d; for (int i = 0; i < d; i++) r[i] += out[(int64_t)ti * d + i] * w; }
+}
+
+/* forward_inner :2087-2157 (pure-CPU branch :2134-2142).  hc == 0 selects the plain pre-norm
+ * residual form (x += mixer(rms(x)*attn_norm); x += ffn(rms(x)*ffn_norm); head on rms(x)*out_norm),
+ * which the reference does not have; hc >= 1 is the reference's hyper-connection plumbing. */
+int orc_forward(const orc_model* m, orc_state* st, const uint32_t* ids, int t, float* logits) {
+    const orc_cfg* c = &m->cfg; int d = c->d, hc = c->hc; int xw = (hc > 0 ? hc : 1) * d; int64_t start = st->pos;
+    if (start + t > c->max_ctx) return -2;
+    float* x = (float*)malloc((size_t)t * xw * 4); float* mx = (float*)malloc((size_t)t * d * 4); float* o = (float*)malloc((size_t)t * d * 4); float* inj = (float*)malloc((size_t)t * (hc > 0 ? hc : 1) * 4);
+    const orc_mat* embd = M(m, -1, ORC_R_TOKEN_EMBD);
+    for (int ti = 0; ti < t; ti++) { orc_mat_row(embd, ids[ti], o); for (int s = 0; s < (hc > 0 ? hc : 1); s++) memcpy(x + ((int64_t)ti * (hc > 0 ? hc : 1) + s) * d, o, (size_t)d * 4); }  /* :2092 */
+    int li = 0, ai = 0; st->router_margin = INFINITY;
+    int nk = c->lin_nk, nv = c->lin_nv, dk = c->lin_dk, dv = c->lin_dv; int ch = 2 * nk * dk + nv * dv; int row = c->n_kv * c->hd;
+    for (int il = 0; il < c->n_layers; il++) {
+        if (hc > 0) hc_mix(m, il, ORC_R_HCA_NORM, ORC_R_HCA_DOWN, ORC_R_HCA_UP, ORC_R_HCA_INJECT, x, t, mx, inj);
+        else for (int ti = 0; ti < t; ti++) rms(x + (int64_t)ti * d, V(m, il, ORC_R_ATTN_NORM), c->eps, mx + (int64_t)ti * d, d);
+        if (is_full(c, il)) {  /* attn :1441-1446 */
+            int nq = c->n_head * 2 * c->hd; float* qf = (float*)malloc((size_t)t * nq * 4); float* kf = (float*)malloc((size_t)t * row * 4); float* vf = (float*)malloc((size_t)t * row * 4); float* att = (float*)malloc((size_t)t * c->n_head * c->hd * 4);
+            orc_matmul(M(m, il, ORC_R_ATTN_Q), mx, t, qf); orc_matmul(M(m, il, ORC_R_ATTN_K), mx, t, kf); orc_matmul(M(m, il, ORC_R_ATTN_V), mx, t, vf);
+            for (int ti = 0; ti < t; ti++) {
+                int64_t pos = start + ti;
+                /* the packed boundary follows the row count after the append (pos + 1 rows); the rows it
+                 * covers are all older than the recent window, so they are already normed and roped */
+                kv_repack(st, ai, pos + 1);
+                orc_attn_core(c, qf + (int64_t)ti * nq, kf + (int64_t)ti * row, vf + (int64_t)ti * row, V(m, il, ORC_R_ATTN_Q_NORM), V(m, il, ORC_R_ATTN_K_NORM), m->rope_inv,
+                              st->k[ai], st->v[ai], pos, st->kw[ai], st->ks[ai], st->vw[ai], st->vs[ai], st->q4n[ai], att + (int64_t)ti * c->n_head * c->hd);
+            }
+            orc_matmul(M(m, il, ORC_R_ATTN_O), att, t, o); free(qf); free(kf); free(vf); free(att); ai++;
+        } else {  /* linear :1617-1621 */
+            float* qkv = (float*)malloc((size_t)t * ch * 4); float* z = (float*)malloc((size_t)t * nv * dv * 4); float* be = (float*)malloc((size_t)t * nv * 4); float* al = (float*)malloc((size_t)t * nv * 4); float* oa = (float*)malloc((size_t)t * nv * dv * 4);
+            orc_matmul(M(m, il, ORC_R_LIN_QKV), mx, t, qkv); orc_matmul(M(m, il, ORC_R_LIN_Z), mx, t, z); orc_matmul(M(m, il, ORC_R_LIN_BETA), mx, t, be); orc_matmul(M(m, il, ORC_R_LIN_ALPHA), mx, t, al);
+            orc_linear_core(c, qkv, z, be, al, V(m, il, ORC_R_LIN_A), V(m, il, ORC_R_LIN_DT), V(m, il, ORC_R_LIN_CONV), V(m, il, ORC_R_LIN_NORM), st->conv[li], st->ssm[li], t, oa);
+            orc_matmul(M(m, il, ORC_R_LIN_OUT), oa, t, o); free(qkv); free(z); free(be); free(al); free(oa); li++;
+        }
+        if (hc > 0) { hc_combine(c, x, o, inj, t); hc_mix(m, il, ORC_R_HCF_NORM, ORC_R_HCF_DOWN, ORC_R_HCF_UP, ORC_R_HCF_INJECT, x, t, mx, inj); }
+        else { for (int64_t i = 0; i < (int64_t)t * d; i++) x[i] += o[i]; for (int ti = 0; ti < t; ti++) rms(x + (int64_t)ti * d, V(m, il, ORC_R_FFN_NORM), c->eps, mx + (int64_t)ti * d, d); }
+        {
+            int32_t* sel = (int32_t*)malloc((size_t)t * c->top_k * 4);
+            orc_moe(c, M(m, il, ORC_R_ROUTER), M(m, il, ORC_R_EXP_GATE), M(m, il, ORC_R_EXP_UP), M(m, il, ORC_R_EXP_DOWN), M(m, il, ORC_R_SH_GATE), M(m, il, ORC_R_SH_UP), M(m, il, ORC_R_SH_DOWN), V(m, il, ORC_R_SH_GATE_INP), mx, t, o, sel, NULL);
+            /* 10th/11th router margin of the last token, for near-tie classification */
+            { float* lg = (float*)malloc((size_t)c->n_exp * 4); orc_mat rt = *M(m, il, ORC_R_ROUTER); orc_matmul(&rt, mx + (int64_t)(t - 1) * d, 1, lg);
+              float kth = INFINITY; for (int j = 0; j < c->top_k; j++) kth = fminf(kth, lg[sel[(t - 1) * c->top_k + j]]);
+              float nxt = -INFINITY; for (int e = 0; e < c->n_exp; e++) { int in = 0; for (int j = 0; j < c->top_k; j++) if (sel[(t - 1) * c->top_k + j] == e) in = 1; if (!in) nxt = fmaxf(nxt, lg[e]); }
+              st->router_margin = fminf(st->router_margin, kth - nxt); free(lg); }
+            free(sel);
+        }
+        if (hc > 0) hc_combine(c, x, o, inj, t); else for (int64_t i = 0; i < (int64_t)t * d; i++) x[i] += o[i];
+    }
+    const float* last = x + (int64_t)(t - 1) * xw;
+    if (hc > 0) hc_mix(m, -1, ORC_R_OUT_HC_NORM, ORC_R_OUT_HC_DOWN, ORC_R_OUT_HC_UP, -1, last, 1, mx, inj);  /* :2152 */
+    else rms(last, V(m, -1, ORC_R_OUT_NORM), c->eps, mx, d);
+    const orc_mat* out = M(m, -1, ORC_R_OUTPUT); if (!out) out = embd;                                          /* :511 */
+    orc_matmul(out, mx, 1, logits);                                                                              /* head_logits :2361-2364 */
+    { uint32_t b = orc_argmax(logits, c->vocab); float second = -INFINITY; for (int i = 0; i < c->vocab; i++) if ((uint32_t)i != b) second = fmaxf(second, logits[i]); st->logit_margin = logits[b] - second; }
+    st->pos = start + t;
+    free(x); free(mx); free(o); free(inj);
+    return 0;
+}

@@ -1,0 +1,228 @@
+// C ABI: context and quantized-matrix entry points (include/pyre_b200.h).
+#include "pb_formats.cuh"
+#include "pb_internal.h"
+
+#include <stdio.h>
+#include <string.h>
+#include <new>
+
+static const char* kNoCtx = "pyre_b200: null context";
+
+int pb_scratch(pb_ctx* ctx, size_t bytes, void** out) {
+    if (bytes > ctx->scratch_bytes) {
+        PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if (ctx->scratch) cudaFree(ctx->scratch);
+        ctx->scratch = nullptr; ctx->scratch_bytes = 0;
+        const size_t want = (bytes + ((size_t)1 << 20)) & ~(((size_t)1 << 20) - 1);
+        PB_CUDA(ctx, cudaMalloc(&ctx->scratch, want));
+        ctx->scratch_bytes = want;
+    }
+    *out = ctx->scratch;
+    return PB_OK;
+}
+
+// Synchronise the stream and turn a non-zero device status word into PB_ERR_DEVICE.
+int pb_sync_check(pb_ctx* ctx, const char* who) {
+    PB_CUDA(ctx, cudaMemcpyAsync(ctx->host_status, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    const int st = *ctx->host_status;
+    if (st) {
+        cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), ctx->stream);
+        PB_FAIL(ctx, PB_ERR_DEVICE, "%s: a kernel reported device status %d", who, st);
+    }
+    return PB_OK;
+}
+
+extern "C" {
+
+int pb_ctx_create(int device, pb_ctx** out) {
+    if (!out) return PB_ERR_ARG;
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) return PB_ERR_CUDA;  // no GPU: fail loudly, there is no CPU path
+    if (device < 0 || device >= n) return PB_ERR_ARG;
+    pb_ctx* c = new (std::nothrow) pb_ctx();
+    if (!c) return PB_ERR_OOM;
+    c->device = device;
+    if (cudaSetDevice(device) != cudaSuccess) { delete c; return PB_ERR_CUDA; }
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete c; return PB_ERR_CUDA; }
+    c->sm_count = prop.multiProcessorCount;
+    c->max_smem_optin = (int)prop.sharedMemPerBlockOptin;
+    if (cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) != cudaSuccess) { delete c; return PB_ERR_CUDA; }
+    c->stream = c->own_stream;
+    if (cudaMalloc(&c->dev_status, 256) != cudaSuccess) { cudaStreamDestroy(c->own_stream); delete c; return PB_ERR_OOM; }
+    cudaMemset(c->dev_status, 0, 256);
+    if (cudaMallocHost(&c->host_status, 256) != cudaSuccess) { cudaFree(c->dev_status); cudaStreamDestroy(c->own_stream); delete c; return PB_ERR_OOM; }
+    *c->host_status = 0;
+    *out = c;
+    return PB_OK;
+}
+
+int pb_ctx_destroy(pb_ctx* ctx) {
+    if (!ctx) return PB_OK;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->dev_status) cudaFree(ctx->dev_status);
+    if (ctx->host_status) cudaFreeHost(ctx->host_status);
+    if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
+    delete ctx;
+    return PB_OK;
+}
+
+const char* pb_last_error(const pb_ctx* ctx) { return ctx ? ctx->err.c_str() : kNoCtx; }
+
+int pb_ctx_set_stream(pb_ctx* ctx, void* s) {
+    if (!ctx) return PB_ERR_ARG;
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ctx->stream = (cudaStream_t)s;
+    return PB_OK;
+}
+
+int pb_ctx_own_stream(pb_ctx* ctx) {
+    if (!ctx) return PB_ERR_ARG;
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ctx->stream = ctx->own_stream;
+    return PB_OK;
+}
+
+int pb_ctx_sync(pb_ctx* ctx) {
+    if (!ctx) return PB_ERR_ARG;
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return PB_OK;
+}
+
+int pb_ctx_device_status(pb_ctx* ctx, int* status) {
+    if (!ctx || !status) return PB_ERR_ARG;
+    PB_CUDA(ctx, cudaMemcpyAsync(status, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (*status) PB_CUDA(ctx, cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), ctx->stream));
+    return PB_OK;
+}
+
+int pb_type_geom(int t, int* e, int* b) { return pb_geom(t, e, b) ? PB_ERR_ARG : PB_OK; }
+
+static int qmat_alloc(pb_ctx* ctx, int type, int64_t rows, int64_t cols, pb_qmat** out) {
+    int el, bs;
+    if (!ctx || !out) return PB_ERR_ARG;
+    *out = nullptr;
+    if (pb_geom(type, &el, &bs)) PB_FAIL(ctx, PB_ERR_ARG, "unsupported ggml type %d", type);
+    if (rows <= 0 || cols <= 0 || cols % el) PB_FAIL(ctx, PB_ERR_ARG, "bad matrix shape %lld x %lld for blocks of %d", (long long)rows, (long long)cols, el);
+    pb_qmat* m = new (std::nothrow) pb_qmat();
+    if (!m) PB_FAIL(ctx, PB_ERR_OOM, "host allocation failed");
+    m->ctx = ctx; m->type = type; m->rows = rows; m->cols = cols;
+    m->row_bytes = cols / el * bs;
+    m->nbytes = (size_t)rows * (size_t)m->row_bytes;
+    PB_CUDA(ctx, cudaSetDevice(ctx->device));
+    // padded so that 16-byte-granular bulk copies of the last rows stay inside the allocation
+    cudaError_t e = cudaMalloc(&m->data, m->nbytes + 256);
+    if (e != cudaSuccess) { delete m; PB_FAIL(ctx, PB_ERR_OOM, "cudaMalloc(%zu): %s", m->nbytes + 256, cudaGetErrorString(e)); }
+    cudaMemsetAsync(m->data + m->nbytes, 0, 256, ctx->stream);
+    *out = m;
+    return PB_OK;
+}
+
+int pb_qmat_upload(pb_ctx* ctx, int type, int64_t rows, int64_t cols, const void* bytes, size_t nbytes, pb_qmat** out) {
+    if (!ctx) return PB_ERR_ARG;
+    if (!bytes) PB_FAIL(ctx, PB_ERR_ARG, "pb_qmat_upload: null data");
+    PB_TRY(qmat_alloc(ctx, type, rows, cols, out));
+    if (nbytes != (*out)->nbytes) { size_t want = (*out)->nbytes; pb_qmat_free(*out); *out = nullptr; PB_FAIL(ctx, PB_ERR_ARG, "pb_qmat_upload: %zu bytes given, %zu expected", nbytes, want); }
+    PB_CUDA(ctx, cudaMemcpyAsync((*out)->data, bytes, nbytes, cudaMemcpyHostToDevice, ctx->stream));
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return PB_OK;
+}
+
+int pb_qmat_synth(pb_ctx* ctx, int type, int64_t rows, int64_t cols, uint64_t seed, uint64_t tid, pb_qmat** out) {
+    if (!ctx) return PB_ERR_ARG;
+    PB_TRY(qmat_alloc(ctx, type, rows, cols, out));
+    pb_qmat* m = *out;
+    int rc;
+    if (type == PB_T_F32) rc = pb_launch_synth_normal(ctx, reinterpret_cast<float*>(m->data), rows * cols, seed, tid, 0.02f);
+    else { int el, bs; pb_geom(type, &el, &bs); rc = pb_launch_synth(ctx, type, m->data, rows * (cols / el), seed, tid); }
+    if (rc != PB_OK) { pb_qmat_free(m); *out = nullptr; }
+    return rc;
+}
+
+int pb_qmat_free(pb_qmat* m) {
+    if (!m) return PB_OK;
+    if (m->owns && m->data) { cudaSetDevice(m->ctx->device); cudaStreamSynchronize(m->ctx->stream); cudaFree(m->data); }
+    delete m;
+    return PB_OK;
+}
+
+int pb_qmat_info(const pb_qmat* m, int* type, int64_t* rows, int64_t* cols, size_t* nbytes) {
+    if (!m) return PB_ERR_ARG;
+    if (type) *type = m->type;
+    if (rows) *rows = m->rows;
+    if (cols) *cols = m->cols;
+    if (nbytes) *nbytes = m->nbytes;
+    return PB_OK;
+}
+
+static int check_rows(pb_ctx* ctx, const pb_qmat* m, int64_t r0, int64_t n, const char* who) {
+    if (!ctx || !m) return PB_ERR_ARG;
+    if (r0 < 0 || n < 0 || r0 + n > m->rows) PB_FAIL(ctx, PB_ERR_ARG, "%s: rows [%lld, %lld) outside 0..%lld", who, (long long)r0, (long long)(r0 + n), (long long)m->rows);
+    return PB_OK;
+}
+
+int pb_qmat_read(pb_ctx* ctx, const pb_qmat* m, int64_t r0, int64_t n, void* bytes) {
+    PB_TRY(check_rows(ctx, m, r0, n, "pb_qmat_read"));
+    if (!bytes) PB_FAIL(ctx, PB_ERR_ARG, "pb_qmat_read: null buffer");
+    PB_CUDA(ctx, cudaMemcpyAsync(bytes, m->data + r0 * m->row_bytes, (size_t)n * m->row_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return PB_OK;
+}
+
+int pb_qmat_dequant_dev(pb_ctx* ctx, const pb_qmat* m, int64_t r0, int64_t n, float* out) {
+    PB_TRY(check_rows(ctx, m, r0, n, "pb_qmat_dequant"));
+    if (!out) PB_FAIL(ctx, PB_ERR_ARG, "pb_qmat_dequant: null output");
+    if ((n * m->cols) % 8) PB_FAIL(ctx, PB_UNSUPPORTED, "pb_qmat_dequant: element count must be a multiple of 8");
+    if (m->type == PB_T_Q8_0 && ((r0 * m->cols) % 256)) PB_FAIL(ctx, PB_UNSUPPORTED, "pb_qmat_dequant: Q8_0 row offset must be a multiple of 256 elements");
+    return pb_launch_dequant(ctx, m->type, m->data + r0 * m->row_bytes, n * m->cols / 8, out);
+}
+
+int pb_qmat_dequant(pb_ctx* ctx, const pb_qmat* m, int64_t r0, int64_t n, float* out_host) {
+    PB_TRY(check_rows(ctx, m, r0, n, "pb_qmat_dequant"));
+    if (!out_host) PB_FAIL(ctx, PB_ERR_ARG, "pb_qmat_dequant: null output");
+    if (n == 0) return PB_OK;
+    void* tmp;
+    const size_t bytes = (size_t)n * m->cols * 4;
+    PB_TRY(pb_scratch(ctx, bytes + 1024, &tmp));
+    PB_TRY(pb_qmat_dequant_dev(ctx, m, r0, n, (float*)tmp));
+    PB_CUDA(ctx, cudaMemcpyAsync(out_host, tmp, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return PB_OK;
+}
+
+int pb_gemv_dev(pb_ctx* ctx, const pb_qmat* m, const float* x, int t, float* y) {
+    if (!ctx || !m) return PB_ERR_ARG;
+    if (!x || !y) PB_FAIL(ctx, PB_ERR_ARG, "pb_gemv: null buffer");
+    if (t < 0) PB_FAIL(ctx, PB_ERR_ARG, "pb_gemv: t=%d", t);
+    for (int t0 = 0; t0 < t; t0 += 16) {
+        PbGemvArgs a;
+        a.w = m->data; a.type = m->type; a.rows = m->rows; a.cols = (int)m->cols;
+        a.x = x + (int64_t)t0 * m->cols; a.ldx = m->cols; a.t = t - t0 < 16 ? t - t0 : 16;
+        a.y = y + (int64_t)t0 * m->rows; a.ldy = m->rows;
+        PB_TRY(pb_launch_gemv(ctx, a));
+    }
+    return PB_OK;
+}
+
+int pb_gemv(pb_ctx* ctx, const pb_qmat* m, const float* x_host, int t, float* y_host) {
+    if (!ctx || !m) return PB_ERR_ARG;
+    if (!x_host || !y_host) PB_FAIL(ctx, PB_ERR_ARG, "pb_gemv: null buffer");
+    if (t <= 0) return t == 0 ? PB_OK : PB_ERR_ARG;
+    const size_t xb = ((size_t)t * m->cols * 4 + 255) & ~(size_t)255, yb = (size_t)t * m->rows * 4;
+    void* tmp;
+    PB_TRY(pb_scratch(ctx, xb + yb, &tmp));
+    float* xd = (float*)tmp;
+    float* yd = (float*)((uint8_t*)tmp + xb);
+    PB_CUDA(ctx, cudaMemcpyAsync(xd, x_host, (size_t)t * m->cols * 4, cudaMemcpyHostToDevice, ctx->stream));
+    PB_TRY(pb_gemv_dev(ctx, m, xd, t, yd));
+    PB_CUDA(ctx, cudaMemcpyAsync(y_host, yd, yb, cudaMemcpyDeviceToHost, ctx->stream));
+    PB_TRY(pb_sync_check(ctx, "pb_gemv"));
+    return PB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,215 @@
+// Decoders for the GGUF block formats of the decode path, written for one warp per
+// 256-weight super-step: lane l decodes 8 weights ("a unit") of the super-step.
+//
+// Layouts and decode expressions restate the reference's dequantizer
+// (src/model/gguf_q.rs:67-166: Q8_0 :79, Q4_K :103-107 with scale_min_k4 :62-64,
+// IQ2_XS :126-129, IQ3_S :141-151; geometry QType::geom :33-41).  Every scale is formed
+// with the same separate f32 roundings as the reference (__fmul_rn, never contracted), so
+// the dequantized value  s * w - m  is bit-identical to the reference's.
+#pragma once
+#include "pb_common.cuh"
+
+#define PB_TABLE_QUAL static __device__ const
+#include "pb_iq_tables.h"
+
+enum : int { PB_T_F32 = 0, PB_T_F16 = 1, PB_T_Q8_0 = 8, PB_T_Q4_K = 12, PB_T_IQ2_XS = 17, PB_T_IQ3_S = 21, PB_T_BF16 = 30 };
+
+// Codebooks staged in shared memory by the kernel that decodes (see pb_load_tables).
+struct PbTables {
+    const uint32_t* iq3s;   // 512 x 4 grid bytes
+    const uint64_t* iq2xs;  // 512 x 8 grid bytes
+    const uint8_t* ksigns;  // 128 sign bytes
+};
+#define PB_TABLE_BYTES (512 * 4 + 512 * 8 + 128)
+
+// Copy the codebooks a format needs into shared memory at `dst` (16-byte aligned,
+// PB_TABLE_BYTES long).  All threads of the CTA call it; the caller synchronises after.
+template <int FMT>
+__device__ __forceinline__ PbTables pb_load_tables(uint8_t* dst, int tid, int nthreads) {
+    PbTables t;
+    uint64_t* g2 = reinterpret_cast<uint64_t*>(dst);
+    uint32_t* g3 = reinterpret_cast<uint32_t*>(dst + 512 * 8);
+    uint8_t* ks = dst + 512 * 8 + 512 * 4;
+    if (FMT == PB_T_IQ3_S)
+        for (int i = tid; i < 512; i += nthreads) g3[i] = PB_IQ3S_GRID[i];
+    if (FMT == PB_T_IQ2_XS) {
+        for (int i = tid; i < 512; i += nthreads) g2[i] = PB_IQ2XS_GRID[i];
+        for (int i = tid; i < 128; i += nthreads) ks[i] = PB_KSIGNS_IQ2XS[i];
+    }
+    t.iq2xs = g2; t.iq3s = g3; t.ksigns = ks;
+    return t;
+}
+
+// One unit: 8 integer-valued weights w (sign applied), the scale of the first and of the
+// second four (sa, sb) and, for formats with a minimum, the offsets (ma, mb):
+//   value[j] = (j < 4 ? sa : sb) * w[j] - (j < 4 ? ma : mb)
+struct PbUnit { float w[8]; float sa, sb, ma, mb; };
+
+template <int FMT> struct PbFmt;
+
+// ---- contiguous-8 formats share the x / y index maps: lane l owns weights 8l..8l+7 ----
+struct PbContig8 {
+    // index (in float4 units, within the 256-wide step) of the two activation quads a lane needs
+    __device__ static __forceinline__ int xa(int lane) { return 2 * lane; }
+    __device__ static __forceinline__ int xb(int lane) { return 2 * lane + 1; }
+    // where float4 number k of a step is stored in the lane-major shared-memory copy of x
+    __device__ static __forceinline__ int perm(int k) { return (k & 1) * 32 + (k >> 1); }
+    // position of weight j of the lane inside the 256-wide step
+    __device__ static __forceinline__ int pos(int lane, int j) { return 8 * lane + j; }
+};
+
+template <> struct PbFmt<PB_T_IQ3_S> : PbContig8 {
+    static constexpr int STEP_BYTES = 110;  // [d f16][qs 64][qh 8][signs 32][scales 4]
+    static constexpr bool HAS_MIN = false;
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables& T, PbUnit& o) {
+        const float d = pb_h2f(*reinterpret_cast<const uint16_t*>(p));
+        const uint32_t qs = *reinterpret_cast<const uint16_t*>(p + 2 + 2 * u);
+        const uint32_t qh = p[66 + (u >> 2)] >> (2 * (u & 3));
+        const uint32_t sg = p[74 + u];
+        const uint32_t sc = p[106 + (u >> 3)];
+        const uint32_t nib = (u & 4) ? (sc >> 4) : (sc & 0xF);
+        o.sa = o.sb = __fmul_rn(d, (float)(1 + 2 * (int)nib));
+        o.ma = o.mb = 0.0f;
+        const uint32_t g1 = T.iq3s[(qs & 0xFF) | ((qh & 1) << 8)];
+        const uint32_t g2 = T.iq3s[(qs >> 8) | ((qh & 2) << 7)];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            float a = (float)((g1 >> (8 * j)) & 0xFF), b = (float)((g2 >> (8 * j)) & 0xFF);
+            o.w[j] = (sg >> j) & 1 ? -a : a;
+            o.w[4 + j] = (sg >> (4 + j)) & 1 ? -b : b;
+        }
+    }
+};
+
+template <> struct PbFmt<PB_T_IQ2_XS> : PbContig8 {
+    static constexpr int STEP_BYTES = 74;  // [d f16][qs 32 x u16][scales 8]
+    static constexpr bool HAS_MIN = false;
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables& T, PbUnit& o) {
+        const float d = pb_h2f(*reinterpret_cast<const uint16_t*>(p));
+        const uint32_t q = *reinterpret_cast<const uint16_t*>(p + 2 + 2 * u);
+        const uint32_t sc = p[66 + (u >> 2)];
+        const uint32_t nib = (u & 2) ? (sc >> 4) : (sc & 0xF);
+        o.sa = o.sb = __fmul_rn(__fmul_rn(d, 0.5f + (float)nib), 0.25f);
+        o.ma = o.mb = 0.0f;
+        const uint64_t g = T.iq2xs[q & 511];
+        const uint32_t sg = T.ksigns[q >> 9];
+        const uint32_t lo = (uint32_t)g, hi = (uint32_t)(g >> 32);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            float a = (float)((lo >> (8 * j)) & 0xFF), b = (float)((hi >> (8 * j)) & 0xFF);
+            o.w[j] = (sg >> j) & 1 ? -a : a;
+            o.w[4 + j] = (sg >> (4 + j)) & 1 ? -b : b;
+        }
+    }
+};
+
+template <> struct PbFmt<PB_T_Q8_0> : PbContig8 {
+    static constexpr int STEP_BYTES = 8 * 34;  // eight [d f16][32 x i8] blocks
+    static constexpr bool HAS_MIN = false;
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables&, PbUnit& o) {
+        const uint8_t* b = p + 34 * (u >> 2);
+        o.sa = o.sb = pb_h2f(*reinterpret_cast<const uint16_t*>(b));
+        o.ma = o.mb = 0.0f;
+        const uint16_t* q = reinterpret_cast<const uint16_t*>(b + 2 + 8 * (u & 3));
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const uint32_t v = q[j];
+            o.w[2 * j] = (float)(int8_t)(v & 0xFF);
+            o.w[2 * j + 1] = (float)(int8_t)(v >> 8);
+        }
+    }
+};
+
+template <> struct PbFmt<PB_T_Q4_K> {
+    static constexpr int STEP_BYTES = 144;  // [d f16][dmin f16][scales 12][qs 128]
+    static constexpr bool HAS_MIN = true;
+    // lane l = (group g = l / 8, quad i = l % 8): low nibbles of qs[32g + 4i .. +3] are weights
+    // 64g + 4i + {0..3}, high nibbles are weights 64g + 32 + 4i + {0..3}
+    __device__ static __forceinline__ int xa(int lane) { return 16 * (lane >> 3) + (lane & 7); }
+    __device__ static __forceinline__ int xb(int lane) { return 16 * (lane >> 3) + 8 + (lane & 7); }
+    __device__ static __forceinline__ int perm(int k) { int g = k >> 4, r = k & 15; return r < 8 ? 8 * g + r : 32 + 8 * g + (r - 8); }
+    __device__ static __forceinline__ int pos(int lane, int j) { return 64 * (lane >> 3) + 4 * (lane & 7) + (j < 4 ? j : 32 + (j - 4)); }
+    __device__ static __forceinline__ void scale_min(int j, const uint8_t* q, uint32_t& sc, uint32_t& m) {
+        if (j < 4) { sc = q[j] & 63; m = q[j + 4] & 63; }
+        else { sc = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4); m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4); }
+    }
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables&, PbUnit& o) {
+        const float d = pb_h2f(*reinterpret_cast<const uint16_t*>(p));
+        const float mn = pb_h2f(*reinterpret_cast<const uint16_t*>(p + 2));
+        const int g = u >> 3, i = u & 7;
+        uint32_t s1, m1, s2, m2;
+        scale_min(2 * g, p + 4, s1, m1);
+        scale_min(2 * g + 1, p + 4, s2, m2);
+        o.sa = __fmul_rn(d, (float)s1); o.ma = __fmul_rn(mn, (float)m1);
+        o.sb = __fmul_rn(d, (float)s2); o.mb = __fmul_rn(mn, (float)m2);
+        const uint32_t q = *reinterpret_cast<const uint32_t*>(p + 16 + 32 * g + 4 * i);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            o.w[j] = (float)((q >> (8 * j)) & 0xF);
+            o.w[4 + j] = (float)((q >> (8 * j + 4)) & 0xF);
+        }
+    }
+};
+
+// Unquantized storage (router weights, hyper-connection matrices): same unit interface.
+template <> struct PbFmt<PB_T_F32> : PbContig8 {
+    static constexpr int STEP_BYTES = 1024;
+    static constexpr bool HAS_MIN = false;
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables&, PbUnit& o) {
+        const float4 a = *reinterpret_cast<const float4*>(p + 32 * u), b = *reinterpret_cast<const float4*>(p + 32 * u + 16);
+        o.w[0] = a.x; o.w[1] = a.y; o.w[2] = a.z; o.w[3] = a.w; o.w[4] = b.x; o.w[5] = b.y; o.w[6] = b.z; o.w[7] = b.w;
+        o.sa = o.sb = 1.0f; o.ma = o.mb = 0.0f;
+    }
+};
+template <> struct PbFmt<PB_T_F16> : PbContig8 {
+    static constexpr int STEP_BYTES = 512;
+    static constexpr bool HAS_MIN = false;
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables&, PbUnit& o) {
+        const uint4 a = *reinterpret_cast<const uint4*>(p + 16 * u);
+        const uint32_t v[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) { o.w[2 * j] = pb_h2f((uint16_t)(v[j] & 0xFFFF)); o.w[2 * j + 1] = pb_h2f((uint16_t)(v[j] >> 16)); }
+        o.sa = o.sb = 1.0f; o.ma = o.mb = 0.0f;
+    }
+};
+template <> struct PbFmt<PB_T_BF16> : PbContig8 {
+    static constexpr int STEP_BYTES = 512;
+    static constexpr bool HAS_MIN = false;
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables&, PbUnit& o) {
+        const uint4 a = *reinterpret_cast<const uint4*>(p + 16 * u);
+        const uint32_t v[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) { o.w[2 * j] = __uint_as_float(v[j] << 16); o.w[2 * j + 1] = __uint_as_float(v[j] & 0xFFFF0000u); }
+        o.sa = o.sb = 1.0f; o.ma = o.mb = 0.0f;
+    }
+};
+
+// Host-side geometry (QType::geom, gguf_q.rs:33-41).
+static inline int pb_geom(int type, int* elems, int* bytes) {
+    int e, b;
+    switch (type) {
+        case PB_T_F32: e = 1; b = 4; break;
+        case PB_T_F16: case PB_T_BF16: e = 1; b = 2; break;
+        case PB_T_Q8_0: e = 32; b = 34; break;
+        case PB_T_Q4_K: e = 256; b = 144; break;
+        case PB_T_IQ2_XS: e = 256; b = 74; break;
+        case PB_T_IQ3_S: e = 256; b = 110; break;
+        default: return -1;
+    }
+    if (elems) *elems = e;
+    if (bytes) *bytes = b;
+    return 0;
+}
+
+// Dispatch a templated callable on the runtime type id.
+#define PB_DISPATCH_FMT(type, F, ...)                                  \
+    switch (type) {                                                    \
+        case PB_T_IQ3_S: { constexpr int FMT = PB_T_IQ3_S; F(__VA_ARGS__); } break;  \
+        case PB_T_IQ2_XS: { constexpr int FMT = PB_T_IQ2_XS; F(__VA_ARGS__); } break; \
+        case PB_T_Q4_K: { constexpr int FMT = PB_T_Q4_K; F(__VA_ARGS__); } break;    \
+        case PB_T_Q8_0: { constexpr int FMT = PB_T_Q8_0; F(__VA_ARGS__); } break;    \
+        case PB_T_F32: { constexpr int FMT = PB_T_F32; F(__VA_ARGS__); } break;      \
+        case PB_T_F16: { constexpr int FMT = PB_T_F16; F(__VA_ARGS__); } break;      \
+        case PB_T_BF16: { constexpr int FMT = PB_T_BF16; F(__VA_ARGS__); } break;    \
+        default: break;                                                \
+    }

@@ -1,0 +1,157 @@
+// Integer dot-product core of the dequant-GEMV kernels.
+//
+// A lane owns a quarter of a 256-weight super-step (64 consecutive weights).  It decodes
+// them to 16 words of packed signed int8 (grid values with their signs, raw int8 for
+// Q8_0, nibbles for Q4_K) plus f32 scales per 16 weights, and dots them with dp4a against
+// activations that were split, per 32-value group, into two int8 levels:
+//     x = s1*q1 + s2*q2 + e,   |e| <= max|x| / (127*127*4)
+// Integer partial sums are exact; each group contributes one f32 FMA per level.  The split
+// keeps the result within ~1e-5 relative of an f32-accumulated dot (the parity tolerance
+// is 1e-3), and turns byte->float conversion, sign handling and 8 FMAs per 8 weights into
+// two SWAR sign operations and two dp4a per 4 weights.
+//
+// Block layouts restate src/model/gguf_q.rs:67-166 of the reference (see pb_formats.cuh).
+#pragma once
+#include "pb_formats.cuh"
+
+// Shared-memory tables used by the decoders.
+struct PbQTabs {
+    const uint32_t* grid3;   // IQ3_S grid; entry i for lane l at [i * rep + (l & (rep-1))]
+    const uint64_t* grid2;   // IQ2_XS grid, same replication scheme in 8-byte units
+    const uint2* sign16;     // nibble -> (byte mask of negative weights, mask & 0x01010101)
+    int rep3, rep2;          // replication factors (1 = plain table)
+};
+
+// load N32 consecutive u32 from a 2-byte-aligned shared-memory address
+template <int N32>
+__device__ __forceinline__ void pb_ld_u32x(const uint8_t* p, uint32_t (&out)[N32]) {
+    const uint32_t sh = ((uint32_t)(uintptr_t)p & 2u) * 8u;          // 0 or 16 bits
+    const uint32_t* a = reinterpret_cast<const uint32_t*>((uintptr_t)p & ~(uintptr_t)3);
+    uint32_t w[N32 + 1];
+#pragma unroll
+    for (int i = 0; i <= N32; i++) w[i] = a[i];
+#pragma unroll
+    for (int i = 0; i < N32; i++) out[i] = __funnelshift_r(w[i], w[i + 1], sh);
+}
+
+// (g ^ M) + C : negate the bytes of g selected by the byte mask M (all bytes of g are <= 127)
+__device__ __forceinline__ uint32_t pb_apply_sign(uint32_t g, uint2 mc) { return (g ^ mc.x) + mc.y; }
+
+struct PbQuarter {
+    int w[16];      // packed signed int8, weight 4k+j of the quarter in byte j of w[k]
+    float sc[4];    // scale of weights 16h .. 16h+15
+    float mn[2];    // Q4_K only: offset of weights 32g .. 32g+31
+};
+
+template <int FMT> struct PbQDec;
+
+template <> struct PbQDec<PB_T_IQ3_S> {
+    static constexpr int STEP_BYTES = 110;
+    static constexpr bool HAS_MIN = false, SCALE16 = false;
+    __device__ static __forceinline__ void quarter(const uint8_t* p, int qt, int lane, const PbQTabs& T, PbQuarter& o) {
+        const float d = pb_h2f(*reinterpret_cast<const uint16_t*>(p));
+        uint32_t qs[4], sg[2];
+        pb_ld_u32x<4>(p + 2 + 16 * qt, qs);
+        pb_ld_u32x<2>(p + 74 + 8 * qt, sg);
+        const uint32_t qh = *reinterpret_cast<const uint16_t*>(p + 66 + 2 * qt);
+        const uint32_t sc = p[106 + qt];
+        const float d0 = d * (float)(1 + 2 * (int)(sc & 0xF)), d1 = d * (float)(1 + 2 * (int)(sc >> 4));
+        o.sc[0] = o.sc[1] = d0; o.sc[2] = o.sc[3] = d1;
+        const uint32_t* tab = T.grid3 + (lane & (T.rep3 - 1));
+#pragma unroll
+        for (int k = 0; k < 16; k++) {
+            const uint32_t byte = (qs[k >> 2] >> (8 * (k & 3))) & 0xFF;
+            const uint32_t hb = k < 8 ? (qh << (8 - k)) & 0x100 : (qh >> (k - 8)) & 0x100;
+            const uint32_t g = tab[(byte | hb) * T.rep3];
+            const uint32_t nib = (sg[k >> 3] >> (4 * (k & 7))) & 0xF;
+            o.w[k] = (int)pb_apply_sign(g, T.sign16[nib]);
+        }
+    }
+};
+
+template <> struct PbQDec<PB_T_IQ2_XS> {
+    static constexpr int STEP_BYTES = 74;
+    static constexpr bool HAS_MIN = false, SCALE16 = true;
+    __device__ static __forceinline__ void quarter(const uint8_t* p, int qt, int lane, const PbQTabs& T, PbQuarter& o) {
+        const float d = pb_h2f(*reinterpret_cast<const uint16_t*>(p));
+        uint32_t qs[4];
+        pb_ld_u32x<4>(p + 2 + 16 * qt, qs);
+        const uint32_t sc = *reinterpret_cast<const uint16_t*>(p + 66 + 2 * qt);
+#pragma unroll
+        for (int h = 0; h < 4; h++) o.sc[h] = d * (0.5f + (float)((sc >> (4 * h)) & 0xF)) * 0.25f;
+        const uint64_t* tab = T.grid2 + (lane & (T.rep2 - 1));
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const uint32_t q = (qs[u >> 1] >> (16 * (u & 1))) & 0xFFFF;
+            const uint64_t g = tab[(q & 511) * T.rep2];
+            const uint32_t s7 = q >> 9;
+            const uint32_t s8 = s7 | ((__popc(s7) & 1) << 7);   // KSIGNS_IQ2XS[i] = i | parity(i) << 7
+            o.w[2 * u] = (int)pb_apply_sign((uint32_t)g, T.sign16[s8 & 0xF]);
+            o.w[2 * u + 1] = (int)pb_apply_sign((uint32_t)(g >> 32), T.sign16[s8 >> 4]);
+        }
+    }
+};
+
+template <> struct PbQDec<PB_T_Q8_0> {
+    static constexpr int STEP_BYTES = 8 * 34;
+    static constexpr bool HAS_MIN = false, SCALE16 = false;
+    __device__ static __forceinline__ void quarter(const uint8_t* p, int qt, int, const PbQTabs&, PbQuarter& o) {
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+            const uint8_t* blk = p + 34 * (2 * qt + b);
+            const float d = pb_h2f(*reinterpret_cast<const uint16_t*>(blk));
+            o.sc[2 * b] = o.sc[2 * b + 1] = d;
+            uint32_t q[8];
+            pb_ld_u32x<8>(blk + 2, q);
+#pragma unroll
+            for (int k = 0; k < 8; k++) o.w[8 * b + k] = (int)q[k];
+        }
+    }
+};
+
+template <> struct PbQDec<PB_T_Q4_K> {
+    static constexpr int STEP_BYTES = 144;
+    static constexpr bool HAS_MIN = true, SCALE16 = false;
+    __device__ static __forceinline__ void quarter(const uint8_t* p, int qt, int, const PbQTabs&, PbQuarter& o) {
+        const uint32_t dm = *reinterpret_cast<const uint32_t*>(p);
+        const float d = pb_h2f((uint16_t)(dm & 0xFFFF)), mn = pb_h2f((uint16_t)(dm >> 16));
+        uint32_t s1, m1, s2, m2;
+        PbFmt<PB_T_Q4_K>::scale_min(2 * qt, p + 4, s1, m1);
+        PbFmt<PB_T_Q4_K>::scale_min(2 * qt + 1, p + 4, s2, m2);
+        o.sc[0] = o.sc[1] = d * (float)s1; o.sc[2] = o.sc[3] = d * (float)s2;
+        o.mn[0] = mn * (float)m1; o.mn[1] = mn * (float)m2;
+        const uint4 a = *reinterpret_cast<const uint4*>(p + 16 + 32 * qt), b = *reinterpret_cast<const uint4*>(p + 32 + 32 * qt);
+        const uint32_t q[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int k = 0; k < 8; k++) { o.w[k] = (int)(q[k] & 0x0F0F0F0Fu); o.w[8 + k] = (int)((q[k] >> 4) & 0x0F0F0F0Fu); }
+    }
+};
+
+// Activations of one column for one quarter: two int8 levels, their scales, and the f32 sum
+// of each 32-value group (used by formats with a minimum).
+struct PbXQuarter {
+    int q1[16], q2[16];
+    float s1[2], s2[2], sum[2];
+};
+
+template <int FMT>
+__device__ __forceinline__ float pb_quarter_dot(const PbQuarter& w, const PbXQuarter& x) {
+    using D = PbQDec<FMT>;
+    float acc = 0.f;
+    constexpr int NH = D::SCALE16 ? 4 : 2;   // integer sums per 16 or per 32 weights
+    constexpr int WPH = 16 / NH;
+#pragma unroll
+    for (int h = 0; h < NH; h++) {
+        int i1 = 0, i2 = 0;
+#pragma unroll
+        for (int k = 0; k < WPH; k++) { i1 = __dp4a(w.w[h * WPH + k], x.q1[h * WPH + k], i1); i2 = __dp4a(w.w[h * WPH + k], x.q2[h * WPH + k], i2); }
+        const int g = h * WPH / 8;
+        acc = fmaf(w.sc[h * (4 / NH)], fmaf(x.s1[g], (float)i1, x.s2[g] * (float)i2), acc);
+    }
+    if (D::HAS_MIN) { acc = fmaf(-w.mn[0], x.sum[0], acc); acc = fmaf(-w.mn[1], x.sum[1], acc); }
+    return acc;
+}
+
+// Layout of the quantized activations in shared memory, per column:
+//   q1 words [cols/4], q2 words [cols/4], then s1[cols/32], s2[cols/32], sum[cols/32]
+__host__ __device__ static inline int pb_xq_words(int cols) { return cols / 2 + 3 * (cols / 32); }

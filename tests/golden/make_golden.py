@@ -1,0 +1,51 @@
+#!/usr/bin/env python3
+"""Regenerate the golden fixtures in this directory.
+
+dequant_<TYPE>.npz : `raw` = four rows of 512 columns of seeded block bytes, `f32` = their
+dequantization by gguf-py 0.19 (`gguf.quants.dequantize`), the tool the reference's
+authors checked their decoder against (docs/development-log.md:434-436 of the reference).
+The bytes come from the oracle's synthetic generator plus fully random bytes with a sane
+f16 scale (the construction of src/model/qdot.rs:1033-1047).
+kv4_vector.npz     : the input vector of src/model/kv4.rs:55-58 and its packed words/scales from the
+oracle, with the properties that test asserts checked at generation time.
+Run from the repository root:  python tests/golden/make_golden.py
+"""
+import sys
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+import oracle  # noqa: E402
+from gguf import quants, GGMLQuantizationType as T  # noqa: E402
+
+HERE = Path(__file__).resolve().parent
+GG = {"Q8_0": T.Q8_0, "Q4_K": T.Q4_K, "IQ2_XS": T.IQ2_XS, "IQ3_S": T.IQ3_S}
+
+
+def main():
+    for name, t in oracle.QUANT_TYPES.items():
+        el, bs = oracle.geom(t)
+        cols, rows = 512, 4
+        a = oracle.synth_rows(t, 0, 11, cols, 0, rows // 2)
+        rng = np.random.default_rng(1234 + t)
+        nb = (rows // 2) * cols // el
+        b = rng.integers(0, 256, size=(nb, bs), dtype=np.uint8)
+        b[:, 1] = rng.integers(0x20, 0x38, nb)  # f16 exponent byte: scales of about 0.01 .. 0.5
+        if name == "Q4_K":
+            b[:, 3] = rng.integers(0x20, 0x38, nb)
+        raw = np.concatenate([a, b.reshape(-1)])
+        f32 = quants.dequantize(raw.reshape(-1, bs), GG[name]).reshape(rows, cols).astype(np.float32)
+        np.savez_compressed(HERE / f"dequant_{name}.npz", raw=raw, f32=f32, rows=rows, cols=cols, type=t)
+        print(name, raw.size, "bytes")
+    x = np.array([(i * np.float32(0.017) - np.float32(1.3)) * (np.float32(4.0) if i % 32 == 7 else np.float32(0.15)) for i in range(256)], dtype=np.float32)
+    w, s = oracle.kv4_pack(x)
+    y = oracle.kv4_unpack(w, s, 256)
+    assert np.all(np.abs(y - x) <= np.repeat(s, 32) * 0.5 + 1e-6)
+    np.savez_compressed(HERE / "kv4_vector.npz", x=x, words=w, scales=s, unpacked=y)
+    print("kv4 ok")
+
+
+if __name__ == "__main__":
+    main()

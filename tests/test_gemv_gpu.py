@@ -1,0 +1,111 @@
+"""GPU parity of dequantization and dequant-GEMV against the CPU oracle, through the C ABI."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import oracle
+import pyre_b200 as pb
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden"
+TYPES = {"Q8_0": pb.Q8_0, "Q4_K": pb.Q4_K, "IQ2_XS": pb.IQ2_XS, "IQ3_S": pb.IQ3_S}
+GEMV_TOL = 1e-3   # relative, f32 accumulate (north-star tolerance)
+
+
+@pytest.mark.parametrize("name", list(TYPES))
+def test_dequant_golden_bit_exact(ctx, name):
+    g = np.load(GOLD / f"dequant_{name}.npz")
+    rows, cols = int(g["rows"]), int(g["cols"])
+    W = pb.QMat.upload(ctx, TYPES[name], rows, cols, g["raw"])
+    y = W.to_f32()
+    assert np.array_equal(y.view(np.uint32), g["f32"].view(np.uint32))
+    assert np.array_equal(W.raw_rows(1, 2), g["raw"].reshape(rows, -1)[1:3].reshape(-1))
+    W.free()
+
+
+@pytest.mark.parametrize("name", list(TYPES))
+def test_dequant_bit_exact_vs_oracle_config0_shape(ctx, name):
+    """Config 0: 4096 x 2048 from seed 0; the device generator must also reproduce the oracle's bytes."""
+    t = TYPES[name]
+    W = pb.QMat.synth(ctx, t, 4096, 2048, 0, 1)
+    Wo = oracle.QMat.synth(t, 4096, 2048, 0, 1)
+    assert np.array_equal(W.raw_rows(0, 4096), Wo.raw())
+    assert np.array_equal(W.to_f32().view(np.uint32), Wo.to_f32().view(np.uint32))
+    W.free()
+
+
+def test_synth_f32_matches_oracle(ctx):
+    W = pb.QMat.synth(ctx, pb.F32, 512, 2048, 7, 3)
+    ref = oracle.synth_normal(7, 3, 0, 512 * 2048, 0.02).reshape(512, 2048)
+    assert np.array_equal(W.to_f32().view(np.uint32), ref.view(np.uint32))
+    assert abs(float(ref.std()) - 0.02) < 5e-4
+    W.free()
+
+
+def test_config0_iq3s_gemv(ctx):
+    """Config 0: W 4096x2048 IQ3_S seed 0, x ~ N(0,1), batch 1; y within 1e-3 relative."""
+    W = pb.QMat.synth(ctx, pb.IQ3_S, 4096, 2048, 0, 1)
+    x = np.random.default_rng(0).standard_normal((1, 2048)).astype(np.float32)
+    y = W.matmul(x)
+    ref = oracle.QMat.synth(oracle.IQ3_S, 4096, 2048, 0, 1).matmul(x)
+    assert rel_err(y, ref) < GEMV_TOL
+    # element-wise form of the tolerance: |y - ref| <= 1e-3 |ref| + 1e-3 rms(ref)
+    assert np.all(np.abs(y - ref) <= GEMV_TOL * np.abs(ref) + GEMV_TOL * np.sqrt(np.mean(ref ** 2)))
+    W.free()
+
+
+@pytest.mark.parametrize("name", list(TYPES) + ["F32"])
+@pytest.mark.parametrize("shape", [(2048, 512), (1024, 2048), (4096, 2048), (515, 2048), (200, 4096), (300, 256), (40, 768)])
+def test_gemv_sweep(ctx, name, shape):
+    """Config 1 shapes (lm-head covered separately) and ragged row counts, batch 1 / 4 / 16 and odd batches."""
+    t = pb.F32 if name == "F32" else TYPES[name]
+    rows, cols = shape
+    W = pb.QMat.synth(ctx, t, rows, cols, 0, 42)
+    Wo = oracle.QMat.synth(t, rows, cols, 0, 42)
+    rng = np.random.default_rng(rows * 31 + cols)
+    for tt in (1, 3, 4, 16, 19):
+        x = rng.standard_normal((tt, cols)).astype(np.float32)
+        y = W.matmul(x)
+        assert y.shape == (tt, rows)
+        assert rel_err(y, Wo.matmul(x)) < GEMV_TOL, (name, shape, tt)
+    assert ctx.device_status() == 0
+    W.free()
+
+
+def test_gemv_lm_head_linearity(ctx):
+    """Full-size lm-head (151936 x 2048 IQ3_S): oracle on a row sample, linearity on all rows."""
+    rows, cols = 151936, 2048
+    W = pb.QMat.synth(ctx, pb.IQ3_S, rows, cols, 0, 2)
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((2, cols)).astype(np.float32)
+    y = W.matmul(x)
+    ysum = W.matmul((x[0] + x[1])[None])
+    assert rel_err(ysum[0], y[0] + y[1]) < 1e-4
+    for r0 in (0, 75000, rows - 64):
+        Wo = oracle.QMat(oracle.IQ3_S, 64, cols, oracle.synth_rows(oracle.IQ3_S, 0, 2, cols, r0, 64))
+        assert rel_err(y[:, r0:r0 + 64], Wo.matmul(x)) < GEMV_TOL
+    W.free()
+
+
+def test_gemv_zero_and_extreme_inputs(ctx):
+    W = pb.QMat.synth(ctx, pb.IQ3_S, 256, 2048, 0, 8)
+    Wo = oracle.QMat.synth(oracle.IQ3_S, 256, 2048, 0, 8)
+    assert np.all(W.matmul(np.zeros((1, 2048), np.float32)) == 0)
+    x = np.zeros((1, 2048), np.float32); x[0, 100] = 1e4; x[0, 1999] = -3e-5
+    assert rel_err(W.matmul(x), Wo.matmul(x)) < GEMV_TOL
+    W.free()
+
+
+def test_bad_arguments_fail_loudly(ctx):
+    with pytest.raises(pb.PyreError):
+        pb.QMat.upload(ctx, 99, 4, 256, np.zeros(16, np.uint8))          # unknown ggml type
+    with pytest.raises(pb.PyreError):
+        pb.QMat.upload(ctx, pb.IQ3_S, 4, 250, np.zeros(440, np.uint8))   # row not a multiple of the block
+    with pytest.raises(pb.PyreError):
+        pb.QMat.upload(ctx, pb.IQ3_S, 4, 256, np.zeros(100, np.uint8))   # truncated data
+    W = pb.QMat.synth(ctx, pb.IQ3_S, 4, 256, 0, 1)
+    with pytest.raises(pb.PyreError):
+        W.raw_rows(2, 5)
+    W.free()
