@@ -100,10 +100,10 @@ __global__ void __launch_bounds__(256) pb_synth_kernel(uint8_t* __restrict__ w, 
     }
 }
 
-__global__ void __launch_bounds__(256) pb_synth_normal_kernel(float* __restrict__ out, int64_t n, uint64_t tkey, float sigma) {
+__global__ void __launch_bounds__(256) pb_synth_normal_kernel(float* __restrict__ out, int64_t n, uint64_t tkey, float sigma, int64_t i0) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const uint64_t k = pb_sm64(tkey ^ ((uint64_t)i * 0xD1342543DE82EF95ull));
+    const uint64_t k = pb_sm64(tkey ^ ((uint64_t)(i0 + i) * 0xD1342543DE82EF95ull));
     out[i] = __fmul_rn(pb_synth_normal(k, 0), sigma);
 }
 
@@ -123,8 +123,14 @@ int pb_launch_synth(pb_ctx* ctx, int type, uint8_t* w, int64_t nblocks, uint64_t
 }
 
 int pb_launch_synth_normal(pb_ctx* ctx, float* out, int64_t n, uint64_t seed, uint64_t tid, float sigma) {
+    return pb_launch_synth_normal_at(ctx, out, n, seed, tid, 0, sigma);
+}
+
+// elements i0 .. i0+n of the synthetic f32 tensor (seed, tid)
+int pb_launch_synth_normal_at(pb_ctx* ctx, float* out, int64_t n, uint64_t seed, uint64_t tid, int64_t i0, float sigma) {
+    if (n <= 0) return PB_OK;
     const uint64_t tkey = pb_sm64(pb_sm64(seed) ^ tid);
-    pb_synth_normal_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(out, n, tkey, sigma);
+    pb_synth_normal_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(out, n, tkey, sigma, i0);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;

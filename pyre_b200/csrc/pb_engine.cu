@@ -1,37 +1,690 @@
-// Model / state / token-loop entry points of the C ABI (include/pyre_b200.h).
+// Model, state and the device-resident token loop behind the C ABI (include/pyre_b200.h).
+//
+// One decode step = one CUDA graph replay: embedding row -> per layer [fused RMSNorm +
+// projection GEMV, Gated DeltaNet step or 4-bit-KV gated attention, output projection with
+// residual add, router, top-k routing, grouped expert SwiGLU, combine] -> lm-head GEMV ->
+// argmax -> position advance.  Nothing returns to the host inside a token; the reference's
+// loop (forward_inner, src/model/qwen4exp_gguf.rs:2087-2157, layer_cube :728-895) reads
+// router logits back to the host in every layer.
+#include "pb_stream.cuh"
 #include "pb_internal.h"
 
 #include <stdio.h>
+#include <new>
+#include <vector>
 
-#define PB_TODO(name) PB_FAIL((pb_ctx*)nullptr, PB_UNSUPPORTED, name)
+struct PbSlot { pb_qmat* mat = nullptr; float* vec = nullptr; int64_t nvec = 0; };
+
+struct pb_model {
+    pb_ctx* ctx = nullptr;
+    pb_cfg cfg{};
+    std::vector<PbSlot> slots;      // [(n_layers + 1)][PB_R_COUNT], index 0 = global
+    std::vector<int> kind, idx;     // per layer: 1 = full attention, 0 = DeltaNet; index among its kind
+    int n_lin = 0, n_attn = 0;
+    bool finalized = false;
+    int ep_rank = 0, ep_world = 1, e_lo = 0, e_hi = 0;
+    float* rope_inv = nullptr;
+    uint64_t weight_bytes_step = 0;
+};
+
+struct PbKv { uint32_t *kw = nullptr, *vw = nullptr; float *ks = nullptr, *vs = nullptr, *kr = nullptr, *vr = nullptr; int64_t* q4n = nullptr; };
+
+struct pb_state {
+    pb_model* m = nullptr;
+    int batch = 0;
+    int64_t pos_host = 0;
+    std::vector<void*> allocs;
+    int64_t* pos = nullptr; uint32_t* ids = nullptr; uint32_t* next = nullptr;
+    float *x = nullptr, *xin = nullptr, *proj = nullptr, *olin = nullptr, *att = nullptr, *rlogits = nullptr, *yout = nullptr;
+    uint32_t* xq = nullptr;
+    int *sel_e = nullptr, *n_used = nullptr, *used_e = nullptr, *used_off = nullptr, *ent_tok = nullptr, *ent_slot = nullptr;
+    float *sel_w = nullptr, *ent_w = nullptr, *h = nullptr, *h_sh = nullptr, *part = nullptr, *part_sh = nullptr, *logits = nullptr;
+    float *part_ml = nullptr, *part_acc = nullptr;
+    int nsplit = 1;
+    int64_t ldproj = 0, ring_cap = 0;
+    std::vector<float*> conv, ssm;
+    std::vector<PbKv> kv;
+    uint32_t* trace = nullptr; int64_t* trace_len = nullptr; int64_t trace_cap = 0;
+    uint32_t* pin_u32 = nullptr;   // pinned staging for ids / next tokens
+    cudaGraphExec_t graph = nullptr;
+    uint64_t steps = 0, kernels_per_step = 0;
+};
+
+static PbSlot& slot(pb_model* m, int layer, int role) { return m->slots[(size_t)(layer + 1) * PB_R_COUNT + role]; }
+static pb_qmat* M(pb_model* m, int layer, int role) { return slot(m, layer, role).mat; }
+static float* V(pb_model* m, int layer, int role) { return slot(m, layer, role).vec; }
+
+template <typename T>
+static int dalloc(pb_state* s, T** p, size_t n) {
+    pb_ctx* ctx = s->m->ctx;
+    void* q = nullptr;
+    PB_CUDA(ctx, cudaMalloc(&q, (n ? n : 1) * sizeof(T) + 256));
+    PB_CUDA(ctx, cudaMemsetAsync(q, 0, (n ? n : 1) * sizeof(T) + 256, ctx->stream));
+    s->allocs.push_back(q);
+    *p = (T*)q;
+    return PB_OK;
+}
 
 extern "C" {
-int pb_model_create(pb_ctx*, const pb_cfg*, pb_model**) { return PB_UNSUPPORTED; }
-int pb_model_set_tensor(pb_model*, int, int, pb_qmat*) { return PB_UNSUPPORTED; }
-int pb_model_set_vec(pb_model*, int, int, const float*, int64_t) { return PB_UNSUPPORTED; }
-int pb_model_finalize(pb_model*, int, int) { return PB_UNSUPPORTED; }
-int pb_model_destroy(pb_model*) { return PB_UNSUPPORTED; }
-int pb_state_create(pb_model*, int, pb_state**) { return PB_UNSUPPORTED; }
-int pb_state_destroy(pb_state*) { return PB_UNSUPPORTED; }
-int pb_state_fill_kv(pb_state*, int, int, const float*, const float*, int64_t) { return PB_UNSUPPORTED; }
-int pb_state_fill_kv_synth(pb_state*, int, int64_t, uint64_t) { return PB_UNSUPPORTED; }
-int pb_state_set_pos(pb_state*, int64_t) { return PB_UNSUPPORTED; }
-int pb_state_pos(const pb_state*, int64_t*) { return PB_UNSUPPORTED; }
-int pb_forward(pb_state*, const uint32_t*, int, float*) { return PB_UNSUPPORTED; }
-int pb_step_greedy(pb_state*, const uint32_t*, uint32_t*) { return PB_UNSUPPORTED; }
-int pb_decode_greedy(pb_state*, const uint32_t*, int, uint32_t*) { return PB_UNSUPPORTED; }
-int pb_verify(pb_state*, const uint32_t*, int, float*) { return PB_UNSUPPORTED; }
-int pb_keep(pb_state*, int, int) { return PB_UNSUPPORTED; }
-int pb_draft(pb_state*, int, uint32_t*, int*) { return PB_UNSUPPORTED; }
-int pb_state_snapshot(pb_state*, void*, size_t*) { return PB_UNSUPPORTED; }
-int pb_state_restore(pb_state*, const void*, size_t) { return PB_UNSUPPORTED; }
-int pb_caps_get(const pb_model*, pb_caps*) { return PB_UNSUPPORTED; }
-int pb_stats_get(const pb_state*, pb_stats*) { return PB_UNSUPPORTED; }
-int pb_moe_forward(pb_state*, int, const float*, int, float*, int32_t*) { return PB_UNSUPPORTED; }
-int pb_deltanet_step(pb_state*, int, const float*, float*) { return PB_UNSUPPORTED; }
-int pb_attn_step(pb_state*, int, const float*, float*) { return PB_UNSUPPORTED; }
-int pb_state_get_lin(pb_state*, int, float*, float*) { return PB_UNSUPPORTED; }
-int pb_state_set_lin(pb_state*, int, const float*, const float*) { return PB_UNSUPPORTED; }
-int pb_kv4_pack(pb_ctx*, const float*, int64_t, uint32_t*, float*) { return PB_UNSUPPORTED; }
-int pb_kv4_unpack(pb_ctx*, const uint32_t*, const float*, int64_t, float*) { return PB_UNSUPPORTED; }
+
+// ------------------------------------------------------------------------------------ model
+
+int pb_model_create(pb_ctx* ctx, const pb_cfg* cfg, pb_model** out) {
+    if (!ctx || !out) return PB_ERR_ARG;
+    *out = nullptr;
+    if (!cfg) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_create: null config");
+    const pb_cfg& c = *cfg;
+    if (c.n_layers <= 0 || c.d <= 0 || c.vocab <= 0 || c.max_ctx <= 0) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_create: non-positive size in config");
+    if (c.hc != 0) PB_FAIL(ctx, PB_UNSUPPORTED, "pb_model_create: hyper-connection streams (hc=%d) are not built yet; use hc=0 (pre-norm residual)", c.hc);
+    if (c.top_k > PB_MAX_TOPK || c.top_k > c.n_exp) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_create: top_k=%d with %d experts", c.top_k, c.n_exp);
+    if (c.kv_bits != 0 && c.kv_bits != 4) PB_FAIL(ctx, PB_UNSUPPORTED, "pb_model_create: kv_bits=%d (0 and 4 are built)", c.kv_bits);
+    if (c.kv_bits == 4 && c.kv_recent < 64) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_create: kv_recent must be at least 64");
+    pb_model* m = new (std::nothrow) pb_model();
+    if (!m) PB_FAIL(ctx, PB_ERR_OOM, "host allocation failed");
+    m->ctx = ctx; m->cfg = c;
+    m->slots.resize((size_t)(c.n_layers + 1) * PB_R_COUNT);
+    for (int il = 0; il < c.n_layers; il++) {
+        const bool full = c.full_every > 0 && (il + 1) % c.full_every == 0;   // :498
+        m->kind.push_back(full ? 1 : 0);
+        m->idx.push_back(full ? m->n_attn++ : m->n_lin++);
+    }
+    *out = m;
+    return PB_OK;
 }
+
+int pb_model_set_tensor(pb_model* m, int layer, int role, pb_qmat* mat) {
+    if (!m || !mat) return PB_ERR_ARG;
+    pb_ctx* ctx = m->ctx;
+    if (layer < -1 || layer >= m->cfg.n_layers || role < 0 || role >= PB_R_COUNT) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_set_tensor: layer %d role %d out of range", layer, role);
+    if (m->finalized) PB_FAIL(ctx, PB_ERR_STATE, "pb_model_set_tensor: model already finalized");
+    PbSlot& s = slot(m, layer, role);
+    if (s.mat) pb_qmat_free(s.mat);
+    s.mat = mat;
+    return PB_OK;
+}
+
+int pb_model_set_vec(pb_model* m, int layer, int role, const float* v, int64_t n) {
+    if (!m) return PB_ERR_ARG;
+    pb_ctx* ctx = m->ctx;
+    if (layer < -1 || layer >= m->cfg.n_layers || role < 0 || role >= PB_R_COUNT || !v || n <= 0) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_set_vec: bad argument (layer %d role %d n %lld)", layer, role, (long long)n);
+    if (m->finalized) PB_FAIL(ctx, PB_ERR_STATE, "pb_model_set_vec: model already finalized");
+    PbSlot& s = slot(m, layer, role);
+    if (s.vec) cudaFree(s.vec);
+    s.vec = nullptr;
+    PB_CUDA(ctx, cudaMalloc(&s.vec, (size_t)n * 4 + 256));
+    PB_CUDA(ctx, cudaMemcpyAsync(s.vec, v, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    s.nvec = n;
+    return PB_OK;
+}
+
+static int need_mat(pb_model* m, int il, int role, int64_t rows, int64_t cols, const char* name, bool quant_only) {
+    pb_ctx* ctx = m->ctx;
+    pb_qmat* q = M(m, il, role);
+    if (!q) PB_FAIL(ctx, PB_ERR_STATE, "layer %d: tensor %s is missing", il, name);
+    if ((rows > 0 && q->rows != rows) || q->cols != cols) PB_FAIL(ctx, PB_ERR_ARG, "layer %d: %s is %lld x %lld, expected %lld x %lld", il, name, (long long)q->rows, (long long)q->cols, (long long)rows, (long long)cols);
+    if (quant_only && !pb_gemvq_supported(q->type, (int)q->cols)) PB_FAIL(ctx, PB_UNSUPPORTED, "layer %d: %s has ggml type %d / %lld columns, which the fused path does not cover", il, name, q->type, (long long)q->cols);
+    return PB_OK;
+}
+static int need_vec(pb_model* m, int il, int role, int64_t n, const char* name) {
+    pb_ctx* ctx = m->ctx;
+    if (!V(m, il, role)) PB_FAIL(ctx, PB_ERR_STATE, "layer %d: vector %s is missing", il, name);
+    if (slot(m, il, role).nvec != n) PB_FAIL(ctx, PB_ERR_ARG, "layer %d: %s has %lld values, expected %lld", il, name, (long long)slot(m, il, role).nvec, (long long)n);
+    return PB_OK;
+}
+
+int pb_model_finalize(pb_model* m, int ep_rank, int ep_world) {
+    if (!m) return PB_ERR_ARG;
+    pb_ctx* ctx = m->ctx;
+    const pb_cfg& c = m->cfg;
+    if (ep_world < 1 || ep_rank < 0 || ep_rank >= ep_world || c.n_exp % ep_world) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_finalize: rank %d of %d with %d experts", ep_rank, ep_world, c.n_exp);
+    m->ep_rank = ep_rank; m->ep_world = ep_world;
+    m->e_lo = ep_rank * (c.n_exp / ep_world); m->e_hi = m->e_lo + c.n_exp / ep_world;
+    const int ch = 2 * c.lin_nk * c.lin_dk + c.lin_nv * c.lin_dv, row = c.n_kv * c.hd;
+    uint64_t wb = 0;
+    PB_TRY(need_mat(m, -1, PB_R_TOKEN_EMBD, c.vocab, c.d, "token_embd", false));
+    if (!M(m, -1, PB_R_OUTPUT)) { /* falls back to token_embd (:511) */ }
+    else PB_TRY(need_mat(m, -1, PB_R_OUTPUT, c.vocab, c.d, "output", true));
+    if (!pb_gemvq_supported((M(m, -1, PB_R_OUTPUT) ? M(m, -1, PB_R_OUTPUT) : M(m, -1, PB_R_TOKEN_EMBD))->type, c.d)) PB_FAIL(ctx, PB_UNSUPPORTED, "lm-head type is not covered by the fused path");
+    PB_TRY(need_vec(m, -1, PB_R_OUT_NORM, c.d, "output_norm"));
+    wb += (M(m, -1, PB_R_OUTPUT) ? M(m, -1, PB_R_OUTPUT) : M(m, -1, PB_R_TOKEN_EMBD))->nbytes;
+    for (int il = 0; il < c.n_layers; il++) {
+        PB_TRY(need_vec(m, il, PB_R_ATTN_NORM, c.d, "attn_norm"));
+        PB_TRY(need_vec(m, il, PB_R_FFN_NORM, c.d, "ffn_norm"));
+        if (m->kind[il]) {
+            PB_TRY(need_mat(m, il, PB_R_ATTN_Q, (int64_t)c.n_head * 2 * c.hd, c.d, "attn_q", true));
+            PB_TRY(need_mat(m, il, PB_R_ATTN_K, row, c.d, "attn_k", true));
+            PB_TRY(need_mat(m, il, PB_R_ATTN_V, row, c.d, "attn_v", true));
+            PB_TRY(need_mat(m, il, PB_R_ATTN_O, c.d, (int64_t)c.n_head * c.hd, "attn_output", true));
+            PB_TRY(need_vec(m, il, PB_R_ATTN_Q_NORM, c.hd, "attn_q_norm"));
+            PB_TRY(need_vec(m, il, PB_R_ATTN_K_NORM, c.hd, "attn_k_norm"));
+            if (M(m, il, PB_R_ATTN_Q)->type != M(m, il, PB_R_ATTN_K)->type || M(m, il, PB_R_ATTN_Q)->type != M(m, il, PB_R_ATTN_V)->type)
+                PB_FAIL(ctx, PB_UNSUPPORTED, "layer %d: attn_q/k/v must share one ggml type", il);
+            wb += M(m, il, PB_R_ATTN_Q)->nbytes + M(m, il, PB_R_ATTN_K)->nbytes + M(m, il, PB_R_ATTN_V)->nbytes + M(m, il, PB_R_ATTN_O)->nbytes;
+        } else {
+            PB_TRY(need_mat(m, il, PB_R_LIN_QKV, ch, c.d, "attn_qkv", true));
+            PB_TRY(need_mat(m, il, PB_R_LIN_Z, (int64_t)c.lin_nv * c.lin_dv, c.d, "attn_gate", true));
+            PB_TRY(need_mat(m, il, PB_R_LIN_BETA, c.lin_nv, c.d, "ssm_beta", true));
+            PB_TRY(need_mat(m, il, PB_R_LIN_ALPHA, c.lin_nv, c.d, "ssm_alpha", true));
+            PB_TRY(need_mat(m, il, PB_R_LIN_OUT, c.d, (int64_t)c.lin_nv * c.lin_dv, "ssm_out", true));
+            PB_TRY(need_vec(m, il, PB_R_LIN_A, c.lin_nv, "ssm_a"));
+            PB_TRY(need_vec(m, il, PB_R_LIN_DT, c.lin_nv, "ssm_dt.bias"));
+            PB_TRY(need_vec(m, il, PB_R_LIN_CONV, (int64_t)ch * c.conv_k, "ssm_conv1d"));
+            PB_TRY(need_vec(m, il, PB_R_LIN_NORM, c.lin_dv, "ssm_norm"));
+            const int t0 = M(m, il, PB_R_LIN_QKV)->type;
+            if (M(m, il, PB_R_LIN_Z)->type != t0 || M(m, il, PB_R_LIN_BETA)->type != t0 || M(m, il, PB_R_LIN_ALPHA)->type != t0)
+                PB_FAIL(ctx, PB_UNSUPPORTED, "layer %d: attn_qkv/attn_gate/ssm_beta/ssm_alpha must share one ggml type", il);
+            wb += M(m, il, PB_R_LIN_QKV)->nbytes + M(m, il, PB_R_LIN_Z)->nbytes + M(m, il, PB_R_LIN_BETA)->nbytes + M(m, il, PB_R_LIN_ALPHA)->nbytes + M(m, il, PB_R_LIN_OUT)->nbytes;
+        }
+        // MoE: the router is f32; expert tensors hold all experts or this rank's contiguous shard
+        PB_TRY(need_mat(m, il, PB_R_ROUTER, c.n_exp, c.d, "ffn_gate_inp", false));
+        if (M(m, il, PB_R_ROUTER)->type != PB_T_F32) PB_FAIL(ctx, PB_UNSUPPORTED, "layer %d: the router must be f32", il);
+        const int64_t nloc = c.n_exp / ep_world;
+        const int roles[3] = {PB_R_EXP_GATE, PB_R_EXP_UP, PB_R_EXP_DOWN};
+        for (int r = 0; r < 3; r++) {
+            pb_qmat* q = M(m, il, roles[r]);
+            const int64_t per = r < 2 ? c.ff_exp : c.d, cols = r < 2 ? c.d : c.ff_exp;
+            if (!q) PB_FAIL(ctx, PB_ERR_STATE, "layer %d: expert tensor %d is missing", il, r);
+            if (q->cols != cols || (q->rows != per * c.n_exp && q->rows != per * nloc)) PB_FAIL(ctx, PB_ERR_ARG, "layer %d: expert tensor %d is %lld x %lld", il, r, (long long)q->rows, (long long)q->cols);
+            if (!pb_gemvq_supported(q->type, (int)cols)) PB_FAIL(ctx, PB_UNSUPPORTED, "layer %d: expert tensor type %d is not covered by the fused path", il, q->type);
+            wb += (uint64_t)c.top_k * per * q->row_bytes;
+        }
+        if (M(m, il, PB_R_EXP_GATE)->type != M(m, il, PB_R_EXP_UP)->type || M(m, il, PB_R_EXP_GATE)->rows != M(m, il, PB_R_EXP_UP)->rows) PB_FAIL(ctx, PB_UNSUPPORTED, "layer %d: gate and up experts must share type and shape", il);
+        if (c.ff_sh != c.ff_exp) PB_FAIL(ctx, PB_UNSUPPORTED, "shared expert width %d differs from the routed width %d", c.ff_sh, c.ff_exp);
+        PB_TRY(need_mat(m, il, PB_R_SH_GATE, c.ff_sh, c.d, "ffn_gate_shexp", true));
+        PB_TRY(need_mat(m, il, PB_R_SH_UP, c.ff_sh, c.d, "ffn_up_shexp", true));
+        PB_TRY(need_mat(m, il, PB_R_SH_DOWN, c.d, c.ff_sh, "ffn_down_shexp", true));
+        if (M(m, il, PB_R_SH_GATE)->type != M(m, il, PB_R_EXP_GATE)->type || M(m, il, PB_R_SH_UP)->type != M(m, il, PB_R_EXP_GATE)->type || M(m, il, PB_R_SH_DOWN)->type != M(m, il, PB_R_EXP_DOWN)->type)
+            PB_FAIL(ctx, PB_UNSUPPORTED, "layer %d: shared-expert tensors must have the types of the routed experts", il);
+        PB_TRY(need_vec(m, il, PB_R_SH_GATE_INP, c.d, "ffn_gate_inp_shexp"));
+        wb += M(m, il, PB_R_ROUTER)->nbytes + M(m, il, PB_R_SH_GATE)->nbytes + M(m, il, PB_R_SH_UP)->nbytes + M(m, il, PB_R_SH_DOWN)->nbytes;
+    }
+    // rope_inv, qn_ctx.rs:168 (unscaled): base^(-2i/n_rot)
+    std::vector<float> inv((size_t)c.n_rot / 2 + 1);
+    for (int i = 0; i < c.n_rot / 2; i++) inv[i] = powf(c.rope_base, -(2.0f * (float)i) / (float)c.n_rot);
+    PB_CUDA(ctx, cudaMalloc(&m->rope_inv, inv.size() * 4));
+    PB_CUDA(ctx, cudaMemcpy(m->rope_inv, inv.data(), inv.size() * 4, cudaMemcpyHostToDevice));
+    m->weight_bytes_step = wb;
+    m->finalized = true;
+    return PB_OK;
+}
+
+int pb_model_destroy(pb_model* m) {
+    if (!m) return PB_OK;
+    cudaSetDevice(m->ctx->device);
+    cudaStreamSynchronize(m->ctx->stream);
+    for (auto& s : m->slots) { if (s.mat) pb_qmat_free(s.mat); if (s.vec) cudaFree(s.vec); }
+    if (m->rope_inv) cudaFree(m->rope_inv);
+    delete m;
+    return PB_OK;
+}
+
+int pb_caps_get(const pb_model* m, pb_caps* caps) {
+    if (!m || !caps) return PB_ERR_ARG;
+    caps->multi_ok = 1; caps->max_window = 8; caps->max_ctx = m->cfg.max_ctx; caps->max_batch = 1024; caps->ep_world = m->ep_world;
+    return PB_OK;
+}
+
+// ------------------------------------------------------------------------------------ state
+
+int pb_state_create(pb_model* m, int batch, pb_state** out) {
+    if (!m || !out) return PB_ERR_ARG;
+    pb_ctx* ctx = m->ctx;
+    *out = nullptr;
+    if (!m->finalized) PB_FAIL(ctx, PB_ERR_STATE, "pb_state_create: call pb_model_finalize first");
+    if (batch < 1 || batch > 1024) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_create: batch %d outside 1..1024", batch);
+    const pb_cfg& c = m->cfg;
+    pb_state* s = new (std::nothrow) pb_state();
+    if (!s) PB_FAIL(ctx, PB_ERR_OOM, "host allocation failed");
+    s->m = m; s->batch = batch;
+    const int B = batch;
+    const int ch = 2 * c.lin_nk * c.lin_dk + c.lin_nv * c.lin_dv;
+    const int64_t lin_proj = (int64_t)ch + (int64_t)c.lin_nv * c.lin_dv + 2 * c.lin_nv;
+    const int64_t att_proj = (int64_t)c.n_head * 2 * c.hd + 2 * (int64_t)c.n_kv * c.hd;
+    s->ldproj = ((lin_proj > att_proj ? lin_proj : att_proj) + 3) & ~(int64_t)3;
+    const int64_t wide = (int64_t)c.lin_nv * c.lin_dv > (int64_t)c.n_head * c.hd ? (int64_t)c.lin_nv * c.lin_dv : (int64_t)c.n_head * c.hd;
+    int rc = PB_OK;
+#define A(p, n) if (rc == PB_OK) rc = dalloc(s, &s->p, (size_t)(n))
+    A(pos, B); A(ids, B); A(next, B);
+    A(x, (size_t)B * c.d); A(xin, (size_t)B * (wide > c.d ? wide : c.d)); A(yout, (size_t)B * c.d);
+    A(proj, (size_t)B * s->ldproj); A(olin, (size_t)B * wide); A(att, (size_t)B * wide);
+    A(rlogits, (size_t)B * (c.n_exp + 1));
+    A(xq, (size_t)B * pb_xq_words(c.d));
+    A(sel_e, (size_t)B * c.top_k); A(sel_w, (size_t)B * c.top_k); A(n_used, 4); A(used_e, c.n_exp + 1); A(used_off, c.n_exp + 2);
+    A(ent_tok, (size_t)B * c.top_k); A(ent_slot, (size_t)B * c.top_k); A(ent_w, (size_t)B * c.top_k);
+    A(h, (size_t)B * c.top_k * c.ff_exp); A(h_sh, (size_t)B * c.ff_sh);
+    A(part, (size_t)B * c.top_k * c.d); A(part_sh, (size_t)B * c.d);
+    A(logits, (size_t)B * c.vocab);
+    s->trace_cap = 4096;
+    A(trace, (size_t)s->trace_cap * B); A(trace_len, 2);
+    // attention: enough splits to cover the SMs about twice over
+    const int G = c.n_kv > 0 ? c.n_head / c.n_kv : 1;
+    int ns = (2 * ctx->sm_count + c.n_kv * B - 1) / (c.n_kv * B > 0 ? c.n_kv * B : 1);
+    if (ns < 1) ns = 1;
+    if (ns > 128) ns = 128;
+    s->nsplit = ns;
+    A(part_ml, (size_t)B * c.n_kv * ns * G * 2); A(part_acc, (size_t)B * c.n_kv * ns * G * c.hd);
+    s->conv.assign(m->n_lin, nullptr); s->ssm.assign(m->n_lin, nullptr); s->kv.assign(m->n_attn, PbKv());
+    for (int i = 0; i < m->n_lin && rc == PB_OK; i++) {
+        rc = dalloc(s, &s->conv[i], (size_t)B * c.conv_k * ch);
+        if (rc == PB_OK) rc = dalloc(s, &s->ssm[i], (size_t)B * c.lin_nv * c.lin_dk * c.lin_dv);
+    }
+    const int64_t rowh = c.hd;
+    s->ring_cap = c.kv_bits == 4 ? (int64_t)c.kv_recent + 64 : (int64_t)c.max_ctx;
+    for (int i = 0; i < m->n_attn && rc == PB_OK; i++) {
+        PbKv& k = s->kv[i];
+        const size_t heads = (size_t)B * c.n_kv;
+        rc = dalloc(s, &k.kr, heads * s->ring_cap * rowh);
+        if (rc == PB_OK) rc = dalloc(s, &k.vr, heads * s->ring_cap * rowh);
+        if (rc == PB_OK) rc = dalloc(s, &k.q4n, (size_t)B);
+        const size_t packed_pos = c.kv_bits == 4 ? (size_t)c.max_ctx : 1;
+        if (rc == PB_OK) rc = dalloc(s, &k.kw, heads * packed_pos * (rowh / 8));
+        if (rc == PB_OK) rc = dalloc(s, &k.vw, heads * packed_pos * (rowh / 8));
+        if (rc == PB_OK) rc = dalloc(s, &k.ks, heads * packed_pos * (rowh / 32));
+        if (rc == PB_OK) rc = dalloc(s, &k.vs, heads * packed_pos * (rowh / 32));
+    }
+#undef A
+    if (rc == PB_OK && cudaMallocHost(&s->pin_u32, (size_t)(s->trace_cap + 2) * B * 4) != cudaSuccess) { ctx->err = "pinned allocation failed"; rc = PB_ERR_OOM; }
+    if (rc == PB_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) { ctx->err = "stream sync failed"; rc = PB_ERR_CUDA; }
+    if (rc != PB_OK) { pb_state_destroy(s); return rc; }
+    *out = s;
+    return PB_OK;
+}
+
+int pb_state_destroy(pb_state* s) {
+    if (!s) return PB_OK;
+    cudaSetDevice(s->m->ctx->device);
+    cudaStreamSynchronize(s->m->ctx->stream);
+    if (s->graph) cudaGraphExecDestroy(s->graph);
+    for (void* p : s->allocs) cudaFree(p);
+    if (s->pin_u32) cudaFreeHost(s->pin_u32);
+    delete s;
+    return PB_OK;
+}
+
+int pb_state_set_pos(pb_state* s, int64_t pos) {
+    if (!s) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx;
+    if (pos < 0 || pos > s->m->cfg.max_ctx) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_set_pos: %lld outside 0..%d", (long long)pos, s->m->cfg.max_ctx);
+    std::vector<int64_t> v((size_t)s->batch, pos);
+    PB_CUDA(ctx, cudaMemcpyAsync(s->pos, v.data(), v.size() * 8, cudaMemcpyHostToDevice, ctx->stream));
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    s->pos_host = pos;
+    return PB_OK;
+}
+int pb_state_pos(const pb_state* s, int64_t* pos) { if (!s || !pos) return PB_ERR_ARG; *pos = s->pos_host; return PB_OK; }
+
+// ---- layer pieces -----------------------------------------------------------------------------
+
+static void seg(PbGemvQArgs& a, int i, pb_qmat* q, int64_t yoff) { a.seg[i].w = q->data; a.seg[i].rows = q->rows; a.seg[i].yoff = yoff; }
+
+// y (+)= W_segs . act(x) for all batch columns, in tiles of 16 columns
+static int gemv_cols(pb_ctx* ctx, PbGemvQArgs a, int B) {
+    const float* x = a.x; float* y = a.y; const float* z = a.z; const uint32_t* xq = a.xq_in;
+    for (int b0 = 0; b0 < B; b0 += 16) {
+        a.t = B - b0 < 16 ? B - b0 : 16;
+        a.x = x ? x + (int64_t)b0 * a.ldx : nullptr; a.y = y + (int64_t)b0 * a.ldy; a.z = z ? z + (int64_t)b0 * a.ldz : nullptr;
+        a.xq_in = xq ? xq + (size_t)b0 * pb_xq_words(a.cols) : nullptr;
+        PB_TRY(pb_launch_gemvq(ctx, a));
+    }
+    return PB_OK;
+}
+
+// Gated DeltaNet mixer: x_in (normalized when norm_w == null) -> y (stored or added)
+static int run_lin(pb_state* s, int il, const float* x_in, const float* norm_w, float* y, int64_t ldy, int accumulate) {
+    pb_model* m = s->m; pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg; const int B = s->batch, li = m->idx[il];
+    const int ch = 2 * c.lin_nk * c.lin_dk + c.lin_nv * c.lin_dv, w = c.lin_nv * c.lin_dv;
+    PbGemvQArgs a; memset(&a, 0, sizeof a);
+    a.type = M(m, il, PB_R_LIN_QKV)->type; a.cols = c.d; a.nseg = 4;
+    seg(a, 0, M(m, il, PB_R_LIN_QKV), 0); seg(a, 1, M(m, il, PB_R_LIN_Z), ch); seg(a, 2, M(m, il, PB_R_LIN_BETA), ch + w); seg(a, 3, M(m, il, PB_R_LIN_ALPHA), ch + w + c.lin_nv);
+    a.x = x_in; a.ldx = c.d; a.y = s->proj; a.ldy = s->ldproj; a.mode = norm_w ? PB_ACT_NORM : PB_ACT_PLAIN; a.norm_w = norm_w; a.eps = c.eps;
+    PB_TRY(gemv_cols(ctx, a, B));
+    PbDeltaParams d; memset(&d, 0, sizeof d);
+    d.proj = s->proj; d.ldp = s->ldproj; d.conv_w = V(m, il, PB_R_LIN_CONV); d.a = V(m, il, PB_R_LIN_A); d.dt = V(m, il, PB_R_LIN_DT);
+    d.conv = s->conv[li]; d.ssm = s->ssm[li]; d.pos = s->pos; d.out = s->olin; d.ldo = w;
+    d.nk = c.lin_nk; d.nv = c.lin_nv; d.dk = c.lin_dk; d.dv = c.lin_dv; d.conv_k = c.conv_k; d.batch = B;
+    PB_TRY(pb_launch_deltanet(ctx, d));
+    PbGemvQArgs o; memset(&o, 0, sizeof o);
+    o.type = M(m, il, PB_R_LIN_OUT)->type; o.cols = w; o.nseg = 1; seg(o, 0, M(m, il, PB_R_LIN_OUT), 0);
+    o.x = s->olin; o.ldx = w; o.y = y; o.ldy = ldy; o.mode = PB_ACT_GNORM; o.norm_w = V(m, il, PB_R_LIN_NORM); o.z = s->proj + ch; o.ldz = s->ldproj; o.head_dim = c.lin_dv; o.eps = c.eps; o.accumulate = accumulate;
+    return gemv_cols(ctx, o, B);
+}
+
+static void attn_params(pb_state* s, int il, PbAttnParams& p) {
+    pb_model* m = s->m; const pb_cfg& c = m->cfg; const PbKv& k = s->kv[m->idx[il]];
+    memset(&p, 0, sizeof p);
+    p.proj = s->proj; p.ldp = s->ldproj; p.qn = V(m, il, PB_R_ATTN_Q_NORM); p.kn = V(m, il, PB_R_ATTN_K_NORM); p.rope_inv = m->rope_inv;
+    p.n_rot = c.n_rot; p.eps = c.eps; p.n_head = c.n_head; p.n_kv = c.n_kv; p.hd = c.hd;
+    p.kw = k.kw; p.ks = k.ks; p.vw = k.vw; p.vs = k.vs; p.kr = k.kr; p.vr = k.vr;
+    p.max_ctx = c.kv_bits == 4 ? c.max_ctx : 1; p.ring_cap = s->ring_cap; p.kv_bits = c.kv_bits; p.kv_recent = c.kv_recent;
+    p.pos = s->pos; p.q4n = k.q4n; p.part_ml = s->part_ml; p.part_acc = s->part_acc; p.nsplit = s->nsplit;
+    p.att = s->att; p.lda = (int64_t)c.n_head * c.hd; p.batch = s->batch;
+}
+
+static int run_attn(pb_state* s, int il, const float* x_in, const float* norm_w, float* y, int64_t ldy, int accumulate) {
+    pb_model* m = s->m; pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg; const int B = s->batch;
+    const int64_t nq = (int64_t)c.n_head * 2 * c.hd, row = (int64_t)c.n_kv * c.hd;
+    PbGemvQArgs a; memset(&a, 0, sizeof a);
+    a.type = M(m, il, PB_R_ATTN_Q)->type; a.cols = c.d; a.nseg = 3;
+    seg(a, 0, M(m, il, PB_R_ATTN_Q), 0); seg(a, 1, M(m, il, PB_R_ATTN_K), nq); seg(a, 2, M(m, il, PB_R_ATTN_V), nq + row);
+    a.x = x_in; a.ldx = c.d; a.y = s->proj; a.ldy = s->ldproj; a.mode = norm_w ? PB_ACT_NORM : PB_ACT_PLAIN; a.norm_w = norm_w; a.eps = c.eps;
+    PB_TRY(gemv_cols(ctx, a, B));
+    PbAttnParams p; attn_params(s, il, p);
+    PB_TRY(pb_launch_kv_append(ctx, p));
+    PB_TRY(pb_launch_attn(ctx, p));
+    PbGemvQArgs o; memset(&o, 0, sizeof o);
+    o.type = M(m, il, PB_R_ATTN_O)->type; o.cols = c.n_head * c.hd; o.nseg = 1; seg(o, 0, M(m, il, PB_R_ATTN_O), 0);
+    o.x = s->att; o.ldx = (int64_t)c.n_head * c.hd; o.y = y; o.ldy = ldy; o.mode = PB_ACT_PLAIN; o.accumulate = accumulate;
+    return gemv_cols(ctx, o, B);
+}
+
+// MoE block on t tokens: x_in [t][d] (normalized when norm_w == null) -> y (stored or added)
+static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, int t, float* y, int64_t ldy, int accumulate) {
+    pb_model* m = s->m; pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg;
+    PbRouterParams r; memset(&r, 0, sizeof r);
+    r.x = x_in; r.ldx = c.d; r.t = t; r.cols = c.d; r.norm_w = norm_w; r.eps = c.eps;
+    r.router = reinterpret_cast<const float*>(M(m, il, PB_R_ROUTER)->data); r.sh_gate_inp = V(m, il, PB_R_SH_GATE_INP); r.n_exp = c.n_exp;
+    r.logits = s->rlogits; r.xq_out = s->xq;
+    PB_TRY(pb_launch_router(ctx, r));
+    PbRouteParams q; memset(&q, 0, sizeof q);
+    q.logits = s->rlogits; q.t = t; q.n_exp = c.n_exp; q.top_k = c.top_k; q.e_lo = m->e_lo; q.e_hi = m->e_hi;
+    q.sel_e = s->sel_e; q.sel_w = s->sel_w; q.n_used = s->n_used; q.used_e = s->used_e; q.used_off = s->used_off;
+    q.ent_tok = s->ent_tok; q.ent_slot = s->ent_slot; q.ent_w = s->ent_w;
+    PB_TRY(pb_launch_route(ctx, q));
+    if (m->ep_world > 1) PB_CUDA(ctx, cudaMemsetAsync(s->part, 0, (size_t)t * c.top_k * c.d * 4, ctx->stream));
+    PbExpertParams e; memset(&e, 0, sizeof e);
+    e.n_used = s->n_used; e.used_e = s->used_e; e.used_off = s->used_off; e.ent_tok = s->ent_tok; e.ent_slot = s->ent_slot; e.ent_w = s->ent_w;
+    e.xq = s->xq; e.h = s->h; e.h_sh = s->h_sh; e.part = s->part; e.part_sh = s->part_sh;
+    e.has_shared = 1; e.t = t; e.top_k = c.top_k; e.n_exp = c.n_exp;
+    pb_qmat* g = M(m, il, PB_R_EXP_GATE);
+    e.e_base = g->rows == (int64_t)c.ff_exp * c.n_exp ? 0 : m->e_lo;
+    e.w_a = g->data; e.w_b = M(m, il, PB_R_EXP_UP)->data; e.sh_a = M(m, il, PB_R_SH_GATE)->data; e.sh_b = M(m, il, PB_R_SH_UP)->data;
+    e.rows_e = c.ff_exp; e.rows_sh = c.ff_sh;
+    PB_TRY(pb_launch_expert_gu(ctx, e, g->type, c.d));
+    pb_qmat* dn = M(m, il, PB_R_EXP_DOWN);
+    e.e_base = dn->rows == (int64_t)c.d * c.n_exp ? 0 : m->e_lo;
+    e.w_a = dn->data; e.w_b = nullptr; e.sh_a = M(m, il, PB_R_SH_DOWN)->data; e.sh_b = nullptr;
+    e.rows_e = c.d; e.rows_sh = c.d;
+    PB_TRY(pb_launch_expert_down(ctx, e, dn->type, c.ff_exp));
+    PbCombineParams k; memset(&k, 0, sizeof k);
+    k.part = s->part; k.part_sh = s->part_sh; k.logits = s->rlogits; k.t = t; k.d = c.d; k.top_k = c.top_k; k.n_exp = c.n_exp;
+    k.y = y; k.ldy = ldy; k.accumulate = accumulate;
+    return pb_launch_moe_combine(ctx, k);
+}
+
+// one decode step for every sequence of the batch, ids already in s->ids
+static int run_step(pb_state* s) {
+    pb_model* m = s->m; pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg; const int B = s->batch;
+    pb_qmat* embd = M(m, -1, PB_R_TOKEN_EMBD);
+    PB_TRY(pb_launch_embed(ctx, embd->type, embd->data, embd->rows, c.d, s->ids, B, s->x, c.d));
+    for (int il = 0; il < c.n_layers; il++) {
+        if (m->kind[il]) PB_TRY(run_attn(s, il, s->x, V(m, il, PB_R_ATTN_NORM), s->x, c.d, 1));
+        else PB_TRY(run_lin(s, il, s->x, V(m, il, PB_R_ATTN_NORM), s->x, c.d, 1));
+        PB_TRY(run_moe(s, il, s->x, V(m, il, PB_R_FFN_NORM), B, s->x, c.d, 1));
+    }
+    pb_qmat* out = M(m, -1, PB_R_OUTPUT) ? M(m, -1, PB_R_OUTPUT) : embd;
+    PbGemvQArgs a; memset(&a, 0, sizeof a);
+    a.type = out->type; a.cols = c.d; a.nseg = 1; seg(a, 0, out, 0);
+    a.x = s->x; a.ldx = c.d; a.y = s->logits; a.ldy = c.vocab; a.mode = PB_ACT_NORM; a.norm_w = V(m, -1, PB_R_OUT_NORM); a.eps = c.eps;
+    PB_TRY(gemv_cols(ctx, a, B));
+    PB_TRY(pb_launch_argmax(ctx, s->logits, c.vocab, c.vocab, B, s->next));
+    return pb_launch_advance(ctx, s->pos, B, s->next, s->ids, s->trace, s->trace_len, s->trace_cap);
+}
+
+// Replays the step graph (captured on first use after one eager warm-up step would be wasteful:
+// the first call runs eagerly and also serves as the configuration pass for kernel attributes).
+static int step_once(pb_state* s) {
+    pb_ctx* ctx = s->m->ctx;
+    if (s->pos_host + 1 > s->m->cfg.max_ctx) PB_FAIL(ctx, PB_ERR_STATE, "context is full (%d positions)", s->m->cfg.max_ctx);
+    if (s->graph) {
+        PB_CUDA(ctx, cudaGraphLaunch(s->graph, ctx->stream));
+        ctx->kernels_launched += s->kernels_per_step;
+    } else if (s->steps == 0) {
+        const uint64_t k0 = ctx->kernels_launched;
+        PB_TRY(run_step(s));
+        s->kernels_per_step = ctx->kernels_launched - k0;
+    } else {
+        cudaGraph_t g = nullptr;
+        PB_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+        const uint64_t k0 = ctx->kernels_launched;
+        const int rc = run_step(s);
+        ctx->kernels_launched = k0;
+        cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+        if (rc != PB_OK) { if (g) cudaGraphDestroy(g); return rc; }
+        if (e != cudaSuccess) PB_FAIL(ctx, PB_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+        e = cudaGraphInstantiate(&s->graph, g, 0);
+        cudaGraphDestroy(g);
+        if (e != cudaSuccess) { s->graph = nullptr; PB_FAIL(ctx, PB_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e)); }
+        PB_CUDA(ctx, cudaGraphLaunch(s->graph, ctx->stream));
+        ctx->kernels_launched += s->kernels_per_step;
+    }
+    s->steps++; s->pos_host++;
+    return PB_OK;
+}
+
+int pb_forward(pb_state* s, const uint32_t* ids_host, int t, float* logits_host) {
+    if (!s) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx;
+    if (!ids_host || !logits_host || t < 1) PB_FAIL(ctx, PB_ERR_ARG, "pb_forward: bad argument");
+    const int B = s->batch;
+    for (int j = 0; j < t; j++) {
+        for (int b = 0; b < B; b++) s->pin_u32[b] = ids_host[(size_t)b * t + j];
+        PB_CUDA(ctx, cudaMemcpyAsync(s->ids, s->pin_u32, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
+        PB_TRY(step_once(s));
+        if (j + 1 < t) PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // the pinned id buffer is reused
+    }
+    PB_CUDA(ctx, cudaMemcpyAsync(logits_host, s->logits, (size_t)B * s->m->cfg.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return pb_sync_check(ctx, "pb_forward");
+}
+
+int pb_step_greedy(pb_state* s, const uint32_t* tok_host, uint32_t* next_host) {
+    if (!s) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx;
+    if (!tok_host || !next_host) PB_FAIL(ctx, PB_ERR_ARG, "pb_step_greedy: null buffer");
+    const int B = s->batch;
+    memcpy(s->pin_u32, tok_host, (size_t)B * 4);
+    PB_CUDA(ctx, cudaMemcpyAsync(s->ids, s->pin_u32, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
+    PB_TRY(step_once(s));
+    PB_CUDA(ctx, cudaMemcpyAsync(s->pin_u32 + B, s->next, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    PB_TRY(pb_sync_check(ctx, "pb_step_greedy"));
+    memcpy(next_host, s->pin_u32 + B, (size_t)B * 4);
+    return PB_OK;
+}
+
+int pb_decode_greedy(pb_state* s, const uint32_t* tok_host, int n, uint32_t* out_host) {
+    if (!s) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx;
+    if (!tok_host || !out_host || n < 1) PB_FAIL(ctx, PB_ERR_ARG, "pb_decode_greedy: bad argument");
+    if (n > s->trace_cap) PB_FAIL(ctx, PB_ERR_ARG, "pb_decode_greedy: at most %lld tokens per call", (long long)s->trace_cap);
+    const int B = s->batch;
+    memcpy(s->pin_u32, tok_host, (size_t)B * 4);
+    PB_CUDA(ctx, cudaMemcpyAsync(s->ids, s->pin_u32, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
+    PB_CUDA(ctx, cudaMemsetAsync(s->trace_len, 0, 8, ctx->stream));
+    for (int j = 0; j < n; j++) PB_TRY(step_once(s));
+    PB_CUDA(ctx, cudaMemcpyAsync(s->pin_u32 + 2 * B, s->trace, (size_t)n * B * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    PB_TRY(pb_sync_check(ctx, "pb_decode_greedy"));
+    for (int j = 0; j < n; j++) for (int b = 0; b < B; b++) out_host[(size_t)b * n + j] = s->pin_u32[2 * B + (size_t)j * B + b];
+    return PB_OK;
+}
+
+// verify / keep / draft / snapshot: declared surface, built in a later step of this file's history
+int pb_verify(pb_state* s, const uint32_t*, int, float*) { if (!s) return PB_ERR_ARG; PB_FAIL(s->m->ctx, PB_UNSUPPORTED, "pb_verify is not built yet"); }
+int pb_keep(pb_state* s, int, int) { if (!s) return PB_ERR_ARG; PB_FAIL(s->m->ctx, PB_UNSUPPORTED, "pb_keep is not built yet"); }
+int pb_draft(pb_state* s, int, uint32_t*, int* n) { if (!s) return PB_ERR_ARG; if (n) *n = 0; PB_FAIL(s->m->ctx, PB_UNSUPPORTED, "no drafter: use the caller's n-gram drafter"); }
+int pb_state_snapshot(pb_state* s, void*, size_t*) { if (!s) return PB_ERR_ARG; PB_FAIL(s->m->ctx, PB_UNSUPPORTED, "pb_state_snapshot is not built yet"); }
+int pb_state_restore(pb_state* s, const void*, size_t) { if (!s) return PB_ERR_ARG; PB_FAIL(s->m->ctx, PB_UNSUPPORTED, "pb_state_restore is not built yet"); }
+
+int pb_stats_get(const pb_state* s, pb_stats* out) {
+    if (!s || !out) return PB_ERR_ARG;
+    const pb_cfg& c = s->m->cfg;
+    out->steps = s->steps; out->kernels_launched = s->kernels_per_step;
+    out->weight_bytes_per_step = s->m->weight_bytes_step;
+    const uint64_t len = (uint64_t)s->pos_host;
+    const uint64_t packed = c.kv_bits == 4 && len > (uint64_t)c.kv_recent ? ((len - c.kv_recent) / 64) * 64 : 0;
+    out->kv_bytes_per_step = (uint64_t)s->m->n_attn * s->batch * 2 * c.n_kv * (packed * (c.hd / 2 + c.hd / 8) + (len - packed) * c.hd * 4);
+    out->state_bytes_per_step = (uint64_t)s->m->n_lin * s->batch * 2 * ((uint64_t)c.lin_nv * c.lin_dk * c.lin_dv * 4);
+    return PB_OK;
+}
+
+// ------------------------------------------------------------------------------------ layer-level entry points
+
+static int layer_ok(pb_state* s, int layer, int want_kind, const char* who) {
+    pb_ctx* ctx = s->m->ctx;
+    if (layer < 0 || layer >= s->m->cfg.n_layers) PB_FAIL(ctx, PB_ERR_ARG, "%s: layer %d out of range", who, layer);
+    if (want_kind >= 0 && s->m->kind[layer] != want_kind) PB_FAIL(ctx, PB_ERR_ARG, "%s: layer %d is not a %s layer", who, layer, want_kind ? "full-attention" : "DeltaNet");
+    return PB_OK;
+}
+
+int pb_moe_forward(pb_state* s, int layer, const float* x_host, int t, float* y_host, int32_t* sel_host) {
+    if (!s) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    PB_TRY(layer_ok(s, layer, -1, "pb_moe_forward"));
+    if (!x_host || !y_host || t < 0 || t > s->batch) PB_FAIL(ctx, PB_ERR_ARG, "pb_moe_forward: t=%d (state batch %d)", t, s->batch);
+    if (t == 0) return PB_OK;
+    PB_CUDA(ctx, cudaMemcpyAsync(s->xin, x_host, (size_t)t * c.d * 4, cudaMemcpyHostToDevice, ctx->stream));
+    PB_TRY(run_moe(s, layer, s->xin, nullptr, t, s->yout, c.d, 0));
+    PB_CUDA(ctx, cudaMemcpyAsync(y_host, s->yout, (size_t)t * c.d * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (sel_host) PB_CUDA(ctx, cudaMemcpyAsync(sel_host, s->sel_e, (size_t)t * c.top_k * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return pb_sync_check(ctx, "pb_moe_forward");
+}
+
+int pb_deltanet_step(pb_state* s, int layer, const float* x_host, float* y_host) {
+    if (!s) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    PB_TRY(layer_ok(s, layer, 0, "pb_deltanet_step"));
+    if (!x_host || !y_host) PB_FAIL(ctx, PB_ERR_ARG, "pb_deltanet_step: null buffer");
+    PB_CUDA(ctx, cudaMemcpyAsync(s->xin, x_host, (size_t)s->batch * c.d * 4, cudaMemcpyHostToDevice, ctx->stream));
+    PB_TRY(run_lin(s, layer, s->xin, nullptr, s->yout, c.d, 0));
+    PB_CUDA(ctx, cudaMemcpyAsync(y_host, s->yout, (size_t)s->batch * c.d * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return pb_sync_check(ctx, "pb_deltanet_step");
+}
+
+int pb_attn_step(pb_state* s, int layer, const float* x_host, float* y_host) {
+    if (!s) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    PB_TRY(layer_ok(s, layer, 1, "pb_attn_step"));
+    if (!x_host || !y_host) PB_FAIL(ctx, PB_ERR_ARG, "pb_attn_step: null buffer");
+    if (s->pos_host + 1 > c.max_ctx) PB_FAIL(ctx, PB_ERR_STATE, "context is full (%d positions)", c.max_ctx);
+    PB_CUDA(ctx, cudaMemcpyAsync(s->xin, x_host, (size_t)s->batch * c.d * 4, cudaMemcpyHostToDevice, ctx->stream));
+    PB_TRY(run_attn(s, layer, s->xin, nullptr, s->yout, c.d, 0));
+    PB_CUDA(ctx, cudaMemcpyAsync(y_host, s->yout, (size_t)s->batch * c.d * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return pb_sync_check(ctx, "pb_attn_step");
+}
+
+// conv history oldest-first [batch][conv_k-1][ch] <-> ring slots (pos + 1 + k) mod conv_k
+int pb_state_get_lin(pb_state* s, int layer, float* conv_host, float* ssm_host) {
+    if (!s) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    PB_TRY(layer_ok(s, layer, 0, "pb_state_get_lin"));
+    const int li = s->m->idx[layer], K = c.conv_k, ch = 2 * c.lin_nk * c.lin_dk + c.lin_nv * c.lin_dv;
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (conv_host)
+        for (int b = 0; b < s->batch; b++) for (int k = 0; k < K - 1; k++)
+            PB_CUDA(ctx, cudaMemcpy(conv_host + ((size_t)b * (K - 1) + k) * ch, s->conv[li] + ((size_t)b * K + (size_t)((s->pos_host + 1 + k) % K)) * ch, (size_t)ch * 4, cudaMemcpyDeviceToHost));
+    if (ssm_host) PB_CUDA(ctx, cudaMemcpy(ssm_host, s->ssm[li], (size_t)s->batch * c.lin_nv * c.lin_dk * c.lin_dv * 4, cudaMemcpyDeviceToHost));
+    return PB_OK;
+}
+int pb_state_set_lin(pb_state* s, int layer, const float* conv_host, const float* ssm_host) {
+    if (!s) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    PB_TRY(layer_ok(s, layer, 0, "pb_state_set_lin"));
+    const int li = s->m->idx[layer], K = c.conv_k, ch = 2 * c.lin_nk * c.lin_dk + c.lin_nv * c.lin_dv;
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (conv_host)
+        for (int b = 0; b < s->batch; b++) for (int k = 0; k < K - 1; k++)
+            PB_CUDA(ctx, cudaMemcpy(s->conv[li] + ((size_t)b * K + (size_t)((s->pos_host + 1 + k) % K)) * ch, conv_host + ((size_t)b * (K - 1) + k) * ch, (size_t)ch * 4, cudaMemcpyHostToDevice));
+    if (ssm_host) PB_CUDA(ctx, cudaMemcpy(s->ssm[li], ssm_host, (size_t)s->batch * c.lin_nv * c.lin_dk * c.lin_dv * 4, cudaMemcpyHostToDevice));
+    return PB_OK;
+}
+
+// Pre-fill one sequence's KV of one attention layer from host rows [n][n_kv*hd] (already normed and roped).
+int pb_state_fill_kv(pb_state* s, int b, int ai, const float* k_host, const float* v_host, int64_t n) {
+    if (!s) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    if (b < 0 || b >= s->batch || ai < 0 || ai >= s->m->n_attn || !k_host || !v_host || n < 0 || n > c.max_ctx) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_fill_kv: bad argument");
+    PbKv& kv = s->kv[ai];
+    const int hd = c.hd, nkv = c.n_kv;
+    const int64_t q4n = c.kv_bits == 4 && n > c.kv_recent ? ((n - c.kv_recent) / 64) * 64 : 0;
+    std::vector<float> tmp((size_t)(n > 0 ? n : 1) * hd);
+    void* scr;
+    PB_TRY(pb_scratch(ctx, (size_t)(q4n > 0 ? q4n : 1) * hd * 4 + 1024, &scr));
+    for (int which = 0; which < 2; which++) {
+        const float* src = which ? v_host : k_host;
+        for (int h = 0; h < nkv; h++) {
+            for (int64_t p = 0; p < n; p++) memcpy(&tmp[(size_t)p * hd], src + ((size_t)p * nkv + h) * hd, (size_t)hd * 4);
+            const size_t head = (size_t)b * nkv + h;
+            if (q4n > 0) {
+                PB_CUDA(ctx, cudaMemcpyAsync(scr, tmp.data(), (size_t)q4n * hd * 4, cudaMemcpyHostToDevice, ctx->stream));
+                PB_TRY(pb_launch_kv4_pack(ctx, (const float*)scr, q4n * hd, (which ? kv.vw : kv.kw) + head * c.max_ctx * (hd / 8), (which ? kv.vs : kv.ks) + head * c.max_ctx * (hd / 32)));
+                PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            }
+            float* ring = (which ? kv.vr : kv.kr) + head * s->ring_cap * hd;
+            for (int64_t p = q4n; p < n; p++) PB_CUDA(ctx, cudaMemcpyAsync(ring + (size_t)(p % s->ring_cap) * hd, &tmp[(size_t)p * hd], (size_t)hd * 4, cudaMemcpyHostToDevice, ctx->stream));
+            PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        }
+    }
+    PB_CUDA(ctx, cudaMemcpy(kv.q4n + b, &q4n, 8, cudaMemcpyHostToDevice));
+    return PB_OK;
+}
+
+int pb_state_fill_kv_synth(pb_state* s, int ai, int64_t n, uint64_t seed) {
+    if (!s) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    if (ai < 0 || ai >= s->m->n_attn || n < 0 || n > c.max_ctx) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_fill_kv_synth: bad argument");
+    PbKv& kv = s->kv[ai];
+    const int hd = c.hd, nkv = c.n_kv;
+    const int64_t q4n = c.kv_bits == 4 && n > c.kv_recent ? ((n - c.kv_recent) / 64) * 64 : 0;
+    void* scr;
+    PB_TRY(pb_scratch(ctx, (size_t)(n > 0 ? n : 1) * hd * 4 + 1024, &scr));
+    float* f = (float*)scr;
+    // element (which, b, h, p, i) of the synthetic cache = normal(seed, tensor id = (ai*2+which), index ((b*nkv+h)*max_ctx+p)*hd+i)
+    for (int which = 0; which < 2; which++)
+        for (int b = 0; b < s->batch; b++)
+            for (int h = 0; h < nkv; h++) {
+                const size_t head = (size_t)b * nkv + h;
+                PB_TRY(pb_launch_synth_normal_at(ctx, f, n * hd, seed, (uint64_t)ai * 2 + which, (int64_t)(head * c.max_ctx) * hd, 1.0f));
+                if (q4n > 0) PB_TRY(pb_launch_kv4_pack(ctx, f, q4n * hd, (which ? kv.vw : kv.kw) + head * c.max_ctx * (hd / 8), (which ? kv.vs : kv.ks) + head * c.max_ctx * (hd / 32)));
+                float* ring = (which ? kv.vr : kv.kr) + head * s->ring_cap * hd;
+                for (int64_t p = q4n; p < n;) {   // contiguous runs inside the ring
+                    const int64_t slot = p % s->ring_cap, run = (n - p) < (s->ring_cap - slot) ? (n - p) : (s->ring_cap - slot);
+                    PB_CUDA(ctx, cudaMemcpyAsync(ring + (size_t)slot * hd, f + (size_t)p * hd, (size_t)run * hd * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+                    p += run;
+                }
+                PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            }
+    std::vector<int64_t> q((size_t)s->batch, q4n);
+    PB_CUDA(ctx, cudaMemcpy(kv.q4n, q.data(), q.size() * 8, cudaMemcpyHostToDevice));
+    return PB_OK;
+}
+
+int pb_kv4_pack(pb_ctx* ctx, const float* x_host, int64_t n, uint32_t* words_host, float* scales_host) {
+    if (!ctx) return PB_ERR_ARG;
+    if (!x_host || !words_host || !scales_host || n < 0 || n % 32) PB_FAIL(ctx, PB_ERR_ARG, "pb_kv4_pack: length %lld is not a multiple of 32", (long long)n);   // kv4.rs:13
+    if (n == 0) return PB_OK;
+    void* scr;
+    const size_t xb = (size_t)n * 4, wb = (size_t)n / 2, sb = (size_t)n / 8;
+    PB_TRY(pb_scratch(ctx, xb + wb + sb + 1024, &scr));
+    float* xd = (float*)scr; uint32_t* wd = (uint32_t*)((uint8_t*)scr + xb); float* sd = (float*)((uint8_t*)scr + xb + wb);
+    PB_CUDA(ctx, cudaMemcpyAsync(xd, x_host, xb, cudaMemcpyHostToDevice, ctx->stream));
+    PB_TRY(pb_launch_kv4_pack(ctx, xd, n, wd, sd));
+    PB_CUDA(ctx, cudaMemcpyAsync(words_host, wd, wb, cudaMemcpyDeviceToHost, ctx->stream));
+    PB_CUDA(ctx, cudaMemcpyAsync(scales_host, sd, sb, cudaMemcpyDeviceToHost, ctx->stream));
+    return pb_sync_check(ctx, "pb_kv4_pack");
+}
+
+int pb_kv4_unpack(pb_ctx* ctx, const uint32_t* words_host, const float* scales_host, int64_t n, float* x_host) {
+    if (!ctx) return PB_ERR_ARG;
+    if (!x_host || !words_host || !scales_host || n < 0 || n % 32) PB_FAIL(ctx, PB_ERR_ARG, "pb_kv4_unpack: length %lld is not a multiple of 32", (long long)n);
+    if (n == 0) return PB_OK;
+    void* scr;
+    const size_t xb = (size_t)n * 4, wb = (size_t)n / 2, sb = (size_t)n / 8;
+    PB_TRY(pb_scratch(ctx, xb + wb + sb + 1024, &scr));
+    float* xd = (float*)scr; uint32_t* wd = (uint32_t*)((uint8_t*)scr + xb); float* sd = (float*)((uint8_t*)scr + xb + wb);
+    PB_CUDA(ctx, cudaMemcpyAsync(wd, words_host, wb, cudaMemcpyHostToDevice, ctx->stream));
+    PB_CUDA(ctx, cudaMemcpyAsync(sd, scales_host, sb, cudaMemcpyHostToDevice, ctx->stream));
+    PB_TRY(pb_launch_kv4_unpack(ctx, wd, sd, n, xd));
+    PB_CUDA(ctx, cudaMemcpyAsync(x_host, xd, xb, cudaMemcpyDeviceToHost, ctx->stream));
+    return pb_sync_check(ctx, "pb_kv4_unpack");
+}
+
+}  // extern "C"

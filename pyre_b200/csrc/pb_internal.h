@@ -2,6 +2,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 #include <string>
 #include <vector>
 
@@ -59,6 +60,7 @@ int pb_sync_check(pb_ctx* ctx, const char* who);
 int pb_launch_dequant(pb_ctx* ctx, int type, const uint8_t* w, int64_t nsteps, float* out);
 int pb_launch_synth(pb_ctx* ctx, int type, uint8_t* w, int64_t nblocks, uint64_t seed, uint64_t tid);
 int pb_launch_synth_normal(pb_ctx* ctx, float* out, int64_t n, uint64_t seed, uint64_t tid, float sigma);
+int pb_launch_synth_normal_at(pb_ctx* ctx, float* out, int64_t n, uint64_t seed, uint64_t tid, int64_t i0, float sigma);
 
 // pb_gemv.cu
 struct PbGemvArgs {
@@ -73,3 +75,113 @@ struct PbGemvArgs {
     int64_t ldy;
 };
 int pb_launch_gemv(pb_ctx* ctx, const PbGemvArgs& a);
+
+// pb_gemvq.cu: integer-core GEMV over up to four same-shaped-row matrices with a fused
+// activation prologue and an optional accumulate (residual) epilogue.
+enum { PB_ACT_PLAIN = 0,   // x as given
+       PB_ACT_NORM = 1,    // rms(x) * norm_w over the whole row
+       PB_ACT_GNORM = 2,   // per head of head_dim: rms(x) * norm_w[head_dim], times sigmoid(z)
+       PB_ACT_PREQ = 3 };  // activations already split into int8 levels (xq_in)
+struct PbGemvSegArg { const uint8_t* w; int64_t rows; int64_t yoff; };
+struct PbGemvQArgs {
+    int type, cols, nseg;
+    PbGemvSegArg seg[4];
+    const float* x; int64_t ldx; int t;
+    float* y; int64_t ldy;
+    int mode; const float* norm_w; const float* z; int64_t ldz; int head_dim; float eps;
+    const uint32_t* xq_in;
+    int accumulate;
+};
+struct PbGemvQSeg { const uint8_t* w; int rows; int chunk0; int yoff; };
+struct PbGemvQParams {
+    PbGemvQSeg seg[4];
+    int nseg;
+    int row_bytes, bpr, rows_per_chunk, nchunks;
+    uint32_t stage_bytes, tab_bytes;
+    int rep;
+    const float* x; int64_t ldx; int t;
+    float* y; int64_t ldy;
+    int mode; const float* norm_w; const float* z; int64_t ldz; int head_dim; float eps;
+    const uint32_t* xq_in;
+    int accumulate;
+    int* status;
+};
+bool pb_gemvq_supported(int type, int cols);
+int pb_launch_gemvq(pb_ctx* ctx, const PbGemvQArgs& a);
+
+// ---------------------------------------------------------------- pb_moe.cu
+#define PB_MAX_TOPK 16
+struct PbRouterParams {
+    const float* x; int64_t ldx; int t; int cols;
+    const float* norm_w; float eps;          // null: x is already normalized
+    const float* router;                      // f32 [n_exp][cols]
+    const float* sh_gate_inp;                 // f32 [cols] or null
+    int n_exp;
+    float* logits;                            // [t][n_exp + 1], last = shared-gate logit
+    uint32_t* xq_out;                         // [t][pb_xq_words(cols)] int8-split activations
+};
+struct PbRouteParams {
+    const float* logits; int t, n_exp, top_k;
+    int e_lo, e_hi;                           // experts held by this GPU
+    int* sel_e; float* sel_w;                 // [t][top_k], ascending expert id
+    int* n_used; int* used_e; int* used_off;  // distinct local experts, entry offsets [n_used + 1]
+    int* ent_tok; int* ent_slot; float* ent_w;
+};
+struct PbExpertParams {
+    const int* n_used; const int* used_e; const int* used_off;
+    const int* ent_tok; const int* ent_slot; const float* ent_w;
+    const uint32_t* xq;                       // gate/up: int8-split activations per token
+    const uint8_t* w_a; const uint8_t* w_b;   // gate/up: gate_exps, up_exps; down: down_exps, unused
+    const uint8_t* sh_a; const uint8_t* sh_b; // shared expert counterparts
+    float* h; float* h_sh;                    // hidden [entry][ff], [t][ff_sh]
+    float* part; float* part_sh;              // down: [t][top_k][d], [t][d]
+    int rows_e, rows_sh, has_shared, t, top_k, n_exp, e_base;
+    int bpr, row_bytes, rows_per_chunk; uint32_t stage_bytes, tab_bytes; int rep;
+    int* status;
+};
+struct PbCombineParams {
+    const float* part; const float* part_sh; const float* logits;
+    int t, d, top_k, n_exp;
+    float* y; int64_t ldy; int accumulate;
+};
+int pb_launch_router(pb_ctx* ctx, const PbRouterParams& p);
+int pb_launch_route(pb_ctx* ctx, const PbRouteParams& p);
+int pb_launch_expert_gu(pb_ctx* ctx, const PbExpertParams& p, int type, int cols);
+int pb_launch_expert_down(pb_ctx* ctx, const PbExpertParams& p, int type, int cols);
+int pb_launch_moe_combine(pb_ctx* ctx, const PbCombineParams& p);
+
+// ---------------------------------------------------------------- pb_deltanet.cu
+struct PbDeltaParams {
+    const float* proj; int64_t ldp;           // [batch][qkv | z | beta | alpha]
+    const float* conv_w; const float* a; const float* dt;
+    float* conv;                              // [batch][conv_k slots][ch] ring
+    float* ssm;                               // [batch][nv][dk][dv]
+    const int64_t* pos;                       // [batch]
+    float* out; int64_t ldo;                  // [batch][nv*dv] readout before the gated norm
+    int nk, nv, dk, dv, conv_k, batch;
+};
+int pb_launch_deltanet(pb_ctx* ctx, const PbDeltaParams& p);
+
+// ---------------------------------------------------------------- pb_attn.cu
+struct PbAttnParams {
+    const float* proj; int64_t ldp;           // [batch][q|gate per head (n_head*2*hd) | k | v]
+    const float* qn; const float* kn; const float* rope_inv;
+    int n_rot; float eps;
+    int n_head, n_kv, hd;
+    uint32_t* kw; float* ks; uint32_t* vw; float* vs;   // packed [batch][n_kv][max_ctx][hd/8], scales [..][hd/32]
+    float* kr; float* vr;                                // f32 ring [batch][n_kv][ring_cap][hd]
+    int64_t max_ctx; int64_t ring_cap; int kv_bits; int kv_recent;
+    const int64_t* pos; int64_t* q4n;                    // [batch]
+    float* part_ml; float* part_acc; int nsplit;
+    float* att; int64_t lda;                             // [batch][n_head*hd]
+    int batch;
+};
+int pb_launch_kv_append(pb_ctx* ctx, const PbAttnParams& p);
+int pb_launch_attn(pb_ctx* ctx, const PbAttnParams& p);
+int pb_launch_kv4_pack(pb_ctx* ctx, const float* x, int64_t n, uint32_t* w, float* sc);
+int pb_launch_kv4_unpack(pb_ctx* ctx, const uint32_t* w, const float* sc, int64_t n, float* x);
+
+// ---------------------------------------------------------------- pb_misc.cu
+int pb_launch_embed(pb_ctx* ctx, int type, const uint8_t* w, int64_t rows, int cols, const uint32_t* ids, int t, float* out, int64_t ldo);
+int pb_launch_argmax(pb_ctx* ctx, const float* logits, int64_t ld, int n, int t, uint32_t* out);
+int pb_launch_advance(pb_ctx* ctx, int64_t* pos, int t, const uint32_t* next, uint32_t* ids, uint32_t* trace, int64_t* trace_len, int64_t trace_cap);

@@ -1,0 +1,427 @@
+// Fused MoE block of the decode path: router + top-k + grouped expert SwiGLU + shared expert.
+//
+// Restates ffn / routed / top_k of the reference (src/model/qwen4exp_gguf.rs:1675-1684,
+// 1721-1793 f32 branch, 3121-3139) and replaces its host-side routing (route_sel :2164-2174,
+// behind a per-layer device->host readback) and the k_xgu* / k_xdown* / k_xgr_topk kernels
+// (src/model/qn_cube.rs:3482-5419, 5210-5256).  Nothing leaves the device:
+//   1. pb_router_kernel   RMSNorm (optional) + f32 router GEMV + shared-gate logit; also emits
+//                         the normalized activations split into int8 levels for the experts
+//   2. pb_route_kernel    per token top-k (descending logit, ties to the lower id, NaN -> -inf),
+//                         softmax over the selection, selection sorted by expert id; builds the
+//                         list of distinct local experts with their (token, slot) entries
+//   3. pb_expert_gu_kernel   h = silu(gate_e x) * (up_e x) for every (expert, token) entry and the
+//                         shared expert; weights streamed once per expert
+//   4. pb_expert_down_kernel part[token][slot] = w * (down_e h); shared expert unweighted
+//   5. pb_moe_combine_kernel y = sigmoid(shared gate) * shared + sum over slots in ascending
+//                         expert id (fixed order: deterministic, independent of the GPU count)
+#include "pb_stream.cuh"
+#include "pb_internal.h"
+
+#include <stdio.h>
+
+// ------------------------------------------------------------------------------------ router
+
+// grid: ceil((n_exp + 1) / 8) CTAs of 256 threads; warp per router row (row n_exp = shared-gate vector)
+__global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p) {
+    extern __shared__ float rs[];   // scale[t] then one row of normalized x (cols floats) for the quantizer
+    float* scale = rs;
+    float* xn = rs + ((p.t + 31) & ~31);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    __shared__ float red[8];
+    // per-token RMS scale (rms(): 1 / sqrt(mean(x^2) + eps), qwen4exp_gguf.rs:209)
+    for (int b = 0; b < p.t; b++) {
+        float s = 1.0f;
+        if (p.norm_w) {
+            float ss = 0.f;
+            for (int c = tid; c < p.cols; c += 256) { const float v = p.x[b * p.ldx + c]; ss += v * v; }
+            ss = pb_warp_sum(ss);
+            __syncthreads();
+            if (lane == 0) red[warp] = ss;
+            __syncthreads();
+            float tot = 0.f;
+            for (int i = 0; i < 8; i++) tot += red[i];
+            s = 1.0f / sqrtf(tot / (float)p.cols + p.eps);
+        }
+        if (tid == 0) scale[b] = s;
+    }
+    __syncthreads();
+    // CTA j emits token j's normalized activations: f32 copy (optional) and int8 split
+    for (int b = blockIdx.x; b < p.t; b += gridDim.x) {
+        for (int c = tid; c < p.cols; c += 256) {
+            float v = p.x[b * p.ldx + c];
+            if (p.norm_w) v = v * scale[b] * p.norm_w[c];
+            xn[c] = v;
+        }
+        __syncthreads();
+        for (int g = warp; g < p.cols / 32; g += 8) pb_split_group(xn[32 * g + lane], lane, g, p.cols, p.xq_out + (size_t)b * pb_xq_words(p.cols));
+        __syncthreads();
+    }
+    const int row = blockIdx.x * 8 + warp;
+    if (row > p.n_exp) return;
+    const float* wrow = row < p.n_exp ? p.router + (size_t)row * p.cols : p.sh_gate_inp;
+    if (!wrow) { if (lane == 0) for (int b = 0; b < p.t; b++) p.logits[b * (p.n_exp + 1) + row] = 0.f; return; }
+    for (int b = 0; b < p.t; b++) {
+        float acc = 0.f;
+        const float s = scale[b];
+        for (int c = lane * 4; c < p.cols; c += 128) {
+            const float4 w = *reinterpret_cast<const float4*>(wrow + c);
+            float4 v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + c);
+            if (p.norm_w) {
+                const float4 n = *reinterpret_cast<const float4*>(p.norm_w + c);
+                v.x = v.x * s * n.x; v.y = v.y * s * n.y; v.z = v.z * s * n.z; v.w = v.w * s * n.w;
+            }
+            acc = fmaf(w.x, v.x, acc); acc = fmaf(w.y, v.y, acc); acc = fmaf(w.z, v.z, acc); acc = fmaf(w.w, v.w, acc);
+        }
+        acc = pb_warp_sum(acc);
+        if (lane == 0) p.logits[b * (p.n_exp + 1) + row] = acc;
+    }
+}
+
+// ------------------------------------------------------------------------------------ routing
+
+// one CTA of 512 threads; warp per token (loops if t > 16)
+__global__ void __launch_bounds__(512) pb_route_kernel(const PbRouteParams p) {
+    extern __shared__ int rsm[];
+    int* cnt = rsm;                 // [n_exp] entries per expert (local experts only)
+    int* cursor = rsm + p.n_exp;    // [n_exp]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int e = tid; e < p.n_exp; e += 512) { cnt[e] = 0; cursor[e] = 0; }
+    __syncthreads();
+    for (int b = warp; b < p.t; b += 16) {
+        const float* lg = p.logits + (size_t)b * (p.n_exp + 1);
+        // lane holds experts lane, lane+32, ... ; NaN -> -inf (nan_clean :3121-3125)
+        float v[32];
+        const int per = (p.n_exp + 31) / 32;
+        for (int i = 0; i < per && i < 32; i++) { const int e = i * 32 + lane; float x = e < p.n_exp ? lg[e] : -INFINITY; v[i] = isnan(x) ? -INFINITY : x; }
+        int sel_e[PB_MAX_TOPK]; float sel_v[PB_MAX_TOPK];
+        for (int j = 0; j < p.top_k; j++) {
+            float bv = -INFINITY; int be = 0x7fffffff;
+            for (int i = 0; i < per && i < 32; i++) { const int e = i * 32 + lane; if (e < p.n_exp && (v[i] > bv || (v[i] == bv && e < be))) { bv = v[i]; be = e; } }
+            // -inf candidates that were already taken are marked with NaN below, so they never compare equal
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+                if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+            }
+            sel_e[j] = be; sel_v[j] = bv;
+            if ((be & 31) == lane) v[be >> 5] = __int_as_float(0x7fc00000);  // taken: NaN compares false everywhere
+        }
+        if (lane == 0) {
+            // softmax over the selection in descending-logit order (top_k :3136-3138, soft_top :3126-3131)
+            float mx = -INFINITY;
+            for (int j = 0; j < p.top_k; j++) mx = fmaxf(mx, sel_v[j]);
+            float w[PB_MAX_TOPK];
+            if (!isfinite(mx)) { for (int j = 0; j < p.top_k; j++) w[j] = 1.0f / (float)(p.top_k > 0 ? p.top_k : 1); }
+            else { float sum = 0.f; for (int j = 0; j < p.top_k; j++) { w[j] = expf(sel_v[j] - mx); sum += w[j]; } for (int j = 0; j < p.top_k; j++) w[j] = w[j] / sum; }
+            // accumulate in ascending expert id (routed f32 branch :1786): insertion sort by id
+            for (int j = 1; j < p.top_k; j++) { const int e = sel_e[j]; const float ww = w[j]; int i = j - 1; while (i >= 0 && sel_e[i] > e) { sel_e[i + 1] = sel_e[i]; w[i + 1] = w[i]; i--; } sel_e[i + 1] = e; w[i + 1] = ww; }
+            for (int j = 0; j < p.top_k; j++) {
+                p.sel_e[b * p.top_k + j] = sel_e[j]; p.sel_w[b * p.top_k + j] = w[j];
+                if (sel_e[j] >= p.e_lo && sel_e[j] < p.e_hi) atomicAdd(&cnt[sel_e[j]], 1);
+            }
+        }
+    }
+    __syncthreads();
+    // compact the distinct local experts in ascending id with entry offsets (thread 0: n_exp <= 1024 steps)
+    if (tid == 0) {
+        int n = 0, off = 0;
+        for (int e = p.e_lo; e < p.e_hi; e++) if (cnt[e]) { p.used_e[n] = e; p.used_off[n] = off; cursor[e] = off; off += cnt[e]; n++; }
+        p.used_off[n] = off;
+        *p.n_used = n;
+    }
+    __syncthreads();
+    for (int i = tid; i < p.t * p.top_k; i += 512) {
+        const int e = p.sel_e[i];
+        if (e >= p.e_lo && e < p.e_hi) { const int pos = atomicAdd(&cursor[e], 1); p.ent_tok[pos] = i / p.top_k; p.ent_slot[pos] = i % p.top_k; p.ent_w[pos] = p.sel_w[i]; }
+    }
+}
+
+// ------------------------------------------------------------------------------------ expert gate/up
+
+template <int FMT, int PASSES>
+__global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbExpertParams p) {
+    using D = PbQDec<FMT>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    PbRing ring;
+    ring.full = reinterpret_cast<uint64_t*>(smem);
+    ring.empty = ring.full + PB_STAGES;
+    uint8_t* sign16 = smem + 128;
+    uint8_t* tab = smem + 256;
+    ring.stages = tab + p.tab_bytes;
+    ring.stage_bytes = p.stage_bytes;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pb_ring_init(ring, tid);
+    __syncthreads();
+
+    const int cols = p.bpr * 256;
+    const int n_used = *p.n_used;
+    const int cpe = p.rows_e / p.rows_per_chunk;                       // chunks per routed expert
+    const int cps = p.has_shared ? p.rows_sh / p.rows_per_chunk : 0;   // chunks of the shared expert
+    const int nchunks = n_used * cpe + cps;
+    const int my_chunks = nchunks > (int)blockIdx.x ? (nchunks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const uint32_t half = (uint32_t)p.rows_per_chunk * p.row_bytes;   // a multiple of 16 by construction
+
+    if (warp == PB_CONSUMERS) {
+        if (lane == 0) {
+            int k = 0;
+            for (; k < my_chunks; k++) {
+                const int chunk = (int)blockIdx.x + k * (int)gridDim.x;
+                const uint8_t *g, *u;
+                if (chunk < n_used * cpe) {
+                    const int s = chunk / cpe, r0 = (chunk - s * cpe) * p.rows_per_chunk;
+                    const int e = p.used_e[s];
+                    if (e < 0 || e >= p.n_exp) { atomicExch(p.status, PB_DEV_BAD_INDEX); break; }
+                    const size_t off = ((size_t)(e - p.e_base) * p.rows_e + r0) * p.row_bytes;
+                    g = p.w_a + off; u = p.w_b + off;
+                } else {
+                    const size_t off = (size_t)(chunk - n_used * cpe) * p.rows_per_chunk * p.row_bytes;
+                    g = p.sh_a + off; u = p.sh_b + off;
+                }
+                if (!pb_ring_acquire(ring, k, 2 * half, p.status)) break;
+                pb_ring_copy(ring, k, 0, g, half);
+                pb_ring_copy(ring, k, half, u, half);
+            }
+            if (k < my_chunks) pb_ring_drain(ring, k);
+        }
+        return;
+    }
+
+    constexpr int CT = PB_CONSUMERS * 32;
+    const PbQTabs T = pb_fill_qtabs<FMT>(sign16, tab, p.rep, tid, CT);
+    pb_named_barrier(1, CT);
+    const int nquarters = 4 * p.bpr;
+    const int lpr = nquarters < 32 ? nquarters : 32, rpw = 32 / lpr;
+    const int sub = lane / lpr, ql = lane - sub * lpr;
+    const int xw = pb_xq_words(cols);
+
+    for (int k = 0; k < my_chunks; k++) {
+        if (!pb_ring_wait(ring, k, p.status)) return;
+        const int chunk = (int)blockIdx.x + k * (int)gridDim.x;
+        const bool shared = chunk >= n_used * cpe;
+        int s = 0, r0, e0 = 0, e1;
+        if (!shared) { s = chunk / cpe; r0 = (chunk - s * cpe) * p.rows_per_chunk; e0 = p.used_off[s]; e1 = p.used_off[s + 1]; }
+        else { r0 = (chunk - n_used * cpe) * p.rows_per_chunk; e1 = p.t; }
+        const uint8_t* base = pb_ring_stage(ring, k);
+        for (int rb = warp * rpw; rb < p.rows_per_chunk; rb += PB_CONSUMERS * rpw) {
+            const int r = rb + sub;
+            PbQuarter wg[PASSES], wu[PASSES];
+#pragma unroll
+            for (int ps = 0; ps < PASSES; ps++) {
+                const int qi = ps * 32 + ql;
+                if (qi < nquarters) {
+                    D::quarter(base + (size_t)r * p.row_bytes + (qi >> 2) * D::STEP_BYTES, qi & 3, lane, T, wg[ps]);
+                    D::quarter(base + half + (size_t)r * p.row_bytes + (qi >> 2) * D::STEP_BYTES, qi & 3, lane, T, wu[ps]);
+                }
+            }
+            for (int en = e0; en < e1; en++) {
+                const int tok = shared ? en : p.ent_tok[en];
+                float g = 0.f, u = 0.f;
+#pragma unroll
+                for (int ps = 0; ps < PASSES; ps++) {
+                    const int qi = ps * 32 + ql;
+                    if (qi < nquarters) {
+                        PbXQuarter xv;
+                        pb_load_xquarter(p.xq + (size_t)tok * xw, cols, qi, xv);
+                        g += pb_quarter_dot<FMT>(wg[ps], xv);
+                        u += pb_quarter_dot<FMT>(wu[ps], xv);
+                    }
+                }
+                for (int o = lpr >> 1; o > 0; o >>= 1) { g += __shfl_xor_sync(0xffffffffu, g, o); u += __shfl_xor_sync(0xffffffffu, u, o); }
+                if (ql == 0) {
+                    // hidden = silu(gate . x) * (up . x)   (routed :1781-1783, ffn :1680)
+                    float* dst = shared ? p.h_sh + (size_t)tok * p.rows_sh : p.h + (size_t)en * p.rows_e;
+                    dst[r0 + r] = pb_silu(g) * u;
+                }
+            }
+        }
+        pb_ring_release(ring, k, lane);
+    }
+}
+
+// ------------------------------------------------------------------------------------ expert down
+
+template <int FMT, int PASSES>
+__global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const PbExpertParams p) {
+    using D = PbQDec<FMT>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    PbRing ring;
+    ring.full = reinterpret_cast<uint64_t*>(smem);
+    ring.empty = ring.full + PB_STAGES;
+    uint8_t* sign16 = smem + 128;
+    uint8_t* tab = smem + 256;
+    const int cols = p.bpr * 256;   // = expert intermediate size
+    const int xw = pb_xq_words(cols);
+    uint32_t* xq = reinterpret_cast<uint32_t*>(tab + p.tab_bytes);
+    ring.stages = reinterpret_cast<uint8_t*>(xq) + (((size_t)xw * 4 + 127) & ~(size_t)127);
+    ring.stage_bytes = p.stage_bytes;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pb_ring_init(ring, tid);
+    __syncthreads();
+
+    const int n_used = *p.n_used;
+    const int cpe = p.rows_e / p.rows_per_chunk;   // output rows (= model width) per expert / rows per chunk
+    const int cps = p.has_shared ? cpe : 0;
+    const int nchunks = n_used * cpe + cps;
+    const int my_chunks = nchunks > (int)blockIdx.x ? (nchunks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const uint32_t bytes = (uint32_t)p.rows_per_chunk * p.row_bytes;
+
+    if (warp == PB_CONSUMERS) {
+        if (lane == 0) {
+            int k = 0;
+            for (; k < my_chunks; k++) {
+                const int chunk = (int)blockIdx.x + k * (int)gridDim.x;
+                const uint8_t* src;
+                if (chunk < n_used * cpe) {
+                    const int s = chunk / cpe, r0 = (chunk - s * cpe) * p.rows_per_chunk;
+                    const int e = p.used_e[s];
+                    if (e < 0 || e >= p.n_exp) { atomicExch(p.status, PB_DEV_BAD_INDEX); break; }
+                    src = p.w_a + ((size_t)(e - p.e_base) * p.rows_e + r0) * p.row_bytes;
+                } else src = p.sh_a + (size_t)(chunk - n_used * cpe) * p.rows_per_chunk * p.row_bytes;
+                if (!pb_ring_acquire(ring, k, bytes, p.status)) break;
+                pb_ring_copy(ring, k, 0, src, bytes);
+            }
+            if (k < my_chunks) pb_ring_drain(ring, k);
+        }
+        return;
+    }
+
+    constexpr int CT = PB_CONSUMERS * 32;
+    const PbQTabs T = pb_fill_qtabs<FMT>(sign16, tab, p.rep, tid, CT);
+    pb_named_barrier(1, CT);
+    const int nquarters = 4 * p.bpr;
+    const int lpr = nquarters < 32 ? nquarters : 32, rpw = 32 / lpr;
+    const int sub = lane / lpr, ql = lane - sub * lpr;
+    const int ng = cols / 32;
+
+    for (int k = 0; k < my_chunks; k++) {
+        if (!pb_ring_wait(ring, k, p.status)) return;
+        const int chunk = (int)blockIdx.x + k * (int)gridDim.x;
+        const bool shared = chunk >= n_used * cpe;
+        int s = 0, r0, e0 = 0, e1;
+        if (!shared) { s = chunk / cpe; r0 = (chunk - s * cpe) * p.rows_per_chunk; e0 = p.used_off[s]; e1 = p.used_off[s + 1]; }
+        else { r0 = (chunk - n_used * cpe) * p.rows_per_chunk; e1 = p.t; }
+        const uint8_t* base = pb_ring_stage(ring, k);
+        for (int en = e0; en < e1; en++) {
+            const int tok = shared ? en : p.ent_tok[en];
+            const float* hv = shared ? p.h_sh + (size_t)tok * cols : p.h + (size_t)en * cols;
+            // split this entry's hidden vector into int8 levels (all consumer warps, one group each)
+            pb_named_barrier(1, CT);
+            for (int g = warp; g < ng; g += PB_CONSUMERS) pb_split_group(hv[32 * g + lane], lane, g, cols, xq);
+            pb_named_barrier(1, CT);
+            float* dst; float wgt = 1.0f;
+            if (shared) dst = p.part_sh + (size_t)tok * p.rows_e;
+            else { dst = p.part + ((size_t)tok * p.top_k + p.ent_slot[en]) * p.rows_e; wgt = p.ent_w[en]; }
+            for (int rb = warp * rpw; rb < p.rows_per_chunk; rb += PB_CONSUMERS * rpw) {
+                const int r = rb + sub;
+                float acc = 0.f;
+#pragma unroll
+                for (int ps = 0; ps < PASSES; ps++) {
+                    const int qi = ps * 32 + ql;
+                    if (qi < nquarters) {
+                        PbQuarter wq; PbXQuarter xv;
+                        D::quarter(base + (size_t)r * p.row_bytes + (qi >> 2) * D::STEP_BYTES, qi & 3, lane, T, wq);
+                        pb_load_xquarter(xq, cols, qi, xv);
+                        acc += pb_quarter_dot<FMT>(wq, xv);
+                    }
+                }
+                for (int o = lpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (ql == 0) dst[r0 + r] = wgt * acc;   // routed :1786: o += w * dot
+            }
+        }
+        pb_ring_release(ring, k, lane);
+    }
+}
+
+// ------------------------------------------------------------------------------------ combine
+
+// y[tok][r] = sigmoid(shared-gate logit) * shared[tok][r] + sum_j part[tok][j][r]  (ascending expert id),
+// then either stored (layer-level call) or added to the residual stream.
+__global__ void __launch_bounds__(256) pb_moe_combine_kernel(const PbCombineParams p) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t)p.t * p.d) return;
+    const int tok = (int)(i / p.d), r = (int)(i - (int64_t)tok * p.d);
+    float y = 0.f;
+    if (p.part_sh) y = p.part_sh[i] * pb_sigm(p.logits[(size_t)tok * (p.n_exp + 1) + p.n_exp]);   // routed :1723
+    float o = 0.f;
+    for (int j = 0; j < p.top_k; j++) o += p.part[((size_t)tok * p.top_k + j) * p.d + r];
+    y += o;
+    float* dst = p.y + (size_t)tok * p.ldy + r;
+    *dst = p.accumulate ? *dst + y : y;
+}
+
+// ------------------------------------------------------------------------------------ launchers
+
+int pb_launch_router(pb_ctx* ctx, const PbRouterParams& p) {
+    if (p.cols % 128) PB_FAIL(ctx, PB_UNSUPPORTED, "router: width %d is not a multiple of 128", p.cols);
+    const int grid = (p.n_exp + 1 + 7) / 8;
+    const size_t smem = (size_t)(((p.t + 31) & ~31) + p.cols) * 4;
+    pb_router_kernel<<<grid, 256, smem, ctx->stream>>>(p);
+    ctx->kernels_launched++;
+    PB_CUDA(ctx, cudaGetLastError());
+    return PB_OK;
+}
+
+int pb_launch_route(pb_ctx* ctx, const PbRouteParams& p) {
+    if (p.top_k > PB_MAX_TOPK || p.n_exp > 1024) PB_FAIL(ctx, PB_UNSUPPORTED, "route: top_k %d / n_exp %d beyond %d / 1024", p.top_k, p.n_exp, PB_MAX_TOPK);
+    pb_route_kernel<<<1, 512, (size_t)p.n_exp * 8, ctx->stream>>>(p);
+    ctx->kernels_launched++;
+    PB_CUDA(ctx, cudaGetLastError());
+    return PB_OK;
+}
+
+template <int FMT, int PASSES, bool DOWN>
+static int launch_expert(pb_ctx* ctx, PbExpertParams p, int cols) {
+    int el, bs;
+    pb_geom(FMT, &el, &bs);
+    p.row_bytes = cols / el * bs; p.bpr = cols / 256;
+    constexpr int entry = pb_tab_entry_bytes<FMT>();
+    p.rep = 1;   // a few MB per launch: the plain codebook; see pb_gemvq.cu for the replicated form
+    p.tab_bytes = entry ? 512 * entry * p.rep : 0;
+    const int lpr = 4 * p.bpr < 32 ? 4 * p.bpr : 32;
+    int rpc = PB_CONSUMERS * (32 / lpr);
+    while ((rpc * p.row_bytes) % 16) rpc *= 2;
+    if (p.rows_e % rpc || (p.has_shared && !DOWN && p.rows_sh % rpc)) PB_FAIL(ctx, PB_UNSUPPORTED, "expert kernel: %d rows per expert is not a multiple of the %d-row chunk", p.rows_e, rpc);
+    p.rows_per_chunk = rpc;
+    const size_t xbytes = DOWN ? (((size_t)pb_xq_words(cols) * 4 + 127) & ~(size_t)127) : 0;
+    p.stage_bytes = (uint32_t)((((size_t)rpc * p.row_bytes * (DOWN ? 1 : 2)) + 16 + 127) & ~(size_t)127);
+    const size_t smem = 256 + p.tab_bytes + xbytes + (size_t)PB_STAGES * p.stage_bytes;
+    if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "expert kernel needs %zu bytes of shared memory", smem);
+    p.status = ctx->dev_status;
+    if (DOWN) {
+        auto kern = pb_expert_down_kernel<FMT, PASSES>;
+        static size_t configured = 0;
+        if (smem > configured) { PB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = smem; }
+        kern<<<ctx->sm_count, PB_KTHREADS, smem, ctx->stream>>>(p);
+    } else {
+        auto kern = pb_expert_gu_kernel<FMT, PASSES>;
+        static size_t configured = 0;
+        if (smem > configured) { PB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = smem; }
+        kern<<<ctx->sm_count, PB_KTHREADS, smem, ctx->stream>>>(p);
+    }
+    ctx->kernels_launched++;
+    PB_CUDA(ctx, cudaGetLastError());
+    return PB_OK;
+}
+
+template <bool DOWN>
+static int launch_expert_type(pb_ctx* ctx, const PbExpertParams& p, int type, int cols) {
+    if (!pb_gemvq_supported(type, cols)) PB_FAIL(ctx, PB_UNSUPPORTED, "expert kernel: ggml type %d with %d columns is not supported", type, cols);
+#define GO(F) return cols <= 2048 ? launch_expert<F, 1, DOWN>(ctx, p, cols) : launch_expert<F, 2, DOWN>(ctx, p, cols)
+    switch (type) {
+        case PB_T_IQ3_S: GO(PB_T_IQ3_S);
+        case PB_T_IQ2_XS: GO(PB_T_IQ2_XS);
+        case PB_T_Q4_K: GO(PB_T_Q4_K);
+        default: GO(PB_T_Q8_0);
+    }
+#undef GO
+}
+
+int pb_launch_expert_gu(pb_ctx* ctx, const PbExpertParams& p, int type, int cols) { return launch_expert_type<false>(ctx, p, type, cols); }
+int pb_launch_expert_down(pb_ctx* ctx, const PbExpertParams& p, int type, int cols) { return launch_expert_type<true>(ctx, p, type, cols); }
+
+int pb_launch_moe_combine(pb_ctx* ctx, const PbCombineParams& p) {
+    const int64_t n = (int64_t)p.t * p.d;
+    pb_moe_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(p);
+    ctx->kernels_launched++;
+    PB_CUDA(ctx, cudaGetLastError());
+    return PB_OK;
+}

@@ -3,12 +3,12 @@
 // A lane owns a quarter of a 256-weight super-step (64 consecutive weights).  It decodes
 // them to 16 words of packed signed int8 (grid values with their signs, raw int8 for
 // Q8_0, nibbles for Q4_K) plus f32 scales per 16 weights, and dots them with dp4a against
-// activations that were split, per 32-value group, into two int8 levels:
-//     x = s1*q1 + s2*q2 + e,   |e| <= max|x| / (127*127*4)
+// activations that were split, per 32-value group, into PB_XLEVELS int8 levels:
+//     x = s1*q1 + s2*q2 + s3*q3 + e,   |e| <= max|x| / (2 * 254^3)
 // Integer partial sums are exact; each group contributes one f32 FMA per level.  The split
-// keeps the result within ~1e-5 relative of an f32-accumulated dot (the parity tolerance
-// is 1e-3), and turns byte->float conversion, sign handling and 8 FMAs per 8 weights into
-// two SWAR sign operations and two dp4a per 4 weights.
+// keeps the result within f32 rounding noise of an f32-accumulated dot (the parity
+// tolerance is 1e-3), and turns byte->float conversion, sign handling and 8 FMAs per 8
+// weights into two SWAR sign operations and PB_XLEVELS dp4a per 4 weights.
 //
 // Block layouts restate src/model/gguf_q.rs:67-166 of the reference (see pb_formats.cuh).
 #pragma once
@@ -127,11 +127,17 @@ template <> struct PbQDec<PB_T_Q4_K> {
     }
 };
 
-// Activations of one column for one quarter: two int8 levels, their scales, and the f32 sum
-// of each 32-value group (used by formats with a minimum).
+// Number of int8 levels the activations are split into.  Each level divides the residual
+// error by ~254: two levels leave ~2e-5 of the largest value of a 32-group, three ~1e-7,
+// i.e. the size of f32 summation-order noise.  Three keeps router top-k decisions and
+// greedy tokens aligned with an f32-accumulated reference over long runs.
+#define PB_XLEVELS 3
+
+// Activations of one column for one quarter: PB_XLEVELS int8 levels, their scales, and the
+// f32 sum of each 32-value group (used by formats with a minimum).
 struct PbXQuarter {
-    int q1[16], q2[16];
-    float s1[2], s2[2], sum[2];
+    int q[PB_XLEVELS][16];
+    float s[PB_XLEVELS][2], sum[2];
 };
 
 template <int FMT>
@@ -142,16 +148,19 @@ __device__ __forceinline__ float pb_quarter_dot(const PbQuarter& w, const PbXQua
     constexpr int WPH = 16 / NH;
 #pragma unroll
     for (int h = 0; h < NH; h++) {
-        int i1 = 0, i2 = 0;
+        int isum[PB_XLEVELS];
 #pragma unroll
-        for (int k = 0; k < WPH; k++) { i1 = __dp4a(w.w[h * WPH + k], x.q1[h * WPH + k], i1); i2 = __dp4a(w.w[h * WPH + k], x.q2[h * WPH + k], i2); }
+        for (int l = 0; l < PB_XLEVELS; l++) isum[l] = 0;
+#pragma unroll
+        for (int k = 0; k < WPH; k++)
+#pragma unroll
+            for (int l = 0; l < PB_XLEVELS; l++) isum[l] = __dp4a(w.w[h * WPH + k], x.q[l][h * WPH + k], isum[l]);
         const int g = h * WPH / 8;
-        acc = fmaf(w.sc[h * (4 / NH)], fmaf(x.s1[g], (float)i1, x.s2[g] * (float)i2), acc);
+        float t = x.s[PB_XLEVELS - 1][g] * (float)isum[PB_XLEVELS - 1];   // smallest level first
+#pragma unroll
+        for (int l = PB_XLEVELS - 2; l >= 0; l--) t = fmaf(x.s[l][g], (float)isum[l], t);
+        acc = fmaf(w.sc[h * (4 / NH)], t, acc);
     }
     if (D::HAS_MIN) { acc = fmaf(-w.mn[0], x.sum[0], acc); acc = fmaf(-w.mn[1], x.sum[1], acc); }
     return acc;
 }
-
-// Layout of the quantized activations in shared memory, per column:
-//   q1 words [cols/4], q2 words [cols/4], then s1[cols/32], s2[cols/32], sum[cols/32]
-__host__ __device__ static inline int pb_xq_words(int cols) { return cols / 2 + 3 * (cols / 32); }

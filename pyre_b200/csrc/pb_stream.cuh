@@ -1,0 +1,131 @@
+// Building blocks shared by the streaming dequant kernels (GEMV modes, expert SwiGLU):
+// the shared-memory stage ring fed by 1-D bulk copies, and the in-kernel preparation of
+// activations (RMSNorm variants + split into two int8 levels).
+#pragma once
+#include "pb_qdot.cuh"
+
+#define PB_CONSUMERS 16
+#define PB_KTHREADS ((PB_CONSUMERS + 1) * 32)
+#define PB_STAGES 4
+
+struct PbRing {
+    uint64_t* full;
+    uint64_t* empty;
+    uint8_t* stages;
+    uint32_t stage_bytes;
+};
+
+__device__ __forceinline__ void pb_named_barrier(int id, int nthreads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory"); }
+
+// thread 0 initialises, every thread of the CTA must then pass a __syncthreads()
+__device__ __forceinline__ void pb_ring_init(const PbRing& r, int tid) {
+    if (tid == 0) {
+        for (int s = 0; s < PB_STAGES; s++) { pb_mbar_init(&r.full[s], 1); pb_mbar_init(&r.empty[s], PB_CONSUMERS); }
+        pb_fence_barrier_init();
+    }
+}
+// producer (one thread): make stage k % S writable, announce `bytes`; the caller then issues the copies
+__device__ __forceinline__ bool pb_ring_acquire(const PbRing& r, int k, uint32_t bytes, int* status) {
+    const int s = k % PB_STAGES;
+    if (k >= PB_STAGES && !pb_mbar_wait(&r.empty[s], ((k / PB_STAGES) - 1) & 1, status, PB_DEV_WAIT_EMPTY_TIMEOUT)) return false;
+    pb_mbar_expect_tx(&r.full[s], bytes);
+    return true;
+}
+__device__ __forceinline__ uint8_t* pb_ring_stage(const PbRing& r, int k) { return r.stages + (size_t)(k % PB_STAGES) * r.stage_bytes; }
+__device__ __forceinline__ void pb_ring_copy(const PbRing& r, int k, uint32_t dst_off, const void* src, uint32_t bytes) {
+    pb_bulk_g2s(pb_ring_stage(r, k) + dst_off, src, bytes, &r.full[k % PB_STAGES]);
+}
+// producer error path: give the copies of the last stages a bounded chance to land before the CTA may exit
+__device__ __forceinline__ void pb_ring_drain(const PbRing& r, int issued) {
+    for (int k = max(0, issued - PB_STAGES); k < issued; k++) pb_mbar_wait(&r.full[k % PB_STAGES], (k / PB_STAGES) & 1, nullptr, 0);
+}
+__device__ __forceinline__ bool pb_ring_wait(const PbRing& r, int k, int* status) {
+    return pb_mbar_wait(&r.full[k % PB_STAGES], (k / PB_STAGES) & 1, status, PB_DEV_WAIT_FULL_TIMEOUT);
+}
+// consumer warp: done with stage k
+__device__ __forceinline__ void pb_ring_release(const PbRing& r, int k, int lane) {
+    __syncwarp();
+    if (lane == 0) pb_mbar_arrive(&r.empty[k % PB_STAGES]);
+}
+
+// word offset of quad i (4 words) of quarter qi inside one level array of nq quarters
+// (quad-major so that a warp's 128-bit loads of consecutive quarters never conflict)
+__device__ __forceinline__ int pb_xq_off(int qi, int i, int nq) { return (i * nq + qi) * 4; }
+
+// Quantized activations of one column: PB_XLEVELS arrays of cols/4 words, then PB_XLEVELS scale
+// arrays and the group sums, cols/32 floats each
+__host__ __device__ static inline int pb_xq_words(int cols) { return PB_XLEVELS * (cols / 4) + (PB_XLEVELS + 1) * (cols / 32); }
+
+// One warp splits the 32-value group g of a column (lane = element, v = its value) into
+// PB_XLEVELS int8 levels and stores them in the quad-major layout at `col` (shared or global memory).
+__device__ __forceinline__ void pb_split_group(float v, int lane, int g, int cols, uint32_t* col) {
+    const int ng = cols / 32, nq = cols / 64;
+    float* sc = reinterpret_cast<float*>(col + PB_XLEVELS * (cols / 4));
+    const float sum = pb_warp_sum(v);
+    const int k = lane >> 2;  // word 0..7 of the group = word 8*(g&1)+k of quarter g/2
+    const int off = pb_xq_off(g >> 1, 2 * (g & 1) + (k >> 2), nq) + (k & 3);
+    float r = v;
+#pragma unroll
+    for (int l = 0; l < PB_XLEVELS; l++) {
+        const float m = pb_warp_max(fabsf(r));
+        const float s = m > 0.f && isfinite(m) ? m / 127.f : 0.f;
+        const int a = s > 0.f ? __float2int_rn(r / s) : 0;
+        r = s > 0.f ? fmaf(-s, (float)a, r) : 0.f;
+        uint32_t pa = (uint32_t)(a & 0xFF) << (8 * (lane & 3));
+        pa |= __shfl_xor_sync(0xffffffffu, pa, 1); pa |= __shfl_xor_sync(0xffffffffu, pa, 2);
+        if ((lane & 3) == 0) col[l * (cols / 4) + off] = pa;
+        if (lane == 0) sc[l * ng + g] = s;
+    }
+    if (lane == 0) sc[PB_XLEVELS * ng + g] = sum;
+}
+
+__device__ __forceinline__ void pb_load_xquarter(const uint32_t* xcol, int cols, int qi, PbXQuarter& o) {
+    const int nq = cols / 64, ng = cols / 32;
+    const float* sc = reinterpret_cast<const float*>(xcol + PB_XLEVELS * (cols / 4));
+#pragma unroll
+    for (int l = 0; l < PB_XLEVELS; l++) {
+        const uint32_t* q = xcol + l * (cols / 4);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint4 a = *reinterpret_cast<const uint4*>(q + pb_xq_off(qi, i, nq));
+            o.q[l][4 * i] = (int)a.x; o.q[l][4 * i + 1] = (int)a.y; o.q[l][4 * i + 2] = (int)a.z; o.q[l][4 * i + 3] = (int)a.w;
+        }
+        o.s[l][0] = sc[l * ng + 2 * qi]; o.s[l][1] = sc[l * ng + 2 * qi + 1];
+    }
+    o.sum[0] = sc[PB_XLEVELS * ng + 2 * qi]; o.sum[1] = sc[PB_XLEVELS * ng + 2 * qi + 1];
+}
+
+// Fill the shared-memory codebooks a format needs.  rep = copies per entry (1, or one per bank).
+template <int FMT>
+__device__ __forceinline__ PbQTabs pb_fill_qtabs(uint8_t* sign16_mem, uint8_t* tab, int rep, int tid, int nthreads) {
+    uint2* sign16 = reinterpret_cast<uint2*>(sign16_mem);
+    if (tid < 16) {
+        uint32_t m = 0;
+        for (int j = 0; j < 4; j++) if (tid & (1 << j)) m |= 0xFFu << (8 * j);
+        sign16[tid] = make_uint2(m, m & 0x01010101u);
+    }
+    if (FMT == PB_T_IQ3_S) {
+        uint32_t* g = reinterpret_cast<uint32_t*>(tab);
+        for (int i = tid; i < 512 * rep; i += nthreads) g[i] = PB_IQ3S_GRID[i / rep];
+    }
+    if (FMT == PB_T_IQ2_XS) {
+        uint64_t* g = reinterpret_cast<uint64_t*>(tab);
+        for (int i = tid; i < 512 * rep; i += nthreads) g[i] = PB_IQ2XS_GRID[i / rep];
+    }
+    PbQTabs T;
+    T.sign16 = sign16; T.grid3 = reinterpret_cast<const uint32_t*>(tab); T.grid2 = reinterpret_cast<const uint64_t*>(tab); T.rep3 = T.rep2 = rep;
+    return T;
+}
+template <int FMT> __host__ __device__ constexpr int pb_tab_entry_bytes() { return FMT == PB_T_IQ3_S ? 4 : (FMT == PB_T_IQ2_XS ? 8 : 0); }
+
+// sum over all consumer threads (PB_CONSUMERS warps) of v; red = PB_CONSUMERS floats of shared memory
+__device__ __forceinline__ float pb_consumer_sum(float v, float* red, int warp, int lane) {
+    v = pb_warp_sum(v);
+    pb_named_barrier(2, PB_CONSUMERS * 32);
+    if (lane == 0) red[warp] = v;
+    pb_named_barrier(2, PB_CONSUMERS * 32);
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < PB_CONSUMERS; i++) t += red[i];
+    return t;
+}

@@ -1,0 +1,159 @@
+"""Model / State: the reference's Qwen-Next model surface over the C ABI.
+
+Mirrors `Model` and `State` of src/model/qwen4exp_gguf.rs in the reference (load :462,
+new_state :1345, forward :2050, forward_multi :2365, spec_keep :2495, snapshot/restore
+:3280/:3294) and the `spec::Target` trait that the engine loop calls (src/spec.rs:106-120):
+step -> forward, verify -> forward_multi, keep -> spec_keep.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import Caps, Cfg, Ctx, QMat, ROLE, Stats, _f32, _p, lib
+
+
+class Model:
+    def __init__(self, ctx: Ctx, cfg: Cfg):
+        self.ctx, self.cfg = ctx, cfg
+        self.h = C.c_void_p()
+        ctx.check(lib().pb_model_create(ctx.h, C.byref(cfg), C.byref(self.h)))
+        self.ep_rank, self.ep_world = 0, 1
+
+    def set_tensor(self, layer: int, role: str, m: QMat):
+        """The model takes ownership of the device matrix."""
+        self.ctx.check(lib().pb_model_set_tensor(self.h, C.c_int(layer), C.c_int(ROLE[role]), m.h))
+        m.owned = False
+
+    def set_vec(self, layer: int, role: str, v: np.ndarray):
+        v = _f32(v).reshape(-1)
+        self.ctx.check(lib().pb_model_set_vec(self.h, C.c_int(layer), C.c_int(ROLE[role]), _p(v), C.c_int64(v.size)))
+
+    def finalize(self, ep_rank: int = 0, ep_world: int = 1):
+        self.ctx.check(lib().pb_model_finalize(self.h, C.c_int(ep_rank), C.c_int(ep_world)))
+        self.ep_rank, self.ep_world = ep_rank, ep_world
+
+    def new_state(self, batch: int = 1) -> "State":
+        return State(self, batch)
+
+    def caps(self) -> Caps:
+        c = Caps()
+        self.ctx.check(lib().pb_caps_get(self.h, C.byref(c)))
+        return c
+
+    def destroy(self):
+        if self.h:
+            lib().pb_model_destroy(self.h)
+            self.h = C.c_void_p()
+
+
+class State:
+    """One conversation per batch slot (State, src/model/qwen4exp_gguf.rs:184-207)."""
+
+    def __init__(self, model: Model, batch: int = 1):
+        self.model, self.batch, self.ctx = model, batch, model.ctx
+        self.h = C.c_void_p()
+        self.ctx.check(lib().pb_state_create(model.h, C.c_int(batch), C.byref(self.h)))
+
+    # ---- token loop -------------------------------------------------------------------
+    def forward(self, ids) -> np.ndarray:
+        """Feed ids [batch][t] (or [t] when batch == 1); logits of the last position, [batch][vocab]."""
+        ids = np.ascontiguousarray(ids, dtype=np.uint32).reshape(self.batch, -1)
+        logits = np.empty((self.batch, self.model.cfg.vocab), dtype=np.float32)
+        self.ctx.check(lib().pb_forward(self.h, _p(ids), C.c_int(ids.shape[1]), _p(logits)))
+        return logits
+
+    def step_greedy(self, tok) -> np.ndarray:
+        tok = np.ascontiguousarray(tok, dtype=np.uint32).reshape(self.batch)
+        nxt = np.empty(self.batch, dtype=np.uint32)
+        self.ctx.check(lib().pb_step_greedy(self.h, _p(tok), _p(nxt)))
+        return nxt
+
+    def decode_greedy(self, tok, n: int) -> np.ndarray:
+        """n greedy tokens per sequence without leaving the device between steps: [batch][n]."""
+        tok = np.ascontiguousarray(tok, dtype=np.uint32).reshape(self.batch)
+        out = np.empty((self.batch, n), dtype=np.uint32)
+        self.ctx.check(lib().pb_decode_greedy(self.h, _p(tok), C.c_int(n), _p(out)))
+        return out
+
+    def forward_multi(self, ids) -> np.ndarray:
+        ids = np.ascontiguousarray(ids, dtype=np.uint32).reshape(-1)
+        logits = np.empty((ids.size, self.model.cfg.vocab), dtype=np.float32)
+        self.ctx.check(lib().pb_verify(self.h, _p(ids), C.c_int(ids.size), _p(logits)))
+        return logits
+
+    def spec_keep(self, t: int, keep: int):
+        self.ctx.check(lib().pb_keep(self.h, C.c_int(t), C.c_int(keep)))
+
+    def snapshot(self) -> bytes:
+        n = C.c_size_t()
+        self.ctx.check(lib().pb_state_snapshot(self.h, None, C.byref(n)))
+        buf = np.empty(n.value, dtype=np.uint8)
+        self.ctx.check(lib().pb_state_snapshot(self.h, _p(buf), C.byref(n)))
+        return buf.tobytes()
+
+    def restore(self, blob: bytes):
+        buf = np.frombuffer(blob, dtype=np.uint8)
+        self.ctx.check(lib().pb_state_restore(self.h, _p(buf), C.c_size_t(buf.size)))
+
+    # ---- position / caches -----------------------------------------------------------
+    def set_pos(self, pos: int):
+        self.ctx.check(lib().pb_state_set_pos(self.h, C.c_int64(pos)))
+
+    def pos(self) -> int:
+        p = C.c_int64()
+        self.ctx.check(lib().pb_state_pos(self.h, C.byref(p)))
+        return p.value
+
+    def fill_kv(self, b: int, attn_index: int, k: np.ndarray, v: np.ndarray):
+        k, v = _f32(k), _f32(v)
+        row = self.model.cfg.n_kv * self.model.cfg.hd
+        self.ctx.check(lib().pb_state_fill_kv(self.h, C.c_int(b), C.c_int(attn_index), _p(k), _p(v), C.c_int64(k.size // row)))
+
+    def fill_kv_synth(self, attn_index: int, n: int, seed: int):
+        self.ctx.check(lib().pb_state_fill_kv_synth(self.h, C.c_int(attn_index), C.c_int64(n), C.c_uint64(seed)))
+
+    def get_lin(self, layer: int):
+        c = self.model.cfg
+        ch = 2 * c.lin_nk * c.lin_dk + c.lin_nv * c.lin_dv
+        conv = np.empty((self.batch, c.conv_k - 1, ch), dtype=np.float32)
+        ssm = np.empty((self.batch, c.lin_nv, c.lin_dk, c.lin_dv), dtype=np.float32)
+        self.ctx.check(lib().pb_state_get_lin(self.h, C.c_int(layer), _p(conv), _p(ssm)))
+        return conv, ssm
+
+    def set_lin(self, layer: int, conv: np.ndarray | None, ssm: np.ndarray | None):
+        conv = None if conv is None else _f32(conv)
+        ssm = None if ssm is None else _f32(ssm)
+        self.ctx.check(lib().pb_state_set_lin(self.h, C.c_int(layer), _p(conv), _p(ssm)))
+
+    def stats(self) -> Stats:
+        st = Stats()
+        self.ctx.check(lib().pb_stats_get(self.h, C.byref(st)))
+        return st
+
+    # ---- layer-level entry points ------------------------------------------------------
+    def moe_forward(self, layer: int, x: np.ndarray):
+        x = _f32(x).reshape(-1, self.model.cfg.d)
+        t = x.shape[0]
+        y = np.empty_like(x)
+        sel = np.empty((t, self.model.cfg.top_k), dtype=np.int32)
+        self.ctx.check(lib().pb_moe_forward(self.h, C.c_int(layer), _p(x), C.c_int(t), _p(y), _p(sel)))
+        return y, sel
+
+    def deltanet_step(self, layer: int, x: np.ndarray) -> np.ndarray:
+        x = _f32(x).reshape(self.batch, self.model.cfg.d)
+        y = np.empty_like(x)
+        self.ctx.check(lib().pb_deltanet_step(self.h, C.c_int(layer), _p(x), _p(y)))
+        return y
+
+    def attn_step(self, layer: int, x: np.ndarray) -> np.ndarray:
+        x = _f32(x).reshape(self.batch, self.model.cfg.d)
+        y = np.empty_like(x)
+        self.ctx.check(lib().pb_attn_step(self.h, C.c_int(layer), _p(x), _p(y)))
+        return y
+
+    def destroy(self):
+        if self.h:
+            lib().pb_state_destroy(self.h)
+            self.h = C.c_void_p()

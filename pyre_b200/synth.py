@@ -1,0 +1,87 @@
+"""Seeded synthetic Qwen-Next-style models (random-init weights of the benchmark shapes).
+
+`model_spec` only *describes* the tensors: quantized matrices by (ggml type, rows, cols,
+tensor id) for the counter-based block generator, f32 vectors as numpy arrays.  The same
+description can therefore be realised on the GPU (`build_model`, device-side generation) and
+by any independent checker that implements the documented generator.
+
+Block fields follow the benchmark's config 0: fp16 super-block scale d ~ |N(0, 0.02)|,
+uniform sub-scales, grid indices and sign bits (see the generator notes in csrc/pb_dequant.cu).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from . import Cfg, Ctx, F32, IQ3_S, QMat, ROLE
+from .model import Model
+
+
+def tensor_id(layer: int, role: str) -> int:
+    return (layer + 1) * 64 + ROLE[role]
+
+
+def is_full(cfg: Cfg, il: int) -> bool:
+    return cfg.full_every > 0 and (il + 1) % cfg.full_every == 0
+
+
+def model_spec(cfg: Cfg, seed: int = 0, qtype: int = IQ3_S):
+    """List of ('mat', layer, role, type, rows, cols, tid) and ('vec', layer, role, array)."""
+    rng = np.random.default_rng(seed)
+    d, hd = cfg.d, cfg.hd
+    ch = 2 * cfg.lin_nk * cfg.lin_dk + cfg.lin_nv * cfg.lin_dv
+    spec = []
+
+    def mat(layer, role, rows, cols, t=qtype):
+        spec.append(("mat", layer, role, t, rows, cols, tensor_id(layer, role)))
+
+    def vec(layer, role, arr):
+        spec.append(("vec", layer, role, np.ascontiguousarray(arr, dtype=np.float32)))
+
+    def gamma(n):  # norm weights, stored pre-folded as (1 + w) like the reference's GGUF
+        return 1.0 + 0.1 * rng.standard_normal(n)
+
+    mat(-1, "TOKEN_EMBD", cfg.vocab, d)
+    mat(-1, "OUTPUT", cfg.vocab, d)
+    vec(-1, "OUT_NORM", gamma(d))
+    for il in range(cfg.n_layers):
+        vec(il, "ATTN_NORM", gamma(d))
+        vec(il, "FFN_NORM", gamma(d))
+        if is_full(cfg, il):
+            mat(il, "ATTN_Q", cfg.n_head * 2 * hd, d)
+            mat(il, "ATTN_K", cfg.n_kv * hd, d)
+            mat(il, "ATTN_V", cfg.n_kv * hd, d)
+            mat(il, "ATTN_O", d, cfg.n_head * hd)
+            vec(il, "ATTN_Q_NORM", gamma(hd))
+            vec(il, "ATTN_K_NORM", gamma(hd))
+        else:
+            mat(il, "LIN_QKV", ch, d)
+            mat(il, "LIN_Z", cfg.lin_nv * cfg.lin_dv, d)
+            mat(il, "LIN_BETA", cfg.lin_nv, d)
+            mat(il, "LIN_ALPHA", cfg.lin_nv, d)
+            mat(il, "LIN_OUT", d, cfg.lin_nv * cfg.lin_dv)
+            vec(il, "LIN_A", -np.exp(0.5 * rng.standard_normal(cfg.lin_nv)))      # ssm_a = -exp(A_log)
+            vec(il, "LIN_DT", rng.standard_normal(cfg.lin_nv))
+            vec(il, "LIN_CONV", 0.5 * rng.standard_normal((ch, cfg.conv_k)))
+            vec(il, "LIN_NORM", gamma(cfg.lin_dv))
+        mat(il, "ROUTER", cfg.n_exp, d, F32)                                        # f32 ~ N(0, 0.02)
+        mat(il, "EXP_GATE", cfg.n_exp * cfg.ff_exp, d)
+        mat(il, "EXP_UP", cfg.n_exp * cfg.ff_exp, d)
+        mat(il, "EXP_DOWN", cfg.n_exp * d, cfg.ff_exp)
+        mat(il, "SH_GATE", cfg.ff_sh, d)
+        mat(il, "SH_UP", cfg.ff_sh, d)
+        mat(il, "SH_DOWN", d, cfg.ff_sh)
+        vec(il, "SH_GATE_INP", 0.02 * rng.standard_normal(d))
+    return spec
+
+
+def build_model(ctx: Ctx, cfg: Cfg, spec, seed: int = 0, ep_rank: int = 0, ep_world: int = 1) -> Model:
+    m = Model(ctx, cfg)
+    for item in spec:
+        if item[0] == "mat":
+            _, layer, role, t, rows, cols, tid = item
+            m.set_tensor(layer, role, QMat.synth(ctx, t, rows, cols, seed, tid))
+        else:
+            _, layer, role, arr = item
+            m.set_vec(layer, role, arr)
+    m.finalize(ep_rank, ep_world)
+    return m
