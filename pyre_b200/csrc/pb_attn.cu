@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(AT_THREADS) pb_kv_append_kernel(const PbAttnPa
 // grid (nsplit, n_kv, batch), 256 threads.  Lane l of a warp owns dims 8l..8l+7 of the head
 // (one packed word, or two float4 of an f32 row); a warp walks tiles of 32 positions.
 template <int G>
-__global__ void __launch_bounds__(AT_THREADS, 2) pb_attn_partial_kernel(const PbAttnParams p) {
+__global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const PbAttnParams p) {
     const int sp = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hd = p.hd, half = p.n_rot / 2;
@@ -197,13 +197,36 @@ __global__ void __launch_bounds__(AT_THREADS, 2) pb_attn_partial_kernel(const Pb
     const float* kr = p.kr + hrow * p.ring_cap * hd;
     const float* vr = p.vr + hrow * p.ring_cap * hd;
     float* pw = prob + warp * AT_TILE * G;
+    // per-warp staging of one packed tile: K/V words [32 pos][hd/8] and scales [32 pos][hd/32]
+    uint32_t* tkw = reinterpret_cast<uint32_t*>(mrg + (size_t)AT_WARPS * G * (2 + hd)) + (size_t)warp * 2 * (AT_TILE * (hd / 8) + AT_TILE * (hd / 32));
+    float* tks = reinterpret_cast<float*>(tkw + AT_TILE * (hd / 8));
+    uint32_t* tvw = reinterpret_cast<uint32_t*>(tks + AT_TILE * (hd / 32));
+    float* tvs = reinterpret_cast<float*>(tvw + AT_TILE * (hd / 8));
 
     for (int64_t t = t0 + warp; t < t1; t += AT_WARPS) {
         const int64_t pbase = t * AT_TILE;
+        // q4n is a multiple of 64 and tiles start at multiples of 32: a tile is entirely packed or entirely f32
+        const bool packed = pbase < q4n;
+        if (packed) {
+            // coalesced 16-byte loads of the whole tile (contiguous in the head-major layout), all issued up front
+            const uint4* gk = reinterpret_cast<const uint4*>(kw + pbase * (hd / 8));
+            const uint4* gv = reinterpret_cast<const uint4*>(vw + pbase * (hd / 8));
+            const uint4* gks = reinterpret_cast<const uint4*>(ks + pbase * (hd / 32));
+            const uint4* gvs = reinterpret_cast<const uint4*>(vs + pbase * (hd / 32));
+            uint4 a[8], c[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) { a[i] = gk[i * 32 + lane]; c[i] = gv[i * 32 + lane]; }
+            const uint4 sa0 = gks[lane], sa1 = gks[32 + lane], sc0 = gvs[lane], sc1 = gvs[32 + lane];
+#pragma unroll
+            for (int i = 0; i < 8; i++) { reinterpret_cast<uint4*>(tkw)[i * 32 + lane] = a[i]; reinterpret_cast<uint4*>(tvw)[i * 32 + lane] = c[i]; }
+            reinterpret_cast<uint4*>(tks)[lane] = sa0; reinterpret_cast<uint4*>(tks)[32 + lane] = sa1;
+            reinterpret_cast<uint4*>(tvs)[lane] = sc0; reinterpret_cast<uint4*>(tvs)[32 + lane] = sc1;
+            __syncwarp();
+        }
         // ---- scores of the 32 positions of the tile, 8 positions at a time: every lane holds the
         //      partial dots of its 8 dims for (8 positions x G heads); a transposed butterfly sums
-        //      them over the warp with 8*G - 8*G/32 shuffles instead of 5 per value, leaving
-        //      values 2l*NV/64.. on lane l, which go through shared memory to "lane = position"
+        //      them over the warp, leaving the totals spread over the lanes, which go through
+        //      shared memory to the "lane = position" layout of the softmax
         float sc[G];
 #pragma unroll
         for (int g = 0; g < G; g++) sc[g] = -INFINITY;
@@ -214,18 +237,18 @@ __global__ void __launch_bounds__(AT_THREADS, 2) pb_attn_partial_kernel(const Pb
             for (int i = 0; i < 8; i++) {
                 const int64_t pp = pbase + i0 + i;
                 float kv[8];
-                if (pp >= n) {
-#pragma unroll
-                    for (int j = 0; j < 8; j++) kv[j] = 0.f;
-                } else if (pp < q4n) {
-                    const uint32_t w = kw[pp * (hd / 8) + lane];
-                    const float s = ks[pp * (hd / 32) + (lane >> 2)];
+                if (packed) {
+                    const uint32_t w = tkw[(i0 + i) * (hd / 8) + lane];
+                    const float s = tks[(i0 + i) * (hd / 32) + (lane >> 2)];
 #pragma unroll
                     for (int j = 0; j < 8; j++) kv[j] = pb_kv4_dequant(w, j, s);
-                } else {
+                } else if (pp < n) {
                     const float4* src = reinterpret_cast<const float4*>(kr + (size_t)(pp % p.ring_cap) * hd + 8 * lane);
                     const float4 a = src[0], c = src[1];
                     kv[0] = a.x; kv[1] = a.y; kv[2] = a.z; kv[3] = a.w; kv[4] = c.x; kv[5] = c.y; kv[6] = c.z; kv[7] = c.w;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) kv[j] = 0.f;
                 }
 #pragma unroll
                 for (int g = 0; g < G; g++) {
@@ -236,14 +259,12 @@ __global__ void __launch_bounds__(AT_THREADS, 2) pb_attn_partial_kernel(const Pb
                 }
             }
             pb_transpose_reduce<8 * G>(part, lane);
-            // lane l now holds the totals of flat indices l*NV/32 .. (NV = 8*G values over 32 lanes)
             constexpr int PER = (8 * G) / 32 > 0 ? (8 * G) / 32 : 1;
             if (8 * G >= 32) {
 #pragma unroll
                 for (int e = 0; e < PER; e++) { const int idx = lane * PER + e; pw[(i0 + idx / G) * G + idx % G] = part[e]; }
             } else {
-                // fewer values than lanes: the butterfly stopped early, lanes with equal (lane >> sh) hold duplicates
-                constexpr int SH = G == 2 ? 1 : 2;      // 16 or 8 values
+                constexpr int SH = G == 2 ? 1 : 2;      // 16 or 8 values: lanes with equal (lane >> SH) hold duplicates
                 const int idx = lane >> SH;
                 if ((lane & ((1 << SH) - 1)) == 0) pw[(i0 + idx / G) * G + idx % G] = part[0];
             }
@@ -268,13 +289,14 @@ __global__ void __launch_bounds__(AT_THREADS, 2) pb_attn_partial_kernel(const Pb
         }
         __syncwarp();
         // ---- P.V for the tile
+#pragma unroll 4
         for (int i = 0; i < AT_TILE; i++) {
             const int64_t pp = pbase + i;
             if (pp >= n) break;
             float vv[8];
-            if (pp < q4n) {
-                const uint32_t w = vw[pp * (hd / 8) + lane];
-                const float s = vs[pp * (hd / 32) + (lane >> 2)];
+            if (packed) {
+                const uint32_t w = tvw[i * (hd / 8) + lane];
+                const float s = tvs[i * (hd / 32) + (lane >> 2)];
 #pragma unroll
                 for (int j = 0; j < 8; j++) vv[j] = pb_kv4_dequant(w, j, s);
             } else {
@@ -325,18 +347,29 @@ __global__ void __launch_bounds__(AT_THREADS, 2) pb_attn_partial_kernel(const Pb
 __global__ void pb_attn_combine_kernel(const PbAttnParams p) {
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     const int G = p.n_head / p.n_kv, kvh = h / G, g = h % G;
-    float M = -INFINITY;
-    for (int s = 0; s < p.nsplit; s++) M = fmaxf(M, p.part_ml[((((size_t)b * p.n_kv + kvh) * p.nsplit + s) * G + g) * 2]);
-    float L = 0.f, o = 0.f;
-    for (int s = 0; s < p.nsplit; s++) {
-        const size_t pi = (((size_t)b * p.n_kv + kvh) * p.nsplit + s) * G + g;
-        const float m = p.part_ml[pi * 2];
-        const float f = m == -INFINITY ? 0.f : expf(m - M);
-        L += p.part_ml[pi * 2 + 1] * f;
-        o = fmaf(p.part_acc[pi * p.hd + d], f, o);
+    __shared__ float fs[128];     // per-split factor exp(m_s - M)
+    __shared__ float ML[2];
+    const size_t base = ((size_t)b * p.n_kv + kvh) * p.nsplit;
+    if (d < 32) {
+        float M = -INFINITY;
+        for (int s = d; s < p.nsplit; s += 32) M = fmaxf(M, p.part_ml[((base + s) * G + g) * 2]);
+        M = pb_warp_max(M);
+        float L = 0.f;
+        for (int s = d; s < p.nsplit; s += 32) {
+            const float m = p.part_ml[((base + s) * G + g) * 2];
+            const float f = m == -INFINITY ? 0.f : expf(m - M);
+            fs[s] = f;
+            L += p.part_ml[((base + s) * G + g) * 2 + 1] * f;
+        }
+        L = pb_warp_sum(L);
+        if (d == 0) { ML[0] = M; ML[1] = L; }
     }
+    __syncthreads();
+    float o = 0.f;
+#pragma unroll 8
+    for (int s = 0; s < p.nsplit; s++) o = fmaf(p.part_acc[((base + s) * G + g) * p.hd + d], fs[s], o);
     const float gate = p.proj[(size_t)b * p.ldp + (size_t)h * 2 * p.hd + p.hd + d];
-    p.att[(size_t)b * p.lda + (size_t)h * p.hd + d] = (o * (1.0f / L)) * pb_sigm(gate);
+    p.att[(size_t)b * p.lda + (size_t)h * p.hd + d] = (o * (1.0f / ML[1])) * pb_sigm(gate);
 }
 
 // ------------------------------------------------------------------------------------ launchers
@@ -351,14 +384,15 @@ int pb_launch_kv_append(pb_ctx* ctx, const PbAttnParams& p) {
 
 int pb_launch_attn(pb_ctx* ctx, const PbAttnParams& p) {
     const int G = p.n_head / p.n_kv;
-    if (p.hd != 256 || p.n_head % p.n_kv || (G != 8 && G != 4 && G != 2 && G != 1))
+    if (p.hd != 256 || p.nsplit > 128 || p.n_head % p.n_kv || (G != 8 && G != 4 && G != 2 && G != 1))
         PB_FAIL(ctx, PB_UNSUPPORTED, "attention: head dim %d with %d query heads per KV head not supported", p.hd, G);
     const dim3 grid(p.nsplit, p.n_kv, p.batch);
-    const size_t smem = ((size_t)G * p.hd + (size_t)AT_WARPS * AT_TILE * G + (size_t)AT_WARPS * G * (2 + p.hd)) * 4;
+    const size_t smem = ((size_t)G * p.hd + (size_t)AT_WARPS * AT_TILE * G + (size_t)AT_WARPS * G * (2 + p.hd) + (size_t)AT_WARPS * 2 * (AT_TILE * (p.hd / 8) + AT_TILE * (p.hd / 32))) * 4;
+    if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "attention needs %zu bytes of shared memory", smem);
 #define GO(GG)                                                                                                                   \
     {                                                                                                                            \
         static bool cfgd = false;                                                                                                \
-        if (!cfgd) { PB_CUDA(ctx, cudaFuncSetAttribute(pb_attn_partial_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)); cfgd = true; } \
+        if (!cfgd) { PB_CUDA(ctx, cudaFuncSetAttribute(pb_attn_partial_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->max_smem_optin)); cfgd = true; } \
         pb_attn_partial_kernel<GG><<<grid, AT_THREADS, smem, ctx->stream>>>(p);                                                  \
     }
     if (G == 8) GO(8) else if (G == 4) GO(4) else if (G == 2) GO(2) else GO(1)

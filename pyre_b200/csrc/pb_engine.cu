@@ -34,7 +34,7 @@ struct pb_state {
     int batch = 0;
     int64_t pos_host = 0;
     std::vector<void*> allocs;
-    int64_t* pos = nullptr; uint32_t* ids = nullptr; uint32_t* next = nullptr;
+    int64_t* pos = nullptr; uint32_t* ids = nullptr; uint32_t* next = nullptr; unsigned long long* amax = nullptr;
     float *x = nullptr, *xin = nullptr, *proj = nullptr, *olin = nullptr, *att = nullptr, *rlogits = nullptr, *yout = nullptr;
     uint32_t* xq = nullptr;
     int *sel_e = nullptr, *n_used = nullptr, *used_e = nullptr, *used_off = nullptr, *ent_tok = nullptr, *ent_slot = nullptr;
@@ -245,7 +245,7 @@ int pb_state_create(pb_model* m, int batch, pb_state** out) {
     const int64_t wide = (int64_t)c.lin_nv * c.lin_dv > (int64_t)c.n_head * c.hd ? (int64_t)c.lin_nv * c.lin_dv : (int64_t)c.n_head * c.hd;
     int rc = PB_OK;
 #define A(p, n) if (rc == PB_OK) rc = dalloc(s, &s->p, (size_t)(n))
-    A(pos, B); A(ids, B); A(next, B);
+    A(pos, B); A(ids, B); A(next, B); A(amax, B);
     A(x, (size_t)B * c.d); A(xin, (size_t)B * (wide > c.d ? wide : c.d)); A(yout, (size_t)B * c.d);
     A(proj, (size_t)B * s->ldproj); A(olin, (size_t)B * wide); A(att, (size_t)B * wide);
     A(rlogits, (size_t)B * (c.n_exp + 1));
@@ -257,9 +257,9 @@ int pb_state_create(pb_model* m, int batch, pb_state** out) {
     A(logits, (size_t)B * c.vocab);
     s->trace_cap = 4096;
     A(trace, (size_t)s->trace_cap * B); A(trace_len, 2);
-    // attention: enough splits to cover the SMs about twice over
+    // attention: one CTA per SM (split x KV head x sequence)
     const int G = c.n_kv > 0 ? c.n_head / c.n_kv : 1;
-    int ns = (2 * ctx->sm_count + c.n_kv * B - 1) / (c.n_kv * B > 0 ? c.n_kv * B : 1);
+    int ns = ctx->sm_count / (c.n_kv * B > 0 ? c.n_kv * B : 1);
     if (ns < 1) ns = 1;
     if (ns > 128) ns = 128;
     s->nsplit = ns;
@@ -427,8 +427,8 @@ static int run_step(pb_state* s) {
     a.type = out->type; a.cols = c.d; a.nseg = 1; seg(a, 0, out, 0);
     a.x = s->x; a.ldx = c.d; a.y = s->logits; a.ldy = c.vocab; a.mode = PB_ACT_NORM; a.norm_w = V(m, -1, PB_R_OUT_NORM); a.eps = c.eps;
     PB_TRY(gemv_cols(ctx, a, B));
-    PB_TRY(pb_launch_argmax(ctx, s->logits, c.vocab, c.vocab, B, s->next));
-    return pb_launch_advance(ctx, s->pos, B, s->next, s->ids, s->trace, s->trace_len, s->trace_cap);
+    PB_TRY(pb_launch_argmax(ctx, s->logits, c.vocab, c.vocab, B, s->amax));
+    return pb_launch_advance(ctx, s->pos, B, s->amax, s->next, s->ids, s->trace, s->trace_len, s->trace_cap);
 }
 
 // Replays the step graph (captured on first use after one eager warm-up step would be wasteful:

@@ -68,20 +68,22 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
     if (p.mode == PB_ACT_PREQ) {
         for (int i = tid; i < NB * xw; i += CT) { const int b = i / xw; xq[i] = b < p.t ? p.xq_in[(size_t)b * xw + (i - b * xw)] : 0u; }
     } else if (p.mode == PB_ACT_GNORM) {
-        // per head: rms_inplace(o, norm, eps) then * sigmoid(z)  (linear_core, qwen4exp_gguf.rs:1667)
-        const int kper = p.head_dim / 32, nheads = cols / p.head_dim;
+        // per head: rms_inplace(o, norm, eps) then * sigmoid(z)  (linear_core, qwen4exp_gguf.rs:1667).
+        // A warp takes one head of 128 (= four groups) per pass: lane l owns elements 4l..4l+3.
+        const int nheads = cols / p.head_dim;
         for (int i = warp; i < NB * nheads; i += PB_CONSUMERS) {
             const int b = i / nheads, h = i - b * nheads;
-            float v[8];
-            float ss = 0.f;
-            for (int k = 0; k < kper; k++) { v[k] = b < p.t ? p.x[b * p.ldx + h * p.head_dim + 32 * k + lane] : 0.f; ss += v[k] * v[k]; }
-            ss = pb_warp_sum(ss);
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (b < p.t) v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + h * p.head_dim + 4 * lane);
+            const float ss = pb_warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
             const float s = 1.0f / sqrtf(ss / (float)p.head_dim + p.eps);
-            for (int k = 0; k < kper; k++) {
-                float o = v[k] * (s * p.norm_w[32 * k + lane]);
-                if (b < p.t) o *= pb_sigm(p.z[b * p.ldz + h * p.head_dim + 32 * k + lane]);
-                pb_split_group(o, lane, h * kper + k, cols, xq + (size_t)b * xw);
+            const float4 w = *reinterpret_cast<const float4*>(p.norm_w + 4 * lane);
+            v.x *= s * w.x; v.y *= s * w.y; v.z *= s * w.z; v.w *= s * w.w;
+            if (b < p.t) {
+                const float4 z = *reinterpret_cast<const float4*>(p.z + b * p.ldz + h * p.head_dim + 4 * lane);
+                v.x *= pb_sigm(z.x); v.y *= pb_sigm(z.y); v.z *= pb_sigm(z.z); v.w *= pb_sigm(z.w);
             }
+            pb_split_groups4(v, lane, h * 4, cols, xq + (size_t)b * xw);
         }
     } else {
         for (int b = 0; b < NB; b++) {
@@ -92,10 +94,14 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
                 ss = pb_consumer_sum(ss, red, warp, lane);
                 s = 1.0f / sqrtf(ss / (float)cols + p.eps);
             }
-            for (int g = warp; g < ng; g += PB_CONSUMERS) {
-                float v = b < p.t ? p.x[b * p.ldx + 32 * g + lane] : 0.f;
-                if (p.mode == PB_ACT_NORM) v = v * s * p.norm_w[32 * g + lane];
-                pb_split_group(v, lane, g, cols, xq + (size_t)b * xw);
+            for (int g0 = warp * 4; g0 < ng; g0 += PB_CONSUMERS * 4) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (b < p.t) v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + 32 * g0 + 4 * lane);
+                if (p.mode == PB_ACT_NORM) {
+                    const float4 w = *reinterpret_cast<const float4*>(p.norm_w + 32 * g0 + 4 * lane);
+                    v.x = v.x * s * w.x; v.y = v.y * s * w.y; v.z = v.z * s * w.z; v.w = v.w * s * w.w;
+                }
+                pb_split_groups4(v, lane, g0, cols, xq + (size_t)b * xw);
             }
         }
     }
@@ -241,13 +247,26 @@ int pb_launch_gemvq(pb_ctx* ctx, const PbGemvQArgs& a) {
     if (pb_geom(a.type, &el, &bs) || !pb_gemvq_supported(a.type, a.cols)) PB_FAIL(ctx, PB_UNSUPPORTED, "gemvq: type %d cols %d not supported by the integer kernel", a.type, a.cols);
     if (a.t < 1 || a.t > 16) PB_FAIL(ctx, PB_ERR_ARG, "gemv: t=%d outside 1..16", a.t);
     if (a.nseg < 1 || a.nseg > 4) PB_FAIL(ctx, PB_ERR_ARG, "gemv: %d segments", a.nseg);
+    if (a.mode == PB_ACT_GNORM && a.head_dim != 128) PB_FAIL(ctx, PB_UNSUPPORTED, "gemv: gated norm over heads of %d (128 is built)", a.head_dim);
+    if (((uintptr_t)a.x & 15) || (a.ldx & 3)) PB_FAIL(ctx, PB_ERR_ARG, "gemv: activations must be 16-byte aligned");
     const int row_bytes = a.cols / el * bs;
-    switch (a.type) {
-        case PB_T_IQ3_S: return launch_q_fmt<PB_T_IQ3_S>(ctx, a, row_bytes);
-        case PB_T_IQ2_XS: return launch_q_fmt<PB_T_IQ2_XS>(ctx, a, row_bytes);
-        case PB_T_Q4_K: return launch_q_fmt<PB_T_Q4_K>(ctx, a, row_bytes);
-        default: return launch_q_fmt<PB_T_Q8_0>(ctx, a, row_bytes);
+    // column tiles: the int8-split activations of one launch must fit in ~96 KB of shared memory
+    int tile = 16;
+    while (tile > 1 && (size_t)tile * pb_xq_words(a.cols) * 4 > 98304) tile /= 2;
+    int rc = PB_OK;
+    for (int t0 = 0; t0 < a.t && rc == PB_OK; t0 += tile) {
+        PbGemvQArgs s = a;
+        s.t = a.t - t0 < tile ? a.t - t0 : tile;
+        s.x = a.x ? a.x + (int64_t)t0 * a.ldx : nullptr; s.y = a.y + (int64_t)t0 * a.ldy; s.z = a.z ? a.z + (int64_t)t0 * a.ldz : nullptr;
+        s.xq_in = a.xq_in ? a.xq_in + (size_t)t0 * pb_xq_words(a.cols) : nullptr;
+        switch (a.type) {
+            case PB_T_IQ3_S: rc = launch_q_fmt<PB_T_IQ3_S>(ctx, s, row_bytes); break;
+            case PB_T_IQ2_XS: rc = launch_q_fmt<PB_T_IQ2_XS>(ctx, s, row_bytes); break;
+            case PB_T_Q4_K: rc = launch_q_fmt<PB_T_Q4_K>(ctx, s, row_bytes); break;
+            default: rc = launch_q_fmt<PB_T_Q8_0>(ctx, s, row_bytes); break;
+        }
     }
+    return rc;
 }
 
 int pb_launch_gemv_f32(pb_ctx* ctx, const PbGemvArgs& a);

@@ -37,48 +37,58 @@ int pb_launch_embed(pb_ctx* ctx, int type, const uint8_t* w, int64_t rows, int c
     return PB_OK;
 }
 
-// sampler::argmax, src/sampler.rs:142-148: first index of the maximum.  grid (t), 1024 threads
-__global__ void __launch_bounds__(1024) pb_argmax_kernel(const float* __restrict__ logits, int64_t ld, int n, uint32_t* __restrict__ out) {
-    const float* v = logits + (size_t)blockIdx.x * ld;
-    float best = -INFINITY; int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < n; i += 1024) { const float x = v[i]; if (x > best || (x == best && i < bi)) { best = x; bi = i; } }
-    __shared__ float sv[32]; __shared__ int si[32];
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-    }
-    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+// sampler::argmax, src/sampler.rs:142-148: first index of the maximum.  grid (blocks, t): every CTA
+// scans a slice and folds its best (value, index) into one 64-bit key per sequence with atomicMax;
+// the key orders by value first and by lower index second, NaN counts as the lowest value.
+__device__ __forceinline__ unsigned long long pb_argmax_key(float v, int i) {
+    uint32_t u = __float_as_uint(v);
+    u = (v != v) ? 0u : ((u & 0x80000000u) ? ~u : (u | 0x80000000u));
+    return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)i);
+}
+__global__ void __launch_bounds__(256) pb_argmax_kernel(const float* __restrict__ logits, int64_t ld, int n, unsigned long long* __restrict__ keys) {
+    const float* v = logits + (size_t)blockIdx.y * ld;
+    unsigned long long best = 0;
+    for (int i = blockIdx.x * 256 + threadIdx.x; i < n; i += gridDim.x * 256) { const unsigned long long k = pb_argmax_key(v[i], i); best = k > best ? k : best; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { const unsigned long long ok = __shfl_xor_sync(0xffffffffu, best, o); best = ok > best ? ok : best; }
+    __shared__ unsigned long long sk[8];
+    if ((threadIdx.x & 31) == 0) sk[threadIdx.x >> 5] = best;
     __syncthreads();
-    if (threadIdx.x < 32) {
-        best = sv[threadIdx.x]; bi = si[threadIdx.x];
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-        }
-        if (threadIdx.x == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0u : (uint32_t)bi;   // all-NaN row: index 0, like the reference loop
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++) best = sk[w] > best ? sk[w] : best;
+        atomicMax(keys + blockIdx.y, best);
     }
 }
 
-int pb_launch_argmax(pb_ctx* ctx, const float* logits, int64_t ld, int n, int t, uint32_t* out) {
-    pb_argmax_kernel<<<t, 1024, 0, ctx->stream>>>(logits, ld, n, out);
+int pb_launch_argmax(pb_ctx* ctx, const float* logits, int64_t ld, int n, int t, unsigned long long* keys) {
+    int blocks = (n + 2047) / 2048;
+    if (blocks > 148) blocks = 148;
+    pb_argmax_kernel<<<dim3(blocks, t), 256, 0, ctx->stream>>>(logits, ld, n, keys);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;
 }
 
-// end of a decode step: pos += 1; optionally feed the chosen tokens back as the next inputs and log them
-__global__ void pb_advance_kernel(int64_t* pos, int t, const uint32_t* next, uint32_t* ids, uint32_t* trace, int64_t* trace_len, int64_t trace_cap) {
+// end of a decode step: decode the argmax keys into token ids (and clear them for the next step),
+// pos += 1, feed the chosen tokens back as the next inputs and log them
+__global__ void pb_advance_kernel(int64_t* pos, int t, unsigned long long* keys, uint32_t* next, uint32_t* ids, uint32_t* trace, int64_t* trace_len, int64_t trace_cap) {
     const int b = threadIdx.x;
-    if (b >= t) return;
-    pos[b] += 1;
-    if (next && ids) ids[b] = next[b];
-    if (next && trace && trace_len) { const int64_t k = *trace_len; if (k < trace_cap) trace[k * t + b] = next[b]; }
+    if (b < t) {
+        const unsigned long long k = keys[b];
+        const uint32_t tok = k ? 0xFFFFFFFFu - (uint32_t)(k & 0xFFFFFFFFull) : 0u;
+        keys[b] = 0;
+        pos[b] += 1;
+        next[b] = tok;
+        ids[b] = tok;
+        const int64_t j = *trace_len;
+        if (j < trace_cap) trace[j * t + b] = tok;
+    }
     __syncthreads();
-    if (b == 0 && trace_len && next && trace) *trace_len += 1;
+    if (b == 0) *trace_len += 1;
 }
 
-int pb_launch_advance(pb_ctx* ctx, int64_t* pos, int t, const uint32_t* next, uint32_t* ids, uint32_t* trace, int64_t* trace_len, int64_t trace_cap) {
-    pb_advance_kernel<<<1, t < 32 ? 32 : ((t + 31) & ~31), 0, ctx->stream>>>(pos, t, next, ids, trace, trace_len, trace_cap);
+int pb_launch_advance(pb_ctx* ctx, int64_t* pos, int t, unsigned long long* keys, uint32_t* next, uint32_t* ids, uint32_t* trace, int64_t* trace_len, int64_t trace_cap) {
+    pb_advance_kernel<<<1, (t + 31) & ~31, 0, ctx->stream>>>(pos, t, keys, next, ids, trace, trace_len, trace_cap);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;

@@ -21,11 +21,12 @@
 
 // ------------------------------------------------------------------------------------ router
 
-// grid: ceil((n_exp + 1) / 8) CTAs of 256 threads; warp per router row (row n_exp = shared-gate vector)
+// grid: ceil((n_exp + 1) / 8) CTAs of 256 threads; warp per router row (row n_exp = shared-gate vector).
+// CTA j additionally splits groups 4j..4j+3 of every token's normalized activations into int8
+// levels for the expert kernels, so that work is spread over the grid.
 __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p) {
-    extern __shared__ float rs[];   // scale[t] then one row of normalized x (cols floats) for the quantizer
+    extern __shared__ float rs[];   // scale[t]
     float* scale = rs;
-    float* xn = rs + ((p.t + 31) & ~31);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     __shared__ float red[8];
     // per-token RMS scale (rms(): 1 / sqrt(mean(x^2) + eps), qwen4exp_gguf.rs:209)
@@ -33,7 +34,7 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p) 
         float s = 1.0f;
         if (p.norm_w) {
             float ss = 0.f;
-            for (int c = tid; c < p.cols; c += 256) { const float v = p.x[b * p.ldx + c]; ss += v * v; }
+            for (int c = tid * 4; c < p.cols; c += 1024) { const float4 v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + c); ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
             ss = pb_warp_sum(ss);
             __syncthreads();
             if (lane == 0) red[warp] = ss;
@@ -45,16 +46,17 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p) 
         if (tid == 0) scale[b] = s;
     }
     __syncthreads();
-    // CTA j emits token j's normalized activations: f32 copy (optional) and int8 split
-    for (int b = blockIdx.x; b < p.t; b += gridDim.x) {
-        for (int c = tid; c < p.cols; c += 256) {
-            float v = p.x[b * p.ldx + c];
-            if (p.norm_w) v = v * scale[b] * p.norm_w[c];
-            xn[c] = v;
+    const int ng = p.cols / 32;
+    for (int g0 = blockIdx.x * 4; g0 < ng; g0 += gridDim.x * 4) {
+        for (int b = warp; b < p.t; b += 8) {
+            float4 v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + 32 * g0 + 4 * lane);
+            if (p.norm_w) {
+                const float4 n = *reinterpret_cast<const float4*>(p.norm_w + 32 * g0 + 4 * lane);
+                const float s = scale[b];
+                v.x = v.x * s * n.x; v.y = v.y * s * n.y; v.z = v.z * s * n.z; v.w = v.w * s * n.w;
+            }
+            pb_split_groups4(v, lane, g0, p.cols, p.xq_out + (size_t)b * pb_xq_words(p.cols));
         }
-        __syncthreads();
-        for (int g = warp; g < p.cols / 32; g += 8) pb_split_group(xn[32 * g + lane], lane, g, p.cols, p.xq_out + (size_t)b * pb_xq_words(p.cols));
-        __syncthreads();
     }
     const int row = blockIdx.x * 8 + warp;
     if (row > p.n_exp) return;
@@ -63,6 +65,7 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p) 
     for (int b = 0; b < p.t; b++) {
         float acc = 0.f;
         const float s = scale[b];
+#pragma unroll 4
         for (int c = lane * 4; c < p.cols; c += 128) {
             const float4 w = *reinterpret_cast<const float4*>(wrow + c);
             float4 v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + c);
@@ -79,55 +82,67 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p) 
 
 // ------------------------------------------------------------------------------------ routing
 
-// one CTA of 512 threads; warp per token (loops if t > 16)
+// one CTA of 512 threads; warp per token (loops if t > 16).  Everything stays in registers:
+// lane l holds experts l, l+32, ... of the token.
 __global__ void __launch_bounds__(512) pb_route_kernel(const PbRouteParams p) {
     extern __shared__ int rsm[];
-    int* cnt = rsm;                 // [n_exp] entries per expert (local experts only)
-    int* cursor = rsm + p.n_exp;    // [n_exp]
+    int* cnt = rsm;                 // [1024] entries per expert (local experts only)
+    int* cursor = rsm + 1024;       // [1024] start offset of the expert's entries, then a fill cursor
+    __shared__ int wsum[2][16];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    for (int e = tid; e < p.n_exp; e += 512) { cnt[e] = 0; cursor[e] = 0; }
+    for (int e = tid; e < 1024; e += 512) { cnt[e] = 0; cursor[e] = 0; }
     __syncthreads();
     for (int b = warp; b < p.t; b += 16) {
         const float* lg = p.logits + (size_t)b * (p.n_exp + 1);
-        // lane holds experts lane, lane+32, ... ; NaN -> -inf (nan_clean :3121-3125)
         float v[32];
-        const int per = (p.n_exp + 31) / 32;
-        for (int i = 0; i < per && i < 32; i++) { const int e = i * 32 + lane; float x = e < p.n_exp ? lg[e] : -INFINITY; v[i] = isnan(x) ? -INFINITY : x; }
-        int sel_e[PB_MAX_TOPK]; float sel_v[PB_MAX_TOPK];
+#pragma unroll
+        for (int i = 0; i < 32; i++) { const int e = i * 32 + lane; const float x = e < p.n_exp ? lg[e] : -INFINITY; v[i] = isnan(x) ? -INFINITY : x; }   // nan_clean :3121-3125
+        int my_e = 0; float my_v = -INFINITY;     // lane j keeps the j-th pick (descending logit, ties to the lower id)
         for (int j = 0; j < p.top_k; j++) {
             float bv = -INFINITY; int be = 0x7fffffff;
-            for (int i = 0; i < per && i < 32; i++) { const int e = i * 32 + lane; if (e < p.n_exp && (v[i] > bv || (v[i] == bv && e < be))) { bv = v[i]; be = e; } }
-            // -inf candidates that were already taken are marked with NaN below, so they never compare equal
+#pragma unroll
+            for (int i = 0; i < 32; i++) { const int e = i * 32 + lane; if (e < p.n_exp && (v[i] > bv || (v[i] == bv && e < be))) { bv = v[i]; be = e; } }
+#pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
                 const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const int oe = __shfl_xor_sync(0xffffffffu, be, o);
                 if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
             }
-            sel_e[j] = be; sel_v[j] = bv;
-            if ((be & 31) == lane) v[be >> 5] = __int_as_float(0x7fc00000);  // taken: NaN compares false everywhere
+            if (lane == j) { my_e = be; my_v = bv; }
+#pragma unroll
+            for (int i = 0; i < 32; i++) if (i * 32 + lane == be) v[i] = __int_as_float(0x7fc00000);   // taken: NaN never compares greater or equal
         }
-        if (lane == 0) {
-            // softmax over the selection in descending-logit order (top_k :3136-3138, soft_top :3126-3131)
-            float mx = -INFINITY;
-            for (int j = 0; j < p.top_k; j++) mx = fmaxf(mx, sel_v[j]);
-            float w[PB_MAX_TOPK];
-            if (!isfinite(mx)) { for (int j = 0; j < p.top_k; j++) w[j] = 1.0f / (float)(p.top_k > 0 ? p.top_k : 1); }
-            else { float sum = 0.f; for (int j = 0; j < p.top_k; j++) { w[j] = expf(sel_v[j] - mx); sum += w[j]; } for (int j = 0; j < p.top_k; j++) w[j] = w[j] / sum; }
-            // accumulate in ascending expert id (routed f32 branch :1786): insertion sort by id
-            for (int j = 1; j < p.top_k; j++) { const int e = sel_e[j]; const float ww = w[j]; int i = j - 1; while (i >= 0 && sel_e[i] > e) { sel_e[i + 1] = sel_e[i]; w[i + 1] = w[i]; i--; } sel_e[i + 1] = e; w[i + 1] = ww; }
-            for (int j = 0; j < p.top_k; j++) {
-                p.sel_e[b * p.top_k + j] = sel_e[j]; p.sel_w[b * p.top_k + j] = w[j];
-                if (sel_e[j] >= p.e_lo && sel_e[j] < p.e_hi) atomicAdd(&cnt[sel_e[j]], 1);
-            }
+        // softmax over the selection, summed in descending-logit order (top_k :3136-3138, soft_top :3126-3131)
+        float mx = lane < p.top_k ? my_v : -INFINITY;
+        mx = pb_warp_max(mx);
+        float w = lane < p.top_k ? expf(my_v - mx) : 0.f;
+        float sum = 0.f;
+        for (int j = 0; j < p.top_k; j++) sum += __shfl_sync(0xffffffffu, w, j);
+        w = isfinite(mx) ? w / sum : 1.0f / (float)(p.top_k > 0 ? p.top_k : 1);
+        // accumulation order = ascending expert id (routed f32 branch :1786): rank of this lane's expert
+        int rank = 0;
+        for (int j = 0; j < p.top_k; j++) { const int oe = __shfl_sync(0xffffffffu, my_e, j); if (oe < my_e) rank++; }
+        if (lane < p.top_k) {
+            p.sel_e[b * p.top_k + rank] = my_e; p.sel_w[b * p.top_k + rank] = w;
+            if (my_e >= p.e_lo && my_e < p.e_hi) atomicAdd(&cnt[my_e], 1);
         }
     }
     __syncthreads();
-    // compact the distinct local experts in ascending id with entry offsets (thread 0: n_exp <= 1024 steps)
-    if (tid == 0) {
-        int n = 0, off = 0;
-        for (int e = p.e_lo; e < p.e_hi; e++) if (cnt[e]) { p.used_e[n] = e; p.used_off[n] = off; cursor[e] = off; off += cnt[e]; n++; }
-        p.used_off[n] = off;
-        *p.n_used = n;
-    }
+    // distinct local experts in ascending id with entry offsets: block-wide exclusive scans of
+    // (used flag, entry count) over expert ids; thread t owns experts 2t and 2t+1
+    const int e0 = 2 * tid, e1 = 2 * tid + 1;
+    const int c0 = e0 < p.n_exp ? cnt[e0] : 0, c1 = e1 < p.n_exp ? cnt[e1] : 0;
+    int f = (c0 > 0) + (c1 > 0), c = c0 + c1;
+    int fi = f, ci = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const int a = __shfl_up_sync(0xffffffffu, fi, o), d = __shfl_up_sync(0xffffffffu, ci, o); if (lane >= o) { fi += a; ci += d; } }
+    if (lane == 31) { wsum[0][warp] = fi; wsum[1][warp] = ci; }
+    __syncthreads();
+    int fb = 0, cb = 0;
+    for (int w2 = 0; w2 < warp; w2++) { fb += wsum[0][w2]; cb += wsum[1][w2]; }
+    int n = fb + fi - f, off = cb + ci - c;   // exclusive prefixes for expert e0
+    if (c0 > 0) { p.used_e[n] = e0; p.used_off[n] = off; cursor[e0] = off; n++; off += c0; }
+    if (c1 > 0) { p.used_e[n] = e1; p.used_off[n] = off; cursor[e1] = off; n++; off += c1; }
+    if (tid == 511) { p.used_off[n] = off; *p.n_used = n; }
     __syncthreads();
     for (int i = tid; i < p.t * p.top_k; i += 512) {
         const int e = p.sel_e[i];
@@ -305,7 +320,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
             const float* hv = shared ? p.h_sh + (size_t)tok * cols : p.h + (size_t)en * cols;
             // split this entry's hidden vector into int8 levels (all consumer warps, one group each)
             pb_named_barrier(1, CT);
-            for (int g = warp; g < ng; g += PB_CONSUMERS) pb_split_group(hv[32 * g + lane], lane, g, cols, xq);
+            for (int g0 = warp * 4; g0 < ng; g0 += PB_CONSUMERS * 4) pb_split_groups4(*reinterpret_cast<const float4*>(hv + 32 * g0 + 4 * lane), lane, g0, cols, xq);
             pb_named_barrier(1, CT);
             float* dst; float wgt = 1.0f;
             if (shared) dst = p.part_sh + (size_t)tok * p.rows_e;
@@ -353,7 +368,7 @@ __global__ void __launch_bounds__(256) pb_moe_combine_kernel(const PbCombinePara
 int pb_launch_router(pb_ctx* ctx, const PbRouterParams& p) {
     if (p.cols % 128) PB_FAIL(ctx, PB_UNSUPPORTED, "router: width %d is not a multiple of 128", p.cols);
     const int grid = (p.n_exp + 1 + 7) / 8;
-    const size_t smem = (size_t)(((p.t + 31) & ~31) + p.cols) * 4;
+    const size_t smem = (size_t)((p.t + 31) & ~31) * 4;
     pb_router_kernel<<<grid, 256, smem, ctx->stream>>>(p);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
@@ -362,7 +377,7 @@ int pb_launch_router(pb_ctx* ctx, const PbRouterParams& p) {
 
 int pb_launch_route(pb_ctx* ctx, const PbRouteParams& p) {
     if (p.top_k > PB_MAX_TOPK || p.n_exp > 1024) PB_FAIL(ctx, PB_UNSUPPORTED, "route: top_k %d / n_exp %d beyond %d / 1024", p.top_k, p.n_exp, PB_MAX_TOPK);
-    pb_route_kernel<<<1, 512, (size_t)p.n_exp * 8, ctx->stream>>>(p);
+    pb_route_kernel<<<1, 512, 2048 * sizeof(int), ctx->stream>>>(p);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;

@@ -56,27 +56,36 @@ __device__ __forceinline__ int pb_xq_off(int qi, int i, int nq) { return (i * nq
 // arrays and the group sums, cols/32 floats each
 __host__ __device__ static inline int pb_xq_words(int cols) { return PB_XLEVELS * (cols / 4) + (PB_XLEVELS + 1) * (cols / 32); }
 
-// One warp splits the 32-value group g of a column (lane = element, v = its value) into
-// PB_XLEVELS int8 levels and stores them in the quad-major layout at `col` (shared or global memory).
-__device__ __forceinline__ void pb_split_group(float v, int lane, int g, int cols, uint32_t* col) {
+// One warp splits FOUR consecutive 32-value groups of a column at once: lane l owns elements
+// 4*(l&7) .. +3 of group g0 + (l>>3), so a reduction over a group is 3 shuffles and every lane
+// packs its own word.  v = the lane's four values.  Output: PB_XLEVELS int8 levels in the
+// quad-major layout at `col` (shared or global memory), their scales and the group sums.
+__device__ __forceinline__ void pb_split_groups4(float4 v, int lane, int g0, int cols, uint32_t* col) {
     const int ng = cols / 32, nq = cols / 64;
     float* sc = reinterpret_cast<float*>(col + PB_XLEVELS * (cols / 4));
-    const float sum = pb_warp_sum(v);
-    const int k = lane >> 2;  // word 0..7 of the group = word 8*(g&1)+k of quarter g/2
+    const int g = g0 + (lane >> 3), k = lane & 7;   // word k of group g = word 8*(g&1)+k of quarter g/2
     const int off = pb_xq_off(g >> 1, 2 * (g & 1) + (k >> 2), nq) + (k & 3);
-    float r = v;
+    float sum = (v.x + v.y) + (v.z + v.w);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1); sum += __shfl_xor_sync(0xffffffffu, sum, 2); sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    float r[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int l = 0; l < PB_XLEVELS; l++) {
-        const float m = pb_warp_max(fabsf(r));
+        float m = fmaxf(fmaxf(fabsf(r[0]), fabsf(r[1])), fmaxf(fabsf(r[2]), fabsf(r[3])));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1)); m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2)); m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
         const float s = m > 0.f && isfinite(m) ? m / 127.f : 0.f;
-        const int a = s > 0.f ? __float2int_rn(r / s) : 0;
-        r = s > 0.f ? fmaf(-s, (float)a, r) : 0.f;
-        uint32_t pa = (uint32_t)(a & 0xFF) << (8 * (lane & 3));
-        pa |= __shfl_xor_sync(0xffffffffu, pa, 1); pa |= __shfl_xor_sync(0xffffffffu, pa, 2);
-        if ((lane & 3) == 0) col[l * (cols / 4) + off] = pa;
-        if (lane == 0) sc[l * ng + g] = s;
+        const float inv = s > 0.f ? 1.0f / s : 0.f;
+        uint32_t pa = 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            int a = __float2int_rn(r[j] * inv);
+            a = max(-127, min(127, a));
+            r[j] = s > 0.f ? fmaf(-s, (float)a, r[j]) : 0.f;
+            pa |= (uint32_t)(a & 0xFF) << (8 * j);
+        }
+        col[l * (cols / 4) + off] = pa;
+        if (k == 0) sc[l * ng + g] = s;
     }
-    if (lane == 0) sc[PB_XLEVELS * ng + g] = sum;
+    if (k == 0) sc[PB_XLEVELS * ng + g] = sum;
 }
 
 __device__ __forceinline__ void pb_load_xquarter(const uint32_t* xcol, int cols, int qi, PbXQuarter& o) {
