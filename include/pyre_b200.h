@@ -85,6 +85,21 @@ int pb_qmat_dequant_dev(pb_ctx* ctx, const pb_qmat* m, int64_t r0, int64_t nrows
  * device-buffer form. */
 int pb_gemv(pb_ctx* ctx, const pb_qmat* m, const float* x_host, int t, float* y_host);
 int pb_gemv_dev(pb_ctx* ctx, const pb_qmat* m, const float* x_dev, int t, float* y_dev);
+/* pb_gemv for callers that must not allocate device memory.  No counterpart in the reference.
+ * Some hosts of this library run with device allocation closed to them: a real-time worker that
+ * may not take the driver's allocator lock in its serving loop, a process whose memory budget was
+ * handed out in full at start-up, or a sandbox that filters cudaMalloc.  pb_gemv grows a
+ * cudaMalloc'd staging buffer on demand; this variant stages x and y in a fixed array that is part
+ * of the library image (PB_GEMV_STATIC_MAX_BYTES, resident on every GPU that loads the library until
+ * the process exits) and calls no cudaMalloc / cudaFree or any allocating routine.  Same kernels and
+ * same results as pb_gemv.  Limit: 256-rounded t*cols*4 plus t*rows*4 bytes must fit the array,
+ * otherwise PB_ERR_ARG with a message naming both sizes.  The first call on a device looks up the
+ * array's device address; make that call before starting any stream capture.  All calls share the one
+ * array and it keeps the previous call's bytes (nothing in it needs to start at zero: x is
+ * overwritten and every y element is stored); two calls that overlap on the GPU, from two contexts
+ * or two streams, race on it. */
+#define PB_GEMV_STATIC_MAX_BYTES (4u << 20)
+int pb_gemv_static(pb_ctx* ctx, const pb_qmat* m, const float* x_host, int t, float* y_host);
 
 /* ---------------------------------------------------------------- model */
 

@@ -203,6 +203,15 @@ class QMat:
         self.ctx.check(lib().pb_gemv(self.ctx.h, self.h, _p(x), C.c_int(t), _p(y)))
         return y
 
+    def matmul_static(self, x: np.ndarray, t: int | None = None) -> np.ndarray:
+        """`matmul` without device allocation: stages through the fixed array built into the
+        library (see pb_gemv_static); raises when t * (cols + rows) floats exceed that array."""
+        x = _f32(x).reshape(-1, self.cols)
+        t = x.shape[0] if t is None else t
+        y = np.empty((t, self.rows), dtype=np.float32)
+        self.ctx.check(lib().pb_gemv_static(self.ctx.h, self.h, _p(x), C.c_int(t), _p(y)))
+        return y
+
     def matmul_dev(self, x_dev: int, t: int, y_dev: int):
         """Device-pointer form (pointers as integers, e.g. torch.Tensor.data_ptr())."""
         self.ctx.check(lib().pb_gemv_dev(self.ctx.h, self.h, C.c_void_p(x_dev), C.c_int(t), C.c_void_p(y_dev)))

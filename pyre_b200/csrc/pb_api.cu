@@ -225,4 +225,34 @@ int pb_gemv(pb_ctx* ctx, const pb_qmat* m, const float* x_host, int t, float* y_
     return PB_OK;
 }
 
+// ---------------------------------------------------------------- pb_gemv_static
+// Device staging area of pb_gemv_static: a fixed array inside the library image instead of a
+// cudaMalloc'd buffer.  Every GPU that loads the library carries these bytes until the
+// process exits.  In host code the symbol is only a stand-in; the device address is fetched
+// with cudaGetSymbolAddress once per device (with that device current) and cached.
+static __device__ __align__(256) unsigned char pb_static_scratch[PB_GEMV_STATIC_MAX_BYTES];
+static void* g_static_scratch_addr[64] = {nullptr};
+
+int pb_gemv_static(pb_ctx* ctx, const pb_qmat* m, const float* x_host, int t, float* y_host) {
+    if (!ctx || !m) return PB_ERR_ARG;
+    if (!x_host || !y_host) PB_FAIL(ctx, PB_ERR_ARG, "pb_gemv_static: null buffer");
+    if (t <= 0) return t == 0 ? PB_OK : PB_ERR_ARG;
+    if (ctx->device < 0 || ctx->device >= 64) PB_FAIL(ctx, PB_UNSUPPORTED, "pb_gemv_static: device index %d", ctx->device);
+    const size_t xb = ((size_t)t * m->cols * 4 + 255) & ~(size_t)255, yb = (size_t)t * m->rows * 4;
+    if (xb + yb > (size_t)PB_GEMV_STATIC_MAX_BYTES)
+        PB_FAIL(ctx, PB_ERR_ARG, "pb_gemv_static: %zu bytes of staging needed (t * (cols + rows) floats), the built-in area holds %u; use pb_gemv", xb + yb, (unsigned)PB_GEMV_STATIC_MAX_BYTES);
+    if (!g_static_scratch_addr[ctx->device]) {   // first call on this device: resolve the device address of the array
+        PB_CUDA(ctx, cudaSetDevice(ctx->device));
+        void* p = nullptr;
+        PB_CUDA(ctx, cudaGetSymbolAddress(&p, pb_static_scratch));
+        g_static_scratch_addr[ctx->device] = p;
+    }
+    float* xd = (float*)g_static_scratch_addr[ctx->device];
+    float* yd = (float*)((uint8_t*)xd + xb);
+    PB_CUDA(ctx, cudaMemcpyAsync(xd, x_host, (size_t)t * m->cols * 4, cudaMemcpyHostToDevice, ctx->stream));
+    PB_TRY(pb_gemv_dev(ctx, m, xd, t, yd));
+    PB_CUDA(ctx, cudaMemcpyAsync(y_host, yd, yb, cudaMemcpyDeviceToHost, ctx->stream));
+    return pb_sync_check(ctx, "pb_gemv_static");
+}
+
 }  // extern "C"
