@@ -60,6 +60,15 @@ int pb_ctx_sync(pb_ctx* ctx);
 /* Reads and clears the device status word (0 = no kernel reported a failure). */
 int pb_ctx_device_status(pb_ctx* ctx, int* status);
 
+/* Expert-parallel group over NCCL (NVLink / NVSwitch), one process per GPU.  It replaces the
+ * reference's CPU/GPU expert split (XCache + CPU pool, src/model/qwen4exp_gguf.rs:66-72, 785-893):
+ * rank r of `world` holds experts [r*n_exp/world, (r+1)*n_exp/world) of every layer.  Rank 0 calls
+ * pb_ep_unique_id, the host distributes the 128 bytes (any transport), then every rank calls
+ * pb_ep_init before pb_model_finalize(model, rank, world).  libnccl.so.2 is loaded on first use. */
+int pb_ep_unique_id(pb_ctx* ctx, void* id128);
+int pb_ep_init(pb_ctx* ctx, const void* id128, int rank, int world);
+int pb_ep_destroy(pb_ctx* ctx);
+
 /* (elements per block, bytes per block) -- QType::geom, src/model/gguf_q.rs:33-41 */
 int pb_type_geom(int ggml_type, int* elems, int* bytes);
 
@@ -72,6 +81,8 @@ int pb_qmat_upload(pb_ctx* ctx, int ggml_type, int64_t rows, int64_t cols, const
 /* Seeded synthetic matrix generated on the GPU (benchmark weights; no counterpart in the
  * reference, whose tests patch LCG-random block bytes the same way, src/model/qdot.rs:1033-1047). */
 int pb_qmat_synth(pb_ctx* ctx, int ggml_type, int64_t rows, int64_t cols, uint64_t seed, uint64_t tensor_id, pb_qmat** out);
+/* Rows [row0, row0 + rows) of the synthetic tensor (seed, tensor_id): one GPU's shard of a fused expert tensor. */
+int pb_qmat_synth_rows(pb_ctx* ctx, int ggml_type, int64_t rows, int64_t cols, uint64_t seed, uint64_t tensor_id, int64_t row0, pb_qmat** out);
 int pb_qmat_free(pb_qmat* m);
 int pb_qmat_info(const pb_qmat* m, int* ggml_type, int64_t* rows, int64_t* cols, size_t* nbytes);
 /* Raw block bytes of rows [r0, r0+nrows) back to the host (QMat::raw_rows :214). */

@@ -126,6 +126,16 @@ class Ctx:
         self.check(lib().pb_ctx_device_status(self.h, C.byref(st)))
         return st.value
 
+    # ---- expert-parallel group (NCCL) ----
+    def ep_unique_id(self) -> bytes:
+        buf = C.create_string_buffer(128)
+        self.check(lib().pb_ep_unique_id(self.h, buf))
+        return buf.raw
+
+    def ep_init(self, uid: bytes, rank: int, world: int):
+        assert len(uid) == 128
+        self.check(lib().pb_ep_init(self.h, C.c_char_p(uid), C.c_int(rank), C.c_int(world)))
+
     def close(self):
         if self.h:
             lib().pb_ctx_destroy(self.h)
@@ -172,6 +182,13 @@ class QMat:
     def synth(cls, ctx: Ctx, t: int, rows: int, cols: int, seed: int, tid: int) -> "QMat":
         h = C.c_void_p()
         ctx.check(lib().pb_qmat_synth(ctx.h, C.c_int(t), C.c_int64(rows), C.c_int64(cols), C.c_uint64(seed), C.c_uint64(tid), C.byref(h)))
+        return cls(ctx, h, t, rows, cols)
+
+    @classmethod
+    def synth_rows(cls, ctx: Ctx, t: int, rows: int, cols: int, seed: int, tid: int, row0: int) -> "QMat":
+        """Rows [row0, row0 + rows) of the synthetic tensor (seed, tid)."""
+        h = C.c_void_p()
+        ctx.check(lib().pb_qmat_synth_rows(ctx.h, C.c_int(t), C.c_int64(rows), C.c_int64(cols), C.c_uint64(seed), C.c_uint64(tid), C.c_int64(row0), C.byref(h)))
         return cls(ctx, h, t, rows, cols)
 
     def row_bytes(self) -> int:

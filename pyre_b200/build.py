@@ -59,7 +59,7 @@ def build(force: bool = False, verbose: bool = False, jobs: int | None = None) -
             sys.stderr.write(out)
         if p.returncode:
             raise RuntimeError(f"nvcc failed on {src.name}")
-    subprocess.run([nvcc(), *ARCH, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart"], check=True)
+    subprocess.run([nvcc(), *ARCH, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart", "-ldl"], check=True)
     return LIB
 
 

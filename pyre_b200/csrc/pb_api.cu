@@ -63,6 +63,7 @@ int pb_ctx_destroy(pb_ctx* ctx) {
     if (!ctx) return PB_OK;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    pb_ep_destroy(ctx);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
     if (ctx->host_status) cudaFreeHost(ctx->host_status);
@@ -134,12 +135,17 @@ int pb_qmat_upload(pb_ctx* ctx, int type, int64_t rows, int64_t cols, const void
 }
 
 int pb_qmat_synth(pb_ctx* ctx, int type, int64_t rows, int64_t cols, uint64_t seed, uint64_t tid, pb_qmat** out) {
+    return pb_qmat_synth_rows(ctx, type, rows, cols, seed, tid, 0, out);
+}
+
+int pb_qmat_synth_rows(pb_ctx* ctx, int type, int64_t rows, int64_t cols, uint64_t seed, uint64_t tid, int64_t row0, pb_qmat** out) {
     if (!ctx) return PB_ERR_ARG;
+    if (row0 < 0) PB_FAIL(ctx, PB_ERR_ARG, "pb_qmat_synth_rows: negative row offset");
     PB_TRY(qmat_alloc(ctx, type, rows, cols, out));
     pb_qmat* m = *out;
     int rc;
-    if (type == PB_T_F32) rc = pb_launch_synth_normal(ctx, reinterpret_cast<float*>(m->data), rows * cols, seed, tid, 0.02f);
-    else { int el, bs; pb_geom(type, &el, &bs); rc = pb_launch_synth(ctx, type, m->data, rows * (cols / el), seed, tid); }
+    if (type == PB_T_F32) rc = pb_launch_synth_normal_at(ctx, reinterpret_cast<float*>(m->data), rows * cols, seed, tid, row0 * cols, 0.02f);
+    else { int el, bs; pb_geom(type, &el, &bs); rc = pb_launch_synth(ctx, type, m->data, rows * (cols / el), seed, tid, row0 * (cols / el)); }
     if (rc != PB_OK) { pb_qmat_free(m); *out = nullptr; }
     return rc;
 }

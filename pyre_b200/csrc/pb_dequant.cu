@@ -75,11 +75,11 @@ __device__ static inline uint16_t pb_synth_scale(uint64_t bkey, int j0) {
 }
 
 template <int FMT>
-__global__ void __launch_bounds__(256) pb_synth_kernel(uint8_t* __restrict__ w, int64_t nblocks, uint64_t tkey) {
+__global__ void __launch_bounds__(256) pb_synth_kernel(uint8_t* __restrict__ w, int64_t nblocks, uint64_t tkey, int64_t block0) {
     constexpr int BS = FMT == PB_T_Q8_0 ? 34 : PbFmt<FMT>::STEP_BYTES;
     const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= nblocks) return;
-    const uint64_t k = pb_sm64(tkey ^ ((uint64_t)b * 0xD1342543DE82EF95ull));
+    const uint64_t k = pb_sm64(tkey ^ ((uint64_t)(block0 + b) * 0xD1342543DE82EF95ull));
     uint16_t* o = reinterpret_cast<uint16_t*>(w + b * BS);  // every block size is even
     o[0] = pb_synth_scale(k, 0);
     int j0 = 3, off = 1, payload = BS - 2;
@@ -107,14 +107,14 @@ __global__ void __launch_bounds__(256) pb_synth_normal_kernel(float* __restrict_
     out[i] = __fmul_rn(pb_synth_normal(k, 0), sigma);
 }
 
-int pb_launch_synth(pb_ctx* ctx, int type, uint8_t* w, int64_t nblocks, uint64_t seed, uint64_t tid) {
+int pb_launch_synth(pb_ctx* ctx, int type, uint8_t* w, int64_t nblocks, uint64_t seed, uint64_t tid, int64_t block0) {
     const uint64_t tkey = pb_sm64(pb_sm64(seed) ^ tid);
     const unsigned grid = (unsigned)((nblocks + 255) / 256);
     switch (type) {
-        case PB_T_Q8_0: pb_synth_kernel<PB_T_Q8_0><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey); break;
-        case PB_T_Q4_K: pb_synth_kernel<PB_T_Q4_K><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey); break;
-        case PB_T_IQ2_XS: pb_synth_kernel<PB_T_IQ2_XS><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey); break;
-        case PB_T_IQ3_S: pb_synth_kernel<PB_T_IQ3_S><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey); break;
+        case PB_T_Q8_0: pb_synth_kernel<PB_T_Q8_0><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
+        case PB_T_Q4_K: pb_synth_kernel<PB_T_Q4_K><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
+        case PB_T_IQ2_XS: pb_synth_kernel<PB_T_IQ2_XS><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
+        case PB_T_IQ3_S: pb_synth_kernel<PB_T_IQ3_S><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
         default: PB_FAIL(ctx, PB_ERR_ARG, "pb_qmat_synth: no generator for ggml type %d", type);
     }
     ctx->kernels_launched++;

@@ -138,6 +138,7 @@ int pb_model_finalize(pb_model* m, int ep_rank, int ep_world) {
     pb_ctx* ctx = m->ctx;
     const pb_cfg& c = m->cfg;
     if (ep_world < 1 || ep_rank < 0 || ep_rank >= ep_world || c.n_exp % ep_world) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_finalize: rank %d of %d with %d experts", ep_rank, ep_world, c.n_exp);
+    if (ep_world > 1 && (!ctx->ep_comm || ctx->ep_world != ep_world || ctx->ep_rank != ep_rank)) PB_FAIL(ctx, PB_ERR_STATE, "pb_model_finalize: call pb_ep_init(rank %d, world %d) on this context first", ep_rank, ep_world);
     m->ep_rank = ep_rank; m->ep_world = ep_world;
     m->e_lo = ep_rank * (c.n_exp / ep_world); m->e_hi = m->e_lo + c.n_exp / ep_world;
     const int ch = 2 * c.lin_nk * c.lin_dk + c.lin_nv * c.lin_dv, row = c.n_kv * c.hd;
@@ -406,6 +407,9 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
     e.w_a = dn->data; e.w_b = nullptr; e.sh_a = M(m, il, PB_R_SH_DOWN)->data; e.sh_b = nullptr;
     e.rows_e = c.d; e.rows_sh = c.d;
     PB_TRY(pb_launch_expert_down(ctx, e, dn->type, c.ff_exp));
+    // expert parallelism: every (token, slot) row was produced on exactly one rank and is zero elsewhere,
+    // so the sum is an exact gather and the combine below sees the same bits for every GPU count
+    if (m->ep_world > 1) PB_TRY(pb_ep_allreduce(ctx, s->part, (size_t)t * c.top_k * c.d));
     PbCombineParams k; memset(&k, 0, sizeof k);
     k.part = s->part; k.part_sh = s->part_sh; k.logits = s->rlogits; k.t = t; k.d = c.d; k.top_k = c.top_k; k.n_exp = c.n_exp;
     k.y = y; k.ldy = ldy; k.accumulate = accumulate;

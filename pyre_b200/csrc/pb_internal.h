@@ -21,7 +21,11 @@ struct pb_ctx {
     void* scratch = nullptr;
     size_t scratch_bytes = 0;
     uint64_t kernels_launched = 0;
+    // expert-parallel group (pb_ep.cu); ep_comm is an ncclComm_t
+    void* ep_comm = nullptr;
+    int ep_rank = 0, ep_world = 1;
 };
+int pb_ep_allreduce(pb_ctx* ctx, float* buf, size_t n);
 
 struct pb_qmat {
     pb_ctx* ctx = nullptr;
@@ -58,7 +62,7 @@ int pb_sync_check(pb_ctx* ctx, const char* who);
 
 // pb_dequant.cu
 int pb_launch_dequant(pb_ctx* ctx, int type, const uint8_t* w, int64_t nsteps, float* out);
-int pb_launch_synth(pb_ctx* ctx, int type, uint8_t* w, int64_t nblocks, uint64_t seed, uint64_t tid);
+int pb_launch_synth(pb_ctx* ctx, int type, uint8_t* w, int64_t nblocks, uint64_t seed, uint64_t tid, int64_t block0 = 0);
 int pb_launch_synth_normal(pb_ctx* ctx, float* out, int64_t n, uint64_t seed, uint64_t tid, float sigma);
 int pb_launch_synth_normal_at(pb_ctx* ctx, float* out, int64_t n, uint64_t seed, uint64_t tid, int64_t i0, float sigma);
 

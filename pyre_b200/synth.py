@@ -13,6 +13,7 @@ from __future__ import annotations
 import numpy as np
 
 from . import Cfg, Ctx, F32, IQ3_S, QMat, ROLE
+from . import parallel
 from .model import Model
 
 
@@ -79,7 +80,13 @@ def build_model(ctx: Ctx, cfg: Cfg, spec, seed: int = 0, ep_rank: int = 0, ep_wo
     for item in spec:
         if item[0] == "mat":
             _, layer, role, t, rows, cols, tid = item
-            m.set_tensor(layer, role, QMat.synth(ctx, t, rows, cols, seed, tid))
+            if ep_world > 1 and role in ("EXP_GATE", "EXP_UP", "EXP_DOWN"):
+                # this rank's contiguous shard of the fused expert tensor
+                per = rows // cfg.n_exp
+                lo, hi = parallel.ep_range(cfg.n_exp, ep_rank, ep_world)
+                m.set_tensor(layer, role, QMat.synth_rows(ctx, t, (hi - lo) * per, cols, seed, tid, lo * per))
+            else:
+                m.set_tensor(layer, role, QMat.synth(ctx, t, rows, cols, seed, tid))
         else:
             _, layer, role, arr = item
             m.set_vec(layer, role, arr)
