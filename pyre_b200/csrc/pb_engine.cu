@@ -47,6 +47,9 @@ struct pb_state {
     uint32_t* trace = nullptr; int64_t* trace_len = nullptr; int64_t trace_cap = 0;
     uint32_t* pin_u32 = nullptr;   // pinned staging for ids / next tokens
     cudaGraphExec_t graph = nullptr;
+    // speculative verify: DeltaNet (conv ring, ssm) after each of the first t-1 tokens of the last window
+    std::vector<float*> ck_conv, ck_ssm;   // [n_lin * PB_MAX_WINDOW]
+    int verify_t = 0; int64_t verify_pos0 = 0;
     uint64_t steps = 0, kernels_per_step = 0;
 };
 
@@ -511,12 +514,146 @@ int pb_decode_greedy(pb_state* s, const uint32_t* tok_host, int n, uint32_t* out
     return PB_OK;
 }
 
-// verify / keep / draft / snapshot: declared surface, built in a later step of this file's history
-int pb_verify(pb_state* s, const uint32_t*, int, float*) { if (!s) return PB_ERR_ARG; PB_FAIL(s->m->ctx, PB_UNSUPPORTED, "pb_verify is not built yet"); }
-int pb_keep(pb_state* s, int, int) { if (!s) return PB_ERR_ARG; PB_FAIL(s->m->ctx, PB_UNSUPPORTED, "pb_keep is not built yet"); }
+#define PB_MAX_WINDOW 8   // draft windows of the reference are at most 8 tokens (src/spec.rs:185)
+
+static size_t conv_elems(const pb_cfg& c, int B) { return (size_t)B * c.conv_k * (2 * c.lin_nk * c.lin_dk + c.lin_nv * c.lin_dv); }
+static size_t ssm_elems(const pb_cfg& c, int B) { return (size_t)B * c.lin_nv * c.lin_dk * c.lin_dv; }
+
+// Model::forward_multi, src/model/qwen4exp_gguf.rs:2365-2480: logits for every fed position and a
+// rollback checkpoint of the recurrent state after each of the first t-1 tokens (:2386-2387).
+// The window is fed token by token through the decode graph (a batched tensor-core GEMM for t >= 16
+// is not built), so the arithmetic is exactly that of t calls of pb_forward.
+int pb_verify(pb_state* s, const uint32_t* ids_host, int t, float* logits_host) {
+    if (!s) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    if (!ids_host || !logits_host) PB_FAIL(ctx, PB_ERR_ARG, "pb_verify: null buffer");
+    if (s->batch != 1) PB_FAIL(ctx, PB_ERR_STATE, "pb_verify: the state must have batch 1 (it has %d)", s->batch);
+    if (t < 1 || t > PB_MAX_WINDOW) PB_FAIL(ctx, PB_ERR_ARG, "pb_verify: window of %d tokens (1..%d)", t, PB_MAX_WINDOW);
+    if (s->pos_host + t > c.max_ctx) PB_FAIL(ctx, PB_ERR_STATE, "context is full (%d positions)", c.max_ctx);
+    const int nl = s->m->n_lin;
+    if (s->ck_conv.empty() && nl > 0) {
+        s->ck_conv.assign((size_t)nl * PB_MAX_WINDOW, nullptr); s->ck_ssm.assign((size_t)nl * PB_MAX_WINDOW, nullptr);
+        for (size_t i = 0; i < s->ck_conv.size(); i++) { PB_TRY(dalloc(s, &s->ck_conv[i], conv_elems(c, 1))); PB_TRY(dalloc(s, &s->ck_ssm[i], ssm_elems(c, 1))); }
+    }
+    s->verify_pos0 = s->pos_host; s->verify_t = 0;
+    for (int j = 0; j < t; j++) {
+        s->pin_u32[0] = ids_host[j];
+        PB_CUDA(ctx, cudaMemcpyAsync(s->ids, s->pin_u32, 4, cudaMemcpyHostToDevice, ctx->stream));
+        PB_TRY(step_once(s));
+        PB_CUDA(ctx, cudaMemcpyAsync(logits_host + (size_t)j * c.vocab, s->logits, (size_t)c.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        if (j + 1 < t)
+            for (int li = 0; li < nl; li++) {
+                PB_CUDA(ctx, cudaMemcpyAsync(s->ck_conv[(size_t)li * PB_MAX_WINDOW + j], s->conv[li], conv_elems(c, 1) * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+                PB_CUDA(ctx, cudaMemcpyAsync(s->ck_ssm[(size_t)li * PB_MAX_WINDOW + j], s->ssm[li], ssm_elems(c, 1) * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+            }
+        PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // the pinned id word is reused
+    }
+    PB_TRY(pb_sync_check(ctx, "pb_verify"));
+    s->verify_t = t;
+    return PB_OK;
+}
+
+// Model::spec_keep :2495-2515: keep the first `keep` of the last t verified tokens: restore the
+// DeltaNet state from checkpoint keep-1 and truncate the KV cache and position.  The packed KV
+// boundary trails the newest position by at least kv_recent >= 64 > window, so truncation never
+// reaches packed rows; ring rows of dropped positions are overwritten when new tokens arrive.
+int pb_keep(pb_state* s, int t, int keep) {
+    if (!s) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    if (s->verify_t == 0 || t != s->verify_t) PB_FAIL(ctx, PB_ERR_STATE, "pb_keep: t=%d does not match the last verify window (%d)", t, s->verify_t);
+    if (keep < 1 || keep > t) PB_FAIL(ctx, PB_ERR_ARG, "pb_keep: keep=%d outside 1..%d", keep, t);
+    if (keep < t) {
+        for (int li = 0; li < s->m->n_lin; li++) {
+            PB_CUDA(ctx, cudaMemcpyAsync(s->conv[li], s->ck_conv[(size_t)li * PB_MAX_WINDOW + keep - 1], conv_elems(c, 1) * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+            PB_CUDA(ctx, cudaMemcpyAsync(s->ssm[li], s->ck_ssm[(size_t)li * PB_MAX_WINDOW + keep - 1], ssm_elems(c, 1) * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+        }
+        PB_TRY(pb_state_set_pos(s, s->verify_pos0 + keep));
+    }
+    s->verify_t = 0;
+    return PB_OK;
+}
+
 int pb_draft(pb_state* s, int, uint32_t*, int* n) { if (!s) return PB_ERR_ARG; if (n) *n = 0; PB_FAIL(s->m->ctx, PB_UNSUPPORTED, "no drafter: use the caller's n-gram drafter"); }
-int pb_state_snapshot(pb_state* s, void*, size_t*) { if (!s) return PB_ERR_ARG; PB_FAIL(s->m->ctx, PB_UNSUPPORTED, "pb_state_snapshot is not built yet"); }
-int pb_state_restore(pb_state* s, const void*, size_t) { if (!s) return PB_ERR_ARG; PB_FAIL(s->m->ctx, PB_UNSUPPORTED, "pb_state_restore is not built yet"); }
+
+// Model::snapshot / restore, Snap :3277-3298.  Layout: header, then per DeltaNet layer [conv ring][ssm],
+// then per attention layer and (sequence, KV head): q4n, packed K words/scales, packed V words/scales for
+// positions [0, q4n), f32 ring rows of K and V for positions [q4n, len).
+struct PbSnapHeader { uint64_t magic; int32_t n_layers, d, batch, kv_bits; int64_t pos; uint64_t bytes; };
+static const uint64_t kSnapMagic = 0x3150414e53425050ull;   // "PPBSNAP1"
+
+static size_t snap_size(const pb_state* s) {
+    const pb_cfg& c = s->m->cfg; const int B = s->batch;
+    const int64_t len = s->pos_host;
+    const int64_t q4n = c.kv_bits == 4 && len > c.kv_recent ? ((len - c.kv_recent) / 64) * 64 : 0;
+    size_t n = sizeof(PbSnapHeader) + (size_t)s->m->n_lin * (conv_elems(c, B) + ssm_elems(c, B)) * 4;
+    const size_t per_head = 8 + 2 * ((size_t)q4n * (c.hd / 8) * 4 + (size_t)q4n * (c.hd / 32) * 4) + 2 * (size_t)(len - q4n) * c.hd * 4;
+    return n + (size_t)s->m->n_attn * B * c.n_kv * per_head;
+}
+
+static int snap_io(pb_state* s, uint8_t* buf, bool save) {
+    pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg; const int B = s->batch;
+    const cudaMemcpyKind kind = save ? cudaMemcpyDeviceToHost : cudaMemcpyHostToDevice;
+    const int64_t len = s->pos_host;
+    const int64_t q4n = c.kv_bits == 4 && len > c.kv_recent ? ((len - c.kv_recent) / 64) * 64 : 0;
+    uint8_t* p = buf + sizeof(PbSnapHeader);
+    auto io = [&](void* dev, size_t bytes) -> int {
+        if (bytes) { if (save) PB_CUDA(ctx, cudaMemcpy(p, dev, bytes, kind)); else PB_CUDA(ctx, cudaMemcpy(dev, p, bytes, kind)); }
+        p += bytes; return PB_OK;
+    };
+    for (int li = 0; li < s->m->n_lin; li++) { PB_TRY(io(s->conv[li], conv_elems(c, B) * 4)); PB_TRY(io(s->ssm[li], ssm_elems(c, B) * 4)); }
+    for (int ai = 0; ai < s->m->n_attn; ai++) {
+        PbKv& k = s->kv[ai];
+        for (int b = 0; b < B; b++)
+            for (int h = 0; h < c.n_kv; h++) {
+                const size_t head = (size_t)b * c.n_kv + h;
+                int64_t q = q4n;
+                if (save) memcpy(p, &q, 8); else PB_CUDA(ctx, cudaMemcpy(k.q4n + b, &q, 8, cudaMemcpyHostToDevice));
+                p += 8;
+                const size_t pm = c.kv_bits == 4 ? (size_t)c.max_ctx : 1;
+                PB_TRY(io(k.kw + head * pm * (c.hd / 8), (size_t)q4n * (c.hd / 8) * 4)); PB_TRY(io(k.ks + head * pm * (c.hd / 32), (size_t)q4n * (c.hd / 32) * 4));
+                PB_TRY(io(k.vw + head * pm * (c.hd / 8), (size_t)q4n * (c.hd / 8) * 4)); PB_TRY(io(k.vs + head * pm * (c.hd / 32), (size_t)q4n * (c.hd / 32) * 4));
+                for (int which = 0; which < 2; which++) {
+                    float* ring = (which ? k.vr : k.kr) + head * s->ring_cap * c.hd;
+                    for (int64_t pp = q4n; pp < len;) {   // contiguous runs inside the ring
+                        const int64_t slot = pp % s->ring_cap, run = (len - pp) < (s->ring_cap - slot) ? (len - pp) : (s->ring_cap - slot);
+                        PB_TRY(io(ring + (size_t)slot * c.hd, (size_t)run * c.hd * 4));
+                        pp += run;
+                    }
+                }
+            }
+    }
+    return PB_OK;
+}
+
+int pb_state_snapshot(pb_state* s, void* buf_host, size_t* nbytes) {
+    if (!s || !nbytes) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx;
+    const size_t need = snap_size(s);
+    if (!buf_host) { *nbytes = need; return PB_OK; }
+    if (*nbytes < need) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_snapshot: buffer of %zu bytes, %zu needed", *nbytes, need);
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    PbSnapHeader h; memset(&h, 0, sizeof h);
+    h.magic = kSnapMagic; h.n_layers = s->m->cfg.n_layers; h.d = s->m->cfg.d; h.batch = s->batch; h.kv_bits = s->m->cfg.kv_bits; h.pos = s->pos_host; h.bytes = need;
+    memcpy(buf_host, &h, sizeof h);
+    PB_TRY(snap_io(s, (uint8_t*)buf_host, true));
+    *nbytes = need;
+    return PB_OK;
+}
+
+int pb_state_restore(pb_state* s, const void* buf_host, size_t nbytes) {
+    if (!s) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx;
+    if (!buf_host || nbytes < sizeof(PbSnapHeader)) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_restore: truncated snapshot");
+    PbSnapHeader h; memcpy(&h, buf_host, sizeof h);
+    if (h.magic != kSnapMagic) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_restore: not a snapshot");
+    if (h.n_layers != s->m->cfg.n_layers || h.d != s->m->cfg.d || h.batch != s->batch || h.kv_bits != s->m->cfg.kv_bits) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_restore: snapshot of a different model or batch");
+    if (h.pos < 0 || h.pos > s->m->cfg.max_ctx || h.bytes != nbytes) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_restore: truncated or corrupt snapshot (%zu bytes, header says %llu)", nbytes, (unsigned long long)h.bytes);
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    PB_TRY(pb_state_set_pos(s, h.pos));
+    if (snap_size(s) != nbytes) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_restore: size mismatch");
+    s->verify_t = 0;
+    return snap_io(s, (uint8_t*)const_cast<void*>(buf_host), false);
+}
 
 int pb_stats_get(const pb_state* s, pb_stats* out) {
     if (!s || !out) return PB_ERR_ARG;

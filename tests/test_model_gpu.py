@@ -73,3 +73,56 @@ def test_context_limit_and_bad_calls(ctx):
     with pytest.raises(pb.PyreError):
         pb.model.Model(ctx, small_cfg(pb, hc=4))              # hyper-connections are not built
     st.destroy(); m.destroy()
+
+
+def test_verify_and_keep_roll_back(ctx):
+    """forward_multi / spec_keep (:2365-2515): per-position logits equal token-by-token forward; keeping a
+    prefix of the window leaves the state exactly as if only that prefix had been fed."""
+    cfg = small_cfg(pb, n_layers=8, kv_bits=4, kv_recent=64, max_ctx=256)
+    spec = synth.model_spec(cfg, 4)
+    m = synth.build_model(ctx, cfg, spec, 4)
+    om, _ = oracle_model(cfg, spec, 4)
+    prompt = np.array([9, 8, 7, 6, 5, 4], np.uint32)
+    window = np.array([100, 200, 300, 400, 500], np.uint32)
+    a = m.new_state(1); a.forward(prompt)
+    lg = a.forward_multi(window)
+    assert lg.shape == (5, cfg.vocab) and a.pos() == 11
+    b = m.new_state(1); b.forward(prompt)
+    ost = om.new_state(); ost.forward(prompt.tolist())
+    for j, tok in enumerate(window):
+        assert np.array_equal(lg[j], b.forward([tok])[0])                    # same kernels, same bits
+        assert rel_err(lg[j], ost.forward([int(tok)])) < 1e-3               # and the oracle agrees
+    a.spec_keep(5, 2)                                                        # accept 100, 200; drop the rest
+    assert a.pos() == 8
+    c = m.new_state(1); c.forward(np.concatenate([prompt, window[:2]]))
+    assert a.decode_greedy([77], 24)[0].tolist() == c.decode_greedy([77], 24)[0].tolist()
+    # keeping the whole window is a no-op; mismatched calls fail loudly
+    a.forward_multi(window[:3]); a.spec_keep(3, 3)
+    with pytest.raises(pb.PyreError):
+        a.spec_keep(3, 1)                                                    # no window pending
+    with pytest.raises(pb.PyreError):
+        a.forward_multi(np.arange(9, dtype=np.uint32))                       # window larger than 8
+    for s in (a, b, c):
+        s.destroy()
+    m.destroy()
+
+
+@pytest.mark.parametrize("kv_bits", [0, 4])
+def test_snapshot_restore(ctx, kv_bits):
+    """snapshot / restore (Snap :3277-3298): a restored state continues with identical tokens."""
+    cfg = small_cfg(pb, n_layers=8, kv_bits=kv_bits, kv_recent=64, max_ctx=400)
+    spec = synth.model_spec(cfg, 6)
+    m = synth.build_model(ctx, cfg, spec, 6)
+    a = m.new_state(1)
+    first = a.decode_greedy([3], 150)[0]                  # crosses the first 4-bit repack boundary at 128
+    blob = a.snapshot()
+    cont = a.decode_greedy([int(first[-1])], 40)[0]
+    b = m.new_state(1)
+    b.restore(blob)
+    assert b.pos() == 150
+    assert b.decode_greedy([int(first[-1])], 40)[0].tolist() == cont.tolist()
+    with pytest.raises(pb.PyreError):
+        b.restore(blob[:100])                              # truncated
+    with pytest.raises(pb.PyreError):
+        m.new_state(2).restore(blob)                       # different batch
+    a.destroy(); b.destroy(); m.destroy()
