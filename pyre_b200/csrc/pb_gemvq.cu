@@ -28,7 +28,6 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
     ring.full = reinterpret_cast<uint64_t*>(smem);
     ring.empty = ring.full + PB_STAGES;
     float* red = reinterpret_cast<float*>(smem + 64);            // PB_CONSUMERS floats
-    uint8_t* sign16 = smem + 128;
     uint8_t* tab = smem + 256;
     const int cols = p.bpr * 256;
     uint32_t* xq = reinterpret_cast<uint32_t*>(tab + p.tab_bytes);
@@ -63,7 +62,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
 
     // ---- consumers: codebooks, activations ----
     constexpr int CT = PB_CONSUMERS * 32;
-    const PbQTabs T = pb_fill_qtabs<FMT>(sign16, tab, p.rep, tid, CT);
+    const PbQTabs T = pb_fill_qtabs<FMT>(tab, p.rep, tid, CT, lane);
     const int ng = cols / 32;
     if (p.mode == PB_ACT_PREQ) {
         for (int i = tid; i < NB * xw; i += CT) { const int b = i / xw; xq[i] = b < p.t ? p.xq_in[(size_t)b * xw + (i - b * xw)] : 0u; }
@@ -129,7 +128,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
         while (s + 1 < p.nseg && chunk >= p.seg[s + 1].chunk0) s++;
         const int r0 = (chunk - p.seg[s].chunk0) * p.rows_per_chunk;
         const int nr = min(p.rows_per_chunk, p.seg[s].rows - r0);
-        const uint8_t* base = pb_ring_stage(ring, k);
+        const uint32_t base = pb_smem_u32(pb_ring_stage(ring, k));
         for (int rb = warp * rpw; rb < nr; rb += PB_CONSUMERS * rpw) {
             const int r = rb + sub;
             const bool valid = r < nr;
@@ -137,13 +136,13 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
 #pragma unroll
             for (int b = 0; b < NB; b++) acc[b] = 0.f;
             if (valid) {
-                const uint8_t* rowp = base + (size_t)r * p.row_bytes;
+                const uint32_t rowp = base + (uint32_t)r * (uint32_t)p.row_bytes;
 #pragma unroll
                 for (int ps = 0; ps < PASSES; ps++) {
                     const int qi = ps * 32 + ql;
                     if (qi < nquarters) {
                         PbQuarter wq;
-                        D::quarter(rowp + (qi >> 2) * D::STEP_BYTES, qi & 3, lane, T, wq);
+                        D::quarter(rowp + (qi >> 2) * D::STEP_BYTES, qi & 3, T, wq);
                         if (NB == 1) {
                             acc[0] += pb_quarter_dot<FMT>(wq, xr[ps]);
                         } else {
@@ -186,7 +185,7 @@ static int launch_q(pb_ctx* ctx, const PbGemvQArgs& a, int row_bytes) {
     // replicate the codebook per bank only when the matrix is large enough to amortise the fill
     constexpr int entry = pb_tab_entry_bytes<FMT>();
     p.rep = entry && wbytes >= ((size_t)8 << 20) ? 128 / entry : 1;
-    p.tab_bytes = entry ? 512 * entry * p.rep : 0;
+    p.tab_bytes = pb_tab_bytes<FMT>(p.rep);
     const size_t xbytes = ((size_t)NB * pb_xq_words(a.cols) * 4 + 127) & ~(size_t)127;
     const size_t fixed = 256 + p.tab_bytes + xbytes;
     int align_rows = 1;

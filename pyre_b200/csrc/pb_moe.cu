@@ -159,7 +159,6 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
     PbRing ring;
     ring.full = reinterpret_cast<uint64_t*>(smem);
     ring.empty = ring.full + PB_STAGES;
-    uint8_t* sign16 = smem + 128;
     uint8_t* tab = smem + 256;
     ring.stages = tab + p.tab_bytes;
     ring.stage_bytes = p.stage_bytes;
@@ -201,7 +200,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
     }
 
     constexpr int CT = PB_CONSUMERS * 32;
-    const PbQTabs T = pb_fill_qtabs<FMT>(sign16, tab, p.rep, tid, CT);
+    const PbQTabs T = pb_fill_qtabs<FMT>(tab, p.rep, tid, CT, lane);
     pb_named_barrier(1, CT);
     const int nquarters = 4 * p.bpr;
     const int lpr = nquarters < 32 ? nquarters : 32, rpw = 32 / lpr;
@@ -215,7 +214,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
         int s = 0, r0, e0 = 0, e1;
         if (!shared) { s = chunk / cpe; r0 = (chunk - s * cpe) * p.rows_per_chunk; e0 = p.used_off[s]; e1 = p.used_off[s + 1]; }
         else { r0 = (chunk - n_used * cpe) * p.rows_per_chunk; e1 = p.t; }
-        const uint8_t* base = pb_ring_stage(ring, k);
+        const uint32_t base = pb_smem_u32(pb_ring_stage(ring, k));
         for (int rb = warp * rpw; rb < p.rows_per_chunk; rb += PB_CONSUMERS * rpw) {
             const int r = rb + sub;
             PbQuarter wg[PASSES], wu[PASSES];
@@ -223,8 +222,8 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
             for (int ps = 0; ps < PASSES; ps++) {
                 const int qi = ps * 32 + ql;
                 if (qi < nquarters) {
-                    D::quarter(base + (size_t)r * p.row_bytes + (qi >> 2) * D::STEP_BYTES, qi & 3, lane, T, wg[ps]);
-                    D::quarter(base + half + (size_t)r * p.row_bytes + (qi >> 2) * D::STEP_BYTES, qi & 3, lane, T, wu[ps]);
+                    D::quarter(base + (uint32_t)r * p.row_bytes + (qi >> 2) * D::STEP_BYTES, qi & 3, T, wg[ps]);
+                    D::quarter(base + half + (uint32_t)r * p.row_bytes + (qi >> 2) * D::STEP_BYTES, qi & 3, T, wu[ps]);
                 }
             }
             for (int en = e0; en < e1; en++) {
@@ -261,7 +260,6 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
     PbRing ring;
     ring.full = reinterpret_cast<uint64_t*>(smem);
     ring.empty = ring.full + PB_STAGES;
-    uint8_t* sign16 = smem + 128;
     uint8_t* tab = smem + 256;
     const int cols = p.bpr * 256;   // = expert intermediate size
     const int xw = pb_xq_words(cols);
@@ -300,7 +298,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
     }
 
     constexpr int CT = PB_CONSUMERS * 32;
-    const PbQTabs T = pb_fill_qtabs<FMT>(sign16, tab, p.rep, tid, CT);
+    const PbQTabs T = pb_fill_qtabs<FMT>(tab, p.rep, tid, CT, lane);
     pb_named_barrier(1, CT);
     const int nquarters = 4 * p.bpr;
     const int lpr = nquarters < 32 ? nquarters : 32, rpw = 32 / lpr;
@@ -314,7 +312,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
         int s = 0, r0, e0 = 0, e1;
         if (!shared) { s = chunk / cpe; r0 = (chunk - s * cpe) * p.rows_per_chunk; e0 = p.used_off[s]; e1 = p.used_off[s + 1]; }
         else { r0 = (chunk - n_used * cpe) * p.rows_per_chunk; e1 = p.t; }
-        const uint8_t* base = pb_ring_stage(ring, k);
+        const uint32_t base = pb_smem_u32(pb_ring_stage(ring, k));
         for (int en = e0; en < e1; en++) {
             const int tok = shared ? en : p.ent_tok[en];
             const float* hv = shared ? p.h_sh + (size_t)tok * cols : p.h + (size_t)en * cols;
@@ -333,7 +331,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
                     const int qi = ps * 32 + ql;
                     if (qi < nquarters) {
                         PbQuarter wq; PbXQuarter xv;
-                        D::quarter(base + (size_t)r * p.row_bytes + (qi >> 2) * D::STEP_BYTES, qi & 3, lane, T, wq);
+                        D::quarter(base + (uint32_t)r * p.row_bytes + (qi >> 2) * D::STEP_BYTES, qi & 3, T, wq);
                         pb_load_xquarter(xq, cols, qi, xv);
                         acc += pb_quarter_dot<FMT>(wq, xv);
                     }
@@ -388,9 +386,8 @@ static int launch_expert(pb_ctx* ctx, PbExpertParams p, int cols) {
     int el, bs;
     pb_geom(FMT, &el, &bs);
     p.row_bytes = cols / el * bs; p.bpr = cols / 256;
-    constexpr int entry = pb_tab_entry_bytes<FMT>();
     p.rep = 1;   // a few MB per launch: the plain codebook; see pb_gemvq.cu for the replicated form
-    p.tab_bytes = entry ? 512 * entry * p.rep : 0;
+    p.tab_bytes = pb_tab_bytes<FMT>(p.rep);
     const int lpr = 4 * p.bpr < 32 ? 4 * p.bpr : 32;
     int rpc = PB_CONSUMERS * (32 / lpr);
     while ((rpc * p.row_bytes) % 16) rpc *= 2;

@@ -8,34 +8,43 @@
 // Integer partial sums are exact; each group contributes one f32 FMA per level.  The split
 // keeps the result within f32 rounding noise of an f32-accumulated dot (the parity
 // tolerance is 1e-3), and turns byte->float conversion, sign handling and 8 FMAs per 8
-// weights into two SWAR sign operations and PB_XLEVELS dp4a per 4 weights.
+// weights into SWAR sign operations and PB_XLEVELS dp4a per 4 weights.
+//
+// All block bytes and tables are read from shared memory through 32-bit shared-space
+// addresses (ld.shared), never through generic pointers.
 //
 // Block layouts restate src/model/gguf_q.rs:67-166 of the reference (see pb_formats.cuh).
 #pragma once
 #include "pb_formats.cuh"
 
-// Shared-memory tables used by the decoders.
+__device__ __forceinline__ uint32_t pb_lds8(uint32_t a) { uint32_t v; asm("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint32_t pb_lds16(uint32_t a) { uint32_t v; asm("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint32_t pb_lds32(uint32_t a) { uint32_t v; asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint2 pb_lds64(uint32_t a) { uint2 v; asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v; }
+__device__ __forceinline__ uint4 pb_lds128(uint32_t a) { uint4 v; asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a)); return v; }
+
+// Shared-memory tables used by the decoders (shared-space byte addresses).
 struct PbQTabs {
-    const uint32_t* grid3;   // IQ3_S grid; entry i for lane l at [i * rep + (l & (rep-1))]
-    const uint64_t* grid2;   // IQ2_XS grid, same replication scheme in 8-byte units
-    const uint2* sign16;     // nibble -> (byte mask of negative weights, mask & 0x01010101)
-    int rep3, rep2;          // replication factors (1 = plain table)
+    uint32_t grid;      // codebook, already offset to this lane's copy; entry i at grid + i * stride
+    uint32_t stride;    // bytes between consecutive entries (entry size * replication)
+    uint32_t sign256;   // 256 x 16 B: sign byte -> (mask_lo, mask_lo & 0x01010101, mask_hi, mask_hi & 0x01010101)
 };
+#define PB_SIGN_LUT_BYTES 4096
 
 // load N32 consecutive u32 from a 2-byte-aligned shared-memory address
 template <int N32>
-__device__ __forceinline__ void pb_ld_u32x(const uint8_t* p, uint32_t (&out)[N32]) {
-    const uint32_t sh = ((uint32_t)(uintptr_t)p & 2u) * 8u;          // 0 or 16 bits
-    const uint32_t* a = reinterpret_cast<const uint32_t*>((uintptr_t)p & ~(uintptr_t)3);
+__device__ __forceinline__ void pb_ld_u32x(uint32_t p, uint32_t (&out)[N32]) {
+    const uint32_t sh = (p & 2u) * 8u;          // 0 or 16 bits
+    const uint32_t a = p & ~3u;
     uint32_t w[N32 + 1];
 #pragma unroll
-    for (int i = 0; i <= N32; i++) w[i] = a[i];
+    for (int i = 0; i <= N32; i++) w[i] = pb_lds32(a + 4 * i);
 #pragma unroll
     for (int i = 0; i < N32; i++) out[i] = __funnelshift_r(w[i], w[i + 1], sh);
 }
 
 // (g ^ M) + C : negate the bytes of g selected by the byte mask M (all bytes of g are <= 127)
-__device__ __forceinline__ uint32_t pb_apply_sign(uint32_t g, uint2 mc) { return (g ^ mc.x) + mc.y; }
+__device__ __forceinline__ int pb_apply_sign(uint32_t g, uint32_t m, uint32_t c) { return (int)((g ^ m) + c); }
 
 struct PbQuarter {
     int w[16];      // packed signed int8, weight 4k+j of the quarter in byte j of w[k]
@@ -48,23 +57,27 @@ template <int FMT> struct PbQDec;
 template <> struct PbQDec<PB_T_IQ3_S> {
     static constexpr int STEP_BYTES = 110;
     static constexpr bool HAS_MIN = false, SCALE16 = false;
-    __device__ static __forceinline__ void quarter(const uint8_t* p, int qt, int lane, const PbQTabs& T, PbQuarter& o) {
-        const float d = pb_h2f(*reinterpret_cast<const uint16_t*>(p));
+    // p = shared address of the 110-byte block, qt = quarter 0..3
+    __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs& T, PbQuarter& o) {
+        const float d = pb_h2f((uint16_t)pb_lds16(p));
         uint32_t qs[4], sg[2];
         pb_ld_u32x<4>(p + 2 + 16 * qt, qs);
         pb_ld_u32x<2>(p + 74 + 8 * qt, sg);
-        const uint32_t qh = *reinterpret_cast<const uint16_t*>(p + 66 + 2 * qt);
-        const uint32_t sc = p[106 + qt];
+        const uint32_t qh = pb_lds16(p + 66 + 2 * qt);
+        const uint32_t sc = pb_lds8(p + 106 + qt);
         const float d0 = d * (float)(1 + 2 * (int)(sc & 0xF)), d1 = d * (float)(1 + 2 * (int)(sc >> 4));
         o.sc[0] = o.sc[1] = d0; o.sc[2] = o.sc[3] = d1;
-        const uint32_t* tab = T.grid3 + (lane & (T.rep3 - 1));
 #pragma unroll
-        for (int k = 0; k < 16; k++) {
-            const uint32_t byte = (qs[k >> 2] >> (8 * (k & 3))) & 0xFF;
-            const uint32_t hb = k < 8 ? (qh << (8 - k)) & 0x100 : (qh >> (k - 8)) & 0x100;
-            const uint32_t g = tab[(byte | hb) * T.rep3];
-            const uint32_t nib = (sg[k >> 3] >> (4 * (k & 7))) & 0xF;
-            o.w[k] = (int)pb_apply_sign(g, T.sign16[nib]);
+        for (int u = 0; u < 8; u++) {          // unit u = entries 2u, 2u+1 and one sign byte
+            const uint32_t w = qs[u >> 1] >> (16 * (u & 1));
+            const uint32_t h0 = 2 * u < 8 ? (qh << (8 - 2 * u)) : (qh >> (2 * u - 8));
+            const uint32_t h1 = 2 * u + 1 < 8 ? (qh << (7 - 2 * u)) : (qh >> (2 * u - 7));
+            const uint32_t i0 = (w & 0xFF) | (h0 & 0x100), i1 = ((w >> 8) & 0xFF) | (h1 & 0x100);
+            const uint32_t g0 = pb_lds32(T.grid + i0 * T.stride), g1 = pb_lds32(T.grid + i1 * T.stride);
+            const uint32_t sb = (sg[u >> 2] >> (8 * (u & 3))) & 0xFF;
+            const uint4 m = pb_lds128(T.sign256 + sb * 16);
+            o.w[2 * u] = pb_apply_sign(g0, m.x, m.y);
+            o.w[2 * u + 1] = pb_apply_sign(g1, m.z, m.w);
         }
     }
 };
@@ -72,22 +85,22 @@ template <> struct PbQDec<PB_T_IQ3_S> {
 template <> struct PbQDec<PB_T_IQ2_XS> {
     static constexpr int STEP_BYTES = 74;
     static constexpr bool HAS_MIN = false, SCALE16 = true;
-    __device__ static __forceinline__ void quarter(const uint8_t* p, int qt, int lane, const PbQTabs& T, PbQuarter& o) {
-        const float d = pb_h2f(*reinterpret_cast<const uint16_t*>(p));
+    __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs& T, PbQuarter& o) {
+        const float d = pb_h2f((uint16_t)pb_lds16(p));
         uint32_t qs[4];
         pb_ld_u32x<4>(p + 2 + 16 * qt, qs);
-        const uint32_t sc = *reinterpret_cast<const uint16_t*>(p + 66 + 2 * qt);
+        const uint32_t sc = pb_lds16(p + 66 + 2 * qt);
 #pragma unroll
         for (int h = 0; h < 4; h++) o.sc[h] = d * (0.5f + (float)((sc >> (4 * h)) & 0xF)) * 0.25f;
-        const uint64_t* tab = T.grid2 + (lane & (T.rep2 - 1));
 #pragma unroll
         for (int u = 0; u < 8; u++) {
             const uint32_t q = (qs[u >> 1] >> (16 * (u & 1))) & 0xFFFF;
-            const uint64_t g = tab[(q & 511) * T.rep2];
+            const uint2 g = pb_lds64(T.grid + (q & 511) * T.stride);
             const uint32_t s7 = q >> 9;
             const uint32_t s8 = s7 | ((__popc(s7) & 1) << 7);   // KSIGNS_IQ2XS[i] = i | parity(i) << 7
-            o.w[2 * u] = (int)pb_apply_sign((uint32_t)g, T.sign16[s8 & 0xF]);
-            o.w[2 * u + 1] = (int)pb_apply_sign((uint32_t)(g >> 32), T.sign16[s8 >> 4]);
+            const uint4 m = pb_lds128(T.sign256 + s8 * 16);
+            o.w[2 * u] = pb_apply_sign(g.x, m.x, m.y);
+            o.w[2 * u + 1] = pb_apply_sign(g.y, m.z, m.w);
         }
     }
 };
@@ -95,11 +108,11 @@ template <> struct PbQDec<PB_T_IQ2_XS> {
 template <> struct PbQDec<PB_T_Q8_0> {
     static constexpr int STEP_BYTES = 8 * 34;
     static constexpr bool HAS_MIN = false, SCALE16 = false;
-    __device__ static __forceinline__ void quarter(const uint8_t* p, int qt, int, const PbQTabs&, PbQuarter& o) {
+    __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs&, PbQuarter& o) {
 #pragma unroll
         for (int b = 0; b < 2; b++) {
-            const uint8_t* blk = p + 34 * (2 * qt + b);
-            const float d = pb_h2f(*reinterpret_cast<const uint16_t*>(blk));
+            const uint32_t blk = p + 34 * (2 * qt + b);
+            const float d = pb_h2f((uint16_t)pb_lds16(blk));
             o.sc[2 * b] = o.sc[2 * b + 1] = d;
             uint32_t q[8];
             pb_ld_u32x<8>(blk + 2, q);
@@ -112,15 +125,21 @@ template <> struct PbQDec<PB_T_Q8_0> {
 template <> struct PbQDec<PB_T_Q4_K> {
     static constexpr int STEP_BYTES = 144;
     static constexpr bool HAS_MIN = true, SCALE16 = false;
-    __device__ static __forceinline__ void quarter(const uint8_t* p, int qt, int, const PbQTabs&, PbQuarter& o) {
-        const uint32_t dm = *reinterpret_cast<const uint32_t*>(p);
-        const float d = pb_h2f((uint16_t)(dm & 0xFFFF)), mn = pb_h2f((uint16_t)(dm >> 16));
-        uint32_t s1, m1, s2, m2;
-        PbFmt<PB_T_Q4_K>::scale_min(2 * qt, p + 4, s1, m1);
-        PbFmt<PB_T_Q4_K>::scale_min(2 * qt + 1, p + 4, s2, m2);
-        o.sc[0] = o.sc[1] = d * (float)s1; o.sc[2] = o.sc[3] = d * (float)s2;
-        o.mn[0] = mn * (float)m1; o.mn[1] = mn * (float)m2;
-        const uint4 a = *reinterpret_cast<const uint4*>(p + 16 + 32 * qt), b = *reinterpret_cast<const uint4*>(p + 32 + 32 * qt);
+    __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs&, PbQuarter& o) {
+        const uint4 hdr = pb_lds128(p);            // d, dmin, 12 scale bytes
+        const float d = pb_h2f((uint16_t)(hdr.x & 0xFFFF)), mn = pb_h2f((uint16_t)(hdr.x >> 16));
+        const uint32_t scw[3] = {hdr.y, hdr.z, hdr.w};
+        auto sb = [&](int i) -> uint32_t { return (scw[i >> 2] >> (8 * (i & 3))) & 0xFF; };
+        uint32_t s[2], m[2];
+#pragma unroll
+        for (int e = 0; e < 2; e++) {              // scale_min_k4, gguf_q.rs:62-64
+            const int j = 2 * qt + e;
+            if (j < 4) { s[e] = sb(j) & 63; m[e] = sb(j + 4) & 63; }
+            else { s[e] = (sb(j + 4) & 0xF) | ((sb(j - 4) >> 6) << 4); m[e] = (sb(j + 4) >> 4) | ((sb(j) >> 6) << 4); }
+        }
+        o.sc[0] = o.sc[1] = d * (float)s[0]; o.sc[2] = o.sc[3] = d * (float)s[1];
+        o.mn[0] = mn * (float)m[0]; o.mn[1] = mn * (float)m[1];
+        const uint4 a = pb_lds128(p + 16 + 32 * qt), b = pb_lds128(p + 32 + 32 * qt);
         const uint32_t q[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
         for (int k = 0; k < 8; k++) { o.w[k] = (int)(q[k] & 0x0F0F0F0Fu); o.w[8 + k] = (int)((q[k] >> 4) & 0x0F0F0F0Fu); }

@@ -104,28 +104,37 @@ __device__ __forceinline__ void pb_load_xquarter(const uint32_t* xcol, int cols,
     o.sum[0] = sc[PB_XLEVELS * ng + 2 * qi]; o.sum[1] = sc[PB_XLEVELS * ng + 2 * qi + 1];
 }
 
-// Fill the shared-memory codebooks a format needs.  rep = copies per entry (1, or one per bank).
+// Fill the shared-memory tables a format needs at `tab` (16-byte aligned, pb_tab_bytes<FMT>(rep) long):
+// the sign look-up table first, then the codebook with `rep` copies of every entry (rep = 1, or one
+// copy per bank so that random look-ups of a warp never conflict).  The caller synchronises after.
+template <int FMT> __host__ __device__ constexpr int pb_tab_entry_bytes() { return FMT == PB_T_IQ3_S ? 4 : (FMT == PB_T_IQ2_XS ? 8 : 0); }
+template <int FMT> __host__ __device__ constexpr uint32_t pb_tab_bytes(int rep) { return pb_tab_entry_bytes<FMT>() ? PB_SIGN_LUT_BYTES + 512 * pb_tab_entry_bytes<FMT>() * rep : 0; }
+
 template <int FMT>
-__device__ __forceinline__ PbQTabs pb_fill_qtabs(uint8_t* sign16_mem, uint8_t* tab, int rep, int tid, int nthreads) {
-    uint2* sign16 = reinterpret_cast<uint2*>(sign16_mem);
-    if (tid < 16) {
-        uint32_t m = 0;
-        for (int j = 0; j < 4; j++) if (tid & (1 << j)) m |= 0xFFu << (8 * j);
-        sign16[tid] = make_uint2(m, m & 0x01010101u);
+__device__ __forceinline__ PbQTabs pb_fill_qtabs(uint8_t* tab, int rep, int tid, int nthreads, int lane) {
+    PbQTabs T;
+    T.sign256 = pb_smem_u32(tab);
+    constexpr int entry = pb_tab_entry_bytes<FMT>();
+    T.stride = entry * rep;
+    T.grid = pb_smem_u32(tab + PB_SIGN_LUT_BYTES) + (lane & (rep - 1)) * entry;
+    if (entry) {
+        uint4* sg = reinterpret_cast<uint4*>(tab);
+        for (int i = tid; i < 256; i += nthreads) {
+            uint32_t lo = 0, hi = 0;
+            for (int j = 0; j < 4; j++) { if (i & (1 << j)) lo |= 0xFFu << (8 * j); if (i & (16 << j)) hi |= 0xFFu << (8 * j); }
+            sg[i] = make_uint4(lo, lo & 0x01010101u, hi, hi & 0x01010101u);
+        }
     }
     if (FMT == PB_T_IQ3_S) {
-        uint32_t* g = reinterpret_cast<uint32_t*>(tab);
+        uint32_t* g = reinterpret_cast<uint32_t*>(tab + PB_SIGN_LUT_BYTES);
         for (int i = tid; i < 512 * rep; i += nthreads) g[i] = PB_IQ3S_GRID[i / rep];
     }
     if (FMT == PB_T_IQ2_XS) {
-        uint64_t* g = reinterpret_cast<uint64_t*>(tab);
+        uint64_t* g = reinterpret_cast<uint64_t*>(tab + PB_SIGN_LUT_BYTES);
         for (int i = tid; i < 512 * rep; i += nthreads) g[i] = PB_IQ2XS_GRID[i / rep];
     }
-    PbQTabs T;
-    T.sign16 = sign16; T.grid3 = reinterpret_cast<const uint32_t*>(tab); T.grid2 = reinterpret_cast<const uint64_t*>(tab); T.rep3 = T.rep2 = rep;
     return T;
 }
-template <int FMT> __host__ __device__ constexpr int pb_tab_entry_bytes() { return FMT == PB_T_IQ3_S ? 4 : (FMT == PB_T_IQ2_XS ? 8 : 0); }
 
 // sum over all consumer threads (PB_CONSUMERS warps) of v; red = PB_CONSUMERS floats of shared memory
 __device__ __forceinline__ float pb_consumer_sum(float v, float* red, int warp, int lane) {
