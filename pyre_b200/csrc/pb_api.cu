@@ -3,6 +3,7 @@
 #include "pb_internal.h"
 
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 #include <new>
 
@@ -55,6 +56,7 @@ int pb_ctx_create(int device, pb_ctx** out) {
     cudaMemset(c->dev_status, 0, 256);
     if (cudaMallocHost(&c->host_status, 256) != cudaSuccess) { cudaFree(c->dev_status); cudaStreamDestroy(c->own_stream); delete c; return PB_ERR_OOM; }
     *c->host_status = 0;
+    { const char* e = getenv("PYRE_B200_PDL"); if (e && e[0] == '0') c->use_pdl = false; }   // PYRE_B200_PDL=0: plain stream order inside the token step
     *out = c;
     return PB_OK;
 }

@@ -84,6 +84,8 @@ __global__ void __launch_bounds__(256) pb_kv4_unpack_kernel(const uint32_t* __re
 __global__ void __launch_bounds__(AT_THREADS) pb_kv_append_kernel(const PbAttnParams p) {
     const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hd = p.hd, nkv = p.n_kv, half = p.n_rot / 2;
+    pb_pdl_wait();
+    pb_pdl_trigger();
     const int64_t pos = p.pos[b];
     const float* proj = p.proj + (size_t)b * p.ldp;
     const float* kraw = proj + (size_t)p.n_head * 2 * hd;
@@ -141,6 +143,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
     const int sp = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hd = p.hd, half = p.n_rot / 2;
+    pb_pdl_wait();
+    pb_pdl_trigger();
     const int64_t pos = p.pos[b], n = pos + 1, q4n = p.kv_bits == 4 ? p.q4n[b] : 0;
     const float* proj = p.proj + (size_t)b * p.ldp;
 
@@ -347,6 +351,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
 __global__ void pb_attn_combine_kernel(const PbAttnParams p) {
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     const int G = p.n_head / p.n_kv, kvh = h / G, g = h % G;
+    pb_pdl_wait();
+    pb_pdl_trigger();
     __shared__ float fs[128];     // per-split factor exp(m_s - M)
     __shared__ float ML[2];
     const size_t base = ((size_t)b * p.n_kv + kvh) * p.nsplit;
@@ -376,7 +382,7 @@ __global__ void pb_attn_combine_kernel(const PbAttnParams p) {
 
 int pb_launch_kv_append(pb_ctx* ctx, const PbAttnParams& p) {
     if (p.hd % 32 || p.n_rot > p.hd || p.n_rot % 2 || p.n_kv > 8) PB_FAIL(ctx, PB_UNSUPPORTED, "attention: head dim %d / rotary dim %d not supported", p.hd, p.n_rot);
-    pb_kv_append_kernel<<<p.batch, AT_THREADS, 0, ctx->stream>>>(p);
+    pb_launch_k(ctx, pb_kv_append_kernel, dim3(p.batch), dim3(AT_THREADS), (size_t)(0), p);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;
@@ -393,13 +399,13 @@ int pb_launch_attn(pb_ctx* ctx, const PbAttnParams& p) {
     {                                                                                                                            \
         static bool cfgd = false;                                                                                                \
         if (!cfgd) { PB_CUDA(ctx, cudaFuncSetAttribute(pb_attn_partial_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->max_smem_optin)); cfgd = true; } \
-        pb_attn_partial_kernel<GG><<<grid, AT_THREADS, smem, ctx->stream>>>(p);                                                  \
+        pb_launch_k(ctx, pb_attn_partial_kernel<GG>, dim3(grid), dim3(AT_THREADS), (size_t)(smem), p);                                                  \
     }
     if (G == 8) GO(8) else if (G == 4) GO(4) else if (G == 2) GO(2) else GO(1)
 #undef GO
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
-    pb_attn_combine_kernel<<<dim3(p.n_head, p.batch), p.hd, 0, ctx->stream>>>(p);
+    pb_launch_k(ctx, pb_attn_combine_kernel, dim3(dim3(p.n_head, p.batch)), dim3(p.hd), (size_t)(0), p);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;
@@ -408,14 +414,14 @@ int pb_launch_attn(pb_ctx* ctx, const PbAttnParams& p) {
 int pb_launch_kv4_pack(pb_ctx* ctx, const float* x, int64_t n, uint32_t* w, float* sc) {
     const int64_t nblocks = n / 32;
     if (nblocks <= 0) return PB_OK;
-    pb_kv4_pack_kernel<<<(unsigned)((nblocks + 7) / 8), 256, 0, ctx->stream>>>(x, nblocks, w, sc);
+    pb_launch_k(ctx, pb_kv4_pack_kernel, dim3((unsigned)((nblocks + 7) / 8)), dim3(256), (size_t)(0), x, nblocks, w, sc);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;
 }
 int pb_launch_kv4_unpack(pb_ctx* ctx, const uint32_t* w, const float* sc, int64_t n, float* x) {
     if (n <= 0) return PB_OK;
-    pb_kv4_unpack_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(w, sc, n, x);
+    pb_launch_k(ctx, pb_kv4_unpack_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), (size_t)(0), w, sc, n, x);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;

@@ -63,6 +63,14 @@ __device__ __forceinline__ void pb_bulk_g2s(void* smem_dst, const void* gsrc, ui
                  : "memory");
 }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may
+// start while its predecessor still runs.  pb_pdl_trigger lets the successor be scheduled;
+// pb_pdl_wait blocks until every predecessor grid has completed and its writes are visible.  All
+// reads of data produced by earlier kernels, and all global writes, come after pb_pdl_wait.
+// Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pb_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float pb_h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
 
 __device__ __forceinline__ float pb_warp_sum(float v) {

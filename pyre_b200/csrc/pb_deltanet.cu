@@ -29,6 +29,8 @@ __global__ void __launch_bounds__(DN_THREADS) pb_deltanet_kernel(const PbDeltaPa
     const int b = blockIdx.y;
     const int kh = h % nk;                                  // V head h reads K head h % nk (:1655)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pb_pdl_wait();
+    pb_pdl_trigger();
     const float* proj = p.proj + (size_t)b * p.ldp;        // [qkv (ch) | z | beta | alpha]
     float* ring = p.conv + (size_t)b * K * ch;             // [K slots][ch]
     const int64_t pos = p.pos[b];
@@ -117,9 +119,9 @@ int pb_launch_deltanet(pb_ctx* ctx, const PbDeltaParams& p) {
         PB_FAIL(ctx, PB_UNSUPPORTED, "deltanet: dk=%d dv=%d conv_k=%d not supported", p.dk, p.dv, p.conv_k);
     const dim3 grid(p.nv * (p.dv / DN_COLS), p.batch);
     const size_t smem = (size_t)(2 * p.dk + DN_COLS + 8 * DN_COLS) * 4;
-    if (p.dk == 128) pb_deltanet_kernel<16><<<grid, DN_THREADS, smem, ctx->stream>>>(p);
-    else if (p.dk == 64) pb_deltanet_kernel<8><<<grid, DN_THREADS, smem, ctx->stream>>>(p);
-    else pb_deltanet_kernel<4><<<grid, DN_THREADS, smem, ctx->stream>>>(p);
+    if (p.dk == 128) pb_launch_k(ctx, pb_deltanet_kernel<16>, dim3(grid), dim3(DN_THREADS), (size_t)(smem), p);
+    else if (p.dk == 64) pb_launch_k(ctx, pb_deltanet_kernel<8>, dim3(grid), dim3(DN_THREADS), (size_t)(smem), p);
+    else pb_launch_k(ctx, pb_deltanet_kernel<4>, dim3(grid), dim3(DN_THREADS), (size_t)(smem), p);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;

@@ -395,7 +395,7 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
     q.sel_e = s->sel_e; q.sel_w = s->sel_w; q.n_used = s->n_used; q.used_e = s->used_e; q.used_off = s->used_off;
     q.ent_tok = s->ent_tok; q.ent_slot = s->ent_slot; q.ent_w = s->ent_w;
     PB_TRY(pb_launch_route(ctx, q));
-    if (m->ep_world > 1) PB_CUDA(ctx, cudaMemsetAsync(s->part, 0, (size_t)t * c.top_k * c.d * 4, ctx->stream));
+    if (m->ep_world > 1) { PB_CUDA(ctx, cudaMemsetAsync(s->part, 0, (size_t)t * c.top_k * c.d * 4, ctx->stream)); ctx->pdl_chain = false; }
     PbExpertParams e; memset(&e, 0, sizeof e);
     e.n_used = s->n_used; e.used_e = s->used_e; e.used_off = s->used_off; e.ent_tok = s->ent_tok; e.ent_slot = s->ent_slot; e.ent_w = s->ent_w;
     e.xq = s->xq; e.h = s->h; e.h_sh = s->h_sh; e.part = s->part; e.part_sh = s->part_sh;
@@ -412,7 +412,7 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
     PB_TRY(pb_launch_expert_down(ctx, e, dn->type, c.ff_exp));
     // expert parallelism: every (token, slot) row was produced on exactly one rank and is zero elsewhere,
     // so the sum is an exact gather and the combine below sees the same bits for every GPU count
-    if (m->ep_world > 1) PB_TRY(pb_ep_allreduce(ctx, s->part, (size_t)t * c.top_k * c.d));
+    if (m->ep_world > 1) { PB_TRY(pb_ep_allreduce(ctx, s->part, (size_t)t * c.top_k * c.d)); ctx->pdl_chain = false; }
     PbCombineParams k; memset(&k, 0, sizeof k);
     k.part = s->part; k.part_sh = s->part_sh; k.logits = s->rlogits; k.t = t; k.d = c.d; k.top_k = c.top_k; k.n_exp = c.n_exp;
     k.y = y; k.ldy = ldy; k.accumulate = accumulate;
@@ -422,6 +422,7 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
 // one decode step for every sequence of the batch, ids already in s->ids
 static int run_step(pb_state* s) {
     pb_model* m = s->m; pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg; const int B = s->batch;
+    struct Scope { pb_ctx* c; Scope(pb_ctx* x) : c(x) { c->pdl_scope++; c->pdl_chain = false; } ~Scope() { c->pdl_scope--; c->pdl_chain = false; } } scope(ctx);
     pb_qmat* embd = M(m, -1, PB_R_TOKEN_EMBD);
     PB_TRY(pb_launch_embed(ctx, embd->type, embd->data, embd->rows, c.d, s->ids, B, s->x, c.d));
     for (int il = 0; il < c.n_layers; il++) {

@@ -36,6 +36,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
     ring.stage_bytes = p.stage_bytes;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pb_pdl_trigger();   // the next kernel may start its own set-up and weight stream
     pb_ring_init(ring, tid);
     __syncthreads();
 
@@ -63,6 +64,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
     // ---- consumers: codebooks, activations ----
     constexpr int CT = PB_CONSUMERS * 32;
     const PbQTabs T = pb_fill_qtabs<FMT>(tab, p.rep, tid, CT, lane);
+    pb_pdl_wait();      // activations (and the residual this kernel may add to) come from earlier kernels
     const int ng = cols / 32;
     if (p.mode == PB_ACT_PREQ) {
         for (int i = tid; i < NB * xw; i += CT) { const int b = i / xw; xq[i] = b < p.t ? p.xq_in[(size_t)b * xw + (i - b * xw)] : 0u; }
@@ -215,7 +217,7 @@ static int launch_q(pb_ctx* ctx, const PbGemvQArgs& a, int row_bytes) {
     static size_t configured = 0;   // per template instance
     if (smem > configured) { PB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = smem; }
     const int grid = nchunks < grid_max ? nchunks : grid_max;
-    kern<<<grid, PB_KTHREADS, smem, ctx->stream>>>(p);
+    pb_launch_k(ctx, kern, dim3(grid), dim3(PB_KTHREADS), (size_t)(smem), p);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;

@@ -22,6 +22,10 @@ struct pb_ctx {
     size_t scratch_bytes = 0;
     uint64_t kernels_launched = 0;
     // expert-parallel group (pb_ep.cu); ep_comm is an ncclComm_t
+    // programmatic dependent launch is used only inside the token step, where every stream op is ours
+    bool use_pdl = true;
+    int pdl_scope = 0;       // > 0 while run_step is issuing launches
+    bool pdl_chain = false;  // the previous op on the stream was one of our kernels
     void* ep_comm = nullptr;
     int ep_rank = 0, ep_world = 1;
 };
@@ -56,6 +60,22 @@ struct pb_qmat {
         int _s = (call);             \
         if (_s != PB_OK) return _s;  \
     } while (0)
+
+// Kernel launch on the context's stream; inside the token step consecutive kernels are chained with
+// programmatic stream serialization (every such kernel calls pb_pdl_wait before touching dependent data).
+template <typename K, typename... A>
+static inline void pb_launch_k(pb_ctx* ctx, K kern, dim3 grid, dim3 block, size_t smem, A... args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = ctx->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = (ctx->use_pdl && ctx->pdl_scope > 0 && ctx->pdl_chain) ? 1 : 0;
+    ctx->pdl_chain = ctx->pdl_scope > 0;
+    cudaLaunchKernelEx(&cfg, kern, args...);   // errors are picked up by cudaGetLastError at the call site
+}
 
 int pb_scratch(pb_ctx* ctx, size_t bytes, void** out);
 int pb_sync_check(pb_ctx* ctx, const char* who);

@@ -9,6 +9,8 @@ template <int FMT>
 __global__ void __launch_bounds__(32) pb_embed_kernel(const uint8_t* __restrict__ w, int64_t rows, int row_bytes, const uint32_t* __restrict__ ids, float* __restrict__ out, int64_t ldo) {
     using F = PbFmt<FMT>;
     const int lane = threadIdx.x, step = blockIdx.x, b = blockIdx.y;
+    pb_pdl_wait();
+    pb_pdl_trigger();
     uint32_t id = ids[b];
     if (id >= rows) id = 0;   // out-of-range token ids read row 0 instead of faulting
     PbTables T;
@@ -29,7 +31,7 @@ int pb_launch_embed(pb_ctx* ctx, int type, const uint8_t* w, int64_t rows, int c
     if (pb_geom(type, &el, &bs) || cols % 256) PB_FAIL(ctx, PB_UNSUPPORTED, "embed: type %d cols %d", type, cols);
     const int row_bytes = cols / el * bs;
     const dim3 grid(cols / 256, t);
-#define LAUNCH() pb_embed_kernel<FMT><<<grid, 32, 0, ctx->stream>>>(w, rows, row_bytes, ids, out, ldo)
+#define LAUNCH() pb_launch_k(ctx, pb_embed_kernel<FMT>, grid, dim3(32), (size_t)0, w, rows, row_bytes, ids, out, ldo)
     PB_DISPATCH_FMT(type, LAUNCH);
 #undef LAUNCH
     ctx->kernels_launched++;
@@ -46,6 +48,8 @@ __device__ __forceinline__ unsigned long long pb_argmax_key(float v, int i) {
     return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)i);
 }
 __global__ void __launch_bounds__(256) pb_argmax_kernel(const float* __restrict__ logits, int64_t ld, int n, unsigned long long* __restrict__ keys) {
+    pb_pdl_wait();
+    pb_pdl_trigger();
     const float* v = logits + (size_t)blockIdx.y * ld;
     unsigned long long best = 0;
     for (int i = blockIdx.x * 256 + threadIdx.x; i < n; i += gridDim.x * 256) { const unsigned long long k = pb_argmax_key(v[i], i); best = k > best ? k : best; }
@@ -63,7 +67,7 @@ __global__ void __launch_bounds__(256) pb_argmax_kernel(const float* __restrict_
 int pb_launch_argmax(pb_ctx* ctx, const float* logits, int64_t ld, int n, int t, unsigned long long* keys) {
     int blocks = (n + 2047) / 2048;
     if (blocks > 148) blocks = 148;
-    pb_argmax_kernel<<<dim3(blocks, t), 256, 0, ctx->stream>>>(logits, ld, n, keys);
+    pb_launch_k(ctx, pb_argmax_kernel, dim3(dim3(blocks, t)), dim3(256), (size_t)(0), logits, ld, n, keys);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;
@@ -73,6 +77,8 @@ int pb_launch_argmax(pb_ctx* ctx, const float* logits, int64_t ld, int n, int t,
 // pos += 1, feed the chosen tokens back as the next inputs and log them
 __global__ void pb_advance_kernel(int64_t* pos, int t, unsigned long long* keys, uint32_t* next, uint32_t* ids, uint32_t* trace, int64_t* trace_len, int64_t trace_cap) {
     const int b = threadIdx.x;
+    pb_pdl_wait();
+    pb_pdl_trigger();
     if (b < t) {
         const unsigned long long k = keys[b];
         const uint32_t tok = k ? 0xFFFFFFFFu - (uint32_t)(k & 0xFFFFFFFFull) : 0u;
@@ -88,7 +94,7 @@ __global__ void pb_advance_kernel(int64_t* pos, int t, unsigned long long* keys,
 }
 
 int pb_launch_advance(pb_ctx* ctx, int64_t* pos, int t, unsigned long long* keys, uint32_t* next, uint32_t* ids, uint32_t* trace, int64_t* trace_len, int64_t trace_cap) {
-    pb_advance_kernel<<<1, (t + 31) & ~31, 0, ctx->stream>>>(pos, t, keys, next, ids, trace, trace_len, trace_cap);
+    pb_launch_k(ctx, pb_advance_kernel, dim3(1), dim3((t + 31) & ~31), (size_t)(0), pos, t, keys, next, ids, trace, trace_len, trace_cap);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;

@@ -29,6 +29,8 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p) 
     float* scale = rs;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     __shared__ float red[8];
+    pb_pdl_wait();
+    pb_pdl_trigger();
     // per-token RMS scale (rms(): 1 / sqrt(mean(x^2) + eps), qwen4exp_gguf.rs:209)
     for (int b = 0; b < p.t; b++) {
         float s = 1.0f;
@@ -90,6 +92,8 @@ __global__ void __launch_bounds__(512) pb_route_kernel(const PbRouteParams p) {
     int* cursor = rsm + 1024;       // [1024] start offset of the expert's entries, then a fill cursor
     __shared__ int wsum[2][16];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pb_pdl_wait();
+    pb_pdl_trigger();
     for (int e = tid; e < 1024; e += 512) { cnt[e] = 0; cursor[e] = 0; }
     __syncthreads();
     for (int b = warp; b < p.t; b += 16) {
@@ -163,8 +167,10 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
     ring.stages = tab + p.tab_bytes;
     ring.stage_bytes = p.stage_bytes;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pb_pdl_trigger();
     pb_ring_init(ring, tid);
     __syncthreads();
+    pb_pdl_wait();   // the expert lists come from the routing kernel
 
     const int cols = p.bpr * 256;
     const int n_used = *p.n_used;
@@ -267,8 +273,10 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
     ring.stages = reinterpret_cast<uint8_t*>(xq) + (((size_t)xw * 4 + 127) & ~(size_t)127);
     ring.stage_bytes = p.stage_bytes;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pb_pdl_trigger();
     pb_ring_init(ring, tid);
     __syncthreads();
+    pb_pdl_wait();   // the expert lists and hidden vectors come from earlier kernels
 
     const int n_used = *p.n_used;
     const int cpe = p.rows_e / p.rows_per_chunk;   // output rows (= model width) per expert / rows per chunk
@@ -349,6 +357,8 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
 // y[tok][r] = sigmoid(shared-gate logit) * shared[tok][r] + sum_j part[tok][j][r]  (ascending expert id),
 // then either stored (layer-level call) or added to the residual stream.
 __global__ void __launch_bounds__(256) pb_moe_combine_kernel(const PbCombineParams p) {
+    pb_pdl_wait();
+    pb_pdl_trigger();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (int64_t)p.t * p.d) return;
     const int tok = (int)(i / p.d), r = (int)(i - (int64_t)tok * p.d);
@@ -367,7 +377,7 @@ int pb_launch_router(pb_ctx* ctx, const PbRouterParams& p) {
     if (p.cols % 128) PB_FAIL(ctx, PB_UNSUPPORTED, "router: width %d is not a multiple of 128", p.cols);
     const int grid = (p.n_exp + 1 + 7) / 8;
     const size_t smem = (size_t)((p.t + 31) & ~31) * 4;
-    pb_router_kernel<<<grid, 256, smem, ctx->stream>>>(p);
+    pb_launch_k(ctx, pb_router_kernel, dim3(grid), dim3(256), (size_t)(smem), p);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;
@@ -375,7 +385,7 @@ int pb_launch_router(pb_ctx* ctx, const PbRouterParams& p) {
 
 int pb_launch_route(pb_ctx* ctx, const PbRouteParams& p) {
     if (p.top_k > PB_MAX_TOPK || p.n_exp > 1024) PB_FAIL(ctx, PB_UNSUPPORTED, "route: top_k %d / n_exp %d beyond %d / 1024", p.top_k, p.n_exp, PB_MAX_TOPK);
-    pb_route_kernel<<<1, 512, 2048 * sizeof(int), ctx->stream>>>(p);
+    pb_launch_k(ctx, pb_route_kernel, dim3(1), dim3(512), (size_t)(2048 * sizeof(int)), p);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;
@@ -402,12 +412,12 @@ static int launch_expert(pb_ctx* ctx, PbExpertParams p, int cols) {
         auto kern = pb_expert_down_kernel<FMT, PASSES>;
         static size_t configured = 0;
         if (smem > configured) { PB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = smem; }
-        kern<<<ctx->sm_count, PB_KTHREADS, smem, ctx->stream>>>(p);
+        pb_launch_k(ctx, kern, dim3(ctx->sm_count), dim3(PB_KTHREADS), (size_t)(smem), p);
     } else {
         auto kern = pb_expert_gu_kernel<FMT, PASSES>;
         static size_t configured = 0;
         if (smem > configured) { PB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = smem; }
-        kern<<<ctx->sm_count, PB_KTHREADS, smem, ctx->stream>>>(p);
+        pb_launch_k(ctx, kern, dim3(ctx->sm_count), dim3(PB_KTHREADS), (size_t)(smem), p);
     }
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
@@ -432,7 +442,7 @@ int pb_launch_expert_down(pb_ctx* ctx, const PbExpertParams& p, int type, int co
 
 int pb_launch_moe_combine(pb_ctx* ctx, const PbCombineParams& p) {
     const int64_t n = (int64_t)p.t * p.d;
-    pb_moe_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(p);
+    pb_launch_k(ctx, pb_moe_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), (size_t)(0), p);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;
