@@ -191,8 +191,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
         for (int j = 0; j < 8; j++) acc[g][j] = 0.f; }
 
     const int64_t ntiles = (n + AT_TILE - 1) / AT_TILE;
-    const int64_t tps = (ntiles + gridDim.x - 1) / gridDim.x;
-    const int64_t t0 = sp * tps, t1 = min(ntiles, t0 + tps);
+    // tiles are dealt round-robin to (split, warp) so that the slower f32 tiles of the recent window
+    // are spread over all CTAs instead of landing on the last splits
     const size_t hrow = (size_t)b * p.n_kv + kvh;
     const uint32_t* kw = p.kw + hrow * p.max_ctx * (hd / 8);
     const uint32_t* vw = p.vw + hrow * p.max_ctx * (hd / 8);
@@ -207,7 +207,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
     uint32_t* tvw = reinterpret_cast<uint32_t*>(tks + AT_TILE * (hd / 32));
     float* tvs = reinterpret_cast<float*>(tvw + AT_TILE * (hd / 8));
 
-    for (int64_t t = t0 + warp; t < t1; t += AT_WARPS) {
+    for (int64_t t = (int64_t)warp * gridDim.x + sp; t < ntiles; t += (int64_t)AT_WARPS * gridDim.x) {
         const int64_t pbase = t * AT_TILE;
         // q4n is a multiple of 64 and tiles start at multiples of 32: a tile is entirely packed or entirely f32
         const bool packed = pbase < q4n;
@@ -347,35 +347,43 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
 
 // ------------------------------------------------------------------------------------ combine
 
-// grid (n_head, batch), hd threads: merge splits, normalize, gate with sigmoid(gate)  (:1607-1610)
-__global__ void pb_attn_combine_kernel(const PbAttnParams p) {
-    const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+// grid (n_head, batch), 4 * hd threads: merge splits, normalize, gate with sigmoid(gate)  (:1607-1610).
+// Thread (q, d) sums the splits s = q, q+4, ... of dimension d; the four partial sums meet in shared memory.
+__global__ void __launch_bounds__(1024) pb_attn_combine_kernel(const PbAttnParams p) {
+    const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x % p.hd, q = threadIdx.x / p.hd;
     const int G = p.n_head / p.n_kv, kvh = h / G, g = h % G;
     pb_pdl_wait();
     pb_pdl_trigger();
     __shared__ float fs[128];     // per-split factor exp(m_s - M)
     __shared__ float ML[2];
+    __shared__ float part[3][256];
     const size_t base = ((size_t)b * p.n_kv + kvh) * p.nsplit;
-    if (d < 32) {
+    if (threadIdx.x < 32) {
+        const int l = threadIdx.x;
         float M = -INFINITY;
-        for (int s = d; s < p.nsplit; s += 32) M = fmaxf(M, p.part_ml[((base + s) * G + g) * 2]);
+        for (int s = l; s < p.nsplit; s += 32) M = fmaxf(M, p.part_ml[((base + s) * G + g) * 2]);
         M = pb_warp_max(M);
         float L = 0.f;
-        for (int s = d; s < p.nsplit; s += 32) {
+        for (int s = l; s < p.nsplit; s += 32) {
             const float m = p.part_ml[((base + s) * G + g) * 2];
             const float f = m == -INFINITY ? 0.f : expf(m - M);
             fs[s] = f;
             L += p.part_ml[((base + s) * G + g) * 2 + 1] * f;
         }
         L = pb_warp_sum(L);
-        if (d == 0) { ML[0] = M; ML[1] = L; }
+        if (l == 0) { ML[0] = M; ML[1] = L; }
     }
     __syncthreads();
     float o = 0.f;
-#pragma unroll 8
-    for (int s = 0; s < p.nsplit; s++) o = fmaf(p.part_acc[((base + s) * G + g) * p.hd + d], fs[s], o);
-    const float gate = p.proj[(size_t)b * p.ldp + (size_t)h * 2 * p.hd + p.hd + d];
-    p.att[(size_t)b * p.lda + (size_t)h * p.hd + d] = (o * (1.0f / ML[1])) * pb_sigm(gate);
+#pragma unroll 4
+    for (int s = q; s < p.nsplit; s += 4) o = fmaf(p.part_acc[((base + s) * G + g) * p.hd + d], fs[s], o);
+    if (q > 0) part[q - 1][d] = o;
+    __syncthreads();
+    if (q == 0) {
+        o = ((o + part[0][d]) + part[1][d]) + part[2][d];
+        const float gate = p.proj[(size_t)b * p.ldp + (size_t)h * 2 * p.hd + p.hd + d];
+        p.att[(size_t)b * p.lda + (size_t)h * p.hd + d] = (o * (1.0f / ML[1])) * pb_sigm(gate);
+    }
 }
 
 // ------------------------------------------------------------------------------------ launchers
@@ -405,7 +413,7 @@ int pb_launch_attn(pb_ctx* ctx, const PbAttnParams& p) {
 #undef GO
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
-    pb_launch_k(ctx, pb_attn_combine_kernel, dim3(dim3(p.n_head, p.batch)), dim3(p.hd), (size_t)(0), p);
+    pb_launch_k(ctx, pb_attn_combine_kernel, dim3(p.n_head, p.batch), dim3(4 * p.hd), (size_t)(0), p);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;

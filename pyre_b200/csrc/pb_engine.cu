@@ -34,7 +34,7 @@ struct pb_state {
     int batch = 0;
     int64_t pos_host = 0;
     std::vector<void*> allocs;
-    int64_t* pos = nullptr; uint32_t* ids = nullptr; uint32_t* next = nullptr; unsigned long long* amax = nullptr;
+    int64_t* pos = nullptr; uint32_t* ids = nullptr; uint32_t* next = nullptr; unsigned long long* amax = nullptr; unsigned int* ticket = nullptr;
     float *x = nullptr, *xin = nullptr, *proj = nullptr, *olin = nullptr, *att = nullptr, *rlogits = nullptr, *yout = nullptr;
     uint32_t* xq = nullptr;
     int *sel_e = nullptr, *n_used = nullptr, *used_e = nullptr, *used_off = nullptr, *ent_tok = nullptr, *ent_slot = nullptr;
@@ -249,7 +249,7 @@ int pb_state_create(pb_model* m, int batch, pb_state** out) {
     const int64_t wide = (int64_t)c.lin_nv * c.lin_dv > (int64_t)c.n_head * c.hd ? (int64_t)c.lin_nv * c.lin_dv : (int64_t)c.n_head * c.hd;
     int rc = PB_OK;
 #define A(p, n) if (rc == PB_OK) rc = dalloc(s, &s->p, (size_t)(n))
-    A(pos, B); A(ids, B); A(next, B); A(amax, B);
+    A(pos, B); A(ids, B); A(next, B); A(amax, B); A(ticket, 4);
     A(x, (size_t)B * c.d); A(xin, (size_t)B * (wide > c.d ? wide : c.d)); A(yout, (size_t)B * c.d);
     A(proj, (size_t)B * s->ldproj); A(olin, (size_t)B * wide); A(att, (size_t)B * wide);
     A(rlogits, (size_t)B * (c.n_exp + 1));
@@ -389,12 +389,11 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
     r.x = x_in; r.ldx = c.d; r.t = t; r.cols = c.d; r.norm_w = norm_w; r.eps = c.eps;
     r.router = reinterpret_cast<const float*>(M(m, il, PB_R_ROUTER)->data); r.sh_gate_inp = V(m, il, PB_R_SH_GATE_INP); r.n_exp = c.n_exp;
     r.logits = s->rlogits; r.xq_out = s->xq;
-    PB_TRY(pb_launch_router(ctx, r));
     PbRouteParams q; memset(&q, 0, sizeof q);
     q.logits = s->rlogits; q.t = t; q.n_exp = c.n_exp; q.top_k = c.top_k; q.e_lo = m->e_lo; q.e_hi = m->e_hi;
     q.sel_e = s->sel_e; q.sel_w = s->sel_w; q.n_used = s->n_used; q.used_e = s->used_e; q.used_off = s->used_off;
     q.ent_tok = s->ent_tok; q.ent_slot = s->ent_slot; q.ent_w = s->ent_w;
-    PB_TRY(pb_launch_route(ctx, q));
+    PB_TRY(pb_launch_router(ctx, r, q, s->ticket));
     if (m->ep_world > 1) { PB_CUDA(ctx, cudaMemsetAsync(s->part, 0, (size_t)t * c.top_k * c.d * 4, ctx->stream)); ctx->pdl_chain = false; }
     PbExpertParams e; memset(&e, 0, sizeof e);
     e.n_used = s->n_used; e.used_e = s->used_e; e.used_off = s->used_off; e.ent_tok = s->ent_tok; e.ent_slot = s->ent_slot; e.ent_w = s->ent_w;
@@ -409,13 +408,15 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
     e.e_base = dn->rows == (int64_t)c.d * c.n_exp ? 0 : m->e_lo;
     e.w_a = dn->data; e.w_b = nullptr; e.sh_a = M(m, il, PB_R_SH_DOWN)->data; e.sh_b = nullptr;
     e.rows_e = c.d; e.rows_sh = c.d;
+    PbCombineParams k; memset(&k, 0, sizeof k);
+    k.part = s->part; k.part_sh = s->part_sh; k.logits = s->rlogits; k.t = t; k.d = c.d; k.top_k = c.top_k; k.n_exp = c.n_exp;
+    k.y = y; k.ldy = ldy; k.accumulate = accumulate;
+    // few tokens on one GPU: the down kernel's last CTA also combines (one launch less per layer)
+    if (m->ep_world == 1 && (int64_t)t * c.d <= 8192) return pb_launch_expert_down(ctx, e, dn->type, c.ff_exp, &k, s->ticket + 1);
     PB_TRY(pb_launch_expert_down(ctx, e, dn->type, c.ff_exp));
     // expert parallelism: every (token, slot) row was produced on exactly one rank and is zero elsewhere,
     // so the sum is an exact gather and the combine below sees the same bits for every GPU count
     if (m->ep_world > 1) { PB_TRY(pb_ep_allreduce(ctx, s->part, (size_t)t * c.top_k * c.d)); ctx->pdl_chain = false; }
-    PbCombineParams k; memset(&k, 0, sizeof k);
-    k.part = s->part; k.part_sh = s->part_sh; k.logits = s->rlogits; k.t = t; k.d = c.d; k.top_k = c.top_k; k.n_exp = c.n_exp;
-    k.y = y; k.ldy = ldy; k.accumulate = accumulate;
     return pb_launch_moe_combine(ctx, k);
 }
 

@@ -168,10 +168,9 @@ struct PbCombineParams {
     int t, d, top_k, n_exp;
     float* y; int64_t ldy; int accumulate;
 };
-int pb_launch_router(pb_ctx* ctx, const PbRouterParams& p);
-int pb_launch_route(pb_ctx* ctx, const PbRouteParams& p);
+int pb_launch_router(pb_ctx* ctx, const PbRouterParams& p, const PbRouteParams& rp, unsigned int* ticket);
 int pb_launch_expert_gu(pb_ctx* ctx, const PbExpertParams& p, int type, int cols);
-int pb_launch_expert_down(pb_ctx* ctx, const PbExpertParams& p, int type, int cols);
+int pb_launch_expert_down(pb_ctx* ctx, const PbExpertParams& p, int type, int cols, const PbCombineParams* cp = nullptr, unsigned int* ticket = nullptr);
 int pb_launch_moe_combine(pb_ctx* ctx, const PbCombineParams& p);
 
 // ---------------------------------------------------------------- pb_deltanet.cu

@@ -6,7 +6,7 @@
 // (src/model/qn_cube.rs:3482-5419, 5210-5256).  Nothing leaves the device:
 //   1. pb_router_kernel   RMSNorm (optional) + f32 router GEMV + shared-gate logit; also emits
 //                         the normalized activations split into int8 levels for the experts
-//   2. pb_route_kernel    per token top-k (descending logit, ties to the lower id, NaN -> -inf),
+//   2. pb_route_body      (last router CTA) per token top-k (descending logit, ties to the lower id, NaN -> -inf),
 //                         softmax over the selection, selection sorted by expert id; builds the
 //                         list of distinct local experts with their (token, slot) entries
 //   3. pb_expert_gu_kernel   h = silu(gate_e x) * (up_e x) for every (expert, token) entry and the
@@ -19,14 +19,83 @@
 
 #include <stdio.h>
 
+// ------------------------------------------------------------------------------------ routing
+
+// Runs in ONE CTA of 256 threads (the last router CTA to finish); warp per token.  Everything stays in
+// registers: lane l holds experts l, l+32, ... of the token.  rsm = 2048 ints of shared memory.
+__device__ __forceinline__ void pb_route_body(const PbRouteParams& p, int* rsm) {
+    int* cnt = rsm;                 // [1024] entries per expert (local experts only)
+    int* cursor = rsm + 1024;       // [1024] start offset of the expert's entries, then a fill cursor
+    __shared__ int wsum[2][8];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int e = tid; e < 1024; e += 256) { cnt[e] = 0; cursor[e] = 0; }
+    __syncthreads();
+    for (int b = warp; b < p.t; b += 8) {
+        const float* lg = p.logits + (size_t)b * (p.n_exp + 1);
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; i++) { const int e = i * 32 + lane; const float x = e < p.n_exp ? __ldcg(lg + e) : -INFINITY; v[i] = isnan(x) ? -INFINITY : x; }   // nan_clean :3121-3125
+        int my_e = 0; float my_v = -INFINITY;     // lane j keeps the j-th pick (descending logit, ties to the lower id)
+        for (int j = 0; j < p.top_k; j++) {
+            float bv = -INFINITY; int be = 0x7fffffff;
+#pragma unroll
+            for (int i = 0; i < 32; i++) { const int e = i * 32 + lane; if (e < p.n_exp && (v[i] > bv || (v[i] == bv && e < be))) { bv = v[i]; be = e; } }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+                if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+            }
+            if (lane == j) { my_e = be; my_v = bv; }
+#pragma unroll
+            for (int i = 0; i < 32; i++) if (i * 32 + lane == be) v[i] = __int_as_float(0x7fc00000);   // taken: NaN never compares greater or equal
+        }
+        // softmax over the selection, summed in descending-logit order (top_k :3136-3138, soft_top :3126-3131)
+        float mx = lane < p.top_k ? my_v : -INFINITY;
+        mx = pb_warp_max(mx);
+        float w = lane < p.top_k ? expf(my_v - mx) : 0.f;
+        float sum = 0.f;
+        for (int j = 0; j < p.top_k; j++) sum += __shfl_sync(0xffffffffu, w, j);
+        w = isfinite(mx) ? w / sum : 1.0f / (float)(p.top_k > 0 ? p.top_k : 1);
+        // accumulation order = ascending expert id (routed f32 branch :1786): rank of this lane's expert
+        int rank = 0;
+        for (int j = 0; j < p.top_k; j++) { const int oe = __shfl_sync(0xffffffffu, my_e, j); if (oe < my_e) rank++; }
+        if (lane < p.top_k) {
+            p.sel_e[b * p.top_k + rank] = my_e; p.sel_w[b * p.top_k + rank] = w;
+            if (my_e >= p.e_lo && my_e < p.e_hi) atomicAdd(&cnt[my_e], 1);
+        }
+    }
+    __syncthreads();
+    // distinct local experts in ascending id with entry offsets: block-wide exclusive scans of
+    // (used flag, entry count) over expert ids; thread t owns experts 4t .. 4t+3
+    int c4[4], f = 0, c = 0;
+#pragma unroll
+    for (int q = 0; q < 4; q++) { const int e = 4 * tid + q; c4[q] = e < p.n_exp ? cnt[e] : 0; f += c4[q] > 0; c += c4[q]; }
+    int fi = f, ci = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const int a = __shfl_up_sync(0xffffffffu, fi, o), d = __shfl_up_sync(0xffffffffu, ci, o); if (lane >= o) { fi += a; ci += d; } }
+    if (lane == 31) { wsum[0][warp] = fi; wsum[1][warp] = ci; }
+    __syncthreads();
+    int fb = 0, cb = 0;
+    for (int w2 = 0; w2 < warp; w2++) { fb += wsum[0][w2]; cb += wsum[1][w2]; }
+    int n = fb + fi - f, off = cb + ci - c;   // exclusive prefixes for expert 4 * tid
+#pragma unroll
+    for (int q = 0; q < 4; q++) if (c4[q] > 0) { const int e = 4 * tid + q; p.used_e[n] = e; p.used_off[n] = off; cursor[e] = off; n++; off += c4[q]; }
+    if (tid == 255) { p.used_off[n] = off; *p.n_used = n; }
+    __syncthreads();
+    for (int i = tid; i < p.t * p.top_k; i += 256) {
+        const int e = p.sel_e[i];
+        if (e >= p.e_lo && e < p.e_hi) { const int pos = atomicAdd(&cursor[e], 1); p.ent_tok[pos] = i / p.top_k; p.ent_slot[pos] = i % p.top_k; p.ent_w[pos] = p.sel_w[i]; }
+    }
+}
+
 // ------------------------------------------------------------------------------------ router
 
 // grid: ceil((n_exp + 1) / 8) CTAs of 256 threads; warp per router row (row n_exp = shared-gate vector).
 // CTA j additionally splits groups 4j..4j+3 of every token's normalized activations into int8
 // levels for the expert kernels, so that work is spread over the grid.
-__global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p) {
-    extern __shared__ float rs[];   // scale[t]
-    float* scale = rs;
+__global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, const PbRouteParams rp, unsigned int* ticket) {
+    extern __shared__ float rs[];   // 2048 ints for the routing pass, then scale[t]
+    float* scale = rs + 2048;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     __shared__ float red[8];
     pb_pdl_wait();
@@ -61,97 +130,38 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p) 
         }
     }
     const int row = blockIdx.x * 8 + warp;
-    if (row > p.n_exp) return;
-    const float* wrow = row < p.n_exp ? p.router + (size_t)row * p.cols : p.sh_gate_inp;
-    if (!wrow) { if (lane == 0) for (int b = 0; b < p.t; b++) p.logits[b * (p.n_exp + 1) + row] = 0.f; return; }
-    for (int b = 0; b < p.t; b++) {
-        float acc = 0.f;
-        const float s = scale[b];
+    if (row <= p.n_exp) {
+        const float* wrow = row < p.n_exp ? p.router + (size_t)row * p.cols : p.sh_gate_inp;
+        for (int b = 0; b < p.t; b++) {
+            float acc = 0.f;
+            const float s = scale[b];
+            if (wrow) {
 #pragma unroll 4
-        for (int c = lane * 4; c < p.cols; c += 128) {
-            const float4 w = *reinterpret_cast<const float4*>(wrow + c);
-            float4 v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + c);
-            if (p.norm_w) {
-                const float4 n = *reinterpret_cast<const float4*>(p.norm_w + c);
-                v.x = v.x * s * n.x; v.y = v.y * s * n.y; v.z = v.z * s * n.z; v.w = v.w * s * n.w;
+                for (int c = lane * 4; c < p.cols; c += 128) {
+                    const float4 w = *reinterpret_cast<const float4*>(wrow + c);
+                    float4 v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + c);
+                    if (p.norm_w) {
+                        const float4 n = *reinterpret_cast<const float4*>(p.norm_w + c);
+                        v.x = v.x * s * n.x; v.y = v.y * s * n.y; v.z = v.z * s * n.z; v.w = v.w * s * n.w;
+                    }
+                    acc = fmaf(w.x, v.x, acc); acc = fmaf(w.y, v.y, acc); acc = fmaf(w.z, v.z, acc); acc = fmaf(w.w, v.w, acc);
+                }
+                acc = pb_warp_sum(acc);
             }
-            acc = fmaf(w.x, v.x, acc); acc = fmaf(w.y, v.y, acc); acc = fmaf(w.z, v.z, acc); acc = fmaf(w.w, v.w, acc);
-        }
-        acc = pb_warp_sum(acc);
-        if (lane == 0) p.logits[b * (p.n_exp + 1) + row] = acc;
-    }
-}
-
-// ------------------------------------------------------------------------------------ routing
-
-// one CTA of 512 threads; warp per token (loops if t > 16).  Everything stays in registers:
-// lane l holds experts l, l+32, ... of the token.
-__global__ void __launch_bounds__(512) pb_route_kernel(const PbRouteParams p) {
-    extern __shared__ int rsm[];
-    int* cnt = rsm;                 // [1024] entries per expert (local experts only)
-    int* cursor = rsm + 1024;       // [1024] start offset of the expert's entries, then a fill cursor
-    __shared__ int wsum[2][16];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    pb_pdl_wait();
-    pb_pdl_trigger();
-    for (int e = tid; e < 1024; e += 512) { cnt[e] = 0; cursor[e] = 0; }
-    __syncthreads();
-    for (int b = warp; b < p.t; b += 16) {
-        const float* lg = p.logits + (size_t)b * (p.n_exp + 1);
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; i++) { const int e = i * 32 + lane; const float x = e < p.n_exp ? lg[e] : -INFINITY; v[i] = isnan(x) ? -INFINITY : x; }   // nan_clean :3121-3125
-        int my_e = 0; float my_v = -INFINITY;     // lane j keeps the j-th pick (descending logit, ties to the lower id)
-        for (int j = 0; j < p.top_k; j++) {
-            float bv = -INFINITY; int be = 0x7fffffff;
-#pragma unroll
-            for (int i = 0; i < 32; i++) { const int e = i * 32 + lane; if (e < p.n_exp && (v[i] > bv || (v[i] == bv && e < be))) { bv = v[i]; be = e; } }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const int oe = __shfl_xor_sync(0xffffffffu, be, o);
-                if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
-            }
-            if (lane == j) { my_e = be; my_v = bv; }
-#pragma unroll
-            for (int i = 0; i < 32; i++) if (i * 32 + lane == be) v[i] = __int_as_float(0x7fc00000);   // taken: NaN never compares greater or equal
-        }
-        // softmax over the selection, summed in descending-logit order (top_k :3136-3138, soft_top :3126-3131)
-        float mx = lane < p.top_k ? my_v : -INFINITY;
-        mx = pb_warp_max(mx);
-        float w = lane < p.top_k ? expf(my_v - mx) : 0.f;
-        float sum = 0.f;
-        for (int j = 0; j < p.top_k; j++) sum += __shfl_sync(0xffffffffu, w, j);
-        w = isfinite(mx) ? w / sum : 1.0f / (float)(p.top_k > 0 ? p.top_k : 1);
-        // accumulation order = ascending expert id (routed f32 branch :1786): rank of this lane's expert
-        int rank = 0;
-        for (int j = 0; j < p.top_k; j++) { const int oe = __shfl_sync(0xffffffffu, my_e, j); if (oe < my_e) rank++; }
-        if (lane < p.top_k) {
-            p.sel_e[b * p.top_k + rank] = my_e; p.sel_w[b * p.top_k + rank] = w;
-            if (my_e >= p.e_lo && my_e < p.e_hi) atomicAdd(&cnt[my_e], 1);
+            if (lane == 0) p.logits[b * (p.n_exp + 1) + row] = acc;
         }
     }
+    // the last CTA to get here routes all tokens: its reads of the logits follow every other CTA's
+    // fence + ticket, the classic last-block pattern; the ticket is reset for the next launch
+    __shared__ int is_last;
+    __threadfence();
     __syncthreads();
-    // distinct local experts in ascending id with entry offsets: block-wide exclusive scans of
-    // (used flag, entry count) over expert ids; thread t owns experts 2t and 2t+1
-    const int e0 = 2 * tid, e1 = 2 * tid + 1;
-    const int c0 = e0 < p.n_exp ? cnt[e0] : 0, c1 = e1 < p.n_exp ? cnt[e1] : 0;
-    int f = (c0 > 0) + (c1 > 0), c = c0 + c1;
-    int fi = f, ci = c;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) { const int a = __shfl_up_sync(0xffffffffu, fi, o), d = __shfl_up_sync(0xffffffffu, ci, o); if (lane >= o) { fi += a; ci += d; } }
-    if (lane == 31) { wsum[0][warp] = fi; wsum[1][warp] = ci; }
+    if (tid == 0) is_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
     __syncthreads();
-    int fb = 0, cb = 0;
-    for (int w2 = 0; w2 < warp; w2++) { fb += wsum[0][w2]; cb += wsum[1][w2]; }
-    int n = fb + fi - f, off = cb + ci - c;   // exclusive prefixes for expert e0
-    if (c0 > 0) { p.used_e[n] = e0; p.used_off[n] = off; cursor[e0] = off; n++; off += c0; }
-    if (c1 > 0) { p.used_e[n] = e1; p.used_off[n] = off; cursor[e1] = off; n++; off += c1; }
-    if (tid == 511) { p.used_off[n] = off; *p.n_used = n; }
-    __syncthreads();
-    for (int i = tid; i < p.t * p.top_k; i += 512) {
-        const int e = p.sel_e[i];
-        if (e >= p.e_lo && e < p.e_hi) { const int pos = atomicAdd(&cursor[e], 1); p.ent_tok[pos] = i / p.top_k; p.ent_slot[pos] = i % p.top_k; p.ent_w[pos] = p.sel_w[i]; }
-    }
+    if (!is_last) return;
+    if (tid == 0) *ticket = 0;
+    __threadfence();
+    pb_route_body(rp, reinterpret_cast<int*>(rs));
 }
 
 // ------------------------------------------------------------------------------------ expert gate/up
@@ -257,10 +267,23 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
     }
 }
 
+// y[tok][r] = sigmoid(shared-gate logit) * shared[tok][r] + sum_j part[tok][j][r]  (ascending expert id),
+// then either stored (layer-level call) or added to the residual stream.  One output element.
+__device__ __forceinline__ void pb_combine_one(const PbCombineParams& p, int64_t i, bool bypass_l1) {
+    const int tok = (int)(i / p.d), r = (int)(i - (int64_t)tok * p.d);
+    float y = 0.f;
+    if (p.part_sh) y = (bypass_l1 ? __ldcg(p.part_sh + i) : p.part_sh[i]) * pb_sigm(p.logits[(size_t)tok * (p.n_exp + 1) + p.n_exp]);   // routed :1723
+    float o = 0.f;
+    for (int j = 0; j < p.top_k; j++) { const float* q = p.part + ((size_t)tok * p.top_k + j) * p.d + r; o += bypass_l1 ? __ldcg(q) : *q; }
+    y += o;
+    float* dst = p.y + (size_t)tok * p.ldy + r;
+    *dst = p.accumulate ? *dst + y : y;
+}
+
 // ------------------------------------------------------------------------------------ expert down
 
 template <int FMT, int PASSES>
-__global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const PbExpertParams p) {
+__global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const PbExpertParams p, const PbCombineParams cp, unsigned int* ticket) {
     using D = PbQDec<FMT>;
     extern __shared__ __align__(128) uint8_t smem[];
     PbRing ring;
@@ -350,6 +373,18 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
         }
         pb_ring_release(ring, k, lane);
     }
+    // optional fused combine (small token counts, single GPU): the last CTA whose consumers get here
+    // sums the partial rows of all CTAs -- last-block pattern: fence, ticket, fence, L1-bypassing reads
+    if (!ticket) return;
+    __shared__ int is_last;
+    __threadfence();
+    pb_named_barrier(1, CT);
+    if (tid == 0) is_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+    pb_named_barrier(1, CT);
+    if (!is_last) return;
+    if (tid == 0) *ticket = 0;
+    __threadfence();
+    for (int64_t i = tid; i < (int64_t)cp.t * cp.d; i += CT) pb_combine_one(cp, i, true);
 }
 
 // ------------------------------------------------------------------------------------ combine
@@ -360,39 +395,24 @@ __global__ void __launch_bounds__(256) pb_moe_combine_kernel(const PbCombinePara
     pb_pdl_wait();
     pb_pdl_trigger();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (int64_t)p.t * p.d) return;
-    const int tok = (int)(i / p.d), r = (int)(i - (int64_t)tok * p.d);
-    float y = 0.f;
-    if (p.part_sh) y = p.part_sh[i] * pb_sigm(p.logits[(size_t)tok * (p.n_exp + 1) + p.n_exp]);   // routed :1723
-    float o = 0.f;
-    for (int j = 0; j < p.top_k; j++) o += p.part[((size_t)tok * p.top_k + j) * p.d + r];
-    y += o;
-    float* dst = p.y + (size_t)tok * p.ldy + r;
-    *dst = p.accumulate ? *dst + y : y;
+    if (i < (int64_t)p.t * p.d) pb_combine_one(p, i, false);
 }
 
 // ------------------------------------------------------------------------------------ launchers
 
-int pb_launch_router(pb_ctx* ctx, const PbRouterParams& p) {
+int pb_launch_router(pb_ctx* ctx, const PbRouterParams& p, const PbRouteParams& rp, unsigned int* ticket) {
     if (p.cols % 128) PB_FAIL(ctx, PB_UNSUPPORTED, "router: width %d is not a multiple of 128", p.cols);
+    if (rp.top_k > PB_MAX_TOPK || rp.n_exp > 1024) PB_FAIL(ctx, PB_UNSUPPORTED, "route: top_k %d / n_exp %d beyond %d / 1024", rp.top_k, rp.n_exp, PB_MAX_TOPK);
     const int grid = (p.n_exp + 1 + 7) / 8;
-    const size_t smem = (size_t)((p.t + 31) & ~31) * 4;
-    pb_launch_k(ctx, pb_router_kernel, dim3(grid), dim3(256), (size_t)(smem), p);
-    ctx->kernels_launched++;
-    PB_CUDA(ctx, cudaGetLastError());
-    return PB_OK;
-}
-
-int pb_launch_route(pb_ctx* ctx, const PbRouteParams& p) {
-    if (p.top_k > PB_MAX_TOPK || p.n_exp > 1024) PB_FAIL(ctx, PB_UNSUPPORTED, "route: top_k %d / n_exp %d beyond %d / 1024", p.top_k, p.n_exp, PB_MAX_TOPK);
-    pb_launch_k(ctx, pb_route_kernel, dim3(1), dim3(512), (size_t)(2048 * sizeof(int)), p);
+    const size_t smem = (size_t)(2048 + ((p.t + 31) & ~31)) * 4;
+    pb_launch_k(ctx, pb_router_kernel, dim3(grid), dim3(256), smem, p, rp, ticket);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;
 }
 
 template <int FMT, int PASSES, bool DOWN>
-static int launch_expert(pb_ctx* ctx, PbExpertParams p, int cols) {
+static int launch_expert(pb_ctx* ctx, PbExpertParams p, int cols, const PbCombineParams* cp, unsigned int* ticket) {
     int el, bs;
     pb_geom(FMT, &el, &bs);
     p.row_bytes = cols / el * bs; p.bpr = cols / 256;
@@ -412,7 +432,8 @@ static int launch_expert(pb_ctx* ctx, PbExpertParams p, int cols) {
         auto kern = pb_expert_down_kernel<FMT, PASSES>;
         static size_t configured = 0;
         if (smem > configured) { PB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = smem; }
-        pb_launch_k(ctx, kern, dim3(ctx->sm_count), dim3(PB_KTHREADS), (size_t)(smem), p);
+        PbCombineParams c0; memset(&c0, 0, sizeof c0);
+        pb_launch_k(ctx, kern, dim3(ctx->sm_count), dim3(PB_KTHREADS), (size_t)(smem), p, cp ? *cp : c0, cp ? ticket : (unsigned int*)nullptr);
     } else {
         auto kern = pb_expert_gu_kernel<FMT, PASSES>;
         static size_t configured = 0;
@@ -425,9 +446,9 @@ static int launch_expert(pb_ctx* ctx, PbExpertParams p, int cols) {
 }
 
 template <bool DOWN>
-static int launch_expert_type(pb_ctx* ctx, const PbExpertParams& p, int type, int cols) {
+static int launch_expert_type(pb_ctx* ctx, const PbExpertParams& p, int type, int cols, const PbCombineParams* cp = nullptr, unsigned int* ticket = nullptr) {
     if (!pb_gemvq_supported(type, cols)) PB_FAIL(ctx, PB_UNSUPPORTED, "expert kernel: ggml type %d with %d columns is not supported", type, cols);
-#define GO(F) return cols <= 2048 ? launch_expert<F, 1, DOWN>(ctx, p, cols) : launch_expert<F, 2, DOWN>(ctx, p, cols)
+#define GO(F) return cols <= 2048 ? launch_expert<F, 1, DOWN>(ctx, p, cols, cp, ticket) : launch_expert<F, 2, DOWN>(ctx, p, cols, cp, ticket)
     switch (type) {
         case PB_T_IQ3_S: GO(PB_T_IQ3_S);
         case PB_T_IQ2_XS: GO(PB_T_IQ2_XS);
@@ -438,7 +459,8 @@ static int launch_expert_type(pb_ctx* ctx, const PbExpertParams& p, int type, in
 }
 
 int pb_launch_expert_gu(pb_ctx* ctx, const PbExpertParams& p, int type, int cols) { return launch_expert_type<false>(ctx, p, type, cols); }
-int pb_launch_expert_down(pb_ctx* ctx, const PbExpertParams& p, int type, int cols) { return launch_expert_type<true>(ctx, p, type, cols); }
+// cp != null: the last CTA also performs the combine (see pb_expert_down_kernel)
+int pb_launch_expert_down(pb_ctx* ctx, const PbExpertParams& p, int type, int cols, const PbCombineParams* cp, unsigned int* ticket) { return launch_expert_type<true>(ctx, p, type, cols, cp, ticket); }
 
 int pb_launch_moe_combine(pb_ctx* ctx, const PbCombineParams& p) {
     const int64_t n = (int64_t)p.t * p.d;
