@@ -1,0 +1,310 @@
+// Batched dequant-GEMM for 4..16 activation columns on the tensor cores (IQ3_S weights).
+//
+//   y[b][yoff_s + r] (+)= sum_c W_s[r][c] * act(x)[b][c]        b = 0 .. t-1 (t <= 16)
+//
+// Used where one weight matrix meets several tokens at once (batched decode, verify windows):
+// the weight bytes are streamed and decoded ONCE for all columns, instead of once per column
+// as in the dp4a GEMV.  Same streaming skeleton (persistent CTAs, producer warp, 1-D bulk
+// copies into a 4-stage ring, bounded mbarrier waits); the arithmetic is
+// mma.sync.m16n8k16 (f16 x f16 -> f32):
+//   - A = 16 rows of decoded weights.  The codebook lives in shared memory as four f16 per
+//     entry; the sub-block multiplier (1 + 2*s <= 31) is folded in exactly (|w| <= 465), the f16
+//     block scale d is applied in f32 once per 256-weight block.
+//   - B = activations split into f16 high and low parts (x = hi + lo, 22 significant bits),
+//     laid out in shared memory in fragment order; an n-tile holds 4 tokens x (hi, lo), so a
+//     thread owns both halves of its tokens and adds them itself.
+//   - the contraction index inside a block is permuted so that thread q of a quad owns the 64
+//     consecutive weights of quarter q (one decode per lane, as in the GEMV); A and B use the
+//     same permutation, so the sum is unchanged.
+// A chunk is 16 rows; the eight consumer warps split its blocks (K) and meet in shared memory.
+// Replaces the reference's batched GEMV / prefill GEMM (k_gemv4*, k_gemm_pf / k_gemm_tc,
+// src/model/qn_cube.rs:71-233, 293-1159) for IQ3_S; other formats keep the dp4a kernel.
+#include "pb_stream.cuh"
+#include "pb_internal.h"
+
+#include <cuda_fp16.h>
+#include <stdio.h>
+
+#define GH_CONSUMERS 8
+#define GH_THREADS ((GH_CONSUMERS + 1) * 32)
+#define GH_ROWS 16
+
+__device__ __forceinline__ void pb_mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// One quarter (64 weights) of an IQ3_S block as 32 half2 words with the sub-block multiplier and
+// the signs applied; returns the block scale d.  tab_h: 512 x 4 f16, sign256 as in pb_qdot.cuh.
+__device__ __forceinline__ float pb_iq3s_quarter_h(uint32_t p, int qt, uint32_t tab_h, uint32_t sign256, uint32_t (&h)[32]) {
+    const float d = pb_h2f((uint16_t)pb_lds16(p));
+    uint32_t qs[4], sg[2];
+    pb_ld_u32x<4>(p + 2 + 16 * qt, qs);
+    pb_ld_u32x<2>(p + 74 + 8 * qt, sg);
+    const uint32_t qh = pb_lds16(p + 66 + 2 * qt);
+    const uint32_t sc = pb_lds8(p + 106 + qt);
+    const __half2 m0 = __half2half2(__int2half_rn(1 + 2 * (int)(sc & 0xF))), m1 = __half2half2(__int2half_rn(1 + 2 * (int)(sc >> 4)));
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+        const uint32_t w = qs[u >> 1] >> (16 * (u & 1));
+        const uint32_t h0 = 2 * u < 8 ? (qh << (8 - 2 * u)) : (qh >> (2 * u - 8));
+        const uint32_t h1 = 2 * u + 1 < 8 ? (qh << (7 - 2 * u)) : (qh >> (2 * u - 7));
+        const uint32_t i0 = (w & 0xFF) | (h0 & 0x100), i1 = ((w >> 8) & 0xFF) | (h1 & 0x100);
+        const uint2 g0 = pb_lds64(tab_h + i0 * 8), g1 = pb_lds64(tab_h + i1 * 8);
+        const uint32_t sb = (sg[u >> 2] >> (8 * (u & 3))) & 0xFF;
+        const uint4 m = pb_lds128(sign256 + sb * 16);   // byte masks: x = entry 2u, z = entry 2u+1
+        // byte mask (0xFF per negative weight) -> f16 sign bits of two half2 words
+        const uint32_t s00 = __byte_perm(m.x, 0, 0x1404) & 0x80008000u, s01 = __byte_perm(m.x, 0, 0x3424) & 0x80008000u;
+        const uint32_t s10 = __byte_perm(m.z, 0, 0x1404) & 0x80008000u, s11 = __byte_perm(m.z, 0, 0x3424) & 0x80008000u;
+        const __half2 mm = u < 4 ? m0 : m1;
+        __half2 a;
+        a = __hmul2(*reinterpret_cast<const __half2*>(&g0.x), mm); h[4 * u + 0] = *reinterpret_cast<uint32_t*>(&a) ^ s00;
+        a = __hmul2(*reinterpret_cast<const __half2*>(&g0.y), mm); h[4 * u + 1] = *reinterpret_cast<uint32_t*>(&a) ^ s01;
+        a = __hmul2(*reinterpret_cast<const __half2*>(&g1.x), mm); h[4 * u + 2] = *reinterpret_cast<uint32_t*>(&a) ^ s10;
+        a = __hmul2(*reinterpret_cast<const __half2*>(&g1.y), mm); h[4 * u + 3] = *reinterpret_cast<uint32_t*>(&a) ^ s11;
+    }
+    return d;
+}
+
+// byte offset of the 8-byte B-fragment slot of (block blk, entry j, n-tile nt, token-in-tile tq, level lv, quarter q)
+__device__ __forceinline__ uint32_t pb_xh_off(int blk, int j, int nt, int NT, int tq, int lv, int q) {
+    return (uint32_t)((((blk * 16 + j) * NT + nt) * 32 + ((2 * tq + lv) * 4 + q)) * 8);
+}
+
+// store 4 consecutive activations (elements c .. c+3, c % 4 == 0) of token b as f16 hi / lo fragments
+__device__ __forceinline__ void pb_xh_store(uint8_t* xh, int NT, int b, int c, float4 v) {
+    const int blk = c >> 8, q = (c >> 6) & 3, j = (c >> 2) & 15, nt = b >> 2, tq = b & 3;
+    const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
+    const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+    const __half2 l01 = __floats2half2_rn(v.x - f01.x, v.y - f01.y), l23 = __floats2half2_rn(v.z - f23.x, v.w - f23.y);
+    *reinterpret_cast<uint2*>(xh + pb_xh_off(blk, j, nt, NT, tq, 0, q)) = make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+    *reinterpret_cast<uint2*>(xh + pb_xh_off(blk, j, nt, NT, tq, 1, q)) = make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
+}
+
+// NST = stages of the ring (4; 2 for rows wider than 2048 columns, whose fragments leave less room)
+template <int NT, int NST>
+__global__ void __launch_bounds__(GH_THREADS, 1) pb_gemmh_iq3s_kernel(const PbGemvQParams p) {
+    constexpr int NB = 4 * NT;
+    extern __shared__ __align__(128) uint8_t smem[];
+    PbRing ring;
+    ring.full = reinterpret_cast<uint64_t*>(smem);
+    ring.empty = ring.full + NST;
+    float* red0 = reinterpret_cast<float*>(smem + 64);            // GH_CONSUMERS floats
+    float* xinv = reinterpret_cast<float*>(smem + 128);           // per token: inverse of the power-of-two prescale
+    uint8_t* tab = smem + 256;                                    // sign table (4 KB) + f16 codebook (4 KB)
+    const int cols = p.bpr * 256;
+    uint8_t* xh = tab + 8192;                                     // B fragments: cols * NB * 4 bytes
+    float* red = reinterpret_cast<float*>(xh + (size_t)cols * NB * 4);   // [2][GH_CONSUMERS][16 rows][NB]
+    ring.stages = reinterpret_cast<uint8_t*>(red) + 2 * GH_CONSUMERS * GH_ROWS * NB * 4;
+    ring.stage_bytes = p.stage_bytes;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pb_pdl_trigger();
+    if (tid == 0) {
+        for (int s = 0; s < NST; s++) { pb_mbar_init(&ring.full[s], 1); pb_mbar_init(&ring.empty[s], GH_CONSUMERS); }
+        pb_fence_barrier_init();
+    }
+    __syncthreads();
+    const int my_chunks = p.nchunks > (int)blockIdx.x ? (p.nchunks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+
+    if (warp == GH_CONSUMERS) {
+        if (lane == 0) {
+            int k = 0;
+            for (; k < my_chunks; k++) {
+                const int chunk = (int)blockIdx.x + k * (int)gridDim.x;
+                int s = 0;
+                while (s + 1 < p.nseg && chunk >= p.seg[s + 1].chunk0) s++;
+                const int r0 = (chunk - p.seg[s].chunk0) * GH_ROWS;
+                const int nr = min(GH_ROWS, p.seg[s].rows - r0);
+                const uint32_t bytes = ((uint32_t)nr * (uint32_t)p.row_bytes + 15u) & ~15u;
+                const int st = k % NST;
+                if (k >= NST && !pb_mbar_wait(&ring.empty[st], ((k / NST) - 1) & 1, p.status, PB_DEV_WAIT_EMPTY_TIMEOUT)) break;
+                pb_mbar_expect_tx(&ring.full[st], bytes);
+                pb_bulk_g2s(ring.stages + (size_t)st * ring.stage_bytes, p.seg[s].w + (size_t)r0 * p.row_bytes, bytes, &ring.full[st]);
+            }
+            // error path: give the copies in flight a bounded chance to land before the CTA may exit
+            if (k < my_chunks) for (int j = max(0, k - NST); j < k; j++) pb_mbar_wait(&ring.full[j % NST], (j / NST) & 1, nullptr, 0);
+        }
+        return;
+    }
+
+    // ---- consumers: tables ----
+    constexpr int CT = GH_CONSUMERS * 32;
+    {
+        uint4* sgn = reinterpret_cast<uint4*>(tab);
+        for (int i = tid; i < 256; i += CT) {
+            uint32_t lo = 0, hi = 0;
+            for (int j = 0; j < 4; j++) { if (i & (1 << j)) lo |= 0xFFu << (8 * j); if (i & (16 << j)) hi |= 0xFFu << (8 * j); }
+            sgn[i] = make_uint4(lo, lo & 0x01010101u, hi, hi & 0x01010101u);
+        }
+        uint2* gh = reinterpret_cast<uint2*>(tab + 4096);
+        for (int i = tid; i < 512; i += CT) {
+            const uint32_t g = PB_IQ3S_GRID[i];
+            const __half2 a = __floats2half2_rn((float)(g & 0xFF), (float)((g >> 8) & 0xFF)), b = __floats2half2_rn((float)((g >> 16) & 0xFF), (float)(g >> 24));
+            gh[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+        }
+    }
+    const uint32_t sign256 = pb_smem_u32(tab), tab_h = pb_smem_u32(tab + 4096);
+    if (tid < NB) xinv[tid] = 1.0f;
+    pb_named_barrier(2, CT);
+    pb_pdl_wait();
+    // ---- activations -> f16 hi/lo fragments ----
+    if (p.mode == PB_ACT_GNORM) {
+        const int nheads = cols / p.head_dim;   // head_dim == 128 (checked on the host)
+        for (int i = warp; i < NB * nheads; i += GH_CONSUMERS) {
+            const int b = i / nheads, h = i - b * nheads;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (b < p.t) {
+                v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + h * p.head_dim + 4 * lane);
+                const float ss = pb_warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+                const float s = 1.0f / sqrtf(ss / (float)p.head_dim + p.eps);
+                const float4 w = *reinterpret_cast<const float4*>(p.norm_w + 4 * lane);
+                const float4 z = *reinterpret_cast<const float4*>(p.z + b * p.ldz + h * p.head_dim + 4 * lane);
+                v.x = v.x * (s * w.x) * pb_sigm(z.x); v.y = v.y * (s * w.y) * pb_sigm(z.y); v.z = v.z * (s * w.z) * pb_sigm(z.z); v.w = v.w * (s * w.w) * pb_sigm(z.w);
+            } else { (void)pb_warp_sum(0.f); }
+            pb_xh_store(xh, NT, b, h * p.head_dim + 4 * lane, v);
+        }
+    } else {
+        for (int b = 0; b < NB; b++) {
+            // one CTA-wide reduction per token: sum of squares (NORM) or largest magnitude (PLAIN)
+            float r = 0.f;
+            if (b < p.t) for (int c = tid; c < cols; c += CT) { const float v = p.x[b * p.ldx + c]; r = p.mode == PB_ACT_NORM ? r + v * v : fmaxf(r, fabsf(v)); }
+            r = p.mode == PB_ACT_NORM ? pb_warp_sum(r) : pb_warp_max(r);
+            pb_named_barrier(2, CT);
+            if (lane == 0) red0[warp] = r;
+            pb_named_barrier(2, CT);
+            float tot = 0.f;
+#pragma unroll
+            for (int i = 0; i < GH_CONSUMERS; i++) tot = p.mode == PB_ACT_NORM ? tot + red0[i] : fmaxf(tot, red0[i]);
+            float s = 1.0f;
+            if (p.mode == PB_ACT_NORM) s = 1.0f / sqrtf(tot / (float)cols + p.eps);
+            else if (tot > 0.f && tot <= 3.0e38f) {
+                // exact power-of-two prescale into [0.5, 1): f16 neither overflows nor loses small columns
+                int e; (void)frexpf(tot, &e);
+                s = ldexpf(1.0f, -e);
+                if (tid == 0) xinv[b] = ldexpf(1.0f, e);
+            }
+            for (int c = tid * 4; c < cols; c += CT * 4) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (b < p.t) {
+                    v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + c);
+                    if (p.mode == PB_ACT_NORM) { const float4 w = *reinterpret_cast<const float4*>(p.norm_w + c); v.x = v.x * s * w.x; v.y = v.y * s * w.y; v.z = v.z * s * w.z; v.w = v.w * s * w.w; }
+                    else { v.x *= s; v.y *= s; v.z *= s; v.w *= s; }
+                }
+                pb_xh_store(xh, NT, b, c, v);
+            }
+        }
+    }
+    pb_named_barrier(1, CT);
+
+    const int g = lane >> 2, q = lane & 3;
+    const uint32_t xh_s = pb_smem_u32(xh);
+    for (int k = 0; k < my_chunks; k++) {
+        if (!pb_mbar_wait(&ring.full[k % NST], (k / NST) & 1, p.status, PB_DEV_WAIT_FULL_TIMEOUT)) return;
+        const int chunk = (int)blockIdx.x + k * (int)gridDim.x;
+        int s = 0;
+        while (s + 1 < p.nseg && chunk >= p.seg[s + 1].chunk0) s++;
+        const int r0 = (chunk - p.seg[s].chunk0) * GH_ROWS;
+        const int nr = min(GH_ROWS, p.seg[s].rows - r0);
+        const uint32_t base = pb_smem_u32(ring.stages + (size_t)(k % NST) * ring.stage_bytes);
+        float tot[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) { tot[nt][0] = tot[nt][1] = tot[nt][2] = tot[nt][3] = 0.f; }
+        for (int blk = warp; blk < p.bpr; blk += GH_CONSUMERS) {   // K split: this warp's blocks of the 16 rows
+            uint32_t ha[32], hb[32];
+            // rows g and g + 8 (rows past the end of the matrix decode stale bytes of the stage; never stored)
+            const float da = pb_iq3s_quarter_h(base + (uint32_t)g * p.row_bytes + blk * 110, q, tab_h, sign256, ha);
+            const float db = pb_iq3s_quarter_h(base + (uint32_t)(g + 8) * p.row_bytes + blk * 110, q, tab_h, sign256, hb);
+            float acc[NT][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const uint2 bx = pb_lds64(xh_s + (uint32_t)((((blk * 16 + j) * NT + nt) * 32 + lane) * 8));
+                    pb_mma_f16(acc[nt], ha[2 * j], hb[2 * j], ha[2 * j + 1], hb[2 * j + 1], bx.x, bx.y);
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                tot[nt][0] = fmaf(da, acc[nt][0], tot[nt][0]); tot[nt][1] = fmaf(da, acc[nt][1], tot[nt][1]);
+                tot[nt][2] = fmaf(db, acc[nt][2], tot[nt][2]); tot[nt][3] = fmaf(db, acc[nt][3], tot[nt][3]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) pb_mbar_arrive(&ring.empty[k % NST]);
+        // this warp's partial [16 rows][NB tokens]: thread (g, q) owns rows g, g+8 and token 4*nt + q (hi + lo columns)
+        float* mine = red + (size_t)((k & 1) * GH_CONSUMERS + warp) * GH_ROWS * NB;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            mine[g * NB + 4 * nt + q] = tot[nt][0] + tot[nt][1];
+            mine[(g + 8) * NB + 4 * nt + q] = tot[nt][2] + tot[nt][3];
+        }
+        pb_named_barrier(1, CT);
+        // 256 threads <-> 16 rows x up to 16 tokens
+        for (int o = tid; o < GH_ROWS * NB; o += CT) {
+            const int r = o / NB, b = o - r * NB;
+            if (r < nr && b < p.t) {
+                const float* src = red + (size_t)(k & 1) * GH_CONSUMERS * GH_ROWS * NB + o;
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < GH_CONSUMERS; w++) v += src[(size_t)w * GH_ROWS * NB];
+                v *= xinv[b];
+                float* dst = p.y + b * p.ldy + p.seg[s].yoff + r0 + r;
+                *dst = p.accumulate ? *dst + v : v;
+            }
+        }
+        // the buffer of parity k & 1 is rewritten two chunks later, after the barrier of chunk k + 1
+    }
+}
+
+template <int NT, int NST>
+static int launch_h(pb_ctx* ctx, const PbGemvQArgs& a) {
+    constexpr int NB = 4 * NT;
+    PbGemvQParams p;
+    memset(&p, 0, sizeof p);
+    p.row_bytes = a.cols / 256 * 110; p.bpr = a.cols / 256; p.nseg = a.nseg;
+    p.x = a.x; p.ldx = a.ldx; p.t = a.t; p.y = a.y; p.ldy = a.ldy; p.status = ctx->dev_status;
+    p.mode = a.mode; p.norm_w = a.norm_w; p.z = a.z; p.ldz = a.ldz; p.head_dim = a.head_dim; p.eps = a.eps; p.accumulate = a.accumulate;
+    p.rows_per_chunk = GH_ROWS;
+    int nchunks = 0;
+    for (int s = 0; s < a.nseg; s++) {
+        p.seg[s].w = a.seg[s].w; p.seg[s].rows = (int)a.seg[s].rows; p.seg[s].yoff = (int)a.seg[s].yoff; p.seg[s].chunk0 = nchunks;
+        nchunks += (int)((a.seg[s].rows + GH_ROWS - 1) / GH_ROWS);
+    }
+    p.nchunks = nchunks;
+    p.stage_bytes = (uint32_t)(((size_t)GH_ROWS * p.row_bytes + 16 + 127) & ~(size_t)127);
+    const size_t smem = 256 + 8192 + (size_t)a.cols * NB * 4 + 2 * GH_CONSUMERS * GH_ROWS * NB * 4 + (size_t)NST * p.stage_bytes;
+    if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "gemm: %zu bytes of shared memory needed for cols=%d t=%d", smem, a.cols, a.t);
+    auto kern = pb_gemmh_iq3s_kernel<NT, NST>;
+    static size_t configured = 0;
+    if (smem > configured) { PB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = smem; }
+    const int grid = nchunks < ctx->sm_count ? nchunks : ctx->sm_count;
+    pb_launch_k(ctx, kern, dim3(grid), dim3(GH_THREADS), smem, p);
+    ctx->kernels_launched++;
+    PB_CUDA(ctx, cudaGetLastError());
+    return PB_OK;
+}
+
+bool pb_gemmh_supported(int type, int cols, int t) { return type == PB_T_IQ3_S && t >= 3 && cols % 256 == 0 && cols >= 256 && cols <= 4096; }
+
+int pb_launch_gemmh(pb_ctx* ctx, const PbGemvQArgs& a) {
+    if (!pb_gemmh_supported(a.type, a.cols, a.t)) PB_FAIL(ctx, PB_UNSUPPORTED, "gemm: type %d cols %d t %d", a.type, a.cols, a.t);
+    if (a.mode == PB_ACT_PREQ) PB_FAIL(ctx, PB_UNSUPPORTED, "gemm: pre-split activations are not accepted");
+    if (a.mode == PB_ACT_GNORM && a.head_dim != 128) PB_FAIL(ctx, PB_UNSUPPORTED, "gemm: gated norm over heads of %d (128 is built)", a.head_dim);
+    if (((uintptr_t)a.x & 15) || (a.ldx & 3)) PB_FAIL(ctx, PB_ERR_ARG, "gemm: activations must be 16-byte aligned");
+    // columns per launch: 16 with a 4-stage ring up to 2048 weight columns, 8 with a 2-stage ring above
+    const bool wide = a.cols > 2048;
+    const int tile = wide ? 8 : 16;
+    int rc = PB_OK;
+    for (int t0 = 0; t0 < a.t && rc == PB_OK; t0 += tile) {
+        PbGemvQArgs s = a;
+        s.t = a.t - t0 < tile ? a.t - t0 : tile;
+        s.x = a.x + (int64_t)t0 * a.ldx; s.y = a.y + (int64_t)t0 * a.ldy; s.z = a.z ? a.z + (int64_t)t0 * a.ldz : nullptr;
+        if (wide) rc = s.t <= 4 ? launch_h<1, 2>(ctx, s) : launch_h<2, 2>(ctx, s);
+        else rc = s.t <= 4 ? launch_h<1, 4>(ctx, s) : (s.t <= 8 ? launch_h<2, 4>(ctx, s) : launch_h<4, 4>(ctx, s));
+    }
+    return rc;
+}

@@ -17,6 +17,7 @@
 // the k_rms* prologues (src/model/qn_cube.rs:257-2331) of the reference.
 #include "pb_stream.cuh"
 #include "pb_internal.h"
+#include <stdlib.h>
 
 #include <stdio.h>
 
@@ -250,6 +251,10 @@ int pb_launch_gemvq(pb_ctx* ctx, const PbGemvQArgs& a) {
     if (a.nseg < 1 || a.nseg > 4) PB_FAIL(ctx, PB_ERR_ARG, "gemv: %d segments", a.nseg);
     if (a.mode == PB_ACT_GNORM && a.head_dim != 128) PB_FAIL(ctx, PB_UNSUPPORTED, "gemv: gated norm over heads of %d (128 is built)", a.head_dim);
     if (((uintptr_t)a.x & 15) || (a.ldx & 3)) PB_FAIL(ctx, PB_ERR_ARG, "gemv: activations must be 16-byte aligned");
+    if (a.mode != PB_ACT_PREQ && pb_gemmh_supported(a.type, a.cols, a.t)) {
+        static const bool use_mma = !(getenv("PYRE_B200_MMA") && atoi(getenv("PYRE_B200_MMA")) == 0);
+        if (use_mma) return pb_launch_gemmh(ctx, a);
+    }
     const int row_bytes = a.cols / el * bs;
     // column tiles: the int8-split activations of one launch must fit in ~96 KB of shared memory
     int tile = 16;

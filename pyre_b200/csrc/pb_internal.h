@@ -132,6 +132,9 @@ struct PbGemvQParams {
 };
 bool pb_gemvq_supported(int type, int cols);
 int pb_launch_gemvq(pb_ctx* ctx, const PbGemvQArgs& a);
+// pb_gemmh.cu: tensor-core path for 3..16 columns of IQ3_S weights
+bool pb_gemmh_supported(int type, int cols, int t);
+int pb_launch_gemmh(pb_ctx* ctx, const PbGemvQArgs& a);
 
 // ---------------------------------------------------------------- pb_moe.cu
 #define PB_MAX_TOPK 16
