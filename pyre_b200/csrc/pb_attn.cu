@@ -6,15 +6,23 @@
 // (src/model/qn_cube.rs:5419-5655, 7394-7500).
 //
 // Cache layout per attention layer (head-major, so the positions of one KV head are one
-// contiguous stream): packed words kw[b][kvh][pos][hd/8] (8 nibbles per u32, low nibble =
-// element 0) with one f32 scale per 32 values ks[b][kvh][pos][hd/32]; positions older than
-// the packed boundary q4n live there, the newest ones in an f32 ring kr[b][kvh][slot][hd],
-// slot = pos mod ring capacity.  q4n = ((len - recent) / 64) * 64, the reference's rule.
+// contiguous stream): packed K words kw[b][kvh][pos][hd/8] (8 nibbles per u32, low nibble =
+// element 0) with one f32 scale per 32 values ks[b][kvh][pos][hd/32]; packed V words are
+// stored position-transposed, vw[b][kvh][pos/8][hd] with position pos%8 of one dimension in
+// nibble pos%8 (same bytes per position, same quantization and scales vs[b][kvh][pos][hd/32]),
+// which is the operand order of the P.V tensor-core product.  Positions older than the packed
+// boundary q4n live there, the newest ones in an f32 ring kr[b][kvh][slot][hd], slot = pos mod
+// ring capacity.  q4n = ((len - recent) / 64) * 64, the reference's rule.
 //
 //   pb_kv_append_kernel    RMSNorm(k) * kn, partial RoPE, append K and V at the position,
 //                          move the packed boundary (packs whole multiples of 64 positions)
 //   pb_attn_partial_kernel split-KV flash-decode: grid (split, KV head, sequence); the 8 query
-//                          heads of a GQA group share every K/V byte that is read
+//                          heads of a GQA group share every K/V byte that is read.  Splits below
+//                          nsplit_packed walk the packed positions on the tensor cores
+//                          (mma.sync m16n8k16 f16, f32 accumulate: nibbles are exact in f16,
+//                          queries and probabilities go in as f16 high + low parts, block scales
+//                          are applied in f32); the remaining splits walk the f32 ring with
+//                          scalar FMAs
 //   pb_attn_combine_kernel merges the splits, normalizes, applies the sigmoid output gate
 #include "pb_common.cuh"
 #include "pb_internal.h"
@@ -65,6 +73,33 @@ __device__ __forceinline__ void pb_kv4_pack_block(float v, int lane, uint32_t* w
     u |= __shfl_xor_sync(0xffffffffu, u, 1); u |= __shfl_xor_sync(0xffffffffu, u, 2); u |= __shfl_xor_sync(0xffffffffu, u, 4);
     if ((lane & 7) == 0) words4[lane >> 3] = u;
     if (lane == 0) *scale = s;
+}
+
+// one warp packs 32 dims of 8 consecutive positions into position-transposed words: lane = dim,
+// v[i] = value of position i; same quantization as pb_kv4_pack_block, one scale per position
+__device__ __forceinline__ uint32_t pb_kv4_pack_vt8(const float (&v)[8], int lane, float* scales, int scale_stride) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float m = pb_warp_max(fabsf(v[i]));
+        const float s = (m > 0.f && isfinite(m)) ? m / 7.0f : 0.f;
+        int q = 0;
+        if (s > 0.f) { float r = roundf(v[i] / s); r = fminf(fmaxf(r, -7.f), 7.f); q = (int)r; }
+        word |= ((uint32_t)q & 0xF) << (4 * i);
+        if (lane == 0) scales[(size_t)i * scale_stride] = s;
+    }
+    return word;
+}
+// x [npos][hd] f32 (npos a multiple of 8) -> w [npos/8][hd] words, sc [npos][hd/32]; one warp per (8 positions, 32 dims)
+__global__ void __launch_bounds__(256) pb_kv4_pack_vt_kernel(const float* __restrict__ x, int64_t npos, int hd, uint32_t* __restrict__ w, float* __restrict__ sc) {
+    const int64_t unit = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31, bpp = hd / 32;
+    if (unit >= (npos / 8) * bpp) return;
+    const int64_t pg = unit / bpp; const int blk = (int)(unit % bpp);
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = x[(pg * 8 + i) * hd + blk * 32 + lane];
+    w[pg * hd + blk * 32 + lane] = pb_kv4_pack_vt8(v, lane, sc + pg * 8 * bpp + blk, bpp);
 }
 
 // generic packer: x [n] f32 -> words [n/8], scales [n/32]; one warp per block
@@ -128,7 +163,16 @@ __global__ void __launch_bounds__(AT_THREADS) pb_kv_append_kernel(const PbAttnPa
         const size_t src = (((size_t)b * nkv + h) * p.ring_cap + (pp % p.ring_cap)) * hd + blk * 32 + lane;
         const size_t row = ((size_t)b * nkv + h) * p.max_ctx + pp;
         pb_kv4_pack_block(p.kr[src], lane, p.kw + row * (hd / 8) + blk * 4, p.ks + row * bpp + blk);
-        pb_kv4_pack_block(p.vr[src], lane, p.vw + row * (hd / 8) + blk * 4, p.vs + row * bpp + blk);
+    }
+    // V: groups of 8 positions (have and want are multiples of 64)
+    const int64_t nvt = (want - have) / 8 * nkv * bpp;
+    for (int64_t i = warp; i < nvt; i += AT_WARPS) {
+        const int blk = (int)(i % bpp); const int h = (int)((i / bpp) % nkv); const int64_t pg = have / 8 + i / ((int64_t)bpp * nkv);
+        const size_t head = (size_t)b * nkv + h;
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[j] = p.vr[(head * p.ring_cap + ((pg * 8 + j) % p.ring_cap)) * hd + blk * 32 + lane];
+        p.vw[head * p.max_ctx * (hd / 8) + (size_t)pg * hd + blk * 32 + lane] = pb_kv4_pack_vt8(v, lane, p.vs + (head * p.max_ctx + pg * 8) * bpp + blk, bpp);
     }
     __syncthreads();
     if (tid == 0) p.q4n[b] = want;
@@ -136,8 +180,177 @@ __global__ void __launch_bounds__(AT_THREADS) pb_kv_append_kernel(const PbAttnPa
 
 // ------------------------------------------------------------------------------------ partial
 
-// grid (nsplit, n_kv, batch), 256 threads.  Lane l of a warp owns dims 8l..8l+7 of the head
-// (one packed word, or two float4 of an f32 row); a warp walks tiles of 32 positions.
+#define AT_STAGE_WORDS 2944   // per warp: K tile 32 x 36 words (padded rows), V tile 1024, K scales 256, V scales 256, scores 256
+#define AT_KSTRIDE 36
+
+__device__ __forceinline__ void pb_mma16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// f16 pair of (a, b) and the f16 pair of what the first rounding lost
+__device__ __forceinline__ void pb_split_h2(float a, float b, uint32_t& hi, uint32_t& lo) {
+    const __half2 h = __floats2half2_rn(a, b);
+    const float2 r = __half22float2(h);
+    const __half2 l = __floats2half2_rn(a - r.x, b - r.y);
+    hi = *reinterpret_cast<const uint32_t*>(&h); lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+// nibbles q and q + 4 of a word of offset-binary nibbles (two's complement ^ 8) -> f16 pair of the signed values
+__device__ __forceinline__ uint32_t pb_nib2_h2(uint32_t x, int sh) {
+    const uint32_t t = ((x >> sh) & 0x000F000Fu) | 0x64006400u;           // 1024 + n
+    const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&t), __float2half2_rn(1032.0f));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+// shared-memory loads that the compiler may not hoist over the per-tile restaging of the buffers
+__device__ __forceinline__ uint32_t pb_ldsv32(uint32_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a) : "memory"); return v; }
+__device__ __forceinline__ uint4 pb_ldsv128(uint32_t a) { uint4 v; asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory"); return v; }
+__device__ __forceinline__ float pb_exp2i(int k) { k = k < -126 ? -126 : (k > 127 ? 127 : k); return __int_as_float((k + 127) << 23); }
+
+// Packed positions on the tensor cores.  Thread (g, q) = (lane >> 2, lane & 3).
+//   S = Q K^T: A rows = query heads (rows >= G are zero), k = the 8 dims of one packed word, in
+//     the order (q, q+4) per thread, [Q_hi | Q_lo] side by side in k; B = K nibbles as f16, the
+//     same registers for both halves of k; column c of an 8-position group is position
+//     (c >> 1) + 4 (c & 1), so that a thread ends up with the scores of positions q and q + 4.
+//   O^T = V^T P^T: A rows = 16 dims, k = the 8 positions of a group (nibbles q, q+4 of the
+//     transposed V word); B = [P_hi ; P_lo] times the V block scale (made per 32-dim block in
+//     f32, relative to a running power-of-two 2^E so that f16 neither overflows nor flushes).
+template <int G>
+__device__ __forceinline__ void pb_attn_mma_tiles(const float* qs, uint32_t* stage, int warp, int lane, int sp, int nsp, const uint32_t* kw,
+                                                  const uint32_t* vw, const float* ks, const float* vs, int64_t ntiles, float* mw) {
+    constexpr int HD = 256;
+    const int g = lane >> 2, q = lane & 3, sh = 4 * q;
+    uint32_t qh[32], ql[32];
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+        const float x0 = g < G ? qs[g * HD + 8 * i + q] : 0.f, x1 = g < G ? qs[g * HD + 8 * i + q + 4] : 0.f;
+        pb_split_h2(x0, x1, qh[i], ql[i]);
+    }
+    float m_run = -INFINITY, l_run = 0.f, acc[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+    constexpr int E_NONE = -100000;
+    int E = E_NONE;
+    uint32_t* tk = stage; uint32_t* tv = stage + 32 * AT_KSTRIDE;
+    float* tks = reinterpret_cast<float*>(tv + 1024); float* tvs = tks + 256;
+    float2* sbuf = reinterpret_cast<float2*>(tvs + 256);   // [4 groups][32 lanes]: scores, then probabilities
+    const uint32_t tk_s = pb_smem_u32(tk), tv_s = pb_smem_u32(tv);
+    const int krow = (g >> 1) + 4 * (g & 1);
+
+    for (int64_t t = (int64_t)warp * nsp + sp; t < ntiles; t += (int64_t)AT_WARPS * nsp) {
+        const int64_t pbase = t * AT_TILE;
+        {
+            const uint4* gk = reinterpret_cast<const uint4*>(kw + pbase * (HD / 8));
+            const uint4* gv = reinterpret_cast<const uint4*>(vw + pbase * (HD / 8));
+            const uint4* gks = reinterpret_cast<const uint4*>(ks + pbase * (HD / 32));
+            const uint4* gvs = reinterpret_cast<const uint4*>(vs + pbase * (HD / 32));
+            uint4 a[8], c[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) { a[i] = gk[i * 32 + lane]; c[i] = gv[i * 32 + lane]; }
+            const uint4 sa0 = gks[lane], sa1 = gks[32 + lane], sc0 = gvs[lane], sc1 = gvs[32 + lane];
+            __syncwarp();   // every lane is done with the previous tile
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int f = i * 32 + lane;
+                uint4 kx = a[i];
+                kx.x ^= 0x88888888u; kx.y ^= 0x88888888u; kx.z ^= 0x88888888u; kx.w ^= 0x88888888u;
+                *reinterpret_cast<uint4*>(tk + (f >> 3) * AT_KSTRIDE + 4 * (f & 7)) = kx;
+                uint4 vx = c[i];
+                vx.x ^= 0x88888888u; vx.y ^= 0x88888888u; vx.z ^= 0x88888888u; vx.w ^= 0x88888888u;
+                reinterpret_cast<uint4*>(tv)[f] = vx;
+            }
+            reinterpret_cast<uint4*>(tks)[lane] = sa0; reinterpret_cast<uint4*>(tks)[32 + lane] = sa1;
+            reinterpret_cast<uint4*>(tvs)[lane] = sc0; reinterpret_cast<uint4*>(tvs)[32 + lane] = sc1;
+            // largest V scale of the tile -> running exponent
+            float vm = fmaxf(fmaxf(fmaxf(__uint_as_float(sc0.x), __uint_as_float(sc0.y)), fmaxf(__uint_as_float(sc0.z), __uint_as_float(sc0.w))),
+                             fmaxf(fmaxf(__uint_as_float(sc1.x), __uint_as_float(sc1.y)), fmaxf(__uint_as_float(sc1.z), __uint_as_float(sc1.w))));
+            vm = pb_warp_max(vm);
+            __syncwarp();
+            float facc = 1.0f;
+            if (vm > 0.f && vm <= 3.0e38f) {
+                const int e = ilogbf(vm) + 1;
+                if (e > E) { facc = E == E_NONE ? 0.f : pb_exp2i(E - e); E = e; }
+            }
+            const float vscl = E == E_NONE ? 0.f : pb_exp2i(-E);
+
+            // ---- scores.  The loops over the four 8-position groups stay rolled (a fully unrolled tile is
+            //      ~40 KB of straight-line code that no warp reuses: instruction fetch then bounds the
+            //      kernel); their per-group values pass through this lane's slots of sbuf
+#pragma unroll 1
+            for (int nt = 0; nt < 4; nt++) {
+                float s0 = 0.f, s1 = 0.f;
+                const uint32_t ka = tk_s + (uint32_t)((8 * nt + krow) * AT_KSTRIDE) * 4;
+                const float* sk = tks + (8 * nt + q) * 8;
+#pragma unroll
+                for (int blk = 0; blk < 8; blk++) {
+                    const uint4 kk = pb_ldsv128(ka + blk * 16);
+                    float c4[4] = {0.f, 0.f, 0.f, 0.f};
+                    uint32_t bb;
+                    bb = pb_nib2_h2(kk.x, sh); pb_mma16(c4, qh[4 * blk + 0], 0u, ql[4 * blk + 0], 0u, bb, bb);
+                    bb = pb_nib2_h2(kk.y, sh); pb_mma16(c4, qh[4 * blk + 1], 0u, ql[4 * blk + 1], 0u, bb, bb);
+                    bb = pb_nib2_h2(kk.z, sh); pb_mma16(c4, qh[4 * blk + 2], 0u, ql[4 * blk + 2], 0u, bb, bb);
+                    bb = pb_nib2_h2(kk.w, sh); pb_mma16(c4, qh[4 * blk + 3], 0u, ql[4 * blk + 3], 0u, bb, bb);
+                    s0 = fmaf(sk[blk], c4[0], s0);
+                    s1 = fmaf(sk[32 + blk], c4[1], s1);
+                }
+                sbuf[nt * 32 + lane] = make_float2(s0, s1);
+            }
+            // ---- online softmax: this thread holds 8 of the 32 scores of head g, its quad the rest
+            float2 S0 = sbuf[lane], S1 = sbuf[32 + lane], S2 = sbuf[64 + lane], S3 = sbuf[96 + lane];
+            float mt = fmaxf(fmaxf(fmaxf(S0.x, S0.y), fmaxf(S1.x, S1.y)), fmaxf(fmaxf(S2.x, S2.y), fmaxf(S3.x, S3.y)));
+            mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 1)); mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 2));
+            const float mn = fmaxf(m_run, mt);
+            const float corr = m_run == -INFINITY ? 0.f : expf(m_run - mn);
+            S0.x = expf(S0.x - mn); S0.y = expf(S0.y - mn); S1.x = expf(S1.x - mn); S1.y = expf(S1.y - mn);
+            S2.x = expf(S2.x - mn); S2.y = expf(S2.y - mn); S3.x = expf(S3.x - mn); S3.y = expf(S3.y - mn);
+            float psum = ((S0.x + S0.y) + (S1.x + S1.y)) + ((S2.x + S2.y) + (S3.x + S3.y));
+            sbuf[lane] = S0; sbuf[32 + lane] = S1; sbuf[64 + lane] = S2; sbuf[96 + lane] = S3;
+            psum += __shfl_xor_sync(0xffffffffu, psum, 1); psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+            l_run = l_run * corr + psum; m_run = mn;
+            // the output columns of this thread are heads 2q and 2q + 1
+            const float cf = corr * facc;
+            const float ca = __shfl_sync(0xffffffffu, cf, 8 * q), cb = __shfl_sync(0xffffffffu, cf, 8 * q + 4);
+#pragma unroll
+            for (int i = 0; i < 16; i++) { acc[i][0] *= ca; acc[i][1] *= cb; acc[i][2] *= ca; acc[i][3] *= cb; }
+            // ---- O^T += V^T (P * scale)^T
+#pragma unroll 1
+            for (int nt = 0; nt < 4; nt++) {
+                const float2 pr = sbuf[nt * 32 + lane];
+                const float* sv = tvs + (8 * nt + q) * 8;
+                const uint32_t va = tv_s + (uint32_t)(nt * HD + g) * 4;
+#pragma unroll
+                for (int blk = 0; blk < 8; blk++) {
+                    const float f0 = pr.x * (sv[blk] * vscl), f1 = pr.y * (sv[32 + blk] * vscl);
+                    uint32_t bh, bl;
+                    pb_split_h2(f0, f1, bh, bl);
+#pragma unroll
+                    for (int h2 = 0; h2 < 2; h2++) {
+                        const int mtile = 2 * blk + h2;
+                        const uint32_t a0 = pb_nib2_h2(pb_ldsv32(va + (uint32_t)(16 * mtile) * 4), sh);
+                        const uint32_t a1 = pb_nib2_h2(pb_ldsv32(va + (uint32_t)(16 * mtile + 8) * 4), sh);
+                        pb_mma16(acc[mtile], a0, a1, a0, a1, bh, bl);
+                    }
+                }
+            }
+        }
+    }
+    // ---- this warp's partial in the merge layout [G][2 + hd]
+    const float oscale = E == E_NONE ? 0.f : pb_exp2i(E);
+#ifdef PB_ATTN_DBG
+    if (lane == 0) printf("E %d oscale %g acc0 %g %g %g %g m %g l %g\n", E, oscale, acc[0][0], acc[0][1], acc[0][2], acc[0][3], m_run, l_run);
+#endif
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        const int d0 = 16 * i + g;
+        if (2 * q < G) { mw[(2 * q) * (2 + HD) + 2 + d0] = acc[i][0] * oscale; mw[(2 * q) * (2 + HD) + 2 + d0 + 8] = acc[i][2] * oscale; }
+        if (2 * q + 1 < G) { mw[(2 * q + 1) * (2 + HD) + 2 + d0] = acc[i][1] * oscale; mw[(2 * q + 1) * (2 + HD) + 2 + d0 + 8] = acc[i][3] * oscale; }
+    }
+    if (q == 0 && g < G) { mw[g * (2 + HD)] = m_run; mw[g * (2 + HD) + 1] = l_run; }
+}
+
+// grid (nsplit, n_kv, batch), 256 threads; a warp walks tiles of 32 positions.  Splits
+// [0, nsplit_packed) take the packed tiles through pb_attn_mma_tiles; the other splits take the
+// tiles from the packed boundary on (all tiles when nsplit_packed == 0) with scalar FMAs, where
+// lane l owns dims 8l..8l+7 of the head.
 template <int G>
 __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const PbAttnParams p) {
     const int sp = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -177,6 +390,26 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
     }
     __syncthreads();
 
+    const int64_t ntiles = (n + AT_TILE - 1) / AT_TILE;
+    // tiles are dealt round-robin to (split, warp) so that the slower f32 tiles of the recent window
+    // are spread over all CTAs instead of landing on the last splits
+    const size_t hrow = (size_t)b * p.n_kv + kvh;
+    const uint32_t* kw = p.kw + hrow * p.max_ctx * (hd / 8);
+    const uint32_t* vw = p.vw + hrow * p.max_ctx * (hd / 8);
+    const float* ks = p.ks + hrow * p.max_ctx * (hd / 32);
+    const float* vs = p.vs + hrow * p.max_ctx * (hd / 32);
+    const float* kr = p.kr + hrow * p.ring_cap * hd;
+    const float* vr = p.vr + hrow * p.ring_cap * hd;
+    float* pw = prob + warp * AT_TILE * G;
+    float* mw = mrg + (size_t)warp * G * (2 + hd);
+    // per-warp staging of one packed tile
+    uint32_t* tkw = reinterpret_cast<uint32_t*>(mrg + (size_t)AT_WARPS * G * (2 + hd)) + (size_t)warp * AT_STAGE_WORDS;
+    const int nsp = p.nsplit_packed, nrs = (int)gridDim.x - nsp;
+    // tiles that are packed and entirely below the current length go to the tensor-core splits
+    const int64_t tpk = nsp > 0 ? (q4n < n ? q4n : n) / AT_TILE : 0;
+    if (sp < nsp) {
+        if (G <= 8) pb_attn_mma_tiles<(G <= 8 ? G : 8)>(qs, tkw, warp, lane, sp, nsp, kw, vw, ks, vs, tpk, mw);
+    } else {
     // this lane's 8 query dims for every head of the group (hd = 256 -> one 8-dim slice per lane)
     float q[G][8];
 #pragma unroll
@@ -190,24 +423,11 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
 #pragma unroll
         for (int j = 0; j < 8; j++) acc[g][j] = 0.f; }
 
-    const int64_t ntiles = (n + AT_TILE - 1) / AT_TILE;
-    // tiles are dealt round-robin to (split, warp) so that the slower f32 tiles of the recent window
-    // are spread over all CTAs instead of landing on the last splits
-    const size_t hrow = (size_t)b * p.n_kv + kvh;
-    const uint32_t* kw = p.kw + hrow * p.max_ctx * (hd / 8);
-    const uint32_t* vw = p.vw + hrow * p.max_ctx * (hd / 8);
-    const float* ks = p.ks + hrow * p.max_ctx * (hd / 32);
-    const float* vs = p.vs + hrow * p.max_ctx * (hd / 32);
-    const float* kr = p.kr + hrow * p.ring_cap * hd;
-    const float* vr = p.vr + hrow * p.ring_cap * hd;
-    float* pw = prob + warp * AT_TILE * G;
-    // per-warp staging of one packed tile: K/V words [32 pos][hd/8] and scales [32 pos][hd/32]
-    uint32_t* tkw = reinterpret_cast<uint32_t*>(mrg + (size_t)AT_WARPS * G * (2 + hd)) + (size_t)warp * 2 * (AT_TILE * (hd / 8) + AT_TILE * (hd / 32));
     float* tks = reinterpret_cast<float*>(tkw + AT_TILE * (hd / 8));
     uint32_t* tvw = reinterpret_cast<uint32_t*>(tks + AT_TILE * (hd / 32));
     float* tvs = reinterpret_cast<float*>(tvw + AT_TILE * (hd / 8));
 
-    for (int64_t t = (int64_t)warp * gridDim.x + sp; t < ntiles; t += (int64_t)AT_WARPS * gridDim.x) {
+    for (int64_t t = tpk + (int64_t)warp * nrs + (sp - nsp); t < ntiles; t += (int64_t)AT_WARPS * nrs) {
         const int64_t pbase = t * AT_TILE;
         // q4n is a multiple of 64 and tiles start at multiples of 32: a tile is entirely packed or entirely f32
         const bool packed = pbase < q4n;
@@ -299,10 +519,9 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
             if (pp >= n) break;
             float vv[8];
             if (packed) {
-                const uint32_t w = tvw[i * (hd / 8) + lane];
                 const float s = tvs[i * (hd / 32) + (lane >> 2)];
 #pragma unroll
-                for (int j = 0; j < 8; j++) vv[j] = pb_kv4_dequant(w, j, s);
+                for (int j = 0; j < 8; j++) vv[j] = pb_kv4_dequant(tvw[(i >> 3) * hd + 8 * lane + j], i & 7, s);   // position-transposed words
             } else {
                 const float4* src = reinterpret_cast<const float4*>(vr + (size_t)(pp % p.ring_cap) * hd + 8 * lane);
                 const float4 a = src[0], c = src[1];
@@ -318,14 +537,14 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
         __syncwarp();
     }
 
-    // ---- merge the 8 warps of the CTA, then write the split's partial
-    float* mw = mrg + (size_t)warp * G * (2 + hd);
 #pragma unroll
     for (int g = 0; g < G; g++) {
         if (lane == 0) { mw[g * (2 + hd)] = m_run[g]; mw[g * (2 + hd) + 1] = l_run[g]; }
 #pragma unroll
         for (int j = 0; j < 8; j++) mw[g * (2 + hd) + 2 + 8 * lane + j] = acc[g][j];
     }
+    }
+    // ---- merge the 8 warps of the CTA, then write the split's partial
     __syncthreads();
     for (int g = warp; g < G; g += AT_WARPS) {
         float M = -INFINITY;
@@ -398,10 +617,11 @@ int pb_launch_kv_append(pb_ctx* ctx, const PbAttnParams& p) {
 
 int pb_launch_attn(pb_ctx* ctx, const PbAttnParams& p) {
     const int G = p.n_head / p.n_kv;
+    if (p.nsplit_packed < 0 || p.nsplit_packed >= p.nsplit || (p.nsplit_packed > 0 && (G > 8 || p.kv_bits != 4))) PB_FAIL(ctx, PB_ERR_ARG, "attention: %d of %d splits on the packed path", p.nsplit_packed, p.nsplit);
     if (p.hd != 256 || p.nsplit > 128 || p.n_head % p.n_kv || (G != 8 && G != 4 && G != 2 && G != 1))
         PB_FAIL(ctx, PB_UNSUPPORTED, "attention: head dim %d with %d query heads per KV head not supported", p.hd, G);
     const dim3 grid(p.nsplit, p.n_kv, p.batch);
-    const size_t smem = ((size_t)G * p.hd + (size_t)AT_WARPS * AT_TILE * G + (size_t)AT_WARPS * G * (2 + p.hd) + (size_t)AT_WARPS * 2 * (AT_TILE * (p.hd / 8) + AT_TILE * (p.hd / 32))) * 4;
+    const size_t smem = ((size_t)G * p.hd + (size_t)AT_WARPS * AT_TILE * G + (size_t)AT_WARPS * G * (2 + p.hd) + (size_t)AT_WARPS * AT_STAGE_WORDS) * 4;
     if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "attention needs %zu bytes of shared memory", smem);
 #define GO(GG)                                                                                                                   \
     {                                                                                                                            \
@@ -423,6 +643,15 @@ int pb_launch_kv4_pack(pb_ctx* ctx, const float* x, int64_t n, uint32_t* w, floa
     const int64_t nblocks = n / 32;
     if (nblocks <= 0) return PB_OK;
     pb_launch_k(ctx, pb_kv4_pack_kernel, dim3((unsigned)((nblocks + 7) / 8)), dim3(256), (size_t)(0), x, nblocks, w, sc);
+    ctx->kernels_launched++;
+    PB_CUDA(ctx, cudaGetLastError());
+    return PB_OK;
+}
+int pb_launch_kv4_pack_vt(pb_ctx* ctx, const float* x, int64_t npos, int hd, uint32_t* w, float* sc) {
+    if (npos <= 0) return PB_OK;
+    if (npos % 8 || hd % 32) PB_FAIL(ctx, PB_ERR_ARG, "kv4 pack: %lld positions of %d dims (multiples of 8 and 32 needed)", (long long)npos, hd);
+    const int64_t units = npos / 8 * (hd / 32);
+    pb_launch_k(ctx, pb_kv4_pack_vt_kernel, dim3((unsigned)((units + 7) / 8)), dim3(256), (size_t)(0), x, npos, hd, w, sc);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;

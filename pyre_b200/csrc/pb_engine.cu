@@ -10,6 +10,7 @@
 #include "pb_internal.h"
 
 #include <stdio.h>
+#include <stdlib.h>
 #include <new>
 #include <vector>
 
@@ -40,7 +41,7 @@ struct pb_state {
     int *sel_e = nullptr, *n_used = nullptr, *used_e = nullptr, *used_off = nullptr, *ent_tok = nullptr, *ent_slot = nullptr;
     float *sel_w = nullptr, *ent_w = nullptr, *h = nullptr, *h_sh = nullptr, *part = nullptr, *part_sh = nullptr, *logits = nullptr;
     float *part_ml = nullptr, *part_acc = nullptr;
-    int nsplit = 1;
+    int nsplit = 1, nsplit_packed = 0;
     int64_t ldproj = 0, ring_cap = 0;
     std::vector<float*> conv, ssm;
     std::vector<PbKv> kv;
@@ -266,6 +267,19 @@ int pb_state_create(pb_model* m, int batch, pb_state** out) {
     int ns = ctx->sm_count / (c.n_kv * B > 0 ? c.n_kv * B : 1);
     if (ns < 1) ns = 1;
     if (ns > 128) ns = 128;
+    // 4-bit cache: one split per (sequence, KV head) walks the f32 ring, the others the packed positions
+    static const bool attn_mma = !(getenv("PYRE_B200_ATTN_MMA") && atoi(getenv("PYRE_B200_ATTN_MMA")) == 0);
+    s->nsplit_packed = 0;
+    if (c.kv_bits == 4 && G <= 8 && c.hd == 256 && attn_mma) {
+        if (ns >= 8) s->nsplit_packed = ns - 1;
+        else {
+            // many (sequence, KV head) pairs: several CTAs per SM's worth of work, so that the tail wave stays short
+            int fine = 4 * ctx->sm_count / (c.n_kv * B);
+            if (fine > 8) fine = 8;
+            s->nsplit_packed = fine > ns ? fine : ns;
+            ns = s->nsplit_packed + 1;
+        }
+    }
     s->nsplit = ns;
     A(part_ml, (size_t)B * c.n_kv * ns * G * 2); A(part_acc, (size_t)B * c.n_kv * ns * G * c.hd);
     s->conv.assign(m->n_lin, nullptr); s->ssm.assign(m->n_lin, nullptr); s->kv.assign(m->n_attn, PbKv());
@@ -361,7 +375,19 @@ static void attn_params(pb_state* s, int il, PbAttnParams& p) {
     p.n_rot = c.n_rot; p.eps = c.eps; p.n_head = c.n_head; p.n_kv = c.n_kv; p.hd = c.hd;
     p.kw = k.kw; p.ks = k.ks; p.vw = k.vw; p.vs = k.vs; p.kr = k.kr; p.vr = k.vr;
     p.max_ctx = c.kv_bits == 4 ? c.max_ctx : 1; p.ring_cap = s->ring_cap; p.kv_bits = c.kv_bits; p.kv_recent = c.kv_recent;
-    p.pos = s->pos; p.q4n = k.q4n; p.part_ml = s->part_ml; p.part_acc = s->part_acc; p.nsplit = s->nsplit;
+    p.pos = s->pos; p.q4n = k.q4n; p.part_ml = s->part_ml; p.part_acc = s->part_acc; p.nsplit = s->nsplit; p.nsplit_packed = s->nsplit_packed;
+    if (s->nsplit_packed > 0) {
+        // share the splits between the packed positions and the f32 ring by estimated work at the
+        // current length (an f32 tile costs about five packed tiles); a captured graph keeps the
+        // share of its capture position, which drifts by a few tiles per thousand tokens
+        const int64_t len = s->pos_host + 1;
+        const int64_t q4 = len > c.kv_recent ? ((len - c.kv_recent) / 64) * 64 : 0;
+        const double wp = (double)(q4 / 32), wr = 5.0 * (double)((len - q4 + 31) / 32);
+        int nrs = (int)(s->nsplit * wr / (wr + wp) + 0.5);
+        if (nrs < 1) nrs = 1;
+        if (nrs > s->nsplit - 1) nrs = s->nsplit - 1;
+        p.nsplit_packed = s->nsplit - nrs;
+    }
     p.att = s->att; p.lda = (int64_t)c.n_head * c.hd; p.batch = s->batch;
 }
 
@@ -758,7 +784,8 @@ int pb_state_fill_kv(pb_state* s, int b, int ai, const float* k_host, const floa
             const size_t head = (size_t)b * nkv + h;
             if (q4n > 0) {
                 PB_CUDA(ctx, cudaMemcpyAsync(scr, tmp.data(), (size_t)q4n * hd * 4, cudaMemcpyHostToDevice, ctx->stream));
-                PB_TRY(pb_launch_kv4_pack(ctx, (const float*)scr, q4n * hd, (which ? kv.vw : kv.kw) + head * c.max_ctx * (hd / 8), (which ? kv.vs : kv.ks) + head * c.max_ctx * (hd / 32)));
+                if (which) PB_TRY(pb_launch_kv4_pack_vt(ctx, (const float*)scr, q4n, hd, kv.vw + head * c.max_ctx * (hd / 8), kv.vs + head * c.max_ctx * (hd / 32)));
+                else PB_TRY(pb_launch_kv4_pack(ctx, (const float*)scr, q4n * hd, kv.kw + head * c.max_ctx * (hd / 8), kv.ks + head * c.max_ctx * (hd / 32)));
                 PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
             }
             float* ring = (which ? kv.vr : kv.kr) + head * s->ring_cap * hd;
@@ -786,7 +813,8 @@ int pb_state_fill_kv_synth(pb_state* s, int ai, int64_t n, uint64_t seed) {
             for (int h = 0; h < nkv; h++) {
                 const size_t head = (size_t)b * nkv + h;
                 PB_TRY(pb_launch_synth_normal_at(ctx, f, n * hd, seed, (uint64_t)ai * 2 + which, (int64_t)(head * c.max_ctx) * hd, 1.0f));
-                if (q4n > 0) PB_TRY(pb_launch_kv4_pack(ctx, f, q4n * hd, (which ? kv.vw : kv.kw) + head * c.max_ctx * (hd / 8), (which ? kv.vs : kv.ks) + head * c.max_ctx * (hd / 32)));
+                if (q4n > 0 && which) PB_TRY(pb_launch_kv4_pack_vt(ctx, f, q4n, hd, kv.vw + head * c.max_ctx * (hd / 8), kv.vs + head * c.max_ctx * (hd / 32)));
+                if (q4n > 0 && !which) PB_TRY(pb_launch_kv4_pack(ctx, f, q4n * hd, kv.kw + head * c.max_ctx * (hd / 8), kv.ks + head * c.max_ctx * (hd / 32)));
                 float* ring = (which ? kv.vr : kv.kr) + head * s->ring_cap * hd;
                 for (int64_t p = q4n; p < n;) {   // contiguous runs inside the ring
                     const int64_t slot = p % s->ring_cap, run = (n - p) < (s->ring_cap - slot) ? (n - p) : (s->ring_cap - slot);

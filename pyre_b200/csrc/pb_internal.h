@@ -199,12 +199,14 @@ struct PbAttnParams {
     int64_t max_ctx; int64_t ring_cap; int kv_bits; int kv_recent;
     const int64_t* pos; int64_t* q4n;                    // [batch]
     float* part_ml; float* part_acc; int nsplit;
+    int nsplit_packed;                                   // splits [0, nsplit_packed) walk the packed positions on the tensor cores
     float* att; int64_t lda;                             // [batch][n_head*hd]
     int batch;
 };
 int pb_launch_kv_append(pb_ctx* ctx, const PbAttnParams& p);
 int pb_launch_attn(pb_ctx* ctx, const PbAttnParams& p);
 int pb_launch_kv4_pack(pb_ctx* ctx, const float* x, int64_t n, uint32_t* w, float* sc);
+int pb_launch_kv4_pack_vt(pb_ctx* ctx, const float* x, int64_t npos, int hd, uint32_t* w, float* sc);   // position-transposed V words
 int pb_launch_kv4_unpack(pb_ctx* ctx, const uint32_t* w, const float* sc, int64_t n, float* x);
 
 // ---------------------------------------------------------------- pb_misc.cu
