@@ -54,6 +54,7 @@ int pb_ctx_create(int device, pb_ctx** out) {
     c->stream = c->own_stream;
     if (cudaMalloc(&c->dev_status, 256) != cudaSuccess) { cudaStreamDestroy(c->own_stream); delete c; return PB_ERR_OOM; }
     cudaMemset(c->dev_status, 0, 256);
+    if (cudaMalloc(&c->xh_buf, PB_XH_BYTES) != cudaSuccess) { cudaFree(c->dev_status); cudaStreamDestroy(c->own_stream); delete c; return PB_ERR_OOM; }
     if (cudaMallocHost(&c->host_status, 256) != cudaSuccess) { cudaFree(c->dev_status); cudaStreamDestroy(c->own_stream); delete c; return PB_ERR_OOM; }
     *c->host_status = 0;
     { const char* e = getenv("PYRE_B200_PDL"); if (e && e[0] == '0') c->use_pdl = false; }   // PYRE_B200_PDL=0: plain stream order inside the token step
@@ -68,6 +69,7 @@ int pb_ctx_destroy(pb_ctx* ctx) {
     pb_ep_destroy(ctx);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
+    if (ctx->xh_buf) cudaFree(ctx->xh_buf);
     if (ctx->host_status) cudaFreeHost(ctx->host_status);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;

@@ -82,6 +82,62 @@ __device__ __forceinline__ void pb_xh_store(uint8_t* xh, int NT, int b, int c, f
     *reinterpret_cast<uint2*>(xh + pb_xh_off(blk, j, nt, NT, tq, 1, q)) = make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
 }
 
+// Activations of up to NB = 4 * NT tokens -> f16 high / low parts in B-fragment order, written once
+// to global memory for all CTAs of the GEMM; grid = NB CTAs (one token slot each, slots >= t are
+// zero), 256 threads.  PLAIN columns get an exact power-of-two prescale into [0.5, 1) (f16 neither
+// overflows nor loses small columns); its inverse goes to xinv.
+template <int NT>
+__global__ void __launch_bounds__(256) pb_xh_prep_kernel(const PbGemvQParams p, uint8_t* __restrict__ xh, float* __restrict__ xinv) {
+    constexpr int CT = 256;
+    const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int cols = p.bpr * 256;
+    __shared__ float red0[8];
+    pb_pdl_wait();
+    pb_pdl_trigger();
+    if (tid == 0) xinv[b] = 1.0f;
+    if (p.mode == PB_ACT_GNORM) {
+        const int nheads = cols / p.head_dim;   // head_dim == 128 (checked on the host)
+        for (int h = warp; h < nheads; h += 8) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (b < p.t) {
+                v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + h * p.head_dim + 4 * lane);
+                const float ss = pb_warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+                const float s = 1.0f / sqrtf(ss / (float)p.head_dim + p.eps);
+                const float4 w = *reinterpret_cast<const float4*>(p.norm_w + 4 * lane);
+                const float4 z = *reinterpret_cast<const float4*>(p.z + b * p.ldz + h * p.head_dim + 4 * lane);
+                v.x = v.x * (s * w.x) * pb_sigm(z.x); v.y = v.y * (s * w.y) * pb_sigm(z.y); v.z = v.z * (s * w.z) * pb_sigm(z.z); v.w = v.w * (s * w.w) * pb_sigm(z.w);
+            }
+            pb_xh_store(xh, NT, b, h * p.head_dim + 4 * lane, v);
+        }
+        return;
+    }
+    // one CTA-wide reduction: sum of squares (NORM) or largest magnitude (PLAIN)
+    float r = 0.f;
+    if (b < p.t) for (int c = tid; c < cols; c += CT) { const float v = p.x[b * p.ldx + c]; r = p.mode == PB_ACT_NORM ? r + v * v : fmaxf(r, fabsf(v)); }
+    r = p.mode == PB_ACT_NORM ? pb_warp_sum(r) : pb_warp_max(r);
+    if (lane == 0) red0[warp] = r;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot = p.mode == PB_ACT_NORM ? tot + red0[i] : fmaxf(tot, red0[i]);
+    float s = 1.0f;
+    if (p.mode == PB_ACT_NORM) s = 1.0f / sqrtf(tot / (float)cols + p.eps);
+    else if (tot > 0.f && tot <= 3.0e38f) {
+        int e; (void)frexpf(tot, &e);
+        s = ldexpf(1.0f, -e);
+        if (tid == 0) xinv[b] = ldexpf(1.0f, e);
+    }
+    for (int c = tid * 4; c < cols; c += CT * 4) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (b < p.t) {
+            v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + c);
+            if (p.mode == PB_ACT_NORM) { const float4 w = *reinterpret_cast<const float4*>(p.norm_w + c); v.x = v.x * s * w.x; v.y = v.y * s * w.y; v.z = v.z * s * w.z; v.w = v.w * s * w.w; }
+            else { v.x *= s; v.y *= s; v.z *= s; v.w *= s; }
+        }
+        pb_xh_store(xh, NT, b, c, v);
+    }
+}
+
 // NST = stages of the ring (4; 2 for rows wider than 2048 columns, whose fragments leave less room)
 template <int NT, int NST>
 __global__ void __launch_bounds__(GH_THREADS, 1) pb_gemmh_iq3s_kernel(const PbGemvQParams p) {
@@ -92,6 +148,7 @@ __global__ void __launch_bounds__(GH_THREADS, 1) pb_gemmh_iq3s_kernel(const PbGe
     ring.empty = ring.full + NST;
     float* red0 = reinterpret_cast<float*>(smem + 64);            // GH_CONSUMERS floats
     float* xinv = reinterpret_cast<float*>(smem + 128);           // per token: inverse of the power-of-two prescale
+    uint64_t* xbar = reinterpret_cast<uint64_t*>(smem + 192);     // completion of the fragment copies
     uint8_t* tab = smem + 256;                                    // sign table (4 KB) + f16 codebook (4 KB)
     const int cols = p.bpr * 256;
     uint8_t* xh = tab + 8192;                                     // B fragments: cols * NB * 4 bytes
@@ -103,6 +160,7 @@ __global__ void __launch_bounds__(GH_THREADS, 1) pb_gemmh_iq3s_kernel(const PbGe
     pb_pdl_trigger();
     if (tid == 0) {
         for (int s = 0; s < NST; s++) { pb_mbar_init(&ring.full[s], 1); pb_mbar_init(&ring.empty[s], GH_CONSUMERS); }
+        pb_mbar_init(xbar, 1);
         pb_fence_barrier_init();
     }
     __syncthreads();
@@ -111,7 +169,17 @@ __global__ void __launch_bounds__(GH_THREADS, 1) pb_gemmh_iq3s_kernel(const PbGe
     if (warp == GH_CONSUMERS) {
         if (lane == 0) {
             int k = 0;
+            bool x_issued = false;
             for (; k < my_chunks; k++) {
+                if (k == NST && !x_issued) {
+                    // the ring is full of weights (which no earlier kernel writes): now wait for the kernel
+                    // that made the fragments and bring them in, in pieces of 16 KB
+                    pb_pdl_wait();
+                    const uint32_t xbytes = (uint32_t)cols * NB * 4;
+                    pb_mbar_expect_tx(xbar, xbytes);
+                    for (uint32_t o = 0; o < xbytes; o += 16384) pb_bulk_g2s(xh + o, p.xh_in + o, min(16384u, xbytes - o), xbar);
+                    x_issued = true;
+                }
                 const int chunk = (int)blockIdx.x + k * (int)gridDim.x;
                 int s = 0;
                 while (s + 1 < p.nseg && chunk >= p.seg[s + 1].chunk0) s++;
@@ -123,8 +191,17 @@ __global__ void __launch_bounds__(GH_THREADS, 1) pb_gemmh_iq3s_kernel(const PbGe
                 pb_mbar_expect_tx(&ring.full[st], bytes);
                 pb_bulk_g2s(ring.stages + (size_t)st * ring.stage_bytes, p.seg[s].w + (size_t)r0 * p.row_bytes, bytes, &ring.full[st]);
             }
+            if (!x_issued) {
+                pb_pdl_wait();
+                const uint32_t xbytes = (uint32_t)cols * NB * 4;
+                pb_mbar_expect_tx(xbar, xbytes);
+                for (uint32_t o = 0; o < xbytes; o += 16384) pb_bulk_g2s(xh + o, p.xh_in + o, min(16384u, xbytes - o), xbar);
+            }
             // error path: give the copies in flight a bounded chance to land before the CTA may exit
-            if (k < my_chunks) for (int j = max(0, k - NST); j < k; j++) pb_mbar_wait(&ring.full[j % NST], (j / NST) & 1, nullptr, 0);
+            if (k < my_chunks) {
+                for (int j = max(0, k - NST); j < k; j++) pb_mbar_wait(&ring.full[j % NST], (j / NST) & 1, nullptr, 0);
+                pb_mbar_wait(xbar, 0, nullptr, 0);
+            }
         }
         return;
     }
@@ -149,53 +226,9 @@ __global__ void __launch_bounds__(GH_THREADS, 1) pb_gemmh_iq3s_kernel(const PbGe
     if (tid < NB) xinv[tid] = 1.0f;
     pb_named_barrier(2, CT);
     pb_pdl_wait();
-    // ---- activations -> f16 hi/lo fragments ----
-    if (p.mode == PB_ACT_GNORM) {
-        const int nheads = cols / p.head_dim;   // head_dim == 128 (checked on the host)
-        for (int i = warp; i < NB * nheads; i += GH_CONSUMERS) {
-            const int b = i / nheads, h = i - b * nheads;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (b < p.t) {
-                v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + h * p.head_dim + 4 * lane);
-                const float ss = pb_warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
-                const float s = 1.0f / sqrtf(ss / (float)p.head_dim + p.eps);
-                const float4 w = *reinterpret_cast<const float4*>(p.norm_w + 4 * lane);
-                const float4 z = *reinterpret_cast<const float4*>(p.z + b * p.ldz + h * p.head_dim + 4 * lane);
-                v.x = v.x * (s * w.x) * pb_sigm(z.x); v.y = v.y * (s * w.y) * pb_sigm(z.y); v.z = v.z * (s * w.z) * pb_sigm(z.z); v.w = v.w * (s * w.w) * pb_sigm(z.w);
-            } else { (void)pb_warp_sum(0.f); }
-            pb_xh_store(xh, NT, b, h * p.head_dim + 4 * lane, v);
-        }
-    } else {
-        for (int b = 0; b < NB; b++) {
-            // one CTA-wide reduction per token: sum of squares (NORM) or largest magnitude (PLAIN)
-            float r = 0.f;
-            if (b < p.t) for (int c = tid; c < cols; c += CT) { const float v = p.x[b * p.ldx + c]; r = p.mode == PB_ACT_NORM ? r + v * v : fmaxf(r, fabsf(v)); }
-            r = p.mode == PB_ACT_NORM ? pb_warp_sum(r) : pb_warp_max(r);
-            pb_named_barrier(2, CT);
-            if (lane == 0) red0[warp] = r;
-            pb_named_barrier(2, CT);
-            float tot = 0.f;
-#pragma unroll
-            for (int i = 0; i < GH_CONSUMERS; i++) tot = p.mode == PB_ACT_NORM ? tot + red0[i] : fmaxf(tot, red0[i]);
-            float s = 1.0f;
-            if (p.mode == PB_ACT_NORM) s = 1.0f / sqrtf(tot / (float)cols + p.eps);
-            else if (tot > 0.f && tot <= 3.0e38f) {
-                // exact power-of-two prescale into [0.5, 1): f16 neither overflows nor loses small columns
-                int e; (void)frexpf(tot, &e);
-                s = ldexpf(1.0f, -e);
-                if (tid == 0) xinv[b] = ldexpf(1.0f, e);
-            }
-            for (int c = tid * 4; c < cols; c += CT * 4) {
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (b < p.t) {
-                    v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + c);
-                    if (p.mode == PB_ACT_NORM) { const float4 w = *reinterpret_cast<const float4*>(p.norm_w + c); v.x = v.x * s * w.x; v.y = v.y * s * w.y; v.z = v.z * s * w.z; v.w = v.w * s * w.w; }
-                    else { v.x *= s; v.y *= s; v.z *= s; v.w *= s; }
-                }
-                pb_xh_store(xh, NT, b, c, v);
-            }
-        }
-    }
+    // ---- f16 hi/lo fragments and prescales made by pb_xh_prep_kernel: wait for the producer's bulk copies ----
+    if (tid < NB) xinv[tid] = p.xinv_in[tid];
+    if (!pb_mbar_wait(xbar, 0, p.status, PB_DEV_WAIT_FULL_TIMEOUT)) return;
     pb_named_barrier(1, CT);
 
     const int g = lane >> 2, q = lane & 3;
@@ -278,6 +311,11 @@ static int launch_h(pb_ctx* ctx, const PbGemvQArgs& a) {
     p.stage_bytes = (uint32_t)(((size_t)GH_ROWS * p.row_bytes + 16 + 127) & ~(size_t)127);
     const size_t smem = 256 + 8192 + (size_t)a.cols * NB * 4 + 2 * GH_CONSUMERS * GH_ROWS * NB * 4 + (size_t)NST * p.stage_bytes;
     if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "gemm: %zu bytes of shared memory needed for cols=%d t=%d", smem, a.cols, a.t);
+    // fragments of this launch's tokens, made once for all CTAs
+    p.xh_in = ctx->xh_buf + 256; p.xinv_in = reinterpret_cast<const float*>(ctx->xh_buf);
+    pb_launch_k(ctx, pb_xh_prep_kernel<NT>, dim3(NB), dim3(256), (size_t)0, p, ctx->xh_buf + 256, reinterpret_cast<float*>(ctx->xh_buf));
+    ctx->kernels_launched++;
+    PB_CUDA(ctx, cudaGetLastError());
     auto kern = pb_gemmh_iq3s_kernel<NT, NST>;
     static size_t configured = 0;
     if (smem > configured) { PB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = smem; }

@@ -13,6 +13,7 @@ struct pb_ctx {
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;   // the stream every kernel of this context is launched on
     int* dev_status = nullptr;       // device status word (see PB_DEV_* in pb_common.cuh)
+    uint8_t* xh_buf = nullptr;       // PB_XH_BYTES: activation fragments of the tensor-core GEMM (pb_gemmh.cu)
     int* host_status = nullptr;      // pinned host mirror, filled by an async copy before each sync
     int sm_count = 148;
     int max_smem_optin = 0;
@@ -107,6 +108,7 @@ enum { PB_ACT_PLAIN = 0,   // x as given
        PB_ACT_GNORM = 2,   // per head of head_dim: rms(x) * norm_w[head_dim], times sigmoid(z)
        PB_ACT_PREQ = 3 };  // activations already split into int8 levels (xq_in)
 struct PbGemvSegArg { const uint8_t* w; int64_t rows; int64_t yoff; };
+#define PB_XH_BYTES (256 + 4096 * 16 * 4)
 struct PbGemvQArgs {
     int type, cols, nseg;
     PbGemvSegArg seg[4];
@@ -127,6 +129,7 @@ struct PbGemvQParams {
     float* y; int64_t ldy;
     int mode; const float* norm_w; const float* z; int64_t ldz; int head_dim; float eps;
     const uint32_t* xq_in;
+    const uint8_t* xh_in; const float* xinv_in;   // pb_gemmh.cu: f16 fragments and prescale inverses made by its prep kernel
     int accumulate;
     int* status;
 };
