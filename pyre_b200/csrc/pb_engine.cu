@@ -39,6 +39,7 @@ struct pb_state {
     float *x = nullptr, *xin = nullptr, *proj = nullptr, *olin = nullptr, *att = nullptr, *rlogits = nullptr, *yout = nullptr;
     uint32_t* xq = nullptr;
     int *sel_e = nullptr, *n_used = nullptr, *used_e = nullptr, *used_off = nullptr, *ent_tok = nullptr, *ent_slot = nullptr;
+    uint32_t* hq = nullptr;
     float *sel_w = nullptr, *ent_w = nullptr, *h = nullptr, *h_sh = nullptr, *part = nullptr, *part_sh = nullptr, *logits = nullptr;
     float *part_ml = nullptr, *part_acc = nullptr;
     int nsplit = 1, nsplit_packed = 0;
@@ -258,6 +259,7 @@ int pb_state_create(pb_model* m, int batch, pb_state** out) {
     A(sel_e, (size_t)B * c.top_k); A(sel_w, (size_t)B * c.top_k); A(n_used, 4); A(used_e, c.n_exp + 1); A(used_off, c.n_exp + 2);
     A(ent_tok, (size_t)B * c.top_k); A(ent_slot, (size_t)B * c.top_k); A(ent_w, (size_t)B * c.top_k);
     A(h, (size_t)B * c.top_k * c.ff_exp); A(h_sh, (size_t)B * c.ff_sh);
+    A(hq, (size_t)B * (c.top_k + 1) * pb_xq_words(c.ff_exp > c.ff_sh ? c.ff_exp : c.ff_sh));
     A(part, (size_t)B * c.top_k * c.d); A(part_sh, (size_t)B * c.d);
     A(logits, (size_t)B * c.vocab);
     s->trace_cap = 4096;
@@ -434,6 +436,7 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
     e.e_base = dn->rows == (int64_t)c.d * c.n_exp ? 0 : m->e_lo;
     e.w_a = dn->data; e.w_b = nullptr; e.sh_a = M(m, il, PB_R_SH_DOWN)->data; e.sh_b = nullptr;
     e.rows_e = c.d; e.rows_sh = c.d;
+    e.hq = t > 1 && t <= s->batch && c.ff_exp == c.ff_sh ? s->hq : nullptr;   // several tokens: levels of the hidden vectors made once
     PbCombineParams k; memset(&k, 0, sizeof k);
     k.part = s->part; k.part_sh = s->part_sh; k.logits = s->rlogits; k.t = t; k.d = c.d; k.top_k = c.top_k; k.n_exp = c.n_exp;
     k.y = y; k.ldy = ldy; k.accumulate = accumulate;

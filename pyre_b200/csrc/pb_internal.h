@@ -164,6 +164,7 @@ struct PbExpertParams {
     const uint8_t* w_a; const uint8_t* w_b;   // gate/up: gate_exps, up_exps; down: down_exps, unused
     const uint8_t* sh_a; const uint8_t* sh_b; // shared expert counterparts
     float* h; float* h_sh;                    // hidden [entry][ff], [t][ff_sh]
+    uint32_t* hq;                             // down, several tokens: int8-split hidden vectors [t * top_k + t][pb_xq_words(ff)], else null
     float* part; float* part_sh;              // down: [t][top_k][d], [t][d]
     int rows_e, rows_sh, has_shared, t, top_k, n_exp, e_base;
     int bpr, row_bytes, rows_per_chunk; uint32_t stage_bytes, tab_bytes; int rep;

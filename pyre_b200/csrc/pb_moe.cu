@@ -282,6 +282,21 @@ __device__ __forceinline__ void pb_combine_one(const PbCombineParams& p, int64_t
 
 // ------------------------------------------------------------------------------------ expert down
 
+// Hidden vectors of all (expert, token) entries and of the shared expert -> int8 levels, once, for the
+// down kernel of a multi-token step.  grid = t * top_k + t CTAs (entry slots past the number of local
+// entries return), one warp per four 32-value groups.
+__global__ void __launch_bounds__(128) pb_split_h_kernel(const PbExpertParams p) {
+    pb_pdl_wait();
+    pb_pdl_trigger();
+    const int cols = p.bpr * 256, xw = pb_xq_words(cols), ne = p.t * p.top_k;
+    const int slot = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float* src;
+    if (slot < ne) { if (slot >= p.used_off[*p.n_used]) return; src = p.h + (size_t)slot * cols; }
+    else { if (!p.has_shared) return; src = p.h_sh + (size_t)(slot - ne) * cols; }
+    uint32_t* dst = p.hq + (size_t)slot * xw;
+    for (int g0 = warp * 4; g0 < cols / 32; g0 += 16) pb_split_groups4(*reinterpret_cast<const float4*>(src + 32 * g0 + 4 * lane), lane, g0, cols, dst);
+}
+
 template <int FMT, int PASSES>
 __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const PbExpertParams p, const PbCombineParams cp, unsigned int* ticket) {
     using D = PbQDec<FMT>;
@@ -344,6 +359,34 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
         if (!shared) { s = chunk / cpe; r0 = (chunk - s * cpe) * p.rows_per_chunk; e0 = p.used_off[s]; e1 = p.used_off[s + 1]; }
         else { r0 = (chunk - n_used * cpe) * p.rows_per_chunk; e1 = p.t; }
         const uint32_t base = pb_smem_u32(pb_ring_stage(ring, k));
+        if (p.hq) {
+            // several tokens: the hidden vectors were split by pb_split_h_kernel; decode each row once
+            // and walk the entries of the expert with their levels read from global memory
+            for (int rb = warp * rpw; rb < p.rows_per_chunk; rb += PB_CONSUMERS * rpw) {
+                const int r = rb + sub;
+                PbQuarter wq[PASSES];
+#pragma unroll
+                for (int ps = 0; ps < PASSES; ps++) {
+                    const int qi = ps * 32 + ql;
+                    if (qi < nquarters) D::quarter(base + (uint32_t)r * p.row_bytes + (qi >> 2) * D::STEP_BYTES, qi & 3, T, wq[ps]);
+                }
+                for (int en = e0; en < e1; en++) {
+                    const int tok = shared ? en : p.ent_tok[en];
+                    const uint32_t* xcol = p.hq + (size_t)(shared ? p.t * p.top_k + en : en) * xw;
+                    float acc = 0.f;
+#pragma unroll
+                    for (int ps = 0; ps < PASSES; ps++) {
+                        const int qi = ps * 32 + ql;
+                        if (qi < nquarters) { PbXQuarter xv; pb_load_xquarter(xcol, cols, qi, xv); acc += pb_quarter_dot<FMT>(wq[ps], xv); }
+                    }
+                    for (int o = lpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                    if (ql == 0) {
+                        if (shared) p.part_sh[(size_t)tok * p.rows_e + r0 + r] = acc;
+                        else p.part[((size_t)tok * p.top_k + p.ent_slot[en]) * p.rows_e + r0 + r] = p.ent_w[en] * acc;
+                    }
+                }
+            }
+        } else
         for (int en = e0; en < e1; en++) {
             const int tok = shared ? en : p.ent_tok[en];
             const float* hv = shared ? p.h_sh + (size_t)tok * cols : p.h + (size_t)en * cols;
@@ -429,6 +472,11 @@ static int launch_expert(pb_ctx* ctx, PbExpertParams p, int cols, const PbCombin
     if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "expert kernel needs %zu bytes of shared memory", smem);
     p.status = ctx->dev_status;
     if (DOWN) {
+        if (p.hq) {
+            pb_launch_k(ctx, pb_split_h_kernel, dim3(p.t * p.top_k + p.t), dim3(128), (size_t)0, p);
+            ctx->kernels_launched++;
+            PB_CUDA(ctx, cudaGetLastError());
+        }
         auto kern = pb_expert_down_kernel<FMT, PASSES>;
         static size_t configured = 0;
         if (smem > configured) { PB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = smem; }
