@@ -97,24 +97,18 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
     extern __shared__ float rs[];   // 2048 ints for the routing pass, then scale[t]
     float* scale = rs + 2048;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    __shared__ float red[8];
     pb_pdl_wait();
     pb_pdl_trigger();
-    // per-token RMS scale (rms(): 1 / sqrt(mean(x^2) + eps), qwen4exp_gguf.rs:209)
-    for (int b = 0; b < p.t; b++) {
+    // per-token RMS scale (rms(): 1 / sqrt(mean(x^2) + eps), qwen4exp_gguf.rs:209); one warp per token
+    for (int b = warp; b < p.t; b += 8) {
         float s = 1.0f;
         if (p.norm_w) {
             float ss = 0.f;
-            for (int c = tid * 4; c < p.cols; c += 1024) { const float4 v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + c); ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+            for (int c = lane * 4; c < p.cols; c += 128) { const float4 v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + c); ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
             ss = pb_warp_sum(ss);
-            __syncthreads();
-            if (lane == 0) red[warp] = ss;
-            __syncthreads();
-            float tot = 0.f;
-            for (int i = 0; i < 8; i++) tot += red[i];
-            s = 1.0f / sqrtf(tot / (float)p.cols + p.eps);
+            s = 1.0f / sqrtf(ss / (float)p.cols + p.eps);
         }
-        if (tid == 0) scale[b] = s;
+        if (lane == 0) scale[b] = s;
     }
     __syncthreads();
     const int ng = p.cols / 32;
@@ -132,6 +126,28 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
     const int row = blockIdx.x * 8 + warp;
     if (row <= p.n_exp) {
         const float* wrow = row < p.n_exp ? p.router + (size_t)row * p.cols : p.sh_gate_inp;
+        if (p.cols == 2048 && wrow) {
+            // the row, times the norm weight, stays in registers for all tokens; the token's scale is
+            // applied to the sum (w . (x s n) = s ((w n) . x) up to rounding)
+            float4 wr[16];
+#pragma unroll
+            for (int k = 0; k < 16; k++) {
+                wr[k] = *reinterpret_cast<const float4*>(wrow + lane * 4 + 128 * k);
+                if (p.norm_w) { const float4 n = *reinterpret_cast<const float4*>(p.norm_w + lane * 4 + 128 * k); wr[k].x *= n.x; wr[k].y *= n.y; wr[k].z *= n.z; wr[k].w *= n.w; }
+            }
+#pragma unroll 2
+            for (int b = 0; b < p.t; b++) {
+                const float* xb = p.x + b * p.ldx + lane * 4;
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+                for (int k = 0; k < 16; k++) {
+                    const float4 v = *reinterpret_cast<const float4*>(xb + 128 * k);
+                    a0 = fmaf(wr[k].x, v.x, a0); a1 = fmaf(wr[k].y, v.y, a1); a2 = fmaf(wr[k].z, v.z, a2); a3 = fmaf(wr[k].w, v.w, a3);
+                }
+                const float acc = pb_warp_sum((a0 + a1) + (a2 + a3)) * scale[b];
+                if (lane == 0) p.logits[b * (p.n_exp + 1) + row] = acc;
+            }
+        } else
         for (int b = 0; b < p.t; b++) {
             float acc = 0.f;
             const float s = scale[b];
