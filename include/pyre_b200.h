@@ -153,6 +153,13 @@ int pb_model_destroy(pb_model* m);
 
 /* new_state :1345-1353; `batch` independent sequences decode together. */
 int pb_state_create(pb_model* m, int batch, pb_state** out);
+/* Expert-parallel models only (a plain state otherwise); no counterpart in the reference, which runs
+ * one sequence on one GPU.  `batch` sequences are THIS rank's share of a global batch of
+ * batch * ep_world: attention, DeltaNet, dense layers and the lm-head run on them alone, and every
+ * MoE block all-gathers the residual rows of all ranks, applies the local experts to every token and
+ * reduce-scatters the partial rows to the tokens' owners.  Every rank must step its state the same
+ * number of times (the collectives pair up); tokens are identical to a single-GPU run. */
+int pb_state_create_sharded(pb_model* m, int batch, pb_state** out);
 int pb_state_destroy(pb_state* s);
 /* Pre-fill attention layer `attn_index` of sequence `b` with n positions of already normed and
  * roped K and V rows [n][n_kv*hd] (f32, host); packs per cfg.kv_bits.  Benchmark set-up for a

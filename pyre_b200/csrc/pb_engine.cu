@@ -43,6 +43,10 @@ struct pb_state {
     float *sel_w = nullptr, *ent_w = nullptr, *h = nullptr, *h_sh = nullptr, *part = nullptr, *part_sh = nullptr, *logits = nullptr;
     float *part_ml = nullptr, *part_acc = nullptr;
     int nsplit = 1, nsplit_packed = 0;
+    // sharded tokens (pb_state_create_sharded): this rank's `batch` sequences are tokens [tok0, tok0 + batch) of
+    // moe_t = batch * ep_world; xg = residual rows of all ranks, part_rs = this rank's reduced partial rows
+    bool sharded = false; int moe_t = 0, tok0 = 0;
+    float *xg = nullptr, *part_rs = nullptr;
     int64_t ldproj = 0, ring_cap = 0;
     std::vector<float*> conv, ssm;
     std::vector<PbKv> kv;
@@ -233,7 +237,7 @@ int pb_caps_get(const pb_model* m, pb_caps* caps) {
 
 // ------------------------------------------------------------------------------------ state
 
-int pb_state_create(pb_model* m, int batch, pb_state** out) {
+static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
     if (!m || !out) return PB_ERR_ARG;
     pb_ctx* ctx = m->ctx;
     *out = nullptr;
@@ -244,6 +248,9 @@ int pb_state_create(pb_model* m, int batch, pb_state** out) {
     if (!s) PB_FAIL(ctx, PB_ERR_OOM, "host allocation failed");
     s->m = m; s->batch = batch;
     const int B = batch;
+    s->sharded = sharded && m->ep_world > 1;
+    s->moe_t = s->sharded ? batch * m->ep_world : batch; s->tok0 = s->sharded ? batch * m->ep_rank : 0;
+    const int Bm = s->moe_t;   // tokens every MoE block of this state sees
     const int ch = 2 * c.lin_nk * c.lin_dk + c.lin_nv * c.lin_dv;
     const int64_t lin_proj = (int64_t)ch + (int64_t)c.lin_nv * c.lin_dv + 2 * c.lin_nv;
     const int64_t att_proj = (int64_t)c.n_head * 2 * c.hd + 2 * (int64_t)c.n_kv * c.hd;
@@ -254,13 +261,14 @@ int pb_state_create(pb_model* m, int batch, pb_state** out) {
     A(pos, B); A(ids, B); A(next, B); A(amax, B); A(ticket, 4);
     A(x, (size_t)B * c.d); A(xin, (size_t)B * (wide > c.d ? wide : c.d)); A(yout, (size_t)B * c.d);
     A(proj, (size_t)B * s->ldproj); A(olin, (size_t)B * wide); A(att, (size_t)B * wide);
-    A(rlogits, (size_t)B * (c.n_exp + 1));
-    A(xq, (size_t)B * pb_xq_words(c.d));
-    A(sel_e, (size_t)B * c.top_k); A(sel_w, (size_t)B * c.top_k); A(n_used, 4); A(used_e, c.n_exp + 1); A(used_off, c.n_exp + 2);
-    A(ent_tok, (size_t)B * c.top_k); A(ent_slot, (size_t)B * c.top_k); A(ent_w, (size_t)B * c.top_k);
-    A(h, (size_t)B * c.top_k * c.ff_exp); A(h_sh, (size_t)B * c.ff_sh);
-    A(hq, (size_t)B * (c.top_k + 1) * pb_xq_words(c.ff_exp > c.ff_sh ? c.ff_exp : c.ff_sh));
-    A(part, (size_t)B * c.top_k * c.d); A(part_sh, (size_t)B * c.d);
+    A(rlogits, (size_t)Bm * (c.n_exp + 1));
+    A(xq, (size_t)Bm * pb_xq_words(c.d));
+    A(sel_e, (size_t)Bm * c.top_k); A(sel_w, (size_t)Bm * c.top_k); A(n_used, 4); A(used_e, c.n_exp + 1); A(used_off, c.n_exp + 2);
+    A(ent_tok, (size_t)Bm * c.top_k); A(ent_slot, (size_t)Bm * c.top_k); A(ent_w, (size_t)Bm * c.top_k);
+    A(h, (size_t)Bm * c.top_k * c.ff_exp); A(h_sh, (size_t)Bm * c.ff_sh);
+    A(hq, (size_t)Bm * (c.top_k + 1) * pb_xq_words(c.ff_exp > c.ff_sh ? c.ff_exp : c.ff_sh));
+    A(part, (size_t)Bm * c.top_k * c.d); A(part_sh, (size_t)Bm * c.d);
+    if (s->sharded) { A(xg, (size_t)Bm * c.d); A(part_rs, (size_t)B * c.top_k * c.d); }
     A(logits, (size_t)B * c.vocab);
     s->trace_cap = 4096;
     A(trace, (size_t)s->trace_cap * B); A(trace_len, 2);
@@ -310,6 +318,11 @@ int pb_state_create(pb_model* m, int batch, pb_state** out) {
     *out = s;
     return PB_OK;
 }
+
+int pb_state_create(pb_model* m, int batch, pb_state** out) { return state_create(m, batch, false, out); }
+// Sharded tokens: `batch` is this rank's share of a global batch of batch * ep_world sequences
+// (a plain state when the model is not expert-parallel).
+int pb_state_create_sharded(pb_model* m, int batch, pb_state** out) { return state_create(m, batch, true, out); }
 
 int pb_state_destroy(pb_state* s) {
     if (!s) return PB_OK;
@@ -413,20 +426,29 @@ static int run_attn(pb_state* s, int il, const float* x_in, const float* norm_w,
 // MoE block on t tokens: x_in [t][d] (normalized when norm_w == null) -> y (stored or added)
 static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, int t, float* y, int64_t ldy, int accumulate) {
     pb_model* m = s->m; pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg;
+    // sharded tokens: the block sees the rows of all ranks (tt tokens), this rank owns [tok0, tok0 + t)
+    const bool sh = s->sharded && t == s->batch;
+    const int tt = sh ? s->moe_t : t, tok0 = sh ? s->tok0 : 0;
+    if (s->sharded && !sh) PB_FAIL(ctx, PB_UNSUPPORTED, "a sharded state runs its MoE blocks on whole steps (%d tokens), not on %d", s->batch, t);
+    if (sh) {
+        PB_TRY(pb_ep_allgather(ctx, x_in, s->xg, (size_t)t * c.d));
+        ctx->pdl_chain = false;
+    }
     PbRouterParams r; memset(&r, 0, sizeof r);
-    r.x = x_in; r.ldx = c.d; r.t = t; r.cols = c.d; r.norm_w = norm_w; r.eps = c.eps;
+    r.x = sh ? s->xg : x_in; r.ldx = c.d; r.t = tt; r.cols = c.d; r.norm_w = norm_w; r.eps = c.eps;
     r.router = reinterpret_cast<const float*>(M(m, il, PB_R_ROUTER)->data); r.sh_gate_inp = V(m, il, PB_R_SH_GATE_INP); r.n_exp = c.n_exp;
     r.logits = s->rlogits; r.xq_out = s->xq;
     PbRouteParams q; memset(&q, 0, sizeof q);
-    q.logits = s->rlogits; q.t = t; q.n_exp = c.n_exp; q.top_k = c.top_k; q.e_lo = m->e_lo; q.e_hi = m->e_hi;
+    q.logits = s->rlogits; q.t = tt; q.n_exp = c.n_exp; q.top_k = c.top_k; q.e_lo = m->e_lo; q.e_hi = m->e_hi;
     q.sel_e = s->sel_e; q.sel_w = s->sel_w; q.n_used = s->n_used; q.used_e = s->used_e; q.used_off = s->used_off;
     q.ent_tok = s->ent_tok; q.ent_slot = s->ent_slot; q.ent_w = s->ent_w;
     PB_TRY(pb_launch_router(ctx, r, q, s->ticket));
-    if (m->ep_world > 1) { PB_CUDA(ctx, cudaMemsetAsync(s->part, 0, (size_t)t * c.top_k * c.d * 4, ctx->stream)); ctx->pdl_chain = false; }
+    if (m->ep_world > 1) { PB_CUDA(ctx, cudaMemsetAsync(s->part, 0, (size_t)tt * c.top_k * c.d * 4, ctx->stream)); ctx->pdl_chain = false; }
     PbExpertParams e; memset(&e, 0, sizeof e);
     e.n_used = s->n_used; e.used_e = s->used_e; e.used_off = s->used_off; e.ent_tok = s->ent_tok; e.ent_slot = s->ent_slot; e.ent_w = s->ent_w;
     e.xq = s->xq; e.h = s->h; e.h_sh = s->h_sh; e.part = s->part; e.part_sh = s->part_sh;
-    e.has_shared = 1; e.t = t; e.top_k = c.top_k; e.n_exp = c.n_exp;
+    e.has_shared = 1; e.t = tt; e.top_k = c.top_k; e.n_exp = c.n_exp;
+    e.sh_tok0 = tok0; e.sh_ntok = t;   // the shared expert runs where the token lives
     pb_qmat* g = M(m, il, PB_R_EXP_GATE);
     e.e_base = g->rows == (int64_t)c.ff_exp * c.n_exp ? 0 : m->e_lo;
     e.w_a = g->data; e.w_b = M(m, il, PB_R_EXP_UP)->data; e.sh_a = M(m, il, PB_R_SH_GATE)->data; e.sh_b = M(m, il, PB_R_SH_UP)->data;
@@ -436,16 +458,17 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
     e.e_base = dn->rows == (int64_t)c.d * c.n_exp ? 0 : m->e_lo;
     e.w_a = dn->data; e.w_b = nullptr; e.sh_a = M(m, il, PB_R_SH_DOWN)->data; e.sh_b = nullptr;
     e.rows_e = c.d; e.rows_sh = c.d;
-    e.hq = t > 1 && t <= s->batch && c.ff_exp == c.ff_sh ? s->hq : nullptr;   // several tokens: levels of the hidden vectors made once
+    e.hq = tt > 1 && tt <= s->moe_t && c.ff_exp == c.ff_sh ? s->hq : nullptr;   // several tokens: levels of the hidden vectors made once
     PbCombineParams k; memset(&k, 0, sizeof k);
-    k.part = s->part; k.part_sh = s->part_sh; k.logits = s->rlogits; k.t = t; k.d = c.d; k.top_k = c.top_k; k.n_exp = c.n_exp;
+    k.part = s->part; k.part_sh = s->part_sh + (size_t)tok0 * c.d; k.logits = s->rlogits + (size_t)tok0 * (c.n_exp + 1); k.t = t; k.d = c.d; k.top_k = c.top_k; k.n_exp = c.n_exp;
     k.y = y; k.ldy = ldy; k.accumulate = accumulate;
     // few tokens on one GPU: the down kernel's last CTA also combines (one launch less per layer)
     if (m->ep_world == 1 && (int64_t)t * c.d <= 8192) return pb_launch_expert_down(ctx, e, dn->type, c.ff_exp, &k, s->ticket + 1);
     PB_TRY(pb_launch_expert_down(ctx, e, dn->type, c.ff_exp));
     // expert parallelism: every (token, slot) row was produced on exactly one rank and is zero elsewhere,
     // so the sum is an exact gather and the combine below sees the same bits for every GPU count
-    if (m->ep_world > 1) { PB_TRY(pb_ep_allreduce(ctx, s->part, (size_t)t * c.top_k * c.d)); ctx->pdl_chain = false; }
+    if (sh) { PB_TRY(pb_ep_reduce_scatter(ctx, s->part, s->part_rs, (size_t)t * c.top_k * c.d)); k.part = s->part_rs; ctx->pdl_chain = false; }
+    else if (m->ep_world > 1) { PB_TRY(pb_ep_allreduce(ctx, s->part, (size_t)t * c.top_k * c.d)); ctx->pdl_chain = false; }
     return pb_launch_moe_combine(ctx, k);
 }
 

@@ -7,6 +7,10 @@
 // one exchange per MoE block makes every rank's partial outputs part[token][slot][d] complete.
 // Each (token, slot) element is produced by exactly one rank and is zero on the others, so an
 // all-reduce(sum) is an exact gather: results are bit-identical for every GPU count.
+// A state made with pb_state_create_sharded instead keeps only this rank's sequences (attention,
+// DeltaNet and dense layers run on them alone); its MoE blocks all-gather the residual rows of all
+// ranks, compute the local experts for every token, and reduce-scatter the partial rows back to
+// the tokens' owners -- the same exact sum, 1/N of the dense work per rank.
 #include "pb_internal.h"
 
 #include <dlfcn.h>
@@ -18,11 +22,13 @@ typedef int (*fn_get_id)(pb_nccl_id*);
 typedef int (*fn_init_rank)(pb_nccl_comm*, int, pb_nccl_id, int);
 typedef int (*fn_destroy)(pb_nccl_comm);
 typedef int (*fn_allreduce)(const void*, void*, size_t, int, int, pb_nccl_comm, cudaStream_t);
+typedef int (*fn_allgather)(const void*, void*, size_t, int, pb_nccl_comm, cudaStream_t);
+typedef int (*fn_reducescatter)(const void*, void*, size_t, int, int, pb_nccl_comm, cudaStream_t);
 typedef const char* (*fn_errstr)(int);
 
 static struct {
     void* lib = nullptr;
-    fn_get_id get_id = nullptr; fn_init_rank init_rank = nullptr; fn_destroy destroy = nullptr; fn_allreduce allreduce = nullptr; fn_errstr errstr = nullptr;
+    fn_get_id get_id = nullptr; fn_init_rank init_rank = nullptr; fn_destroy destroy = nullptr; fn_allreduce allreduce = nullptr; fn_allgather allgather = nullptr; fn_reducescatter reducescatter = nullptr; fn_errstr errstr = nullptr;
 } g_nccl;
 
 static int load_nccl(pb_ctx* ctx) {
@@ -35,8 +41,10 @@ static int load_nccl(pb_ctx* ctx) {
     g_nccl.init_rank = (fn_init_rank)dlsym(h, "ncclCommInitRank");
     g_nccl.destroy = (fn_destroy)dlsym(h, "ncclCommDestroy");
     g_nccl.allreduce = (fn_allreduce)dlsym(h, "ncclAllReduce");
+    g_nccl.allgather = (fn_allgather)dlsym(h, "ncclAllGather");
+    g_nccl.reducescatter = (fn_reducescatter)dlsym(h, "ncclReduceScatter");
     g_nccl.errstr = (fn_errstr)dlsym(h, "ncclGetErrorString");
-    if (!g_nccl.get_id || !g_nccl.init_rank || !g_nccl.destroy || !g_nccl.allreduce) PB_FAIL(ctx, PB_UNSUPPORTED, "libnccl.so.2 lacks a required symbol");
+    if (!g_nccl.get_id || !g_nccl.init_rank || !g_nccl.destroy || !g_nccl.allreduce || !g_nccl.allgather || !g_nccl.reducescatter) PB_FAIL(ctx, PB_UNSUPPORTED, "libnccl.so.2 lacks a required symbol");
     g_nccl.lib = h;
     return PB_OK;
 }
@@ -84,5 +92,18 @@ int pb_ep_destroy(pb_ctx* ctx) {
 int pb_ep_allreduce(pb_ctx* ctx, float* buf, size_t n) {
     if (!ctx->ep_comm) PB_FAIL(ctx, PB_ERR_STATE, "expert-parallel model without pb_ep_init");
     PB_NCCL(ctx, g_nccl.allreduce(buf, buf, n, /*ncclFloat32*/ 7, /*ncclSum*/ 0, ctx->ep_comm, ctx->stream));
+    return PB_OK;
+}
+
+// recv[r * n .. (r + 1) * n) = rank r's send[0 .. n), on the context's stream
+int pb_ep_allgather(pb_ctx* ctx, const float* send, float* recv, size_t n) {
+    if (!ctx->ep_comm) PB_FAIL(ctx, PB_ERR_STATE, "expert-parallel model without pb_ep_init");
+    PB_NCCL(ctx, g_nccl.allgather(send, recv, n, /*ncclFloat32*/ 7, ctx->ep_comm, ctx->stream));
+    return PB_OK;
+}
+// recv[0 .. n) = sum over ranks of their send[rank * n .. (rank + 1) * n)
+int pb_ep_reduce_scatter(pb_ctx* ctx, const float* send, float* recv, size_t n) {
+    if (!ctx->ep_comm) PB_FAIL(ctx, PB_ERR_STATE, "expert-parallel model without pb_ep_init");
+    PB_NCCL(ctx, g_nccl.reducescatter(send, recv, n, /*ncclFloat32*/ 7, /*ncclSum*/ 0, ctx->ep_comm, ctx->stream));
     return PB_OK;
 }

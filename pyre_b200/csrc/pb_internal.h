@@ -31,6 +31,8 @@ struct pb_ctx {
     int ep_rank = 0, ep_world = 1;
 };
 int pb_ep_allreduce(pb_ctx* ctx, float* buf, size_t n);
+int pb_ep_allgather(pb_ctx* ctx, const float* send, float* recv, size_t n);
+int pb_ep_reduce_scatter(pb_ctx* ctx, const float* send, float* recv, size_t n);
 
 struct pb_qmat {
     pb_ctx* ctx = nullptr;
@@ -167,6 +169,7 @@ struct PbExpertParams {
     uint32_t* hq;                             // down, several tokens: int8-split hidden vectors [t * top_k + t][pb_xq_words(ff)], else null
     float* part; float* part_sh;              // down: [t][top_k][d], [t][d]
     int rows_e, rows_sh, has_shared, t, top_k, n_exp, e_base;
+    int sh_tok0, sh_ntok;                     // tokens [sh_tok0, sh_tok0 + sh_ntok) get the shared expert here
     int bpr, row_bytes, rows_per_chunk; uint32_t stage_bytes, tab_bytes; int rep;
     int* status;
 };

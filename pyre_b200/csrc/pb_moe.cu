@@ -245,7 +245,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
         const bool shared = chunk >= n_used * cpe;
         int s = 0, r0, e0 = 0, e1;
         if (!shared) { s = chunk / cpe; r0 = (chunk - s * cpe) * p.rows_per_chunk; e0 = p.used_off[s]; e1 = p.used_off[s + 1]; }
-        else { r0 = (chunk - n_used * cpe) * p.rows_per_chunk; e1 = p.t; }
+        else { r0 = (chunk - n_used * cpe) * p.rows_per_chunk; e1 = p.sh_ntok; }
         const uint32_t base = pb_smem_u32(pb_ring_stage(ring, k));
         for (int rb = warp * rpw; rb < p.rows_per_chunk; rb += PB_CONSUMERS * rpw) {
             const int r = rb + sub;
@@ -259,7 +259,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
                 }
             }
             for (int en = e0; en < e1; en++) {
-                const int tok = shared ? en : p.ent_tok[en];
+                const int tok = shared ? p.sh_tok0 + en : p.ent_tok[en];
                 float g = 0.f, u = 0.f;
 #pragma unroll
                 for (int ps = 0; ps < PASSES; ps++) {
@@ -308,7 +308,7 @@ __global__ void __launch_bounds__(128) pb_split_h_kernel(const PbExpertParams p)
     const int slot = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float* src;
     if (slot < ne) { if (slot >= p.used_off[*p.n_used]) return; src = p.h + (size_t)slot * cols; }
-    else { if (!p.has_shared) return; src = p.h_sh + (size_t)(slot - ne) * cols; }
+    else { const int tok = slot - ne; if (!p.has_shared || tok < p.sh_tok0 || tok >= p.sh_tok0 + p.sh_ntok) return; src = p.h_sh + (size_t)tok * cols; }
     uint32_t* dst = p.hq + (size_t)slot * xw;
     for (int g0 = warp * 4; g0 < cols / 32; g0 += 16) pb_split_groups4(*reinterpret_cast<const float4*>(src + 32 * g0 + 4 * lane), lane, g0, cols, dst);
 }
@@ -373,7 +373,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
         const bool shared = chunk >= n_used * cpe;
         int s = 0, r0, e0 = 0, e1;
         if (!shared) { s = chunk / cpe; r0 = (chunk - s * cpe) * p.rows_per_chunk; e0 = p.used_off[s]; e1 = p.used_off[s + 1]; }
-        else { r0 = (chunk - n_used * cpe) * p.rows_per_chunk; e1 = p.t; }
+        else { r0 = (chunk - n_used * cpe) * p.rows_per_chunk; e1 = p.sh_ntok; }
         const uint32_t base = pb_smem_u32(pb_ring_stage(ring, k));
         if (p.hq) {
             // several tokens: the hidden vectors were split by pb_split_h_kernel; decode each row once
@@ -387,8 +387,8 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
                     if (qi < nquarters) D::quarter(base + (uint32_t)r * p.row_bytes + (qi >> 2) * D::STEP_BYTES, qi & 3, T, wq[ps]);
                 }
                 for (int en = e0; en < e1; en++) {
-                    const int tok = shared ? en : p.ent_tok[en];
-                    const uint32_t* xcol = p.hq + (size_t)(shared ? p.t * p.top_k + en : en) * xw;
+                    const int tok = shared ? p.sh_tok0 + en : p.ent_tok[en];
+                    const uint32_t* xcol = p.hq + (size_t)(shared ? p.t * p.top_k + tok : en) * xw;
                     float acc = 0.f;
 #pragma unroll
                     for (int ps = 0; ps < PASSES; ps++) {
@@ -404,7 +404,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
             }
         } else
         for (int en = e0; en < e1; en++) {
-            const int tok = shared ? en : p.ent_tok[en];
+            const int tok = shared ? p.sh_tok0 + en : p.ent_tok[en];
             const float* hv = shared ? p.h_sh + (size_t)tok * cols : p.h + (size_t)en * cols;
             // split this entry's hidden vector into int8 levels (all consumer warps, one group each)
             pb_named_barrier(1, CT);
@@ -475,7 +475,10 @@ static int launch_expert(pb_ctx* ctx, PbExpertParams p, int cols, const PbCombin
     int el, bs;
     pb_geom(FMT, &el, &bs);
     p.row_bytes = cols / el * bs; p.bpr = cols / 256;
-    p.rep = 1;   // a few MB per launch: the plain codebook; see pb_gemvq.cu for the replicated form
+    // a few MB per launch at one or two tokens: the plain codebook; many tokens select most experts
+    // (hundreds of MB), where the per-bank replicated form of pb_gemvq.cu pays for its fill
+    constexpr int entry = pb_tab_entry_bytes<FMT>();
+    p.rep = entry && p.t >= 4 ? 128 / entry : 1;
     p.tab_bytes = pb_tab_bytes<FMT>(p.rep);
     const int lpr = 4 * p.bpr < 32 ? 4 * p.bpr : 32;
     int rpc = PB_CONSUMERS * (32 / lpr);

@@ -34,8 +34,10 @@ class Model:
         self.ctx.check(lib().pb_model_finalize(self.h, C.c_int(ep_rank), C.c_int(ep_world)))
         self.ep_rank, self.ep_world = ep_rank, ep_world
 
-    def new_state(self, batch: int = 1) -> "State":
-        return State(self, batch)
+    def new_state(self, batch: int = 1, sharded: bool = False) -> "State":
+        """sharded=True (expert-parallel models): `batch` sequences are this rank's share of a global
+        batch of batch * world; see pb_state_create_sharded."""
+        return State(self, batch, sharded)
 
     def caps(self) -> Caps:
         c = Caps()
@@ -51,10 +53,11 @@ class Model:
 class State:
     """One conversation per batch slot (State, src/model/qwen4exp_gguf.rs:184-207)."""
 
-    def __init__(self, model: Model, batch: int = 1):
+    def __init__(self, model: Model, batch: int = 1, sharded: bool = False):
         self.model, self.batch, self.ctx = model, batch, model.ctx
         self.h = C.c_void_p()
-        self.ctx.check(lib().pb_state_create(model.h, C.c_int(batch), C.byref(self.h)))
+        create = lib().pb_state_create_sharded if sharded else lib().pb_state_create
+        self.ctx.check(create(model.h, C.c_int(batch), C.byref(self.h)))
 
     # ---- token loop -------------------------------------------------------------------
     def forward(self, ids) -> np.ndarray:

@@ -93,3 +93,65 @@ def gpu_ep_tokens(rank, world, port, out_dir):
         np.save(Path(out_dir) / "single.npy", s1.decode_greedy([5, 600], 40))
         s1.destroy(); m1.destroy(); ctx1.close()
     dist.barrier(); ctx.close(); dist.destroy_process_group()
+
+
+def gpu_sharded_tokens(rank, world, port, out_dir):
+    """NCCL, one GPU per rank, sharded tokens: rank r decodes sequences [2r, 2r+2) of a global batch of
+    2 * world; dense layers see only the local sequences, MoE blocks all-gather / reduce-scatter.  The
+    tokens equal a single-GPU run of the whole batch."""
+    import torch
+    import pyre_b200 as pb
+    from pyre_b200 import parallel, synth
+    from helpers import small_cfg
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist = _init(rank, world, port, "gloo")
+    ctx = pb.Ctx(rank)
+    parallel.init_expert_parallel(ctx, dist, rank, world)
+    cfg = small_cfg(pb, n_layers=8, kv_bits=4, kv_recent=64, max_ctx=256)
+    spec = synth.model_spec(cfg, 3)
+    m = synth.build_model(ctx, cfg, spec, 3, rank, world)
+    first = np.array([5, 600, 77, 1000, 9, 321, 42, 800], np.uint32)[:2 * world]
+    st = m.new_state(2, sharded=True)
+    toks = st.decode_greedy(first[2 * rank:2 * rank + 2], 40)
+    np.save(Path(out_dir) / f"sh{rank}.npy", toks)
+    st.destroy(); m.destroy()
+    if rank == 0:
+        ctx1 = pb.Ctx(0)
+        m1 = synth.build_model(ctx1, cfg, spec, 3)
+        s1 = m1.new_state(2 * world)
+        np.save(Path(out_dir) / "single.npy", s1.decode_greedy(first, 40))
+        s1.destroy(); m1.destroy(); ctx1.close()
+    dist.barrier(); ctx.close(); dist.destroy_process_group()
+
+
+def cpu_sharded_bookkeeping(rank, world, port, out_dir):
+    """gloo, CPU: the exchange of a sharded MoE block -- all-gather of the local rows, per-rank partial
+    rows for the local experts of every token, reduce-scatter to the owners -- returns to every rank
+    exactly the rows a single process computes for its tokens."""
+    import torch
+    from pyre_b200 import parallel
+    dist = _init(rank, world, port, "gloo")
+    t, d, top_k, n_exp = 3, 8, 2, 4
+    rng = np.random.default_rng(11)
+    x_all = rng.standard_normal((world * t, d)).astype(np.float32)           # same on every rank
+    sel = np.stack([np.sort(rng.choice(n_exp, top_k, replace=False)) for _ in range(world * t)])
+    W = rng.standard_normal((n_exp, d, d)).astype(np.float32)
+    ref = np.stack([[W[e] @ x_all[tok] for e in sel[tok]] for tok in range(world * t)]).astype(np.float32)
+    mine = torch.from_numpy(x_all[rank * t:(rank + 1) * t].copy())
+    gathered = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(gathered, mine)
+    xg = torch.cat(gathered).numpy()
+    assert np.array_equal(xg, x_all)
+    lo, hi = parallel.ep_range(n_exp, rank, world)
+    part = np.zeros((world * t, top_k, d), np.float32)
+    for tok in range(world * t):
+        for slot, e in enumerate(sel[tok]):
+            if lo <= e < hi:
+                part[tok, slot] = W[e] @ xg[tok]
+    # gloo has no reduce_scatter: all-reduce, then keep the local slice (the same sum of one row and zeros)
+    full = torch.from_numpy(part.copy()); dist.all_reduce(full); out = full[rank * t:(rank + 1) * t]
+    assert np.array_equal(out.numpy().view(np.uint32), ref[rank * t:(rank + 1) * t].view(np.uint32))
+    if rank == 0:
+        np.save(Path(out_dir) / "ok.npy", np.ones(1))
+    dist.barrier(); dist.destroy_process_group()

@@ -44,3 +44,22 @@ def test_expert_parallel_tokens_identical_two_gpus():
         _spawn(ep_worker.gpu_ep_tokens, 2, d)
         a, b, s = np.load(f"{d}/ep0.npy"), np.load(f"{d}/ep1.npy"), np.load(f"{d}/single.npy")
         assert np.array_equal(a, b) and np.array_equal(a, s)
+
+
+def test_sharded_exchange_world2_gloo():
+    import ep_worker
+    with tempfile.TemporaryDirectory() as d:
+        _spawn(ep_worker.cpu_sharded_bookkeeping, 2, d)
+        assert np.load(f"{d}/ok.npy")[0] == 1
+
+
+@pytest.mark.gpu
+def test_sharded_tokens_identical_two_gpus():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import ep_worker
+    with tempfile.TemporaryDirectory() as d:
+        _spawn(ep_worker.gpu_sharded_tokens, 2, d)
+        a, b, s = np.load(f"{d}/sh0.npy"), np.load(f"{d}/sh1.npy"), np.load(f"{d}/single.npy")
+        assert np.array_equal(np.concatenate([a, b]), s)
