@@ -178,9 +178,11 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(batch, gpus, replicas=False):
+def workload_config(batch, gpus, replicas=False, replicated_ep=False):
     return {"workload": "config 4: Qwen-Next-style 48-layer hybrid decoder, IQ3_S, hidden 2048, 512 experts top-10, vocab 151936, 4-bit KV pre-filled with 32768 positions, greedy decode",
-            "batch": batch, "context": CTX_PREFILL, "residual": "pre-norm (hc=0)", "parallelism": "single GPU" if gpus == 1 else (f"{gpus} independent replicas" if replicas else f"expert-parallel x{gpus} (512/{gpus} experts per GPU, dense weights replicated, one NCCL all-reduce per MoE block)"),
+            "batch": batch, "context": CTX_PREFILL, "residual": "pre-norm (hc=0)", "parallelism": "single GPU" if gpus == 1 else (f"{gpus} independent replicas" if replicas else (
+                f"expert-parallel x{gpus}, replicated tokens (512/{gpus} experts per GPU, every GPU steps all sequences, one NCCL all-reduce per MoE block)" if replicated_ep else
+                f"expert-parallel x{gpus}, sharded tokens ({batch} sequence(s) per GPU, 512/{gpus} experts per GPU, dense weights replicated; per MoE block one NCCL all-gather of the residual rows and one reduce-scatter of the expert outputs)")),
             "l2": "weights touched per step (>1.7 GB) exceed the 126 MB L2; the lm-head roofline launch streams 134 MB"}
 
 
@@ -203,12 +205,13 @@ def run_ours(args):
     t_build = time.time()
     spec = synth.model_spec(cfg, SEED)
     ep = world > 1 and not args.replicas
+    sharded = ep and not args.replicated_ep          # each rank steps its own B sequences; global batch = B * world
     if ep:
         from pyre_b200 import parallel
         import torch.distributed as dist
         parallel.init_expert_parallel(ctx, dist, rank, world, device=torch.device("cuda", local))
     model = synth.build_model(ctx, cfg, spec, SEED, rank if ep else 0, world if ep else 1)
-    st = model.new_state(B)
+    st = model.new_state(B, sharded=sharded)
     n_attn = cfg.n_layers // cfg.full_every
     for ai in range(n_attn):
         st.fill_kv_synth(ai, CTX_PREFILL, SEED + 1)
@@ -284,14 +287,15 @@ def run_ours(args):
     if rank == 0:
         # expert parallelism: all ranks advance the same B sequences together (strong scaling);
         # --replicas: every rank decodes its own B sequences (weak scaling, no collective)
-        value = B * args.steps / (ms / 1e3) * (world if args.replicas else 1)
-        e2e_v = B * args.steps / (ms_e2e / 1e3) * (world if args.replicas else 1)
+        mult = world if (args.replicas or sharded) else 1
+        value = B * args.steps / (ms / 1e3) * mult
+        e2e_v = B * args.steps / (ms_e2e / 1e3) * mult
         step_bytes = stats.weight_bytes_per_step + stats.kv_bytes_per_step + stats.state_bytes_per_step
         peak, which = measured_peaks()
         line = {"metric": "decode_tok_per_s", "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-                "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "weak" if (args.replicas or world == 1) else "strong", "vs_baseline": None, "dtype": "int8 (dp4a: decoded weights x int8-split activations) at batch 1, f16 mma.sync with f16 hi/lo activations for 3+ tokens and attention; f32 accumulate",
-                "data": "synthetic", "config": workload_config(B, world, args.replicas),
-                "e2e": {"value": round(e2e_v, 2), "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B * cfg.vocab, "ms_per_step": round(ms_e2e / args.steps, 4)},
+                "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "weak" if (args.replicas or sharded or world == 1) else "strong", "vs_baseline": None, "dtype": "int8 (dp4a: decoded weights x int8-split activations) at batch 1, f16 mma.sync with f16 hi/lo activations for 3+ tokens and attention; f32 accumulate",
+                "data": "synthetic", "config": workload_config(B, world, args.replicas, args.replicated_ep),
+                "e2e": {"value": round(e2e_v, 2), "unit": "tok/s", "h2d_bytes_per_step": 4 * B * mult, "d2h_bytes_per_step": 4 * B * cfg.vocab * mult, "ms_per_step": round(ms_e2e / args.steps, 4)},
                 "gpu_launches": int(stats.kernels_launched) * args.steps,
                 "roofline": roof,
                 "step_roofline": {"bytes_per_step": int(step_bytes), "weights": int(stats.weight_bytes_per_step), "kv": int(stats.kv_bytes_per_step), "state": int(stats.state_bytes_per_step),
@@ -299,25 +303,31 @@ def run_ours(args):
                 "clocks": clocks, "build_s": round(t_build, 1), "layers": cfg.n_layers}
         if not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(pb, B)
-    # ---- the batch-32 half of the headline metric (single GPU, default run): same model, 32 sequences
-    if world == 1 and B == 1 and not args.no_bs32:
+    # ---- the batch-32 half of the headline metric: 32 sequences in all (32 / N per GPU when sharded)
+    if B == 1 and not args.no_bs32 and (world == 1 or (sharded and 32 % world == 0)):
         st.destroy()
-        B2 = 32
-        st = model.new_state(B2)
+        B2 = 32 // world
+        st = model.new_state(B2, sharded=sharded)
         for ai in range(n_attn):
             st.fill_kv_synth(ai, CTX_PREFILL, SEED + 1)
         st.set_pos(CTX_PREFILL)
-        st.decode_greedy(np.arange(B2, dtype=np.uint32) + 1, 3)
+        st.decode_greedy(np.arange(B2, dtype=np.uint32) + 1 + rank * B2, 3)
         steps2 = max(4, args.steps // 4)
-        torch.cuda.synchronize()
+        barrier()
         b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(stream):
             b0.record(stream)
-            st.decode_greedy(np.arange(B2, dtype=np.uint32) + 7, steps2)
+            st.decode_greedy(np.arange(B2, dtype=np.uint32) + 7 + rank * B2, steps2)
             b1.record(stream)
-        torch.cuda.synchronize()
+        barrier()
         ms2 = b0.elapsed_time(b1)
-        line["batch32"] = {"value": round(B2 * steps2 / (ms2 / 1e3), 2), "unit": "tok/s", "ms_per_step": round(ms2 / steps2, 4), "steps": steps2, "batch": B2, "context": CTX_PREFILL}
+        if world > 1:
+            import torch.distributed as dist
+            t2 = torch.tensor([ms2], device="cuda")
+            dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+            ms2 = float(t2[0])
+        if rank == 0:
+            line["batch32"] = {"value": round(32 * steps2 / (ms2 / 1e3), 2), "unit": "tok/s", "ms_per_step": round(ms2 / steps2, 4), "steps": steps2, "batch": 32, "per_gpu": B2, "context": CTX_PREFILL}
     if rank == 0:
         print(json.dumps(line), flush=True)
     st.destroy(); model.destroy()
@@ -336,6 +346,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-bs32", action="store_true", help="skip the batch-32 leg of the default run")
+    ap.add_argument("--replicated-ep", action="store_true", help="N>1: expert parallelism with every GPU stepping all sequences (all-reduce) instead of sharded tokens")
     ap.add_argument("--replicas", action="store_true", help="N>1: independent replicas instead of expert parallelism")
     args = ap.parse_args()
     if args.impl == "reference":
