@@ -67,9 +67,12 @@ __device__ __forceinline__ float pb_iq3s_quarter_h(uint32_t p, int qt, uint32_t 
     return d;
 }
 
-// byte offset of the 8-byte B-fragment slot of (block blk, entry j, n-tile nt, token-in-tile tq, level lv, quarter q)
+// byte offset of the 8-byte B-fragment slot of (block blk, entry j, n-tile nt, token-in-tile tq, level lv, quarter q).
+// The slots of n-tiles 2p and 2p+1 of one lane are adjacent, so one 128-bit load feeds two mma.
 __device__ __forceinline__ uint32_t pb_xh_off(int blk, int j, int nt, int NT, int tq, int lv, int q) {
-    return (uint32_t)((((blk * 16 + j) * NT + nt) * 32 + ((2 * tq + lv) * 4 + q)) * 8);
+    const int lane = (2 * tq + lv) * 4 + q;
+    if (NT == 1) return (uint32_t)(((blk * 16 + j) * 32 + lane) * 8);
+    return (uint32_t)(((((blk * 16 + j) * (NT / 2) + (nt >> 1)) * 32 + lane) * 2 + (nt & 1)) * 8);
 }
 
 // store 4 consecutive activations (elements c .. c+3, c % 4 == 0) of token b as f16 hi / lo fragments
@@ -254,10 +257,16 @@ __global__ void __launch_bounds__(GH_THREADS, 1) pb_gemmh_iq3s_kernel(const PbGe
             for (int nt = 0; nt < NT; nt++) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
 #pragma unroll
             for (int j = 0; j < 16; j++) {
+                if (NT == 1) {
+                    const uint2 bx = pb_lds64(xh_s + (uint32_t)(((blk * 16 + j) * 32 + lane) * 8));
+                    pb_mma_f16(acc[0], ha[2 * j], hb[2 * j], ha[2 * j + 1], hb[2 * j + 1], bx.x, bx.y);
+                } else {
 #pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    const uint2 bx = pb_lds64(xh_s + (uint32_t)((((blk * 16 + j) * NT + nt) * 32 + lane) * 8));
-                    pb_mma_f16(acc[nt], ha[2 * j], hb[2 * j], ha[2 * j + 1], hb[2 * j + 1], bx.x, bx.y);
+                    for (int np = 0; np < NT / 2; np++) {
+                        const uint4 bx = pb_lds128(xh_s + (uint32_t)((((blk * 16 + j) * (NT / 2) + np) * 32 + lane) * 16));
+                        pb_mma_f16(acc[2 * np], ha[2 * j], hb[2 * j], ha[2 * j + 1], hb[2 * j + 1], bx.x, bx.y);
+                        pb_mma_f16(acc[2 * np + 1], ha[2 * j], hb[2 * j], ha[2 * j + 1], hb[2 * j + 1], bx.z, bx.w);
+                    }
                 }
             }
 #pragma unroll
