@@ -36,8 +36,9 @@ __device__ __forceinline__ void pb_mma_f16(float (&c)[4], uint32_t a0, uint32_t 
 }
 
 // One quarter (64 weights) of an IQ3_S block as 32 half2 words with the sub-block multiplier and
-// the signs applied; returns the block scale d.  tab_h: 512 x 4 f16, sign256 as in pb_qdot.cuh.
-__device__ __forceinline__ float pb_iq3s_quarter_h(uint32_t p, int qt, uint32_t tab_h, uint32_t sign256, uint32_t (&h)[32]) {
+// the signs applied; returns the block scale d.  tab_h: this lane's copy of the f16 codebook (512 x 4 f16,
+// four interleaved copies: entry i of copy c at (4 i + c) * 8 bytes, so lanes of different copies never share a bank).
+__device__ __forceinline__ float pb_iq3s_quarter_h(uint32_t p, int qt, uint32_t tab_h, uint32_t (&h)[32]) {
     const float d = pb_h2f((uint16_t)pb_lds16(p));
     uint32_t qs[4], sg[2];
     pb_ld_u32x<4>(p + 2 + 16 * qt, qs);
@@ -47,16 +48,15 @@ __device__ __forceinline__ float pb_iq3s_quarter_h(uint32_t p, int qt, uint32_t 
     const __half2 m0 = __half2half2(__int2half_rn(1 + 2 * (int)(sc & 0xF))), m1 = __half2half2(__int2half_rn(1 + 2 * (int)(sc >> 4)));
 #pragma unroll
     for (int u = 0; u < 8; u++) {
-        const uint32_t w = qs[u >> 1] >> (16 * (u & 1));
-        const uint32_t h0 = 2 * u < 8 ? (qh << (8 - 2 * u)) : (qh >> (2 * u - 8));
-        const uint32_t h1 = 2 * u + 1 < 8 ? (qh << (7 - 2 * u)) : (qh >> (2 * u - 7));
-        const uint32_t i0 = (w & 0xFF) | (h0 & 0x100), i1 = ((w >> 8) & 0xFF) | (h1 & 0x100);
-        const uint2 g0 = pb_lds64(tab_h + i0 * 8), g1 = pb_lds64(tab_h + i1 * 8);
-        const uint32_t sb = (sg[u >> 2] >> (8 * (u & 3))) & 0xFF;
-        const uint4 m = pb_lds128(sign256 + sb * 16);   // byte masks: x = entry 2u, z = entry 2u+1
-        // byte mask (0xFF per negative weight) -> f16 sign bits of two half2 words
-        const uint32_t s00 = __byte_perm(m.x, 0, 0x1404) & 0x80008000u, s01 = __byte_perm(m.x, 0, 0x3424) & 0x80008000u;
-        const uint32_t s10 = __byte_perm(m.z, 0, 0x1404) & 0x80008000u, s11 = __byte_perm(m.z, 0, 0x3424) & 0x80008000u;
+        const uint32_t hb = pb_spread4((qh >> (4 * (u >> 1))) & 0xF);
+        const uint32_t i0 = (u & 1) ? pb_iq3s_index<2>(qs[u >> 1], hb) : pb_iq3s_index<0>(qs[u >> 1], hb);
+        const uint32_t i1 = (u & 1) ? pb_iq3s_index<3>(qs[u >> 1], hb) : pb_iq3s_index<1>(qs[u >> 1], hb);
+        const uint2 g0 = pb_lds64(tab_h + i0 * 32), g1 = pb_lds64(tab_h + i1 * 32);
+        // f16 sign bits by arithmetic: bit k of a nibble -> 0x80 in byte k, then into bytes 1 and 3 of two words
+        const uint32_t sb = sg[u >> 2] >> (8 * (u & 3));
+        const uint32_t ca = ((sb & 0xF) * 0x10204080u) & 0x80808080u, cb = (((sb >> 4) & 0xF) * 0x10204080u) & 0x80808080u;
+        const uint32_t s00 = __byte_perm(ca, 0, 0x1404), s01 = __byte_perm(ca, 0, 0x3424);
+        const uint32_t s10 = __byte_perm(cb, 0, 0x1404), s11 = __byte_perm(cb, 0, 0x3424);
         const __half2 mm = u < 4 ? m0 : m1;
         __half2 a;
         a = __hmul2(*reinterpret_cast<const __half2*>(&g0.x), mm); h[4 * u + 0] = *reinterpret_cast<uint32_t*>(&a) ^ s00;
@@ -152,9 +152,9 @@ __global__ void __launch_bounds__(GH_THREADS, 1) pb_gemmh_iq3s_kernel(const PbGe
     float* red0 = reinterpret_cast<float*>(smem + 64);            // GH_CONSUMERS floats
     float* xinv = reinterpret_cast<float*>(smem + 128);           // per token: inverse of the power-of-two prescale
     uint64_t* xbar = reinterpret_cast<uint64_t*>(smem + 192);     // completion of the fragment copies
-    uint8_t* tab = smem + 256;                                    // sign table (4 KB) + f16 codebook (4 KB)
+    uint8_t* tab = smem + 256;                                    // f16 codebook, four interleaved copies (16 KB)
     const int cols = p.bpr * 256;
-    uint8_t* xh = tab + 8192;                                     // B fragments: cols * NB * 4 bytes
+    uint8_t* xh = tab + 16384;                                    // B fragments: cols * NB * 4 bytes
     float* red = reinterpret_cast<float*>(xh + (size_t)cols * NB * 4);   // [2][GH_CONSUMERS][16 rows][NB]
     ring.stages = reinterpret_cast<uint8_t*>(red) + 2 * GH_CONSUMERS * GH_ROWS * NB * 4;
     ring.stage_bytes = p.stage_bytes;
@@ -212,20 +212,15 @@ __global__ void __launch_bounds__(GH_THREADS, 1) pb_gemmh_iq3s_kernel(const PbGe
     // ---- consumers: tables ----
     constexpr int CT = GH_CONSUMERS * 32;
     {
-        uint4* sgn = reinterpret_cast<uint4*>(tab);
-        for (int i = tid; i < 256; i += CT) {
-            uint32_t lo = 0, hi = 0;
-            for (int j = 0; j < 4; j++) { if (i & (1 << j)) lo |= 0xFFu << (8 * j); if (i & (16 << j)) hi |= 0xFFu << (8 * j); }
-            sgn[i] = make_uint4(lo, lo & 0x01010101u, hi, hi & 0x01010101u);
-        }
-        uint2* gh = reinterpret_cast<uint2*>(tab + 4096);
+        uint2* gh = reinterpret_cast<uint2*>(tab);
         for (int i = tid; i < 512; i += CT) {
             const uint32_t g = PB_IQ3S_GRID[i];
             const __half2 a = __floats2half2_rn((float)(g & 0xFF), (float)((g >> 8) & 0xFF)), b = __floats2half2_rn((float)((g >> 16) & 0xFF), (float)(g >> 24));
-            gh[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+            const uint2 e = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+            gh[4 * i] = e; gh[4 * i + 1] = e; gh[4 * i + 2] = e; gh[4 * i + 3] = e;
         }
     }
-    const uint32_t sign256 = pb_smem_u32(tab), tab_h = pb_smem_u32(tab + 4096);
+    const uint32_t tab_h = pb_smem_u32(tab) + (lane & 3) * 8;
     if (tid < NB) xinv[tid] = 1.0f;
     pb_named_barrier(2, CT);
     pb_pdl_wait();
@@ -250,8 +245,8 @@ __global__ void __launch_bounds__(GH_THREADS, 1) pb_gemmh_iq3s_kernel(const PbGe
         for (int blk = warp; blk < p.bpr; blk += GH_CONSUMERS) {   // K split: this warp's blocks of the 16 rows
             uint32_t ha[32], hb[32];
             // rows g and g + 8 (rows past the end of the matrix decode stale bytes of the stage; never stored)
-            const float da = pb_iq3s_quarter_h(base + (uint32_t)g * p.row_bytes + blk * 110, q, tab_h, sign256, ha);
-            const float db = pb_iq3s_quarter_h(base + (uint32_t)(g + 8) * p.row_bytes + blk * 110, q, tab_h, sign256, hb);
+            const float da = pb_iq3s_quarter_h(base + (uint32_t)g * p.row_bytes + blk * 110, q, tab_h, ha);
+            const float db = pb_iq3s_quarter_h(base + (uint32_t)(g + 8) * p.row_bytes + blk * 110, q, tab_h, hb);
             float acc[NT][4];
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
@@ -318,7 +313,7 @@ static int launch_h(pb_ctx* ctx, const PbGemvQArgs& a) {
     }
     p.nchunks = nchunks;
     p.stage_bytes = (uint32_t)(((size_t)GH_ROWS * p.row_bytes + 16 + 127) & ~(size_t)127);
-    const size_t smem = 256 + 8192 + (size_t)a.cols * NB * 4 + 2 * GH_CONSUMERS * GH_ROWS * NB * 4 + (size_t)NST * p.stage_bytes;
+    const size_t smem = 256 + 16384 + (size_t)a.cols * NB * 4 + 2 * GH_CONSUMERS * GH_ROWS * NB * 4 + (size_t)NST * p.stage_bytes;
     if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "gemm: %zu bytes of shared memory needed for cols=%d t=%d", smem, a.cols, a.t);
     // fragments of this launch's tokens, made once for all CTAs
     p.xh_in = ctx->xh_buf + 256; p.xinv_in = reinterpret_cast<const float*>(ctx->xh_buf);

@@ -132,6 +132,26 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
         const int r0 = (chunk - p.seg[s].chunk0) * p.rows_per_chunk;
         const int nr = min(p.rows_per_chunk, p.seg[s].rows - r0);
         const uint32_t base = pb_smem_u32(pb_ring_stage(ring, k));
+        if (FMT == PB_T_IQ3_S && NB == 1 && PASSES == 1 && lpr == 32) {
+            // one column, full-width rows: two rows per iteration, so that the two independent decode
+            // chains overlap each other's shared-memory latency (a row past nr decodes stale bytes of the
+            // stage and is not stored)
+            float* ybase = p.y + p.seg[s].yoff + r0;
+            for (int ra = warp; ra < nr; ra += 2 * PB_CONSUMERS) {
+                const int rc = ra + PB_CONSUMERS;
+                const bool two = rc < p.rows_per_chunk;
+                float v0 = pb_iq3s_quarter_dot(base + (uint32_t)ra * (uint32_t)p.row_bytes + (ql >> 2) * D::STEP_BYTES, ql & 3, T, xr[0]);
+                float v1 = pb_iq3s_quarter_dot(base + (uint32_t)(two ? rc : ra) * (uint32_t)p.row_bytes + (ql >> 2) * D::STEP_BYTES, ql & 3, T, xr[0]);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) { v0 += __shfl_xor_sync(0xffffffffu, v0, o); v1 += __shfl_xor_sync(0xffffffffu, v1, o); }
+                if (lane == 0) {
+                    ybase[ra] = p.accumulate ? ybase[ra] + v0 : v0;
+                    if (two && rc < nr) ybase[rc] = p.accumulate ? ybase[rc] + v1 : v1;
+                }
+            }
+            pb_ring_release(ring, k, lane);
+            continue;
+        }
         for (int rb = warp * rpw; rb < nr; rb += PB_CONSUMERS * rpw) {
             const int r = rb + sub;
             const bool valid = r < nr;
@@ -144,6 +164,10 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
                 for (int ps = 0; ps < PASSES; ps++) {
                     const int qi = ps * 32 + ql;
                     if (qi < nquarters) {
+                        if (FMT == PB_T_IQ3_S && NB == 1) {
+                            acc[0] += pb_iq3s_quarter_dot(rowp + (qi >> 2) * D::STEP_BYTES, qi & 3, T, xr[ps]);
+                            continue;
+                        }
                         PbQuarter wq;
                         D::quarter(rowp + (qi >> 2) * D::STEP_BYTES, qi & 3, T, wq);
                         if (NB == 1) {

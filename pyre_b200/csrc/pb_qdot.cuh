@@ -46,6 +46,21 @@ __device__ __forceinline__ void pb_ld_u32x(uint32_t p, uint32_t (&out)[N32]) {
 // (g ^ M) + C : negate the bytes of g selected by the byte mask M (all bytes of g are <= 127)
 __device__ __forceinline__ int pb_apply_sign(uint32_t g, uint32_t m, uint32_t c) { return (int)((g ^ m) + c); }
 
+__device__ __forceinline__ uint32_t pb_prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d; asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel)); return d;
+}
+// bit k of the nibble n -> byte k (0 or 1)
+__device__ __forceinline__ uint32_t pb_spread4(uint32_t n) { return (n * 0x00204081u) & 0x01010101u; }
+// IQ3_S: index of entry J of a group of four = qs byte J | high bit << 8.  hbytes = pb_spread4 of the
+// group's four high bits; prmt zero-fills the upper bytes through its sign-replication mode.
+template <int J> __device__ __forceinline__ uint32_t pb_iq3s_index(uint32_t qs_word, uint32_t hbytes) {
+    constexpr uint32_t sel = (uint32_t)(((12 + J) << 12) | ((12 + J) << 8) | ((4 + J) << 4) | J);
+    return pb_prmt(qs_word, hbytes, sel);
+}
+// IQ3_S grid values are odd (1, 3, .. 15), so xor with 0xFE negates a byte: -g = g ^ 0xFE.
+// c = pb_spread4 of the entry's four sign bits.
+__device__ __forceinline__ int pb_iq3s_sign(uint32_t g, uint32_t c) { return (int)(g ^ (c * 254u)); }
+
 struct PbQuarter {
     int w[16];      // packed signed int8, weight 4k+j of the quarter in byte j of w[k]
     float sc[4];    // scale of weights 16h .. 16h+15
@@ -68,16 +83,13 @@ template <> struct PbQDec<PB_T_IQ3_S> {
         const float d0 = d * (float)(1 + 2 * (int)(sc & 0xF)), d1 = d * (float)(1 + 2 * (int)(sc >> 4));
         o.sc[0] = o.sc[1] = d0; o.sc[2] = o.sc[3] = d1;
 #pragma unroll
-        for (int u = 0; u < 8; u++) {          // unit u = entries 2u, 2u+1 and one sign byte
-            const uint32_t w = qs[u >> 1] >> (16 * (u & 1));
-            const uint32_t h0 = 2 * u < 8 ? (qh << (8 - 2 * u)) : (qh >> (2 * u - 8));
-            const uint32_t h1 = 2 * u + 1 < 8 ? (qh << (7 - 2 * u)) : (qh >> (2 * u - 7));
-            const uint32_t i0 = (w & 0xFF) | (h0 & 0x100), i1 = ((w >> 8) & 0xFF) | (h1 & 0x100);
-            const uint32_t g0 = pb_lds32(T.grid + i0 * T.stride), g1 = pb_lds32(T.grid + i1 * T.stride);
-            const uint32_t sb = (sg[u >> 2] >> (8 * (u & 3))) & 0xFF;
-            const uint4 m = pb_lds128(T.sign256 + sb * 16);
-            o.w[2 * u] = pb_apply_sign(g0, m.x, m.y);
-            o.w[2 * u + 1] = pb_apply_sign(g1, m.z, m.w);
+        for (int k = 0; k < 4; k++) {          // four entries: one qs word, four high bits, two sign bytes
+            const uint32_t hb = pb_spread4((qh >> (4 * k)) & 0xF);
+            const uint32_t sw = sg[k >> 1] >> (16 * (k & 1));
+            o.w[4 * k + 0] = pb_iq3s_sign(pb_lds32(T.grid + pb_iq3s_index<0>(qs[k], hb) * T.stride), pb_spread4(sw & 0xF));
+            o.w[4 * k + 1] = pb_iq3s_sign(pb_lds32(T.grid + pb_iq3s_index<1>(qs[k], hb) * T.stride), pb_spread4((sw >> 4) & 0xF));
+            o.w[4 * k + 2] = pb_iq3s_sign(pb_lds32(T.grid + pb_iq3s_index<2>(qs[k], hb) * T.stride), pb_spread4((sw >> 8) & 0xF));
+            o.w[4 * k + 3] = pb_iq3s_sign(pb_lds32(T.grid + pb_iq3s_index<3>(qs[k], hb) * T.stride), pb_spread4((sw >> 12) & 0xF));
         }
     }
 };
@@ -181,5 +193,53 @@ __device__ __forceinline__ float pb_quarter_dot(const PbQuarter& w, const PbXQua
         acc = fmaf(w.sc[h * (4 / NH)], t, acc);
     }
     if (D::HAS_MIN) { acc = fmaf(-w.mn[0], x.sum[0], acc); acc = fmaf(-w.mn[1], x.sum[1], acc); }
+    return acc;
+}
+
+// ---- fused decode + dot for IQ3_S (one column) --------------------------------------------------------
+// Same arithmetic as PbQDec<IQ3_S>::quarter followed by pb_quarter_dot, written so that each codebook
+// entry costs one byte-permute (index = qs byte | high bit << 8), one multiply-add (address) and one
+// load: the eight high bits of a 32-weight half are first spread into bytes with a multiply
+// (n * 0x00204081 & 0x01010101 puts bit k of n into byte k), then prmt picks (qs byte, high byte)
+// and zero-fills the rest through its sign-replication mode.  Integer sums go straight into the
+// per-group accumulators; no decoded quarter is kept.
+__device__ __forceinline__ float pb_iq3s_quarter_dot(uint32_t p, int qt, const PbQTabs& T, const PbXQuarter& x) {
+    const float d = pb_h2f((uint16_t)pb_lds16(p));
+    uint32_t qs[4], sg[2];
+    pb_ld_u32x<4>(p + 2 + 16 * qt, qs);
+    pb_ld_u32x<2>(p + 74 + 8 * qt, sg);
+    const uint32_t qh = pb_lds16(p + 66 + 2 * qt);
+    const uint32_t sc = pb_lds8(p + 106 + qt);
+    float acc = 0.f;
+#pragma unroll
+    for (int h = 0; h < 2; h++) {                 // 32 weights = 8 entries = 4 sign bytes
+        int isum[PB_XLEVELS];
+#pragma unroll
+        for (int l = 0; l < PB_XLEVELS; l++) isum[l] = 0;
+#pragma unroll
+        for (int k = 0; k < 2; k++) {             // 4 entries share one qs word and one spread of high bits
+            const uint32_t word = qs[2 * h + k];
+            const uint32_t hb = pb_spread4((qh >> (8 * h + 4 * k)) & 0xF);
+            const uint32_t i0 = pb_iq3s_index<0>(word, hb), i1 = pb_iq3s_index<1>(word, hb), i2 = pb_iq3s_index<2>(word, hb), i3 = pb_iq3s_index<3>(word, hb);
+            const uint32_t g0 = pb_lds32(T.grid + i0 * T.stride), g1 = pb_lds32(T.grid + i1 * T.stride);
+            const uint32_t g2 = pb_lds32(T.grid + i2 * T.stride), g3 = pb_lds32(T.grid + i3 * T.stride);
+            // signs by arithmetic: shared-memory wavefronts, not issue slots, bound this loop when the
+            // masks came from a table
+            const uint32_t sw = sg[h] >> (16 * k);
+            const int w0 = pb_iq3s_sign(g0, pb_spread4(sw & 0xF)), w1 = pb_iq3s_sign(g1, pb_spread4((sw >> 4) & 0xF));
+            const int w2 = pb_iq3s_sign(g2, pb_spread4((sw >> 8) & 0xF)), w3 = pb_iq3s_sign(g3, pb_spread4((sw >> 12) & 0xF));
+            const int e = 8 * h + 4 * k;
+#pragma unroll
+            for (int l = 0; l < PB_XLEVELS; l++) {
+                isum[l] = __dp4a(w0, x.q[l][e], isum[l]); isum[l] = __dp4a(w1, x.q[l][e + 1], isum[l]);
+                isum[l] = __dp4a(w2, x.q[l][e + 2], isum[l]); isum[l] = __dp4a(w3, x.q[l][e + 3], isum[l]);
+            }
+        }
+        float t = x.s[PB_XLEVELS - 1][h] * (float)isum[PB_XLEVELS - 1];   // smallest level first, as pb_quarter_dot
+#pragma unroll
+        for (int l = PB_XLEVELS - 2; l >= 0; l--) t = fmaf(x.s[l][h], (float)isum[l], t);
+        const float db = d * (float)(1 + 2 * (int)((sc >> (4 * h)) & 0xF));
+        acc = fmaf(db, t, acc);
+    }
     return acc;
 }
