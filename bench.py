@@ -37,6 +37,10 @@ CTX_PREFILL = 32768
 SEED = 0
 
 
+# DRAM bytes of one lm-head launch measured by ncu (133.78 MB read + 3.54 MB written)
+LMHEAD_DRAM_TRAFFIC = 137324032
+
+
 def full_cfg(pb, batch_room=1280, n_layers=48):
     return pb.make_cfg(n_layers=n_layers, d=2048, n_head=16, n_kv=2, hd=256, n_rot=64, rope_base=1e7, eps=1e-6,
                        n_exp=512, top_k=10, ff_exp=512, ff_sh=512, lin_nk=16, lin_nv=32, lin_dk=128, lin_dv=128,
@@ -57,9 +61,25 @@ class ClockSampler:
     Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
     def __init__(self, device: int):
-        self.device, self.rows, self.proc = device, [], None
+        self.device, self.rows, self.proc, self.nvml, self.stop_flag = device, [], None, None, False
 
     def start(self):
+        # NVML polled from a thread every 20 ms (read-only queries); nvidia-smi -lms as the fallback
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.device)
+            try:
+                import torch
+                uuid = str(torch.cuda.get_device_properties(self.device).uuid)
+                h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+            except Exception:
+                pass
+            self.nvml = (pynvml, h)
+            threading.Thread(target=self._poll, daemon=True).start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.device)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -67,11 +87,29 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
+    def _poll(self):
+        pynvml, h = self.nvml
+        names = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
+        while not self.stop_flag:
+            try:
+                sm = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+                mx = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+                try:
+                    bits = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except Exception:
+                    bits = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                row = ["", str(sm), str(mx), "", ""] + ["Active" if bits & b else "Not Active" for _, b in names]
+                self.rows.append(row)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
     def _pump(self):
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
+        self.stop_flag = True
         if self.proc:
             self.proc.terminate()
         sm = [float(r[1]) for r in self.rows if len(r) > 8 and r[1].replace(".", "").isdigit()]
@@ -281,7 +319,7 @@ def run_ours(args):
         alg = W.nbytes() + 4 * (cfg.d + cfg.vocab)
         ach = alg / us / 1e3
         roof = {"bound": "hbm", "kernel": "pb_gemvq_kernel<IQ3_S> lm-head 151936x2048", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 4),
-                "peak_source": which, "traffic": None, "us_per_launch": round(us, 2), "algorithmic_bytes": alg}
+                "peak_source": which, "traffic": LMHEAD_DRAM_TRAFFIC, "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this launch (profiles/gemvq_iq3s_lmhead.md)", "us_per_launch": round(us, 2), "algorithmic_bytes": alg}
         W.free()
 
     if rank == 0:
