@@ -60,6 +60,34 @@ def test_batch_sequences_are_independent(ctx):
     stb.destroy(); m.destroy()
 
 
+def test_large_batch_matches_single_sequences(ctx):
+    """20 sequences with a 4-bit KV cache (tensor-core GEMM tiles of 16 + 4 tokens, pre-split expert hidden
+    vectors, fine attention splits) produce the tokens of single-sequence runs."""
+    cfg = small_cfg(pb, n_layers=8, kv_bits=4, kv_recent=64, max_ctx=256)
+    spec = synth.model_spec(cfg, 4)
+    m = synth.build_model(ctx, cfg, spec, 4)
+    rng = np.random.default_rng(12)
+    k = rng.standard_normal((150, cfg.n_kv * cfg.hd)).astype(np.float32); v = rng.standard_normal((150, cfg.n_kv * cfg.hd)).astype(np.float32)
+    firsts = [(37 * i + 5) % cfg.vocab for i in range(20)]
+
+    def prefilled(batch):
+        st = m.new_state(batch)
+        for b in range(batch):
+            for ai in range(cfg.n_layers // cfg.full_every):
+                st.fill_kv(b, ai, k, v)
+        st.set_pos(150)
+        return st
+
+    stb = prefilled(20)
+    outb = stb.decode_greedy(firsts, 16)
+    for i in (0, 7, 19):
+        s1 = prefilled(1)
+        assert s1.decode_greedy([firsts[i]], 16)[0].tolist() == outb[i].tolist(), i
+        s1.destroy()
+    assert ctx.device_status() == 0
+    stb.destroy(); m.destroy()
+
+
 def test_context_limit_and_bad_calls(ctx):
     cfg = small_cfg(pb, n_layers=4, max_ctx=8)
     spec = synth.model_spec(cfg, 0)
