@@ -172,7 +172,8 @@ int pb_state_pos(const pb_state* s, int64_t* pos);
 
 /* Model::forward(ids, st) -> logits, src/model/qwen4exp_gguf.rs:2050-2157 (= spec::Target::step,
  * src/spec.rs:106-120, QnTarget::step src/engine_qn.rs:247).  ids_host [batch][t]; the logits of
- * the last fed token of each sequence go to logits_host [batch][vocab]. */
+ * the last fed token of each sequence go to logits_host [batch][vocab].  A prompt (t >= 3) of a
+ * batch-1 state runs in windows of up to 8 tokens that stream every weight matrix once per window. */
 int pb_forward(pb_state* s, const uint32_t* ids_host, int t, float* logits_host);
 /* forward + sampler::argmax (src/sampler.rs:142-148) on the device: next_host [batch]. */
 int pb_step_greedy(pb_state* s, const uint32_t* tok_host, uint32_t* next_host);
@@ -181,7 +182,9 @@ int pb_step_greedy(pb_state* s, const uint32_t* tok_host, uint32_t* next_host);
 int pb_decode_greedy(pb_state* s, const uint32_t* tok_host, int n, uint32_t* out_host);
 
 /* Model::forward_multi :2365-2480 (= Target::verify): logits for every fed position,
- * logits_host [t][vocab]; records per-position rollback checkpoints.  batch must be 1. */
+ * logits_host [t][vocab]; records per-position rollback checkpoints.  batch must be 1, t <= 8.
+ * One batched pass: weights are streamed once for all t tokens (tensor cores from 3 tokens on), the
+ * recurrences run token by token; agrees with t calls of pb_forward to rounding, not bit for bit. */
 int pb_verify(pb_state* s, const uint32_t* ids_host, int t, float* logits_host);
 /* Model::spec_keep :2495-2515 (= Target::keep): keep the first `keep` of the last t verified tokens. */
 int pb_keep(pb_state* s, int t, int keep);

@@ -14,6 +14,10 @@
 #include <new>
 #include <vector>
 
+#define PB_MAX_WINDOW 8   // draft windows of the reference are at most 8 tokens (src/spec.rs:185)
+static size_t conv_elems(const pb_cfg& c, int B) { return (size_t)B * c.conv_k * (2 * c.lin_nk * c.lin_dk + c.lin_nv * c.lin_dv); }
+static size_t ssm_elems(const pb_cfg& c, int B) { return (size_t)B * c.lin_nv * c.lin_dk * c.lin_dv; }
+
 struct PbSlot { pb_qmat* mat = nullptr; float* vec = nullptr; int64_t nvec = 0; };
 
 struct pb_model {
@@ -46,6 +50,10 @@ struct pb_state {
     // sharded tokens (pb_state_create_sharded): this rank's `batch` sequences are tokens [tok0, tok0 + batch) of
     // moe_t = batch * ep_world; xg = residual rows of all ranks, part_rs = this rank's reduced partial rows
     bool sharded = false; int moe_t = 0, tok0 = 0;
+    // window mode (batch 1): win_t > 0 while a window of consecutive tokens of the one sequence runs through
+    // the layers as columns; wpos[j] = position of column j; win_ckpt = keep DeltaNet checkpoints
+    int win_t = 0; bool win_ckpt = false; int64_t* wpos = nullptr;
+    int moe_cap = 0;   // rows of the MoE work buffers
     float *xg = nullptr, *part_rs = nullptr;
     int64_t ldproj = 0, ring_cap = 0;
     std::vector<float*> conv, ssm;
@@ -250,7 +258,9 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
     const int B = batch;
     s->sharded = sharded && m->ep_world > 1;
     s->moe_t = s->sharded ? batch * m->ep_world : batch; s->tok0 = s->sharded ? batch * m->ep_rank : 0;
-    const int Bm = s->moe_t;   // tokens every MoE block of this state sees
+    const int Ba = (B == 1 && !s->sharded) ? PB_MAX_WINDOW : B;   // activation rows: a batch-1 state also runs windows of up to 8 tokens
+    const int Bm = s->moe_t > Ba ? s->moe_t : Ba;                 // tokens a MoE block of this state may see
+    s->moe_cap = Bm;
     const int ch = 2 * c.lin_nk * c.lin_dk + c.lin_nv * c.lin_dv;
     const int64_t lin_proj = (int64_t)ch + (int64_t)c.lin_nv * c.lin_dv + 2 * c.lin_nv;
     const int64_t att_proj = (int64_t)c.n_head * 2 * c.hd + 2 * (int64_t)c.n_kv * c.hd;
@@ -258,9 +268,9 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
     const int64_t wide = (int64_t)c.lin_nv * c.lin_dv > (int64_t)c.n_head * c.hd ? (int64_t)c.lin_nv * c.lin_dv : (int64_t)c.n_head * c.hd;
     int rc = PB_OK;
 #define A(p, n) if (rc == PB_OK) rc = dalloc(s, &s->p, (size_t)(n))
-    A(pos, B); A(ids, B); A(next, B); A(amax, B); A(ticket, 4);
-    A(x, (size_t)B * c.d); A(xin, (size_t)B * (wide > c.d ? wide : c.d)); A(yout, (size_t)B * c.d);
-    A(proj, (size_t)B * s->ldproj); A(olin, (size_t)B * wide); A(att, (size_t)B * wide);
+    A(pos, B); A(ids, Ba); A(next, Ba); A(amax, Ba); A(ticket, 4); A(wpos, PB_MAX_WINDOW);
+    A(x, (size_t)Ba * c.d); A(xin, (size_t)Ba * (wide > c.d ? wide : c.d)); A(yout, (size_t)Ba * c.d);
+    A(proj, (size_t)Ba * s->ldproj); A(olin, (size_t)Ba * wide); A(att, (size_t)Ba * wide);
     A(rlogits, (size_t)Bm * (c.n_exp + 1));
     A(xq, (size_t)Bm * pb_xq_words(c.d));
     A(sel_e, (size_t)Bm * c.top_k); A(sel_w, (size_t)Bm * c.top_k); A(n_used, 4); A(used_e, c.n_exp + 1); A(used_off, c.n_exp + 2);
@@ -269,7 +279,7 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
     A(hq, (size_t)Bm * (c.top_k + 1) * pb_xq_words(c.ff_exp > c.ff_sh ? c.ff_exp : c.ff_sh));
     A(part, (size_t)Bm * c.top_k * c.d); A(part_sh, (size_t)Bm * c.d);
     if (s->sharded) { A(xg, (size_t)Bm * c.d); A(part_rs, (size_t)B * c.top_k * c.d); }
-    A(logits, (size_t)B * c.vocab);
+    A(logits, (size_t)Ba * c.vocab);
     s->trace_cap = 4096;
     A(trace, (size_t)s->trace_cap * B); A(trace_len, 2);
     // attention: one CTA per SM (split x KV head x sequence)
@@ -371,16 +381,28 @@ static int run_lin(pb_state* s, int il, const float* x_in, const float* norm_w, 
     a.type = M(m, il, PB_R_LIN_QKV)->type; a.cols = c.d; a.nseg = 4;
     seg(a, 0, M(m, il, PB_R_LIN_QKV), 0); seg(a, 1, M(m, il, PB_R_LIN_Z), ch); seg(a, 2, M(m, il, PB_R_LIN_BETA), ch + w); seg(a, 3, M(m, il, PB_R_LIN_ALPHA), ch + w + c.lin_nv);
     a.x = x_in; a.ldx = c.d; a.y = s->proj; a.ldy = s->ldproj; a.mode = norm_w ? PB_ACT_NORM : PB_ACT_PLAIN; a.norm_w = norm_w; a.eps = c.eps;
-    PB_TRY(gemv_cols(ctx, a, B));
+    const int ncol = s->win_t > 0 ? s->win_t : B;   // window mode: the columns are consecutive tokens of sequence 0
+    PB_TRY(gemv_cols(ctx, a, ncol));
     PbDeltaParams d; memset(&d, 0, sizeof d);
     d.proj = s->proj; d.ldp = s->ldproj; d.conv_w = V(m, il, PB_R_LIN_CONV); d.a = V(m, il, PB_R_LIN_A); d.dt = V(m, il, PB_R_LIN_DT);
     d.conv = s->conv[li]; d.ssm = s->ssm[li]; d.pos = s->pos; d.out = s->olin; d.ldo = w;
     d.nk = c.lin_nk; d.nv = c.lin_nv; d.dk = c.lin_dk; d.dv = c.lin_dv; d.conv_k = c.conv_k; d.batch = B;
-    PB_TRY(pb_launch_deltanet(ctx, d));
+    if (s->win_t > 0) {
+        // the recurrence is sequential: one launch per token, with a rollback checkpoint after each but the last
+        for (int j = 0; j < s->win_t; j++) {
+            d.proj = s->proj + (size_t)j * s->ldproj; d.out = s->olin + (size_t)j * w; d.pos = s->wpos + j; d.batch = 1;
+            PB_TRY(pb_launch_deltanet(ctx, d));
+            if (s->win_ckpt && j + 1 < s->win_t) {
+                PB_CUDA(ctx, cudaMemcpyAsync(s->ck_conv[(size_t)li * PB_MAX_WINDOW + j], s->conv[li], conv_elems(c, 1) * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+                PB_CUDA(ctx, cudaMemcpyAsync(s->ck_ssm[(size_t)li * PB_MAX_WINDOW + j], s->ssm[li], ssm_elems(c, 1) * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+                ctx->pdl_chain = false;
+            }
+        }
+    } else PB_TRY(pb_launch_deltanet(ctx, d));
     PbGemvQArgs o; memset(&o, 0, sizeof o);
     o.type = M(m, il, PB_R_LIN_OUT)->type; o.cols = w; o.nseg = 1; seg(o, 0, M(m, il, PB_R_LIN_OUT), 0);
     o.x = s->olin; o.ldx = w; o.y = y; o.ldy = ldy; o.mode = PB_ACT_GNORM; o.norm_w = V(m, il, PB_R_LIN_NORM); o.z = s->proj + ch; o.ldz = s->ldproj; o.head_dim = c.lin_dv; o.eps = c.eps; o.accumulate = accumulate;
-    return gemv_cols(ctx, o, B);
+    return gemv_cols(ctx, o, ncol);
 }
 
 static void attn_params(pb_state* s, int il, PbAttnParams& p) {
@@ -413,14 +435,24 @@ static int run_attn(pb_state* s, int il, const float* x_in, const float* norm_w,
     a.type = M(m, il, PB_R_ATTN_Q)->type; a.cols = c.d; a.nseg = 3;
     seg(a, 0, M(m, il, PB_R_ATTN_Q), 0); seg(a, 1, M(m, il, PB_R_ATTN_K), nq); seg(a, 2, M(m, il, PB_R_ATTN_V), nq + row);
     a.x = x_in; a.ldx = c.d; a.y = s->proj; a.ldy = s->ldproj; a.mode = norm_w ? PB_ACT_NORM : PB_ACT_PLAIN; a.norm_w = norm_w; a.eps = c.eps;
-    PB_TRY(gemv_cols(ctx, a, B));
+    const int ncol = s->win_t > 0 ? s->win_t : B;
+    PB_TRY(gemv_cols(ctx, a, ncol));
     PbAttnParams p; attn_params(s, il, p);
-    PB_TRY(pb_launch_kv_append(ctx, p));
-    PB_TRY(pb_launch_attn(ctx, p));
+    if (s->win_t > 0) {
+        // causal inside the window: token j is appended, then attends to positions <= its own
+        for (int j = 0; j < s->win_t; j++) {
+            p.proj = s->proj + (size_t)j * s->ldproj; p.pos = s->wpos + j; p.att = s->att + (size_t)j * p.lda; p.batch = 1;
+            PB_TRY(pb_launch_kv_append(ctx, p));
+            PB_TRY(pb_launch_attn(ctx, p));
+        }
+    } else {
+        PB_TRY(pb_launch_kv_append(ctx, p));
+        PB_TRY(pb_launch_attn(ctx, p));
+    }
     PbGemvQArgs o; memset(&o, 0, sizeof o);
     o.type = M(m, il, PB_R_ATTN_O)->type; o.cols = c.n_head * c.hd; o.nseg = 1; seg(o, 0, M(m, il, PB_R_ATTN_O), 0);
     o.x = s->att; o.ldx = (int64_t)c.n_head * c.hd; o.y = y; o.ldy = ldy; o.mode = PB_ACT_PLAIN; o.accumulate = accumulate;
-    return gemv_cols(ctx, o, B);
+    return gemv_cols(ctx, o, ncol);
 }
 
 // MoE block on t tokens: x_in [t][d] (normalized when norm_w == null) -> y (stored or added)
@@ -458,7 +490,8 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
     e.e_base = dn->rows == (int64_t)c.d * c.n_exp ? 0 : m->e_lo;
     e.w_a = dn->data; e.w_b = nullptr; e.sh_a = M(m, il, PB_R_SH_DOWN)->data; e.sh_b = nullptr;
     e.rows_e = c.d; e.rows_sh = c.d;
-    e.hq = tt > 1 && tt <= s->moe_t && c.ff_exp == c.ff_sh ? s->hq : nullptr;   // several tokens: levels of the hidden vectors made once
+    if (tt > s->moe_cap) PB_FAIL(ctx, PB_ERR_ARG, "MoE block on %d tokens, buffers hold %d", tt, s->moe_cap);
+    e.hq = tt > 1 && c.ff_exp == c.ff_sh ? s->hq : nullptr;   // several tokens: levels of the hidden vectors made once
     PbCombineParams k; memset(&k, 0, sizeof k);
     k.part = s->part; k.part_sh = s->part_sh + (size_t)tok0 * c.d; k.logits = s->rlogits + (size_t)tok0 * (c.n_exp + 1); k.t = t; k.d = c.d; k.top_k = c.top_k; k.n_exp = c.n_exp;
     k.y = y; k.ldy = ldy; k.accumulate = accumulate;
@@ -490,6 +523,33 @@ static int run_step(pb_state* s) {
     PB_TRY(gemv_cols(ctx, a, B));
     PB_TRY(pb_launch_argmax(ctx, s->logits, c.vocab, c.vocab, B, s->amax));
     return pb_launch_advance(ctx, s->pos, B, s->amax, s->next, s->ids, s->trace, s->trace_len, s->trace_cap);
+}
+
+// A window of t consecutive tokens of the one sequence of a batch-1 state (ids already in s->ids[0..t)):
+// every weight matrix is streamed once for all t tokens (tensor-core GEMM from 3 tokens on); only the
+// recurrences (DeltaNet state, KV append + attention) run token by token.  Logits of all positions go to
+// s->logits [t][vocab] when all_logits, else only the last position's to row 0.  Model::forward_multi,
+// src/model/qwen4exp_gguf.rs:2365-2480.
+static int run_window(pb_state* s, int t, bool ckpt, bool all_logits) {
+    pb_model* m = s->m; pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg;
+    struct Scope { pb_ctx* c; pb_state* s; Scope(pb_ctx* x, pb_state* y, int t, bool k) : c(x), s(y) { c->pdl_scope++; c->pdl_chain = false; s->win_t = t; s->win_ckpt = k; }
+                   ~Scope() { c->pdl_scope--; c->pdl_chain = false; s->win_t = 0; s->win_ckpt = false; } } scope(ctx, s, t, ckpt);
+    PB_TRY(pb_launch_window_pos(ctx, s->pos, s->wpos, t, 0));
+    pb_qmat* embd = M(m, -1, PB_R_TOKEN_EMBD);
+    PB_TRY(pb_launch_embed(ctx, embd->type, embd->data, embd->rows, c.d, s->ids, t, s->x, c.d));
+    for (int il = 0; il < c.n_layers; il++) {
+        if (m->kind[il]) PB_TRY(run_attn(s, il, s->x, V(m, il, PB_R_ATTN_NORM), s->x, c.d, 1));
+        else PB_TRY(run_lin(s, il, s->x, V(m, il, PB_R_ATTN_NORM), s->x, c.d, 1));
+        PB_TRY(run_moe(s, il, s->x, V(m, il, PB_R_FFN_NORM), t, s->x, c.d, 1));
+    }
+    pb_qmat* out = M(m, -1, PB_R_OUTPUT) ? M(m, -1, PB_R_OUTPUT) : embd;
+    PbGemvQArgs a; memset(&a, 0, sizeof a);
+    a.type = out->type; a.cols = c.d; a.nseg = 1; seg(a, 0, out, 0);
+    a.x = all_logits ? s->x : s->x + (size_t)(t - 1) * c.d; a.ldx = c.d; a.y = s->logits; a.ldy = c.vocab; a.mode = PB_ACT_NORM; a.norm_w = V(m, -1, PB_R_OUT_NORM); a.eps = c.eps;
+    PB_TRY(gemv_cols(ctx, a, all_logits ? t : 1));
+    PB_TRY(pb_launch_window_pos(ctx, s->pos, s->wpos, t, 1));   // position += t
+    s->pos_host += t;
+    return PB_OK;
 }
 
 // Replays the step graph (captured on first use after one eager warm-up step would be wasteful:
@@ -528,6 +588,20 @@ int pb_forward(pb_state* s, const uint32_t* ids_host, int t, float* logits_host)
     pb_ctx* ctx = s->m->ctx;
     if (!ids_host || !logits_host || t < 1) PB_FAIL(ctx, PB_ERR_ARG, "pb_forward: bad argument");
     const int B = s->batch;
+    if (B == 1 && !s->sharded && t >= 3) {
+        // a prompt of one sequence: windows of up to 8 tokens, each streaming the weights once
+        if (s->pos_host + t > s->m->cfg.max_ctx) PB_FAIL(ctx, PB_ERR_STATE, "context is full (%d positions)", s->m->cfg.max_ctx);
+        for (int j0 = 0; j0 < t; j0 += PB_MAX_WINDOW) {
+            const int n = t - j0 < PB_MAX_WINDOW ? t - j0 : PB_MAX_WINDOW;
+            for (int j = 0; j < n; j++) s->pin_u32[j] = ids_host[j0 + j];
+            PB_CUDA(ctx, cudaMemcpyAsync(s->ids, s->pin_u32, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
+            PB_TRY(run_window(s, n, false, false));
+            if (j0 + n < t) PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // the pinned id buffer is reused
+        }
+        s->verify_t = 0;
+        PB_CUDA(ctx, cudaMemcpyAsync(logits_host, s->logits, (size_t)s->m->cfg.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        return pb_sync_check(ctx, "pb_forward");
+    }
     for (int j = 0; j < t; j++) {
         for (int b = 0; b < B; b++) s->pin_u32[b] = ids_host[(size_t)b * t + j];
         PB_CUDA(ctx, cudaMemcpyAsync(s->ids, s->pin_u32, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
@@ -568,15 +642,13 @@ int pb_decode_greedy(pb_state* s, const uint32_t* tok_host, int n, uint32_t* out
     return PB_OK;
 }
 
-#define PB_MAX_WINDOW 8   // draft windows of the reference are at most 8 tokens (src/spec.rs:185)
 
-static size_t conv_elems(const pb_cfg& c, int B) { return (size_t)B * c.conv_k * (2 * c.lin_nk * c.lin_dk + c.lin_nv * c.lin_dv); }
-static size_t ssm_elems(const pb_cfg& c, int B) { return (size_t)B * c.lin_nv * c.lin_dk * c.lin_dv; }
 
 // Model::forward_multi, src/model/qwen4exp_gguf.rs:2365-2480: logits for every fed position and a
 // rollback checkpoint of the recurrent state after each of the first t-1 tokens (:2386-2387).
-// The window is fed token by token through the decode graph (a batched tensor-core GEMM for t >= 16
-// is not built), so the arithmetic is exactly that of t calls of pb_forward.
+// The window runs through run_window: weights are streamed once for all t tokens (tensor-core GEMM from
+// three tokens on), the recurrences token by token; results agree with t calls of pb_forward to rounding
+// (different summation order), not bit for bit.
 int pb_verify(pb_state* s, const uint32_t* ids_host, int t, float* logits_host) {
     if (!s) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
@@ -590,18 +662,10 @@ int pb_verify(pb_state* s, const uint32_t* ids_host, int t, float* logits_host) 
         for (size_t i = 0; i < s->ck_conv.size(); i++) { PB_TRY(dalloc(s, &s->ck_conv[i], conv_elems(c, 1))); PB_TRY(dalloc(s, &s->ck_ssm[i], ssm_elems(c, 1))); }
     }
     s->verify_pos0 = s->pos_host; s->verify_t = 0;
-    for (int j = 0; j < t; j++) {
-        s->pin_u32[0] = ids_host[j];
-        PB_CUDA(ctx, cudaMemcpyAsync(s->ids, s->pin_u32, 4, cudaMemcpyHostToDevice, ctx->stream));
-        PB_TRY(step_once(s));
-        PB_CUDA(ctx, cudaMemcpyAsync(logits_host + (size_t)j * c.vocab, s->logits, (size_t)c.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
-        if (j + 1 < t)
-            for (int li = 0; li < nl; li++) {
-                PB_CUDA(ctx, cudaMemcpyAsync(s->ck_conv[(size_t)li * PB_MAX_WINDOW + j], s->conv[li], conv_elems(c, 1) * 4, cudaMemcpyDeviceToDevice, ctx->stream));
-                PB_CUDA(ctx, cudaMemcpyAsync(s->ck_ssm[(size_t)li * PB_MAX_WINDOW + j], s->ssm[li], ssm_elems(c, 1) * 4, cudaMemcpyDeviceToDevice, ctx->stream));
-            }
-        PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // the pinned id word is reused
-    }
+    for (int j = 0; j < t; j++) s->pin_u32[j] = ids_host[j];
+    PB_CUDA(ctx, cudaMemcpyAsync(s->ids, s->pin_u32, (size_t)t * 4, cudaMemcpyHostToDevice, ctx->stream));
+    PB_TRY(run_window(s, t, true, true));
+    PB_CUDA(ctx, cudaMemcpyAsync(logits_host, s->logits, (size_t)t * c.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
     PB_TRY(pb_sync_check(ctx, "pb_verify"));
     s->verify_t = t;
     return PB_OK;

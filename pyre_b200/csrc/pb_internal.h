@@ -219,4 +219,5 @@ int pb_launch_kv4_unpack(pb_ctx* ctx, const uint32_t* w, const float* sc, int64_
 // ---------------------------------------------------------------- pb_misc.cu
 int pb_launch_embed(pb_ctx* ctx, int type, const uint8_t* w, int64_t rows, int cols, const uint32_t* ids, int t, float* out, int64_t ldo);
 int pb_launch_argmax(pb_ctx* ctx, const float* logits, int64_t ld, int n, int t, unsigned long long* keys);
+int pb_launch_window_pos(pb_ctx* ctx, int64_t* pos, int64_t* wpos, int t, int advance);
 int pb_launch_advance(pb_ctx* ctx, int64_t* pos, int t, unsigned long long* keys, uint32_t* next, uint32_t* ids, uint32_t* trace, int64_t* trace_len, int64_t trace_cap);

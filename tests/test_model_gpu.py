@@ -104,8 +104,9 @@ def test_context_limit_and_bad_calls(ctx):
 
 
 def test_verify_and_keep_roll_back(ctx):
-    """forward_multi / spec_keep (:2365-2515): per-position logits equal token-by-token forward; keeping a
-    prefix of the window leaves the state exactly as if only that prefix had been fed."""
+    """forward_multi / spec_keep (:2365-2515): per-position logits agree with token-by-token forward (the
+    window streams each weight once for all its tokens on the tensor-core path, so summation order differs:
+    1e-5, not bit for bit); keeping a prefix of the window leaves the state as if only that prefix had been fed."""
     cfg = small_cfg(pb, n_layers=8, kv_bits=4, kv_recent=64, max_ctx=256)
     spec = synth.model_spec(cfg, 4)
     m = synth.build_model(ctx, cfg, spec, 4)
@@ -118,7 +119,7 @@ def test_verify_and_keep_roll_back(ctx):
     b = m.new_state(1); b.forward(prompt)
     ost = om.new_state(); ost.forward(prompt.tolist())
     for j, tok in enumerate(window):
-        assert np.array_equal(lg[j], b.forward([tok])[0])                    # same kernels, same bits
+        assert rel_err(lg[j], b.forward([tok])[0]) < 1e-5                    # batched window vs one token at a time
         assert rel_err(lg[j], ost.forward([int(tok)])) < 1e-3               # and the oracle agrees
     a.spec_keep(5, 2)                                                        # accept 100, 200; drop the rest
     assert a.pos() == 8
