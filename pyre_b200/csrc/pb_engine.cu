@@ -54,6 +54,7 @@ struct pb_state {
     // the layers as columns; wpos[j] = position of column j; win_ckpt = keep DeltaNet checkpoints
     int win_t = 0; bool win_ckpt = false; int64_t* wpos = nullptr;
     int moe_cap = 0;   // rows of the MoE work buffers
+    cudaGraphExec_t win_graph[4 * (PB_MAX_WINDOW + 1)] = {}; unsigned char win_runs[4 * (PB_MAX_WINDOW + 1)] = {};   // per (t, ckpt, all_logits)
     float *xg = nullptr, *part_rs = nullptr;
     int64_t ldproj = 0, ring_cap = 0;
     std::vector<float*> conv, ssm;
@@ -339,6 +340,7 @@ int pb_state_destroy(pb_state* s) {
     cudaSetDevice(s->m->ctx->device);
     cudaStreamSynchronize(s->m->ctx->stream);
     if (s->graph) cudaGraphExecDestroy(s->graph);
+    for (cudaGraphExec_t g : s->win_graph) if (g) cudaGraphExecDestroy(g);
     for (void* p : s->allocs) cudaFree(p);
     if (s->pin_u32) cudaFreeHost(s->pin_u32);
     delete s;
@@ -547,7 +549,33 @@ static int run_window(pb_state* s, int t, bool ckpt, bool all_logits) {
     a.type = out->type; a.cols = c.d; a.nseg = 1; seg(a, 0, out, 0);
     a.x = all_logits ? s->x : s->x + (size_t)(t - 1) * c.d; a.ldx = c.d; a.y = s->logits; a.ldy = c.vocab; a.mode = PB_ACT_NORM; a.norm_w = V(m, -1, PB_R_OUT_NORM); a.eps = c.eps;
     PB_TRY(gemv_cols(ctx, a, all_logits ? t : 1));
-    PB_TRY(pb_launch_window_pos(ctx, s->pos, s->wpos, t, 1));   // position += t
+    return pb_launch_window_pos(ctx, s->pos, s->wpos, t, 1);   // position += t
+}
+
+// run_window as a CUDA graph per (t, ckpt, all_logits): eager the first time (kernel attributes), captured the
+// second, replayed afterwards -- a window is ~1500 launches, whose host cost would otherwise dominate.
+static int window_once(pb_state* s, int t, bool ckpt, bool all_logits) {
+    pb_ctx* ctx = s->m->ctx;
+    const int key = t * 4 + (ckpt ? 2 : 0) + (all_logits ? 1 : 0);
+    if (s->win_graph[key]) {
+        PB_CUDA(ctx, cudaGraphLaunch(s->win_graph[key], ctx->stream));
+    } else if (s->win_runs[key] == 0) {
+        PB_TRY(run_window(s, t, ckpt, all_logits));
+        s->win_runs[key] = 1;
+    } else {
+        cudaGraph_t g = nullptr;
+        PB_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+        const uint64_t k0 = ctx->kernels_launched;
+        const int rc = run_window(s, t, ckpt, all_logits);
+        ctx->kernels_launched = k0;
+        cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+        if (rc != PB_OK) { if (g) cudaGraphDestroy(g); return rc; }
+        if (e != cudaSuccess) PB_FAIL(ctx, PB_ERR_CUDA, "window graph capture failed: %s", cudaGetErrorString(e));
+        e = cudaGraphInstantiate(&s->win_graph[key], g, 0);
+        cudaGraphDestroy(g);
+        if (e != cudaSuccess) { s->win_graph[key] = nullptr; PB_FAIL(ctx, PB_ERR_CUDA, "window graph instantiate failed: %s", cudaGetErrorString(e)); }
+        PB_CUDA(ctx, cudaGraphLaunch(s->win_graph[key], ctx->stream));
+    }
     s->pos_host += t;
     return PB_OK;
 }
@@ -595,7 +623,7 @@ int pb_forward(pb_state* s, const uint32_t* ids_host, int t, float* logits_host)
             const int n = t - j0 < PB_MAX_WINDOW ? t - j0 : PB_MAX_WINDOW;
             for (int j = 0; j < n; j++) s->pin_u32[j] = ids_host[j0 + j];
             PB_CUDA(ctx, cudaMemcpyAsync(s->ids, s->pin_u32, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
-            PB_TRY(run_window(s, n, false, false));
+            PB_TRY(window_once(s, n, false, false));
             if (j0 + n < t) PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // the pinned id buffer is reused
         }
         s->verify_t = 0;
@@ -664,7 +692,7 @@ int pb_verify(pb_state* s, const uint32_t* ids_host, int t, float* logits_host) 
     s->verify_pos0 = s->pos_host; s->verify_t = 0;
     for (int j = 0; j < t; j++) s->pin_u32[j] = ids_host[j];
     PB_CUDA(ctx, cudaMemcpyAsync(s->ids, s->pin_u32, (size_t)t * 4, cudaMemcpyHostToDevice, ctx->stream));
-    PB_TRY(run_window(s, t, true, true));
+    PB_TRY(window_once(s, t, true, true));
     PB_CUDA(ctx, cudaMemcpyAsync(logits_host, s->logits, (size_t)t * c.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
     PB_TRY(pb_sync_check(ctx, "pb_verify"));
     s->verify_t = t;

@@ -446,6 +446,97 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
     for (int64_t i = tid; i < (int64_t)cp.t * cp.d; i += CT) pb_combine_one(cp, i, true);
 }
 
+// ------------------------------------------------------------------------------------ expert down, one token
+
+// One token on one GPU: the work is cut by OUTPUT ROWS instead of by expert.  CTA c owns rows
+// [16 c, 16 c + 16) of every selected expert and of the shared expert, so the weighted sum over the
+// experts (ascending expert id, then the shared expert as in pb_combine_one) is formed inside the CTA
+// and written straight to y: no partial-row buffer, no combine pass, no per-chunk barriers.  All
+// row slices (<= 16 x 16 rows) are requested up front; the hidden vectors of all entries are split into
+// int8 levels once per CTA.
+#define PB_DR_ROWS 16
+#define PB_DR_MAXE 16
+template <int FMT>
+__global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_rows_kernel(const PbExpertParams p, const PbCombineParams cp) {
+    using D = PbQDec<FMT>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);                       // [PB_DR_MAXE]
+    float* res = reinterpret_cast<float*>(smem + 128);                        // [PB_DR_MAXE][16 rows]
+    uint8_t* tab = smem + 128 + PB_DR_MAXE * PB_DR_ROWS * 4;
+    const int cols = p.bpr * 256, xw = pb_xq_words(cols);
+    uint32_t* xq = reinterpret_cast<uint32_t*>(tab + p.tab_bytes);            // [n_used + 1][xw]
+    const uint32_t slice = (uint32_t)PB_DR_ROWS * p.row_bytes;                // bytes of one expert's 16 rows
+    uint8_t* stages = reinterpret_cast<uint8_t*>(xq) + (((size_t)PB_DR_MAXE * xw * 4 + 127) & ~(size_t)127);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pb_pdl_trigger();
+    if (tid == 0) {
+        for (int i = 0; i < PB_DR_MAXE; i++) pb_mbar_init(&full[i], 1);
+        pb_fence_barrier_init();
+    }
+    __syncthreads();
+    pb_pdl_wait();   // expert lists and hidden vectors come from earlier kernels
+    const int n_used = *p.n_used;
+    const int nsl = n_used + (p.has_shared ? 1 : 0);   // slices: the used experts in ascending id, then the shared expert
+    const int r0 = (int)blockIdx.x * PB_DR_ROWS;
+    if (nsl > PB_DR_MAXE) { if (tid == 0) atomicExch(p.status, PB_DEV_BAD_INDEX); return; }
+
+    if (warp == PB_CONSUMERS) {
+        if (lane == 0) {
+            int k = 0;
+            for (; k < nsl; k++) {
+                const uint8_t* src;
+                if (k < n_used) {
+                    const int e = p.used_e[k];
+                    if (e < 0 || e >= p.n_exp) { atomicExch(p.status, PB_DEV_BAD_INDEX); break; }
+                    src = p.w_a + ((size_t)(e - p.e_base) * p.rows_e + r0) * p.row_bytes;
+                } else src = p.sh_a + (size_t)r0 * p.row_bytes;
+                pb_mbar_expect_tx(&full[k], slice);
+                pb_bulk_g2s(stages + (size_t)k * slice, src, slice, &full[k]);
+            }
+            // a slice that was not requested is completed by hand so that no consumer waits for it
+            for (int j = k; j < nsl; j++) pb_mbar_arrive(&full[j]);
+        }
+        return;
+    }
+
+    constexpr int CT = PB_CONSUMERS * 32;
+    const PbQTabs T = pb_fill_qtabs<FMT>(tab, p.rep, tid, CT, lane);
+    // int8 levels of every entry's hidden vector (entry k of expert slice k: one token), four groups per warp pass
+    const int gpe = cols / 128;   // warp passes per entry
+    for (int i = warp; i < nsl * gpe; i += PB_CONSUMERS) {
+        const int k = i / gpe, g0 = (i - k * gpe) * 4;
+        const float* hv = k < n_used ? p.h + (size_t)p.used_off[k] * cols : p.h_sh + (size_t)p.sh_tok0 * cols;
+        pb_split_groups4(*reinterpret_cast<const float4*>(hv + 32 * g0 + 4 * lane), lane, g0, cols, xq + (size_t)k * xw);
+    }
+    pb_named_barrier(1, CT);
+
+    const int nquarters = 4 * p.bpr;                    // <= 32 (checked on the host)
+    const int rpw = 32 / nquarters, sub = lane / nquarters, ql = lane - sub * nquarters;
+    const int ppe = PB_DR_ROWS / rpw;                   // warp passes per slice
+    for (int i = warp; i < nsl * ppe; i += PB_CONSUMERS) {
+        const int k = i / ppe, r = (i - k * ppe) * rpw + sub;
+        if (!pb_mbar_wait(&full[k], 0, p.status, PB_DEV_WAIT_FULL_TIMEOUT)) break;
+        PbQuarter wq; PbXQuarter xv;
+        D::quarter(pb_smem_u32(stages + (size_t)k * slice) + (uint32_t)r * p.row_bytes + (ql >> 2) * D::STEP_BYTES, ql & 3, T, wq);
+        pb_load_xquarter(xq + (size_t)k * xw, cols, ql, xv);
+        float acc = pb_quarter_dot<FMT>(wq, xv);
+        for (int o = nquarters >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (ql == 0) res[k * PB_DR_ROWS + r] = acc;
+    }
+    pb_named_barrier(1, CT);
+    if (tid < PB_DR_ROWS) {
+        // pb_combine_one for token sh_tok0: sigmoid(gate) * shared + sum over slots in ascending expert id
+        float y = 0.f;
+        if (p.has_shared) y = __fmul_rn(res[n_used * PB_DR_ROWS + tid], pb_sigm(cp.logits[(size_t)p.sh_tok0 * (cp.n_exp + 1) + cp.n_exp]));
+        float o = 0.f;
+        // product rounded, then added (no fused multiply-add): the bits of the partial-row path
+        for (int k = 0; k < n_used; k++) o = __fadd_rn(o, __fmul_rn(p.ent_w[p.used_off[k]], res[k * PB_DR_ROWS + tid]));
+        y = __fadd_rn(y, o);
+        float* dst = cp.y + (size_t)p.sh_tok0 * cp.ldy + r0 + tid;
+        *dst = cp.accumulate ? *dst + y : y;
+    }
+}
+
 // ------------------------------------------------------------------------------------ combine
 
 // y[tok][r] = sigmoid(shared-gate logit) * shared[tok][r] + sum_j part[tok][j][r]  (ascending expert id),
@@ -490,6 +581,20 @@ static int launch_expert(pb_ctx* ctx, PbExpertParams p, int cols, const PbCombin
     const size_t smem = 256 + p.tab_bytes + xbytes + (size_t)PB_STAGES * p.stage_bytes;
     if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "expert kernel needs %zu bytes of shared memory", smem);
     p.status = ctx->dev_status;
+    if (DOWN && cp && p.t == 1 && p.top_k + 1 <= PB_DR_MAXE && p.rows_e % PB_DR_ROWS == 0 && 4 * p.bpr <= 32 && PB_DR_ROWS % (32 / (4 * p.bpr)) == 0 && PASSES == 1) {
+        // one token, combine requested: the row-partitioned kernel writes y directly
+        const size_t xbytes1 = (((size_t)PB_DR_MAXE * pb_xq_words(cols) * 4 + 127) & ~(size_t)127);
+        const size_t smem1 = 128 + PB_DR_MAXE * PB_DR_ROWS * 4 + p.tab_bytes + xbytes1 + (size_t)PB_DR_MAXE * PB_DR_ROWS * p.row_bytes;
+        if (smem1 <= (size_t)ctx->max_smem_optin) {
+            auto kern = pb_expert_down_rows_kernel<FMT>;
+            static size_t configured1 = 0;
+            if (smem1 > configured1) { PB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1)); configured1 = smem1; }
+            pb_launch_k(ctx, kern, dim3(p.rows_e / PB_DR_ROWS), dim3(PB_KTHREADS), smem1, p, *cp);
+            ctx->kernels_launched++;
+            PB_CUDA(ctx, cudaGetLastError());
+            return PB_OK;
+        }
+    }
     if (DOWN) {
         if (p.hq) {
             pb_launch_k(ctx, pb_split_h_kernel, dim3(p.t * p.top_k + p.t), dim3(128), (size_t)0, p);
