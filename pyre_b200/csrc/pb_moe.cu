@@ -93,14 +93,17 @@ __device__ __forceinline__ void pb_route_body(const PbRouteParams& p, int* rsm) 
 // grid: ceil((n_exp + 1) / 8) CTAs of 256 threads; warp per router row (row n_exp = shared-gate vector).
 // CTA j additionally splits groups 4j..4j+3 of every token's normalized activations into int8
 // levels for the expert kernels, so that work is spread over the grid.
+#define PB_ROUTER_TPG 8   // tokens per router CTA (one warp each for the RMS scales)
 __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, const PbRouteParams rp, unsigned int* ticket) {
     extern __shared__ float rs[];   // 2048 ints for the routing pass, then scale[t]
     float* scale = rs + 2048;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     pb_pdl_wait();
     pb_pdl_trigger();
+    // grid.y cuts the tokens into groups of PB_ROUTER_TPG: this CTA handles tokens [b_lo, b_hi)
+    const int b_lo = (int)blockIdx.y * PB_ROUTER_TPG, b_hi = min(p.t, b_lo + PB_ROUTER_TPG);
     // per-token RMS scale (rms(): 1 / sqrt(mean(x^2) + eps), qwen4exp_gguf.rs:209); one warp per token
-    for (int b = warp; b < p.t; b += 8) {
+    for (int b = b_lo + warp; b < b_hi; b += 8) {
         float s = 1.0f;
         if (p.norm_w) {
             float ss = 0.f;
@@ -113,7 +116,7 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
     __syncthreads();
     const int ng = p.cols / 32;
     for (int g0 = blockIdx.x * 4; g0 < ng; g0 += gridDim.x * 4) {
-        for (int b = warp; b < p.t; b += 8) {
+        for (int b = b_lo + warp; b < b_hi; b += 8) {
             float4 v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + 32 * g0 + 4 * lane);
             if (p.norm_w) {
                 const float4 n = *reinterpret_cast<const float4*>(p.norm_w + 32 * g0 + 4 * lane);
@@ -136,7 +139,7 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
                 if (p.norm_w) { const float4 n = *reinterpret_cast<const float4*>(p.norm_w + lane * 4 + 128 * k); wr[k].x *= n.x; wr[k].y *= n.y; wr[k].z *= n.z; wr[k].w *= n.w; }
             }
 #pragma unroll 2
-            for (int b = 0; b < p.t; b++) {
+            for (int b = b_lo; b < b_hi; b++) {
                 const float* xb = p.x + b * p.ldx + lane * 4;
                 float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
@@ -148,7 +151,7 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
                 if (lane == 0) p.logits[b * (p.n_exp + 1) + row] = acc;
             }
         } else
-        for (int b = 0; b < p.t; b++) {
+        for (int b = b_lo; b < b_hi; b++) {
             float acc = 0.f;
             const float s = scale[b];
             if (wrow) {
@@ -172,7 +175,7 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
     __shared__ int is_last;
     __threadfence();
     __syncthreads();
-    if (tid == 0) is_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+    if (tid == 0) is_last = atomicAdd(ticket, 1u) == gridDim.x * gridDim.y - 1;
     __syncthreads();
     if (!is_last) return;
     if (tid == 0) *ticket = 0;
@@ -555,7 +558,7 @@ int pb_launch_router(pb_ctx* ctx, const PbRouterParams& p, const PbRouteParams& 
     if (rp.top_k > PB_MAX_TOPK || rp.n_exp > 1024) PB_FAIL(ctx, PB_UNSUPPORTED, "route: top_k %d / n_exp %d beyond %d / 1024", rp.top_k, rp.n_exp, PB_MAX_TOPK);
     const int grid = (p.n_exp + 1 + 7) / 8;
     const size_t smem = (size_t)(2048 + ((p.t + 31) & ~31)) * 4;
-    pb_launch_k(ctx, pb_router_kernel, dim3(grid), dim3(256), smem, p, rp, ticket);
+    pb_launch_k(ctx, pb_router_kernel, dim3(grid, (p.t + PB_ROUTER_TPG - 1) / PB_ROUTER_TPG), dim3(256), smem, p, rp, ticket);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;
