@@ -208,6 +208,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
     const int nchunks = n_used * cpe + cps;
     const int my_chunks = nchunks > (int)blockIdx.x ? (nchunks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
     const uint32_t half = (uint32_t)p.rows_per_chunk * p.row_bytes;   // a multiple of 16 by construction
+    const uint32_t xbytes = (uint32_t)pb_xq_words(p.bpr * 256) * 4;   // one token's activation levels (a multiple of 16)
 
     if (warp == PB_CONSUMERS) {
         if (lane == 0) {
@@ -225,9 +226,13 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
                     const size_t off = (size_t)(chunk - n_used * cpe) * p.rows_per_chunk * p.row_bytes;
                     g = p.sh_a + off; u = p.sh_b + off;
                 }
-                if (!pb_ring_acquire(ring, k, 2 * half, p.status)) break;
+                // the activation levels of the chunk's first entry ride along, so that the consumers read them
+                // from shared memory instead of waiting for L2 after the decode
+                const int tok0 = chunk < n_used * cpe ? p.ent_tok[p.used_off[chunk / cpe]] : p.sh_tok0;
+                if (!pb_ring_acquire(ring, k, 2 * half + xbytes, p.status)) break;
                 pb_ring_copy(ring, k, 0, g, half);
                 pb_ring_copy(ring, k, half, u, half);
+                pb_ring_copy(ring, k, 2 * half, p.xq + (size_t)tok0 * pb_xq_words(p.bpr * 256), xbytes);
             }
             if (k < my_chunks) pb_ring_drain(ring, k);
         }
@@ -263,13 +268,14 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
             }
             for (int en = e0; en < e1; en++) {
                 const int tok = shared ? p.sh_tok0 + en : p.ent_tok[en];
+                const uint32_t* xcol = en == e0 ? reinterpret_cast<const uint32_t*>(pb_ring_stage(ring, k) + 2 * half) : p.xq + (size_t)tok * xw;
                 float g = 0.f, u = 0.f;
 #pragma unroll
                 for (int ps = 0; ps < PASSES; ps++) {
                     const int qi = ps * 32 + ql;
                     if (qi < nquarters) {
                         PbXQuarter xv;
-                        pb_load_xquarter(p.xq + (size_t)tok * xw, cols, qi, xv);
+                        pb_load_xquarter(xcol, cols, qi, xv);
                         g += pb_quarter_dot<FMT>(wg[ps], xv);
                         u += pb_quarter_dot<FMT>(wu[ps], xv);
                     }
@@ -580,7 +586,7 @@ static int launch_expert(pb_ctx* ctx, PbExpertParams p, int cols, const PbCombin
     if (p.rows_e % rpc || (p.has_shared && !DOWN && p.rows_sh % rpc)) PB_FAIL(ctx, PB_UNSUPPORTED, "expert kernel: %d rows per expert is not a multiple of the %d-row chunk", p.rows_e, rpc);
     p.rows_per_chunk = rpc;
     const size_t xbytes = DOWN ? (((size_t)pb_xq_words(cols) * 4 + 127) & ~(size_t)127) : 0;
-    p.stage_bytes = (uint32_t)((((size_t)rpc * p.row_bytes * (DOWN ? 1 : 2)) + 16 + 127) & ~(size_t)127);
+    p.stage_bytes = (uint32_t)((((size_t)rpc * p.row_bytes * (DOWN ? 1 : 2)) + (DOWN ? 0 : (size_t)pb_xq_words(cols) * 4) + 16 + 127) & ~(size_t)127);
     const size_t smem = 256 + p.tab_bytes + xbytes + (size_t)PB_STAGES * p.stage_bytes;
     if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "expert kernel needs %zu bytes of shared memory", smem);
     p.status = ctx->dev_status;
