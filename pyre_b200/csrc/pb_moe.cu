@@ -347,6 +347,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
     const int nchunks = n_used * cpe + cps;
     const int my_chunks = nchunks > (int)blockIdx.x ? (nchunks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
     const uint32_t bytes = (uint32_t)p.rows_per_chunk * p.row_bytes;
+    const uint32_t hbytes = (uint32_t)xw * 4;   // levels of one hidden vector (a multiple of 16)
 
     if (warp == PB_CONSUMERS) {
         if (lane == 0) {
@@ -360,6 +361,14 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
                     if (e < 0 || e >= p.n_exp) { atomicExch(p.status, PB_DEV_BAD_INDEX); break; }
                     src = p.w_a + ((size_t)(e - p.e_base) * p.rows_e + r0) * p.row_bytes;
                 } else src = p.sh_a + (size_t)(chunk - n_used * cpe) * p.rows_per_chunk * p.row_bytes;
+                if (p.hq) {
+                    // several tokens: the levels of the chunk's first hidden vector ride along with the weights
+                    const size_t slot = chunk < n_used * cpe ? (size_t)p.used_off[chunk / cpe] : (size_t)p.t * p.top_k + p.sh_tok0;
+                    if (!pb_ring_acquire(ring, k, bytes + hbytes, p.status)) break;
+                    pb_ring_copy(ring, k, 0, src, bytes);
+                    pb_ring_copy(ring, k, bytes, p.hq + slot * xw, hbytes);
+                    continue;
+                }
                 if (!pb_ring_acquire(ring, k, bytes, p.status)) break;
                 pb_ring_copy(ring, k, 0, src, bytes);
             }
@@ -397,7 +406,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
                 }
                 for (int en = e0; en < e1; en++) {
                     const int tok = shared ? p.sh_tok0 + en : p.ent_tok[en];
-                    const uint32_t* xcol = p.hq + (size_t)(shared ? p.t * p.top_k + tok : en) * xw;
+                    const uint32_t* xcol = en == e0 ? reinterpret_cast<const uint32_t*>(pb_ring_stage(ring, k) + bytes) : p.hq + (size_t)(shared ? p.t * p.top_k + tok : en) * xw;
                     float acc = 0.f;
 #pragma unroll
                     for (int ps = 0; ps < PASSES; ps++) {
@@ -586,7 +595,7 @@ static int launch_expert(pb_ctx* ctx, PbExpertParams p, int cols, const PbCombin
     if (p.rows_e % rpc || (p.has_shared && !DOWN && p.rows_sh % rpc)) PB_FAIL(ctx, PB_UNSUPPORTED, "expert kernel: %d rows per expert is not a multiple of the %d-row chunk", p.rows_e, rpc);
     p.rows_per_chunk = rpc;
     const size_t xbytes = DOWN ? (((size_t)pb_xq_words(cols) * 4 + 127) & ~(size_t)127) : 0;
-    p.stage_bytes = (uint32_t)((((size_t)rpc * p.row_bytes * (DOWN ? 1 : 2)) + (DOWN ? 0 : (size_t)pb_xq_words(cols) * 4) + 16 + 127) & ~(size_t)127);
+    p.stage_bytes = (uint32_t)((((size_t)rpc * p.row_bytes * (DOWN ? 1 : 2)) + (size_t)pb_xq_words(cols) * 4 + 16 + 127) & ~(size_t)127);
     const size_t smem = 256 + p.tab_bytes + xbytes + (size_t)PB_STAGES * p.stage_bytes;
     if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "expert kernel needs %zu bytes of shared memory", smem);
     p.status = ctx->dev_status;
