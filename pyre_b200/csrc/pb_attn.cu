@@ -63,13 +63,17 @@ __device__ __forceinline__ float pb_kv4_dequant(uint32_t w, int j, float s) {
     return (float)q * s;
 }
 
+// nibble j of a cache word (offset binary)
+__device__ __forceinline__ float pb_kv4_dequant8(uint32_t w, int j, float s) { return (float)((int)((w >> (4 * j)) & 0xF) - 8) * s; }
+
 // one warp packs one 32-value block: lane = element.  kv4::pack, src/model/kv4.rs:12-32
-__device__ __forceinline__ void pb_kv4_pack_block(float v, int lane, uint32_t* words4, float* scale) {
+// bias = 0: two's-complement nibbles (kv4.rs); bias = 8: offset-binary nibbles q + 8, the form the cache keeps
+__device__ __forceinline__ void pb_kv4_pack_block(float v, int lane, uint32_t* words4, float* scale, int bias) {
     const float m = pb_warp_max(fabsf(v));
     const float s = (m > 0.f && isfinite(m)) ? m / 7.0f : 0.f;
     int q = 0;
     if (s > 0.f) { float r = roundf(v / s); r = fminf(fmaxf(r, -7.f), 7.f); q = (int)r; }
-    uint32_t u = ((uint32_t)q & 0xF) << (4 * (lane & 7));
+    uint32_t u = ((uint32_t)(q + bias) & 0xF) << (4 * (lane & 7));
     u |= __shfl_xor_sync(0xffffffffu, u, 1); u |= __shfl_xor_sync(0xffffffffu, u, 2); u |= __shfl_xor_sync(0xffffffffu, u, 4);
     if ((lane & 7) == 0) words4[lane >> 3] = u;
     if (lane == 0) *scale = s;
@@ -77,7 +81,7 @@ __device__ __forceinline__ void pb_kv4_pack_block(float v, int lane, uint32_t* w
 
 // one warp packs 32 dims of 8 consecutive positions into position-transposed words: lane = dim,
 // v[i] = value of position i; same quantization as pb_kv4_pack_block, one scale per position
-__device__ __forceinline__ uint32_t pb_kv4_pack_vt8(const float (&v)[8], int lane, float* scales, int scale_stride) {
+__device__ __forceinline__ uint32_t pb_kv4_pack_vt8(const float (&v)[8], int lane, float* scales, int scale_stride, int bias) {
     uint32_t word = 0;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
@@ -85,13 +89,13 @@ __device__ __forceinline__ uint32_t pb_kv4_pack_vt8(const float (&v)[8], int lan
         const float s = (m > 0.f && isfinite(m)) ? m / 7.0f : 0.f;
         int q = 0;
         if (s > 0.f) { float r = roundf(v[i] / s); r = fminf(fmaxf(r, -7.f), 7.f); q = (int)r; }
-        word |= ((uint32_t)q & 0xF) << (4 * i);
+        word |= ((uint32_t)(q + bias) & 0xF) << (4 * i);
         if (lane == 0) scales[(size_t)i * scale_stride] = s;
     }
     return word;
 }
 // x [npos][hd] f32 (npos a multiple of 8) -> w [npos/8][hd] words, sc [npos][hd/32]; one warp per (8 positions, 32 dims)
-__global__ void __launch_bounds__(256) pb_kv4_pack_vt_kernel(const float* __restrict__ x, int64_t npos, int hd, uint32_t* __restrict__ w, float* __restrict__ sc) {
+__global__ void __launch_bounds__(256) pb_kv4_pack_vt_kernel(const float* __restrict__ x, int64_t npos, int hd, uint32_t* __restrict__ w, float* __restrict__ sc, int bias) {
     const int64_t unit = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31, bpp = hd / 32;
     if (unit >= (npos / 8) * bpp) return;
@@ -99,14 +103,14 @@ __global__ void __launch_bounds__(256) pb_kv4_pack_vt_kernel(const float* __rest
     float v[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) v[i] = x[(pg * 8 + i) * hd + blk * 32 + lane];
-    w[pg * hd + blk * 32 + lane] = pb_kv4_pack_vt8(v, lane, sc + pg * 8 * bpp + blk, bpp);
+    w[pg * hd + blk * 32 + lane] = pb_kv4_pack_vt8(v, lane, sc + pg * 8 * bpp + blk, bpp, bias);
 }
 
 // generic packer: x [n] f32 -> words [n/8], scales [n/32]; one warp per block
-__global__ void __launch_bounds__(256) pb_kv4_pack_kernel(const float* __restrict__ x, int64_t nblocks, uint32_t* __restrict__ w, float* __restrict__ sc) {
+__global__ void __launch_bounds__(256) pb_kv4_pack_kernel(const float* __restrict__ x, int64_t nblocks, uint32_t* __restrict__ w, float* __restrict__ sc, int bias) {
     const int64_t blk = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (blk >= nblocks) return;
-    pb_kv4_pack_block(x[blk * 32 + (threadIdx.x & 31)], threadIdx.x & 31, w + blk * 4, sc + blk);
+    pb_kv4_pack_block(x[blk * 32 + (threadIdx.x & 31)], threadIdx.x & 31, w + blk * 4, sc + blk, bias);
 }
 __global__ void __launch_bounds__(256) pb_kv4_unpack_kernel(const uint32_t* __restrict__ w, const float* __restrict__ sc, int64_t n, float* __restrict__ x) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -162,7 +166,7 @@ __global__ void __launch_bounds__(AT_THREADS) pb_kv_append_kernel(const PbAttnPa
         const int blk = (int)(i % bpp); const int h = (int)((i / bpp) % nkv); const int64_t pp = have + i / ((int64_t)bpp * nkv);
         const size_t src = (((size_t)b * nkv + h) * p.ring_cap + (pp % p.ring_cap)) * hd + blk * 32 + lane;
         const size_t row = ((size_t)b * nkv + h) * p.max_ctx + pp;
-        pb_kv4_pack_block(p.kr[src], lane, p.kw + row * (hd / 8) + blk * 4, p.ks + row * bpp + blk);
+        pb_kv4_pack_block(p.kr[src], lane, p.kw + row * (hd / 8) + blk * 4, p.ks + row * bpp + blk, 8);
     }
     // V: groups of 8 positions (have and want are multiples of 64)
     const int64_t nvt = (want - have) / 8 * nkv * bpp;
@@ -172,7 +176,7 @@ __global__ void __launch_bounds__(AT_THREADS) pb_kv_append_kernel(const PbAttnPa
         float v[8];
 #pragma unroll
         for (int j = 0; j < 8; j++) v[j] = p.vr[(head * p.ring_cap + ((pg * 8 + j) % p.ring_cap)) * hd + blk * 32 + lane];
-        p.vw[head * p.max_ctx * (hd / 8) + (size_t)pg * hd + blk * 32 + lane] = pb_kv4_pack_vt8(v, lane, p.vs + (head * p.max_ctx + pg * 8) * bpp + blk, bpp);
+        p.vw[head * p.max_ctx * (hd / 8) + (size_t)pg * hd + blk * 32 + lane] = pb_kv4_pack_vt8(v, lane, p.vs + (head * p.max_ctx + pg * 8) * bpp + blk, bpp, 8);
     }
     __syncthreads();
     if (tid == 0) p.q4n[b] = want;
@@ -180,7 +184,8 @@ __global__ void __launch_bounds__(AT_THREADS) pb_kv_append_kernel(const PbAttnPa
 
 // ------------------------------------------------------------------------------------ partial
 
-#define AT_STAGE_WORDS 2944   // per warp: K tile 32 x 36 words (padded rows), V tile 1024, K scales 256, V scales 256, scores 256
+#define AT_BUF_WORDS 2688     // one tile buffer: K 32 x 36 words (padded rows), V 1024, K scales 256, V scales 256
+#define AT_STAGE_WORDS (2 * AT_BUF_WORDS + 256)   // per warp: two tile buffers (the next tile loads while this one is used) + 256 scores
 #define AT_KSTRIDE 36
 
 __device__ __forceinline__ void pb_mma16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -195,12 +200,18 @@ __device__ __forceinline__ void pb_split_h2(float a, float b, uint32_t& hi, uint
     const __half2 l = __floats2half2_rn(a - r.x, b - r.y);
     hi = *reinterpret_cast<const uint32_t*>(&h); lo = *reinterpret_cast<const uint32_t*>(&l);
 }
-// nibbles q and q + 4 of a word of offset-binary nibbles (two's complement ^ 8) -> f16 pair of the signed values
+// nibbles q and q + 4 of a cache word (offset-binary nibbles) -> f16 pair of the signed values
 __device__ __forceinline__ uint32_t pb_nib2_h2(uint32_t x, int sh) {
     const uint32_t t = ((x >> sh) & 0x000F000Fu) | 0x64006400u;           // 1024 + n
     const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&t), __float2half2_rn(1032.0f));
     return *reinterpret_cast<const uint32_t*>(&r);
 }
+__device__ __forceinline__ void pb_cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(pb_smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void pb_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void pb_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 // shared-memory loads that the compiler may not hoist over the per-tile restaging of the buffers
 __device__ __forceinline__ uint32_t pb_ldsv32(uint32_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a) : "memory"); return v; }
 __device__ __forceinline__ uint4 pb_ldsv128(uint32_t a) { uint4 v; asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory"); return v; }
@@ -230,41 +241,40 @@ __device__ __forceinline__ void pb_attn_mma_tiles(const float* qs, uint32_t* sta
     for (int i = 0; i < 16; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
     constexpr int E_NONE = -100000;
     int E = E_NONE;
-    uint32_t* tk = stage; uint32_t* tv = stage + 32 * AT_KSTRIDE;
-    float* tks = reinterpret_cast<float*>(tv + 1024); float* tvs = tks + 256;
-    float2* sbuf = reinterpret_cast<float2*>(tvs + 256);   // [4 groups][32 lanes]: scores, then probabilities
-    const uint32_t tk_s = pb_smem_u32(tk), tv_s = pb_smem_u32(tv);
+    float2* sbuf = reinterpret_cast<float2*>(stage + 2 * AT_BUF_WORDS);   // [4 groups][32 lanes]: scores, then probabilities
     const int krow = (g >> 1) + 4 * (g & 1);
-
-    for (int64_t t = (int64_t)warp * nsp + sp; t < ntiles; t += (int64_t)AT_WARPS * nsp) {
+    // asynchronous copy of tile t into buffer `buf`: every lane moves 8 + 8 + 2 + 2 pieces of 16 bytes
+    auto fetch = [&](int64_t t, int buf) {
+        uint32_t* bk = stage + buf * AT_BUF_WORDS; uint32_t* bv = bk + 32 * AT_KSTRIDE; uint32_t* bs = bv + 1024;
         const int64_t pbase = t * AT_TILE;
+        const uint4* gk = reinterpret_cast<const uint4*>(kw + pbase * (HD / 8));
+        const uint4* gv = reinterpret_cast<const uint4*>(vw + pbase * (HD / 8));
+        const uint4* gks = reinterpret_cast<const uint4*>(ks + pbase * (HD / 32));
+        const uint4* gvs = reinterpret_cast<const uint4*>(vs + pbase * (HD / 32));
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int f = i * 32 + lane;
+            pb_cp_async16(bk + (f >> 3) * AT_KSTRIDE + 4 * (f & 7), gk + f);
+            pb_cp_async16(bv + 4 * f, gv + f);
+        }
+        pb_cp_async16(bs + 4 * lane, gks + lane); pb_cp_async16(bs + 128 + 4 * lane, gks + 32 + lane);
+        pb_cp_async16(bs + 256 + 4 * lane, gvs + lane); pb_cp_async16(bs + 384 + 4 * lane, gvs + 32 + lane);
+        pb_cp_async_commit();
+    };
+    const int64_t t_first = (int64_t)warp * nsp + sp, t_step = (int64_t)AT_WARPS * nsp;
+    if (t_first < ntiles) fetch(t_first, 0);
+    int buf = 0;
+    for (int64_t t = t_first; t < ntiles; t += t_step, buf ^= 1) {
         {
-            const uint4* gk = reinterpret_cast<const uint4*>(kw + pbase * (HD / 8));
-            const uint4* gv = reinterpret_cast<const uint4*>(vw + pbase * (HD / 8));
-            const uint4* gks = reinterpret_cast<const uint4*>(ks + pbase * (HD / 32));
-            const uint4* gvs = reinterpret_cast<const uint4*>(vs + pbase * (HD / 32));
-            uint4 a[8], c[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) { a[i] = gk[i * 32 + lane]; c[i] = gv[i * 32 + lane]; }
-            const uint4 sa0 = gks[lane], sa1 = gks[32 + lane], sc0 = gvs[lane], sc1 = gvs[32 + lane];
-            __syncwarp();   // every lane is done with the previous tile
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const int f = i * 32 + lane;
-                uint4 kx = a[i];
-                kx.x ^= 0x88888888u; kx.y ^= 0x88888888u; kx.z ^= 0x88888888u; kx.w ^= 0x88888888u;
-                *reinterpret_cast<uint4*>(tk + (f >> 3) * AT_KSTRIDE + 4 * (f & 7)) = kx;
-                uint4 vx = c[i];
-                vx.x ^= 0x88888888u; vx.y ^= 0x88888888u; vx.z ^= 0x88888888u; vx.w ^= 0x88888888u;
-                reinterpret_cast<uint4*>(tv)[f] = vx;
-            }
-            reinterpret_cast<uint4*>(tks)[lane] = sa0; reinterpret_cast<uint4*>(tks)[32 + lane] = sa1;
-            reinterpret_cast<uint4*>(tvs)[lane] = sc0; reinterpret_cast<uint4*>(tvs)[32 + lane] = sc1;
+            if (t + t_step < ntiles) { fetch(t + t_step, buf ^ 1); pb_cp_async_wait<1>(); } else pb_cp_async_wait<0>();
+            __syncwarp();   // every lane's pieces of this tile have landed
+            uint32_t* tk = stage + buf * AT_BUF_WORDS; uint32_t* tv = tk + 32 * AT_KSTRIDE;
+            float* tks = reinterpret_cast<float*>(tv + 1024); float* tvs = tks + 256;
+            const uint32_t tk_s = pb_smem_u32(tk), tv_s = pb_smem_u32(tv);
             // largest V scale of the tile -> running exponent
-            float vm = fmaxf(fmaxf(fmaxf(__uint_as_float(sc0.x), __uint_as_float(sc0.y)), fmaxf(__uint_as_float(sc0.z), __uint_as_float(sc0.w))),
-                             fmaxf(fmaxf(__uint_as_float(sc1.x), __uint_as_float(sc1.y)), fmaxf(__uint_as_float(sc1.z), __uint_as_float(sc1.w))));
+            const float4 sc0 = *reinterpret_cast<const float4*>(tvs + 4 * lane), sc1 = *reinterpret_cast<const float4*>(tvs + 128 + 4 * lane);
+            float vm = fmaxf(fmaxf(fmaxf(sc0.x, sc0.y), fmaxf(sc0.z, sc0.w)), fmaxf(fmaxf(sc1.x, sc1.y), fmaxf(sc1.z, sc1.w)));
             vm = pb_warp_max(vm);
-            __syncwarp();
             float facc = 1.0f;
             if (vm > 0.f && vm <= 3.0e38f) {
                 const int e = ilogbf(vm) + 1;
@@ -331,9 +341,12 @@ __device__ __forceinline__ void pb_attn_mma_tiles(const float* qs, uint32_t* sta
                     }
                 }
             }
+            __syncwarp();   // all lanes are done with this buffer before the next iteration refills it
         }
     }
-    // ---- this warp's partial in the merge layout [G][2 + hd]
+    // ---- this warp's partial in the merge layout [G][2 + hd]; the merge buffer overlays the tile buffers,
+    //      so every warp of the CTA (all of them run this function) must be done with its tiles first
+    __syncthreads();
     const float oscale = E == E_NONE ? 0.f : pb_exp2i(E);
 #ifdef PB_ATTN_DBG
     if (lane == 0) printf("E %d oscale %g acc0 %g %g %g %g m %g l %g\n", E, oscale, acc[0][0], acc[0][1], acc[0][2], acc[0][3], m_run, l_run);
@@ -364,7 +377,9 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
     extern __shared__ float asm_[];
     float* qs = asm_;                         // [G][hd] normalized, roped, scaled queries
     float* prob = asm_ + G * hd;              // [AT_WARPS][AT_TILE][G] tile probabilities
-    float* mrg = prob + AT_WARPS * AT_TILE * G;   // [AT_WARPS][G][2 + hd] merge buffer
+    // per-warp tile buffers; the merge buffer [AT_WARPS][G][2 + hd] reuses their space once every warp is done with its tiles
+    uint32_t* stage_base = reinterpret_cast<uint32_t*>(prob + AT_WARPS * AT_TILE * G);
+    float* mrg = reinterpret_cast<float*>(stage_base);
 
     // queries of this GQA group: rms_inplace(q, qn), rope, times 1/sqrt(hd)  (:1603-1606)
     for (int g = warp; g < G; g += AT_WARPS) {
@@ -403,7 +418,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
     float* pw = prob + warp * AT_TILE * G;
     float* mw = mrg + (size_t)warp * G * (2 + hd);
     // per-warp staging of one packed tile
-    uint32_t* tkw = reinterpret_cast<uint32_t*>(mrg + (size_t)AT_WARPS * G * (2 + hd)) + (size_t)warp * AT_STAGE_WORDS;
+    uint32_t* tkw = stage_base + (size_t)warp * AT_STAGE_WORDS;
     const int nsp = p.nsplit_packed, nrs = (int)gridDim.x - nsp;
     // tiles that are packed and entirely below the current length go to the tensor-core splits
     const int64_t tpk = nsp > 0 ? (q4n < n ? q4n : n) / AT_TILE : 0;
@@ -465,7 +480,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
                     const uint32_t w = tkw[(i0 + i) * (hd / 8) + lane];
                     const float s = tks[(i0 + i) * (hd / 32) + (lane >> 2)];
 #pragma unroll
-                    for (int j = 0; j < 8; j++) kv[j] = pb_kv4_dequant(w, j, s);
+                    for (int j = 0; j < 8; j++) kv[j] = pb_kv4_dequant8(w, j, s);
                 } else if (pp < n) {
                     const float4* src = reinterpret_cast<const float4*>(kr + (size_t)(pp % p.ring_cap) * hd + 8 * lane);
                     const float4 a = src[0], c = src[1];
@@ -521,7 +536,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
             if (packed) {
                 const float s = tvs[i * (hd / 32) + (lane >> 2)];
 #pragma unroll
-                for (int j = 0; j < 8; j++) vv[j] = pb_kv4_dequant(tvw[(i >> 3) * hd + 8 * lane + j], i & 7, s);   // position-transposed words
+                for (int j = 0; j < 8; j++) vv[j] = pb_kv4_dequant8(tvw[(i >> 3) * hd + 8 * lane + j], i & 7, s);   // position-transposed words
             } else {
                 const float4* src = reinterpret_cast<const float4*>(vr + (size_t)(pp % p.ring_cap) * hd + 8 * lane);
                 const float4 a = src[0], c = src[1];
@@ -537,6 +552,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
         __syncwarp();
     }
 
+    __syncthreads();   // the merge buffer overlays the tile buffers of all warps
 #pragma unroll
     for (int g = 0; g < G; g++) {
         if (lane == 0) { mw[g * (2 + hd)] = m_run[g]; mw[g * (2 + hd) + 1] = l_run[g]; }
@@ -621,7 +637,7 @@ int pb_launch_attn(pb_ctx* ctx, const PbAttnParams& p) {
     if (p.hd != 256 || p.nsplit > 128 || p.n_head % p.n_kv || (G != 8 && G != 4 && G != 2 && G != 1))
         PB_FAIL(ctx, PB_UNSUPPORTED, "attention: head dim %d with %d query heads per KV head not supported", p.hd, G);
     const dim3 grid(p.nsplit, p.n_kv, p.batch);
-    const size_t smem = ((size_t)G * p.hd + (size_t)AT_WARPS * AT_TILE * G + (size_t)AT_WARPS * G * (2 + p.hd) + (size_t)AT_WARPS * AT_STAGE_WORDS) * 4;
+    const size_t smem = ((size_t)G * p.hd + (size_t)AT_WARPS * AT_TILE * G + (size_t)AT_WARPS * AT_STAGE_WORDS) * 4;   // the merge buffer (AT_WARPS * G * (2 + hd) floats) fits inside the tile buffers
     if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "attention needs %zu bytes of shared memory", smem);
 #define GO(GG)                                                                                                                   \
     {                                                                                                                            \
@@ -639,19 +655,19 @@ int pb_launch_attn(pb_ctx* ctx, const PbAttnParams& p) {
     return PB_OK;
 }
 
-int pb_launch_kv4_pack(pb_ctx* ctx, const float* x, int64_t n, uint32_t* w, float* sc) {
+int pb_launch_kv4_pack(pb_ctx* ctx, const float* x, int64_t n, uint32_t* w, float* sc, int bias) {
     const int64_t nblocks = n / 32;
     if (nblocks <= 0) return PB_OK;
-    pb_launch_k(ctx, pb_kv4_pack_kernel, dim3((unsigned)((nblocks + 7) / 8)), dim3(256), (size_t)(0), x, nblocks, w, sc);
+    pb_launch_k(ctx, pb_kv4_pack_kernel, dim3((unsigned)((nblocks + 7) / 8)), dim3(256), (size_t)(0), x, nblocks, w, sc, bias);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;
 }
-int pb_launch_kv4_pack_vt(pb_ctx* ctx, const float* x, int64_t npos, int hd, uint32_t* w, float* sc) {
+int pb_launch_kv4_pack_vt(pb_ctx* ctx, const float* x, int64_t npos, int hd, uint32_t* w, float* sc, int bias) {
     if (npos <= 0) return PB_OK;
     if (npos % 8 || hd % 32) PB_FAIL(ctx, PB_ERR_ARG, "kv4 pack: %lld positions of %d dims (multiples of 8 and 32 needed)", (long long)npos, hd);
     const int64_t units = npos / 8 * (hd / 32);
-    pb_launch_k(ctx, pb_kv4_pack_vt_kernel, dim3((unsigned)((units + 7) / 8)), dim3(256), (size_t)(0), x, npos, hd, w, sc);
+    pb_launch_k(ctx, pb_kv4_pack_vt_kernel, dim3((unsigned)((units + 7) / 8)), dim3(256), (size_t)(0), x, npos, hd, w, sc, bias);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;

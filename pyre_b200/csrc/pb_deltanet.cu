@@ -36,6 +36,19 @@ __global__ void __launch_bounds__(DN_THREADS) pb_deltanet_kernel(const PbDeltaPa
     const int64_t pos = p.pos[b];
     const int wslot = (int)(pos % K);                       // slot that receives the current input
 
+    // the state slice is requested first: rows i in [warp*rpw, (warp+1)*rpw), column j0 + lane; its DRAM
+    // latency then overlaps the conv / norm / gate phases below, which do not depend on it
+    constexpr int rpw = RPW;   // rows per warp = dk / 8 (16 for dk = 128)
+    float* S = p.ssm + (((size_t)b * nv + h) * dk) * dv + j0 + lane;
+    float s[RPW];
+    // (only with few sequences: with thousands of CTAs the SM already overlaps them, and holding the slice
+    // through the first phases costs more than it hides)
+    const bool early = gridDim.y <= 4;
+    if (early) {
+#pragma unroll
+        for (int r = 0; r < rpw; r++) s[r] = S[(size_t)(warp * rpw + r) * dv];
+    }
+
     extern __shared__ float sm[];
     float* qs = sm;              // [dk] normalized q
     float* ks = sm + dk;         // [dk] normalized k
@@ -78,15 +91,12 @@ __global__ void __launch_bounds__(DN_THREADS) pb_deltanet_kernel(const PbDeltaPa
     const float g = expf(pb_softplus(alpha + p.dt[h]) * p.a[h]);
     const float bt = pb_sigm(beta);
 
-    // 4) state slice: rows i in [warp*rpw, (warp+1)*rpw), column j0 + lane
-    constexpr int rpw = RPW;   // rows per warp = dk / 8 (16 for dk = 128)
-    float* S = p.ssm + (((size_t)b * nv + h) * dk) * dv + j0 + lane;
-    float s[RPW];
+    // 4) state slice (loaded at the top)
     float mem = 0.f;
 #pragma unroll
     for (int r = 0; r < rpw; r++) {
         const int i = warp * rpw + r;
-        s[r] = S[(size_t)i * dv] * g;          // S *= g
+        s[r] = (early ? s[r] : S[(size_t)i * dv]) * g;   // S *= g
         mem = fmaf(s[r], ks[i], mem);           // mem_j = sum_i S[i][j] k_i
     }
     red[warp * DN_COLS + lane] = mem;

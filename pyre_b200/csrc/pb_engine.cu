@@ -366,6 +366,9 @@ static void seg(PbGemvQArgs& a, int i, pb_qmat* q, int64_t yoff) { a.seg[i].w = 
 // y (+)= W_segs . act(x) for all batch columns, in tiles of 16 columns
 static int gemv_cols(pb_ctx* ctx, PbGemvQArgs a, int B) {
     const float* x = a.x; float* y = a.y; const float* z = a.z; const uint32_t* xq = a.xq_in;
+    // the tensor-core path takes all columns at once (one staging pass for all its launches)
+    static const bool use_mma = !(getenv("PYRE_B200_MMA") && atoi(getenv("PYRE_B200_MMA")) == 0);
+    if (use_mma && a.mode != PB_ACT_PREQ && pb_gemmh_supported(a.type, a.cols, B) && (size_t)B * a.cols * 4 + 256 * (size_t)((B + 7) / 8) <= PB_XH_BYTES) { a.t = B; return pb_launch_gemvq(ctx, a); }
     for (int b0 = 0; b0 < B; b0 += 16) {
         a.t = B - b0 < 16 ? B - b0 : 16;
         a.x = x ? x + (int64_t)b0 * a.ldx : nullptr; a.y = y + (int64_t)b0 * a.ldy; a.z = z ? z + (int64_t)b0 * a.ldz : nullptr;
@@ -902,8 +905,8 @@ int pb_state_fill_kv(pb_state* s, int b, int ai, const float* k_host, const floa
             const size_t head = (size_t)b * nkv + h;
             if (q4n > 0) {
                 PB_CUDA(ctx, cudaMemcpyAsync(scr, tmp.data(), (size_t)q4n * hd * 4, cudaMemcpyHostToDevice, ctx->stream));
-                if (which) PB_TRY(pb_launch_kv4_pack_vt(ctx, (const float*)scr, q4n, hd, kv.vw + head * c.max_ctx * (hd / 8), kv.vs + head * c.max_ctx * (hd / 32)));
-                else PB_TRY(pb_launch_kv4_pack(ctx, (const float*)scr, q4n * hd, kv.kw + head * c.max_ctx * (hd / 8), kv.ks + head * c.max_ctx * (hd / 32)));
+                if (which) PB_TRY(pb_launch_kv4_pack_vt(ctx, (const float*)scr, q4n, hd, kv.vw + head * c.max_ctx * (hd / 8), kv.vs + head * c.max_ctx * (hd / 32), 8));
+                else PB_TRY(pb_launch_kv4_pack(ctx, (const float*)scr, q4n * hd, kv.kw + head * c.max_ctx * (hd / 8), kv.ks + head * c.max_ctx * (hd / 32), 8));
                 PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
             }
             float* ring = (which ? kv.vr : kv.kr) + head * s->ring_cap * hd;
@@ -931,8 +934,8 @@ int pb_state_fill_kv_synth(pb_state* s, int ai, int64_t n, uint64_t seed) {
             for (int h = 0; h < nkv; h++) {
                 const size_t head = (size_t)b * nkv + h;
                 PB_TRY(pb_launch_synth_normal_at(ctx, f, n * hd, seed, (uint64_t)ai * 2 + which, (int64_t)(head * c.max_ctx) * hd, 1.0f));
-                if (q4n > 0 && which) PB_TRY(pb_launch_kv4_pack_vt(ctx, f, q4n, hd, kv.vw + head * c.max_ctx * (hd / 8), kv.vs + head * c.max_ctx * (hd / 32)));
-                if (q4n > 0 && !which) PB_TRY(pb_launch_kv4_pack(ctx, f, q4n * hd, kv.kw + head * c.max_ctx * (hd / 8), kv.ks + head * c.max_ctx * (hd / 32)));
+                if (q4n > 0 && which) PB_TRY(pb_launch_kv4_pack_vt(ctx, f, q4n, hd, kv.vw + head * c.max_ctx * (hd / 8), kv.vs + head * c.max_ctx * (hd / 32), 8));
+                if (q4n > 0 && !which) PB_TRY(pb_launch_kv4_pack(ctx, f, q4n * hd, kv.kw + head * c.max_ctx * (hd / 8), kv.ks + head * c.max_ctx * (hd / 32), 8));
                 float* ring = (which ? kv.vr : kv.kr) + head * s->ring_cap * hd;
                 for (int64_t p = q4n; p < n;) {   // contiguous runs inside the ring
                     const int64_t slot = p % s->ring_cap, run = (n - p) < (s->ring_cap - slot) ? (n - p) : (s->ring_cap - slot);
@@ -955,7 +958,7 @@ int pb_kv4_pack(pb_ctx* ctx, const float* x_host, int64_t n, uint32_t* words_hos
     PB_TRY(pb_scratch(ctx, xb + wb + sb + 1024, &scr));
     float* xd = (float*)scr; uint32_t* wd = (uint32_t*)((uint8_t*)scr + xb); float* sd = (float*)((uint8_t*)scr + xb + wb);
     PB_CUDA(ctx, cudaMemcpyAsync(xd, x_host, xb, cudaMemcpyHostToDevice, ctx->stream));
-    PB_TRY(pb_launch_kv4_pack(ctx, xd, n, wd, sd));
+    PB_TRY(pb_launch_kv4_pack(ctx, xd, n, wd, sd, 0));
     PB_CUDA(ctx, cudaMemcpyAsync(words_host, wd, wb, cudaMemcpyDeviceToHost, ctx->stream));
     PB_CUDA(ctx, cudaMemcpyAsync(scales_host, sd, sb, cudaMemcpyDeviceToHost, ctx->stream));
     return pb_sync_check(ctx, "pb_kv4_pack");

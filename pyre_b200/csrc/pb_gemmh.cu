@@ -85,30 +85,40 @@ __device__ __forceinline__ void pb_xh_store(uint8_t* xh, int NT, int b, int c, f
     *reinterpret_cast<uint2*>(xh + pb_xh_off(blk, j, nt, NT, tq, 1, q)) = make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
 }
 
-// Activations of up to NB = 4 * NT tokens -> f16 high / low parts in B-fragment order, written once
-// to global memory for all CTAs of the GEMM; grid = NB CTAs (one token slot each, slots >= t are
-// zero), 256 threads.  PLAIN columns get an exact power-of-two prescale into [0.5, 1) (f16 neither
-// overflows nor loses small columns); its inverse goes to xinv.
-template <int NT>
-__global__ void __launch_bounds__(256) pb_xh_prep_kernel(const PbGemvQParams p, uint8_t* __restrict__ xh, float* __restrict__ xinv) {
+// Activations of all t tokens of a GEMM -> f16 high / low parts in B-fragment order, written once to
+// global memory for all CTAs of all its launches.  The tokens are cut into tiles of `tile` (16 or 8);
+// a tile of tt tokens uses NT = 1 / 2 / 4 n-tiles (4 * NT token slots, the unused ones zero) and lives at
+// xbuf + tile_index * tile_stride: 256 bytes of per-token prescale inverses, then the fragments.
+// grid = number of tiles * tile CTAs (one token slot each), 256 threads.  PLAIN columns get an exact
+// power-of-two prescale into [0.5, 1) (f16 neither overflows nor loses small columns).
+__global__ void __launch_bounds__(256) pb_xh_prep_kernel(const PbGemvQParams p, uint8_t* __restrict__ xbuf, int tile, size_t tile_stride) {
     constexpr int CT = 256;
-    const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int ti = (int)blockIdx.x / tile, b = (int)blockIdx.x - ti * tile;   // tile, slot inside the tile
+    const int tt = min(tile, p.t - ti * tile);                                  // tokens of this tile
+    const int NT = tt <= 4 ? 1 : (tt <= 8 ? 2 : 4);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cols = p.bpr * 256;
     __shared__ float red0[8];
     pb_pdl_wait();
     pb_pdl_trigger();
+    if (b >= 4 * NT) return;
+    const bool live = b < tt;
+    const float* x = p.x + (size_t)(ti * tile + b) * p.ldx;
+    const float* z = p.z ? p.z + (size_t)(ti * tile + b) * p.ldz : nullptr;
+    uint8_t* xh = xbuf + (size_t)ti * tile_stride + 256;
+    float* xinv = reinterpret_cast<float*>(xbuf + (size_t)ti * tile_stride);
     if (tid == 0) xinv[b] = 1.0f;
     if (p.mode == PB_ACT_GNORM) {
         const int nheads = cols / p.head_dim;   // head_dim == 128 (checked on the host)
         for (int h = warp; h < nheads; h += 8) {
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (b < p.t) {
-                v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + h * p.head_dim + 4 * lane);
+            if (live) {
+                v = *reinterpret_cast<const float4*>(x + h * p.head_dim + 4 * lane);
                 const float ss = pb_warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
                 const float s = 1.0f / sqrtf(ss / (float)p.head_dim + p.eps);
                 const float4 w = *reinterpret_cast<const float4*>(p.norm_w + 4 * lane);
-                const float4 z = *reinterpret_cast<const float4*>(p.z + b * p.ldz + h * p.head_dim + 4 * lane);
-                v.x = v.x * (s * w.x) * pb_sigm(z.x); v.y = v.y * (s * w.y) * pb_sigm(z.y); v.z = v.z * (s * w.z) * pb_sigm(z.z); v.w = v.w * (s * w.w) * pb_sigm(z.w);
+                const float4 zz = *reinterpret_cast<const float4*>(z + h * p.head_dim + 4 * lane);
+                v.x = v.x * (s * w.x) * pb_sigm(zz.x); v.y = v.y * (s * w.y) * pb_sigm(zz.y); v.z = v.z * (s * w.z) * pb_sigm(zz.z); v.w = v.w * (s * w.w) * pb_sigm(zz.w);
             }
             pb_xh_store(xh, NT, b, h * p.head_dim + 4 * lane, v);
         }
@@ -116,7 +126,7 @@ __global__ void __launch_bounds__(256) pb_xh_prep_kernel(const PbGemvQParams p, 
     }
     // one CTA-wide reduction: sum of squares (NORM) or largest magnitude (PLAIN)
     float r = 0.f;
-    if (b < p.t) for (int c = tid; c < cols; c += CT) { const float v = p.x[b * p.ldx + c]; r = p.mode == PB_ACT_NORM ? r + v * v : fmaxf(r, fabsf(v)); }
+    if (live) for (int c = tid; c < cols; c += CT) { const float v = x[c]; r = p.mode == PB_ACT_NORM ? r + v * v : fmaxf(r, fabsf(v)); }
     r = p.mode == PB_ACT_NORM ? pb_warp_sum(r) : pb_warp_max(r);
     if (lane == 0) red0[warp] = r;
     __syncthreads();
@@ -132,8 +142,8 @@ __global__ void __launch_bounds__(256) pb_xh_prep_kernel(const PbGemvQParams p, 
     }
     for (int c = tid * 4; c < cols; c += CT * 4) {
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (b < p.t) {
-            v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + c);
+        if (live) {
+            v = *reinterpret_cast<const float4*>(x + c);
             if (p.mode == PB_ACT_NORM) { const float4 w = *reinterpret_cast<const float4*>(p.norm_w + c); v.x = v.x * s * w.x; v.y = v.y * s * w.y; v.z = v.z * s * w.z; v.w = v.w * s * w.w; }
             else { v.x *= s; v.y *= s; v.z *= s; v.w *= s; }
         }
@@ -298,7 +308,7 @@ __global__ void __launch_bounds__(GH_THREADS, 1) pb_gemmh_iq3s_kernel(const PbGe
 }
 
 template <int NT, int NST>
-static int launch_h(pb_ctx* ctx, const PbGemvQArgs& a) {
+static int launch_h(pb_ctx* ctx, const PbGemvQArgs& a, const uint8_t* tile_buf) {
     constexpr int NB = 4 * NT;
     PbGemvQParams p;
     memset(&p, 0, sizeof p);
@@ -315,11 +325,7 @@ static int launch_h(pb_ctx* ctx, const PbGemvQArgs& a) {
     p.stage_bytes = (uint32_t)(((size_t)GH_ROWS * p.row_bytes + 16 + 127) & ~(size_t)127);
     const size_t smem = 256 + 16384 + (size_t)a.cols * NB * 4 + 2 * GH_CONSUMERS * GH_ROWS * NB * 4 + (size_t)NST * p.stage_bytes;
     if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "gemm: %zu bytes of shared memory needed for cols=%d t=%d", smem, a.cols, a.t);
-    // fragments of this launch's tokens, made once for all CTAs
-    p.xh_in = ctx->xh_buf + 256; p.xinv_in = reinterpret_cast<const float*>(ctx->xh_buf);
-    pb_launch_k(ctx, pb_xh_prep_kernel<NT>, dim3(NB), dim3(256), (size_t)0, p, ctx->xh_buf + 256, reinterpret_cast<float*>(ctx->xh_buf));
-    ctx->kernels_launched++;
-    PB_CUDA(ctx, cudaGetLastError());
+    p.xh_in = tile_buf + 256; p.xinv_in = reinterpret_cast<const float*>(tile_buf);
     auto kern = pb_gemmh_iq3s_kernel<NT, NST>;
     static size_t configured = 0;
     if (smem > configured) { PB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = smem; }
@@ -340,13 +346,26 @@ int pb_launch_gemmh(pb_ctx* ctx, const PbGemvQArgs& a) {
     // columns per launch: 16 with a 4-stage ring up to 2048 weight columns, 8 with a 2-stage ring above
     const bool wide = a.cols > 2048;
     const int tile = wide ? 8 : 16;
+    const int ntiles = (a.t + tile - 1) / tile;
+    const size_t tile_stride = 256 + (size_t)a.cols * tile * 4;
+    if (ntiles * tile_stride > PB_XH_BYTES) PB_FAIL(ctx, PB_UNSUPPORTED, "gemm: %d tokens of %d columns exceed the %d-byte fragment buffer", a.t, a.cols, (int)PB_XH_BYTES);
+    {   // fragments of all tokens, made once for all launches and CTAs of this GEMM
+        PbGemvQParams p;
+        memset(&p, 0, sizeof p);
+        p.bpr = a.cols / 256; p.x = a.x; p.ldx = a.ldx; p.t = a.t; p.mode = a.mode; p.norm_w = a.norm_w; p.z = a.z; p.ldz = a.ldz; p.head_dim = a.head_dim; p.eps = a.eps;
+        pb_launch_k(ctx, pb_xh_prep_kernel, dim3(ntiles * tile), dim3(256), (size_t)0, p, ctx->xh_buf, tile, tile_stride);
+        ctx->kernels_launched++;
+        PB_CUDA(ctx, cudaGetLastError());
+    }
     int rc = PB_OK;
-    for (int t0 = 0; t0 < a.t && rc == PB_OK; t0 += tile) {
+    for (int ti = 0; ti < ntiles && rc == PB_OK; ti++) {
+        const int t0 = ti * tile;
         PbGemvQArgs s = a;
         s.t = a.t - t0 < tile ? a.t - t0 : tile;
         s.x = a.x + (int64_t)t0 * a.ldx; s.y = a.y + (int64_t)t0 * a.ldy; s.z = a.z ? a.z + (int64_t)t0 * a.ldz : nullptr;
-        if (wide) rc = s.t <= 4 ? launch_h<1, 2>(ctx, s) : launch_h<2, 2>(ctx, s);
-        else rc = s.t <= 4 ? launch_h<1, 4>(ctx, s) : (s.t <= 8 ? launch_h<2, 4>(ctx, s) : launch_h<4, 4>(ctx, s));
+        const uint8_t* tb = ctx->xh_buf + (size_t)ti * tile_stride;
+        if (wide) rc = s.t <= 4 ? launch_h<1, 2>(ctx, s, tb) : launch_h<2, 2>(ctx, s, tb);
+        else rc = s.t <= 4 ? launch_h<1, 4>(ctx, s, tb) : (s.t <= 8 ? launch_h<2, 4>(ctx, s, tb) : launch_h<4, 4>(ctx, s, tb));
     }
     return rc;
 }

@@ -271,14 +271,14 @@ bool pb_gemvq_supported(int type, int cols) {
 int pb_launch_gemvq(pb_ctx* ctx, const PbGemvQArgs& a) {
     int el, bs;
     if (pb_geom(a.type, &el, &bs) || !pb_gemvq_supported(a.type, a.cols)) PB_FAIL(ctx, PB_UNSUPPORTED, "gemvq: type %d cols %d not supported by the integer kernel", a.type, a.cols);
-    if (a.t < 1 || a.t > 16) PB_FAIL(ctx, PB_ERR_ARG, "gemv: t=%d outside 1..16", a.t);
-    if (a.nseg < 1 || a.nseg > 4) PB_FAIL(ctx, PB_ERR_ARG, "gemv: %d segments", a.nseg);
-    if (a.mode == PB_ACT_GNORM && a.head_dim != 128) PB_FAIL(ctx, PB_UNSUPPORTED, "gemv: gated norm over heads of %d (128 is built)", a.head_dim);
-    if (((uintptr_t)a.x & 15) || (a.ldx & 3)) PB_FAIL(ctx, PB_ERR_ARG, "gemv: activations must be 16-byte aligned");
     if (a.mode != PB_ACT_PREQ && pb_gemmh_supported(a.type, a.cols, a.t)) {
         static const bool use_mma = !(getenv("PYRE_B200_MMA") && atoi(getenv("PYRE_B200_MMA")) == 0);
         if (use_mma) return pb_launch_gemmh(ctx, a);
     }
+    if (a.t < 1 || a.t > 16) PB_FAIL(ctx, PB_ERR_ARG, "gemv: t=%d outside 1..16", a.t);
+    if (a.nseg < 1 || a.nseg > 4) PB_FAIL(ctx, PB_ERR_ARG, "gemv: %d segments", a.nseg);
+    if (a.mode == PB_ACT_GNORM && a.head_dim != 128) PB_FAIL(ctx, PB_UNSUPPORTED, "gemv: gated norm over heads of %d (128 is built)", a.head_dim);
+    if (((uintptr_t)a.x & 15) || (a.ldx & 3)) PB_FAIL(ctx, PB_ERR_ARG, "gemv: activations must be 16-byte aligned");
     const int row_bytes = a.cols / el * bs;
     // column tiles: the int8-split activations of one launch must fit in ~96 KB of shared memory
     int tile = 16;

@@ -110,7 +110,7 @@ enum { PB_ACT_PLAIN = 0,   // x as given
        PB_ACT_GNORM = 2,   // per head of head_dim: rms(x) * norm_w[head_dim], times sigmoid(z)
        PB_ACT_PREQ = 3 };  // activations already split into int8 levels (xq_in)
 struct PbGemvSegArg { const uint8_t* w; int64_t rows; int64_t yoff; };
-#define PB_XH_BYTES (256 + 4096 * 16 * 4)
+#define PB_XH_BYTES ((size_t)8 << 20)   // fragment buffer of the tensor-core GEMM: t * cols * 4 bytes + 256 per tile (e.g. 512 tokens of 4096 columns)
 struct PbGemvQArgs {
     int type, cols, nseg;
     PbGemvSegArg seg[4];
@@ -212,8 +212,8 @@ struct PbAttnParams {
 };
 int pb_launch_kv_append(pb_ctx* ctx, const PbAttnParams& p);
 int pb_launch_attn(pb_ctx* ctx, const PbAttnParams& p);
-int pb_launch_kv4_pack(pb_ctx* ctx, const float* x, int64_t n, uint32_t* w, float* sc);
-int pb_launch_kv4_pack_vt(pb_ctx* ctx, const float* x, int64_t npos, int hd, uint32_t* w, float* sc);   // position-transposed V words
+int pb_launch_kv4_pack(pb_ctx* ctx, const float* x, int64_t n, uint32_t* w, float* sc, int bias);   // bias 0: kv4.rs nibbles; 8: cache form
+int pb_launch_kv4_pack_vt(pb_ctx* ctx, const float* x, int64_t npos, int hd, uint32_t* w, float* sc, int bias);   // position-transposed V words
 int pb_launch_kv4_unpack(pb_ctx* ctx, const uint32_t* w, const float* sc, int64_t n, float* x);
 
 // ---------------------------------------------------------------- pb_misc.cu
