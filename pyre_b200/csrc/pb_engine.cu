@@ -3,7 +3,9 @@
 // One decode step = one CUDA graph replay: embedding row -> per layer [fused RMSNorm +
 // projection GEMV, Gated DeltaNet step or 4-bit-KV gated attention, output projection with
 // residual add, router, top-k routing, grouped expert SwiGLU, combine] -> lm-head GEMV ->
-// argmax -> position advance.  Nothing returns to the host inside a token; the reference's
+// argmax -> position advance.  Windows of up to 8 consecutive tokens of one sequence (verify, prompt
+// feed) run as one pass that streams every weight once (run_window).  Nothing returns to the host
+// inside a token; the reference's
 // loop (forward_inner, src/model/qwen4exp_gguf.rs:2087-2157, layer_cube :728-895) reads
 // router logits back to the host in every layer.
 #include "pb_stream.cuh"
@@ -295,8 +297,8 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
         if (ns >= 8) s->nsplit_packed = ns - 1;
         else {
             // many (sequence, KV head) pairs: several CTAs per SM's worth of work, so that the tail wave stays short
-            int fine = 4 * ctx->sm_count / (c.n_kv * B);
-            if (fine > 8) fine = 8;
+            int fine = 8 * ctx->sm_count / (c.n_kv * B);
+            if (fine > 16) fine = 16;
             s->nsplit_packed = fine > ns ? fine : ns;
             ns = s->nsplit_packed + 1;
         }

@@ -6,13 +6,16 @@
 // (TMA) copies of whole row chunks into a 4-stage shared-memory ring, mbarrier full/empty
 // hand-off with bounded waits, sixteen consumer warps.  Arithmetic core (pb_qdot.cuh):
 //   - the CTA prepares the activations once: optional RMSNorm (plain or per-head gated), then
-//     a split into two int8 levels per 32 values;
+//     a split into PB_XLEVELS int8 levels per 32 values;
 //   - a lane owns a quarter super-step (64 weights) of a row, so block fields are fetched
 //     once per 64 weights; a warp covers 2048 columns of a row per pass (or several
 //     shorter rows side by side);
-//   - codebook entries are used as packed int8 directly (SWAR sign, dp4a); for large
-//     matrices the IQ3_S / IQ2_XS codebook is replicated once per shared-memory bank so that
-//     random lookups never conflict (64 KB of the 227 KB per SM).
+//   - codebook entries are used as packed int8 directly (dp4a); IQ3_S indices are built with prmt and
+//     its signs applied by arithmetic (xor 0xFE negates the odd grid values), because table reads
+//     made shared-memory wavefronts the bound; for large matrices the IQ3_S / IQ2_XS codebook is
+//     replicated once per shared-memory bank so that random lookups never conflict (64 KB of the
+//     227 KB per SM);
+//   - three or more columns of IQ3_S weights go to the tensor-core kernel of pb_gemmh.cu instead.
 // Replaces QMat::matmul (src/model/gguf_q.rs:217-242), the k_gemv* / k_gemv_iq4* kernels and
 // the k_rms* prologues (src/model/qn_cube.rs:257-2331) of the reference.
 #include "pb_stream.cuh"

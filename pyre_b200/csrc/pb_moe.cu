@@ -11,9 +11,12 @@
 //                         list of distinct local experts with their (token, slot) entries
 //   3. pb_expert_gu_kernel   h = silu(gate_e x) * (up_e x) for every (expert, token) entry and the
 //                         shared expert; weights streamed once per expert
-//   4. pb_expert_down_kernel part[token][slot] = w * (down_e h); shared expert unweighted
-//   5. pb_moe_combine_kernel y = sigmoid(shared gate) * shared + sum over slots in ascending
+//   4. pb_split_h_kernel  (several tokens) the hidden vectors of all entries split into int8 levels once
+//   5. pb_expert_down_kernel part[token][slot] = w * (down_e h); shared expert unweighted
+//   6. pb_moe_combine_kernel y = sigmoid(shared gate) * shared + sum over slots in ascending
 //                         expert id (fixed order: deterministic, independent of the GPU count)
+//   One token on one GPU replaces 4-6 by pb_expert_down_rows_kernel, which cuts the work by output rows
+//   and forms the same ordered sum inside each CTA.
 #include "pb_stream.cuh"
 #include "pb_internal.h"
 

@@ -8,7 +8,9 @@
 // Integer partial sums are exact; each group contributes one f32 FMA per level.  The split
 // keeps the result within f32 rounding noise of an f32-accumulated dot (the parity
 // tolerance is 1e-3), and turns byte->float conversion, sign handling and 8 FMAs per 8
-// weights into SWAR sign operations and PB_XLEVELS dp4a per 4 weights.
+// weights into SWAR sign operations and PB_XLEVELS dp4a per 4 weights.  IQ3_S, the format of the
+// model, has its own index / sign arithmetic (pb_iq3s_index, pb_iq3s_sign) and a fused decode + dot
+// for one column (pb_iq3s_quarter_dot).
 //
 // All block bytes and tables are read from shared memory through 32-bit shared-space
 // addresses (ld.shared), never through generic pointers.
