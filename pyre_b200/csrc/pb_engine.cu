@@ -57,7 +57,8 @@ struct pb_state {
     int win_t = 0; bool win_ckpt = false; int64_t* wpos = nullptr;
     int moe_cap = 0;   // rows of the MoE work buffers
     cudaGraphExec_t win_graph[4 * (PB_MAX_WINDOW + 1)] = {}; unsigned char win_runs[4 * (PB_MAX_WINDOW + 1)] = {};   // per (t, ckpt, all_logits)
-    float *xg = nullptr, *part_rs = nullptr;
+    float *xg = nullptr, *xs = nullptr, *part_rs = nullptr;   // gathered / local rows [token][d + logits], reduced partial rows
+    int64_t ldg = 0;                                          // row stride of xg / xs
     int64_t ldproj = 0, ring_cap = 0;
     std::vector<float*> conv, ssm;
     std::vector<PbKv> kv;
@@ -281,7 +282,8 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
     A(h, (size_t)Bm * c.top_k * c.ff_exp); A(h_sh, (size_t)Bm * c.ff_sh);
     A(hq, (size_t)Bm * (c.top_k + 1) * pb_xq_words(c.ff_exp > c.ff_sh ? c.ff_exp : c.ff_sh));
     A(part, (size_t)Bm * c.top_k * c.d); A(part_sh, (size_t)Bm * c.d);
-    if (s->sharded) { A(xg, (size_t)Bm * c.d); A(part_rs, (size_t)B * c.top_k * c.d); }
+    s->ldg = c.d + ((c.n_exp + 1 + 3) & ~3);
+    if (s->sharded) { A(xg, (size_t)Bm * s->ldg); A(xs, (size_t)B * s->ldg); A(part_rs, (size_t)B * c.top_k * c.d); }
     A(logits, (size_t)Ba * c.vocab);
     s->trace_cap = 4096;
     A(trace, (size_t)s->trace_cap * B); A(trace_len, 2);
@@ -469,18 +471,29 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
     const bool sh = s->sharded && t == s->batch;
     const int tt = sh ? s->moe_t : t, tok0 = sh ? s->tok0 : 0;
     if (s->sharded && !sh) PB_FAIL(ctx, PB_UNSUPPORTED, "a sharded state runs its MoE blocks on whole steps (%d tokens), not on %d", s->batch, t);
-    if (sh) {
-        PB_TRY(pb_ep_allgather(ctx, x_in, s->xg, (size_t)t * c.d));
-        ctx->pdl_chain = false;
-    }
     PbRouterParams r; memset(&r, 0, sizeof r);
-    r.x = sh ? s->xg : x_in; r.ldx = c.d; r.t = tt; r.cols = c.d; r.norm_w = norm_w; r.eps = c.eps;
+    r.cols = c.d; r.norm_w = norm_w; r.eps = c.eps;
     r.router = reinterpret_cast<const float*>(M(m, il, PB_R_ROUTER)->data); r.sh_gate_inp = V(m, il, PB_R_SH_GATE_INP); r.n_exp = c.n_exp;
-    r.logits = s->rlogits; r.xq_out = s->xq;
+    r.xq_out = s->xq;
     PbRouteParams q; memset(&q, 0, sizeof q);
-    q.logits = s->rlogits; q.t = tt; q.n_exp = c.n_exp; q.top_k = c.top_k; q.e_lo = m->e_lo; q.e_hi = m->e_hi;
+    q.t = tt; q.n_exp = c.n_exp; q.top_k = c.top_k; q.e_lo = m->e_lo; q.e_hi = m->e_hi;
     q.sel_e = s->sel_e; q.sel_w = s->sel_w; q.n_used = s->n_used; q.used_e = s->used_e; q.used_off = s->used_off;
     q.ent_tok = s->ent_tok; q.ent_slot = s->ent_slot; q.ent_w = s->ent_w;
+    const float* logits; int64_t ldl;
+    if (sh) {
+        // router logits of the local tokens, written next to a copy of their residual rows; one all-gather
+        // moves both; then every rank splits and routes all tokens
+        r.phase = 1; r.x = x_in; r.ldx = c.d; r.t = t; r.logits = s->xs + c.d; r.ldl = s->ldg; r.xcopy = s->xs;
+        PB_TRY(pb_launch_router(ctx, r, q, s->ticket));
+        PB_TRY(pb_ep_allgather(ctx, s->xs, s->xg, (size_t)t * s->ldg));
+        ctx->pdl_chain = false;
+        r.phase = 2; r.x = s->xg; r.ldx = s->ldg; r.t = tt; r.logits = s->xg + c.d; r.xcopy = nullptr;
+        logits = s->xg + c.d; ldl = s->ldg;
+    } else {
+        r.phase = 0; r.x = x_in; r.ldx = c.d; r.t = tt; r.logits = s->rlogits; r.ldl = c.n_exp + 1;
+        logits = s->rlogits; ldl = c.n_exp + 1;
+    }
+    q.logits = logits; q.ldl = ldl;
     PB_TRY(pb_launch_router(ctx, r, q, s->ticket));
     if (m->ep_world > 1) { PB_CUDA(ctx, cudaMemsetAsync(s->part, 0, (size_t)tt * c.top_k * c.d * 4, ctx->stream)); ctx->pdl_chain = false; }
     PbExpertParams e; memset(&e, 0, sizeof e);
@@ -500,7 +513,7 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
     if (tt > s->moe_cap) PB_FAIL(ctx, PB_ERR_ARG, "MoE block on %d tokens, buffers hold %d", tt, s->moe_cap);
     e.hq = tt > 1 && c.ff_exp == c.ff_sh ? s->hq : nullptr;   // several tokens: levels of the hidden vectors made once
     PbCombineParams k; memset(&k, 0, sizeof k);
-    k.part = s->part; k.part_sh = s->part_sh + (size_t)tok0 * c.d; k.logits = s->rlogits + (size_t)tok0 * (c.n_exp + 1); k.t = t; k.d = c.d; k.top_k = c.top_k; k.n_exp = c.n_exp;
+    k.part = s->part; k.part_sh = s->part_sh + (size_t)tok0 * c.d; k.logits = logits + (size_t)tok0 * ldl; k.ldl = ldl; k.t = t; k.d = c.d; k.top_k = c.top_k; k.n_exp = c.n_exp;
     k.y = y; k.ldy = ldy; k.accumulate = accumulate;
     // few tokens on one GPU: the down kernel's last CTA also combines (one launch less per layer)
     if (m->ep_world == 1 && (int64_t)t * c.d <= 8192) return pb_launch_expert_down(ctx, e, dn->type, c.ff_exp, &k, s->ticket + 1);

@@ -149,11 +149,15 @@ struct PbRouterParams {
     const float* router;                      // f32 [n_exp][cols]
     const float* sh_gate_inp;                 // f32 [cols] or null
     int n_exp;
-    float* logits;                            // [t][n_exp + 1], last = shared-gate logit
+    float* logits; int64_t ldl;               // [t][ldl >= n_exp + 1], entry n_exp = shared-gate logit
     uint32_t* xq_out;                         // [t][pb_xq_words(cols)] int8-split activations
+    // phase 0: everything.  Sharded tokens split it around the all-gather: phase 1 = logits of the local
+    // tokens plus a raw copy of their rows into xcopy (row stride ldl); phase 2 = split + routing of all
+    // gathered tokens (no GEMV)
+    int phase; float* xcopy;
 };
 struct PbRouteParams {
-    const float* logits; int t, n_exp, top_k;
+    const float* logits; int64_t ldl; int t, n_exp, top_k;
     int e_lo, e_hi;                           // experts held by this GPU
     int* sel_e; float* sel_w;                 // [t][top_k], ascending expert id
     int* n_used; int* used_e; int* used_off;  // distinct local experts, entry offsets [n_used + 1]
@@ -174,7 +178,7 @@ struct PbExpertParams {
     int* status;
 };
 struct PbCombineParams {
-    const float* part; const float* part_sh; const float* logits;
+    const float* part; const float* part_sh; const float* logits; int64_t ldl;
     int t, d, top_k, n_exp;
     float* y; int64_t ldy; int accumulate;
 };

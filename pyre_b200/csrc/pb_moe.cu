@@ -34,7 +34,7 @@ __device__ __forceinline__ void pb_route_body(const PbRouteParams& p, int* rsm) 
     for (int e = tid; e < 1024; e += 256) { cnt[e] = 0; cursor[e] = 0; }
     __syncthreads();
     for (int b = warp; b < p.t; b += 8) {
-        const float* lg = p.logits + (size_t)b * (p.n_exp + 1);
+        const float* lg = p.logits + (size_t)b * p.ldl;
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; i++) { const int e = i * 32 + lane; const float x = e < p.n_exp ? __ldcg(lg + e) : -INFINITY; v[i] = isnan(x) ? -INFINITY : x; }   // nan_clean :3121-3125
@@ -121,6 +121,7 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
     for (int g0 = blockIdx.x * 4; g0 < ng; g0 += gridDim.x * 4) {
         for (int b = b_lo + warp; b < b_hi; b += 8) {
             float4 v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + 32 * g0 + 4 * lane);
+            if (p.phase == 1) { *reinterpret_cast<float4*>(p.xcopy + b * p.ldl + 32 * g0 + 4 * lane) = v; continue; }   // raw row for the all-gather
             if (p.norm_w) {
                 const float4 n = *reinterpret_cast<const float4*>(p.norm_w + 32 * g0 + 4 * lane);
                 const float s = scale[b];
@@ -130,7 +131,7 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
         }
     }
     const int row = blockIdx.x * 8 + warp;
-    if (row <= p.n_exp) {
+    if (p.phase != 2 && row <= p.n_exp) {
         const float* wrow = row < p.n_exp ? p.router + (size_t)row * p.cols : p.sh_gate_inp;
         if (p.cols == 2048 && wrow) {
             // the row, times the norm weight, stays in registers for all tokens; the token's scale is
@@ -151,7 +152,7 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
                     a0 = fmaf(wr[k].x, v.x, a0); a1 = fmaf(wr[k].y, v.y, a1); a2 = fmaf(wr[k].z, v.z, a2); a3 = fmaf(wr[k].w, v.w, a3);
                 }
                 const float acc = pb_warp_sum((a0 + a1) + (a2 + a3)) * scale[b];
-                if (lane == 0) p.logits[b * (p.n_exp + 1) + row] = acc;
+                if (lane == 0) p.logits[b * p.ldl + row] = acc;
             }
         } else
         for (int b = b_lo; b < b_hi; b++) {
@@ -170,9 +171,10 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
                 }
                 acc = pb_warp_sum(acc);
             }
-            if (lane == 0) p.logits[b * (p.n_exp + 1) + row] = acc;
+            if (lane == 0) p.logits[b * p.ldl + row] = acc;
         }
     }
+    if (p.phase == 1) return;
     // the last CTA to get here routes all tokens: its reads of the logits follow every other CTA's
     // fence + ticket, the classic last-block pattern; the ticket is reset for the next launch
     __shared__ int is_last;
@@ -300,7 +302,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
 __device__ __forceinline__ void pb_combine_one(const PbCombineParams& p, int64_t i, bool bypass_l1) {
     const int tok = (int)(i / p.d), r = (int)(i - (int64_t)tok * p.d);
     float y = 0.f;
-    if (p.part_sh) y = (bypass_l1 ? __ldcg(p.part_sh + i) : p.part_sh[i]) * pb_sigm(p.logits[(size_t)tok * (p.n_exp + 1) + p.n_exp]);   // routed :1723
+    if (p.part_sh) y = (bypass_l1 ? __ldcg(p.part_sh + i) : p.part_sh[i]) * pb_sigm(p.logits[(size_t)tok * p.ldl + p.n_exp]);   // routed :1723
     float o = 0.f;
     for (int j = 0; j < p.top_k; j++) { const float* q = p.part + ((size_t)tok * p.top_k + j) * p.d + r; o += bypass_l1 ? __ldcg(q) : *q; }
     y += o;
@@ -548,7 +550,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_rows_kernel(con
     if (tid < PB_DR_ROWS) {
         // pb_combine_one for token sh_tok0: sigmoid(gate) * shared + sum over slots in ascending expert id
         float y = 0.f;
-        if (p.has_shared) y = __fmul_rn(res[n_used * PB_DR_ROWS + tid], pb_sigm(cp.logits[(size_t)p.sh_tok0 * (cp.n_exp + 1) + cp.n_exp]));
+        if (p.has_shared) y = __fmul_rn(res[n_used * PB_DR_ROWS + tid], pb_sigm(cp.logits[(size_t)p.sh_tok0 * cp.ldl + cp.n_exp]));
         float o = 0.f;
         // product rounded, then added (no fused multiply-add): the bits of the partial-row path
         for (int k = 0; k < n_used; k++) o = __fadd_rn(o, __fmul_rn(p.ent_w[p.used_off[k]], res[k * PB_DR_ROWS + tid]));
@@ -574,7 +576,7 @@ __global__ void __launch_bounds__(256) pb_moe_combine_kernel(const PbCombinePara
 int pb_launch_router(pb_ctx* ctx, const PbRouterParams& p, const PbRouteParams& rp, unsigned int* ticket) {
     if (p.cols % 128) PB_FAIL(ctx, PB_UNSUPPORTED, "router: width %d is not a multiple of 128", p.cols);
     if (rp.top_k > PB_MAX_TOPK || rp.n_exp > 1024) PB_FAIL(ctx, PB_UNSUPPORTED, "route: top_k %d / n_exp %d beyond %d / 1024", rp.top_k, rp.n_exp, PB_MAX_TOPK);
-    const int grid = (p.n_exp + 1 + 7) / 8;
+    const int grid = p.phase == 2 ? (p.cols / 128 > 0 ? p.cols / 128 : 1) : (p.n_exp + 1 + 7) / 8;   // phase 2 only splits (4 groups of 32 per CTA) and routes
     const size_t smem = (size_t)(2048 + ((p.t + 31) & ~31)) * 4;
     pb_launch_k(ctx, pb_router_kernel, dim3(grid, (p.t + PB_ROUTER_TPG - 1) / PB_ROUTER_TPG), dim3(256), smem, p, rp, ticket);
     ctx->kernels_launched++;
