@@ -341,6 +341,21 @@ def run_ours(args):
                 "clocks": clocks, "build_s": round(t_build, 1), "layers": cfg.n_layers}
         if not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(pb, B)
+    # ---- verify window (speculative decoding): 8 tokens in one batched pass on the tensor-core GEMM
+    verify = None
+    if world == 1 and B == 1 and not args.no_bs32:
+        win = np.arange(8, dtype=np.uint32) + 100
+        for _ in range(3):
+            st.forward_multi(win); st.spec_keep(8, 1)
+        torch.cuda.synchronize(); t0 = time.time()
+        reps = 5
+        for _ in range(reps):
+            st.forward_multi(win); st.spec_keep(8, 1)
+        torch.cuda.synchronize()
+        vms = (time.time() - t0) / reps * 1e3
+        verify = {"window": 8, "ms": round(vms, 3), "ms_per_token": round(vms / 8, 3), "note": "pb_verify + pb_keep, host ids in, 8 x vocab logits out, wall clock"}
+        if rank == 0:
+            line["verify"] = verify
     # ---- the batch-32 half of the headline metric: 32 sequences in all (32 / N per GPU when sharded)
     if B == 1 and not args.no_bs32 and (world == 1 or (sharded and 32 % world == 0)):
         st.destroy()
