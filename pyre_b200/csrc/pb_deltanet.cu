@@ -20,12 +20,14 @@
 #define DN_THREADS 256
 #define DN_COLS 32   // state columns per CTA
 
-template <int RPW>
+// NS = column slices of 32 one CTA walks in turn (1: most CTAs, shortest latency; dv / 32: the conv, norm and gate
+// phases run once per head instead of once per slice, which pays when there are thousands of CTAs)
+template <int RPW, int NS>
 __global__ void __launch_bounds__(DN_THREADS) pb_deltanet_kernel(const PbDeltaParams p) {
     const int nk = p.nk, nv = p.nv, dk = p.dk, dv = p.dv, K = p.conv_k;
     const int ch = 2 * nk * dk + nv * dv;
-    const int splits = dv / DN_COLS;
-    const int h = blockIdx.x / splits, j0 = (blockIdx.x % splits) * DN_COLS;
+    const int splits = dv / (DN_COLS * NS);
+    const int h = blockIdx.x / splits, j0 = (blockIdx.x % splits) * DN_COLS * NS;
     const int b = blockIdx.y;
     const int kh = h % nk;                                  // V head h reads K head h % nk (:1655)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -52,13 +54,13 @@ __global__ void __launch_bounds__(DN_THREADS) pb_deltanet_kernel(const PbDeltaPa
     extern __shared__ float sm[];
     float* qs = sm;              // [dk] normalized q
     float* ks = sm + dk;         // [dk] normalized k
-    float* vs = sm + 2 * dk;     // [DN_COLS]
-    float* red = sm + 2 * dk + DN_COLS;   // [8 warps][DN_COLS]
+    float* vs = sm + 2 * dk;     // [DN_COLS * NS]
+    float* red = sm + 2 * dk + DN_COLS * NS;   // [8 warps][DN_COLS]
     __shared__ float nrm[2];
 
     // 1) conv + SiLU for the channels this CTA needs: q and k of head kh, v columns j0..j0+31 of head h
     //    o = w[c*K + K-1] * cur + sum_{k < K-1} w[c*K + k] * hist[k]  (hist oldest first)   (:1645)
-    for (int i = tid; i < 2 * dk + DN_COLS; i += DN_THREADS) {
+    for (int i = tid; i < 2 * dk + DN_COLS * NS; i += DN_THREADS) {
         int c;
         if (i < dk) c = kh * dk + i;
         else if (i < 2 * dk) c = nk * dk + kh * dk + (i - dk);
@@ -91,47 +93,56 @@ __global__ void __launch_bounds__(DN_THREADS) pb_deltanet_kernel(const PbDeltaPa
     const float g = expf(pb_softplus(alpha + p.dt[h]) * p.a[h]);
     const float bt = pb_sigm(beta);
 
-    // 4) state slice (loaded at the top)
-    float mem = 0.f;
+    // 4) state slices (the first one was requested at the top when `early`)
+#pragma unroll 1
+    for (int sl = 0; sl < NS; sl++) {
+        float* Ss = S + sl * DN_COLS;
+        float mem = 0.f;
 #pragma unroll
-    for (int r = 0; r < rpw; r++) {
-        const int i = warp * rpw + r;
-        s[r] = (early ? s[r] : S[(size_t)i * dv]) * g;   // S *= g
-        mem = fmaf(s[r], ks[i], mem);           // mem_j = sum_i S[i][j] k_i
-    }
-    red[warp * DN_COLS + lane] = mem;
-    __syncthreads();
-    mem = 0.f;
+        for (int r = 0; r < rpw; r++) {
+            const int i = warp * rpw + r;
+            s[r] = ((early && sl == 0) ? s[r] : Ss[(size_t)i * dv]) * g;   // S *= g
+            mem = fmaf(s[r], ks[i], mem);           // mem_j = sum_i S[i][j] k_i
+        }
+        if (sl > 0) __syncthreads();                // the previous slice's readers of red are done
+        red[warp * DN_COLS + lane] = mem;
+        __syncthreads();
+        mem = 0.f;
 #pragma unroll
-    for (int w = 0; w < 8; w++) mem += red[w * DN_COLS + lane];
-    const float delta = (vs[lane] - mem) * bt;  // (:1663)
-    __syncthreads();
-    float o = 0.f;
+        for (int w = 0; w < 8; w++) mem += red[w * DN_COLS + lane];
+        const float delta = (vs[sl * DN_COLS + lane] - mem) * bt;  // (:1663)
+        __syncthreads();
+        float o = 0.f;
 #pragma unroll
-    for (int r = 0; r < rpw; r++) {
-        const int i = warp * rpw + r;
-        s[r] = fmaf(ks[i], delta, s[r]);        // S[i][j] += k_i * delta_j
-        o = fmaf(s[r], qs[i], o);                // o_j = sum_i S[i][j] q_i
-        S[(size_t)i * dv] = s[r];
-    }
-    red[warp * DN_COLS + lane] = o;
-    __syncthreads();
-    if (warp == 0) {
-        o = 0.f;
+        for (int r = 0; r < rpw; r++) {
+            const int i = warp * rpw + r;
+            s[r] = fmaf(ks[i], delta, s[r]);        // S[i][j] += k_i * delta_j
+            o = fmaf(s[r], qs[i], o);                // o_j = sum_i S[i][j] q_i
+            Ss[(size_t)i * dv] = s[r];
+        }
+        red[warp * DN_COLS + lane] = o;
+        __syncthreads();
+        if (warp == 0) {
+            o = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; w++) o += red[w * DN_COLS + lane];
-        p.out[(size_t)b * p.ldo + h * dv + j0 + lane] = o;   // readout before the gated norm
+            for (int w = 0; w < 8; w++) o += red[w * DN_COLS + lane];
+            p.out[(size_t)b * p.ldo + h * dv + j0 + sl * DN_COLS + lane] = o;   // readout before the gated norm
+        }
     }
 }
 
 int pb_launch_deltanet(pb_ctx* ctx, const PbDeltaParams& p) {
     if (p.dv % DN_COLS || (p.dk != 128 && p.dk != 64 && p.dk != 32) || p.conv_k < 2 || p.conv_k > 8)
         PB_FAIL(ctx, PB_UNSUPPORTED, "deltanet: dk=%d dv=%d conv_k=%d not supported", p.dk, p.dv, p.conv_k);
-    const dim3 grid(p.nv * (p.dv / DN_COLS), p.batch);
-    const size_t smem = (size_t)(2 * p.dk + DN_COLS + 8 * DN_COLS) * 4;
-    if (p.dk == 128) pb_launch_k(ctx, pb_deltanet_kernel<16>, dim3(grid), dim3(DN_THREADS), (size_t)(smem), p);
-    else if (p.dk == 64) pb_launch_k(ctx, pb_deltanet_kernel<8>, dim3(grid), dim3(DN_THREADS), (size_t)(smem), p);
-    else pb_launch_k(ctx, pb_deltanet_kernel<4>, dim3(grid), dim3(DN_THREADS), (size_t)(smem), p);
+    // many sequences: a CTA walks all slices of its head (conv / norm / gates once per head)
+    const bool whole = p.batch >= 8 && p.dv == 4 * DN_COLS;
+    const dim3 grid(p.nv * (whole ? 1 : p.dv / DN_COLS), p.batch);
+    const size_t smem = (size_t)(2 * p.dk + DN_COLS * (whole ? 4 : 1) + 8 * DN_COLS) * 4;
+#define GO(R)                                                                                             \
+    if (whole) pb_launch_k(ctx, pb_deltanet_kernel<R, 4>, dim3(grid), dim3(DN_THREADS), (size_t)(smem), p); \
+    else pb_launch_k(ctx, pb_deltanet_kernel<R, 1>, dim3(grid), dim3(DN_THREADS), (size_t)(smem), p);
+    if (p.dk == 128) { GO(16) } else if (p.dk == 64) { GO(8) } else { GO(4) }
+#undef GO
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;
