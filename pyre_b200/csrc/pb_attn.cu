@@ -442,8 +442,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
     uint32_t* tvw = reinterpret_cast<uint32_t*>(tks + AT_TILE * (hd / 32));
     float* tvs = reinterpret_cast<float*>(tvw + AT_TILE * (hd / 8));
 
-    for (int64_t t = tpk + (int64_t)warp * nrs + (sp - nsp); t < ntiles; t += (int64_t)AT_WARPS * nrs) {
-        const int64_t pbase = t * AT_TILE;
+    // scalar tiles: 32 positions when this path also walks packed tiles (no tensor-core splits), else 8, so that
+    // the f32 window spreads over many warps (a 32-position f32 tile is ten times a packed one and would
+    // alone set the kernel's duration)
+    const int stile = nsp > 0 ? 8 : AT_TILE;
+    const int64_t ntiles_s = (n + stile - 1) / stile;
+    for (int64_t t = tpk * (AT_TILE / stile) + (int64_t)warp * nrs + (sp - nsp); t < ntiles_s; t += (int64_t)AT_WARPS * nrs) {
+        const int64_t pbase = t * stile;
         // q4n is a multiple of 64 and tiles start at multiples of 32: a tile is entirely packed or entirely f32
         const bool packed = pbase < q4n;
         if (packed) {
@@ -469,7 +474,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
         float sc[G];
 #pragma unroll
         for (int g = 0; g < G; g++) sc[g] = -INFINITY;
-        for (int i0 = 0; i0 < AT_TILE; i0 += 8) {
+        for (int i0 = 0; i0 < stile; i0 += 8) {
             if (pbase + i0 >= n) break;
             float part[8 * G];
 #pragma unroll
@@ -510,7 +515,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
         }
         __syncwarp();
 #pragma unroll
-        for (int g = 0; g < G; g++) if (pbase + lane < n) sc[g] = pw[lane * G + g];
+        for (int g = 0; g < G; g++) if (lane < stile && pbase + lane < n) sc[g] = pw[lane * G + g];
         __syncwarp();
         // ---- online softmax over the tile (lane = position)
         float corr[G];
@@ -529,7 +534,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
         __syncwarp();
         // ---- P.V for the tile
 #pragma unroll 4
-        for (int i = 0; i < AT_TILE; i++) {
+        for (int i = 0; i < stile; i++) {
             const int64_t pp = pbase + i;
             if (pp >= n) break;
             float vv[8];

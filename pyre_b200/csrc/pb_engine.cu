@@ -424,11 +424,11 @@ static void attn_params(pb_state* s, int il, PbAttnParams& p) {
     p.pos = s->pos; p.q4n = k.q4n; p.part_ml = s->part_ml; p.part_acc = s->part_acc; p.nsplit = s->nsplit; p.nsplit_packed = s->nsplit_packed;
     if (s->nsplit_packed > 0) {
         // share the splits between the packed positions and the f32 ring by estimated work at the
-        // current length (an f32 tile costs about five packed tiles); a captured graph keeps the
+        // current length; a captured graph keeps the
         // share of its capture position, which drifts by a few tiles per thousand tokens
         const int64_t len = s->pos_host + 1;
         const int64_t q4 = len > c.kv_recent ? ((len - c.kv_recent) / 64) * 64 : 0;
-        const double wp = (double)(q4 / 32), wr = 5.0 * (double)((len - q4 + 31) / 32);
+        const double wp = (double)(q4 / 32), wr = 2.0 * (double)((len - q4 + 7) / 8);   // an f32 tile of 8 positions costs about two packed tiles of 32
         int nrs = (int)(s->nsplit * wr / (wr + wp) + 0.5);
         if (nrs < 1) nrs = 1;
         if (nrs > s->nsplit - 1) nrs = s->nsplit - 1;
