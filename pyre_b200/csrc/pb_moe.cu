@@ -19,6 +19,7 @@
 //   and forms the same ordered sum inside each CTA.
 #include "pb_stream.cuh"
 #include "pb_internal.h"
+#include "pb_topk.cuh"
 
 #include <stdio.h>
 
@@ -35,23 +36,20 @@ __device__ __forceinline__ void pb_route_body(const PbRouteParams& p, int* rsm) 
     __syncthreads();
     for (int b = warp; b < p.t; b += 8) {
         const float* lg = p.logits + (size_t)b * p.ldl;
-        float v[32];
+        // lane j keeps the j-th pick (descending logit, ties to the lower id, NaN as -inf: pb_topk.cuh)
+        unsigned long long pick;
+        if (p.n_exp <= 512) {
+            unsigned long long keys[16];
 #pragma unroll
-        for (int i = 0; i < 32; i++) { const int e = i * 32 + lane; const float x = e < p.n_exp ? __ldcg(lg + e) : -INFINITY; v[i] = isnan(x) ? -INFINITY : x; }   // nan_clean :3121-3125
-        int my_e = 0; float my_v = -INFINITY;     // lane j keeps the j-th pick (descending logit, ties to the lower id)
-        for (int j = 0; j < p.top_k; j++) {
-            float bv = -INFINITY; int be = 0x7fffffff;
+            for (int i = 0; i < 16; i++) { const int e = i * 32 + lane; keys[i] = e < p.n_exp ? pb_topk_key(__ldcg(lg + e), e) : 0ull; }
+            pick = pb_warp_topk<16>(keys, p.top_k, lane);
+        } else {
+            unsigned long long keys[32];
 #pragma unroll
-            for (int i = 0; i < 32; i++) { const int e = i * 32 + lane; if (e < p.n_exp && (v[i] > bv || (v[i] == bv && e < be))) { bv = v[i]; be = e; } }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, o); const int oe = __shfl_xor_sync(0xffffffffu, be, o);
-                if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
-            }
-            if (lane == j) { my_e = be; my_v = bv; }
-#pragma unroll
-            for (int i = 0; i < 32; i++) if (i * 32 + lane == be) v[i] = __int_as_float(0x7fc00000);   // taken: NaN never compares greater or equal
+            for (int i = 0; i < 32; i++) { const int e = i * 32 + lane; keys[i] = e < p.n_exp ? pb_topk_key(__ldcg(lg + e), e) : 0ull; }
+            pick = pb_warp_topk<32>(keys, p.top_k, lane);
         }
+        const int my_e = pb_topk_id(pick); const float my_v = pb_topk_val(pick);
         // softmax over the selection, summed in descending-logit order (top_k :3136-3138, soft_top :3126-3131)
         float mx = lane < p.top_k ? my_v : -INFINITY;
         mx = pb_warp_max(mx);
