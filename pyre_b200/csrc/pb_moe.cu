@@ -399,6 +399,11 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
         if (p.hq) {
             // several tokens: the hidden vectors were split by pb_split_h_kernel; decode each row once
             // and walk the entries of the expert with their levels read from global memory
+            // entry bookkeeping of the chunk (token, slot, weight), one entry per lane, requested before the decode:
+            // read inside the entry loop each of these global loads would stall the store that ends an entry
+            const bool lanes_hold = !shared && e1 - e0 <= 32;
+            int l_tok = 0, l_slot = 0; float l_w = 0.f;
+            if (lanes_hold && e0 + lane < e1) { l_tok = p.ent_tok[e0 + lane]; l_slot = p.ent_slot[e0 + lane]; l_w = p.ent_w[e0 + lane]; }
             for (int rb = warp * rpw; rb < p.rows_per_chunk; rb += PB_CONSUMERS * rpw) {
                 const int r = rb + sub;
                 PbQuarter wq[PASSES];
@@ -408,7 +413,10 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
                     if (qi < nquarters) D::quarter(base + (uint32_t)r * p.row_bytes + (qi >> 2) * D::STEP_BYTES, qi & 3, T, wq[ps]);
                 }
                 for (int en = e0; en < e1; en++) {
-                    const int tok = shared ? p.sh_tok0 + en : p.ent_tok[en];
+                    int tok, slot = 0; float wgt = 1.0f;
+                    if (lanes_hold) { tok = __shfl_sync(0xffffffffu, l_tok, en - e0); slot = __shfl_sync(0xffffffffu, l_slot, en - e0); wgt = __shfl_sync(0xffffffffu, l_w, en - e0); }
+                    else if (shared) tok = p.sh_tok0 + en;
+                    else { tok = p.ent_tok[en]; slot = p.ent_slot[en]; wgt = p.ent_w[en]; }
                     const uint32_t* xcol = en == e0 ? reinterpret_cast<const uint32_t*>(pb_ring_stage(ring, k) + bytes) : p.hq + (size_t)(shared ? p.t * p.top_k + tok : en) * xw;
                     float acc = 0.f;
 #pragma unroll
@@ -419,7 +427,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
                     for (int o = lpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
                     if (ql == 0) {
                         if (shared) p.part_sh[(size_t)tok * p.rows_e + r0 + r] = acc;
-                        else p.part[((size_t)tok * p.top_k + p.ent_slot[en]) * p.rows_e + r0 + r] = p.ent_w[en] * acc;
+                        else p.part[((size_t)tok * p.top_k + slot) * p.rows_e + r0 + r] = wgt * acc;
                     }
                 }
             }
