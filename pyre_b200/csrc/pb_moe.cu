@@ -188,6 +188,8 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
 
 // ------------------------------------------------------------------------------------ expert gate/up
 
+#define PB_SH_GROUP 4   // tokens per virtual shared expert (see pb_expert_gu_kernel)
+
 template <int FMT, int PASSES>
 __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbExpertParams p) {
     using D = PbQDec<FMT>;
@@ -207,7 +209,11 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
     const int cols = p.bpr * 256;
     const int n_used = *p.n_used;
     const int cpe = p.rows_e / p.rows_per_chunk;                       // chunks per routed expert
-    const int cps = p.has_shared ? p.rows_sh / p.rows_per_chunk : 0;   // chunks of the shared expert
+    // the shared expert serves every token: its tokens are cut into groups of PB_SH_GROUP, each group a
+    // virtual expert with its own chunks, so that no chunk carries 32 tokens' worth of dots (those chunks
+    // used to finish last and left most SMs idle)
+    const int cps1 = p.has_shared ? p.rows_sh / p.rows_per_chunk : 0;   // row chunks of the shared expert
+    const int cps = cps1 * ((p.sh_ntok + PB_SH_GROUP - 1) / PB_SH_GROUP);
     const int nchunks = n_used * cpe + cps;
     const int my_chunks = nchunks > (int)blockIdx.x ? (nchunks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
     const uint32_t half = (uint32_t)p.rows_per_chunk * p.row_bytes;   // a multiple of 16 by construction
@@ -226,12 +232,12 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
                     const size_t off = ((size_t)(e - p.e_base) * p.rows_e + r0) * p.row_bytes;
                     g = p.w_a + off; u = p.w_b + off;
                 } else {
-                    const size_t off = (size_t)(chunk - n_used * cpe) * p.rows_per_chunk * p.row_bytes;
+                    const size_t off = (size_t)((chunk - n_used * cpe) % cps1) * p.rows_per_chunk * p.row_bytes;
                     g = p.sh_a + off; u = p.sh_b + off;
                 }
                 // the activation levels of the chunk's first entry ride along, so that the consumers read them
                 // from shared memory instead of waiting for L2 after the decode
-                const int tok0 = chunk < n_used * cpe ? p.ent_tok[p.used_off[chunk / cpe]] : p.sh_tok0;
+                const int tok0 = chunk < n_used * cpe ? p.ent_tok[p.used_off[chunk / cpe]] : p.sh_tok0 + ((chunk - n_used * cpe) / cps1) * PB_SH_GROUP;
                 if (!pb_ring_acquire(ring, k, 2 * half + xbytes, p.status)) break;
                 pb_ring_copy(ring, k, 0, g, half);
                 pb_ring_copy(ring, k, half, u, half);
@@ -256,7 +262,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
         const bool shared = chunk >= n_used * cpe;
         int s = 0, r0, e0 = 0, e1;
         if (!shared) { s = chunk / cpe; r0 = (chunk - s * cpe) * p.rows_per_chunk; e0 = p.used_off[s]; e1 = p.used_off[s + 1]; }
-        else { r0 = (chunk - n_used * cpe) * p.rows_per_chunk; e1 = p.sh_ntok; }
+        else { const int sc = chunk - n_used * cpe; r0 = (sc % cps1) * p.rows_per_chunk; e0 = (sc / cps1) * PB_SH_GROUP; e1 = min(p.sh_ntok, e0 + PB_SH_GROUP); }
         const uint32_t base = pb_smem_u32(pb_ring_stage(ring, k));
         for (int rb = warp * rpw; rb < p.rows_per_chunk; rb += PB_CONSUMERS * rpw) {
             const int r = rb + sub;
@@ -346,7 +352,8 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
 
     const int n_used = *p.n_used;
     const int cpe = p.rows_e / p.rows_per_chunk;   // output rows (= model width) per expert / rows per chunk
-    const int cps = p.has_shared ? cpe : 0;
+    const int cps1 = p.has_shared ? cpe : 0;   // shared expert: token groups as in pb_expert_gu_kernel
+    const int cps = cps1 * ((p.sh_ntok + PB_SH_GROUP - 1) / PB_SH_GROUP);
     const int nchunks = n_used * cpe + cps;
     const int my_chunks = nchunks > (int)blockIdx.x ? (nchunks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
     const uint32_t bytes = (uint32_t)p.rows_per_chunk * p.row_bytes;
@@ -363,10 +370,10 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
                     const int e = p.used_e[s];
                     if (e < 0 || e >= p.n_exp) { atomicExch(p.status, PB_DEV_BAD_INDEX); break; }
                     src = p.w_a + ((size_t)(e - p.e_base) * p.rows_e + r0) * p.row_bytes;
-                } else src = p.sh_a + (size_t)(chunk - n_used * cpe) * p.rows_per_chunk * p.row_bytes;
+                } else src = p.sh_a + (size_t)((chunk - n_used * cpe) % cps1) * p.rows_per_chunk * p.row_bytes;
                 if (p.hq) {
                     // several tokens: the levels of the chunk's first hidden vector ride along with the weights
-                    const size_t slot = chunk < n_used * cpe ? (size_t)p.used_off[chunk / cpe] : (size_t)p.t * p.top_k + p.sh_tok0;
+                    const size_t slot = chunk < n_used * cpe ? (size_t)p.used_off[chunk / cpe] : (size_t)p.t * p.top_k + p.sh_tok0 + ((chunk - n_used * cpe) / cps1) * PB_SH_GROUP;
                     if (!pb_ring_acquire(ring, k, bytes + hbytes, p.status)) break;
                     pb_ring_copy(ring, k, 0, src, bytes);
                     pb_ring_copy(ring, k, bytes, p.hq + slot * xw, hbytes);
@@ -394,7 +401,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
         const bool shared = chunk >= n_used * cpe;
         int s = 0, r0, e0 = 0, e1;
         if (!shared) { s = chunk / cpe; r0 = (chunk - s * cpe) * p.rows_per_chunk; e0 = p.used_off[s]; e1 = p.used_off[s + 1]; }
-        else { r0 = (chunk - n_used * cpe) * p.rows_per_chunk; e1 = p.sh_ntok; }
+        else { const int sc = chunk - n_used * cpe; r0 = (sc % cps1) * p.rows_per_chunk; e0 = (sc / cps1) * PB_SH_GROUP; e1 = min(p.sh_ntok, e0 + PB_SH_GROUP); }
         const uint32_t base = pb_smem_u32(pb_ring_stage(ring, k));
         if (p.hq) {
             // several tokens: the hidden vectors were split by pb_split_h_kernel; decode each row once
