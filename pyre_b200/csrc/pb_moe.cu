@@ -219,32 +219,61 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
     const uint32_t half = (uint32_t)p.rows_per_chunk * p.row_bytes;   // a multiple of 16 by construction
     const uint32_t xbytes = (uint32_t)pb_xq_words(p.bpr * 256) * 4;   // one token's activation levels (a multiple of 16)
 
+    // chunk headers {first row, first entry, end entry, shared flag}, one per stage, written by the producer:
+    // the consumers start a chunk without a division or a dependent chain of global loads
+    int4* hdr = reinterpret_cast<int4*>(smem + 128);
     if (warp == PB_CONSUMERS) {
-        if (lane == 0) {
-            int k = 0;
-            for (; k < my_chunks; k++) {
-                const int chunk = (int)blockIdx.x + k * (int)gridDim.x;
-                const uint8_t *g, *u;
+        // the whole warp looks up the metadata of 32 chunks at a time (expert id, entry range, first token: up
+        // to three dependent global loads each, in parallel over the lanes); lane 0 then issues the copies
+        int k = 0; bool ok = true;
+        for (int k0 = 0; k0 < my_chunks && ok; k0 += 32) {
+            const int kk = k0 + lane;
+            int m_e = 0, m_r0 = 0, m_e0 = 0, m_e1 = 0, m_tok0 = 0, m_sh = 0;
+            if (kk < my_chunks) {
+                const int chunk = (int)blockIdx.x + kk * (int)gridDim.x;
                 if (chunk < n_used * cpe) {
-                    const int s = chunk / cpe, r0 = (chunk - s * cpe) * p.rows_per_chunk;
-                    const int e = p.used_e[s];
-                    if (e < 0 || e >= p.n_exp) { atomicExch(p.status, PB_DEV_BAD_INDEX); break; }
-                    const size_t off = ((size_t)(e - p.e_base) * p.rows_e + r0) * p.row_bytes;
-                    g = p.w_a + off; u = p.w_b + off;
+                    const int s = chunk / cpe;
+                    m_r0 = (chunk - s * cpe) * p.rows_per_chunk;
+                    m_e = p.used_e[s]; m_e0 = p.used_off[s]; m_e1 = p.used_off[s + 1];
+                    m_tok0 = m_e0 >= 0 && m_e0 < p.t * p.top_k ? p.ent_tok[m_e0] : -1;
                 } else {
-                    const size_t off = (size_t)((chunk - n_used * cpe) % cps1) * p.rows_per_chunk * p.row_bytes;
-                    g = p.sh_a + off; u = p.sh_b + off;
+                    const int sc = chunk - n_used * cpe;
+                    m_sh = 1; m_r0 = (sc % cps1) * p.rows_per_chunk;
+                    m_e0 = (sc / cps1) * PB_SH_GROUP; m_e1 = min(p.sh_ntok, m_e0 + PB_SH_GROUP);
+                    m_tok0 = p.sh_tok0 + m_e0;
                 }
-                // the activation levels of the chunk's first entry ride along, so that the consumers read them
-                // from shared memory instead of waiting for L2 after the decode
-                const int tok0 = chunk < n_used * cpe ? p.ent_tok[p.used_off[chunk / cpe]] : p.sh_tok0 + ((chunk - n_used * cpe) / cps1) * PB_SH_GROUP;
-                if (!pb_ring_acquire(ring, k, 2 * half + xbytes, p.status)) break;
-                pb_ring_copy(ring, k, 0, g, half);
-                pb_ring_copy(ring, k, half, u, half);
-                pb_ring_copy(ring, k, 2 * half, p.xq + (size_t)tok0 * pb_xq_words(p.bpr * 256), xbytes);
             }
-            if (k < my_chunks) pb_ring_drain(ring, k);
+            const int nk = min(32, my_chunks - k0);
+            for (int j = 0; j < nk; j++, k++) {
+                const int e = __shfl_sync(0xffffffffu, m_e, j), r0 = __shfl_sync(0xffffffffu, m_r0, j), e0 = __shfl_sync(0xffffffffu, m_e0, j);
+                const int e1 = __shfl_sync(0xffffffffu, m_e1, j), sh = __shfl_sync(0xffffffffu, m_sh, j);
+                int good = 1;
+                if (lane == 0) {
+                    if (!sh && (e < 0 || e >= p.n_exp)) { atomicExch(p.status, PB_DEV_BAD_INDEX); good = 0; }
+                    else if (!pb_ring_acquire_wait(ring, k, p.status)) good = 0;
+                    else {
+                        const uint8_t *g, *u;
+                        if (!sh) { const size_t off = ((size_t)(e - p.e_base) * p.rows_e + r0) * p.row_bytes; g = p.w_a + off; u = p.w_b + off; }
+                        else { const size_t off = (size_t)r0 * p.row_bytes; g = p.sh_a + off; u = p.sh_b + off; }
+                        hdr[k % PB_STAGES] = make_int4(r0, e0, e1, sh);
+                        pb_ring_announce(ring, k, 2 * half + xbytes);
+                        pb_ring_copy(ring, k, 0, g, half);
+                        pb_ring_copy(ring, k, half, u, half);
+                    }
+                }
+                good = __shfl_sync(0xffffffffu, good, 0);
+                if (!good) { ok = false; break; }
+                // the activation levels of the chunk's first entry ride along, so that the consumers read them from
+                // shared memory instead of waiting for L2 after the decode.  The token comes from a second dependent
+                // load, awaited only here, after the weights are on their way.
+                int tok0 = __shfl_sync(0xffffffffu, m_tok0, j);
+                if (lane == 0) {
+                    if (tok0 < 0 || tok0 >= p.t) { atomicExch(p.status, PB_DEV_BAD_INDEX); tok0 = 0; }   // the announced bytes must still arrive
+                    pb_ring_copy(ring, k, 2 * half, p.xq + (size_t)tok0 * pb_xq_words(p.bpr * 256), xbytes);
+                }
+            }
         }
+        if (!ok && lane == 0) pb_ring_drain(ring, k);
         return;
     }
 
@@ -258,11 +287,13 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
 
     for (int k = 0; k < my_chunks; k++) {
         if (!pb_ring_wait(ring, k, p.status)) return;
-        const int chunk = (int)blockIdx.x + k * (int)gridDim.x;
-        const bool shared = chunk >= n_used * cpe;
-        int s = 0, r0, e0 = 0, e1;
-        if (!shared) { s = chunk / cpe; r0 = (chunk - s * cpe) * p.rows_per_chunk; e0 = p.used_off[s]; e1 = p.used_off[s + 1]; }
-        else { const int sc = chunk - n_used * cpe; r0 = (sc % cps1) * p.rows_per_chunk; e0 = (sc / cps1) * PB_SH_GROUP; e1 = min(p.sh_ntok, e0 + PB_SH_GROUP); }
+        const int4 hd = hdr[k % PB_STAGES];
+        const int r0 = hd.x, e0 = hd.y, e1 = hd.z;
+        const bool shared = hd.w != 0;
+        // tokens of the entries after the first, one per lane, requested before the decode
+        const bool lanes_hold = e1 - e0 <= 33;
+        int l_tok = 0;
+        if (!shared && lanes_hold && e0 + 1 + lane < e1) l_tok = p.ent_tok[e0 + 1 + lane];
         const uint32_t base = pb_smem_u32(pb_ring_stage(ring, k));
         for (int rb = warp * rpw; rb < p.rows_per_chunk; rb += PB_CONSUMERS * rpw) {
             const int r = rb + sub;
@@ -276,7 +307,9 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
                 }
             }
             for (int en = e0; en < e1; en++) {
-                const int tok = shared ? p.sh_tok0 + en : p.ent_tok[en];
+                int tok = 0;
+                if (shared) tok = p.sh_tok0 + en;
+                else if (en > e0) tok = lanes_hold ? __shfl_sync(0xffffffffu, l_tok, en - e0 - 1) : p.ent_tok[en];
                 const uint32_t* xcol = en == e0 ? reinterpret_cast<const uint32_t*>(pb_ring_stage(ring, k) + 2 * half) : p.xq + (size_t)tok * xw;
                 float g = 0.f, u = 0.f;
 #pragma unroll
@@ -359,31 +392,52 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
     const uint32_t bytes = (uint32_t)p.rows_per_chunk * p.row_bytes;
     const uint32_t hbytes = (uint32_t)xw * 4;   // levels of one hidden vector (a multiple of 16)
 
+    int4* hdr = reinterpret_cast<int4*>(smem + 128);   // chunk headers as in pb_expert_gu_kernel
     if (warp == PB_CONSUMERS) {
-        if (lane == 0) {
-            int k = 0;
-            for (; k < my_chunks; k++) {
-                const int chunk = (int)blockIdx.x + k * (int)gridDim.x;
-                const uint8_t* src;
+        int k = 0; bool ok = true;
+        for (int k0 = 0; k0 < my_chunks && ok; k0 += 32) {
+            const int kk = k0 + lane;
+            int m_e = 0, m_r0 = 0, m_e0 = 0, m_e1 = 0, m_sh = 0;
+            if (kk < my_chunks) {
+                const int chunk = (int)blockIdx.x + kk * (int)gridDim.x;
                 if (chunk < n_used * cpe) {
-                    const int s = chunk / cpe, r0 = (chunk - s * cpe) * p.rows_per_chunk;
-                    const int e = p.used_e[s];
-                    if (e < 0 || e >= p.n_exp) { atomicExch(p.status, PB_DEV_BAD_INDEX); break; }
-                    src = p.w_a + ((size_t)(e - p.e_base) * p.rows_e + r0) * p.row_bytes;
-                } else src = p.sh_a + (size_t)((chunk - n_used * cpe) % cps1) * p.rows_per_chunk * p.row_bytes;
-                if (p.hq) {
-                    // several tokens: the levels of the chunk's first hidden vector ride along with the weights
-                    const size_t slot = chunk < n_used * cpe ? (size_t)p.used_off[chunk / cpe] : (size_t)p.t * p.top_k + p.sh_tok0 + ((chunk - n_used * cpe) / cps1) * PB_SH_GROUP;
-                    if (!pb_ring_acquire(ring, k, bytes + hbytes, p.status)) break;
-                    pb_ring_copy(ring, k, 0, src, bytes);
-                    pb_ring_copy(ring, k, bytes, p.hq + slot * xw, hbytes);
-                    continue;
+                    const int s = chunk / cpe;
+                    m_r0 = (chunk - s * cpe) * p.rows_per_chunk;
+                    m_e = p.used_e[s]; m_e0 = p.used_off[s]; m_e1 = p.used_off[s + 1];
+                } else {
+                    const int sc = chunk - n_used * cpe;
+                    m_sh = 1; m_r0 = (sc % cps1) * p.rows_per_chunk;
+                    m_e0 = (sc / cps1) * PB_SH_GROUP; m_e1 = min(p.sh_ntok, m_e0 + PB_SH_GROUP);
                 }
-                if (!pb_ring_acquire(ring, k, bytes, p.status)) break;
-                pb_ring_copy(ring, k, 0, src, bytes);
             }
-            if (k < my_chunks) pb_ring_drain(ring, k);
+            const int nk = min(32, my_chunks - k0);
+            for (int j = 0; j < nk; j++, k++) {
+                const int e = __shfl_sync(0xffffffffu, m_e, j), r0 = __shfl_sync(0xffffffffu, m_r0, j), e0 = __shfl_sync(0xffffffffu, m_e0, j);
+                const int e1 = __shfl_sync(0xffffffffu, m_e1, j), sh = __shfl_sync(0xffffffffu, m_sh, j);
+                int good = 1;
+                if (lane == 0) {
+                    if (!sh && (e < 0 || e >= p.n_exp || e0 < 0 || e0 >= p.t * p.top_k)) { atomicExch(p.status, PB_DEV_BAD_INDEX); good = 0; }
+                    else if (!pb_ring_acquire_wait(ring, k, p.status)) good = 0;
+                    else {
+                        const uint8_t* src = sh ? p.sh_a + (size_t)r0 * p.row_bytes : p.w_a + ((size_t)(e - p.e_base) * p.rows_e + r0) * p.row_bytes;
+                        hdr[k % PB_STAGES] = make_int4(r0, e0, e1, sh);
+                        if (p.hq) {
+                            // several tokens: the levels of the chunk's first hidden vector ride along with the weights
+                            const size_t slot = sh ? (size_t)p.t * p.top_k + p.sh_tok0 + e0 : (size_t)e0;
+                            pb_ring_announce(ring, k, bytes + hbytes);
+                            pb_ring_copy(ring, k, 0, src, bytes);
+                            pb_ring_copy(ring, k, bytes, p.hq + slot * xw, hbytes);
+                        } else {
+                            pb_ring_announce(ring, k, bytes);
+                            pb_ring_copy(ring, k, 0, src, bytes);
+                        }
+                    }
+                }
+                good = __shfl_sync(0xffffffffu, good, 0);
+                if (!good) { ok = false; break; }
+            }
         }
+        if (!ok && lane == 0) pb_ring_drain(ring, k);
         return;
     }
 
@@ -397,11 +451,9 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
 
     for (int k = 0; k < my_chunks; k++) {
         if (!pb_ring_wait(ring, k, p.status)) return;
-        const int chunk = (int)blockIdx.x + k * (int)gridDim.x;
-        const bool shared = chunk >= n_used * cpe;
-        int s = 0, r0, e0 = 0, e1;
-        if (!shared) { s = chunk / cpe; r0 = (chunk - s * cpe) * p.rows_per_chunk; e0 = p.used_off[s]; e1 = p.used_off[s + 1]; }
-        else { const int sc = chunk - n_used * cpe; r0 = (sc % cps1) * p.rows_per_chunk; e0 = (sc / cps1) * PB_SH_GROUP; e1 = min(p.sh_ntok, e0 + PB_SH_GROUP); }
+        const int4 hd = hdr[k % PB_STAGES];
+        const int r0 = hd.x, e0 = hd.y, e1 = hd.z;
+        const bool shared = hd.w != 0;
         const uint32_t base = pb_smem_u32(pb_ring_stage(ring, k));
         if (p.hq) {
             // several tokens: the hidden vectors were split by pb_split_h_kernel; decode each row once

@@ -31,6 +31,13 @@ __device__ __forceinline__ bool pb_ring_acquire(const PbRing& r, int k, uint32_t
     pb_mbar_expect_tx(&r.full[s], bytes);
     return true;
 }
+// the same in two steps, for a producer that writes a chunk header between them: wait until stage
+// k % S is writable, (plain shared-memory stores of the header), then announce `bytes`.  The arrive of
+// pb_ring_announce has release semantics and the consumers' wait acquires, so they see the header.
+__device__ __forceinline__ bool pb_ring_acquire_wait(const PbRing& r, int k, int* status) {
+    return k < PB_STAGES || pb_mbar_wait(&r.empty[k % PB_STAGES], ((k / PB_STAGES) - 1) & 1, status, PB_DEV_WAIT_EMPTY_TIMEOUT);
+}
+__device__ __forceinline__ void pb_ring_announce(const PbRing& r, int k, uint32_t bytes) { pb_mbar_expect_tx(&r.full[k % PB_STAGES], bytes); }
 __device__ __forceinline__ uint8_t* pb_ring_stage(const PbRing& r, int k) { return r.stages + (size_t)(k % PB_STAGES) * r.stage_bytes; }
 __device__ __forceinline__ void pb_ring_copy(const PbRing& r, int k, uint32_t dst_off, const void* src, uint32_t bytes) {
     pb_bulk_g2s(pb_ring_stage(r, k) + dst_off, src, bytes, &r.full[k % PB_STAGES]);
