@@ -55,6 +55,17 @@ __device__ __forceinline__ bool pb_mbar_wait(uint64_t* bar, uint32_t parity, int
     if (status) atomicExch(status, code);
     return false;
 }
+// The same for a waiter that is far ahead of the event (a producer waiting for a stage of its ring to be
+// released): it sleeps between the polls from the start.  A bare polling loop issues an instruction every few
+// cycles and takes a quarter of the issue slots of its SM sub-partition away from the warps that do the work.
+__device__ __forceinline__ bool pb_mbar_wait_relaxed(uint64_t* bar, uint32_t parity, int* status, int code) {
+    for (uint32_t i = 0; i < PB_SPIN_LIMIT; i++) {
+        if (pb_mbar_try_wait(bar, parity)) return true;
+        __nanosleep(256);
+    }
+    if (status) atomicExch(status, code);
+    return false;
+}
 // 1-D bulk copy global -> this CTA's shared memory, completion counted in bytes on `bar`.
 // Both addresses must be 16-byte aligned and `bytes` a multiple of 16.
 __device__ __forceinline__ void pb_bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {

@@ -200,7 +200,7 @@ __global__ void __launch_bounds__(GH_THREADS, 1) pb_gemmh_iq3s_kernel(const PbGe
                 const int nr = min(GH_ROWS, p.seg[s].rows - r0);
                 const uint32_t bytes = ((uint32_t)nr * (uint32_t)p.row_bytes + 15u) & ~15u;
                 const int st = k % NST;
-                if (k >= NST && !pb_mbar_wait(&ring.empty[st], ((k / NST) - 1) & 1, p.status, PB_DEV_WAIT_EMPTY_TIMEOUT)) break;
+                if (k >= NST && !pb_mbar_wait_relaxed(&ring.empty[st], ((k / NST) - 1) & 1, p.status, PB_DEV_WAIT_EMPTY_TIMEOUT)) break;
                 pb_mbar_expect_tx(&ring.full[st], bytes);
                 pb_bulk_g2s(ring.stages + (size_t)st * ring.stage_bytes, p.seg[s].w + (size_t)r0 * p.row_bytes, bytes, &ring.full[st]);
             }

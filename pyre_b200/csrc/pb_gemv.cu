@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) pb_gemv_f32_kernel(const Gemv
             bool ok = true;
             for (int k = 0; k < my_chunks && ok; k++) {
                 const int s = k % GEMV_STAGES;
-                if (k >= GEMV_STAGES) ok = pb_mbar_wait(&empty[s], ((k / GEMV_STAGES) - 1) & 1, p.status, PB_DEV_WAIT_EMPTY_TIMEOUT);
+                if (k >= GEMV_STAGES) ok = pb_mbar_wait_relaxed(&empty[s], ((k / GEMV_STAGES) - 1) & 1, p.status, PB_DEV_WAIT_EMPTY_TIMEOUT);
                 if (!ok) break;
                 const int64_t chunk = (int64_t)blockIdx.x + (int64_t)k * gridDim.x;
                 const int64_t r0 = chunk * p.rows_per_chunk;

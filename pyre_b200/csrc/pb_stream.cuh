@@ -27,7 +27,7 @@ __device__ __forceinline__ void pb_ring_init(const PbRing& r, int tid) {
 // producer (one thread): make stage k % S writable, announce `bytes`; the caller then issues the copies
 __device__ __forceinline__ bool pb_ring_acquire(const PbRing& r, int k, uint32_t bytes, int* status) {
     const int s = k % PB_STAGES;
-    if (k >= PB_STAGES && !pb_mbar_wait(&r.empty[s], ((k / PB_STAGES) - 1) & 1, status, PB_DEV_WAIT_EMPTY_TIMEOUT)) return false;
+    if (k >= PB_STAGES && !pb_mbar_wait_relaxed(&r.empty[s], ((k / PB_STAGES) - 1) & 1, status, PB_DEV_WAIT_EMPTY_TIMEOUT)) return false;
     pb_mbar_expect_tx(&r.full[s], bytes);
     return true;
 }
@@ -35,7 +35,7 @@ __device__ __forceinline__ bool pb_ring_acquire(const PbRing& r, int k, uint32_t
 // k % S is writable, (plain shared-memory stores of the header), then announce `bytes`.  The arrive of
 // pb_ring_announce has release semantics and the consumers' wait acquires, so they see the header.
 __device__ __forceinline__ bool pb_ring_acquire_wait(const PbRing& r, int k, int* status) {
-    return k < PB_STAGES || pb_mbar_wait(&r.empty[k % PB_STAGES], ((k / PB_STAGES) - 1) & 1, status, PB_DEV_WAIT_EMPTY_TIMEOUT);
+    return k < PB_STAGES || pb_mbar_wait_relaxed(&r.empty[k % PB_STAGES], ((k / PB_STAGES) - 1) & 1, status, PB_DEV_WAIT_EMPTY_TIMEOUT);
 }
 __device__ __forceinline__ void pb_ring_announce(const PbRing& r, int k, uint32_t bytes) { pb_mbar_expect_tx(&r.full[k % PB_STAGES], bytes); }
 __device__ __forceinline__ uint8_t* pb_ring_stage(const PbRing& r, int k) { return r.stages + (size_t)(k % PB_STAGES) * r.stage_bytes; }
