@@ -218,10 +218,11 @@ __device__ __forceinline__ uint4 pb_ldsv128(uint32_t a) { uint4 v; asm volatile(
 __device__ __forceinline__ float pb_exp2i(int k) { k = k < -126 ? -126 : (k > 127 ? 127 : k); return __int_as_float((k + 127) << 23); }
 
 // Packed positions on the tensor cores.  Thread (g, q) = (lane >> 2, lane & 3).
-//   S = Q K^T: A rows = query heads (rows >= G are zero), k = the 8 dims of one packed word, in
-//     the order (q, q+4) per thread, [Q_hi | Q_lo] side by side in k; B = K nibbles as f16, the
-//     same registers for both halves of k; column c of an 8-position group is position
-//     (c >> 1) + 4 (c & 1), so that a thread ends up with the scores of positions q and q + 4.
+//   S = Q K^T: A rows 0..7 = the query heads in f16 (rows >= G are zero), rows 8..15 = what the f16
+//     rounding of the same heads lost; k = the 16 dims of two packed words, in the order (q, q+4)
+//     per thread and word; B = K nibbles as f16; column c of an 8-position group is position
+//     (c >> 1) + 4 (c & 1), so that a thread ends up with the scores of positions q and q + 4
+//     (hi part in its row g, lo part in its row g + 8, added in f32).
 //   O^T = V^T P^T: A rows = 16 dims, k = the 8 positions of a group (nibbles q, q+4 of the
 //     transposed V word); B = [P_hi ; P_lo] times the V block scale (made per 32-dim block in
 //     f32, relative to a running power-of-two 2^E so that f16 neither overflows nor flushes).
@@ -230,11 +231,14 @@ __device__ __forceinline__ void pb_attn_mma_tiles(const float* qs, uint32_t* sta
                                                   const uint32_t* vw, const float* ks, const float* vs, int64_t ntiles, float* mw) {
     constexpr int HD = 256;
     const int g = lane >> 2, q = lane & 3, sh = 4 * q;
-    uint32_t qh[32], ql[32];
+    // A fragments of the scores: rows 0..7 = the f16 of the heads' queries, rows 8..15 = what that rounding lost;
+    // the 16 k of fragment i are the dims of cache words 2i and 2i + 1 (dims 8w + q and 8w + q + 4 per word w).
+    // Kept as register quads {hi w, lo w, hi w+1, lo w+1}: exactly the operand layout of the instruction.
+    uint32_t qa[16][4];
 #pragma unroll
     for (int i = 0; i < 32; i++) {
         const float x0 = g < G ? qs[g * HD + 8 * i + q] : 0.f, x1 = g < G ? qs[g * HD + 8 * i + q + 4] : 0.f;
-        pb_split_h2(x0, x1, qh[i], ql[i]);
+        pb_split_h2(x0, x1, qa[i >> 1][2 * (i & 1)], qa[i >> 1][2 * (i & 1) + 1]);
     }
     float m_run = -INFINITY, l_run = 0.f, acc[16][4];
 #pragma unroll
@@ -294,13 +298,11 @@ __device__ __forceinline__ void pb_attn_mma_tiles(const float* qs, uint32_t* sta
                 for (int blk = 0; blk < 8; blk++) {
                     const uint4 kk = pb_ldsv128(ka + blk * 16);
                     float c4[4] = {0.f, 0.f, 0.f, 0.f};
-                    uint32_t bb;
-                    bb = pb_nib2_h2(kk.x, sh); pb_mma16(c4, qh[4 * blk + 0], 0u, ql[4 * blk + 0], 0u, bb, bb);
-                    bb = pb_nib2_h2(kk.y, sh); pb_mma16(c4, qh[4 * blk + 1], 0u, ql[4 * blk + 1], 0u, bb, bb);
-                    bb = pb_nib2_h2(kk.z, sh); pb_mma16(c4, qh[4 * blk + 2], 0u, ql[4 * blk + 2], 0u, bb, bb);
-                    bb = pb_nib2_h2(kk.w, sh); pb_mma16(c4, qh[4 * blk + 3], 0u, ql[4 * blk + 3], 0u, bb, bb);
-                    s0 = fmaf(sk[blk], c4[0], s0);
-                    s1 = fmaf(sk[32 + blk], c4[1], s1);
+                    pb_mma16(c4, qa[2 * blk][0], qa[2 * blk][1], qa[2 * blk][2], qa[2 * blk][3], pb_nib2_h2(kk.x, sh), pb_nib2_h2(kk.y, sh));
+                    pb_mma16(c4, qa[2 * blk + 1][0], qa[2 * blk + 1][1], qa[2 * blk + 1][2], qa[2 * blk + 1][3], pb_nib2_h2(kk.z, sh), pb_nib2_h2(kk.w, sh));
+                    // rows g and g + 8 of the product: the hi and the lo part of the same score
+                    s0 = fmaf(sk[blk], c4[0] + c4[2], s0);
+                    s1 = fmaf(sk[32 + blk], c4[1] + c4[3], s1);
                 }
                 sbuf[nt * 32 + lane] = make_float2(s0, s1);
             }
