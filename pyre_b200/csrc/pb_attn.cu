@@ -223,9 +223,10 @@ __device__ __forceinline__ float pb_exp2i(int k) { k = k < -126 ? -126 : (k > 12
 //     per thread and word; B = K nibbles as f16; column c of an 8-position group is position
 //     (c >> 1) + 4 (c & 1), so that a thread ends up with the scores of positions q and q + 4
 //     (hi part in its row g, lo part in its row g + 8, added in f32).
-//   O^T = V^T P^T: A rows = 16 dims, k = the 8 positions of a group (nibbles q, q+4 of the
-//     transposed V word); B = [P_hi ; P_lo] times the V block scale (made per 32-dim block in
-//     f32, relative to a running power-of-two 2^E so that f16 neither overflows nor flushes).
+//   O^T = V^T P^T: A rows = 16 dims, k = the 16 positions of two groups (nibbles q, q+4 of the
+//     transposed V words); B = P times the V block scale (made per 32-dim block in f32, relative
+//     to a running power-of-two 2^E so that f16 neither overflows nor flushes), as f16 in one mma
+//     and the rounding remainder in a second one.
 template <int G>
 __device__ __forceinline__ void pb_attn_mma_tiles(const float* qs, uint32_t* stage, int warp, int lane, int sp, int nsp, const uint32_t* kw,
                                                   const uint32_t* vw, const float* ks, const float* vs, int64_t ntiles, float* mw) {
@@ -323,23 +324,27 @@ __device__ __forceinline__ void pb_attn_mma_tiles(const float* qs, uint32_t* sta
             const float ca = __shfl_sync(0xffffffffu, cf, 8 * q), cb = __shfl_sync(0xffffffffu, cf, 8 * q + 4);
 #pragma unroll
             for (int i = 0; i < 16; i++) { acc[i][0] *= ca; acc[i][1] *= cb; acc[i][2] *= ca; acc[i][3] *= cb; }
-            // ---- O^T += V^T (P * scale)^T
+            // ---- O^T += V^T (P * scale)^T, two 8-position groups per mma (k = 16 positions), once with the f16 of
+            //      the scaled probabilities and once with what that rounding lost
 #pragma unroll 1
-            for (int nt = 0; nt < 4; nt++) {
-                const float2 pr = sbuf[nt * 32 + lane];
-                const float* sv = tvs + (8 * nt + q) * 8;
-                const uint32_t va = tv_s + (uint32_t)(nt * HD + g) * 4;
+            for (int np = 0; np < 2; np++) {
+                const float2 pr0 = sbuf[(2 * np) * 32 + lane], pr1 = sbuf[(2 * np + 1) * 32 + lane];
+                const float* sv = tvs + (16 * np + q) * 8;
+                const uint32_t va = tv_s + (uint32_t)(2 * np * HD + g) * 4;
 #pragma unroll
                 for (int blk = 0; blk < 8; blk++) {
-                    const float f0 = pr.x * (sv[blk] * vscl), f1 = pr.y * (sv[32 + blk] * vscl);
-                    uint32_t bh, bl;
-                    pb_split_h2(f0, f1, bh, bl);
+                    uint32_t bh0, bl0, bh1, bl1;
+                    pb_split_h2(pr0.x * (sv[blk] * vscl), pr0.y * (sv[32 + blk] * vscl), bh0, bl0);
+                    pb_split_h2(pr1.x * (sv[64 + blk] * vscl), pr1.y * (sv[96 + blk] * vscl), bh1, bl1);
 #pragma unroll
                     for (int h2 = 0; h2 < 2; h2++) {
                         const int mtile = 2 * blk + h2;
                         const uint32_t a0 = pb_nib2_h2(pb_ldsv32(va + (uint32_t)(16 * mtile) * 4), sh);
                         const uint32_t a1 = pb_nib2_h2(pb_ldsv32(va + (uint32_t)(16 * mtile + 8) * 4), sh);
-                        pb_mma16(acc[mtile], a0, a1, a0, a1, bh, bl);
+                        const uint32_t a2 = pb_nib2_h2(pb_ldsv32(va + (uint32_t)(HD + 16 * mtile) * 4), sh);
+                        const uint32_t a3 = pb_nib2_h2(pb_ldsv32(va + (uint32_t)(HD + 16 * mtile + 8) * 4), sh);
+                        pb_mma16(acc[mtile], a0, a1, a2, a3, bh0, bh1);
+                        pb_mma16(acc[mtile], a0, a1, a2, a3, bl0, bl1);
                     }
                 }
             }
