@@ -62,6 +62,16 @@ template <int J> __device__ __forceinline__ uint32_t pb_iq3s_index(uint32_t qs_w
 // IQ3_S grid values are odd (1, 3, .. 15), so xor with 0xFE negates a byte: -g = g ^ 0xFE.
 // c = pb_spread4 of the entry's four sign bits.
 __device__ __forceinline__ int pb_iq3s_sign(uint32_t g, uint32_t c) { return (int)(g ^ (c * 254u)); }
+// The same from the packed sign bits: entry J (0..7) of a 32-weight half takes bits 4J..4J+3 of `sg`.
+// n * 0x10204080 puts bit k of the nibble n at bit 8k + 7 (no two partial products meet, so no carries);
+// prmt in sign-replication mode turns those into bytes 0x00 / 0xFF; one logic op then flips bits 1..7
+// of the selected bytes.  Odd entries keep their nibble in place (n << 4) and multiply by the constant
+// shifted down by 4, which saves the shift.
+template <int J> __device__ __forceinline__ int pb_iq3s_sign8(uint32_t g, uint32_t sg) {
+    const uint32_t t = (J >> 1) ? sg >> (8 * (J >> 1)) : sg;
+    const uint32_t m = (J & 1) ? (t & 0xF0u) * 0x01020408u : (t & 0xFu) * 0x10204080u;
+    return (int)(g ^ (pb_prmt(m, 0u, 0xBA98u) & 0xFEFEFEFEu));
+}
 
 struct PbQuarter {
     int w[16];      // packed signed int8, weight 4k+j of the quarter in byte j of w[k]
@@ -87,11 +97,13 @@ template <> struct PbQDec<PB_T_IQ3_S> {
 #pragma unroll
         for (int k = 0; k < 4; k++) {          // four entries: one qs word, four high bits, two sign bytes
             const uint32_t hb = pb_spread4((qh >> (4 * k)) & 0xF);
-            const uint32_t sw = sg[k >> 1] >> (16 * (k & 1));
-            o.w[4 * k + 0] = pb_iq3s_sign(pb_lds32(T.grid + pb_iq3s_index<0>(qs[k], hb) * T.stride), pb_spread4(sw & 0xF));
-            o.w[4 * k + 1] = pb_iq3s_sign(pb_lds32(T.grid + pb_iq3s_index<1>(qs[k], hb) * T.stride), pb_spread4((sw >> 4) & 0xF));
-            o.w[4 * k + 2] = pb_iq3s_sign(pb_lds32(T.grid + pb_iq3s_index<2>(qs[k], hb) * T.stride), pb_spread4((sw >> 8) & 0xF));
-            o.w[4 * k + 3] = pb_iq3s_sign(pb_lds32(T.grid + pb_iq3s_index<3>(qs[k], hb) * T.stride), pb_spread4((sw >> 12) & 0xF));
+            const uint32_t sw = sg[k >> 1];
+            const uint32_t g0 = pb_lds32(T.grid + pb_iq3s_index<0>(qs[k], hb) * T.stride), g1 = pb_lds32(T.grid + pb_iq3s_index<1>(qs[k], hb) * T.stride);
+            const uint32_t g2 = pb_lds32(T.grid + pb_iq3s_index<2>(qs[k], hb) * T.stride), g3 = pb_lds32(T.grid + pb_iq3s_index<3>(qs[k], hb) * T.stride);
+            o.w[4 * k + 0] = (k & 1) ? pb_iq3s_sign8<4>(g0, sw) : pb_iq3s_sign8<0>(g0, sw);
+            o.w[4 * k + 1] = (k & 1) ? pb_iq3s_sign8<5>(g1, sw) : pb_iq3s_sign8<1>(g1, sw);
+            o.w[4 * k + 2] = (k & 1) ? pb_iq3s_sign8<6>(g2, sw) : pb_iq3s_sign8<2>(g2, sw);
+            o.w[4 * k + 3] = (k & 1) ? pb_iq3s_sign8<7>(g3, sw) : pb_iq3s_sign8<3>(g3, sw);
         }
     }
 };
@@ -227,9 +239,8 @@ __device__ __forceinline__ float pb_iq3s_quarter_dot(uint32_t p, int qt, const P
             const uint32_t g2 = pb_lds32(T.grid + i2 * T.stride), g3 = pb_lds32(T.grid + i3 * T.stride);
             // signs by arithmetic: shared-memory wavefronts, not issue slots, bound this loop when the
             // masks came from a table
-            const uint32_t sw = sg[h] >> (16 * k);
-            const int w0 = pb_iq3s_sign(g0, pb_spread4(sw & 0xF)), w1 = pb_iq3s_sign(g1, pb_spread4((sw >> 4) & 0xF));
-            const int w2 = pb_iq3s_sign(g2, pb_spread4((sw >> 8) & 0xF)), w3 = pb_iq3s_sign(g3, pb_spread4((sw >> 12) & 0xF));
+            const int w0 = k ? pb_iq3s_sign8<4>(g0, sg[h]) : pb_iq3s_sign8<0>(g0, sg[h]), w1 = k ? pb_iq3s_sign8<5>(g1, sg[h]) : pb_iq3s_sign8<1>(g1, sg[h]);
+            const int w2 = k ? pb_iq3s_sign8<6>(g2, sg[h]) : pb_iq3s_sign8<2>(g2, sg[h]), w3 = k ? pb_iq3s_sign8<7>(g3, sg[h]) : pb_iq3s_sign8<3>(g3, sg[h]);
             const int e = 8 * h + 4 * k;
 #pragma unroll
             for (int l = 0; l < PB_XLEVELS; l++) {
