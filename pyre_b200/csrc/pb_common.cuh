@@ -50,7 +50,7 @@ __device__ __forceinline__ bool pb_mbar_try_wait(uint64_t* bar, uint32_t parity)
 __device__ __forceinline__ bool pb_mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
     for (uint32_t i = 0; i < PB_SPIN_LIMIT; i++) {
         if (pb_mbar_try_wait(bar, parity)) return true;
-        if (i > 256) __nanosleep(64);
+        if (i > 32) __nanosleep(96);
     }
     if (status) atomicExch(status, code);
     return false;
