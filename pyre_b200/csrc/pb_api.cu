@@ -128,12 +128,28 @@ static int qmat_alloc(pb_ctx* ctx, int type, int64_t rows, int64_t cols, pb_qmat
     return PB_OK;
 }
 
+// IQ3_S matrices get a second copy in the re-coded form the streaming kernels read (pb_repack.cu).
+// PYRE_B200_REPACK=0 keeps only the native bytes (the kernels then decode IQ3_S itself).
+static int qmat_recode(pb_ctx* ctx, pb_qmat* m) {
+    static const bool on = !(getenv("PYRE_B200_REPACK") && atoi(getenv("PYRE_B200_REPACK")) == 0);
+    const int64_t bpr = m->cols / 256;
+    if (!on || m->type != PB_T_IQ3_S || m->cols % 256 || (bpr & 1)) return PB_OK;   // rows of the copy must stay 16-byte aligned
+    m->r_row_bytes = bpr * 136;
+    const size_t nb = (size_t)m->rows * (size_t)m->r_row_bytes;
+    cudaError_t e = cudaMalloc(&m->rdata, nb + 256);
+    if (e != cudaSuccess) { m->rdata = nullptr; PB_FAIL(ctx, PB_ERR_OOM, "cudaMalloc(%zu) for the re-coded copy: %s", nb + 256, cudaGetErrorString(e)); }
+    cudaMemsetAsync(m->rdata + nb, 0, 256, ctx->stream);
+    return pb_launch_repack_iq3s(ctx, m->data, m->rdata, m->rows * bpr);
+}
+
 int pb_qmat_upload(pb_ctx* ctx, int type, int64_t rows, int64_t cols, const void* bytes, size_t nbytes, pb_qmat** out) {
     if (!ctx) return PB_ERR_ARG;
     if (!bytes) PB_FAIL(ctx, PB_ERR_ARG, "pb_qmat_upload: null data");
     PB_TRY(qmat_alloc(ctx, type, rows, cols, out));
     if (nbytes != (*out)->nbytes) { size_t want = (*out)->nbytes; pb_qmat_free(*out); *out = nullptr; PB_FAIL(ctx, PB_ERR_ARG, "pb_qmat_upload: %zu bytes given, %zu expected", nbytes, want); }
     PB_CUDA(ctx, cudaMemcpyAsync((*out)->data, bytes, nbytes, cudaMemcpyHostToDevice, ctx->stream));
+    int rc = qmat_recode(ctx, *out);
+    if (rc != PB_OK) { pb_qmat_free(*out); *out = nullptr; return rc; }
     PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return PB_OK;
 }
@@ -150,13 +166,14 @@ int pb_qmat_synth_rows(pb_ctx* ctx, int type, int64_t rows, int64_t cols, uint64
     int rc;
     if (type == PB_T_F32) rc = pb_launch_synth_normal_at(ctx, reinterpret_cast<float*>(m->data), rows * cols, seed, tid, row0 * cols, 0.02f);
     else { int el, bs; pb_geom(type, &el, &bs); rc = pb_launch_synth(ctx, type, m->data, rows * (cols / el), seed, tid, row0 * (cols / el)); }
+    if (rc == PB_OK) rc = qmat_recode(ctx, m);
     if (rc != PB_OK) { pb_qmat_free(m); *out = nullptr; }
     return rc;
 }
 
 int pb_qmat_free(pb_qmat* m) {
     if (!m) return PB_OK;
-    if (m->owns && m->data) { cudaSetDevice(m->ctx->device); cudaStreamSynchronize(m->ctx->stream); cudaFree(m->data); }
+    if (m->owns && m->data) { cudaSetDevice(m->ctx->device); cudaStreamSynchronize(m->ctx->stream); cudaFree(m->data); if (m->rdata) cudaFree(m->rdata); }
     delete m;
     return PB_OK;
 }
@@ -211,7 +228,7 @@ int pb_gemv_dev(pb_ctx* ctx, const pb_qmat* m, const float* x, int t, float* y) 
     if (t < 0) PB_FAIL(ctx, PB_ERR_ARG, "pb_gemv: t=%d", t);
     for (int t0 = 0; t0 < t; t0 += 16) {
         PbGemvArgs a;
-        a.w = m->data; a.type = m->type; a.rows = m->rows; a.cols = (int)m->cols;
+        a.w = m->data; a.wr = m->rdata; a.type = m->type; a.rows = m->rows; a.cols = (int)m->cols;
         a.x = x + (int64_t)t0 * m->cols; a.ldx = m->cols; a.t = t - t0 < 16 ? t - t0 : 16;
         a.y = y + (int64_t)t0 * m->rows; a.ldy = m->rows;
         PB_TRY(pb_launch_gemv(ctx, a));

@@ -365,7 +365,7 @@ int pb_state_pos(const pb_state* s, int64_t* pos) { if (!s || !pos) return PB_ER
 
 // ---- layer pieces -----------------------------------------------------------------------------
 
-static void seg(PbGemvQArgs& a, int i, pb_qmat* q, int64_t yoff) { a.seg[i].w = q->data; a.seg[i].rows = q->rows; a.seg[i].yoff = yoff; }
+static void seg(PbGemvQArgs& a, int i, pb_qmat* q, int64_t yoff) { a.seg[i].w = q->data; a.seg[i].wr = q->rdata; a.seg[i].rows = q->rows; a.seg[i].yoff = yoff; }
 
 // y (+)= W_segs . act(x) for all batch columns, in tiles of 16 columns
 static int gemv_cols(pb_ctx* ctx, PbGemvQArgs a, int B) {
@@ -503,12 +503,18 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
     e.sh_tok0 = tok0; e.sh_ntok = t;   // the shared expert runs where the token lives
     pb_qmat* g = M(m, il, PB_R_EXP_GATE);
     e.e_base = g->rows == (int64_t)c.ff_exp * c.n_exp ? 0 : m->e_lo;
-    e.w_a = g->data; e.w_b = M(m, il, PB_R_EXP_UP)->data; e.sh_a = M(m, il, PB_R_SH_GATE)->data; e.sh_b = M(m, il, PB_R_SH_UP)->data;
+    pb_qmat *up = M(m, il, PB_R_EXP_UP), *shg = M(m, il, PB_R_SH_GATE), *shu = M(m, il, PB_R_SH_UP);
+    e.w_a = g->data; e.w_b = up->data; e.sh_a = shg->data; e.sh_b = shu->data;
+    int gu_type = g->type;
+    if (g->rdata && up->rdata && shg->rdata && shu->rdata) { e.w_a = g->rdata; e.w_b = up->rdata; e.sh_a = shg->rdata; e.sh_b = shu->rdata; gu_type = PB_T_IQ3S_N4; }   // re-coded copies
     e.rows_e = c.ff_exp; e.rows_sh = c.ff_sh;
-    PB_TRY(pb_launch_expert_gu(ctx, e, g->type, c.d));
+    PB_TRY(pb_launch_expert_gu(ctx, e, gu_type, c.d));
     pb_qmat* dn = M(m, il, PB_R_EXP_DOWN);
     e.e_base = dn->rows == (int64_t)c.d * c.n_exp ? 0 : m->e_lo;
-    e.w_a = dn->data; e.w_b = nullptr; e.sh_a = M(m, il, PB_R_SH_DOWN)->data; e.sh_b = nullptr;
+    pb_qmat* shd = M(m, il, PB_R_SH_DOWN);
+    e.w_a = dn->data; e.w_b = nullptr; e.sh_a = shd->data; e.sh_b = nullptr;
+    int dn_type = dn->type;
+    if (dn->rdata && shd->rdata) { e.w_a = dn->rdata; e.sh_a = shd->rdata; dn_type = PB_T_IQ3S_N4; }
     e.rows_e = c.d; e.rows_sh = c.d;
     if (tt > s->moe_cap) PB_FAIL(ctx, PB_ERR_ARG, "MoE block on %d tokens, buffers hold %d", tt, s->moe_cap);
     e.hq = tt > 1 && c.ff_exp == c.ff_sh ? s->hq : nullptr;   // several tokens: levels of the hidden vectors made once
@@ -516,8 +522,8 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
     k.part = s->part; k.part_sh = s->part_sh + (size_t)tok0 * c.d; k.logits = logits + (size_t)tok0 * ldl; k.ldl = ldl; k.t = t; k.d = c.d; k.top_k = c.top_k; k.n_exp = c.n_exp;
     k.y = y; k.ldy = ldy; k.accumulate = accumulate;
     // few tokens on one GPU: the down kernel's last CTA also combines (one launch less per layer)
-    if (m->ep_world == 1 && (int64_t)t * c.d <= 8192) return pb_launch_expert_down(ctx, e, dn->type, c.ff_exp, &k, s->ticket + 1);
-    PB_TRY(pb_launch_expert_down(ctx, e, dn->type, c.ff_exp));
+    if (m->ep_world == 1 && (int64_t)t * c.d <= 8192) return pb_launch_expert_down(ctx, e, dn_type, c.ff_exp, &k, s->ticket + 1);
+    PB_TRY(pb_launch_expert_down(ctx, e, dn_type, c.ff_exp));
     // expert parallelism: every (token, slot) row was produced on exactly one rank and is zero elsewhere,
     // so the sum is an exact gather and the combine below sees the same bits for every GPU count
     if (sh) { PB_TRY(pb_ep_reduce_scatter(ctx, s->part, s->part_rs, (size_t)t * c.top_k * c.d)); k.part = s->part_rs; ctx->pdl_chain = false; }

@@ -12,7 +12,12 @@
 #define PB_TABLE_QUAL static __device__ const
 #include "pb_iq_tables.h"
 
-enum : int { PB_T_F32 = 0, PB_T_F16 = 1, PB_T_Q8_0 = 8, PB_T_Q4_K = 12, PB_T_IQ2_XS = 17, PB_T_IQ3_S = 21, PB_T_BF16 = 30 };
+enum : int { PB_T_F32 = 0, PB_T_F16 = 1, PB_T_Q8_0 = 8, PB_T_Q4_K = 12, PB_T_IQ2_XS = 17, PB_T_IQ3_S = 21, PB_T_BF16 = 30,
+             // internal, never a ggml id: IQ3_S re-coded at upload into 4-bit codes (see pb_repack.cu).  Every IQ3_S
+             // codebook value is odd (1..15), so a weight is one of the sixteen values -15, -13, .. 15 = 2 c - 15.
+             // Block of 256 weights, 136 bytes: [d f16][2 pad][4 bytes of 4-bit sub-scales as in IQ3_S][32 words];
+             // word m holds weights 8m..8m+3 in the low nibbles of its bytes and 8m+4..8m+7 in the high nibbles.
+             PB_T_IQ3S_N4 = 121 };
 
 // Codebooks staged in shared memory by the kernel that decodes (see pb_load_tables).
 struct PbTables {
@@ -194,6 +199,7 @@ static inline int pb_geom(int type, int* elems, int* bytes) {
         case PB_T_Q4_K: e = 256; b = 144; break;
         case PB_T_IQ2_XS: e = 256; b = 74; break;
         case PB_T_IQ3_S: e = 256; b = 110; break;
+        case PB_T_IQ3S_N4: e = 256; b = 136; break;
         default: return -1;
     }
     if (elems) *elems = e;

@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
 #pragma unroll
         for (int ps = 0; ps < PASSES; ps++) {
             const int qi = ps * 32 + ql;
-            if (qi < nquarters) pb_load_xquarter(xq, cols, qi, xr[ps]);
+            if (qi < nquarters) pb_load_xquarter<PbQDec<FMT>::AFFINE>(xq, cols, qi, xr[ps]);
         }
     }
 
@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
         const int r0 = (chunk - p.seg[s].chunk0) * p.rows_per_chunk;
         const int nr = min(p.rows_per_chunk, p.seg[s].rows - r0);
         const uint32_t base = pb_smem_u32(pb_ring_stage(ring, k));
-        if (FMT == PB_T_IQ3_S && NB == 1 && PASSES == 1 && lpr == 32) {
+        if ((FMT == PB_T_IQ3_S || FMT == PB_T_IQ3S_N4) && NB == 1 && PASSES == 1 && lpr == 32) {
             // one column, full-width rows: two rows per iteration, so that the two independent decode
             // chains overlap each other's shared-memory latency (a row past nr decodes stale bytes of the
             // stage and is not stored)
@@ -143,8 +143,8 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
             for (int ra = warp; ra < nr; ra += 2 * PB_CONSUMERS) {
                 const int rc = ra + PB_CONSUMERS;
                 const bool two = rc < p.rows_per_chunk;
-                float v0 = pb_iq3s_quarter_dot(base + (uint32_t)ra * (uint32_t)p.row_bytes + (ql >> 2) * D::STEP_BYTES, ql & 3, T, xr[0]);
-                float v1 = pb_iq3s_quarter_dot(base + (uint32_t)(two ? rc : ra) * (uint32_t)p.row_bytes + (ql >> 2) * D::STEP_BYTES, ql & 3, T, xr[0]);
+                float v0 = pb_decode_dot<FMT>(base + (uint32_t)ra * (uint32_t)p.row_bytes + (ql >> 2) * D::STEP_BYTES, ql & 3, T, xr[0]);
+                float v1 = pb_decode_dot<FMT>(base + (uint32_t)(two ? rc : ra) * (uint32_t)p.row_bytes + (ql >> 2) * D::STEP_BYTES, ql & 3, T, xr[0]);
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) { v0 += __shfl_xor_sync(0xffffffffu, v0, o); v1 += __shfl_xor_sync(0xffffffffu, v1, o); }
                 if (lane == 0) {
@@ -179,7 +179,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
 #pragma unroll 1
                             for (int b = 0; b < NB; b++) {
                                 PbXQuarter xv;
-                                pb_load_xquarter(xq + (size_t)b * xw, cols, qi, xv);
+                                pb_load_xquarter<PbQDec<FMT>::AFFINE>(xq + (size_t)b * xw, cols, qi, xv);
                                 acc[b] += pb_quarter_dot<FMT>(wq, xv);
                             }
                         }
@@ -223,7 +223,9 @@ static int launch_q(pb_ctx* ctx, const PbGemvQArgs& a, int row_bytes) {
     if (fixed + (size_t)PB_STAGES * (align_rows * row_bytes + 144) > (size_t)ctx->max_smem_optin)
         PB_FAIL(ctx, PB_UNSUPPORTED, "gemv: cols=%d with %d columns does not fit shared memory", a.cols, a.t);
     size_t stage_cap = ((size_t)ctx->max_smem_optin - fixed) / PB_STAGES;
-    if (stage_cap > 32768) stage_cap = 32768;
+    // the re-coded format needs no tables and little arithmetic: larger stages keep more bytes in flight
+    const size_t cap_max = FMT == PB_T_IQ3S_N4 ? 53248 : 32768;
+    if (stage_cap > cap_max) stage_cap = cap_max;
     const int lpr = 4 * p.bpr < 32 ? 4 * p.bpr : 32;
     const int step_rows = PB_CONSUMERS * (32 / lpr);   // rows one sweep of the consumer warps covers
     int rpc = step_rows * 2;
@@ -266,11 +268,12 @@ static int launch_q_fmt(pb_ctx* ctx, const PbGemvQArgs& a, int row_bytes) {
 }
 
 bool pb_gemvq_supported(int type, int cols) {
-    const bool quant = type == PB_T_IQ3_S || type == PB_T_IQ2_XS || type == PB_T_Q4_K || type == PB_T_Q8_0;
+    const bool quant = type == PB_T_IQ3_S || type == PB_T_IQ3S_N4 || type == PB_T_IQ2_XS || type == PB_T_Q4_K || type == PB_T_Q8_0;
     const int bpr = cols / 256;
     return quant && cols % 256 == 0 && bpr > 0 && (bpr & (bpr - 1)) == 0 && cols <= 4096;
 }
 
+static int launch_gemvq_dp4a(pb_ctx* ctx, const PbGemvQArgs& a, int el, int bs);
 int pb_launch_gemvq(pb_ctx* ctx, const PbGemvQArgs& a) {
     int el, bs;
     if (pb_geom(a.type, &el, &bs) || !pb_gemvq_supported(a.type, a.cols)) PB_FAIL(ctx, PB_UNSUPPORTED, "gemvq: type %d cols %d not supported by the integer kernel", a.type, a.cols);
@@ -278,6 +281,17 @@ int pb_launch_gemvq(pb_ctx* ctx, const PbGemvQArgs& a) {
         static const bool use_mma = !(getenv("PYRE_B200_MMA") && atoi(getenv("PYRE_B200_MMA")) == 0);
         if (use_mma) return pb_launch_gemmh(ctx, a);
     }
+    PbGemvQArgs b = a;
+    if (a.type == PB_T_IQ3_S) {
+        // every segment has a re-coded copy: stream that one
+        bool all = true;
+        for (int s = 0; s < a.nseg && s < 4; s++) all = all && a.seg[s].wr != nullptr;
+        if (all) { b.type = PB_T_IQ3S_N4; for (int s = 0; s < a.nseg && s < 4; s++) b.seg[s].w = a.seg[s].wr; pb_geom(b.type, &el, &bs); }
+    }
+    return launch_gemvq_dp4a(ctx, b, el, bs);
+}
+
+static int launch_gemvq_dp4a(pb_ctx* ctx, const PbGemvQArgs& a, int el, int bs) {
     if (a.t < 1 || a.t > 16) PB_FAIL(ctx, PB_ERR_ARG, "gemv: t=%d outside 1..16", a.t);
     if (a.nseg < 1 || a.nseg > 4) PB_FAIL(ctx, PB_ERR_ARG, "gemv: %d segments", a.nseg);
     if (a.mode == PB_ACT_GNORM && a.head_dim != 128) PB_FAIL(ctx, PB_UNSUPPORTED, "gemv: gated norm over heads of %d (128 is built)", a.head_dim);
@@ -294,6 +308,7 @@ int pb_launch_gemvq(pb_ctx* ctx, const PbGemvQArgs& a) {
         s.xq_in = a.xq_in ? a.xq_in + (size_t)t0 * pb_xq_words(a.cols) : nullptr;
         switch (a.type) {
             case PB_T_IQ3_S: rc = launch_q_fmt<PB_T_IQ3_S>(ctx, s, row_bytes); break;
+            case PB_T_IQ3S_N4: rc = launch_q_fmt<PB_T_IQ3S_N4>(ctx, s, row_bytes); break;
             case PB_T_IQ2_XS: rc = launch_q_fmt<PB_T_IQ2_XS>(ctx, s, row_bytes); break;
             case PB_T_Q4_K: rc = launch_q_fmt<PB_T_Q4_K>(ctx, s, row_bytes); break;
             default: rc = launch_q_fmt<PB_T_Q8_0>(ctx, s, row_bytes); break;
@@ -310,7 +325,7 @@ int pb_launch_gemv(pb_ctx* ctx, const PbGemvArgs& a) {
     if (a.rows <= 0) return PB_OK;
     PbGemvQArgs q;
     memset(&q, 0, sizeof q);
-    q.type = a.type; q.cols = a.cols; q.nseg = 1; q.seg[0].w = a.w; q.seg[0].rows = a.rows; q.seg[0].yoff = 0;
+    q.type = a.type; q.cols = a.cols; q.nseg = 1; q.seg[0].w = a.w; q.seg[0].wr = a.wr; q.seg[0].rows = a.rows; q.seg[0].yoff = 0;
     q.x = a.x; q.ldx = a.ldx; q.t = a.t; q.y = a.y; q.ldy = a.ldy; q.mode = PB_ACT_PLAIN;
     return pb_launch_gemvq(ctx, q);
 }

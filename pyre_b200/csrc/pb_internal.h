@@ -40,6 +40,11 @@ struct pb_qmat {
     int64_t rows = 0, cols = 0;
     int64_t row_bytes = 0;
     uint8_t* data = nullptr;   // device, 256-byte aligned, padded by >= 256 bytes past the last row
+    // IQ3_S only: the same weights re-coded as PB_T_IQ3S_N4 (4-bit codes, decoded with two logic operations per
+    // eight weights instead of a codebook walk); the streaming kernels read this copy, `data` stays for
+    // pb_qmat_read / dequant / embedding rows and the tensor-core GEMM
+    uint8_t* rdata = nullptr;
+    int64_t r_row_bytes = 0;
     size_t nbytes = 0;         // rows * row_bytes
     bool owns = true;          // false for row-range views into another matrix
 };
@@ -92,6 +97,7 @@ int pb_launch_synth_normal_at(pb_ctx* ctx, float* out, int64_t n, uint64_t seed,
 // pb_gemv.cu
 struct PbGemvArgs {
     const uint8_t* w;   // first row of the matrix (16-byte aligned)
+    const uint8_t* wr = nullptr;   // the same rows in the re-coded form (pb_qmat::rdata), or null
     int type;
     int64_t rows;
     int cols;
@@ -102,6 +108,7 @@ struct PbGemvArgs {
     int64_t ldy;
 };
 int pb_launch_gemv(pb_ctx* ctx, const PbGemvArgs& a);
+int pb_launch_repack_iq3s(pb_ctx* ctx, const uint8_t* src, uint8_t* dst, int64_t nblocks);
 
 // pb_gemvq.cu: integer-core GEMV over up to four same-shaped-row matrices with a fused
 // activation prologue and an optional accumulate (residual) epilogue.
@@ -109,7 +116,7 @@ enum { PB_ACT_PLAIN = 0,   // x as given
        PB_ACT_NORM = 1,    // rms(x) * norm_w over the whole row
        PB_ACT_GNORM = 2,   // per head of head_dim: rms(x) * norm_w[head_dim], times sigmoid(z)
        PB_ACT_PREQ = 3 };  // activations already split into int8 levels (xq_in)
-struct PbGemvSegArg { const uint8_t* w; int64_t rows; int64_t yoff; };
+struct PbGemvSegArg { const uint8_t* w; int64_t rows; int64_t yoff; const uint8_t* wr; };   // wr: re-coded rows (pb_qmat::rdata) or null
 #define PB_XH_BYTES ((size_t)8 << 20)   // fragment buffer of the tensor-core GEMM: t * cols * 4 bytes + 256 per tile (e.g. 512 tokens of 4096 columns)
 struct PbGemvQArgs {
     int type, cols, nseg;

@@ -317,7 +317,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
                     const int qi = ps * 32 + ql;
                     if (qi < nquarters) {
                         PbXQuarter xv;
-                        pb_load_xquarter(xcol, cols, qi, xv);
+                        pb_load_xquarter<PbQDec<FMT>::AFFINE>(xcol, cols, qi, xv);
                         g += pb_quarter_dot<FMT>(wg[ps], xv);
                         u += pb_quarter_dot<FMT>(wu[ps], xv);
                     }
@@ -481,7 +481,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
 #pragma unroll
                     for (int ps = 0; ps < PASSES; ps++) {
                         const int qi = ps * 32 + ql;
-                        if (qi < nquarters) { PbXQuarter xv; pb_load_xquarter(xcol, cols, qi, xv); acc += pb_quarter_dot<FMT>(wq[ps], xv); }
+                        if (qi < nquarters) { PbXQuarter xv; pb_load_xquarter<PbQDec<FMT>::AFFINE>(xcol, cols, qi, xv); acc += pb_quarter_dot<FMT>(wq[ps], xv); }
                     }
                     for (int o = lpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
                     if (ql == 0) {
@@ -510,7 +510,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
                     if (qi < nquarters) {
                         PbQuarter wq; PbXQuarter xv;
                         D::quarter(base + (uint32_t)r * p.row_bytes + (qi >> 2) * D::STEP_BYTES, qi & 3, T, wq);
-                        pb_load_xquarter(xq, cols, qi, xv);
+                        pb_load_xquarter<PbQDec<FMT>::AFFINE>(xq, cols, qi, xv);
                         acc += pb_quarter_dot<FMT>(wq, xv);
                     }
                 }
@@ -606,7 +606,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_rows_kernel(con
         if (!pb_mbar_wait(&full[k], 0, p.status, PB_DEV_WAIT_FULL_TIMEOUT)) break;
         PbQuarter wq; PbXQuarter xv;
         D::quarter(pb_smem_u32(stages + (size_t)k * slice) + (uint32_t)r * p.row_bytes + (ql >> 2) * D::STEP_BYTES, ql & 3, T, wq);
-        pb_load_xquarter(xq + (size_t)k * xw, cols, ql, xv);
+        pb_load_xquarter<PbQDec<FMT>::AFFINE>(xq + (size_t)k * xw, cols, ql, xv);
         float acc = pb_quarter_dot<FMT>(wq, xv);
         for (int o = nquarters >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
         if (ql == 0) res[k * PB_DR_ROWS + r] = acc;
@@ -711,6 +711,7 @@ static int launch_expert_type(pb_ctx* ctx, const PbExpertParams& p, int type, in
 #define GO(F) return cols <= 2048 ? launch_expert<F, 1, DOWN>(ctx, p, cols, cp, ticket) : launch_expert<F, 2, DOWN>(ctx, p, cols, cp, ticket)
     switch (type) {
         case PB_T_IQ3_S: GO(PB_T_IQ3_S);
+        case PB_T_IQ3S_N4: GO(PB_T_IQ3S_N4);
         case PB_T_IQ2_XS: GO(PB_T_IQ2_XS);
         case PB_T_Q4_K: GO(PB_T_Q4_K);
         default: GO(PB_T_Q8_0);

@@ -83,7 +83,7 @@ template <int FMT> struct PbQDec;
 
 template <> struct PbQDec<PB_T_IQ3_S> {
     static constexpr int STEP_BYTES = 110;
-    static constexpr bool HAS_MIN = false, SCALE16 = false;
+    static constexpr bool HAS_MIN = false, SCALE16 = false, AFFINE = false;
     // p = shared address of the 110-byte block, qt = quarter 0..3
     __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs& T, PbQuarter& o) {
         const float d = pb_h2f((uint16_t)pb_lds16(p));
@@ -110,7 +110,7 @@ template <> struct PbQDec<PB_T_IQ3_S> {
 
 template <> struct PbQDec<PB_T_IQ2_XS> {
     static constexpr int STEP_BYTES = 74;
-    static constexpr bool HAS_MIN = false, SCALE16 = true;
+    static constexpr bool HAS_MIN = false, SCALE16 = true, AFFINE = false;
     __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs& T, PbQuarter& o) {
         const float d = pb_h2f((uint16_t)pb_lds16(p));
         uint32_t qs[4];
@@ -133,7 +133,7 @@ template <> struct PbQDec<PB_T_IQ2_XS> {
 
 template <> struct PbQDec<PB_T_Q8_0> {
     static constexpr int STEP_BYTES = 8 * 34;
-    static constexpr bool HAS_MIN = false, SCALE16 = false;
+    static constexpr bool HAS_MIN = false, SCALE16 = false, AFFINE = false;
     __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs&, PbQuarter& o) {
 #pragma unroll
         for (int b = 0; b < 2; b++) {
@@ -150,7 +150,7 @@ template <> struct PbQDec<PB_T_Q8_0> {
 
 template <> struct PbQDec<PB_T_Q4_K> {
     static constexpr int STEP_BYTES = 144;
-    static constexpr bool HAS_MIN = true, SCALE16 = false;
+    static constexpr bool HAS_MIN = true, SCALE16 = false, AFFINE = false;
     __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs&, PbQuarter& o) {
         const uint4 hdr = pb_lds128(p);            // d, dmin, 12 scale bytes
         const float d = pb_h2f((uint16_t)(hdr.x & 0xFFFF)), mn = pb_h2f((uint16_t)(hdr.x >> 16));
@@ -172,6 +172,32 @@ template <> struct PbQDec<PB_T_Q4_K> {
     }
 };
 
+// IQ3_S re-coded into 4-bit codes c (weight = 2 c - 15): the quarter holds the codes, unsigned, and
+// pb_quarter_dot removes the offset with the integer sums of the activation levels:
+// sum (2 c - 15) q = 2 sum c q - 15 sum q, exact in integers.
+template <> struct PbQDec<PB_T_IQ3S_N4> {
+    static constexpr int STEP_BYTES = 136;
+    static constexpr bool HAS_MIN = false, SCALE16 = false, AFFINE = true;
+    __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs&, PbQuarter& o) {
+        const uint32_t hdr = pb_lds32(p);
+        const float d = pb_h2f((uint16_t)(hdr & 0xFFFF));
+        const uint32_t sc = pb_lds8(p + 4 + qt);
+        const float d0 = d * (float)(1 + 2 * (int)(sc & 0xF)), d1 = d * (float)(1 + 2 * (int)(sc >> 4));
+        o.sc[0] = o.sc[1] = d0; o.sc[2] = o.sc[3] = d1;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint2 c = pb_lds64(p + 8 + 32 * qt + 8 * i);
+            o.w[4 * i + 0] = (int)(c.x & 0x0F0F0F0Fu); o.w[4 * i + 1] = (int)((c.x >> 4) & 0x0F0F0F0Fu);
+            o.w[4 * i + 2] = (int)(c.y & 0x0F0F0F0Fu); o.w[4 * i + 3] = (int)((c.y >> 4) & 0x0F0F0F0Fu);
+        }
+    }
+};
+
+// unsigned bytes of a times signed bytes of b
+__device__ __forceinline__ int pb_dp4a_us(int a, int b, int c) {
+    int d; asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
+}
+
 // Number of int8 levels the activations are split into.  Each level divides the residual
 // error by ~254: two levels leave ~2e-5 of the largest value of a 32-group, three ~1e-7,
 // i.e. the size of f32 summation-order noise.  Three keeps router top-k decisions and
@@ -183,6 +209,7 @@ template <> struct PbQDec<PB_T_Q4_K> {
 struct PbXQuarter {
     int q[PB_XLEVELS][16];
     float s[PB_XLEVELS][2], sum[2];
+    int is[PB_XLEVELS][2];   // integer sum of each level over a 32-group (loaded only for offset-coded formats)
 };
 
 template <int FMT>
@@ -199,8 +226,12 @@ __device__ __forceinline__ float pb_quarter_dot(const PbQuarter& w, const PbXQua
 #pragma unroll
         for (int k = 0; k < WPH; k++)
 #pragma unroll
-            for (int l = 0; l < PB_XLEVELS; l++) isum[l] = __dp4a(w.w[h * WPH + k], x.q[l][h * WPH + k], isum[l]);
+            for (int l = 0; l < PB_XLEVELS; l++) isum[l] = D::AFFINE ? pb_dp4a_us(w.w[h * WPH + k], x.q[l][h * WPH + k], isum[l]) : __dp4a(w.w[h * WPH + k], x.q[l][h * WPH + k], isum[l]);
         const int g = h * WPH / 8;
+        if (D::AFFINE) {
+#pragma unroll
+            for (int l = 0; l < PB_XLEVELS; l++) isum[l] = 2 * isum[l] - 15 * x.is[l][g];
+        }
         float t = x.s[PB_XLEVELS - 1][g] * (float)isum[PB_XLEVELS - 1];   // smallest level first
 #pragma unroll
         for (int l = PB_XLEVELS - 2; l >= 0; l--) t = fmaf(x.s[l][g], (float)isum[l], t);
@@ -255,4 +286,13 @@ __device__ __forceinline__ float pb_iq3s_quarter_dot(uint32_t p, int qt, const P
         acc = fmaf(db, t, acc);
     }
     return acc;
+}
+
+// decode one quarter and dot it with one column's activations
+template <int FMT>
+__device__ __forceinline__ float pb_decode_dot(uint32_t p, int qt, const PbQTabs& T, const PbXQuarter& x) {
+    if (FMT == PB_T_IQ3_S) return pb_iq3s_quarter_dot(p, qt, T, x);
+    PbQuarter w;
+    PbQDec<FMT>::quarter(p, qt, T, w);
+    return pb_quarter_dot<FMT>(w, x);
 }

@@ -60,8 +60,9 @@ __device__ __forceinline__ void pb_ring_release(const PbRing& r, int k, int lane
 __device__ __forceinline__ int pb_xq_off(int qi, int i, int nq) { return (i * nq + qi) * 4; }
 
 // Quantized activations of one column: PB_XLEVELS arrays of cols/4 words, then PB_XLEVELS scale
-// arrays and the group sums, cols/32 floats each
-__host__ __device__ static inline int pb_xq_words(int cols) { return PB_XLEVELS * (cols / 4) + (PB_XLEVELS + 1) * (cols / 32); }
+// arrays and the group sums, cols/32 floats each, then PB_XLEVELS arrays of cols/32 integers: the sum of
+// each level's int8 values over a group (for weight formats whose codes carry an offset)
+__host__ __device__ static inline int pb_xq_words(int cols) { return PB_XLEVELS * (cols / 4) + (2 * PB_XLEVELS + 1) * (cols / 32); }
 
 // One warp splits FOUR consecutive 32-value groups of a column at once: lane l owns elements
 // 4*(l&7) .. +3 of group g0 + (l>>3), so a reduction over a group is 3 shuffles and every lane
@@ -82,19 +83,23 @@ __device__ __forceinline__ void pb_split_groups4(float4 v, int lane, int g0, int
         const float s = m > 0.f && isfinite(m) ? m / 127.f : 0.f;
         const float inv = s > 0.f ? 1.0f / s : 0.f;
         uint32_t pa = 0;
+        int asum = 0;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             int a = __float2int_rn(r[j] * inv);
             a = max(-127, min(127, a));
             r[j] = s > 0.f ? fmaf(-s, (float)a, r[j]) : 0.f;
             pa |= (uint32_t)(a & 0xFF) << (8 * j);
+            asum += a;
         }
+        asum += __shfl_xor_sync(0xffffffffu, asum, 1); asum += __shfl_xor_sync(0xffffffffu, asum, 2); asum += __shfl_xor_sync(0xffffffffu, asum, 4);
         col[l * (cols / 4) + off] = pa;
-        if (k == 0) sc[l * ng + g] = s;
+        if (k == 0) { sc[l * ng + g] = s; reinterpret_cast<int*>(sc)[(PB_XLEVELS + 1 + l) * ng + g] = asum; }
     }
     if (k == 0) sc[PB_XLEVELS * ng + g] = sum;
 }
 
+template <bool ISUM = false>
 __device__ __forceinline__ void pb_load_xquarter(const uint32_t* xcol, int cols, int qi, PbXQuarter& o) {
     const int nq = cols / 64, ng = cols / 32;
     const float* sc = reinterpret_cast<const float*>(xcol + PB_XLEVELS * (cols / 4));
@@ -109,6 +114,11 @@ __device__ __forceinline__ void pb_load_xquarter(const uint32_t* xcol, int cols,
         o.s[l][0] = sc[l * ng + 2 * qi]; o.s[l][1] = sc[l * ng + 2 * qi + 1];
     }
     o.sum[0] = sc[PB_XLEVELS * ng + 2 * qi]; o.sum[1] = sc[PB_XLEVELS * ng + 2 * qi + 1];
+    if (ISUM) {
+        const int* is = reinterpret_cast<const int*>(sc) + (PB_XLEVELS + 1) * ng;
+#pragma unroll
+        for (int l = 0; l < PB_XLEVELS; l++) { o.is[l][0] = is[l * ng + 2 * qi]; o.is[l][1] = is[l * ng + 2 * qi + 1]; }
+    }
 }
 
 // Fill the shared-memory tables a format needs at `tab` (16-byte aligned, pb_tab_bytes<FMT>(rep) long):
