@@ -67,6 +67,36 @@ __device__ __forceinline__ float pb_iq3s_quarter_h(uint32_t p, int qt, uint32_t 
     return d;
 }
 
+// The same 32 half2 words from a block re-coded into 4-bit codes (PB_T_IQ3S_N4, weight = 2 c - 15): a byte
+// permute puts two codes into the mantissas of two f16 with the exponent of 1024 (0x6400 | c = 1024 + c,
+// exact), one subtraction leaves c, one fused multiply-add makes (2 c - 15) * multiplier -- all exact in
+// f16, so the words equal those of pb_iq3s_quarter_h bit for bit.
+__device__ __forceinline__ float pb_n4_quarter_h(uint32_t p, int qt, uint32_t (&h)[32]) {
+    const float d = pb_h2f((uint16_t)(pb_lds32(p) & 0xFFFF));
+    const uint32_t sc = pb_lds8(p + 4 + qt);
+    const float f0 = (float)(1 + 2 * (int)(sc & 0xF)), f1 = (float)(1 + 2 * (int)(sc >> 4));
+    const __half2 a0 = __float2half2_rn(2.0f * f0), b0 = __float2half2_rn(-15.0f * f0);
+    const __half2 a1 = __float2half2_rn(2.0f * f1), b1 = __float2half2_rn(-15.0f * f1);
+    const __half2 k1024 = __float2half2_rn(1024.0f);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint2 c = pb_lds64(p + 8 + 32 * qt + 8 * i);
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int u = 2 * i + j;
+            const uint32_t w = j ? c.y : c.x;
+            const uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
+            const uint32_t r[4] = {pb_prmt(lo, 0x64006400u, 0x7150u), pb_prmt(lo, 0x64006400u, 0x7352u), pb_prmt(hi, 0x64006400u, 0x7150u), pb_prmt(hi, 0x64006400u, 0x7352u)};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const __half2 v = __hfma2(__hsub2(*reinterpret_cast<const __half2*>(&r[e]), k1024), u < 4 ? a0 : a1, u < 4 ? b0 : b1);
+                h[4 * u + e] = *reinterpret_cast<const uint32_t*>(&v);
+            }
+        }
+    }
+    return d;
+}
+
 // byte offset of the 8-byte B-fragment slot of (block blk, entry j, n-tile nt, token-in-tile tq, level lv, quarter q).
 // The slots of n-tiles 2p and 2p+1 of one lane are adjacent, so one 128-bit load feeds two mma.
 __device__ __forceinline__ uint32_t pb_xh_off(int blk, int j, int nt, int NT, int tq, int lv, int q) {
@@ -152,7 +182,8 @@ __global__ void __launch_bounds__(256) pb_xh_prep_kernel(const PbGemvQParams p, 
 }
 
 // NST = stages of the ring (4; 2 for rows wider than 2048 columns, whose fragments leave less room)
-template <int NT, int NST>
+// RC: the weights are the re-coded copy (136-byte blocks, no codebook table)
+template <int NT, int NST, bool RC>
 __global__ void __launch_bounds__(GH_THREADS, 1) pb_gemmh_iq3s_kernel(const PbGemvQParams p) {
     constexpr int NB = 4 * NT;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -164,7 +195,7 @@ __global__ void __launch_bounds__(GH_THREADS, 1) pb_gemmh_iq3s_kernel(const PbGe
     uint64_t* xbar = reinterpret_cast<uint64_t*>(smem + 192);     // completion of the fragment copies
     uint8_t* tab = smem + 256;                                    // f16 codebook, four interleaved copies (16 KB)
     const int cols = p.bpr * 256;
-    uint8_t* xh = tab + 16384;                                    // B fragments: cols * NB * 4 bytes
+    uint8_t* xh = tab + (RC ? 0 : 16384);                         // B fragments: cols * NB * 4 bytes
     float* red = reinterpret_cast<float*>(xh + (size_t)cols * NB * 4);   // [2][GH_CONSUMERS][16 rows][NB]
     ring.stages = reinterpret_cast<uint8_t*>(red) + 2 * GH_CONSUMERS * GH_ROWS * NB * 4;
     ring.stage_bytes = p.stage_bytes;
@@ -221,7 +252,7 @@ __global__ void __launch_bounds__(GH_THREADS, 1) pb_gemmh_iq3s_kernel(const PbGe
 
     // ---- consumers: tables ----
     constexpr int CT = GH_CONSUMERS * 32;
-    {
+    if (!RC) {   // the re-coded form needs no codebook (and the fragments start where the table would be)
         uint2* gh = reinterpret_cast<uint2*>(tab);
         for (int i = tid; i < 512; i += CT) {
             const uint32_t g = PB_IQ3S_GRID[i];
@@ -255,8 +286,8 @@ __global__ void __launch_bounds__(GH_THREADS, 1) pb_gemmh_iq3s_kernel(const PbGe
         for (int blk = warp; blk < p.bpr; blk += GH_CONSUMERS) {   // K split: this warp's blocks of the 16 rows
             uint32_t ha[32], hb[32];
             // rows g and g + 8 (rows past the end of the matrix decode stale bytes of the stage; never stored)
-            const float da = pb_iq3s_quarter_h(base + (uint32_t)g * p.row_bytes + blk * 110, q, tab_h, ha);
-            const float db = pb_iq3s_quarter_h(base + (uint32_t)(g + 8) * p.row_bytes + blk * 110, q, tab_h, hb);
+            const float da = RC ? pb_n4_quarter_h(base + (uint32_t)g * p.row_bytes + blk * 136, q, ha) : pb_iq3s_quarter_h(base + (uint32_t)g * p.row_bytes + blk * 110, q, tab_h, ha);
+            const float db = RC ? pb_n4_quarter_h(base + (uint32_t)(g + 8) * p.row_bytes + blk * 136, q, hb) : pb_iq3s_quarter_h(base + (uint32_t)(g + 8) * p.row_bytes + blk * 110, q, tab_h, hb);
             float acc[NT][4];
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
@@ -307,26 +338,26 @@ __global__ void __launch_bounds__(GH_THREADS, 1) pb_gemmh_iq3s_kernel(const PbGe
     }
 }
 
-template <int NT, int NST>
+template <int NT, int NST, bool RC>
 static int launch_h(pb_ctx* ctx, const PbGemvQArgs& a, const uint8_t* tile_buf) {
     constexpr int NB = 4 * NT;
     PbGemvQParams p;
     memset(&p, 0, sizeof p);
-    p.row_bytes = a.cols / 256 * 110; p.bpr = a.cols / 256; p.nseg = a.nseg;
+    p.row_bytes = a.cols / 256 * (RC ? 136 : 110); p.bpr = a.cols / 256; p.nseg = a.nseg;
     p.x = a.x; p.ldx = a.ldx; p.t = a.t; p.y = a.y; p.ldy = a.ldy; p.status = ctx->dev_status;
     p.mode = a.mode; p.norm_w = a.norm_w; p.z = a.z; p.ldz = a.ldz; p.head_dim = a.head_dim; p.eps = a.eps; p.accumulate = a.accumulate;
     p.rows_per_chunk = GH_ROWS;
     int nchunks = 0;
     for (int s = 0; s < a.nseg; s++) {
-        p.seg[s].w = a.seg[s].w; p.seg[s].rows = (int)a.seg[s].rows; p.seg[s].yoff = (int)a.seg[s].yoff; p.seg[s].chunk0 = nchunks;
+        p.seg[s].w = RC ? a.seg[s].wr : a.seg[s].w; p.seg[s].rows = (int)a.seg[s].rows; p.seg[s].yoff = (int)a.seg[s].yoff; p.seg[s].chunk0 = nchunks;
         nchunks += (int)((a.seg[s].rows + GH_ROWS - 1) / GH_ROWS);
     }
     p.nchunks = nchunks;
     p.stage_bytes = (uint32_t)(((size_t)GH_ROWS * p.row_bytes + 16 + 127) & ~(size_t)127);
-    const size_t smem = 256 + 16384 + (size_t)a.cols * NB * 4 + 2 * GH_CONSUMERS * GH_ROWS * NB * 4 + (size_t)NST * p.stage_bytes;
+    const size_t smem = 256 + (RC ? 0 : 16384) + (size_t)a.cols * NB * 4 + 2 * GH_CONSUMERS * GH_ROWS * NB * 4 + (size_t)NST * p.stage_bytes;
     if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "gemm: %zu bytes of shared memory needed for cols=%d t=%d", smem, a.cols, a.t);
     p.xh_in = tile_buf + 256; p.xinv_in = reinterpret_cast<const float*>(tile_buf);
-    auto kern = pb_gemmh_iq3s_kernel<NT, NST>;
+    auto kern = pb_gemmh_iq3s_kernel<NT, NST, RC>;
     static size_t configured = 0;
     if (smem > configured) { PB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = smem; }
     const int grid = nchunks < ctx->sm_count ? nchunks : ctx->sm_count;
@@ -357,6 +388,8 @@ int pb_launch_gemmh(pb_ctx* ctx, const PbGemvQArgs& a) {
         ctx->kernels_launched++;
         PB_CUDA(ctx, cudaGetLastError());
     }
+    bool recoded = true;   // every segment has a re-coded copy
+    for (int sg = 0; sg < a.nseg && sg < 4; sg++) recoded = recoded && a.seg[sg].wr != nullptr;
     int rc = PB_OK;
     for (int ti = 0; ti < ntiles && rc == PB_OK; ti++) {
         const int t0 = ti * tile;
@@ -364,8 +397,11 @@ int pb_launch_gemmh(pb_ctx* ctx, const PbGemvQArgs& a) {
         s.t = a.t - t0 < tile ? a.t - t0 : tile;
         s.x = a.x + (int64_t)t0 * a.ldx; s.y = a.y + (int64_t)t0 * a.ldy; s.z = a.z ? a.z + (int64_t)t0 * a.ldz : nullptr;
         const uint8_t* tb = ctx->xh_buf + (size_t)ti * tile_stride;
-        if (wide) rc = s.t <= 4 ? launch_h<1, 2>(ctx, s, tb) : launch_h<2, 2>(ctx, s, tb);
-        else rc = s.t <= 4 ? launch_h<1, 4>(ctx, s, tb) : (s.t <= 8 ? launch_h<2, 4>(ctx, s, tb) : launch_h<4, 4>(ctx, s, tb));
+        if (recoded) {
+            if (wide) rc = s.t <= 4 ? launch_h<1, 2, true>(ctx, s, tb) : launch_h<2, 2, true>(ctx, s, tb);
+            else rc = s.t <= 4 ? launch_h<1, 4, true>(ctx, s, tb) : (s.t <= 8 ? launch_h<2, 4, true>(ctx, s, tb) : launch_h<4, 4, true>(ctx, s, tb));
+        } else if (wide) rc = s.t <= 4 ? launch_h<1, 2, false>(ctx, s, tb) : launch_h<2, 2, false>(ctx, s, tb);
+        else rc = s.t <= 4 ? launch_h<1, 4, false>(ctx, s, tb) : (s.t <= 8 ? launch_h<2, 4, false>(ctx, s, tb) : launch_h<4, 4, false>(ctx, s, tb));
     }
     return rc;
 }

@@ -109,3 +109,42 @@ def test_bad_arguments_fail_loudly(ctx):
     with pytest.raises(pb.PyreError):
         W.raw_rows(2, 5)
     W.free()
+
+
+_NATIVE_SCRIPT = r"""
+import sys, numpy as np
+import pyre_b200 as pb
+ctx = pb.Ctx()
+out = {}
+for rows, cols, t in [(4096, 2048, 1), (2048, 512, 2), (515, 2048, 1), (200, 4096, 1), (1024, 2048, 8), (515, 2048, 16), (200, 4096, 5), (2048, 512, 12)]:
+    W = pb.QMat.synth(ctx, pb.IQ3_S, rows, cols, 0, 5)
+    x = np.random.default_rng(rows + cols).standard_normal((t, cols)).astype(np.float32)
+    out[f"{rows}x{cols}x{t}"] = W.matmul(x)
+    W.free()
+np.savez(sys.argv[1], **out)
+"""
+
+
+def test_iq3s_recoded_and_native_kernels_agree_bit_for_bit(ctx, tmp_path):
+    """IQ3_S matrices are streamed from a copy re-coded into 4-bit codes (weight = 2c - 15).  The
+    re-coding is lossless and the offset is removed in integers, so the GEMV through the re-coded copy
+    must equal the GEMV over the native GGUF blocks (PYRE_B200_REPACK=0) bit for bit -- on the dp4a path
+    (1-2 tokens) and on the tensor-core path (3 and more)."""
+    import os
+    import subprocess
+    import sys
+    res = {}
+    for mode in ("1", "0"):
+        f = tmp_path / f"gemv_repack{mode}.npz"
+        env = dict(os.environ, PYRE_B200_REPACK=mode)
+        root = str(Path(__file__).resolve().parent.parent)
+        env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
+        subprocess.run([sys.executable, "-c", _NATIVE_SCRIPT, str(f)], check=True, env=env, cwd=root, timeout=300)
+        res[mode] = dict(np.load(f))
+    assert set(res["0"]) == set(res["1"]) and len(res["0"]) == 8
+    for k in res["0"]:
+        assert np.array_equal(res["0"][k].view(np.uint32), res["1"][k].view(np.uint32)), k
+    # and both against the oracle
+    x = np.random.default_rng(4096 + 2048).standard_normal((1, 2048)).astype(np.float32)
+    ref = oracle.QMat.synth(oracle.IQ3_S, 4096, 2048, 0, 5).matmul(x)
+    assert rel_err(res["1"]["4096x2048x1"], ref) < GEMV_TOL
