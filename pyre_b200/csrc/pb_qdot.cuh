@@ -209,7 +209,7 @@ __device__ __forceinline__ int pb_dp4a_us(int a, int b, int c) {
 struct PbXQuarter {
     int q[PB_XLEVELS][16];
     float s[PB_XLEVELS][2], sum[2];
-    int is[PB_XLEVELS][2];   // integer sum of each level over a 32-group (loaded only for offset-coded formats)
+    int is[PB_XLEVELS][2];   // -15 * integer sum of each level over a 32-group (loaded only for offset-coded formats)
 };
 
 template <int FMT>
@@ -230,7 +230,7 @@ __device__ __forceinline__ float pb_quarter_dot(const PbQuarter& w, const PbXQua
         const int g = h * WPH / 8;
         if (D::AFFINE) {
 #pragma unroll
-            for (int l = 0; l < PB_XLEVELS; l++) isum[l] = 2 * isum[l] - 15 * x.is[l][g];
+            for (int l = 0; l < PB_XLEVELS; l++) isum[l] = 2 * isum[l] + x.is[l][g];   // x.is = -15 * (sum of the level over the group)
         }
         float t = x.s[PB_XLEVELS - 1][g] * (float)isum[PB_XLEVELS - 1];   // smallest level first
 #pragma unroll

@@ -60,8 +60,8 @@ __device__ __forceinline__ void pb_ring_release(const PbRing& r, int k, int lane
 __device__ __forceinline__ int pb_xq_off(int qi, int i, int nq) { return (i * nq + qi) * 4; }
 
 // Quantized activations of one column: PB_XLEVELS arrays of cols/4 words, then PB_XLEVELS scale
-// arrays and the group sums, cols/32 floats each, then PB_XLEVELS arrays of cols/32 integers: the sum of
-// each level's int8 values over a group (for weight formats whose codes carry an offset)
+// arrays and the group sums, cols/32 floats each, then PB_XLEVELS arrays of cols/32 integers: -15 times the
+// sum of each level's int8 values over a group (the offset term of weight formats coded as 2 c - 15)
 __host__ __device__ static inline int pb_xq_words(int cols) { return PB_XLEVELS * (cols / 4) + (2 * PB_XLEVELS + 1) * (cols / 32); }
 
 // One warp splits FOUR consecutive 32-value groups of a column at once: lane l owns elements
@@ -94,7 +94,7 @@ __device__ __forceinline__ void pb_split_groups4(float4 v, int lane, int g0, int
         }
         asum += __shfl_xor_sync(0xffffffffu, asum, 1); asum += __shfl_xor_sync(0xffffffffu, asum, 2); asum += __shfl_xor_sync(0xffffffffu, asum, 4);
         col[l * (cols / 4) + off] = pa;
-        if (k == 0) { sc[l * ng + g] = s; reinterpret_cast<int*>(sc)[(PB_XLEVELS + 1 + l) * ng + g] = asum; }
+        if (k == 0) { sc[l * ng + g] = s; reinterpret_cast<int*>(sc)[(PB_XLEVELS + 1 + l) * ng + g] = -15 * asum; }   // stored ready for 2 A - 15 S
     }
     if (k == 0) sc[PB_XLEVELS * ng + g] = sum;
 }
