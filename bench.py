@@ -222,7 +222,7 @@ def workload_config(batch, gpus, replicas=False, replicated_ep=False):
             "batch": batch, "context": CTX_PREFILL, "residual": "pre-norm (hc=0)", "parallelism": "single GPU" if gpus == 1 else (f"{gpus} independent replicas" if replicas else (
                 f"expert-parallel x{gpus}, replicated tokens (512/{gpus} experts per GPU, every GPU steps all sequences, one NCCL all-reduce per MoE block)" if replicated_ep else
                 f"expert-parallel x{gpus}, sharded tokens ({batch} sequence(s) per GPU, 512/{gpus} experts per GPU, dense weights replicated; per MoE block one NCCL all-gather of the residual rows and one reduce-scatter of the expert outputs)")),
-            "l2": "weights touched per step (>1.7 GB) exceed the 126 MB L2; the lm-head roofline launch streams 134 MB"}
+            "l2": "weights touched per step (>1.7 GB) exceed the 126 MB L2; the lm-head roofline launch streams 165 MB"}
 
 
 # ---------------------------------------------------------------------------------------------------
