@@ -182,6 +182,7 @@ struct PbExpertParams {
     int rows_e, rows_sh, has_shared, t, top_k, n_exp, e_base;
     int sh_tok0, sh_ntok;                     // tokens [sh_tok0, sh_tok0 + sh_ntok) get the shared expert here
     int bpr, row_bytes, rows_per_chunk; uint32_t stage_bytes, tab_bytes; int rep;
+    int nx;                                   // activation-level vectors of a chunk's first nx entries ride along with its weights
     int* status;
 };
 struct PbCombineParams {

@@ -228,19 +228,21 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
         int k = 0; bool ok = true;
         for (int k0 = 0; k0 < my_chunks && ok; k0 += 32) {
             const int kk = k0 + lane;
-            int m_e = 0, m_r0 = 0, m_e0 = 0, m_e1 = 0, m_tok0 = 0, m_sh = 0;
+            int m_e = 0, m_r0 = 0, m_e0 = 0, m_e1 = 0, m_tok0 = 0, m_tok1 = 0, m_sh = 0;
             if (kk < my_chunks) {
                 const int chunk = (int)blockIdx.x + kk * (int)gridDim.x;
                 if (chunk < n_used * cpe) {
                     const int s = chunk / cpe;
                     m_r0 = (chunk - s * cpe) * p.rows_per_chunk;
                     m_e = p.used_e[s]; m_e0 = p.used_off[s]; m_e1 = p.used_off[s + 1];
-                    m_tok0 = m_e0 >= 0 && m_e0 < p.t * p.top_k ? p.ent_tok[m_e0] : -1;
+                    const bool in = m_e0 >= 0 && m_e0 < p.t * p.top_k;
+                    m_tok0 = in ? p.ent_tok[m_e0] : -1;
+                    m_tok1 = in && m_e1 - m_e0 > 1 && m_e0 + 1 < p.t * p.top_k ? p.ent_tok[m_e0 + 1] : 0;
                 } else {
                     const int sc = chunk - n_used * cpe;
                     m_sh = 1; m_r0 = (sc % cps1) * p.rows_per_chunk;
                     m_e0 = (sc / cps1) * PB_SH_GROUP; m_e1 = min(p.sh_ntok, m_e0 + PB_SH_GROUP);
-                    m_tok0 = p.sh_tok0 + m_e0;
+                    m_tok0 = p.sh_tok0 + m_e0; m_tok1 = m_tok0 + 1;
                 }
             }
             const int nk = min(32, my_chunks - k0);
@@ -256,20 +258,24 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
                         if (!sh) { const size_t off = ((size_t)(e - p.e_base) * p.rows_e + r0) * p.row_bytes; g = p.w_a + off; u = p.w_b + off; }
                         else { const size_t off = (size_t)r0 * p.row_bytes; g = p.sh_a + off; u = p.sh_b + off; }
                         hdr[k % PB_STAGES] = make_int4(r0, e0, e1, sh);
-                        pb_ring_announce(ring, k, 2 * half + xbytes);
+                        pb_ring_announce(ring, k, 2 * half + xbytes * (uint32_t)min(p.nx, max(1, e1 - e0)));
                         pb_ring_copy(ring, k, 0, g, half);
                         pb_ring_copy(ring, k, half, u, half);
                     }
                 }
                 good = __shfl_sync(0xffffffffu, good, 0);
                 if (!good) { ok = false; break; }
-                // the activation levels of the chunk's first entry ride along, so that the consumers read them from
-                // shared memory instead of waiting for L2 after the decode.  The token comes from a second dependent
-                // load, awaited only here, after the weights are on their way.
-                int tok0 = __shfl_sync(0xffffffffu, m_tok0, j);
+                // the activation levels of the chunk's first entries (p.nx of them, at most two) ride along, so that the
+                // consumers read them from shared memory instead of waiting for L2 after the decode.  The tokens come
+                // from a second dependent load, awaited only here, after the weights are on their way.
+                int tok0 = __shfl_sync(0xffffffffu, m_tok0, j), tok1 = __shfl_sync(0xffffffffu, m_tok1, j);
                 if (lane == 0) {
                     if (tok0 < 0 || tok0 >= p.t) { atomicExch(p.status, PB_DEV_BAD_INDEX); tok0 = 0; }   // the announced bytes must still arrive
                     pb_ring_copy(ring, k, 2 * half, p.xq + (size_t)tok0 * pb_xq_words(p.bpr * 256), xbytes);
+                    if (p.nx > 1 && e1 - e0 > 1) {
+                        if (tok1 < 0 || tok1 >= p.t) { atomicExch(p.status, PB_DEV_BAD_INDEX); tok1 = 0; }
+                        pb_ring_copy(ring, k, 2 * half + xbytes, p.xq + (size_t)tok1 * pb_xq_words(p.bpr * 256), xbytes);
+                    }
                 }
             }
         }
@@ -310,7 +316,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
                 int tok = 0;
                 if (shared) tok = p.sh_tok0 + en;
                 else if (en > e0) tok = lanes_hold ? __shfl_sync(0xffffffffu, l_tok, en - e0 - 1) : p.ent_tok[en];
-                const uint32_t* xcol = en == e0 ? reinterpret_cast<const uint32_t*>(pb_ring_stage(ring, k) + 2 * half) : p.xq + (size_t)tok * xw;
+                const uint32_t* xcol = en - e0 < p.nx ? reinterpret_cast<const uint32_t*>(pb_ring_stage(ring, k) + 2 * half + (uint32_t)(en - e0) * xbytes) : p.xq + (size_t)tok * xw;
                 float g = 0.f, u = 0.f;
 #pragma unroll
                 for (int ps = 0; ps < PASSES; ps++) {
@@ -423,10 +429,12 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
                         hdr[k % PB_STAGES] = make_int4(r0, e0, e1, sh);
                         if (p.hq) {
                             // several tokens: the levels of the chunk's first hidden vector ride along with the weights
+                            // (the hidden vectors of an expert's entries, and of consecutive tokens, are adjacent in hq)
                             const size_t slot = sh ? (size_t)p.t * p.top_k + p.sh_tok0 + e0 : (size_t)e0;
-                            pb_ring_announce(ring, k, bytes + hbytes);
+                            const uint32_t hb = hbytes * (uint32_t)min(p.nx, max(1, e1 - e0));
+                            pb_ring_announce(ring, k, bytes + hb);
                             pb_ring_copy(ring, k, 0, src, bytes);
-                            pb_ring_copy(ring, k, bytes, p.hq + slot * xw, hbytes);
+                            pb_ring_copy(ring, k, bytes, p.hq + slot * xw, hb);
                         } else {
                             pb_ring_announce(ring, k, bytes);
                             pb_ring_copy(ring, k, 0, src, bytes);
@@ -476,7 +484,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
                     if (lanes_hold) { tok = __shfl_sync(0xffffffffu, l_tok, en - e0); slot = __shfl_sync(0xffffffffu, l_slot, en - e0); wgt = __shfl_sync(0xffffffffu, l_w, en - e0); }
                     else if (shared) tok = p.sh_tok0 + en;
                     else { tok = p.ent_tok[en]; slot = p.ent_slot[en]; wgt = p.ent_w[en]; }
-                    const uint32_t* xcol = en == e0 ? reinterpret_cast<const uint32_t*>(pb_ring_stage(ring, k) + bytes) : p.hq + (size_t)(shared ? p.t * p.top_k + tok : en) * xw;
+                    const uint32_t* xcol = en - e0 < p.nx ? reinterpret_cast<const uint32_t*>(pb_ring_stage(ring, k) + bytes + (uint32_t)(en - e0) * hbytes) : p.hq + (size_t)(shared ? p.t * p.top_k + tok : en) * xw;
                     float acc = 0.f;
 #pragma unroll
                     for (int ps = 0; ps < PASSES; ps++) {
@@ -665,7 +673,14 @@ static int launch_expert(pb_ctx* ctx, PbExpertParams p, int cols, const PbCombin
     if (p.rows_e % rpc || (p.has_shared && !DOWN && p.rows_sh % rpc)) PB_FAIL(ctx, PB_UNSUPPORTED, "expert kernel: %d rows per expert is not a multiple of the %d-row chunk", p.rows_e, rpc);
     p.rows_per_chunk = rpc;
     const size_t xbytes = DOWN ? (((size_t)pb_xq_words(cols) * 4 + 127) & ~(size_t)127) : 0;
-    p.stage_bytes = (uint32_t)((((size_t)rpc * p.row_bytes * (DOWN ? 1 : 2)) + (size_t)pb_xq_words(cols) * 4 + 16 + 127) & ~(size_t)127);
+    // a stage = the chunk's rows + the activation levels of its first nx entries: two (gate/up) or four (down) where
+    // shared memory allows (formats without tables), else one
+    p.nx = p.t == 1 ? 1 : (DOWN ? 4 : 2);   // one token: one entry per expert, and smaller stages start sooner
+    p.stage_bytes = (uint32_t)((((size_t)rpc * p.row_bytes * (DOWN ? 1 : 2)) + (size_t)p.nx * pb_xq_words(cols) * 4 + 16 + 127) & ~(size_t)127);
+    if (256 + p.tab_bytes + xbytes + (size_t)PB_STAGES * p.stage_bytes > (size_t)ctx->max_smem_optin) {
+        p.nx = 1;
+        p.stage_bytes = (uint32_t)((((size_t)rpc * p.row_bytes * (DOWN ? 1 : 2)) + (size_t)pb_xq_words(cols) * 4 + 16 + 127) & ~(size_t)127);
+    }
     const size_t smem = 256 + p.tab_bytes + xbytes + (size_t)PB_STAGES * p.stage_bytes;
     if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "expert kernel needs %zu bytes of shared memory", smem);
     p.status = ctx->dev_status;
