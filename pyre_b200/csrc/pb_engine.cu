@@ -494,8 +494,8 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
         logits = s->rlogits; ldl = c.n_exp + 1;
     }
     q.logits = logits; q.ldl = ldl;
+    if (m->ep_world > 1) { r.zero = s->part; r.zero_n = (int64_t)tt * c.top_k * c.d; }   // rows of other ranks' experts stay zero
     PB_TRY(pb_launch_router(ctx, r, q, s->ticket));
-    if (m->ep_world > 1) { PB_CUDA(ctx, cudaMemsetAsync(s->part, 0, (size_t)tt * c.top_k * c.d * 4, ctx->stream)); ctx->pdl_chain = false; }
     PbExpertParams e; memset(&e, 0, sizeof e);
     e.n_used = s->n_used; e.used_e = s->used_e; e.used_off = s->used_off; e.ent_tok = s->ent_tok; e.ent_slot = s->ent_slot; e.ent_w = s->ent_w;
     e.xq = s->xq; e.h = s->h; e.h_sh = s->h_sh; e.part = s->part; e.part_sh = s->part_sh;

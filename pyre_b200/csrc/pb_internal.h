@@ -162,6 +162,7 @@ struct PbRouterParams {
     // tokens plus a raw copy of their rows into xcopy (row stride ldl); phase 2 = split + routing of all
     // gathered tokens (no GEMV)
     int phase; float* xcopy;
+    float* zero; int64_t zero_n;              // phases 0 and 2: zero_n floats (a multiple of 4) cleared for the expert kernels (expert parallelism)
 };
 struct PbRouteParams {
     const float* logits; int64_t ldl; int t, n_exp, top_k;

@@ -101,6 +101,13 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     pb_pdl_wait();
     pb_pdl_trigger();
+    if (p.zero && p.phase != 1) {
+        // expert parallelism: the partial-row buffer must be zero where other ranks' experts write; cleared
+        // here instead of by a memset node between the launches (which would also end the dependent-launch chain)
+        float4* z = reinterpret_cast<float4*>(p.zero);
+        const int64_t n4 = p.zero_n / 4, nthreads = (int64_t)gridDim.x * gridDim.y * 256;
+        for (int64_t i = ((int64_t)blockIdx.y * gridDim.x + blockIdx.x) * 256 + tid; i < n4; i += nthreads) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     // grid.y cuts the tokens into groups of PB_ROUTER_TPG: this CTA handles tokens [b_lo, b_hi)
     const int b_lo = (int)blockIdx.y * PB_ROUTER_TPG, b_hi = min(p.t, b_lo + PB_ROUTER_TPG);
     // per-token RMS scale (rms(): 1 / sqrt(mean(x^2) + eps), qwen4exp_gguf.rs:209); one warp per token
