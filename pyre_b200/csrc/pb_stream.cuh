@@ -111,13 +111,16 @@ __device__ __forceinline__ void pb_load_xquarter(const uint32_t* xcol, int cols,
             const uint4 a = *reinterpret_cast<const uint4*>(q + pb_xq_off(qi, i, nq));
             o.q[l][4 * i] = (int)a.x; o.q[l][4 * i + 1] = (int)a.y; o.q[l][4 * i + 2] = (int)a.z; o.q[l][4 * i + 3] = (int)a.w;
         }
-        o.s[l][0] = sc[l * ng + 2 * qi]; o.s[l][1] = sc[l * ng + 2 * qi + 1];
+        // the two groups of a quarter are neighbours: one 64-bit load (ng is even, so the pair is 8-byte aligned)
+        const float2 s2 = *reinterpret_cast<const float2*>(sc + l * ng + 2 * qi);
+        o.s[l][0] = s2.x; o.s[l][1] = s2.y;
     }
-    o.sum[0] = sc[PB_XLEVELS * ng + 2 * qi]; o.sum[1] = sc[PB_XLEVELS * ng + 2 * qi + 1];
+    const float2 m2 = *reinterpret_cast<const float2*>(sc + PB_XLEVELS * ng + 2 * qi);
+    o.sum[0] = m2.x; o.sum[1] = m2.y;
     if (ISUM) {
         const int* is = reinterpret_cast<const int*>(sc) + (PB_XLEVELS + 1) * ng;
 #pragma unroll
-        for (int l = 0; l < PB_XLEVELS; l++) { o.is[l][0] = is[l * ng + 2 * qi]; o.is[l][1] = is[l * ng + 2 * qi + 1]; }
+        for (int l = 0; l < PB_XLEVELS; l++) { const int2 i2 = *reinterpret_cast<const int2*>(is + l * ng + 2 * qi); o.is[l][0] = i2.x; o.is[l][1] = i2.y; }
     }
 }
 
