@@ -129,6 +129,8 @@ class ClockSampler:
 
 def cpu_baseline(pb, batch: int, budget_s: float = 25.0):
     import oracle
+    # all host cores this process may use: torchrun exports OMP_NUM_THREADS=1 to its workers
+    oracle.set_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     from pyre_b200 import synth
     sys.path.insert(0, str(ROOT / "tests"))
     cfg = full_cfg(pb)
@@ -340,7 +342,7 @@ def run_ours(args):
                 "step_roofline": {"bytes_per_step": int(step_bytes), "weights": int(stats.weight_bytes_per_step), "kv": int(stats.kv_bytes_per_step), "state": int(stats.state_bytes_per_step),
                                   "achieved_gbs": round(step_bytes / (ms / args.steps) / 1e6, 1), "frac_of_peak": round(step_bytes / (ms / args.steps) / 1e6 / peak, 4), "peak_source": which},
                 "clocks": clocks, "build_s": round(t_build, 1), "layers": cfg.n_layers}
-        if not args.no_cpu:
+        if not args.no_cpu and world == 1:   # the CPU leg belongs to the single-GPU line only
             line["cpu_baseline"] = cpu_baseline(pb, B)
     # ---- verify window (speculative decoding): 8 tokens in one batched pass on the tensor-core GEMM
     verify = None

@@ -65,6 +65,8 @@ def lib():
         L.orc_model_new.restype = C.c_void_p
         L.orc_state_new.restype = C.c_void_p
         L.orc_threads.restype = C.c_int
+        L.orc_set_threads.argtypes = [C.c_int]
+        L.orc_set_threads.restype = None
         _lib = L
     return _lib
 
@@ -79,6 +81,11 @@ def _f32(a):
 
 def threads() -> int:
     return lib().orc_threads()
+
+
+def set_threads(n: int) -> None:
+    """Use n threads in the row-parallel loops (overrides an inherited OMP_NUM_THREADS)."""
+    lib().orc_set_threads(int(n))
 
 
 def geom(t: int):

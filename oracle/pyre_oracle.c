@@ -67,6 +67,17 @@ int orc_threads(void) {
 #endif
 }
 
+/* Thread count of the row-parallel loops (QMat::matmul splits rows over rayon's pool, gguf_q.rs:233-241;
+ * the reference sizes that pool itself, main.rs:251).  A launcher may have exported OMP_NUM_THREADS=1
+ * for its worker processes; a timed CPU run calls this with the number of cores it may use. */
+void orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* ------------------------------------------------------------------ block formats */
 
 int orc_type_geom(int type, int* el, int* by) {  /* gguf_q.rs:33-41 */

@@ -45,6 +45,7 @@ void orc_mat_row_raw(const orc_mat* m, int64_t r, uint8_t* out);
 void orc_mat_row(const orc_mat* m, int64_t r, float* y);       /* QMat::row :210 */
 void orc_matmul(const orc_mat* m, const float* x, int t, float* y);  /* QMat::matmul :217-242 (t<16 branch) */
 int orc_threads(void);
+void orc_set_threads(int n);   /* threads of the row-parallel loops from now on */
 
 /* Seeded synthetic block fields (see the generator section of pyre_oracle.c). */
 void orc_synth_rows(int type, uint64_t seed, uint64_t tid, int64_t cols, int64_t r0, int64_t nrows, uint8_t* out);
