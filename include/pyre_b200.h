@@ -59,6 +59,21 @@ int pb_ctx_own_stream(pb_ctx* ctx);
 int pb_ctx_sync(pb_ctx* ctx);
 /* Reads and clears the device status word (0 = no kernel reported a failure). */
 int pb_ctx_device_status(pb_ctx* ctx, int* status);
+/* Non-blocking check for the host's idle / step hooks (Model::idle_hook and step_hook,
+ * src/model/qwen4exp_gguf.rs:2024-2034; the reference also resizes its expert cache there, which has no
+ * counterpart: every expert is resident).  *busy = 1 while work of this context is still running on the GPU.
+ * When the GPU is idle and a kernel has reported a failure the call returns PB_ERR_DEVICE and clears the word. */
+int pb_poll(pb_ctx* ctx, int* busy);
+/* Tracing (the reference stamps its expert chain with a device clock, src/model/xchain.rs:1-111).  While enabled,
+ * every launch of a streaming kernel (GEMV, router, expert gate/up, expert down, DeltaNet, fused step) is handed
+ * the next of `slots` stamp slots and records %globaltimer nanoseconds at fixed points: words 0-5 by its first CTA
+ * (entry, set-up done, predecessor's data visible, activations ready, first weights landed, last store), words 6-7
+ * by its last CTA (entry, last store); the fused step kernel records one word per phase instead.  A captured
+ * graph keeps its slots, so a replay overwrites them: read after the step of interest.  slots = 0 turns tracing off.
+ * pb_ctx_stamps_read copies min(max_slots, used) slots of 8 words and the kernel id of each (1 GEMV, 2 router,
+ * 3 gate/up, 4 down, 5 DeltaNet, 7 fused step) and returns the number of slots used in *n_slots. */
+int pb_ctx_stamps_enable(pb_ctx* ctx, int slots);
+int pb_ctx_stamps_read(pb_ctx* ctx, uint64_t* stamps_host, int32_t* kernel_ids_host, int max_slots, int* n_slots);
 
 /* Expert-parallel group over NCCL (NVLink / NVSwitch), one process per GPU.  It replaces the
  * reference's CPU/GPU expert split (XCache + CPU pool, src/model/qwen4exp_gguf.rs:66-72, 785-893):
@@ -203,6 +218,8 @@ int pb_caps_get(const pb_model* m, pb_caps* caps);
 /* Counters for the reference's metrics hooks (src/metrics.rs:6-7). */
 typedef struct pb_stats {
     uint64_t steps, kernels_launched, weight_bytes_per_step, kv_bytes_per_step, state_bytes_per_step;
+    uint64_t device_ns;     /* GPU time of this state's token-loop calls so far (CUDA events around each call; add_gpu_ns) */
+    uint64_t exchange_ns;   /* of which: waiting for other GPUs in the expert exchange (0 on one GPU) */
 } pb_stats;
 int pb_stats_get(const pb_state* s, pb_stats* out);
 

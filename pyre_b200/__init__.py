@@ -54,11 +54,11 @@ class Caps(C.Structure):
 
 
 class Stats(C.Structure):
-    _fields_ = [(n, C.c_uint64) for n in ("steps", "kernels_launched", "weight_bytes_per_step", "kv_bytes_per_step", "state_bytes_per_step")]
+    _fields_ = [(n, C.c_uint64) for n in ("steps", "kernels_launched", "weight_bytes_per_step", "kv_bytes_per_step", "state_bytes_per_step", "device_ns", "exchange_ns")]
 
 
 def make_cfg(**kw) -> Cfg:
-    """BASELINE-shaped defaults (hidden 2048, 16:2 heads of 256, 512 experts top-10, DeltaNet 16/32 x 128)."""
+    """Defaults of the benchmark model (hidden 2048, 16:2 heads of 256, 512 experts top-10, DeltaNet 16/32 x 128)."""
     c = Cfg()
     d = dict(n_layers=4, d=2048, hc=0, hc_lr=0, n_head=16, n_kv=2, hd=256, n_rot=64, rope_base=1e7, eps=1e-6,
              n_exp=512, top_k=10, ff_exp=512, ff_sh=512, lin_nk=16, lin_nv=32, lin_dk=128, lin_dv=128,
@@ -125,6 +125,24 @@ class Ctx:
         st = C.c_int()
         self.check(lib().pb_ctx_device_status(self.h, C.byref(st)))
         return st.value
+
+    def poll(self) -> bool:
+        """True while work of this context is still running on the GPU (pb_poll); raises on a reported device failure."""
+        busy = C.c_int()
+        self.check(lib().pb_poll(self.h, C.byref(busy)))
+        return bool(busy.value)
+
+    def stamps_enable(self, slots: int):
+        self.check(lib().pb_ctx_stamps_enable(self.h, C.c_int(slots)))
+
+    def stamps_read(self, max_slots: int = 8192):
+        """(stamps [n][8] uint64 nanoseconds, kernel ids [n]) of the launches traced so far."""
+        st = np.zeros((max_slots, 8), dtype=np.uint64)
+        ids = np.zeros(max_slots, dtype=np.int32)
+        n = C.c_int()
+        self.check(lib().pb_ctx_stamps_read(self.h, _p(st), _p(ids), C.c_int(max_slots), C.byref(n)))
+        k = min(n.value, max_slots)
+        return st[:k], ids[:k]
 
     # ---- expert-parallel group (NCCL) ----
     def ep_unique_id(self) -> bytes:

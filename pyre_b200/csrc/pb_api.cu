@@ -1,13 +1,31 @@
 // C ABI: context and quantized-matrix entry points (include/pyre_b200.h).
 #include "pb_formats.cuh"
+#include "pb_common.cuh"
 #include "pb_internal.h"
 
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 #include <new>
+#include <pthread.h>
 
 static const char* kNoCtx = "pyre_b200: null context";
+
+int pb_enter(pb_ctx* ctx) {
+    if (!ctx) return PB_ERR_ARG;
+    // the reference's worker loads the model and makes every call on one thread (src/engine_qn.rs:13-17);
+    // PYRE_B200_CHECK_THREAD=1 turns a call from another thread into an error instead of undefined behaviour
+    if (ctx->check_thread && (unsigned long)pthread_self() != ctx->owner_thread) PB_FAIL(ctx, PB_ERR_STATE, "context used from a thread other than the one that created it");
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != ctx->device) PB_CUDA(ctx, cudaSetDevice(ctx->device));
+    return PB_OK;
+}
+
+unsigned long long* pb_stamp_slot(pb_ctx* ctx, int kernel_id) {
+    if (!ctx->stamps || ctx->stamp_next >= ctx->stamp_slots) return nullptr;
+    ctx->stamp_ids[ctx->stamp_next] = kernel_id;
+    return ctx->stamps + (size_t)PB_STAMP_WORDS * ctx->stamp_next++;
+}
 
 int pb_scratch(pb_ctx* ctx, size_t bytes, void** out) {
     if (bytes > ctx->scratch_bytes) {
@@ -57,6 +75,8 @@ int pb_ctx_create(int device, pb_ctx** out) {
     if (cudaMalloc(&c->xh_buf, PB_XH_BYTES) != cudaSuccess) { cudaFree(c->dev_status); cudaStreamDestroy(c->own_stream); delete c; return PB_ERR_OOM; }
     if (cudaMallocHost(&c->host_status, 256) != cudaSuccess) { cudaFree(c->dev_status); cudaStreamDestroy(c->own_stream); delete c; return PB_ERR_OOM; }
     *c->host_status = 0;
+    c->owner_thread = (unsigned long)pthread_self();
+    { const char* e = getenv("PYRE_B200_CHECK_THREAD"); c->check_thread = e && e[0] == '1'; }
     { const char* e = getenv("PYRE_B200_PDL"); if (e && e[0] == '0') c->use_pdl = false; }   // PYRE_B200_PDL=0: plain stream order inside the token step
     *out = c;
     return PB_OK;
@@ -68,6 +88,7 @@ int pb_ctx_destroy(pb_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     pb_ep_destroy(ctx);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->stamps) cudaFree(ctx->stamps);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
     if (ctx->xh_buf) cudaFree(ctx->xh_buf);
     if (ctx->host_status) cudaFreeHost(ctx->host_status);
@@ -80,6 +101,7 @@ const char* pb_last_error(const pb_ctx* ctx) { return ctx ? ctx->err.c_str() : k
 
 int pb_ctx_set_stream(pb_ctx* ctx, void* s) {
     if (!ctx) return PB_ERR_ARG;
+    PB_TRY(pb_enter(ctx));
     PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     ctx->stream = (cudaStream_t)s;
     return PB_OK;
@@ -87,6 +109,7 @@ int pb_ctx_set_stream(pb_ctx* ctx, void* s) {
 
 int pb_ctx_own_stream(pb_ctx* ctx) {
     if (!ctx) return PB_ERR_ARG;
+    PB_TRY(pb_enter(ctx));
     PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     ctx->stream = ctx->own_stream;
     return PB_OK;
@@ -94,15 +117,51 @@ int pb_ctx_own_stream(pb_ctx* ctx) {
 
 int pb_ctx_sync(pb_ctx* ctx) {
     if (!ctx) return PB_ERR_ARG;
+    PB_TRY(pb_enter(ctx));
     PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return PB_OK;
 }
 
 int pb_ctx_device_status(pb_ctx* ctx, int* status) {
     if (!ctx || !status) return PB_ERR_ARG;
+    PB_TRY(pb_enter(ctx));
     PB_CUDA(ctx, cudaMemcpyAsync(status, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (*status) PB_CUDA(ctx, cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), ctx->stream));
+    return PB_OK;
+}
+
+int pb_poll(pb_ctx* ctx, int* busy) {
+    if (!ctx || !busy) return PB_ERR_ARG;
+    PB_TRY(pb_enter(ctx));
+    const cudaError_t e = cudaStreamQuery(ctx->stream);
+    if (e == cudaErrorNotReady) { *busy = 1; return PB_OK; }
+    *busy = 0;
+    if (e != cudaSuccess) PB_FAIL(ctx, PB_ERR_CUDA, "cudaStreamQuery: %s", cudaGetErrorString(e));
+    return pb_sync_check(ctx, "pb_poll");   // idle: the status word can be read without waiting
+}
+
+int pb_ctx_stamps_enable(pb_ctx* ctx, int slots) {
+    if (!ctx || slots < 0) return PB_ERR_ARG;
+    PB_TRY(pb_enter(ctx));
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->stamps) { cudaFree(ctx->stamps); ctx->stamps = nullptr; }
+    ctx->stamp_slots = 0; ctx->stamp_next = 0; ctx->stamp_ids.clear();
+    if (slots == 0) return PB_OK;
+    PB_CUDA(ctx, cudaMalloc(&ctx->stamps, (size_t)slots * PB_STAMP_WORDS * 8));
+    PB_CUDA(ctx, cudaMemset(ctx->stamps, 0, (size_t)slots * PB_STAMP_WORDS * 8));
+    ctx->stamp_slots = slots; ctx->stamp_ids.assign((size_t)slots, 0);
+    return PB_OK;
+}
+
+int pb_ctx_stamps_read(pb_ctx* ctx, uint64_t* stamps_host, int32_t* kernel_ids_host, int max_slots, int* n_slots) {
+    if (!ctx || !n_slots) return PB_ERR_ARG;
+    PB_TRY(pb_enter(ctx));
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    const int n = ctx->stamp_next < max_slots ? ctx->stamp_next : max_slots;
+    if (n > 0 && stamps_host) PB_CUDA(ctx, cudaMemcpy(stamps_host, ctx->stamps, (size_t)n * PB_STAMP_WORDS * 8, cudaMemcpyDeviceToHost));
+    if (n > 0 && kernel_ids_host) for (int i = 0; i < n; i++) kernel_ids_host[i] = ctx->stamp_ids[i];
+    *n_slots = ctx->stamp_next;
     return PB_OK;
 }
 
@@ -119,7 +178,7 @@ static int qmat_alloc(pb_ctx* ctx, int type, int64_t rows, int64_t cols, pb_qmat
     m->ctx = ctx; m->type = type; m->rows = rows; m->cols = cols;
     m->row_bytes = cols / el * bs;
     m->nbytes = (size_t)rows * (size_t)m->row_bytes;
-    PB_CUDA(ctx, cudaSetDevice(ctx->device));
+    { const int rc = pb_enter(ctx); if (rc != PB_OK) { delete m; return rc; } }
     // padded so that 16-byte-granular bulk copies of the last rows stay inside the allocation
     cudaError_t e = cudaMalloc(&m->data, m->nbytes + 256);
     if (e != cudaSuccess) { delete m; PB_FAIL(ctx, PB_ERR_OOM, "cudaMalloc(%zu): %s", m->nbytes + 256, cudaGetErrorString(e)); }
@@ -195,6 +254,7 @@ static int check_rows(pb_ctx* ctx, const pb_qmat* m, int64_t r0, int64_t n, cons
 
 int pb_qmat_read(pb_ctx* ctx, const pb_qmat* m, int64_t r0, int64_t n, void* bytes) {
     PB_TRY(check_rows(ctx, m, r0, n, "pb_qmat_read"));
+    PB_TRY(pb_enter(ctx));
     if (!bytes) PB_FAIL(ctx, PB_ERR_ARG, "pb_qmat_read: null buffer");
     PB_CUDA(ctx, cudaMemcpyAsync(bytes, m->data + r0 * m->row_bytes, (size_t)n * m->row_bytes, cudaMemcpyDeviceToHost, ctx->stream));
     PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -203,6 +263,7 @@ int pb_qmat_read(pb_ctx* ctx, const pb_qmat* m, int64_t r0, int64_t n, void* byt
 
 int pb_qmat_dequant_dev(pb_ctx* ctx, const pb_qmat* m, int64_t r0, int64_t n, float* out) {
     PB_TRY(check_rows(ctx, m, r0, n, "pb_qmat_dequant"));
+    PB_TRY(pb_enter(ctx));
     if (!out) PB_FAIL(ctx, PB_ERR_ARG, "pb_qmat_dequant: null output");
     if ((n * m->cols) % 8) PB_FAIL(ctx, PB_UNSUPPORTED, "pb_qmat_dequant: element count must be a multiple of 8");
     if (m->type == PB_T_Q8_0 && ((r0 * m->cols) % 256)) PB_FAIL(ctx, PB_UNSUPPORTED, "pb_qmat_dequant: Q8_0 row offset must be a multiple of 256 elements");
@@ -213,6 +274,7 @@ int pb_qmat_dequant(pb_ctx* ctx, const pb_qmat* m, int64_t r0, int64_t n, float*
     PB_TRY(check_rows(ctx, m, r0, n, "pb_qmat_dequant"));
     if (!out_host) PB_FAIL(ctx, PB_ERR_ARG, "pb_qmat_dequant: null output");
     if (n == 0) return PB_OK;
+    PB_TRY(pb_enter(ctx));
     void* tmp;
     const size_t bytes = (size_t)n * m->cols * 4;
     PB_TRY(pb_scratch(ctx, bytes + 1024, &tmp));
@@ -226,6 +288,7 @@ int pb_gemv_dev(pb_ctx* ctx, const pb_qmat* m, const float* x, int t, float* y) 
     if (!ctx || !m) return PB_ERR_ARG;
     if (!x || !y) PB_FAIL(ctx, PB_ERR_ARG, "pb_gemv: null buffer");
     if (t < 0) PB_FAIL(ctx, PB_ERR_ARG, "pb_gemv: t=%d", t);
+    PB_TRY(pb_enter(ctx));
     for (int t0 = 0; t0 < t; t0 += 16) {
         PbGemvArgs a;
         a.w = m->data; a.wr = m->rdata; a.type = m->type; a.rows = m->rows; a.cols = (int)m->cols;
@@ -240,6 +303,7 @@ int pb_gemv(pb_ctx* ctx, const pb_qmat* m, const float* x_host, int t, float* y_
     if (!ctx || !m) return PB_ERR_ARG;
     if (!x_host || !y_host) PB_FAIL(ctx, PB_ERR_ARG, "pb_gemv: null buffer");
     if (t <= 0) return t == 0 ? PB_OK : PB_ERR_ARG;
+    PB_TRY(pb_enter(ctx));
     const size_t xb = ((size_t)t * m->cols * 4 + 255) & ~(size_t)255, yb = (size_t)t * m->rows * 4;
     void* tmp;
     PB_TRY(pb_scratch(ctx, xb + yb, &tmp));
@@ -256,7 +320,8 @@ int pb_gemv(pb_ctx* ctx, const pb_qmat* m, const float* x_host, int t, float* y_
 // Device staging area of pb_gemv_static: a fixed array inside the library image instead of a
 // cudaMalloc'd buffer.  Every GPU that loads the library carries these bytes until the
 // process exits.  In host code the symbol is only a stand-in; the device address is fetched
-// with cudaGetSymbolAddress once per device (with that device current) and cached.
+// with cudaGetSymbolAddress once per device (with that device current) and cached.  The cache is
+// filled without a lock: two threads that race on a device's slot both store the same address.
 static __device__ __align__(256) unsigned char pb_static_scratch[PB_GEMV_STATIC_MAX_BYTES];
 static void* g_static_scratch_addr[64] = {nullptr};
 
@@ -268,8 +333,8 @@ int pb_gemv_static(pb_ctx* ctx, const pb_qmat* m, const float* x_host, int t, fl
     const size_t xb = ((size_t)t * m->cols * 4 + 255) & ~(size_t)255, yb = (size_t)t * m->rows * 4;
     if (xb + yb > (size_t)PB_GEMV_STATIC_MAX_BYTES)
         PB_FAIL(ctx, PB_ERR_ARG, "pb_gemv_static: %zu bytes of staging needed (t * (cols + rows) floats), the built-in area holds %u; use pb_gemv", xb + yb, (unsigned)PB_GEMV_STATIC_MAX_BYTES);
+    PB_TRY(pb_enter(ctx));   // the context's GPU is current on every call, not only on the first
     if (!g_static_scratch_addr[ctx->device]) {   // first call on this device: resolve the device address of the array
-        PB_CUDA(ctx, cudaSetDevice(ctx->device));
         void* p = nullptr;
         PB_CUDA(ctx, cudaGetSymbolAddress(&p, pb_static_scratch));
         g_static_scratch_addr[ctx->device] = p;

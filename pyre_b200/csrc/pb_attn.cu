@@ -426,7 +426,19 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
     float* mw = mrg + (size_t)warp * G * (2 + hd);
     // per-warp staging of one packed tile
     uint32_t* tkw = stage_base + (size_t)warp * AT_STAGE_WORDS;
-    const int nsp = p.nsplit_packed, nrs = (int)gridDim.x - nsp;
+    // Share of the splits that walk the packed positions on the tensor cores (p.nsplit_packed > 0 enables that
+    // path), by estimated work at the sequence's current length: an f32 tile of 8 positions costs about two
+    // packed tiles of 32.  Computed here, from the position and the packed boundary the device holds, so that a
+    // captured graph keeps the right share however far the context has grown since its capture.
+    int nsp = 0;
+    if (p.nsplit_packed > 0) {
+        const int64_t q4 = q4n < n ? q4n : n;
+        const float wp = (float)(q4 / 32), wr = 2.0f * (float)((n - q4 + 7) / 8);
+        int nr = (int)((float)gridDim.x * wr / (wr + wp) + 0.5f);
+        nr = nr < 1 ? 1 : (nr > (int)gridDim.x - 1 ? (int)gridDim.x - 1 : nr);
+        nsp = (int)gridDim.x - nr;
+    }
+    const int nrs = (int)gridDim.x - nsp;
     // tiles that are packed and entirely below the current length go to the tensor-core splits
     const int64_t tpk = nsp > 0 ? (q4n < n ? q4n : n) / AT_TILE : 0;
     if (sp < nsp) {
@@ -653,8 +665,7 @@ int pb_launch_attn(pb_ctx* ctx, const PbAttnParams& p) {
     if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "attention needs %zu bytes of shared memory", smem);
 #define GO(GG)                                                                                                                   \
     {                                                                                                                            \
-        static bool cfgd = false;                                                                                                \
-        if (!cfgd) { PB_CUDA(ctx, cudaFuncSetAttribute(pb_attn_partial_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->max_smem_optin)); cfgd = true; } \
+        PB_TRY(pb_ensure_smem(ctx, pb_attn_partial_kernel<GG>, (size_t)ctx->max_smem_optin));                                     \
         pb_launch_k(ctx, pb_attn_partial_kernel<GG>, dim3(grid), dim3(AT_THREADS), (size_t)(smem), p);                                                  \
     }
     if (G == 8) GO(8) else if (G == 4) GO(4) else if (G == 2) GO(2) else GO(1)

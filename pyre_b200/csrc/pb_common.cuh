@@ -82,6 +82,15 @@ __device__ __forceinline__ void pb_bulk_g2s(void* smem_dst, const void* gsrc, ui
 __device__ __forceinline__ void pb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pb_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Phase stamps (tracing): when a launch was given a stamp slot, thread 0 of its first and of its last CTA record
+// %globaltimer (ns) at fixed points of the kernel; the host reads the slots back after the step (pb_ctx_stamps_read).
+// The reference traces its expert chain the same way (src/model/xchain.rs:1-111).  PB_STAMP_WORDS words per launch:
+//   first CTA: 0 entry, 1 set-up done, 2 predecessor's data visible, 3 activations ready, 4 first stage landed, 5 last store
+//   last CTA : 6 entry, 7 last store
+#define PB_STAMP_WORDS 8
+__device__ __forceinline__ unsigned long long pb_globaltimer() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ void pb_stamp(unsigned long long* slot, int phase, bool who) { if (slot && who) slot[phase] = pb_globaltimer(); }
+
 __device__ __forceinline__ float pb_h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
 
 __device__ __forceinline__ float pb_warp_sum(float v) {

@@ -31,8 +31,11 @@ __global__ void __launch_bounds__(DN_THREADS) pb_deltanet_kernel(const PbDeltaPa
     const int b = blockIdx.y;
     const int kh = h % nk;                                  // V head h reads K head h % nk (:1655)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool st_first = tid == 0 && blockIdx.x == 0 && blockIdx.y == 0, st_last = tid == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1;
+    pb_stamp(p.stamps, 0, st_first); pb_stamp(p.stamps, 6, st_last);
     pb_pdl_wait();
     pb_pdl_trigger();
+    pb_stamp(p.stamps, 2, st_first);
     const float* proj = p.proj + (size_t)b * p.ldp;        // [qkv (ch) | z | beta | alpha]
     float* ring = p.conv + (size_t)b * K * ch;             // [K slots][ch]
     const int64_t pos = p.pos[b];
@@ -88,6 +91,7 @@ __global__ void __launch_bounds__(DN_THREADS) pb_deltanet_kernel(const PbDeltaPa
     for (int i = tid; i < 2 * dk; i += DN_THREADS) sm[i] *= nrm[i < dk ? 0 : 1];
     __syncthreads();
 
+    pb_stamp(p.stamps, 3, st_first);   // conv and norms done
     // 3) gates (:1660)
     const float alpha = proj[ch + nv * dv + nv + h], beta = proj[ch + nv * dv + h];
     const float g = expf(pb_softplus(alpha + p.dt[h]) * p.a[h]);
@@ -129,9 +133,12 @@ __global__ void __launch_bounds__(DN_THREADS) pb_deltanet_kernel(const PbDeltaPa
             p.out[(size_t)b * p.ldo + h * dv + j0 + sl * DN_COLS + lane] = o;   // readout before the gated norm
         }
     }
+    pb_stamp(p.stamps, 5, st_first); pb_stamp(p.stamps, 7, st_last);
 }
 
-int pb_launch_deltanet(pb_ctx* ctx, const PbDeltaParams& p) {
+int pb_launch_deltanet(pb_ctx* ctx, const PbDeltaParams& p0) {
+    PbDeltaParams p = p0;
+    p.stamps = pb_stamp_slot(ctx, PB_K_DELTANET);
     if (p.dv % DN_COLS || (p.dk != 128 && p.dk != 64 && p.dk != 32) || p.conv_k < 2 || p.conv_k > 8)
         PB_FAIL(ctx, PB_UNSUPPORTED, "deltanet: dk=%d dv=%d conv_k=%d not supported", p.dk, p.dv, p.conv_k);
     // many sequences: a CTA walks all slices of its head (conv / norm / gates once per head)

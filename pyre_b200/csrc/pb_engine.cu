@@ -69,7 +69,22 @@ struct pb_state {
     std::vector<float*> ck_conv, ck_ssm;   // [n_lin * PB_MAX_WINDOW]
     int verify_t = 0; int64_t verify_pos0 = 0;
     uint64_t steps = 0, kernels_per_step = 0;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;   // GPU time of the token-loop calls (pb_stats.device_ns)
+    bool ev_open = false; uint64_t device_ns = 0;
 };
+// Brackets the GPU work of one token-loop call with two events; the elapsed time is added up once the call has synchronised.
+static void timing_begin(pb_state* s) {
+    pb_ctx* ctx = s->m->ctx;
+    if (!s->ev0 && (cudaEventCreate(&s->ev0) != cudaSuccess || cudaEventCreate(&s->ev1) != cudaSuccess)) { s->ev0 = s->ev1 = nullptr; return; }
+    s->ev_open = cudaEventRecord(s->ev0, ctx->stream) == cudaSuccess;
+}
+static void timing_stop(pb_state* s) { if (s->ev_open && cudaEventRecord(s->ev1, s->m->ctx->stream) != cudaSuccess) s->ev_open = false; }
+static void timing_collect(pb_state* s) {   // after the stream was synchronised
+    if (!s->ev_open) return;
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, s->ev0, s->ev1) == cudaSuccess) s->device_ns += (uint64_t)((double)ms * 1e6);
+    s->ev_open = false;
+}
 
 static PbSlot& slot(pb_model* m, int layer, int role) { return m->slots[(size_t)(layer + 1) * PB_R_COUNT + role]; }
 static pb_qmat* M(pb_model* m, int layer, int role) { return slot(m, layer, role).mat; }
@@ -116,6 +131,7 @@ int pb_model_create(pb_ctx* ctx, const pb_cfg* cfg, pb_model** out) {
 int pb_model_set_tensor(pb_model* m, int layer, int role, pb_qmat* mat) {
     if (!m || !mat) return PB_ERR_ARG;
     pb_ctx* ctx = m->ctx;
+    PB_TRY(pb_enter(ctx));
     if (layer < -1 || layer >= m->cfg.n_layers || role < 0 || role >= PB_R_COUNT) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_set_tensor: layer %d role %d out of range", layer, role);
     if (m->finalized) PB_FAIL(ctx, PB_ERR_STATE, "pb_model_set_tensor: model already finalized");
     PbSlot& s = slot(m, layer, role);
@@ -127,6 +143,7 @@ int pb_model_set_tensor(pb_model* m, int layer, int role, pb_qmat* mat) {
 int pb_model_set_vec(pb_model* m, int layer, int role, const float* v, int64_t n) {
     if (!m) return PB_ERR_ARG;
     pb_ctx* ctx = m->ctx;
+    PB_TRY(pb_enter(ctx));
     if (layer < -1 || layer >= m->cfg.n_layers || role < 0 || role >= PB_R_COUNT || !v || n <= 0) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_set_vec: bad argument (layer %d role %d n %lld)", layer, role, (long long)n);
     if (m->finalized) PB_FAIL(ctx, PB_ERR_STATE, "pb_model_set_vec: model already finalized");
     PbSlot& s = slot(m, layer, role);
@@ -157,6 +174,7 @@ static int need_vec(pb_model* m, int il, int role, int64_t n, const char* name) 
 int pb_model_finalize(pb_model* m, int ep_rank, int ep_world) {
     if (!m) return PB_ERR_ARG;
     pb_ctx* ctx = m->ctx;
+    PB_TRY(pb_enter(ctx));
     const pb_cfg& c = m->cfg;
     if (ep_world < 1 || ep_rank < 0 || ep_rank >= ep_world || c.n_exp % ep_world) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_finalize: rank %d of %d with %d experts", ep_rank, ep_world, c.n_exp);
     if (ep_world > 1 && (!ctx->ep_comm || ctx->ep_world != ep_world || ctx->ep_rank != ep_rank)) PB_FAIL(ctx, PB_ERR_STATE, "pb_model_finalize: call pb_ep_init(rank %d, world %d) on this context first", ep_rank, ep_world);
@@ -253,6 +271,7 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
     if (!m || !out) return PB_ERR_ARG;
     pb_ctx* ctx = m->ctx;
     *out = nullptr;
+    PB_TRY(pb_enter(ctx));
     if (!m->finalized) PB_FAIL(ctx, PB_ERR_STATE, "pb_state_create: call pb_model_finalize first");
     if (batch < 1 || batch > 1024) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_create: batch %d outside 1..1024", batch);
     const pb_cfg& c = m->cfg;
@@ -344,6 +363,8 @@ int pb_state_destroy(pb_state* s) {
     cudaSetDevice(s->m->ctx->device);
     cudaStreamSynchronize(s->m->ctx->stream);
     if (s->graph) cudaGraphExecDestroy(s->graph);
+    if (s->ev0) cudaEventDestroy(s->ev0);
+    if (s->ev1) cudaEventDestroy(s->ev1);
     for (cudaGraphExec_t g : s->win_graph) if (g) cudaGraphExecDestroy(g);
     for (void* p : s->allocs) cudaFree(p);
     if (s->pin_u32) cudaFreeHost(s->pin_u32);
@@ -354,7 +375,22 @@ int pb_state_destroy(pb_state* s) {
 int pb_state_set_pos(pb_state* s, int64_t pos) {
     if (!s) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx;
+    PB_TRY(pb_enter(ctx));
     if (pos < 0 || pos > s->m->cfg.max_ctx) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_set_pos: %lld outside 0..%d", (long long)pos, s->m->cfg.max_ctx);
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    // The packed boundary of the 4-bit cache only ever advances on the device (pb_kv_append_kernel): positions
+    // below it exist in packed form only.  Rewinding to 0 starts a fresh sequence (boundary back to 0); a
+    // position below the boundary cannot be served (the reference's spec_keep drops packed rows in that
+    // case, kv8_drop :2507; here the f32 rows are gone) and is refused.
+    if (s->m->cfg.kv_bits == 4 && s->m->n_attn > 0) {
+        std::vector<int64_t> q((size_t)s->batch);
+        for (int ai = 0; ai < s->m->n_attn; ai++) {
+            if (pos == 0) { PB_CUDA(ctx, cudaMemsetAsync(s->kv[ai].q4n, 0, (size_t)s->batch * 8, ctx->stream)); continue; }
+            PB_CUDA(ctx, cudaMemcpy(q.data(), s->kv[ai].q4n, q.size() * 8, cudaMemcpyDeviceToHost));
+            for (int b = 0; b < s->batch; b++)
+                if (pos < q[b]) PB_FAIL(ctx, PB_ERR_STATE, "pb_state_set_pos: position %lld is below the packed KV boundary %lld of sequence %d", (long long)pos, (long long)q[b], b);
+        }
+    }
     std::vector<int64_t> v((size_t)s->batch, pos);
     PB_CUDA(ctx, cudaMemcpyAsync(s->pos, v.data(), v.size() * 8, cudaMemcpyHostToDevice, ctx->stream));
     PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -422,18 +458,6 @@ static void attn_params(pb_state* s, int il, PbAttnParams& p) {
     p.kw = k.kw; p.ks = k.ks; p.vw = k.vw; p.vs = k.vs; p.kr = k.kr; p.vr = k.vr;
     p.max_ctx = c.kv_bits == 4 ? c.max_ctx : 1; p.ring_cap = s->ring_cap; p.kv_bits = c.kv_bits; p.kv_recent = c.kv_recent;
     p.pos = s->pos; p.q4n = k.q4n; p.part_ml = s->part_ml; p.part_acc = s->part_acc; p.nsplit = s->nsplit; p.nsplit_packed = s->nsplit_packed;
-    if (s->nsplit_packed > 0) {
-        // share the splits between the packed positions and the f32 ring by estimated work at the
-        // current length; a captured graph keeps the
-        // share of its capture position, which drifts by a few tiles per thousand tokens
-        const int64_t len = s->pos_host + 1;
-        const int64_t q4 = len > c.kv_recent ? ((len - c.kv_recent) / 64) * 64 : 0;
-        const double wp = (double)(q4 / 32), wr = 2.0 * (double)((len - q4 + 7) / 8);   // an f32 tile of 8 positions costs about two packed tiles of 32
-        int nrs = (int)(s->nsplit * wr / (wr + wp) + 0.5);
-        if (nrs < 1) nrs = 1;
-        if (nrs > s->nsplit - 1) nrs = s->nsplit - 1;
-        p.nsplit_packed = s->nsplit - nrs;
-    }
     p.att = s->att; p.lda = (int64_t)c.n_head * c.hd; p.batch = s->batch;
 }
 
@@ -638,11 +662,13 @@ static int step_once(pb_state* s) {
 int pb_forward(pb_state* s, const uint32_t* ids_host, int t, float* logits_host) {
     if (!s) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx;
+    PB_TRY(pb_enter(ctx));
     if (!ids_host || !logits_host || t < 1) PB_FAIL(ctx, PB_ERR_ARG, "pb_forward: bad argument");
     const int B = s->batch;
     if (B == 1 && !s->sharded && t >= 3) {
         // a prompt of one sequence: windows of up to 8 tokens, each streaming the weights once
         if (s->pos_host + t > s->m->cfg.max_ctx) PB_FAIL(ctx, PB_ERR_STATE, "context is full (%d positions)", s->m->cfg.max_ctx);
+        timing_begin(s);
         for (int j0 = 0; j0 < t; j0 += PB_MAX_WINDOW) {
             const int n = t - j0 < PB_MAX_WINDOW ? t - j0 : PB_MAX_WINDOW;
             for (int j = 0; j < n; j++) s->pin_u32[j] = ids_host[j0 + j];
@@ -651,29 +677,40 @@ int pb_forward(pb_state* s, const uint32_t* ids_host, int t, float* logits_host)
             if (j0 + n < t) PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // the pinned id buffer is reused
         }
         s->verify_t = 0;
+        timing_stop(s);
         PB_CUDA(ctx, cudaMemcpyAsync(logits_host, s->logits, (size_t)s->m->cfg.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
-        return pb_sync_check(ctx, "pb_forward");
+        const int rcw = pb_sync_check(ctx, "pb_forward");
+        timing_collect(s);
+        return rcw;
     }
+    timing_begin(s);
     for (int j = 0; j < t; j++) {
         for (int b = 0; b < B; b++) s->pin_u32[b] = ids_host[(size_t)b * t + j];
         PB_CUDA(ctx, cudaMemcpyAsync(s->ids, s->pin_u32, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
         PB_TRY(step_once(s));
         if (j + 1 < t) PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // the pinned id buffer is reused
     }
+    timing_stop(s);
     PB_CUDA(ctx, cudaMemcpyAsync(logits_host, s->logits, (size_t)B * s->m->cfg.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    return pb_sync_check(ctx, "pb_forward");
+    const int rc = pb_sync_check(ctx, "pb_forward");
+    timing_collect(s);
+    return rc;
 }
 
 int pb_step_greedy(pb_state* s, const uint32_t* tok_host, uint32_t* next_host) {
     if (!s) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx;
+    PB_TRY(pb_enter(ctx));
     if (!tok_host || !next_host) PB_FAIL(ctx, PB_ERR_ARG, "pb_step_greedy: null buffer");
     const int B = s->batch;
     memcpy(s->pin_u32, tok_host, (size_t)B * 4);
     PB_CUDA(ctx, cudaMemcpyAsync(s->ids, s->pin_u32, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
+    timing_begin(s);
     PB_TRY(step_once(s));
+    timing_stop(s);
     PB_CUDA(ctx, cudaMemcpyAsync(s->pin_u32 + B, s->next, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream));
     PB_TRY(pb_sync_check(ctx, "pb_step_greedy"));
+    timing_collect(s);
     memcpy(next_host, s->pin_u32 + B, (size_t)B * 4);
     return PB_OK;
 }
@@ -681,15 +718,19 @@ int pb_step_greedy(pb_state* s, const uint32_t* tok_host, uint32_t* next_host) {
 int pb_decode_greedy(pb_state* s, const uint32_t* tok_host, int n, uint32_t* out_host) {
     if (!s) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx;
+    PB_TRY(pb_enter(ctx));
     if (!tok_host || !out_host || n < 1) PB_FAIL(ctx, PB_ERR_ARG, "pb_decode_greedy: bad argument");
     if (n > s->trace_cap) PB_FAIL(ctx, PB_ERR_ARG, "pb_decode_greedy: at most %lld tokens per call", (long long)s->trace_cap);
     const int B = s->batch;
     memcpy(s->pin_u32, tok_host, (size_t)B * 4);
     PB_CUDA(ctx, cudaMemcpyAsync(s->ids, s->pin_u32, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
     PB_CUDA(ctx, cudaMemsetAsync(s->trace_len, 0, 8, ctx->stream));
+    timing_begin(s);
     for (int j = 0; j < n; j++) PB_TRY(step_once(s));
+    timing_stop(s);
     PB_CUDA(ctx, cudaMemcpyAsync(s->pin_u32 + 2 * B, s->trace, (size_t)n * B * 4, cudaMemcpyDeviceToHost, ctx->stream));
     PB_TRY(pb_sync_check(ctx, "pb_decode_greedy"));
+    timing_collect(s);
     for (int j = 0; j < n; j++) for (int b = 0; b < B; b++) out_host[(size_t)b * n + j] = s->pin_u32[2 * B + (size_t)j * B + b];
     return PB_OK;
 }
@@ -704,6 +745,7 @@ int pb_decode_greedy(pb_state* s, const uint32_t* tok_host, int n, uint32_t* out
 int pb_verify(pb_state* s, const uint32_t* ids_host, int t, float* logits_host) {
     if (!s) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    PB_TRY(pb_enter(ctx));
     if (!ids_host || !logits_host) PB_FAIL(ctx, PB_ERR_ARG, "pb_verify: null buffer");
     if (s->batch != 1) PB_FAIL(ctx, PB_ERR_STATE, "pb_verify: the state must have batch 1 (it has %d)", s->batch);
     if (t < 1 || t > PB_MAX_WINDOW) PB_FAIL(ctx, PB_ERR_ARG, "pb_verify: window of %d tokens (1..%d)", t, PB_MAX_WINDOW);
@@ -716,9 +758,12 @@ int pb_verify(pb_state* s, const uint32_t* ids_host, int t, float* logits_host) 
     s->verify_pos0 = s->pos_host; s->verify_t = 0;
     for (int j = 0; j < t; j++) s->pin_u32[j] = ids_host[j];
     PB_CUDA(ctx, cudaMemcpyAsync(s->ids, s->pin_u32, (size_t)t * 4, cudaMemcpyHostToDevice, ctx->stream));
+    timing_begin(s);
     PB_TRY(window_once(s, t, true, true));
+    timing_stop(s);
     PB_CUDA(ctx, cudaMemcpyAsync(logits_host, s->logits, (size_t)t * c.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
     PB_TRY(pb_sync_check(ctx, "pb_verify"));
+    timing_collect(s);
     s->verify_t = t;
     return PB_OK;
 }
@@ -730,6 +775,7 @@ int pb_verify(pb_state* s, const uint32_t* ids_host, int t, float* logits_host) 
 int pb_keep(pb_state* s, int t, int keep) {
     if (!s) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    PB_TRY(pb_enter(ctx));
     if (s->verify_t == 0 || t != s->verify_t) PB_FAIL(ctx, PB_ERR_STATE, "pb_keep: t=%d does not match the last verify window (%d)", t, s->verify_t);
     if (keep < 1 || keep > t) PB_FAIL(ctx, PB_ERR_ARG, "pb_keep: keep=%d outside 1..%d", keep, t);
     if (keep < t) {
@@ -751,20 +797,33 @@ int pb_draft(pb_state* s, int, uint32_t*, int* n) { if (!s) return PB_ERR_ARG; i
 struct PbSnapHeader { uint64_t magic; int32_t n_layers, d, batch, kv_bits; int64_t pos; uint64_t bytes; };
 static const uint64_t kSnapMagic = 0x3150414e53425050ull;   // "PPBSNAP1"
 
-static size_t snap_size(const pb_state* s) {
+// q4[ai * B + b] = packed boundary of sequence b in attention layer ai.  The boundary is what the device holds
+// (after a rollback it is ahead of the value the current length alone would give), so a snapshot reads it back
+// and stores it; a restore takes it from the snapshot.
+static size_t snap_size(const pb_state* s, const std::vector<int64_t>& q4) {
     const pb_cfg& c = s->m->cfg; const int B = s->batch;
     const int64_t len = s->pos_host;
-    const int64_t q4n = c.kv_bits == 4 && len > c.kv_recent ? ((len - c.kv_recent) / 64) * 64 : 0;
     size_t n = sizeof(PbSnapHeader) + (size_t)s->m->n_lin * (conv_elems(c, B) + ssm_elems(c, B)) * 4;
-    const size_t per_head = 8 + 2 * ((size_t)q4n * (c.hd / 8) * 4 + (size_t)q4n * (c.hd / 32) * 4) + 2 * (size_t)(len - q4n) * c.hd * 4;
-    return n + (size_t)s->m->n_attn * B * c.n_kv * per_head;
+    for (int ai = 0; ai < s->m->n_attn; ai++)
+        for (int b = 0; b < B; b++) {
+            const int64_t q4n = q4[(size_t)ai * B + b];
+            n += (size_t)c.n_kv * (8 + 2 * ((size_t)q4n * (c.hd / 8) * 4 + (size_t)q4n * (c.hd / 32) * 4) + 2 * (size_t)(len - q4n) * c.hd * 4);
+        }
+    return n;
+}
+static int snap_read_q4(pb_state* s, std::vector<int64_t>& q4) {
+    pb_ctx* ctx = s->m->ctx; const int B = s->batch;
+    q4.assign((size_t)s->m->n_attn * B, 0);
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (int ai = 0; ai < s->m->n_attn; ai++) PB_CUDA(ctx, cudaMemcpy(q4.data() + (size_t)ai * B, s->kv[ai].q4n, (size_t)B * 8, cudaMemcpyDeviceToHost));
+    for (int64_t v : q4) if (v < 0 || v > s->pos_host || v % 64) PB_FAIL(ctx, PB_ERR_STATE, "packed KV boundary %lld does not fit the position %lld", (long long)v, (long long)s->pos_host);
+    return PB_OK;
 }
 
-static int snap_io(pb_state* s, uint8_t* buf, bool save) {
+static int snap_io(pb_state* s, uint8_t* buf, bool save, const std::vector<int64_t>& q4) {
     pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg; const int B = s->batch;
     const cudaMemcpyKind kind = save ? cudaMemcpyDeviceToHost : cudaMemcpyHostToDevice;
     const int64_t len = s->pos_host;
-    const int64_t q4n = c.kv_bits == 4 && len > c.kv_recent ? ((len - c.kv_recent) / 64) * 64 : 0;
     uint8_t* p = buf + sizeof(PbSnapHeader);
     auto io = [&](void* dev, size_t bytes) -> int {
         if (bytes) { if (save) PB_CUDA(ctx, cudaMemcpy(p, dev, bytes, kind)); else PB_CUDA(ctx, cudaMemcpy(dev, p, bytes, kind)); }
@@ -776,6 +835,7 @@ static int snap_io(pb_state* s, uint8_t* buf, bool save) {
         for (int b = 0; b < B; b++)
             for (int h = 0; h < c.n_kv; h++) {
                 const size_t head = (size_t)b * c.n_kv + h;
+                const int64_t q4n = q4[(size_t)ai * B + b];
                 int64_t q = q4n;
                 if (save) memcpy(p, &q, 8); else PB_CUDA(ctx, cudaMemcpy(k.q4n + b, &q, 8, cudaMemcpyHostToDevice));
                 p += 8;
@@ -798,14 +858,17 @@ static int snap_io(pb_state* s, uint8_t* buf, bool save) {
 int pb_state_snapshot(pb_state* s, void* buf_host, size_t* nbytes) {
     if (!s || !nbytes) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx;
-    const size_t need = snap_size(s);
+    PB_TRY(pb_enter(ctx));
+    std::vector<int64_t> q4;
+    PB_TRY(snap_read_q4(s, q4));
+    const size_t need = snap_size(s, q4);
     if (!buf_host) { *nbytes = need; return PB_OK; }
     if (*nbytes < need) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_snapshot: buffer of %zu bytes, %zu needed", *nbytes, need);
     PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     PbSnapHeader h; memset(&h, 0, sizeof h);
     h.magic = kSnapMagic; h.n_layers = s->m->cfg.n_layers; h.d = s->m->cfg.d; h.batch = s->batch; h.kv_bits = s->m->cfg.kv_bits; h.pos = s->pos_host; h.bytes = need;
     memcpy(buf_host, &h, sizeof h);
-    PB_TRY(snap_io(s, (uint8_t*)buf_host, true));
+    PB_TRY(snap_io(s, (uint8_t*)buf_host, true, q4));
     *nbytes = need;
     return PB_OK;
 }
@@ -813,16 +876,34 @@ int pb_state_snapshot(pb_state* s, void* buf_host, size_t* nbytes) {
 int pb_state_restore(pb_state* s, const void* buf_host, size_t nbytes) {
     if (!s) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx;
+    PB_TRY(pb_enter(ctx));
     if (!buf_host || nbytes < sizeof(PbSnapHeader)) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_restore: truncated snapshot");
     PbSnapHeader h; memcpy(&h, buf_host, sizeof h);
     if (h.magic != kSnapMagic) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_restore: not a snapshot");
     if (h.n_layers != s->m->cfg.n_layers || h.d != s->m->cfg.d || h.batch != s->batch || h.kv_bits != s->m->cfg.kv_bits) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_restore: snapshot of a different model or batch");
     if (h.pos < 0 || h.pos > s->m->cfg.max_ctx || h.bytes != nbytes) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_restore: truncated or corrupt snapshot (%zu bytes, header says %llu)", nbytes, (unsigned long long)h.bytes);
     PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    // walk the snapshot once for the stored boundaries (first field of every (layer, sequence, KV head) section)
+    const pb_cfg& c = s->m->cfg; const int B = s->batch;
+    std::vector<int64_t> q4((size_t)s->m->n_attn * B, 0);
+    {
+        size_t off = sizeof(PbSnapHeader) + (size_t)s->m->n_lin * (conv_elems(c, B) + ssm_elems(c, B)) * 4;
+        for (int ai = 0; ai < s->m->n_attn; ai++)
+            for (int b = 0; b < B; b++)
+                for (int hh = 0; hh < c.n_kv; hh++) {
+                    if (off + 8 > nbytes) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_restore: truncated snapshot");
+                    int64_t q; memcpy(&q, (const uint8_t*)buf_host + off, 8);
+                    if (q < 0 || q > h.pos || q % 64 || (c.kv_bits != 4 && q != 0)) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_restore: corrupt snapshot (packed boundary %lld at position %lld)", (long long)q, (long long)h.pos);
+                    q4[(size_t)ai * B + b] = q;
+                    off += 8 + 2 * ((size_t)q * (c.hd / 8) * 4 + (size_t)q * (c.hd / 32) * 4) + 2 * (size_t)(h.pos - q) * c.hd * 4;
+                }
+        if (off != nbytes) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_restore: size mismatch");
+    }
+    // position first (a fresh boundary of 0 so that any position is accepted), then the sections
+    for (int ai = 0; ai < s->m->n_attn; ai++) PB_CUDA(ctx, cudaMemsetAsync(s->kv[ai].q4n, 0, (size_t)B * 8, ctx->stream));
     PB_TRY(pb_state_set_pos(s, h.pos));
-    if (snap_size(s) != nbytes) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_restore: size mismatch");
     s->verify_t = 0;
-    return snap_io(s, (uint8_t*)const_cast<void*>(buf_host), false);
+    return snap_io(s, (uint8_t*)const_cast<void*>(buf_host), false, q4);
 }
 
 int pb_stats_get(const pb_state* s, pb_stats* out) {
@@ -834,6 +915,7 @@ int pb_stats_get(const pb_state* s, pb_stats* out) {
     const uint64_t packed = c.kv_bits == 4 && len > (uint64_t)c.kv_recent ? ((len - c.kv_recent) / 64) * 64 : 0;
     out->kv_bytes_per_step = (uint64_t)s->m->n_attn * s->batch * 2 * c.n_kv * (packed * (c.hd / 2 + c.hd / 8) + (len - packed) * c.hd * 4);
     out->state_bytes_per_step = (uint64_t)s->m->n_lin * s->batch * 2 * ((uint64_t)c.lin_nv * c.lin_dk * c.lin_dv * 4);
+    out->device_ns = s->device_ns; out->exchange_ns = 0;
     return PB_OK;
 }
 
@@ -849,6 +931,7 @@ static int layer_ok(pb_state* s, int layer, int want_kind, const char* who) {
 int pb_moe_forward(pb_state* s, int layer, const float* x_host, int t, float* y_host, int32_t* sel_host) {
     if (!s) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    PB_TRY(pb_enter(ctx));
     PB_TRY(layer_ok(s, layer, -1, "pb_moe_forward"));
     if (!x_host || !y_host || t < 0 || t > s->batch) PB_FAIL(ctx, PB_ERR_ARG, "pb_moe_forward: t=%d (state batch %d)", t, s->batch);
     if (t == 0) return PB_OK;
@@ -862,6 +945,7 @@ int pb_moe_forward(pb_state* s, int layer, const float* x_host, int t, float* y_
 int pb_deltanet_step(pb_state* s, int layer, const float* x_host, float* y_host) {
     if (!s) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    PB_TRY(pb_enter(ctx));
     PB_TRY(layer_ok(s, layer, 0, "pb_deltanet_step"));
     if (!x_host || !y_host) PB_FAIL(ctx, PB_ERR_ARG, "pb_deltanet_step: null buffer");
     PB_CUDA(ctx, cudaMemcpyAsync(s->xin, x_host, (size_t)s->batch * c.d * 4, cudaMemcpyHostToDevice, ctx->stream));
@@ -873,6 +957,7 @@ int pb_deltanet_step(pb_state* s, int layer, const float* x_host, float* y_host)
 int pb_attn_step(pb_state* s, int layer, const float* x_host, float* y_host) {
     if (!s) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    PB_TRY(pb_enter(ctx));
     PB_TRY(layer_ok(s, layer, 1, "pb_attn_step"));
     if (!x_host || !y_host) PB_FAIL(ctx, PB_ERR_ARG, "pb_attn_step: null buffer");
     if (s->pos_host + 1 > c.max_ctx) PB_FAIL(ctx, PB_ERR_STATE, "context is full (%d positions)", c.max_ctx);
@@ -886,6 +971,7 @@ int pb_attn_step(pb_state* s, int layer, const float* x_host, float* y_host) {
 int pb_state_get_lin(pb_state* s, int layer, float* conv_host, float* ssm_host) {
     if (!s) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    PB_TRY(pb_enter(ctx));
     PB_TRY(layer_ok(s, layer, 0, "pb_state_get_lin"));
     const int li = s->m->idx[layer], K = c.conv_k, ch = 2 * c.lin_nk * c.lin_dk + c.lin_nv * c.lin_dv;
     PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -898,6 +984,7 @@ int pb_state_get_lin(pb_state* s, int layer, float* conv_host, float* ssm_host) 
 int pb_state_set_lin(pb_state* s, int layer, const float* conv_host, const float* ssm_host) {
     if (!s) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    PB_TRY(pb_enter(ctx));
     PB_TRY(layer_ok(s, layer, 0, "pb_state_set_lin"));
     const int li = s->m->idx[layer], K = c.conv_k, ch = 2 * c.lin_nk * c.lin_dk + c.lin_nv * c.lin_dv;
     PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -912,6 +999,7 @@ int pb_state_set_lin(pb_state* s, int layer, const float* conv_host, const float
 int pb_state_fill_kv(pb_state* s, int b, int ai, const float* k_host, const float* v_host, int64_t n) {
     if (!s) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    PB_TRY(pb_enter(ctx));
     if (b < 0 || b >= s->batch || ai < 0 || ai >= s->m->n_attn || !k_host || !v_host || n < 0 || n > c.max_ctx) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_fill_kv: bad argument");
     PbKv& kv = s->kv[ai];
     const int hd = c.hd, nkv = c.n_kv;
@@ -942,6 +1030,7 @@ int pb_state_fill_kv(pb_state* s, int b, int ai, const float* k_host, const floa
 int pb_state_fill_kv_synth(pb_state* s, int ai, int64_t n, uint64_t seed) {
     if (!s) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    PB_TRY(pb_enter(ctx));
     if (ai < 0 || ai >= s->m->n_attn || n < 0 || n > c.max_ctx) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_fill_kv_synth: bad argument");
     PbKv& kv = s->kv[ai];
     const int hd = c.hd, nkv = c.n_kv;
@@ -974,6 +1063,7 @@ int pb_kv4_pack(pb_ctx* ctx, const float* x_host, int64_t n, uint32_t* words_hos
     if (!ctx) return PB_ERR_ARG;
     if (!x_host || !words_host || !scales_host || n < 0 || n % 32) PB_FAIL(ctx, PB_ERR_ARG, "pb_kv4_pack: length %lld is not a multiple of 32", (long long)n);   // kv4.rs:13
     if (n == 0) return PB_OK;
+    PB_TRY(pb_enter(ctx));
     void* scr;
     const size_t xb = (size_t)n * 4, wb = (size_t)n / 2, sb = (size_t)n / 8;
     PB_TRY(pb_scratch(ctx, xb + wb + sb + 1024, &scr));
@@ -989,6 +1079,7 @@ int pb_kv4_unpack(pb_ctx* ctx, const uint32_t* words_host, const float* scales_h
     if (!ctx) return PB_ERR_ARG;
     if (!x_host || !words_host || !scales_host || n < 0 || n % 32) PB_FAIL(ctx, PB_ERR_ARG, "pb_kv4_unpack: length %lld is not a multiple of 32", (long long)n);
     if (n == 0) return PB_OK;
+    PB_TRY(pb_enter(ctx));
     void* scr;
     const size_t xb = (size_t)n * 4, wb = (size_t)n / 2, sb = (size_t)n / 8;
     PB_TRY(pb_scratch(ctx, xb + wb + sb + 1024, &scr));

@@ -358,8 +358,7 @@ static int launch_h(pb_ctx* ctx, const PbGemvQArgs& a, const uint8_t* tile_buf) 
     if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "gemm: %zu bytes of shared memory needed for cols=%d t=%d", smem, a.cols, a.t);
     p.xh_in = tile_buf + 256; p.xinv_in = reinterpret_cast<const float*>(tile_buf);
     auto kern = pb_gemmh_iq3s_kernel<NT, NST, RC>;
-    static size_t configured = 0;
-    if (smem > configured) { PB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = smem; }
+    PB_TRY(pb_ensure_smem(ctx, kern, smem));
     const int grid = nchunks < ctx->sm_count ? nchunks : ctx->sm_count;
     pb_launch_k(ctx, kern, dim3(grid), dim3(GH_THREADS), smem, p);
     ctx->kernels_launched++;

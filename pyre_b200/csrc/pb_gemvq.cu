@@ -40,9 +40,12 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
     ring.stage_bytes = p.stage_bytes;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool st_first = tid == 0 && blockIdx.x == 0, st_last = tid == 0 && blockIdx.x == gridDim.x - 1;
+    pb_stamp(p.stamps, 0, st_first); pb_stamp(p.stamps, 6, st_last);
     pb_pdl_trigger();   // the next kernel may start its own set-up and weight stream
     pb_ring_init(ring, tid);
     __syncthreads();
+    pb_stamp(p.stamps, 1, st_first);
 
     const int my_chunks = p.nchunks > (int)blockIdx.x ? (p.nchunks - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
@@ -69,6 +72,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
     constexpr int CT = PB_CONSUMERS * 32;
     const PbQTabs T = pb_fill_qtabs<FMT>(tab, p.rep, tid, CT, lane);
     pb_pdl_wait();      // activations (and the residual this kernel may add to) come from earlier kernels
+    pb_stamp(p.stamps, 2, st_first);
     const int ng = cols / 32;
     if (p.mode == PB_ACT_PREQ) {
         for (int i = tid; i < NB * xw; i += CT) { const int b = i / xw; xq[i] = b < p.t ? p.xq_in[(size_t)b * xw + (i - b * xw)] : 0u; }
@@ -111,6 +115,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
         }
     }
     pb_named_barrier(1, CT);
+    pb_stamp(p.stamps, 3, st_first);
 
     // lane -> (row sub-index, quarter)
     const int nquarters = 4 * p.bpr;
@@ -129,6 +134,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
 
     for (int k = 0; k < my_chunks; k++) {
         if (!pb_ring_wait(ring, k, p.status)) return;
+        if (k == 0) pb_stamp(p.stamps, 4, st_first);
         const int chunk = (int)blockIdx.x + k * (int)gridDim.x;
         int s = 0;
         while (s + 1 < p.nseg && chunk >= p.seg[s + 1].chunk0) s++;
@@ -198,6 +204,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
         }
         pb_ring_release(ring, k, lane);
     }
+    pb_stamp(p.stamps, 5, st_first); pb_stamp(p.stamps, 7, st_last);
 }
 
 template <int FMT, int NB, int PASSES>
@@ -208,6 +215,7 @@ static int launch_q(pb_ctx* ctx, const PbGemvQArgs& a, int row_bytes) {
     p.x = a.x; p.ldx = a.ldx; p.t = a.t; p.y = a.y; p.ldy = a.ldy; p.status = ctx->dev_status;
     p.mode = a.mode; p.norm_w = a.norm_w; p.z = a.z; p.ldz = a.ldz; p.head_dim = a.head_dim; p.eps = a.eps;
     p.xq_in = a.xq_in; p.accumulate = a.accumulate;
+    p.stamps = pb_stamp_slot(ctx, PB_K_GEMVQ);
     const int grid_max = ctx->sm_count;
     int64_t total_rows = 0;
     for (int s = 0; s < a.nseg; s++) total_rows += a.seg[s].rows;
@@ -244,8 +252,7 @@ static int launch_q(pb_ctx* ctx, const PbGemvQArgs& a, int row_bytes) {
     const size_t smem = fixed + (size_t)PB_STAGES * p.stage_bytes;
     if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "gemv: %zu bytes of shared memory needed for cols=%d t=%d", smem, a.cols, a.t);
     auto kern = pb_gemvq_kernel<FMT, NB, PASSES>;
-    static size_t configured = 0;   // per template instance
-    if (smem > configured) { PB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = smem; }
+    PB_TRY(pb_ensure_smem(ctx, kern, smem));
     const int grid = nchunks < grid_max ? nchunks : grid_max;
     pb_launch_k(ctx, kern, dim3(grid), dim3(PB_KTHREADS), (size_t)(smem), p);
     ctx->kernels_launched++;

@@ -2,7 +2,9 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
 #include <string.h>
+#include <map>
 #include <string>
 #include <vector>
 
@@ -29,7 +31,18 @@ struct pb_ctx {
     bool pdl_chain = false;  // the previous op on the stream was one of our kernels
     void* ep_comm = nullptr;
     int ep_rank = 0, ep_world = 1;
+    // largest dynamic shared-memory size set so far per kernel function: the attribute belongs to the device's
+    // copy of the function, so the cache lives in the context, not in the process
+    std::map<const void*, size_t> smem_cfg;
+    // tracing: stamp slots handed to the launches of the streaming kernels while enabled (pb_ctx_stamps_enable)
+    unsigned long long* stamps = nullptr; int stamp_slots = 0, stamp_next = 0;
+    std::vector<int> stamp_ids;   // kernel id (PB_K_*) per handed-out slot
+    unsigned long owner_thread = 0;   // pthread id of the creating thread (checked when PYRE_B200_CHECK_THREAD=1)
+    bool check_thread = false;
 };
+// Every extern "C" entry point that touches the device calls this first: makes the context's GPU current
+// (a process may hold contexts on several GPUs) and, in the debug mode, verifies the calling thread.
+int pb_enter(pb_ctx* ctx);
 int pb_ep_allreduce(pb_ctx* ctx, float* buf, size_t n);
 int pb_ep_allgather(pb_ctx* ctx, const float* send, float* recv, size_t n);
 int pb_ep_reduce_scatter(pb_ctx* ctx, const float* send, float* recv, size_t n);
@@ -84,6 +97,22 @@ static inline void pb_launch_k(pb_ctx* ctx, K kern, dim3 grid, dim3 block, size_
     ctx->pdl_chain = ctx->pdl_scope > 0;
     cudaLaunchKernelEx(&cfg, kern, args...);   // errors are picked up by cudaGetLastError at the call site
 }
+
+// Raise the kernel's dynamic shared-memory limit on this context's device when `smem` exceeds what was set before.
+template <typename K>
+static inline int pb_ensure_smem(pb_ctx* ctx, K kern, size_t smem) {
+    const void* key = reinterpret_cast<const void*>(kern);
+    auto it = ctx->smem_cfg.find(key);
+    if (it != ctx->smem_cfg.end() && it->second >= smem) return PB_OK;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { char b[256]; snprintf(b, sizeof b, "cudaFuncSetAttribute(%zu bytes of shared memory): %s", smem, cudaGetErrorString(e)); ctx->err = b; return PB_ERR_CUDA; }
+    ctx->smem_cfg[key] = smem;
+    return PB_OK;
+}
+
+// next stamp slot (PB_STAMP_WORDS words), or null when tracing is off or the slots are used up; kernel_id is recorded on the host
+unsigned long long* pb_stamp_slot(pb_ctx* ctx, int kernel_id);
+enum { PB_K_GEMVQ = 1, PB_K_ROUTER = 2, PB_K_EXPERT_GU = 3, PB_K_EXPERT_DOWN = 4, PB_K_DELTANET = 5, PB_K_ATTN = 6, PB_K_STEP = 7 };
 
 int pb_scratch(pb_ctx* ctx, size_t bytes, void** out);
 int pb_sync_check(pb_ctx* ctx, const char* who);
@@ -141,6 +170,7 @@ struct PbGemvQParams {
     const uint8_t* xh_in; const float* xinv_in;   // pb_gemmh.cu: f16 fragments and prescale inverses made by its prep kernel
     int accumulate;
     int* status;
+    unsigned long long* stamps;
 };
 bool pb_gemvq_supported(int type, int cols);
 int pb_launch_gemvq(pb_ctx* ctx, const PbGemvQArgs& a);
@@ -163,6 +193,7 @@ struct PbRouterParams {
     // gathered tokens (no GEMV)
     int phase; float* xcopy;
     float* zero; int64_t zero_n;              // phases 0 and 2: zero_n floats (a multiple of 4) cleared for the expert kernels (expert parallelism)
+    unsigned long long* stamps;
 };
 struct PbRouteParams {
     const float* logits; int64_t ldl; int t, n_exp, top_k;
@@ -185,6 +216,7 @@ struct PbExpertParams {
     int bpr, row_bytes, rows_per_chunk; uint32_t stage_bytes, tab_bytes; int rep;
     int nx;                                   // activation-level vectors of a chunk's first nx entries ride along with its weights
     int* status;
+    unsigned long long* stamps;
 };
 struct PbCombineParams {
     const float* part; const float* part_sh; const float* logits; int64_t ldl;
@@ -205,6 +237,7 @@ struct PbDeltaParams {
     const int64_t* pos;                       // [batch]
     float* out; int64_t ldo;                  // [batch][nv*dv] readout before the gated norm
     int nk, nv, dk, dv, conv_k, batch;
+    unsigned long long* stamps;
 };
 int pb_launch_deltanet(pb_ctx* ctx, const PbDeltaParams& p);
 

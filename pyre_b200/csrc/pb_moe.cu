@@ -99,8 +99,11 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
     extern __shared__ float rs[];   // 2048 ints for the routing pass, then scale[t]
     float* scale = rs + 2048;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool st_first = tid == 0 && blockIdx.x == 0 && blockIdx.y == 0;
+    pb_stamp(p.stamps, 0, st_first);
     pb_pdl_wait();
     pb_pdl_trigger();
+    pb_stamp(p.stamps, 2, st_first);
     if (p.zero && p.phase != 1) {
         // expert parallelism: the partial-row buffer must be zero where other ranks' experts write; cleared
         // here instead of by a memset node between the launches (which would also end the dependent-launch chain)
@@ -135,6 +138,7 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
             pb_split_groups4(v, lane, g0, p.cols, p.xq_out + (size_t)b * pb_xq_words(p.cols));
         }
     }
+    pb_stamp(p.stamps, 3, st_first);   // activations split
     const int row = blockIdx.x * 8 + warp;
     if (p.phase != 2 && row <= p.n_exp) {
         const float* wrow = row < p.n_exp ? p.router + (size_t)row * p.cols : p.sh_gate_inp;
@@ -185,12 +189,16 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
     __shared__ int is_last;
     __threadfence();
     __syncthreads();
+    pb_stamp(p.stamps, 5, st_first);   // this CTA's logits stored
     if (tid == 0) is_last = atomicAdd(ticket, 1u) == gridDim.x * gridDim.y - 1;
     __syncthreads();
     if (!is_last) return;
     if (tid == 0) *ticket = 0;
     __threadfence();
+    pb_stamp(p.stamps, 6, tid == 0);   // the routing pass starts (all logits are in)
     pb_route_body(rp, reinterpret_cast<int*>(rs));
+    __syncthreads();
+    pb_stamp(p.stamps, 7, tid == 0);
 }
 
 // ------------------------------------------------------------------------------------ expert gate/up
@@ -208,10 +216,14 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
     ring.stages = tab + p.tab_bytes;
     ring.stage_bytes = p.stage_bytes;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool st_first = tid == 0 && blockIdx.x == 0, st_last = tid == 0 && blockIdx.x == gridDim.x - 1;
+    pb_stamp(p.stamps, 0, st_first); pb_stamp(p.stamps, 6, st_last);
     pb_pdl_trigger();
     pb_ring_init(ring, tid);
     __syncthreads();
+    pb_stamp(p.stamps, 1, st_first);
     pb_pdl_wait();   // the expert lists come from the routing kernel
+    pb_stamp(p.stamps, 2, st_first);
 
     const int cols = p.bpr * 256;
     const int n_used = *p.n_used;
@@ -297,9 +309,11 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
     const int lpr = nquarters < 32 ? nquarters : 32, rpw = 32 / lpr;
     const int sub = lane / lpr, ql = lane - sub * lpr;
     const int xw = pb_xq_words(cols);
+    pb_stamp(p.stamps, 3, st_first);
 
     for (int k = 0; k < my_chunks; k++) {
         if (!pb_ring_wait(ring, k, p.status)) return;
+        if (k == 0) pb_stamp(p.stamps, 4, st_first);
         const int4 hd = hdr[k % PB_STAGES];
         const int r0 = hd.x, e0 = hd.y, e1 = hd.z;
         const bool shared = hd.w != 0;
@@ -345,6 +359,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_gu_kernel(const PbEx
         }
         pb_ring_release(ring, k, lane);
     }
+    pb_stamp(p.stamps, 5, st_first); pb_stamp(p.stamps, 7, st_last);
 }
 
 // y[tok][r] = sigmoid(shared-gate logit) * shared[tok][r] + sum_j part[tok][j][r]  (ascending expert id),
@@ -571,13 +586,17 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_rows_kernel(con
     const uint32_t slice = (uint32_t)PB_DR_ROWS * p.row_bytes;                // bytes of one expert's 16 rows
     uint8_t* stages = reinterpret_cast<uint8_t*>(xq) + (((size_t)PB_DR_MAXE * xw * 4 + 127) & ~(size_t)127);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool st_first = tid == 0 && blockIdx.x == 0, st_last = tid == 0 && blockIdx.x == gridDim.x - 1;
+    pb_stamp(p.stamps, 0, st_first); pb_stamp(p.stamps, 6, st_last);
     pb_pdl_trigger();
     if (tid == 0) {
         for (int i = 0; i < PB_DR_MAXE; i++) pb_mbar_init(&full[i], 1);
         pb_fence_barrier_init();
     }
     __syncthreads();
+    pb_stamp(p.stamps, 1, st_first);
     pb_pdl_wait();   // expert lists and hidden vectors come from earlier kernels
+    pb_stamp(p.stamps, 2, st_first);
     const int n_used = *p.n_used;
     const int nsl = n_used + (p.has_shared ? 1 : 0);   // slices: the used experts in ascending id, then the shared expert
     const int r0 = (int)blockIdx.x * PB_DR_ROWS;
@@ -612,6 +631,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_rows_kernel(con
         pb_split_groups4(*reinterpret_cast<const float4*>(hv + 32 * g0 + 4 * lane), lane, g0, cols, xq + (size_t)k * xw);
     }
     pb_named_barrier(1, CT);
+    pb_stamp(p.stamps, 3, st_first);
 
     const int nquarters = 4 * p.bpr;                    // <= 32 (checked on the host)
     const int rpw = 32 / nquarters, sub = lane / nquarters, ql = lane - sub * nquarters;
@@ -619,6 +639,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_rows_kernel(con
     for (int i = warp; i < nsl * ppe; i += PB_CONSUMERS) {
         const int k = i / ppe, r = (i - k * ppe) * rpw + sub;
         if (!pb_mbar_wait(&full[k], 0, p.status, PB_DEV_WAIT_FULL_TIMEOUT)) break;
+        if (i == 0) pb_stamp(p.stamps, 4, st_first);
         PbQuarter wq; PbXQuarter xv;
         D::quarter(pb_smem_u32(stages + (size_t)k * slice) + (uint32_t)r * p.row_bytes + (ql >> 2) * D::STEP_BYTES, ql & 3, T, wq);
         pb_load_xquarter<PbQDec<FMT>::AFFINE>(xq + (size_t)k * xw, cols, ql, xv);
@@ -638,6 +659,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_rows_kernel(con
         float* dst = cp.y + (size_t)p.sh_tok0 * cp.ldy + r0 + tid;
         *dst = cp.accumulate ? *dst + y : y;
     }
+    pb_stamp(p.stamps, 5, st_first); pb_stamp(p.stamps, 7, st_last);
 }
 
 // ------------------------------------------------------------------------------------ combine
@@ -658,7 +680,9 @@ int pb_launch_router(pb_ctx* ctx, const PbRouterParams& p, const PbRouteParams& 
     if (rp.top_k > PB_MAX_TOPK || rp.n_exp > 1024) PB_FAIL(ctx, PB_UNSUPPORTED, "route: top_k %d / n_exp %d beyond %d / 1024", rp.top_k, rp.n_exp, PB_MAX_TOPK);
     const int grid = p.phase == 2 ? (p.cols / 128 > 0 ? p.cols / 128 : 1) : (p.n_exp + 1 + 7) / 8;   // phase 2 only splits (4 groups of 32 per CTA) and routes
     const size_t smem = (size_t)(2048 + ((p.t + 31) & ~31)) * 4;
-    pb_launch_k(ctx, pb_router_kernel, dim3(grid, (p.t + PB_ROUTER_TPG - 1) / PB_ROUTER_TPG), dim3(256), smem, p, rp, ticket);
+    PbRouterParams ps = p;
+    ps.stamps = pb_stamp_slot(ctx, PB_K_ROUTER);
+    pb_launch_k(ctx, pb_router_kernel, dim3(grid, (p.t + PB_ROUTER_TPG - 1) / PB_ROUTER_TPG), dim3(256), smem, ps, rp, ticket);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;
@@ -691,14 +715,14 @@ static int launch_expert(pb_ctx* ctx, PbExpertParams p, int cols, const PbCombin
     const size_t smem = 256 + p.tab_bytes + xbytes + (size_t)PB_STAGES * p.stage_bytes;
     if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "expert kernel needs %zu bytes of shared memory", smem);
     p.status = ctx->dev_status;
+    p.stamps = pb_stamp_slot(ctx, DOWN ? PB_K_EXPERT_DOWN : PB_K_EXPERT_GU);
     if (DOWN && cp && p.t == 1 && p.top_k + 1 <= PB_DR_MAXE && p.rows_e % PB_DR_ROWS == 0 && 4 * p.bpr <= 32 && PB_DR_ROWS % (32 / (4 * p.bpr)) == 0 && PASSES == 1) {
         // one token, combine requested: the row-partitioned kernel writes y directly
         const size_t xbytes1 = (((size_t)PB_DR_MAXE * pb_xq_words(cols) * 4 + 127) & ~(size_t)127);
         const size_t smem1 = 128 + PB_DR_MAXE * PB_DR_ROWS * 4 + p.tab_bytes + xbytes1 + (size_t)PB_DR_MAXE * PB_DR_ROWS * p.row_bytes;
         if (smem1 <= (size_t)ctx->max_smem_optin) {
             auto kern = pb_expert_down_rows_kernel<FMT>;
-            static size_t configured1 = 0;
-            if (smem1 > configured1) { PB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1)); configured1 = smem1; }
+            PB_TRY(pb_ensure_smem(ctx, kern, smem1));
             pb_launch_k(ctx, kern, dim3(p.rows_e / PB_DR_ROWS), dim3(PB_KTHREADS), smem1, p, *cp);
             ctx->kernels_launched++;
             PB_CUDA(ctx, cudaGetLastError());
@@ -712,14 +736,12 @@ static int launch_expert(pb_ctx* ctx, PbExpertParams p, int cols, const PbCombin
             PB_CUDA(ctx, cudaGetLastError());
         }
         auto kern = pb_expert_down_kernel<FMT, PASSES>;
-        static size_t configured = 0;
-        if (smem > configured) { PB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = smem; }
+        PB_TRY(pb_ensure_smem(ctx, kern, smem));
         PbCombineParams c0; memset(&c0, 0, sizeof c0);
         pb_launch_k(ctx, kern, dim3(ctx->sm_count), dim3(PB_KTHREADS), (size_t)(smem), p, cp ? *cp : c0, cp ? ticket : (unsigned int*)nullptr);
     } else {
         auto kern = pb_expert_gu_kernel<FMT, PASSES>;
-        static size_t configured = 0;
-        if (smem > configured) { PB_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = smem; }
+        PB_TRY(pb_ensure_smem(ctx, kern, smem));
         pb_launch_k(ctx, kern, dim3(ctx->sm_count), dim3(PB_KTHREADS), (size_t)(smem), p);
     }
     ctx->kernels_launched++;

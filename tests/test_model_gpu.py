@@ -155,3 +155,91 @@ def test_snapshot_restore(ctx, kv_bits):
     with pytest.raises(pb.PyreError):
         m.new_state(2).restore(blob)                       # different batch
     a.destroy(); b.destroy(); m.destroy()
+
+
+def test_snapshot_after_rollback_across_repack_boundary(ctx):
+    """A verify window that crosses a 64-position repack boundary moves the packed boundary of the 4-bit cache
+    forward; rolling the window back (spec_keep) does not move it back.  A snapshot taken then must carry the
+    boundary the device holds, and a state restored from it must continue exactly like the original."""
+    cfg = small_cfg(pb, n_layers=8, kv_bits=4, kv_recent=64, max_ctx=400)
+    spec = synth.model_spec(cfg, 8)
+    m = synth.build_model(ctx, cfg, spec, 8)
+    a = m.new_state(1)
+    a.forward((np.arange(121, dtype=np.uint32) * 7 + 3) % cfg.vocab)       # pos 121; ring capacity 64 + 64
+    a.forward_multi(np.array([5, 6, 7, 8, 9, 10, 11, 12], np.uint32))       # len reaches 129: positions 0..63 packed
+    a.spec_keep(8, 1)                                                      # back to pos 122, boundary stays at 64
+    assert a.pos() == 122
+    blob = a.snapshot()
+    b = m.new_state(1)
+    b.restore(blob)
+    assert b.pos() == 122
+    ta = a.decode_greedy([77], 48)[0].tolist()
+    tb = b.decode_greedy([77], 48)[0].tolist()
+    assert ta == tb
+    with pytest.raises(pb.PyreError) as e:
+        a.set_pos(10)                                                      # below the packed boundary
+    assert e.value.status == pb.PB_ERR_STATE
+    for s in (a, b):
+        s.destroy()
+    m.destroy()
+
+
+def test_rewound_state_equals_fresh_state(ctx):
+    """set_pos(0) starts a new sequence in a used state: the packed boundary goes back to 0, so new f32 rows are not
+    mistaken for packed ones.  With the DeltaNet state cleared the tokens equal those of a fresh state."""
+    cfg = small_cfg(pb, n_layers=8, kv_bits=4, kv_recent=64, max_ctx=400)
+    spec = synth.model_spec(cfg, 9)
+    m = synth.build_model(ctx, cfg, spec, 9)
+    a = m.new_state(1)
+    a.decode_greedy([3], 200)                                              # boundary at 128 by now
+    a.set_pos(0)
+    ch = 2 * cfg.lin_nk * cfg.lin_dk + cfg.lin_nv * cfg.lin_dv
+    for il in range(cfg.n_layers):
+        if (il + 1) % cfg.full_every:
+            a.set_lin(il, np.zeros((1, cfg.conv_k - 1, ch), np.float32), np.zeros((1, cfg.lin_nv, cfg.lin_dk, cfg.lin_dv), np.float32))
+    f = m.new_state(1)
+    assert a.decode_greedy([9], 150)[0].tolist() == f.decode_greedy([9], 150)[0].tolist()
+    a.destroy(); f.destroy(); m.destroy()
+
+
+def test_step_graph_captured_early_serves_a_long_context(ctx):
+    """The step graph is captured on the second step.  Captured at an almost empty context and replayed after the
+    cache was filled to thousands of positions, it must still give the tokens of a graph captured at that length:
+    the split of attention work between packed and f32 positions is made on the device from the current length."""
+    cfg = small_cfg(pb, n_layers=4, kv_bits=4, kv_recent=64, max_ctx=4400)
+    spec = synth.model_spec(cfg, 10)
+    m = synth.build_model(ctx, cfg, spec, 10)
+    rng = np.random.default_rng(5)
+    k = rng.standard_normal((4000, cfg.n_kv * cfg.hd)).astype(np.float32); v = rng.standard_normal((4000, cfg.n_kv * cfg.hd)).astype(np.float32)
+    early = m.new_state(1)
+    early.decode_greedy([1], 4)                                            # graph captured at positions 1..3
+    early.set_pos(0)
+    for il in range(cfg.n_layers):
+        if (il + 1) % cfg.full_every:
+            ch = 2 * cfg.lin_nk * cfg.lin_dk + cfg.lin_nv * cfg.lin_dv
+            early.set_lin(il, np.zeros((1, cfg.conv_k - 1, ch), np.float32), np.zeros((1, cfg.lin_nv, cfg.lin_dk, cfg.lin_dv), np.float32))
+    late = m.new_state(1)
+    for s in (early, late):
+        s.fill_kv(0, 0, k, v); s.set_pos(4000)
+    assert early.decode_greedy([2], 24)[0].tolist() == late.decode_greedy([2], 24)[0].tolist()
+    early.destroy(); late.destroy(); m.destroy()
+
+
+def test_contexts_on_two_devices_in_one_process():
+    """One process may hold a context per GPU: kernel attributes (shared-memory limits) are kept per context and
+    every entry point makes its context's GPU current."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    outs = []
+    ctxs = [pb.Ctx(0), pb.Ctx(1)]
+    x = np.random.default_rng(0).standard_normal((1, 2048)).astype(np.float32)
+    mats = [pb.QMat.synth(c, pb.IQ3_S, 4096, 2048, 0, 5) for c in ctxs]
+    for _ in range(2):                                                     # alternate, so the current device keeps changing
+        for W in mats:
+            outs.append(W.matmul(x))
+    assert all(np.array_equal(outs[0], o) for o in outs[1:])
+    for W in mats:
+        W.free()
+    for c in ctxs:
+        c.close()
