@@ -71,7 +71,9 @@ int pb_poll(pb_ctx* ctx, int* busy);
  * by its last CTA (entry, last store); the fused step kernel records one word per phase instead.  A captured
  * graph keeps its slots, so a replay overwrites them: read after the step of interest.  slots = 0 turns tracing off.
  * pb_ctx_stamps_read copies min(max_slots, used) slots of 8 words and the kernel id of each (1 GEMV, 2 router,
- * 3 gate/up, 4 down, 5 DeltaNet, 7 fused step) and returns the number of slots used in *n_slots. */
+ * 3 gate/up, 4 down, 5 DeltaNet; operations inside the fused step kernel: 101 GEMV, 102 DeltaNet, 103 router,
+ * 104 gate/up, 105 down, stamped at operation start / grid barrier passed / activations ready / first weights
+ * landed / end) and returns the number of slots used in *n_slots. */
 int pb_ctx_stamps_enable(pb_ctx* ctx, int slots);
 int pb_ctx_stamps_read(pb_ctx* ctx, uint64_t* stamps_host, int32_t* kernel_ids_host, int max_slots, int* n_slots);
 
@@ -238,6 +240,13 @@ int pb_attn_step(pb_state* s, int layer, const float* x_host, float* y_host);
  * conv [batch][conv_k-1][ch]. */
 int pb_state_get_lin(pb_state* s, int layer, float* conv_host, float* ssm_host);
 int pb_state_set_lin(pb_state* s, int layer, const float* conv_host, const float* ssm_host);
+/* Inspection: the first n floats of one of the step's activation buffers as the last operation left them
+ * (what: 0 residual x [batch][d], 1 projection outputs, 2 DeltaNet readout, 3 attention output, 4 router logits
+ * [n_exp + 1], 5 routed experts' hidden vectors in accumulation order [top_k][ff], 6 shared expert's hidden vector,
+ * 7 with tracing on before the state's first step: the fused step kernel's clock stamps, per operation uint64 [CTA][4]
+ * (operation start, grid barrier passed, operation end, producer warp done) followed by 32 fine-grained stamps of CTA 0,
+ * read as 2 floats per stamp). */
+int pb_state_peek(pb_state* s, int what, float* out_host, int64_t n);
 
 /* 4-bit KV packing on the device: kv4::pack / kv4::get, src/model/kv4.rs:12-42.
  * x_host [n] f32 (n a multiple of 32) -> words_host [n/8], scales_host [n/32]. */

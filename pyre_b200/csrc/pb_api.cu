@@ -47,6 +47,7 @@ int pb_sync_check(pb_ctx* ctx, const char* who) {
     const int st = *ctx->host_status;
     if (st) {
         cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), ctx->stream);
+        cudaMemsetAsync(ctx->grid_sync, 0, 256, ctx->stream);   // a fused step that gave up leaves its barrier counter mid-way
         PB_FAIL(ctx, PB_ERR_DEVICE, "%s: a kernel reported device status %d", who, st);
     }
     return PB_OK;
@@ -73,6 +74,8 @@ int pb_ctx_create(int device, pb_ctx** out) {
     if (cudaMalloc(&c->dev_status, 256) != cudaSuccess) { cudaStreamDestroy(c->own_stream); delete c; return PB_ERR_OOM; }
     cudaMemset(c->dev_status, 0, 256);
     if (cudaMalloc(&c->xh_buf, PB_XH_BYTES) != cudaSuccess) { cudaFree(c->dev_status); cudaStreamDestroy(c->own_stream); delete c; return PB_ERR_OOM; }
+    if (cudaMalloc(&c->grid_sync, 256) != cudaSuccess) { cudaFree(c->xh_buf); cudaFree(c->dev_status); cudaStreamDestroy(c->own_stream); delete c; return PB_ERR_OOM; }
+    cudaMemset(c->grid_sync, 0, 256);
     if (cudaMallocHost(&c->host_status, 256) != cudaSuccess) { cudaFree(c->dev_status); cudaStreamDestroy(c->own_stream); delete c; return PB_ERR_OOM; }
     *c->host_status = 0;
     c->owner_thread = (unsigned long)pthread_self();
@@ -91,6 +94,7 @@ int pb_ctx_destroy(pb_ctx* ctx) {
     if (ctx->stamps) cudaFree(ctx->stamps);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
     if (ctx->xh_buf) cudaFree(ctx->xh_buf);
+    if (ctx->grid_sync) cudaFree(ctx->grid_sync);
     if (ctx->host_status) cudaFreeHost(ctx->host_status);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;

@@ -10,6 +10,7 @@
 // router logits back to the host in every layer.
 #include "pb_stream.cuh"
 #include "pb_internal.h"
+#include "pb_step.cuh"
 
 #include <stdio.h>
 #include <stdlib.h>
@@ -69,6 +70,13 @@ struct pb_state {
     std::vector<float*> ck_conv, ck_ssm;   // [n_lin * PB_MAX_WINDOW]
     int verify_t = 0; int64_t verify_pos0 = 0;
     uint64_t steps = 0, kernels_per_step = 0;
+    // fused step (pb_step.cu), one sequence on one GPU: operation list on the device, launch segments (runs of operations
+    // between attention cores, which keep their own kernels), hidden vectors of the selected experts
+    int fused = -1;                                   // -1 not decided yet, 0 not eligible, 1 built
+    PbStepOp* fops = nullptr; float* fh = nullptr; PsLayout flay{};
+    unsigned long long* ftrace = nullptr; int ftrace_ops = 0;   // tracing: per-CTA stamps [op][grid][4]
+    struct FSeg { int begin, end, attn_layer, nbar; };   // attn_layer >= 0: the attention core of that layer follows the segment; nbar: its grid barriers
+    std::vector<FSeg> fsegs;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;   // GPU time of the token-loop calls (pb_stats.device_ns)
     bool ev_open = false; uint64_t device_ns = 0;
 };
@@ -304,6 +312,7 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
     s->ldg = c.d + ((c.n_exp + 1 + 3) & ~3);
     if (s->sharded) { A(xg, (size_t)Bm * s->ldg); A(xs, (size_t)B * s->ldg); A(part_rs, (size_t)B * c.top_k * c.d); }
     A(logits, (size_t)Ba * c.vocab);
+    if (B == 1 && !s->sharded) { A(fops, (size_t)c.n_layers * 8 + 8); A(fh, (size_t)(c.top_k + 1) * c.ff_exp); }
     s->trace_cap = 4096;
     A(trace, (size_t)s->trace_cap * B); A(trace_len, 2);
     // attention: one CTA per SM (split x KV head x sequence)
@@ -555,9 +564,172 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
     return pb_launch_moe_combine(ctx, k);
 }
 
+
+// ------------------------------------------------------------------------------------ fused step (pb_step.cu)
+
+static bool recoded(pb_qmat* q) { return q && q->type == PB_T_IQ3_S && q->rdata != nullptr; }
+
+// Decides whether the state can run its steps through the fused kernel and, if so, builds the operation list.
+// Conditions: one sequence, one GPU, pre-norm residual, every quantized matrix with a re-coded copy (IQ3_S), widths
+// the kernel's lane mappings cover.  PYRE_B200_FUSED=0 keeps the per-operation kernels.
+static int fused_build(pb_state* s) {
+    pb_model* m = s->m; pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg;
+    s->fused = 0;
+    const bool on = !(getenv("PYRE_B200_FUSED") && atoi(getenv("PYRE_B200_FUSED")) == 0);   // read when a state takes its first step
+    if (!on || s->batch != 1 || s->sharded || m->ep_world != 1 || c.hc != 0) return PB_OK;
+    const int d = c.d, ff = c.ff_exp, w_lin = c.lin_nv * c.lin_dv, w_att = c.n_head * c.hd;
+    auto pow2 = [](int v) { return v > 0 && (v & (v - 1)) == 0; };
+    if (d % 256 || d > 2048 || !pow2(d / 64) || ff % 512 || !pow2(ff / 64) || ff / 64 > 32 || c.ff_sh != ff) return PB_OK;
+    if (c.top_k + 1 > 16 || c.n_exp > 1024 || d % 16 || d / 16 > ctx->sm_count) return PB_OK;
+    pb_qmat* head = M(m, -1, PB_R_OUTPUT) ? M(m, -1, PB_R_OUTPUT) : M(m, -1, PB_R_TOKEN_EMBD);
+    if (!recoded(head)) return PB_OK;
+    int maxcols = d;
+    for (int il = 0; il < c.n_layers; il++) {
+        if (m->kind[il]) {
+            if (!recoded(M(m, il, PB_R_ATTN_Q)) || !recoded(M(m, il, PB_R_ATTN_K)) || !recoded(M(m, il, PB_R_ATTN_V)) || !recoded(M(m, il, PB_R_ATTN_O))) return PB_OK;
+            if (w_att % 256 || w_att > 4096 || !pow2(w_att / 64)) return PB_OK;
+            maxcols = w_att > maxcols ? w_att : maxcols;
+        } else {
+            if (!recoded(M(m, il, PB_R_LIN_QKV)) || !recoded(M(m, il, PB_R_LIN_Z)) || !recoded(M(m, il, PB_R_LIN_BETA)) || !recoded(M(m, il, PB_R_LIN_ALPHA)) || !recoded(M(m, il, PB_R_LIN_OUT))) return PB_OK;
+            if (w_lin % 256 || w_lin > 4096 || !pow2(w_lin / 64) || c.lin_dk != 128 || c.lin_dv != 128 || c.conv_k > 8 || c.lin_nv * (c.lin_dv / 32) > ctx->sm_count) return PB_OK;
+            maxcols = w_lin > maxcols ? w_lin : maxcols;
+        }
+        const int roles[6] = {PB_R_EXP_GATE, PB_R_EXP_UP, PB_R_EXP_DOWN, PB_R_SH_GATE, PB_R_SH_UP, PB_R_SH_DOWN};
+        for (int r : roles) if (!recoded(M(m, il, r))) return PB_OK;
+        if (M(m, il, PB_R_EXP_GATE)->rows != (int64_t)c.n_exp * ff) return PB_OK;   // all experts resident (no expert parallelism)
+    }
+    // ---- shared-memory layout
+    PsLayout L;
+    auto up128 = [](size_t v) { return (uint32_t)((v + 127) & ~(size_t)127); };
+    L.xf_off = 8192;                                                            // after the misc area and the warps' operation copies
+    const size_t xf_bytes = (size_t)maxcols * 4 > 12288 ? (size_t)maxcols * 4 : 12288;   // also the DeltaNet unit's scratch and the routing keys (10.5 KB)
+    L.nw_off = up128(L.xf_off + xf_bytes);
+    L.xq_off = up128(L.nw_off + (size_t)d * 4);
+    const size_t xq_a = (size_t)pb_xq_words(maxcols) * 4, xq_b = (size_t)(c.top_k + 1) * pb_xq_words(ff) * 4;
+    L.stage_off = up128(L.xq_off + (xq_a > xq_b ? xq_a : xq_b));
+    const size_t avail = (size_t)ctx->max_smem_optin > L.stage_off ? (size_t)ctx->max_smem_optin - L.stage_off : 0;
+    size_t stage = avail / PS_STAGES;
+    if (stage > 34944) stage = 34944;
+    stage &= ~(size_t)127;
+    L.stage_bytes = (uint32_t)stage; L.total = L.stage_off + PS_STAGES * L.stage_bytes;
+    auto n4_row = [](int cols) { return cols / 256 * 136; };
+    auto rows_per_chunk = [&](int cols) {
+        const int lpr = cols / 64 < 32 ? cols / 64 : 32, step_rows = PB_CONSUMERS * (32 / lpr);
+        int rpc = (int)(stage / (size_t)n4_row(cols)) / step_rows * step_rows;
+        if (rpc > 2 * step_rows) rpc = 2 * step_rows;
+        return rpc;
+    };
+    const int rpw_d = 32 / (d / 64 < 32 ? d / 64 : 32), rg = 8 * rpw_d;
+    if (rows_per_chunk(d) <= 0 || rows_per_chunk(maxcols) <= 0 || ff % rg || (size_t)2 * rg * n4_row(d) > stage || (size_t)d * 4 > stage || (size_t)16 * n4_row(ff) > stage) return PB_OK;
+    // ---- operations
+    std::vector<PbStepOp> ops;
+    s->fsegs.clear();
+    int seg_begin = 0;
+    auto push = [&](PbStepOp& op, int kind) {
+        op.kind = kind;
+        op.flags = (int)ops.size() == seg_begin ? 0 : PS_F_BARRIER;
+        op.stamps = pb_stamp_slot(ctx, 100 + kind);   // traced as operation kinds 101..105
+        ops.push_back(op);
+    };
+    auto gemv = [&](int cols, int mode, const float* x, const float* norm_w, const float* z, float* y, int accumulate, std::initializer_list<std::pair<pb_qmat*, int>> segs) {
+        PbStepOp op; memset(&op, 0, sizeof op);
+        PsGemvOp& g = op.g;
+        g.cols = cols; g.row_bytes = n4_row(cols); g.rows_per_chunk = rows_per_chunk(cols); g.mode = mode; g.accumulate = accumulate; g.head_dim = c.lin_dv;
+        g.x = x; g.norm_w = norm_w; g.z = z; g.y = y; g.eps = c.eps;
+        int nchunks = 0;
+        for (auto& sg : segs) {
+            PbGemvQSeg& q = g.seg[g.nseg++];
+            q.w = sg.first->rdata; q.rows = (int)sg.first->rows; q.yoff = sg.second; q.chunk0 = nchunks;
+            nchunks += (int)((sg.first->rows + g.rows_per_chunk - 1) / g.rows_per_chunk);
+        }
+        g.nchunks = nchunks;
+        push(op, PS_GEMV);
+    };
+    const int ch = 2 * c.lin_nk * c.lin_dk + w_lin;
+    for (int il = 0; il < c.n_layers; il++) {
+        if (m->kind[il]) {
+            const int nq = c.n_head * 2 * c.hd, row = c.n_kv * c.hd;
+            gemv(d, PB_ACT_NORM, s->x, V(m, il, PB_R_ATTN_NORM), nullptr, s->proj, 0, {{M(m, il, PB_R_ATTN_Q), 0}, {M(m, il, PB_R_ATTN_K), nq}, {M(m, il, PB_R_ATTN_V), nq + row}});
+            s->fsegs.push_back({seg_begin, (int)ops.size(), il, 0});
+            seg_begin = (int)ops.size();
+            gemv(w_att, PB_ACT_PLAIN, s->att, nullptr, nullptr, s->x, 1, {{M(m, il, PB_R_ATTN_O), 0}});
+        } else {
+            const int li = m->idx[il];
+            gemv(d, PB_ACT_NORM, s->x, V(m, il, PB_R_ATTN_NORM), nullptr, s->proj, 0,
+                 {{M(m, il, PB_R_LIN_QKV), 0}, {M(m, il, PB_R_LIN_Z), ch}, {M(m, il, PB_R_LIN_BETA), ch + w_lin}, {M(m, il, PB_R_LIN_ALPHA), ch + w_lin + c.lin_nv}});
+            PbStepOp op; memset(&op, 0, sizeof op);
+            PbDeltaParams& dp = op.d;
+            dp.proj = s->proj; dp.ldp = s->ldproj; dp.conv_w = V(m, il, PB_R_LIN_CONV); dp.a = V(m, il, PB_R_LIN_A); dp.dt = V(m, il, PB_R_LIN_DT);
+            dp.conv = s->conv[li]; dp.ssm = s->ssm[li]; dp.pos = s->pos; dp.out = s->olin; dp.ldo = w_lin;
+            dp.nk = c.lin_nk; dp.nv = c.lin_nv; dp.dk = c.lin_dk; dp.dv = c.lin_dv; dp.conv_k = c.conv_k; dp.batch = 1;
+            push(op, PS_DELTA);
+            gemv(w_lin, PB_ACT_GNORM, s->olin, V(m, il, PB_R_LIN_NORM), s->proj + ch, s->x, 1, {{M(m, il, PB_R_LIN_OUT), 0}});
+        }
+        {
+            PbStepOp op; memset(&op, 0, sizeof op);
+            PsRouterOp& r = op.r;
+            r.x = s->x; r.norm_w = V(m, il, PB_R_FFN_NORM); r.router = reinterpret_cast<const float*>(M(m, il, PB_R_ROUTER)->data); r.sh_gate_inp = V(m, il, PB_R_SH_GATE_INP);
+            r.logits = s->rlogits; r.n_exp = c.n_exp; r.cols = d; r.eps = c.eps;
+            r.rows_per_chunk = (int)(stage / ((size_t)d * 4)) < PB_CONSUMERS ? (int)(stage / ((size_t)d * 4)) : PB_CONSUMERS;
+            r.nchunks = (c.n_exp + r.rows_per_chunk - 1) / r.rows_per_chunk + 1;
+            push(op, PS_ROUTER);
+        }
+        {
+            PbStepOp op; memset(&op, 0, sizeof op);
+            PsMoeOp& e = op.m;
+            e.gate = M(m, il, PB_R_EXP_GATE)->rdata; e.up = M(m, il, PB_R_EXP_UP)->rdata; e.down = M(m, il, PB_R_EXP_DOWN)->rdata;
+            e.sh_gate = M(m, il, PB_R_SH_GATE)->rdata; e.sh_up = M(m, il, PB_R_SH_UP)->rdata; e.sh_down = M(m, il, PB_R_SH_DOWN)->rdata;
+            e.logits = s->rlogits; e.h = s->fh; e.y = s->x; e.n_exp = c.n_exp; e.top_k = c.top_k; e.ff = ff; e.d = d; e.e_base = 0;
+            e.row_bytes_gu = n4_row(d); e.row_bytes_dn = n4_row(ff); e.rg = rg;
+            const int spc = (int)(stage / ((size_t)16 * n4_row(ff)));
+            e.spc = spc < c.top_k + 1 ? spc : c.top_k + 1;
+            PbStepOp op2 = op;
+            push(op, PS_GU);
+            push(op2, PS_DOWN);
+        }
+    }
+    gemv(d, PB_ACT_NORM, s->x, V(m, -1, PB_R_OUT_NORM), nullptr, s->logits, 0, {{head, 0}});
+    s->fsegs.push_back({seg_begin, (int)ops.size(), -1, 0});
+    for (pb_state::FSeg& sg : s->fsegs) for (int i = sg.begin; i < sg.end; i++) sg.nbar += (ops[i].flags & PS_F_BARRIER) ? 1 : 0;
+    if (ctx->stamps) {   // tracing on: every CTA stamps every operation
+        const size_t per = (size_t)ctx->sm_count * 4 + 32;   // per-CTA stamps, then 32 fine-grained stamps of CTA 0
+        PB_TRY(dalloc(s, &s->ftrace, ops.size() * per));
+        for (size_t i = 0; i < ops.size(); i++) ops[i].trace = s->ftrace + i * per;
+        s->ftrace_ops = (int)ops.size();
+    }
+    PB_CUDA(ctx, cudaMemcpyAsync(s->fops, ops.data(), ops.size() * sizeof(PbStepOp), cudaMemcpyHostToDevice, ctx->stream));
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // `ops` is a local
+    s->flay = L;
+    s->fused = 1;
+    return PB_OK;
+}
+
+// one decode step of a batch-1 state through the fused kernel: embedding, then for every run of operations between
+// attention cores one launch of pb_step_kernel, the attention cores with their own kernels, argmax, position advance
+static int run_step_fused(pb_state* s) {
+    pb_model* m = s->m; pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg;
+    struct Scope { pb_ctx* c; Scope(pb_ctx* x) : c(x) { c->pdl_scope++; c->pdl_chain = false; } ~Scope() { c->pdl_scope--; c->pdl_chain = false; } } scope(ctx);
+    pb_qmat* embd = M(m, -1, PB_R_TOKEN_EMBD);
+    PB_TRY(pb_launch_embed(ctx, embd->type, embd->data, embd->rows, c.d, s->ids, 1, s->x, c.d));
+    for (const pb_state::FSeg& sg : s->fsegs) {
+        PsParams P; memset(&P, 0, sizeof P);
+        P.ops = s->fops; P.op_begin = sg.begin; P.op_end = sg.end; P.nbar = sg.nbar; P.sync = ctx->grid_sync; P.pos = s->pos; P.lay = s->flay; P.status = ctx->dev_status;
+        PB_TRY(pb_launch_step(ctx, P));
+        if (sg.attn_layer >= 0) {
+            PbAttnParams p; attn_params(s, sg.attn_layer, p);
+            PB_TRY(pb_launch_kv_append(ctx, p));
+            PB_TRY(pb_launch_attn(ctx, p));
+        }
+    }
+    PB_TRY(pb_launch_argmax(ctx, s->logits, c.vocab, c.vocab, 1, s->amax));
+    return pb_launch_advance(ctx, s->pos, 1, s->amax, s->next, s->ids, s->trace, s->trace_len, s->trace_cap);
+}
+
 // one decode step for every sequence of the batch, ids already in s->ids
 static int run_step(pb_state* s) {
     pb_model* m = s->m; pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg; const int B = s->batch;
+    if (s->fused < 0) PB_TRY(fused_build(s));
+    if (s->fused == 1) return run_step_fused(s);
     struct Scope { pb_ctx* c; Scope(pb_ctx* x) : c(x) { c->pdl_scope++; c->pdl_chain = false; } ~Scope() { c->pdl_scope--; c->pdl_chain = false; } } scope(ctx);
     pb_qmat* embd = M(m, -1, PB_R_TOKEN_EMBD);
     PB_TRY(pb_launch_embed(ctx, embd->type, embd->data, embd->rows, c.d, s->ids, B, s->x, c.d));
@@ -965,6 +1137,28 @@ int pb_attn_step(pb_state* s, int layer, const float* x_host, float* y_host) {
     PB_TRY(run_attn(s, layer, s->xin, nullptr, s->yout, c.d, 0));
     PB_CUDA(ctx, cudaMemcpyAsync(y_host, s->yout, (size_t)s->batch * c.d * 4, cudaMemcpyDeviceToHost, ctx->stream));
     return pb_sync_check(ctx, "pb_attn_step");
+}
+
+int pb_state_peek(pb_state* s, int what, float* out_host, int64_t n) {
+    if (!s) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    PB_TRY(pb_enter(ctx));
+    const float* src = nullptr;
+    switch (what) {
+        case 0: src = s->x; break;
+        case 1: src = s->proj; break;
+        case 2: src = s->olin; break;
+        case 3: src = s->att; break;
+        case 4: src = s->rlogits; break;
+        case 5: src = s->fused == 1 ? s->fh : s->h; break;
+        case 6: src = s->fused == 1 ? s->fh + (size_t)c.top_k * c.ff_exp : s->h_sh; break;
+        case 7: src = reinterpret_cast<const float*>(s->ftrace); break;   // per-CTA stamps of the fused step: [op][grid][4] uint64 (n counts floats)
+        default: break;
+    }
+    if (!src || !out_host || n <= 0) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_peek: bad argument");
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    PB_CUDA(ctx, cudaMemcpy(out_host, src, (size_t)n * 4, cudaMemcpyDeviceToHost));
+    return PB_OK;
 }
 
 // conv history oldest-first [batch][conv_k-1][ch] <-> ring slots (pos + 1 + k) mod conv_k

@@ -82,34 +82,27 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
         const int nheads = cols / p.head_dim;
         for (int i = warp; i < NB * nheads; i += PB_CONSUMERS) {
             const int b = i / nheads, h = i - b * nheads;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (b < p.t) v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + h * p.head_dim + 4 * lane);
-            const float ss = pb_warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
-            const float s = 1.0f / sqrtf(ss / (float)p.head_dim + p.eps);
-            const float4 w = *reinterpret_cast<const float4*>(p.norm_w + 4 * lane);
-            v.x *= s * w.x; v.y *= s * w.y; v.z *= s * w.z; v.w *= s * w.w;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f), sg = make_float4(1.f, 1.f, 1.f, 1.f);
             if (b < p.t) {
+                v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + h * p.head_dim + 4 * lane);
                 const float4 z = *reinterpret_cast<const float4*>(p.z + b * p.ldz + h * p.head_dim + 4 * lane);
-                v.x *= pb_sigm(z.x); v.y *= pb_sigm(z.y); v.z *= pb_sigm(z.z); v.w *= pb_sigm(z.w);
+                sg = make_float4(pb_sigm(z.x), pb_sigm(z.y), pb_sigm(z.z), pb_sigm(z.w));
             }
+            v = pb_gnorm_vec(v, *reinterpret_cast<const float4*>(p.norm_w + 4 * lane), sg, p.head_dim, p.eps);
             pb_split_groups4(v, lane, h * 4, cols, xq + (size_t)b * xw);
         }
     } else {
         for (int b = 0; b < NB; b++) {
             float s = 1.0f;
             if (p.mode == PB_ACT_NORM && b < p.t) {  // rms(): x * s * w  (qwen4exp_gguf.rs:209)
-                float ss = 0.f;
-                for (int c = tid; c < cols; c += CT) { const float v = p.x[b * p.ldx + c]; ss += v * v; }
+                float ss = pb_strided_ss(p.x + b * p.ldx, cols, tid, CT);
                 ss = pb_consumer_sum(ss, red, warp, lane);
                 s = 1.0f / sqrtf(ss / (float)cols + p.eps);
             }
             for (int g0 = warp * 4; g0 < ng; g0 += PB_CONSUMERS * 4) {
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (b < p.t) v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + 32 * g0 + 4 * lane);
-                if (p.mode == PB_ACT_NORM) {
-                    const float4 w = *reinterpret_cast<const float4*>(p.norm_w + 32 * g0 + 4 * lane);
-                    v.x = v.x * s * w.x; v.y = v.y * s * w.y; v.z = v.z * s * w.z; v.w = v.w * s * w.w;
-                }
+                if (p.mode == PB_ACT_NORM) v = pb_norm_vec(v, s, *reinterpret_cast<const float4*>(p.norm_w + 32 * g0 + 4 * lane));
                 pb_split_groups4(v, lane, g0, cols, xq + (size_t)b * xw);
             }
         }

@@ -37,6 +37,7 @@ struct pb_ctx {
     // tracing: stamp slots handed to the launches of the streaming kernels while enabled (pb_ctx_stamps_enable)
     unsigned long long* stamps = nullptr; int stamp_slots = 0, stamp_next = 0;
     std::vector<int> stamp_ids;   // kernel id (PB_K_*) per handed-out slot
+    unsigned long long* grid_sync = nullptr;   // fused step kernel: [0] arrival counter of its grid barriers, [1] counter value at launch
     unsigned long owner_thread = 0;   // pthread id of the creating thread (checked when PYRE_B200_CHECK_THREAD=1)
     bool check_thread = false;
 };

@@ -20,6 +20,7 @@
 #include "pb_stream.cuh"
 #include "pb_internal.h"
 #include "pb_topk.cuh"
+#include "pb_router.cuh"
 
 #include <stdio.h>
 
@@ -36,30 +37,9 @@ __device__ __forceinline__ void pb_route_body(const PbRouteParams& p, int* rsm) 
     __syncthreads();
     for (int b = warp; b < p.t; b += 8) {
         const float* lg = p.logits + (size_t)b * p.ldl;
-        // lane j keeps the j-th pick (descending logit, ties to the lower id, NaN as -inf: pb_topk.cuh)
-        unsigned long long pick;
-        if (p.n_exp <= 512) {
-            unsigned long long keys[16];
-#pragma unroll
-            for (int i = 0; i < 16; i++) { const int e = i * 32 + lane; keys[i] = e < p.n_exp ? pb_topk_key(__ldcg(lg + e), e) : 0ull; }
-            pick = pb_warp_topk<16>(keys, p.top_k, lane);
-        } else {
-            unsigned long long keys[32];
-#pragma unroll
-            for (int i = 0; i < 32; i++) { const int e = i * 32 + lane; keys[i] = e < p.n_exp ? pb_topk_key(__ldcg(lg + e), e) : 0ull; }
-            pick = pb_warp_topk<32>(keys, p.top_k, lane);
-        }
-        const int my_e = pb_topk_id(pick); const float my_v = pb_topk_val(pick);
-        // softmax over the selection, summed in descending-logit order (top_k :3136-3138, soft_top :3126-3131)
-        float mx = lane < p.top_k ? my_v : -INFINITY;
-        mx = pb_warp_max(mx);
-        float w = lane < p.top_k ? expf(my_v - mx) : 0.f;
-        float sum = 0.f;
-        for (int j = 0; j < p.top_k; j++) sum += __shfl_sync(0xffffffffu, w, j);
-        w = isfinite(mx) ? w / sum : 1.0f / (float)(p.top_k > 0 ? p.top_k : 1);
-        // accumulation order = ascending expert id (routed f32 branch :1786): rank of this lane's expert
-        int rank = 0;
-        for (int j = 0; j < p.top_k; j++) { const int oe = __shfl_sync(0xffffffffu, my_e, j); if (oe < my_e) rank++; }
+        // lane j keeps the j-th pick, its softmax weight and its rank by expert id (pb_topk.cuh)
+        int my_e, rank; float w;
+        pb_route_token(lg, p.n_exp, p.top_k, lane, my_e, w, rank);
         if (lane < p.top_k) {
             p.sel_e[b * p.top_k + rank] = my_e; p.sel_w[b * p.top_k + rank] = w;
             if (my_e >= p.e_lo && my_e < p.e_hi) atomicAdd(&cnt[my_e], 1);
@@ -115,13 +95,7 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
     const int b_lo = (int)blockIdx.y * PB_ROUTER_TPG, b_hi = min(p.t, b_lo + PB_ROUTER_TPG);
     // per-token RMS scale (rms(): 1 / sqrt(mean(x^2) + eps), qwen4exp_gguf.rs:209); one warp per token
     for (int b = b_lo + warp; b < b_hi; b += 8) {
-        float s = 1.0f;
-        if (p.norm_w) {
-            float ss = 0.f;
-            for (int c = lane * 4; c < p.cols; c += 128) { const float4 v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + c); ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
-            ss = pb_warp_sum(ss);
-            s = 1.0f / sqrtf(ss / (float)p.cols + p.eps);
-        }
+        const float s = p.norm_w ? pb_row_rms_scale(p.x + b * p.ldx, p.cols, p.eps, lane) : 1.0f;
         if (lane == 0) scale[b] = s;
     }
     __syncthreads();
@@ -143,43 +117,17 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
     if (p.phase != 2 && row <= p.n_exp) {
         const float* wrow = row < p.n_exp ? p.router + (size_t)row * p.cols : p.sh_gate_inp;
         if (p.cols == 2048 && wrow) {
-            // the row, times the norm weight, stays in registers for all tokens; the token's scale is
-            // applied to the sum (w . (x s n) = s ((w n) . x) up to rounding)
-            float4 wr[16];
-#pragma unroll
-            for (int k = 0; k < 16; k++) {
-                wr[k] = *reinterpret_cast<const float4*>(wrow + lane * 4 + 128 * k);
-                if (p.norm_w) { const float4 n = *reinterpret_cast<const float4*>(p.norm_w + lane * 4 + 128 * k); wr[k].x *= n.x; wr[k].y *= n.y; wr[k].z *= n.z; wr[k].w *= n.w; }
-            }
+            // the row, times the norm weight, stays in registers for all tokens
+            PbRouterRow2048 rr;
+            rr.load(wrow, p.norm_w, lane);
 #pragma unroll 2
             for (int b = b_lo; b < b_hi; b++) {
-                const float* xb = p.x + b * p.ldx + lane * 4;
-                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll
-                for (int k = 0; k < 16; k++) {
-                    const float4 v = *reinterpret_cast<const float4*>(xb + 128 * k);
-                    a0 = fmaf(wr[k].x, v.x, a0); a1 = fmaf(wr[k].y, v.y, a1); a2 = fmaf(wr[k].z, v.z, a2); a3 = fmaf(wr[k].w, v.w, a3);
-                }
-                const float acc = pb_warp_sum((a0 + a1) + (a2 + a3)) * scale[b];
+                const float acc = rr.dot(p.x + b * p.ldx, scale[b], lane);
                 if (lane == 0) p.logits[b * p.ldl + row] = acc;
             }
         } else
         for (int b = b_lo; b < b_hi; b++) {
-            float acc = 0.f;
-            const float s = scale[b];
-            if (wrow) {
-#pragma unroll 4
-                for (int c = lane * 4; c < p.cols; c += 128) {
-                    const float4 w = *reinterpret_cast<const float4*>(wrow + c);
-                    float4 v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + c);
-                    if (p.norm_w) {
-                        const float4 n = *reinterpret_cast<const float4*>(p.norm_w + c);
-                        v.x = v.x * s * n.x; v.y = v.y * s * n.y; v.z = v.z * s * n.z; v.w = v.w * s * n.w;
-                    }
-                    acc = fmaf(w.x, v.x, acc); acc = fmaf(w.y, v.y, acc); acc = fmaf(w.z, v.z, acc); acc = fmaf(w.w, v.w, acc);
-                }
-                acc = pb_warp_sum(acc);
-            }
+            const float acc = wrow ? pb_router_row_dot(wrow, p.norm_w, p.x + b * p.ldx, scale[b], p.cols, lane) : 0.f;
             if (lane == 0) p.logits[b * p.ldl + row] = acc;
         }
     }

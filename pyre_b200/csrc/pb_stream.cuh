@@ -68,35 +68,58 @@ __host__ __device__ static inline int pb_xq_words(int cols) { return PB_XLEVELS 
 // 4*(l&7) .. +3 of group g0 + (l>>3), so a reduction over a group is 3 shuffles and every lane
 // packs its own word.  v = the lane's four values.  Output: PB_XLEVELS int8 levels in the
 // quad-major layout at `col` (shared or global memory), their scales and the group sums.
+// All sixteen warps of a CTA run this at the same moment, so it is written for instruction throughput: rounding to
+// an integer is a float addition of 1.5 * 2^23 (round-to-nearest-even, as cvt.rni; conversions are quarter-rate),
+// and the integer sums of the three levels share one pair of shuffle reductions.  WITH_SUM = false skips the f32
+// group sums, which only formats with a minimum (Q4_K) read.
+template <bool WITH_SUM = true>
 __device__ __forceinline__ void pb_split_groups4(float4 v, int lane, int g0, int cols, uint32_t* col) {
     const int ng = cols / 32, nq = cols / 64;
     float* sc = reinterpret_cast<float*>(col + PB_XLEVELS * (cols / 4));
     const int g = g0 + (lane >> 3), k = lane & 7;   // word k of group g = word 8*(g&1)+k of quarter g/2
     const int off = pb_xq_off(g >> 1, 2 * (g & 1) + (k >> 2), nq) + (k & 3);
-    float sum = (v.x + v.y) + (v.z + v.w);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1); sum += __shfl_xor_sync(0xffffffffu, sum, 2); sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    float sum = 0.f;
+    if (WITH_SUM) {
+        sum = (v.x + v.y) + (v.z + v.w);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1); sum += __shfl_xor_sync(0xffffffffu, sum, 2); sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    }
     float r[4] = {v.x, v.y, v.z, v.w};
+    const float kMagic = 12582912.0f;   // 1.5 * 2^23: adding it leaves round-to-nearest-even(t) in the low mantissa bits
+    int asum[PB_XLEVELS];
+    float sl[PB_XLEVELS];
 #pragma unroll
     for (int l = 0; l < PB_XLEVELS; l++) {
         float m = fmaxf(fmaxf(fabsf(r[0]), fabsf(r[1])), fmaxf(fabsf(r[2]), fabsf(r[3])));
         m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1)); m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2)); m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
-        const float s = m > 0.f && isfinite(m) ? m / 127.f : 0.f;
-        const float inv = s > 0.f ? 1.0f / s : 0.f;
+        // scale = max / 127 and its reciprocal, by a multiplication and the fast reciprocal: any scale with |r| / s <= 127.5
+        // serves (what a level does not represent is carried into the next one); groups below 1e-30 count as zero
+        const float s = m > 1e-30f && isfinite(m) ? m * (1.0f / 127.f) : 0.f;
+        const float inv = s > 0.f ? __fdividef(1.0f, s) : 0.f;
         uint32_t pa = 0;
-        int asum = 0;
+        int as = 0;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            int a = __float2int_rn(r[j] * inv);
-            a = max(-127, min(127, a));
-            r[j] = s > 0.f ? fmaf(-s, (float)a, r[j]) : 0.f;
+            const float t = s > 0.f ? fminf(fmaxf(r[j] * inv, -127.f), 127.f) : 0.f;
+            const float tm = t + kMagic;
+            const int a = __float_as_int(tm) - 0x4B400000;
+            r[j] = s > 0.f ? fmaf(-s, tm - kMagic, r[j]) : 0.f;
             pa |= (uint32_t)(a & 0xFF) << (8 * j);
-            asum += a;
+            as += a;
         }
-        asum += __shfl_xor_sync(0xffffffffu, asum, 1); asum += __shfl_xor_sync(0xffffffffu, asum, 2); asum += __shfl_xor_sync(0xffffffffu, asum, 4);
         col[l * (cols / 4) + off] = pa;
-        if (k == 0) { sc[l * ng + g] = s; reinterpret_cast<int*>(sc)[(PB_XLEVELS + 1 + l) * ng + g] = -15 * asum; }   // stored ready for 2 A - 15 S
+        asum[l] = as; sl[l] = s;
     }
-    if (k == 0) sc[PB_XLEVELS * ng + g] = sum;
+    // sums of the levels over the group: levels 0 and 1 biased into the two halves of one word (|sum over 8 lanes| <= 4064)
+    static_assert(PB_XLEVELS == 3, "the packed reduction below is written for three levels");
+    int p01 = (asum[0] + 512) | ((asum[1] + 512) << 16), p2 = asum[2];
+    p01 += __shfl_xor_sync(0xffffffffu, p01, 1); p01 += __shfl_xor_sync(0xffffffffu, p01, 2); p01 += __shfl_xor_sync(0xffffffffu, p01, 4);
+    p2 += __shfl_xor_sync(0xffffffffu, p2, 1); p2 += __shfl_xor_sync(0xffffffffu, p2, 2); p2 += __shfl_xor_sync(0xffffffffu, p2, 4);
+    if (k == 0) {
+        const int tot[3] = {(p01 & 0xFFFF) - 4096, (p01 >> 16) - 4096, p2};
+#pragma unroll
+        for (int l = 0; l < PB_XLEVELS; l++) { sc[l * ng + g] = sl[l]; reinterpret_cast<int*>(sc)[(PB_XLEVELS + 1 + l) * ng + g] = -15 * tot[l]; }   // stored ready for 2 A - 15 S
+        if (WITH_SUM) sc[PB_XLEVELS * ng + g] = sum;
+    }
 }
 
 template <bool ISUM = false>
@@ -166,4 +189,23 @@ __device__ __forceinline__ float pb_consumer_sum(float v, float* red, int warp, 
 #pragma unroll
     for (int i = 0; i < PB_CONSUMERS; i++) t += red[i];
     return t;
+}
+
+// ---- pieces of the activation prologues shared by pb_gemvq_kernel and the fused step kernel (same bits from both) ----
+// sum of squares of x[tid], x[tid + n], x[tid + 2n], ... : the partition of the RMSNorm prologue
+__device__ __forceinline__ float pb_strided_ss(const float* x, int cols, int tid, int nthreads) {
+    float ss = 0.f;
+    for (int c = tid; c < cols; c += nthreads) { const float v = x[c]; ss = fmaf(v, v, ss); }   // spelled out: see pb_row_rms_scale
+    return ss;
+}
+// x * s * w per element (rms(): qwen4exp_gguf.rs:209)
+__device__ __forceinline__ float4 pb_norm_vec(float4 v, float s, float4 w) { v.x = v.x * s * w.x; v.y = v.y * s * w.y; v.z = v.z * s * w.z; v.w = v.w * s * w.w; return v; }
+// one head of 128 values held by a warp (lane l: elements 4l..4l+3): rms_inplace(o, norm, eps), then * sg (= sigmoid(z), or ones)
+// (linear_core, qwen4exp_gguf.rs:1667)
+__device__ __forceinline__ float4 pb_gnorm_vec(float4 v, float4 w, float4 sg, int head_dim, float eps) {
+    const float ss = pb_warp_sum(fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, __fmul_rn(v.w, v.w)))));   // spelled out: see pb_row_rms_scale
+    const float s = 1.0f / sqrtf(ss / (float)head_dim + eps);
+    v.x *= s * w.x; v.y *= s * w.y; v.z *= s * w.z; v.w *= s * w.w;
+    v.x *= sg.x; v.y *= sg.y; v.z *= sg.z; v.w *= sg.w;
+    return v;
 }

@@ -41,3 +41,39 @@ __device__ __forceinline__ unsigned long long pb_warp_topk(unsigned long long (&
     }
     return mine;
 }
+
+// Second half of the routing of one token (one warp): lane j < top_k holds the j-th pick (descending logit, ties to the
+// lower id, NaN as -inf) as a key; it ends up with the expert id, the softmax weight over the selection (summed in
+// descending-logit order: top_k :3136-3138, soft_top :3126-3131; all-NaN / all -inf gives uniform weights) and `rank` =
+// its position when the selection is sorted by ascending expert id, the order in which the expert outputs are
+// accumulated (routed, f32 branch :1786).
+__device__ __forceinline__ void pb_route_finish(unsigned long long pick, int top_k, int lane, int& my_e, float& w, int& rank) {
+    my_e = pb_topk_id(pick);
+    const float my_v = pb_topk_val(pick);
+    float mx = lane < top_k ? my_v : -INFINITY;
+    mx = pb_warp_max(mx);
+    w = lane < top_k ? expf(my_v - mx) : 0.f;
+    float sum = 0.f;
+    for (int j = 0; j < top_k; j++) sum += __shfl_sync(0xffffffffu, w, j);
+    w = isfinite(mx) ? w / sum : 1.0f / (float)(top_k > 0 ? top_k : 1);
+    rank = 0;
+    for (int j = 0; j < top_k; j++) { const int oe = __shfl_sync(0xffffffffu, my_e, j); if (oe < my_e) rank++; }
+}
+
+// Routing of one token by one warp.  lg: n_exp <= 1024 logits, read with L1-bypassing loads (they may have been written
+// by other SMs of this launch).
+__device__ __forceinline__ void pb_route_token(const float* lg, int n_exp, int top_k, int lane, int& my_e, float& w, int& rank) {
+    unsigned long long pick;
+    if (n_exp <= 512) {
+        unsigned long long keys[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) { const int e = i * 32 + lane; keys[i] = e < n_exp ? pb_topk_key(__ldcg(lg + e), e) : 0ull; }
+        pick = pb_warp_topk<16>(keys, top_k, lane);
+    } else {
+        unsigned long long keys[32];
+#pragma unroll
+        for (int i = 0; i < 32; i++) { const int e = i * 32 + lane; keys[i] = e < n_exp ? pb_topk_key(__ldcg(lg + e), e) : 0ull; }
+        pick = pb_warp_topk<32>(keys, top_k, lane);
+    }
+    pb_route_finish(pick, top_k, lane, my_e, w, rank);
+}

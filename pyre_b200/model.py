@@ -130,6 +130,13 @@ class State:
         ssm = None if ssm is None else _f32(ssm)
         self.ctx.check(lib().pb_state_set_lin(self.h, C.c_int(layer), _p(conv), _p(ssm)))
 
+    def peek(self, what: int, n: int) -> np.ndarray:
+        """First n floats of an activation buffer after the last step (pb_state_peek): 0 residual, 1 projections,
+        2 DeltaNet readout, 3 attention output, 4 router logits, 5 routed hidden vectors, 6 shared hidden vector."""
+        out = np.empty(n, dtype=np.float32)
+        self.ctx.check(lib().pb_state_peek(self.h, C.c_int(what), _p(out), C.c_int64(n)))
+        return out
+
     def stats(self) -> Stats:
         st = Stats()
         self.ctx.check(lib().pb_stats_get(self.h, C.byref(st)))

@@ -25,7 +25,8 @@ from collections import defaultdict
 
 import numpy as np
 
-KNAMES = {1: "gemv", 2: "router", 3: "expert gate/up", 4: "expert down", 5: "deltanet", 6: "attention", 7: "fused step"}
+KNAMES = {1: "gemv", 2: "router", 3: "expert gate/up", 4: "expert down", 5: "deltanet", 6: "attention",
+          101: "fused: gemv", 102: "fused: deltanet", 103: "fused: router", 104: "fused: expert gate/up", 105: "fused: expert down"}
 
 
 def launches_table(st: np.ndarray, ids: np.ndarray, label_of=None) -> str:
@@ -34,7 +35,7 @@ def launches_table(st: np.ndarray, ids: np.ndarray, label_of=None) -> str:
     prev_end = None
     for i in range(len(ids)):
         w = st[i].astype(np.int64)
-        if ids[i] == 7 or w[0] == 0:
+        if w[0] == 0:
             prev_end = None
             continue
         end_first = w[5] if w[5] else w[0]
@@ -79,9 +80,12 @@ def main():
     stamps, ids = ctx.stamps_read()
     per_step = int(st.stats().kernels_launched)
     text = [f"decode step, {a.layers} layers, context {a.ctx}, {per_step} launches per step, {len(ids)} traced launches (all times in microseconds, medians)"]
-    if len(ids) and ids[-1] == 7:
-        text.append("fused step kernel: see pb_step phases")
-    n = len(ids) // 2
+    fused = bool(len(ids)) and int(ids.max()) > 100
+    if fused:   # the operations of the fused step kernel keep the slots they were given when the list was built
+        text.append("operations of the fused step kernel (launch gap = end of the previous operation in CTA 0 -> start of this one; dep wait = grid barrier)")
+        n = 0
+    else:
+        n = len(ids) // 2
     text.append(launches_table(stamps[n:], ids[n:]))
     step = stamps[n:]
     nz = step[step > 0]

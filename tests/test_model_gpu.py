@@ -243,3 +243,52 @@ def test_contexts_on_two_devices_in_one_process():
         W.free()
     for c in ctxs:
         c.close()
+
+
+def _fused_cfg(**kw):
+    """A scaled-down hybrid model whose every matrix has a re-coded copy, so that a batch-1 state takes its steps
+    through the fused step kernel (expert width 512; hidden 512)."""
+    base = dict(n_layers=8, ff_exp=512, ff_sh=512, kv_bits=4, kv_recent=64, max_ctx=256)
+    base.update(kw)
+    return small_cfg(pb, **base)
+
+
+def test_fused_step_matches_per_operation_kernels_bit_for_bit(ctx, monkeypatch):
+    """The fused step kernel runs the arithmetic of the per-operation kernels: logits and tokens must be identical,
+    not merely close.  PYRE_B200_FUSED=0 (read at a state's first step) keeps a state on the per-operation path."""
+    cfg = _fused_cfg()
+    spec = synth.model_spec(cfg, 11)
+    m = synth.build_model(ctx, cfg, spec, 11)
+    fused = m.new_state(1)
+    monkeypatch.setenv("PYRE_B200_FUSED", "0")
+    plain = m.new_state(1)
+    lp = plain.forward([5])[0]                                   # first step decides the path of `plain`
+    monkeypatch.delenv("PYRE_B200_FUSED")
+    lf = fused.forward([5])[0]
+    assert fused.stats().kernels_launched < plain.stats().kernels_launched   # the fused path really ran
+    assert np.array_equal(lf.view(np.uint32), lp.view(np.uint32))
+    tok = int(lf.argmax())
+    for _ in range(6):                                           # eager step, captured graph, replays
+        lf, lp = fused.forward([tok])[0], plain.forward([tok])[0]
+        assert np.array_equal(lf.view(np.uint32), lp.view(np.uint32))
+        tok = int(lf.argmax())
+    assert fused.decode_greedy([tok], 150)[0].tolist() == plain.decode_greedy([tok], 150)[0].tolist()   # crosses a KV repack boundary
+    assert ctx.device_status() == 0
+    fused.destroy(); plain.destroy(); m.destroy()
+
+
+def test_fused_step_greedy_identity_vs_oracle(ctx):
+    cfg = _fused_cfg()
+    spec = synth.model_spec(cfg, 12)
+    m = synth.build_model(ctx, cfg, spec, 12)
+    om, _ = oracle_model(cfg, spec, 12)
+    st, ost = m.new_state(1), om.new_state()
+    tok = otok = 17
+    for i in range(64):
+        lg = st.forward([tok])[0]
+        lo = ost.forward([otok])
+        assert rel_err(lg, lo) < 1e-3, i
+        tok, otok = int(lg.argmax()), oracle.argmax(lo)
+        assert tok == otok, (i, ost.margins())
+    assert ctx.device_status() == 0
+    st.destroy(); m.destroy()
