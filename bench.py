@@ -214,7 +214,7 @@ def workload_config(batch, gpus, replicas=False, replicated_ep=False):
     return {"workload": "config 4: Qwen-Next-style 48-layer hybrid decoder, IQ3_S, hidden 2048, 512 experts top-10, vocab 151936, 4-bit KV pre-filled with 32768 positions, greedy decode",
             "batch": batch, "context": CTX_PREFILL, "residual": "pre-norm (hc=0)", "parallelism": "single GPU" if gpus == 1 else (f"{gpus} independent replicas" if replicas else (
                 f"expert-parallel x{gpus}, replicated tokens (512/{gpus} experts per GPU, every GPU steps all sequences, one NCCL all-reduce per MoE block)" if replicated_ep else
-                f"expert-parallel x{gpus}, sharded tokens ({batch} sequence(s) per GPU, 512/{gpus} experts per GPU, dense weights replicated; per MoE block one NCCL all-gather of the residual rows and one reduce-scatter of the expert outputs)")),
+                f"expert-parallel x{gpus}, sharded tokens ({batch} sequence(s) per GPU, 512/{gpus} experts per GPU, dense weights replicated; per MoE block the residual rows and the expert outputs cross NVLink by stores into peer memory from the library's own kernels, ordered by sequence-numbered flags; no NCCL on the data path)")),
             "l2": "weights touched per step (>1.7 GB) exceed the 126 MB L2; the lm-head roofline launch streams 165 MB"}
 
 
@@ -313,7 +313,7 @@ def run_ours(args):
         alg = W.nbytes() + 4 * (cfg.d + cfg.vocab)
         ach = alg / us / 1e3
         roof = {"bound": "hbm", "kernel": "pb_gemvq_kernel<IQ3_S re-coded to 4-bit codes> lm-head 151936x2048", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 4),
-                "peak_source": which, "traffic": LMHEAD_DRAM_TRAFFIC, "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this launch (profiles/gemvq_iq3s_recoded_lmhead.md); the re-coded copy is 136 bytes per 256 weights, the GGUF block 110", "us_per_launch": round(us, 2), "algorithmic_bytes": alg}
+                "peak_source": which, "traffic": LMHEAD_DRAM_TRAFFIC, "traffic_source": "constant: dram__bytes_read.sum + dram__bytes_write.sum of one profiler capture of this same launch (same shape, same kernel), not re-measured by this run; the re-coded copy is 136 bytes per 256 weights, the GGUF block 110", "us_per_launch": round(us, 2), "algorithmic_bytes": alg}
         W.free()
 
     if rank == 0:
@@ -375,9 +375,62 @@ def run_ours(args):
             ms2 = float(t2[0])
         if rank == 0:
             line["batch32"] = {"value": round(32 * steps2 / (ms2 / 1e3), 2), "unit": "tok/s", "ms_per_step": round(ms2 / steps2, 4), "steps": steps2, "batch": 32, "per_gpu": B2, "context": CTX_PREFILL}
+    st.destroy()
+    if world > 1 and sharded and not args.no_variants:
+        import torch.distributed as dist
+
+        def timed_decode(model_, sharded_, steps_):
+            s_ = model_.new_state(B, sharded=sharded_)
+            for ai in range(n_attn):
+                s_.fill_kv_synth(ai, CTX_PREFILL, SEED + 1)
+            s_.set_pos(CTX_PREFILL)
+            s_.decode_greedy(first, 3)
+            barrier()
+            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.stream(stream):
+                c0.record(stream)
+                s_.decode_greedy(tok, steps_)
+                c1.record(stream)
+            barrier()
+            t_ = torch.tensor([c0.elapsed_time(c1)], device="cuda")
+            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+            xns = s_.stats().exchange_ns
+            s_.destroy()
+            return float(t_[0]), xns
+
+        vsteps = max(8, args.steps // 2)
+        # the same sharded step with the two NCCL collectives per MoE block instead of the in-kernel peer exchange
+        os.environ["PYRE_B200_EP_EXCHANGE"] = "nccl"
+        ms_nccl, _ = timed_decode(model, True, vsteps)
+        del os.environ["PYRE_B200_EP_EXCHANGE"]
+        ms_p2p, xns = timed_decode(model, True, vsteps)
+        model.destroy(); model = None
+        # independent replicas: every GPU holds all experts and decodes its own sequences, nothing is exchanged
+        full = synth.build_model(ctx, cfg, spec, SEED, 0, 1)
+        ms_rep, _ = timed_decode(full, False, vsteps)
+        full.destroy()
+        # greedy ids of sharded decoding against one GPU stepping the whole batch (8 layers of the same shapes, 32 tokens)
+        cfg_s = full_cfg(pb, batch_room=64, n_layers=8)
+        spec_s = synth.model_spec(cfg_s, SEED + 2)
+        m_s = synth.build_model(ctx, cfg_s, spec_s, SEED + 2, rank, world)
+        s_s = m_s.new_state(1, sharded=True)
+        mine = torch.from_numpy(s_s.decode_greedy(np.array([1 + rank], np.uint32), 32).astype(np.int64)).cuda()
+        s_s.destroy(); m_s.destroy()
+        got = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(got, mine)
+        if rank == 0:
+            m_1 = synth.build_model(ctx, cfg_s, spec_s, SEED + 2, 0, 1)
+            s_1 = m_1.new_state(world)
+            want = s_1.decode_greedy(np.arange(world, dtype=np.uint32) + 1, 32).astype(np.int64)
+            s_1.destroy(); m_1.destroy()
+            line["ep_tokens_identical"] = bool(np.array_equal(torch.cat(got).cpu().numpy(), want))
+            per = lambda ms_: {"tok_per_s": round(B * world * vsteps / (ms_ / 1e3), 2), "ms_per_step": round(ms_ / vsteps, 4)}
+            line["exchange"] = {"steps": vsteps, "p2p": {**per(ms_p2p), "handshake_ms_per_step": round(xns / 1e6 / (vsteps + 3), 4)}, "nccl": per(ms_nccl), "replicas": per(ms_rep),
+                                "note": "p2p = stores into peer memory + flags inside the library's kernels (the default, also the headline value); nccl = all-gather + reduce-scatter per MoE block; replicas = every GPU holds all experts, nothing exchanged"}
     if rank == 0:
         print(json.dumps(line), flush=True)
-    st.destroy(); model.destroy()
+    if model is not None:
+        model.destroy()
     if world > 1:
         import torch.distributed as dist
         dist.barrier(); dist.destroy_process_group()
@@ -394,6 +447,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-bs32", action="store_true", help="skip the batch-32 leg of the default run")
     ap.add_argument("--replicated-ep", action="store_true", help="N>1: expert parallelism with every GPU stepping all sequences (all-reduce) instead of sharded tokens")
+    ap.add_argument("--no-variants", action="store_true", help="N>1: skip the NCCL / replicas comparison and the token-identity check")
     ap.add_argument("--replicas", action="store_true", help="N>1: independent replicas instead of expert parallelism")
     args = ap.parse_args()
     if args.impl == "reference":

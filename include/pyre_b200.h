@@ -85,6 +85,10 @@ int pb_ctx_stamps_read(pb_ctx* ctx, uint64_t* stamps_host, int32_t* kernel_ids_h
 int pb_ep_unique_id(pb_ctx* ctx, void* id128);
 int pb_ep_init(pb_ctx* ctx, const void* id128, int rank, int world);
 int pb_ep_destroy(pb_ctx* ctx);
+/* Failure detection of the peer exchange, testable on one GPU: runs one bounded hand-shake (`spins` polls of about 0.2 us)
+ * whose partner never answers.  Returns PB_ERR_DEVICE (the wait gave up and said so in the device status word); the context
+ * stays usable.  The reference bounds its CPU/GPU hand-shakes the same way (pyre_wait_flag, src/model/qwen4exp_gguf.rs:229-238). */
+int pb_ep_probe_wait_timeout(pb_ctx* ctx, unsigned int spins);
 
 /* (elements per block, bytes per block) -- QType::geom, src/model/gguf_q.rs:33-41 */
 int pb_type_geom(int ggml_type, int* elems, int* bytes);

@@ -144,6 +144,11 @@ class Ctx:
         k = min(n.value, max_slots)
         return st[:k], ids[:k]
 
+    def ep_probe_wait_timeout(self, spins: int = 2000):
+        """Run one peer hand-shake whose partner never answers (pb_ep_probe_wait_timeout): raises PB_ERR_DEVICE once the
+        bounded wait ran out; the context stays usable."""
+        self.check(lib().pb_ep_probe_wait_timeout(self.h, C.c_uint(spins)))
+
     # ---- expert-parallel group (NCCL) ----
     def ep_unique_id(self) -> bytes:
         buf = C.create_string_buffer(128)

@@ -60,6 +60,8 @@ struct pb_state {
     cudaGraphExec_t win_graph[4 * (PB_MAX_WINDOW + 1)] = {}; unsigned char win_runs[4 * (PB_MAX_WINDOW + 1)] = {};   // per (t, ckpt, all_logits)
     float *xg = nullptr, *xs = nullptr, *part_rs = nullptr;   // gathered / local rows [token][d + logits], reduced partial rows
     int64_t ldg = 0;                                          // row stride of xg / xs
+    // peer exchange (pb_ep.cu): xg and part_rs live in a block mapped into every rank; the kernels store into the peers' blocks
+    bool p2p = false; PbEpSymm symm; PbEpExch exch{}; float** part_tok = nullptr; unsigned long long* ep_seq = nullptr;
     int64_t ldproj = 0, ring_cap = 0;
     std::vector<float*> conv, ssm;
     std::vector<PbKv> kv;
@@ -310,7 +312,36 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
     A(hq, (size_t)Bm * (c.top_k + 1) * pb_xq_words(c.ff_exp > c.ff_sh ? c.ff_exp : c.ff_sh));
     A(part, (size_t)Bm * c.top_k * c.d); A(part_sh, (size_t)Bm * c.d);
     s->ldg = c.d + ((c.n_exp + 1 + 3) & ~3);
-    if (s->sharded) { A(xg, (size_t)Bm * s->ldg); A(xs, (size_t)B * s->ldg); A(part_rs, (size_t)B * c.top_k * c.d); }
+    if (s->sharded) {
+        A(xs, (size_t)B * s->ldg); A(ep_seq, 4);
+        // PYRE_B200_EP_EXCHANGE=nccl keeps the two NCCL collectives per MoE block; the default is the in-kernel peer exchange
+        const char* ex = getenv("PYRE_B200_EP_EXCHANGE");
+        const bool want_p2p = !(ex && strcmp(ex, "nccl") == 0) && m->ep_world <= PB_EP_MAX_WORLD;
+        if (want_p2p && rc == PB_OK) {
+            const size_t xg_bytes = ((size_t)Bm * s->ldg * 4 + 255) & ~(size_t)255, part_bytes = ((size_t)B * c.top_k * c.d * 4 + 255) & ~(size_t)255;
+            const size_t flag_bytes = ((size_t)2 * m->ep_world * 8 + 255) & ~(size_t)255;
+            rc = pb_ep_symm_alloc(ctx, xg_bytes + part_bytes + flag_bytes, &s->symm);
+            if (rc == PB_OK) {
+                s->p2p = true;
+                s->xg = reinterpret_cast<float*>(s->symm.local);
+                s->part_rs = reinterpret_cast<float*>(reinterpret_cast<char*>(s->symm.local) + xg_bytes);
+                PbEpExch& x = s->exch;
+                x.rank = m->ep_rank; x.world = m->ep_world; x.seq_base = s->ep_seq; x.wait_ns = s->ep_seq + 1; x.status = ctx->dev_status;
+                const char* lim = getenv("PYRE_B200_EP_SPIN");
+                x.spin_limit = lim ? (unsigned)atoi(lim) : (5u << 20);   // about a second of polling
+                std::vector<float*> pt((size_t)Bm);
+                for (int p = 0; p < m->ep_world; p++) {
+                    char* base = reinterpret_cast<char*>(s->symm.peer[p]);
+                    x.peer_xg[p] = reinterpret_cast<float*>(base);
+                    x.peer_flags[p] = reinterpret_cast<unsigned long long*>(base + xg_bytes + part_bytes);
+                    for (int j = 0; j < B; j++) pt[(size_t)p * B + j] = reinterpret_cast<float*>(base + xg_bytes) + (size_t)j * c.top_k * c.d;
+                }
+                A(part_tok, (size_t)Bm);
+                if (rc == PB_OK && cudaMemcpyAsync(s->part_tok, pt.data(), pt.size() * sizeof(float*), cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) rc = PB_ERR_CUDA;
+                if (rc == PB_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = PB_ERR_CUDA;   // `pt` is a local
+            }
+        } else { A(xg, (size_t)Bm * s->ldg); A(part_rs, (size_t)B * c.top_k * c.d); }
+    }
     A(logits, (size_t)Ba * c.vocab);
     if (B == 1 && !s->sharded) { A(fops, (size_t)c.n_layers * 8 + 8); A(fh, (size_t)(c.top_k + 1) * c.ff_exp); }
     s->trace_cap = 4096;
@@ -376,6 +407,7 @@ int pb_state_destroy(pb_state* s) {
     if (s->ev1) cudaEventDestroy(s->ev1);
     for (cudaGraphExec_t g : s->win_graph) if (g) cudaGraphExecDestroy(g);
     for (void* p : s->allocs) cudaFree(p);
+    pb_ep_symm_free(s->m->ctx, &s->symm);
     if (s->pin_u32) cudaFreeHost(s->pin_u32);
     delete s;
     return PB_OK;
@@ -518,8 +550,8 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
         // moves both; then every rank splits and routes all tokens
         r.phase = 1; r.x = x_in; r.ldx = c.d; r.t = t; r.logits = s->xs + c.d; r.ldl = s->ldg; r.xcopy = s->xs;
         PB_TRY(pb_launch_router(ctx, r, q, s->ticket));
-        PB_TRY(pb_ep_allgather(ctx, s->xs, s->xg, (size_t)t * s->ldg));
-        ctx->pdl_chain = false;
+        if (s->p2p) PB_TRY(pb_launch_ep_push_rows(ctx, s->exch, s->xs, (int64_t)t * s->ldg, (int64_t)tok0 * s->ldg, 2 * il));
+        else { PB_TRY(pb_ep_allgather(ctx, s->xs, s->xg, (size_t)t * s->ldg)); ctx->pdl_chain = false; }
         r.phase = 2; r.x = s->xg; r.ldx = s->ldg; r.t = tt; r.logits = s->xg + c.d; r.xcopy = nullptr;
         logits = s->xg + c.d; ldl = s->ldg;
     } else {
@@ -527,7 +559,7 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
         logits = s->rlogits; ldl = c.n_exp + 1;
     }
     q.logits = logits; q.ldl = ldl;
-    if (m->ep_world > 1) { r.zero = s->part; r.zero_n = (int64_t)tt * c.top_k * c.d; }   // rows of other ranks' experts stay zero
+    if (m->ep_world > 1 && !(sh && s->p2p)) { r.zero = s->part; r.zero_n = (int64_t)tt * c.top_k * c.d; }   // rows of other ranks' experts stay zero (summed exchanges)
     PB_TRY(pb_launch_router(ctx, r, q, s->ticket));
     PbExpertParams e; memset(&e, 0, sizeof e);
     e.n_used = s->n_used; e.used_e = s->used_e; e.used_off = s->used_off; e.ent_tok = s->ent_tok; e.ent_slot = s->ent_slot; e.ent_w = s->ent_w;
@@ -553,13 +585,16 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
     e.hq = tt > 1 && c.ff_exp == c.ff_sh ? s->hq : nullptr;   // several tokens: levels of the hidden vectors made once
     PbCombineParams k; memset(&k, 0, sizeof k);
     k.part = s->part; k.part_sh = s->part_sh + (size_t)tok0 * c.d; k.logits = logits + (size_t)tok0 * ldl; k.ldl = ldl; k.t = t; k.d = c.d; k.top_k = c.top_k; k.n_exp = c.n_exp;
+    if (sh) { k.logits = s->xs + c.d; k.ldl = s->ldg; }   // this rank's own copy of its tokens' logits: the gathered buffer may already be receiving the next block's rows
+    if (sh && s->p2p) e.part_tok = s->part_tok;            // finished rows go straight into the memory of the token's owner
     k.y = y; k.ldy = ldy; k.accumulate = accumulate;
     // few tokens on one GPU: the down kernel's last CTA also combines (one launch less per layer)
     if (m->ep_world == 1 && (int64_t)t * c.d <= 8192) return pb_launch_expert_down(ctx, e, dn_type, c.ff_exp, &k, s->ticket + 1);
     PB_TRY(pb_launch_expert_down(ctx, e, dn_type, c.ff_exp));
     // expert parallelism: every (token, slot) row was produced on exactly one rank and is zero elsewhere,
     // so the sum is an exact gather and the combine below sees the same bits for every GPU count
-    if (sh) { PB_TRY(pb_ep_reduce_scatter(ctx, s->part, s->part_rs, (size_t)t * c.top_k * c.d)); k.part = s->part_rs; ctx->pdl_chain = false; }
+    if (sh && s->p2p) { PB_TRY(pb_launch_ep_signal_wait(ctx, s->exch, 1, 2 * il + 1)); k.part = s->part_rs; }
+    else if (sh) { PB_TRY(pb_ep_reduce_scatter(ctx, s->part, s->part_rs, (size_t)t * c.top_k * c.d)); k.part = s->part_rs; ctx->pdl_chain = false; }
     else if (m->ep_world > 1) { PB_TRY(pb_ep_allreduce(ctx, s->part, (size_t)t * c.top_k * c.d)); ctx->pdl_chain = false; }
     return pb_launch_moe_combine(ctx, k);
 }
@@ -744,7 +779,7 @@ static int run_step(pb_state* s) {
     a.x = s->x; a.ldx = c.d; a.y = s->logits; a.ldy = c.vocab; a.mode = PB_ACT_NORM; a.norm_w = V(m, -1, PB_R_OUT_NORM); a.eps = c.eps;
     PB_TRY(gemv_cols(ctx, a, B));
     PB_TRY(pb_launch_argmax(ctx, s->logits, c.vocab, c.vocab, B, s->amax));
-    return pb_launch_advance(ctx, s->pos, B, s->amax, s->next, s->ids, s->trace, s->trace_len, s->trace_cap);
+    return pb_launch_advance(ctx, s->pos, B, s->amax, s->next, s->ids, s->trace, s->trace_len, s->trace_cap, s->p2p ? s->ep_seq : nullptr, 2ull * c.n_layers);
 }
 
 // A window of t consecutive tokens of the one sequence of a batch-1 state (ids already in s->ids[0..t)):
@@ -1088,6 +1123,10 @@ int pb_stats_get(const pb_state* s, pb_stats* out) {
     out->kv_bytes_per_step = (uint64_t)s->m->n_attn * s->batch * 2 * c.n_kv * (packed * (c.hd / 2 + c.hd / 8) + (len - packed) * c.hd * 4);
     out->state_bytes_per_step = (uint64_t)s->m->n_lin * s->batch * 2 * ((uint64_t)c.lin_nv * c.lin_dk * c.lin_dv * 4);
     out->device_ns = s->device_ns; out->exchange_ns = 0;
+    if (s->p2p) {   // time inside the peer hand-shakes (store fence + flag + wait for the peer), averaged over the peers; synchronises the stream
+        unsigned long long ns = 0;
+        if (cudaStreamSynchronize(s->m->ctx->stream) == cudaSuccess && cudaMemcpy(&ns, s->ep_seq + 1, 8, cudaMemcpyDeviceToHost) == cudaSuccess) out->exchange_ns = ns / (uint64_t)s->m->ep_world;
+    }
     return PB_OK;
 }
 

@@ -44,6 +44,30 @@ struct pb_ctx {
 // Every extern "C" entry point that touches the device calls this first: makes the context's GPU current
 // (a process may hold contexts on several GPUs) and, in the debug mode, verifies the calling thread.
 int pb_enter(pb_ctx* ctx);
+// In-kernel peer exchange of a sharded state (pb_ep.cu): every rank owns one block of device memory with the same layout,
+// mapped into all ranks of the node (CUDA IPC); kernels store straight into the peers' blocks and hand over with
+// sequence-numbered flags (bounded waits, a time-out sets the device status word).
+#define PB_EP_MAX_WORLD 16
+struct PbEpExch {
+    int rank, world;
+    float* peer_xg[PB_EP_MAX_WORLD];                  // each rank's gathered-row buffer [moe_t][ldg]
+    unsigned long long* peer_flags[PB_EP_MAX_WORLD];  // each rank's flag array [2 kinds][world]: flags[kind][src] = last sequence number src finished
+    const unsigned long long* seq_base;               // this rank's sequence base: advanced by 2 * n_layers per step
+    unsigned int spin_limit;                          // polls (of about 0.2 us) before a wait gives up
+    unsigned long long* wait_ns;                      // time spent in hand-shakes, summed over the world's CTAs (or null)
+    int* status;
+};
+struct PbEpSymm {
+    void* local = nullptr; size_t bytes = 0;
+    void* peer[PB_EP_MAX_WORLD] = {};                 // peer[rank] == local
+};
+int pb_ep_symm_alloc(pb_ctx* ctx, size_t bytes, PbEpSymm* out);   // collective over the expert-parallel group
+void pb_ep_symm_free(pb_ctx* ctx, PbEpSymm* m);
+// rows[0 .. n) (floats) of this rank -> every rank's gathered-row buffer at float offset dst_off; then exchange `exch` of kind 0 is
+// announced to every rank and awaited from every rank
+int pb_launch_ep_push_rows(pb_ctx* ctx, const PbEpExch& x, const float* rows, int64_t n, int64_t dst_off, int exch);
+// announce exchange `exch` of `kind` to every rank (this rank's stores into their memory are complete) and await theirs
+int pb_launch_ep_signal_wait(pb_ctx* ctx, const PbEpExch& x, int kind, int exch);
 int pb_ep_allreduce(pb_ctx* ctx, float* buf, size_t n);
 int pb_ep_allgather(pb_ctx* ctx, const float* send, float* recv, size_t n);
 int pb_ep_reduce_scatter(pb_ctx* ctx, const float* send, float* recv, size_t n);
@@ -212,6 +236,7 @@ struct PbExpertParams {
     float* h; float* h_sh;                    // hidden [entry][ff], [t][ff_sh]
     uint32_t* hq;                             // down, several tokens: int8-split hidden vectors [t * top_k + t][pb_xq_words(ff)], else null
     float* part; float* part_sh;              // down: [t][top_k][d], [t][d]
+    float* const* part_tok;                   // down, peer exchange: part_tok[token] = [top_k][d] block in the memory of the token's owner (else null)
     int rows_e, rows_sh, has_shared, t, top_k, n_exp, e_base;
     int sh_tok0, sh_ntok;                     // tokens [sh_tok0, sh_tok0 + sh_ntok) get the shared expert here
     int bpr, row_bytes, rows_per_chunk; uint32_t stage_bytes, tab_bytes; int rep;
@@ -267,4 +292,5 @@ int pb_launch_kv4_unpack(pb_ctx* ctx, const uint32_t* w, const float* sc, int64_
 int pb_launch_embed(pb_ctx* ctx, int type, const uint8_t* w, int64_t rows, int cols, const uint32_t* ids, int t, float* out, int64_t ldo);
 int pb_launch_argmax(pb_ctx* ctx, const float* logits, int64_t ld, int n, int t, unsigned long long* keys);
 int pb_launch_window_pos(pb_ctx* ctx, int64_t* pos, int64_t* wpos, int t, int advance);
-int pb_launch_advance(pb_ctx* ctx, int64_t* pos, int t, unsigned long long* keys, uint32_t* next, uint32_t* ids, uint32_t* trace, int64_t* trace_len, int64_t trace_cap);
+int pb_launch_advance(pb_ctx* ctx, int64_t* pos, int t, unsigned long long* keys, uint32_t* next, uint32_t* ids, uint32_t* trace, int64_t* trace_len, int64_t trace_cap,
+                      unsigned long long* ep_seq = nullptr, unsigned long long ep_seq_step = 0);

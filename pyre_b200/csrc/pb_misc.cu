@@ -75,7 +75,8 @@ int pb_launch_argmax(pb_ctx* ctx, const float* logits, int64_t ld, int n, int t,
 
 // end of a decode step: decode the argmax keys into token ids (and clear them for the next step),
 // pos += 1, feed the chosen tokens back as the next inputs and log them
-__global__ void pb_advance_kernel(int64_t* pos, int t, unsigned long long* keys, uint32_t* next, uint32_t* ids, uint32_t* trace, int64_t* trace_len, int64_t trace_cap) {
+__global__ void pb_advance_kernel(int64_t* pos, int t, unsigned long long* keys, uint32_t* next, uint32_t* ids, uint32_t* trace, int64_t* trace_len, int64_t trace_cap,
+                                  unsigned long long* ep_seq, unsigned long long ep_seq_step) {
     const int b = threadIdx.x;
     pb_pdl_wait();
     pb_pdl_trigger();
@@ -91,10 +92,12 @@ __global__ void pb_advance_kernel(int64_t* pos, int t, unsigned long long* keys,
     }
     __syncthreads();
     if (b == 0) *trace_len += 1;
+    if (b == 0 && ep_seq) *ep_seq += ep_seq_step;   // the next step's peer exchanges carry new sequence numbers
 }
 
-int pb_launch_advance(pb_ctx* ctx, int64_t* pos, int t, unsigned long long* keys, uint32_t* next, uint32_t* ids, uint32_t* trace, int64_t* trace_len, int64_t trace_cap) {
-    pb_launch_k(ctx, pb_advance_kernel, dim3(1), dim3((t + 31) & ~31), (size_t)(0), pos, t, keys, next, ids, trace, trace_len, trace_cap);
+int pb_launch_advance(pb_ctx* ctx, int64_t* pos, int t, unsigned long long* keys, uint32_t* next, uint32_t* ids, uint32_t* trace, int64_t* trace_len, int64_t trace_cap,
+                      unsigned long long* ep_seq, unsigned long long ep_seq_step) {
+    pb_launch_k(ctx, pb_advance_kernel, dim3(1), dim3((t + 31) & ~31), (size_t)(0), pos, t, keys, next, ids, trace, trace_len, trace_cap, ep_seq, ep_seq_step);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;

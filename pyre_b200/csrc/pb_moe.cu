@@ -464,6 +464,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
                     for (int o = lpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
                     if (ql == 0) {
                         if (shared) p.part_sh[(size_t)tok * p.rows_e + r0 + r] = acc;
+                        else if (p.part_tok) p.part_tok[tok][(size_t)slot * p.rows_e + r0 + r] = wgt * acc;   // straight into the owner's memory
                         else p.part[((size_t)tok * p.top_k + slot) * p.rows_e + r0 + r] = wgt * acc;
                     }
                 }
@@ -478,7 +479,7 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_kernel(const Pb
             pb_named_barrier(1, CT);
             float* dst; float wgt = 1.0f;
             if (shared) dst = p.part_sh + (size_t)tok * p.rows_e;
-            else { dst = p.part + ((size_t)tok * p.top_k + p.ent_slot[en]) * p.rows_e; wgt = p.ent_w[en]; }
+            else { dst = p.part_tok ? p.part_tok[tok] + (size_t)p.ent_slot[en] * p.rows_e : p.part + ((size_t)tok * p.top_k + p.ent_slot[en]) * p.rows_e; wgt = p.ent_w[en]; }
             for (int rb = warp * rpw; rb < p.rows_per_chunk; rb += PB_CONSUMERS * rpw) {
                 const int r = rb + sub;
                 float acc = 0.f;

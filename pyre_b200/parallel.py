@@ -35,3 +35,40 @@ def init_expert_parallel(ctx, dist, rank: int, world: int, device=None):
     """Create the library's NCCL communicator on `ctx` for this rank."""
     uid = share_unique_id(dist, ctx.ep_unique_id, rank, device)
     ctx.ep_init(uid, rank, world)
+
+
+class FlagExchange:
+    """Host model of the flag protocol the peer-exchange kernels run on the device (csrc/pb_ep.cu).
+
+    `flags` is one shared array [world][kinds][world] of unsigned 64-bit counters (on the device: one [kinds][world]
+    array in every rank's memory, mapped into every rank).  flags[dst][kind][src] holds the sequence number of the
+    last exchange of `kind` that `src` completed towards `dst`.  Sequence numbers only grow, so a waiter compares with
+    `>=` and a fast peer that is already one exchange ahead never makes a slow one miss a value.  A wait is bounded:
+    after `spin_limit` polls it gives up and reports a timeout instead of blocking (the device kernel then records a
+    status that makes the host call return PB_ERR_DEVICE).
+    """
+
+    def __init__(self, flags, rank: int, world: int, spin_limit: int = 100000, pause=None):
+        self.flags, self.rank, self.world, self.spin_limit, self.pause = flags, rank, world, spin_limit, pause
+
+    def post(self, kind: int, seq: int):
+        for p in range(self.world):
+            self.flags[p, kind, self.rank] = seq
+
+    def wait(self, kind: int, seq: int) -> bool:
+        """True once every peer announced exchange `seq` of `kind`; False when the bounded wait ran out."""
+        for p in range(self.world):
+            ok = False
+            for _ in range(self.spin_limit):
+                if int(self.flags[self.rank, kind, p]) >= seq:
+                    ok = True
+                    break
+                if self.pause:
+                    self.pause()
+            if not ok:
+                return False
+        return True
+
+    def exchange(self, kind: int, seq: int) -> bool:
+        self.post(kind, seq)
+        return self.wait(kind, seq)

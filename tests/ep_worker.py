@@ -112,10 +112,20 @@ def gpu_sharded_tokens(rank, world, port, out_dir):
     spec = synth.model_spec(cfg, 3)
     m = synth.build_model(ctx, cfg, spec, 3, rank, world)
     first = np.array([5, 600, 77, 1000, 9, 321, 42, 800], np.uint32)[:2 * world]
-    st = m.new_state(2, sharded=True)
+    st = m.new_state(2, sharded=True)             # default: in-kernel peer exchange
     toks = st.decode_greedy(first[2 * rank:2 * rank + 2], 40)
     np.save(Path(out_dir) / f"sh{rank}.npy", toks)
-    st.destroy(); m.destroy()
+    assert st.stats().exchange_ns > 0             # the peer hand-shakes ran (they account their own time)
+    os.environ["PYRE_B200_EP_EXCHANGE"] = "nccl"  # the same through NCCL all-gather + reduce-scatter
+    st2 = m.new_state(2, sharded=True)
+    toks2 = st2.decode_greedy(first[2 * rank:2 * rank + 2], 40)
+    del os.environ["PYRE_B200_EP_EXCHANGE"]
+    assert st2.stats().exchange_ns == 0
+    assert np.array_equal(toks, toks2)
+    # both states alive at once, stepping alternately: each owns its exchange block and sequence counter
+    a = st.decode_greedy(toks[:, -1].copy(), 8); b = st2.decode_greedy(toks2[:, -1].copy(), 8)
+    assert np.array_equal(a, b)
+    st2.destroy(); st.destroy(); m.destroy()
     if rank == 0:
         ctx1 = pb.Ctx(0)
         m1 = synth.build_model(ctx1, cfg, spec, 3)
@@ -154,4 +164,33 @@ def cpu_sharded_bookkeeping(rank, world, port, out_dir):
     assert np.array_equal(out.numpy().view(np.uint32), ref[rank * t:(rank + 1) * t].view(np.uint32))
     if rank == 0:
         np.save(Path(out_dir) / "ok.npy", np.ones(1))
+    dist.barrier(); dist.destroy_process_group()
+
+
+def cpu_flag_protocol(rank, world, port, out_dir):
+    """CPU, two processes over one memory-mapped flag array: the sequence-numbered hand-shake of the peer exchange.
+    Exchange 1 and 2 complete on both ranks (rank 1 runs ahead and posts 2 before rank 0 looked at 1); rank 1 then
+    stops posting, and rank 0's bounded wait for exchange 3 reports a timeout instead of blocking."""
+    import time
+    from pyre_b200 import parallel
+    dist = _init(rank, world, port, "gloo")
+    path = Path(out_dir) / "flags.bin"
+    if rank == 0:
+        np.zeros((world, 2, world), np.uint64).tofile(path)
+    dist.barrier()
+    flags = np.memmap(path, dtype=np.uint64, mode="r+", shape=(world, 2, world))
+    fx = parallel.FlagExchange(flags, rank, world, spin_limit=400, pause=lambda: time.sleep(0.005))
+    res = []
+    if rank == 1:
+        fx.post(0, 1); fx.post(0, 2); flags.flush()          # a fast peer: two exchanges announced back to back
+        res = [fx.wait(0, 1), fx.wait(0, 2)]
+        assert res == [True, True]
+    else:
+        time.sleep(0.2)                                       # a slow rank: it first sees the value 2
+        res = [fx.exchange(0, 1), fx.exchange(0, 2)]
+        assert res == [True, True]
+        short = parallel.FlagExchange(flags, rank, world, spin_limit=40, pause=lambda: time.sleep(0.005))
+        assert short.exchange(0, 3) is False                  # rank 1 never posts 3: the wait gives up
+        assert short.exchange(1, 1) is False                  # the other kind has its own counters
+        np.save(Path(out_dir) / "flag_ok.npy", np.ones(1))
     dist.barrier(); dist.destroy_process_group()

@@ -63,3 +63,30 @@ def test_sharded_tokens_identical_two_gpus():
         _spawn(ep_worker.gpu_sharded_tokens, 2, d)
         a, b, s = np.load(f"{d}/sh0.npy"), np.load(f"{d}/sh1.npy"), np.load(f"{d}/single.npy")
         assert np.array_equal(np.concatenate([a, b]), s)
+
+
+def test_flag_protocol_world2_bounded_wait():
+    import ep_worker
+    with tempfile.TemporaryDirectory() as d:
+        _spawn(ep_worker.cpu_flag_protocol, 2, d)
+        assert np.load(f"{d}/flag_ok.npy")[0] == 1
+
+
+@pytest.mark.gpu
+def test_peer_wait_that_nobody_answers_returns_device_error():
+    """A hand-shake whose partner never posts its flag: the kernel's bounded wait runs out, the call returns
+    PB_ERR_DEVICE, and the context serves the next call."""
+    import pyre_b200 as pb
+    ctx = pb.Ctx(0)
+    with pytest.raises(pb.PyreError) as e:
+        ctx.ep_probe_wait_timeout(2000)
+    assert e.value.status == pb.PB_ERR_DEVICE
+    assert ctx.device_status() == 0
+    W = pb.QMat.synth(ctx, pb.IQ3_S, 64, 256, 0, 1)     # the next call on the same context works
+    x = np.random.default_rng(0).standard_normal((1, 256)).astype(np.float32)
+    y = W.matmul(x)
+    assert np.allclose(y, x @ W.to_f32().T, rtol=2e-3, atol=2e-3)
+    with pytest.raises(pb.PyreError):
+        ctx.ep_probe_wait_timeout(500)                   # and a second timeout is reported again
+    assert W.matmul(x).shape == (1, 64)
+    W.free(); ctx.close()
