@@ -61,7 +61,7 @@ struct pb_state {
     float *xg = nullptr, *xs = nullptr, *part_rs = nullptr;   // gathered / local rows [token][d + logits], reduced partial rows
     int64_t ldg = 0;                                          // row stride of xg / xs
     // peer exchange (pb_ep.cu): xg and part_rs live in a block mapped into every rank; the kernels store into the peers' blocks
-    bool p2p = false; PbEpSymm symm; PbEpExch exch{}; float** part_tok = nullptr; unsigned long long* ep_seq = nullptr;
+    bool p2p = false; PbEpSymm symm; PbEpExch exch{}; PbEpExch* exch_dev = nullptr; float** part_tok = nullptr; unsigned long long* ep_seq = nullptr;
     int64_t ldproj = 0, ring_cap = 0;
     std::vector<float*> conv, ssm;
     std::vector<PbKv> kv;
@@ -336,8 +336,9 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
                     x.peer_flags[p] = reinterpret_cast<unsigned long long*>(base + xg_bytes + part_bytes);
                     for (int j = 0; j < B; j++) pt[(size_t)p * B + j] = reinterpret_cast<float*>(base + xg_bytes) + (size_t)j * c.top_k * c.d;
                 }
-                A(part_tok, (size_t)Bm);
+                A(part_tok, (size_t)Bm); A(exch_dev, 1);
                 if (rc == PB_OK && cudaMemcpyAsync(s->part_tok, pt.data(), pt.size() * sizeof(float*), cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) rc = PB_ERR_CUDA;
+                if (rc == PB_OK && cudaMemcpyAsync(s->exch_dev, &s->exch, sizeof(PbEpExch), cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) rc = PB_ERR_CUDA;
                 if (rc == PB_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = PB_ERR_CUDA;   // `pt` is a local
             }
         } else { A(xg, (size_t)Bm * s->ldg); A(part_rs, (size_t)B * c.top_k * c.d); }
@@ -549,8 +550,9 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
         // router logits of the local tokens, written next to a copy of their residual rows; one all-gather
         // moves both; then every rank splits and routes all tokens
         r.phase = 1; r.x = x_in; r.ldx = c.d; r.t = t; r.logits = s->xs + c.d; r.ldl = s->ldg; r.xcopy = s->xs;
+        if (s->p2p) { r.exch = s->exch_dev; r.exch_idx = 2 * il; r.peer_off = (int64_t)tok0 * s->ldg; }   // the router stores into every rank's gathered buffer and hand-shakes
         PB_TRY(pb_launch_router(ctx, r, q, s->ticket));
-        if (s->p2p) PB_TRY(pb_launch_ep_push_rows(ctx, s->exch, s->xs, (int64_t)t * s->ldg, (int64_t)tok0 * s->ldg, 2 * il));
+        if (s->p2p) r.exch = nullptr;
         else { PB_TRY(pb_ep_allgather(ctx, s->xs, s->xg, (size_t)t * s->ldg)); ctx->pdl_chain = false; }
         r.phase = 2; r.x = s->xg; r.ldx = s->ldg; r.t = tt; r.logits = s->xg + c.d; r.xcopy = nullptr;
         logits = s->xg + c.d; ldl = s->ldg;
@@ -593,7 +595,7 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
     PB_TRY(pb_launch_expert_down(ctx, e, dn_type, c.ff_exp));
     // expert parallelism: every (token, slot) row was produced on exactly one rank and is zero elsewhere,
     // so the sum is an exact gather and the combine below sees the same bits for every GPU count
-    if (sh && s->p2p) { PB_TRY(pb_launch_ep_signal_wait(ctx, s->exch, 1, 2 * il + 1)); k.part = s->part_rs; }
+    if (sh && s->p2p) { k.exch = s->exch_dev; k.exch_idx = 2 * il + 1; k.part = s->part_rs; }   // the combine kernel announces and waits
     else if (sh) { PB_TRY(pb_ep_reduce_scatter(ctx, s->part, s->part_rs, (size_t)t * c.top_k * c.d)); k.part = s->part_rs; ctx->pdl_chain = false; }
     else if (m->ep_world > 1) { PB_TRY(pb_ep_allreduce(ctx, s->part, (size_t)t * c.top_k * c.d)); ctx->pdl_chain = false; }
     return pb_launch_moe_combine(ctx, k);

@@ -13,6 +13,7 @@
 // the tokens' owners -- the same exact sum, 1/N of the dense work per rank.
 #include "pb_common.cuh"
 #include "pb_internal.h"
+#include "pb_ep.cuh"
 
 #include <dlfcn.h>
 #include <stdio.h>
@@ -122,31 +123,6 @@ int pb_ep_reduce_scatter(pb_ctx* ctx, const float* send, float* recv, size_t n) 
 //            call returns PB_ERR_DEVICE (the reference's pyre_wait_flag does the same for its CPU/GPU hand-shake,
 //            src/model/qwen4exp_gguf.rs:229-238).
 // Only plain loads and stores touch peer memory (no bulk copy engine reads or writes it).
-
-enum : int { PB_DEV_PEER_TIMEOUT = 5 };   // a peer did not announce an exchange in time
-
-__device__ __forceinline__ unsigned long long pb_ld_acquire_sys(const unsigned long long* p) {
-    unsigned long long v;
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void pb_st_release_sys(unsigned long long* p, unsigned long long v) {
-    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-// thread 0 of CTA p: tell rank p that this rank finished exchange `seq` of `kind`, then wait for rank p's announcement
-__device__ __forceinline__ void pb_ep_handshake(const PbEpExch& x, int p, int kind, unsigned long long seq) {
-    const unsigned long long t0 = pb_globaltimer();
-    __threadfence_system();
-    pb_st_release_sys(x.peer_flags[p] + (size_t)kind * x.world + x.rank, seq);
-    const unsigned long long* mine = x.peer_flags[x.rank] + (size_t)kind * x.world + p;
-    bool ok = false;
-    for (unsigned int i = 0; i < x.spin_limit; i++) {
-        if (pb_ld_acquire_sys(mine) >= seq) { ok = true; break; }
-        if (i > 64) __nanosleep(200);
-    }
-    if (!ok) atomicExch(x.status, PB_DEV_PEER_TIMEOUT);
-    if (x.wait_ns) atomicAdd(x.wait_ns, pb_globaltimer() - t0);   // summed over the world's CTAs; the host divides
-}
 
 // grid = world CTAs of 256 threads: CTA p serves rank p
 __global__ void __launch_bounds__(256) pb_ep_push_rows_kernel(const PbEpExch x, const float* __restrict__ rows, int64_t n, int64_t dst_off, int exch) {

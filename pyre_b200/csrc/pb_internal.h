@@ -219,6 +219,9 @@ struct PbRouterParams {
     int phase; float* xcopy;
     float* zero; int64_t zero_n;              // phases 0 and 2: zero_n floats (a multiple of 4) cleared for the expert kernels (expert parallelism)
     unsigned long long* stamps;
+    // phase 1 with a peer exchange (device copy of the descriptor): rows and logits are also stored into every rank's
+    // gathered buffer at float offset peer_off, and the last CTA hand-shakes exchange number exch_idx with all ranks
+    const PbEpExch* exch; int exch_idx; int64_t peer_off;
 };
 struct PbRouteParams {
     const float* logits; int64_t ldl; int t, n_exp, top_k;
@@ -248,6 +251,9 @@ struct PbCombineParams {
     const float* part; const float* part_sh; const float* logits; int64_t ldl;
     int t, d, top_k, n_exp;
     float* y; int64_t ldy; int accumulate;
+    // peer exchange (device copy of the descriptor): before reading `part`, announce exchange exch_idx (kind 1: this
+    // rank's expert rows are stored in their owners' memory) and wait for every rank's announcement
+    const PbEpExch* exch; int exch_idx;
 };
 int pb_launch_router(pb_ctx* ctx, const PbRouterParams& p, const PbRouteParams& rp, unsigned int* ticket);
 int pb_launch_expert_gu(pb_ctx* ctx, const PbExpertParams& p, int type, int cols);

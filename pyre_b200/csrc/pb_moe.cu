@@ -21,6 +21,7 @@
 #include "pb_internal.h"
 #include "pb_topk.cuh"
 #include "pb_router.cuh"
+#include "pb_ep.cuh"
 
 #include <stdio.h>
 
@@ -103,7 +104,11 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
     for (int g0 = blockIdx.x * 4; g0 < ng; g0 += gridDim.x * 4) {
         for (int b = b_lo + warp; b < b_hi; b += 8) {
             float4 v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + 32 * g0 + 4 * lane);
-            if (p.phase == 1) { *reinterpret_cast<float4*>(p.xcopy + b * p.ldl + 32 * g0 + 4 * lane) = v; continue; }   // raw row for the all-gather
+            if (p.phase == 1) {   // raw row for the gather: the local copy, and with a peer exchange every rank's gathered buffer
+                *reinterpret_cast<float4*>(p.xcopy + b * p.ldl + 32 * g0 + 4 * lane) = v;
+                if (p.exch) for (int q = 0; q < p.exch->world; q++) *reinterpret_cast<float4*>(p.exch->peer_xg[q] + p.peer_off + b * p.ldl + 32 * g0 + 4 * lane) = v;
+                continue;
+            }
             if (p.norm_w) {
                 const float4 n = *reinterpret_cast<const float4*>(p.norm_w + 32 * g0 + 4 * lane);
                 const float s = scale[b];
@@ -124,14 +129,29 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
             for (int b = b_lo; b < b_hi; b++) {
                 const float acc = rr.dot(p.x + b * p.ldx, scale[b], lane);
                 if (lane == 0) p.logits[b * p.ldl + row] = acc;
+                if (p.exch && lane < p.exch->world) p.exch->peer_xg[lane][p.peer_off + b * p.ldl + p.cols + row] = acc;
             }
         } else
         for (int b = b_lo; b < b_hi; b++) {
             const float acc = wrow ? pb_router_row_dot(wrow, p.norm_w, p.x + b * p.ldx, scale[b], p.cols, lane) : 0.f;
             if (lane == 0) p.logits[b * p.ldl + row] = acc;
+            if (p.exch && lane < p.exch->world) p.exch->peer_xg[lane][p.peer_off + b * p.ldl + p.cols + row] = acc;
         }
     }
-    if (p.phase == 1) return;
+    if (p.phase == 1) {
+        if (!p.exch) return;
+        // peer exchange: every CTA fences its stores into peer memory and takes a ticket; the last one announces the
+        // exchange to every rank and waits for theirs (one thread per rank)
+        __shared__ int last1;
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) last1 = atomicAdd(ticket, 1u) == gridDim.x * gridDim.y - 1;
+        __syncthreads();
+        if (!last1) return;
+        if (tid == 0) *ticket = 0;
+        if (tid < p.exch->world) pb_ep_handshake(*p.exch, tid, 0, *p.exch->seq_base + (unsigned long long)p.exch_idx + 1);
+        return;
+    }
     // the last CTA to get here routes all tokens: its reads of the logits follow every other CTA's
     // fence + ticket, the classic last-block pattern; the ticket is reset for the next launch
     __shared__ int is_last;
@@ -616,8 +636,17 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_expert_down_rows_kernel(con
 // y[tok][r] = sigmoid(shared-gate logit) * shared[tok][r] + sum_j part[tok][j][r]  (ascending expert id),
 // then either stored (layer-level call) or added to the residual stream.
 __global__ void __launch_bounds__(256) pb_moe_combine_kernel(const PbCombineParams p) {
-    pb_pdl_wait();
+    pb_pdl_wait();      // with a peer exchange: this rank's expert rows are stored in their owners' memory
     pb_pdl_trigger();
+    if (p.exch) {
+        // CTA 0 announces, every CTA waits for all ranks (one thread per rank); the barrier hands the acquired view on
+        if ((int)threadIdx.x < p.exch->world) {
+            const unsigned long long seq = *p.exch->seq_base + (unsigned long long)p.exch_idx + 1;
+            if (blockIdx.x == 0) pb_ep_handshake(*p.exch, threadIdx.x, 1, seq);
+            else pb_ep_wait(*p.exch, threadIdx.x, 1, seq);
+        }
+        __syncthreads();
+    }
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < (int64_t)p.t * p.d) pb_combine_one(p, i, false);
 }
