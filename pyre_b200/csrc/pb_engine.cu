@@ -446,8 +446,9 @@ int pb_state_pos(const pb_state* s, int64_t* pos) { if (!s || !pos) return PB_ER
 static void seg(PbGemvQArgs& a, int i, pb_qmat* q, int64_t yoff) { a.seg[i].w = q->data; a.seg[i].wr = q->rdata; a.seg[i].rows = q->rows; a.seg[i].yoff = yoff; }
 
 // y (+)= W_segs . act(x) for all batch columns, in tiles of 16 columns
-static int gemv_cols(pb_ctx* ctx, PbGemvQArgs a, int B) {
+static int gemv_cols(pb_ctx* ctx, PbGemvQArgs a, int B, bool prefill = false) {
     const float* x = a.x; float* y = a.y; const float* z = a.z; const uint32_t* xq = a.xq_in;
+    a.exact = prefill ? 0 : 1;   // decode steps and verify windows keep exact weights; prefill chunks may take the tcgen05 GEMM
     // the tensor-core path takes all columns at once (one staging pass for all its launches)
     static const bool use_mma = !(getenv("PYRE_B200_MMA") && atoi(getenv("PYRE_B200_MMA")) == 0);
     if (use_mma && a.mode != PB_ACT_PREQ && pb_gemmh_supported(a.type, a.cols, B) && (size_t)B * a.cols * 4 + 256 * (size_t)((B + 7) / 8) <= PB_XH_BYTES) { a.t = B; return pb_launch_gemvq(ctx, a); }

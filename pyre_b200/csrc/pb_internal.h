@@ -171,7 +171,7 @@ enum { PB_ACT_PLAIN = 0,   // x as given
        PB_ACT_GNORM = 2,   // per head of head_dim: rms(x) * norm_w[head_dim], times sigmoid(z)
        PB_ACT_PREQ = 3 };  // activations already split into int8 levels (xq_in)
 struct PbGemvSegArg { const uint8_t* w; int64_t rows; int64_t yoff; const uint8_t* wr; };   // wr: re-coded rows (pb_qmat::rdata) or null
-#define PB_XH_BYTES ((size_t)8 << 20)   // fragment buffer of the tensor-core GEMM: t * cols * 4 bytes + 256 per tile (e.g. 512 tokens of 4096 columns)
+#define PB_XH_BYTES (((size_t)16 << 20) + 8192)   // operand buffer of the tensor-core GEMMs: t * cols * 4 bytes + a header (e.g. 1024 tokens of 4096 columns)
 struct PbGemvQArgs {
     int type, cols, nseg;
     PbGemvSegArg seg[4];
@@ -180,6 +180,7 @@ struct PbGemvQArgs {
     int mode; const float* norm_w; const float* z; int64_t ldz; int head_dim; float eps;
     const uint32_t* xq_in;
     int accumulate;
+    int exact;   // keep the kernels whose weights enter the products exactly (decode steps feed recurrent state); 0 lets 16+ tokens use the tcgen05 GEMM, whose f16 weights carry one rounding
 };
 struct PbGemvQSeg { const uint8_t* w; int rows; int chunk0; int yoff; };
 struct PbGemvQParams {
@@ -202,6 +203,10 @@ int pb_launch_gemvq(pb_ctx* ctx, const PbGemvQArgs& a);
 // pb_gemmh.cu: tensor-core path for 3..16 columns of IQ3_S weights
 bool pb_gemmh_supported(int type, int cols, int t);
 int pb_launch_gemmh(pb_ctx* ctx, const PbGemvQArgs& a);
+// pb_gemmtc.cu: tcgen05 path for 16 and more columns of IQ3_S weights that have a re-coded copy
+bool pb_gemmtc_supported(int type, int cols, int t);
+int pb_launch_gemmtc(pb_ctx* ctx, const PbGemvQArgs& a);
+int pb_gemmtc_max_tokens(int cols);   // tokens one launch accepts (operand buffer), a multiple of 128
 
 // ---------------------------------------------------------------- pb_moe.cu
 #define PB_MAX_TOPK 16

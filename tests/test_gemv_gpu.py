@@ -116,7 +116,7 @@ import sys, numpy as np
 import pyre_b200 as pb
 ctx = pb.Ctx()
 out = {}
-for rows, cols, t in [(4096, 2048, 1), (2048, 512, 2), (515, 2048, 1), (200, 4096, 1), (1024, 2048, 8), (515, 2048, 16), (200, 4096, 5), (2048, 512, 12)]:
+for rows, cols, t in [(4096, 2048, 1), (2048, 512, 2), (515, 2048, 1), (200, 4096, 1), (1024, 2048, 8), (515, 2048, 15), (200, 4096, 5), (2048, 512, 12)]:
     W = pb.QMat.synth(ctx, pb.IQ3_S, rows, cols, 0, 5)
     x = np.random.default_rng(rows + cols).standard_normal((t, cols)).astype(np.float32)
     out[f"{rows}x{cols}x{t}"] = W.matmul(x)
@@ -129,7 +129,8 @@ def test_iq3s_recoded_and_native_kernels_agree_bit_for_bit(ctx, tmp_path):
     """IQ3_S matrices are streamed from a copy re-coded into 4-bit codes (weight = 2c - 15).  The
     re-coding is lossless and the offset is removed in integers, so the GEMV through the re-coded copy
     must equal the GEMV over the native GGUF blocks (PYRE_B200_REPACK=0) bit for bit -- on the dp4a path
-    (1-2 tokens) and on the tensor-core path (3 and more)."""
+    (1-2 tokens) and on the warp-level tensor-core path (3 to 15 tokens; 16 and more go to the tcgen05 GEMM, which
+    exists only for the re-coded copy and is compared with the oracle in test_gemmtc_gpu.py)."""
     import os
     import subprocess
     import sys
