@@ -189,6 +189,9 @@ int pb_state_fill_kv(pb_state* s, int b, int attn_index, const float* k_host, co
 /* Same with seeded synthetic N(0,1) rows generated on the GPU. */
 int pb_state_fill_kv_synth(pb_state* s, int attn_index, int64_t n, uint64_t seed);
 int pb_state_set_pos(pb_state* s, int64_t pos);
+/* A fresh conversation in an existing state: position 0, the DeltaNet conv history and recurrent state zeroed, the packed
+ * boundary of the 4-bit KV cache back to 0 (Model::new_state, src/model/qwen4exp_gguf.rs:3199-3213, without its allocations). */
+int pb_state_reset(pb_state* s);
 int pb_state_pos(const pb_state* s, int64_t* pos);
 
 /* Model::forward(ids, st) -> logits, src/model/qwen4exp_gguf.rs:2050-2157 (= spec::Target::step,

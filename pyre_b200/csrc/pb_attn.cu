@@ -117,47 +117,11 @@ __global__ void __launch_bounds__(256) pb_kv4_unpack_kernel(const uint32_t* __re
     if (i < n) x[i] = pb_kv4_dequant(w[i / 8], (int)(i % 8), sc[i / 32]);
 }
 
-// ------------------------------------------------------------------------------------ append
-
-// grid (batch), 256 threads
-__global__ void __launch_bounds__(AT_THREADS) pb_kv_append_kernel(const PbAttnParams p) {
-    const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int hd = p.hd, nkv = p.n_kv, half = p.n_rot / 2;
-    pb_pdl_wait();
-    pb_pdl_trigger();
-    const int64_t pos = p.pos[b];
-    const float* proj = p.proj + (size_t)b * p.ldp;
-    const float* kraw = proj + (size_t)p.n_head * 2 * hd;
-    const float* vraw = kraw + (size_t)nkv * hd;
-    const int64_t slot = pos % p.ring_cap;
-    __shared__ float sc[8];
-    for (int h = warp; h < nkv; h += AT_WARPS) {
-        float ss = 0.f;
-        for (int i = lane; i < hd; i += 32) { const float v = kraw[h * hd + i]; ss += v * v; }
-        ss = pb_warp_sum(ss);
-        if (lane == 0) sc[h & 7] = 1.0f / sqrtf(ss / (float)hd + p.eps);
-        __syncwarp();
-        const float s = sc[h & 7];
-        float* kd = p.kr + (((size_t)b * nkv + h) * p.ring_cap + slot) * hd;
-        float* vd = p.vr + (((size_t)b * nkv + h) * p.ring_cap + slot) * hd;
-        for (int i = lane; i < hd; i += 32) {
-            // rms_inplace: x *= s * w  (:210); rope rotates dims i and i + n_rot/2 for i < n_rot/2 (:1436-1439)
-            float x = kraw[h * hd + i] * (s * p.kn[i]);
-            if (i < p.n_rot) {
-                const int j = i < half ? i : i - half;
-                const float other = kraw[h * hd + (i < half ? i + half : i - half)] * (s * p.kn[i < half ? i + half : i - half]);
-                float sn, co;
-                sincosf((float)pos * p.rope_inv[j], &sn, &co);
-                x = i < half ? x * co - other * sn : x * co + other * sn;
-            }
-            kd[i] = x;
-            vd[i] = vraw[h * hd + i];
-        }
-    }
-    if (p.kv_bits != 4) return;
-    __syncthreads();
-    // packed boundary for len = pos + 1 rows (kv_push :1520): whole multiples of 64 positions
-    const int64_t len = pos + 1, have = p.q4n[b];
+// Moves the packed boundary of sequence b to where `len` rows put it (kv_push :1520: whole multiples of 64 positions):
+// the rows in between are read from the f32 ring and stored in 4-bit form.  All AT_THREADS threads of one CTA.
+__device__ __forceinline__ void pb_kv_pack_upto(const PbAttnParams& p, int b, int64_t len, int tid, int warp, int lane) {
+    const int hd = p.hd, nkv = p.n_kv;
+    const int64_t have = p.q4n[b];
     const int64_t want = len > p.kv_recent ? ((len - p.kv_recent) / 64) * 64 : 0;
     if (want <= have) return;
     const int bpp = hd / 32;                                  // blocks per position per head
@@ -180,6 +144,61 @@ __global__ void __launch_bounds__(AT_THREADS) pb_kv_append_kernel(const PbAttnPa
     }
     __syncthreads();
     if (tid == 0) p.q4n[b] = want;
+}
+
+// ------------------------------------------------------------------------------------ append
+
+// grid (batch), 256 threads
+__global__ void __launch_bounds__(AT_THREADS) pb_kv_append_kernel(const PbAttnParams p) {
+    const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int hd = p.hd, nkv = p.n_kv, half = p.n_rot / 2;
+    pb_pdl_wait();
+    pb_pdl_trigger();
+    const int64_t pos = p.pos[b];
+    const int cb = p.window ? 0 : b;                          // cache of the sequence this token belongs to
+    const float* proj = p.proj + (size_t)b * p.ldp;
+    const float* kraw = proj + (size_t)p.n_head * 2 * hd;
+    const float* vraw = kraw + (size_t)nkv * hd;
+    const int64_t slot = pos % p.ring_cap;
+    __shared__ float sc[8];
+    for (int h = warp; h < nkv; h += AT_WARPS) {
+        float ss = 0.f;
+        for (int i = lane; i < hd; i += 32) { const float v = kraw[h * hd + i]; ss += v * v; }
+        ss = pb_warp_sum(ss);
+        if (lane == 0) sc[h & 7] = 1.0f / sqrtf(ss / (float)hd + p.eps);
+        __syncwarp();
+        const float s = sc[h & 7];
+        float* kd = p.kr + (((size_t)cb * nkv + h) * p.ring_cap + slot) * hd;
+        float* vd = p.vr + (((size_t)cb * nkv + h) * p.ring_cap + slot) * hd;
+        for (int i = lane; i < hd; i += 32) {
+            // rms_inplace: x *= s * w  (:210); rope rotates dims i and i + n_rot/2 for i < n_rot/2 (:1436-1439)
+            float x = kraw[h * hd + i] * (s * p.kn[i]);
+            if (i < p.n_rot) {
+                const int j = i < half ? i : i - half;
+                const float other = kraw[h * hd + (i < half ? i + half : i - half)] * (s * p.kn[i < half ? i + half : i - half]);
+                float sn, co;
+                sincosf((float)pos * p.rope_inv[j], &sn, &co);
+                x = i < half ? x * co - other * sn : x * co + other * sn;
+            }
+            kd[i] = x;
+            vd[i] = vraw[h * hd + i];
+        }
+    }
+    if (p.kv_bits != 4 || p.window) return;
+    __syncthreads();
+    pb_kv_pack_upto(p, b, pos + 1, tid, warp, lane);
+}
+
+// window mode: one CTA moves the packed boundary of sequence 0 to where the window's last token puts it, and keeps the
+// boundary from before the window in q4n[1]
+__global__ void __launch_bounds__(AT_THREADS) pb_kv_pack_kernel(const PbAttnParams p) {
+    const int tid = threadIdx.x;
+    pb_pdl_wait();
+    pb_pdl_trigger();
+    const int64_t have = p.q4n[0];
+    __syncthreads();
+    if (tid == 0) p.q4n[1] = have;
+    pb_kv_pack_upto(p, 0, p.pos[p.batch - 1] + 1, tid, tid >> 5, tid & 31);
 }
 
 // ------------------------------------------------------------------------------------ partial
@@ -378,7 +397,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
     const int hd = p.hd, half = p.n_rot / 2;
     pb_pdl_wait();
     pb_pdl_trigger();
-    const int64_t pos = p.pos[b], n = pos + 1, q4n = p.kv_bits == 4 ? p.q4n[b] : 0;
+    const int64_t pos = p.pos[b], n = pos + 1;
+    // window mode: this token sees as packed what a token-by-token run would have packed when it was appended
+    int64_t q4n = 0;
+    if (p.kv_bits == 4) {
+        if (p.window) { const int64_t rule = n > p.kv_recent ? ((n - p.kv_recent) / 64) * 64 : 0, prev = p.q4n[1]; q4n = rule > prev ? rule : prev; }
+        else q4n = p.q4n[b];
+    }
     const float* proj = p.proj + (size_t)b * p.ldp;
 
     extern __shared__ float asm_[];
@@ -415,7 +440,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
     const int64_t ntiles = (n + AT_TILE - 1) / AT_TILE;
     // tiles are dealt round-robin to (split, warp) so that the slower f32 tiles of the recent window
     // are spread over all CTAs instead of landing on the last splits
-    const size_t hrow = (size_t)b * p.n_kv + kvh;
+    const size_t hrow = (size_t)(p.window ? 0 : b) * p.n_kv + kvh;
     const uint32_t* kw = p.kw + hrow * p.max_ctx * (hd / 8);
     const uint32_t* vw = p.vw + hrow * p.max_ctx * (hd / 8);
     const float* ks = p.ks + hrow * p.max_ctx * (hd / 32);
@@ -650,6 +675,14 @@ __global__ void __launch_bounds__(1024) pb_attn_combine_kernel(const PbAttnParam
 int pb_launch_kv_append(pb_ctx* ctx, const PbAttnParams& p) {
     if (p.hd % 32 || p.n_rot > p.hd || p.n_rot % 2 || p.n_kv > 8) PB_FAIL(ctx, PB_UNSUPPORTED, "attention: head dim %d / rotary dim %d not supported", p.hd, p.n_rot);
     pb_launch_k(ctx, pb_kv_append_kernel, dim3(p.batch), dim3(AT_THREADS), (size_t)(0), p);
+    ctx->kernels_launched++;
+    PB_CUDA(ctx, cudaGetLastError());
+    return PB_OK;
+}
+
+int pb_launch_kv_pack(pb_ctx* ctx, const PbAttnParams& p) {
+    if (!p.window || p.kv_bits != 4) return PB_OK;
+    pb_launch_k(ctx, pb_kv_pack_kernel, dim3(1), dim3(AT_THREADS), (size_t)(0), p);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;

@@ -18,6 +18,9 @@
 #include <vector>
 
 #define PB_MAX_WINDOW 8   // draft windows of the reference are at most 8 tokens (src/spec.rs:185)
+#define PB_PREFILL_CHUNK 256   // prompt tokens per batched pass; prompts are cut on the absolute grid of this size (src/engine_qn.rs:34-38, 92-139)
+#define PB_WIN_SPLITS 4        // attention splits per (token, KV head) of a prefill chunk: three walk the packed positions, one the f32 ring
+#define PB_WIN_KEYS (4 * (PB_MAX_WINDOW + 1) + 1)   // graphs per (t <= 8, ckpt, all_logits), plus one for a full prefill chunk
 static size_t conv_elems(const pb_cfg& c, int B) { return (size_t)B * c.conv_k * (2 * c.lin_nk * c.lin_dk + c.lin_nv * c.lin_dv); }
 static size_t ssm_elems(const pb_cfg& c, int B) { return (size_t)B * c.lin_nv * c.lin_dk * c.lin_dv; }
 
@@ -57,7 +60,7 @@ struct pb_state {
     // the layers as columns; wpos[j] = position of column j; win_ckpt = keep DeltaNet checkpoints
     int win_t = 0; bool win_ckpt = false; int64_t* wpos = nullptr;
     int moe_cap = 0;   // rows of the MoE work buffers
-    cudaGraphExec_t win_graph[4 * (PB_MAX_WINDOW + 1)] = {}; unsigned char win_runs[4 * (PB_MAX_WINDOW + 1)] = {};   // per (t, ckpt, all_logits)
+    cudaGraphExec_t win_graph[PB_WIN_KEYS] = {}; unsigned char win_runs[PB_WIN_KEYS] = {};
     float *xg = nullptr, *xs = nullptr, *part_rs = nullptr;   // gathered / local rows [token][d + logits], reduced partial rows
     int64_t ldg = 0;                                          // row stride of xg / xs
     // peer exchange (pb_ep.cu): xg and part_rs live in a block mapped into every rank; the kernels store into the peers' blocks
@@ -291,7 +294,8 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
     const int B = batch;
     s->sharded = sharded && m->ep_world > 1;
     s->moe_t = s->sharded ? batch * m->ep_world : batch; s->tok0 = s->sharded ? batch * m->ep_rank : 0;
-    const int Ba = (B == 1 && !s->sharded) ? PB_MAX_WINDOW : B;   // activation rows: a batch-1 state also runs windows of up to 8 tokens
+    const bool solo = B == 1 && !s->sharded;
+    const int Ba = solo ? PB_PREFILL_CHUNK : B;   // activation rows: a batch-1 state also runs verify windows (up to 8 tokens) and prefill chunks (up to 256)
     const int Bm = s->moe_t > Ba ? s->moe_t : Ba;                 // tokens a MoE block of this state may see
     s->moe_cap = Bm;
     const int ch = 2 * c.lin_nk * c.lin_dk + c.lin_nv * c.lin_dv;
@@ -301,7 +305,7 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
     const int64_t wide = (int64_t)c.lin_nv * c.lin_dv > (int64_t)c.n_head * c.hd ? (int64_t)c.lin_nv * c.lin_dv : (int64_t)c.n_head * c.hd;
     int rc = PB_OK;
 #define A(p, n) if (rc == PB_OK) rc = dalloc(s, &s->p, (size_t)(n))
-    A(pos, B); A(ids, Ba); A(next, Ba); A(amax, Ba); A(ticket, 4); A(wpos, PB_MAX_WINDOW);
+    A(pos, B); A(ids, Ba); A(next, Ba); A(amax, Ba); A(ticket, 4); A(wpos, PB_PREFILL_CHUNK);
     A(x, (size_t)Ba * c.d); A(xin, (size_t)Ba * (wide > c.d ? wide : c.d)); A(yout, (size_t)Ba * c.d);
     A(proj, (size_t)Ba * s->ldproj); A(olin, (size_t)Ba * wide); A(att, (size_t)Ba * wide);
     A(rlogits, (size_t)Bm * (c.n_exp + 1));
@@ -343,7 +347,7 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
             }
         } else { A(xg, (size_t)Bm * s->ldg); A(part_rs, (size_t)B * c.top_k * c.d); }
     }
-    A(logits, (size_t)Ba * c.vocab);
+    A(logits, (size_t)(solo ? PB_MAX_WINDOW : B) * c.vocab);   // a prefill chunk keeps only its last token's logits
     if (B == 1 && !s->sharded) { A(fops, (size_t)c.n_layers * 8 + 8); A(fh, (size_t)(c.top_k + 1) * c.ff_exp); }
     s->trace_cap = 4096;
     A(trace, (size_t)s->trace_cap * B); A(trace_len, 2);
@@ -366,14 +370,17 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
         }
     }
     s->nsplit = ns;
-    A(part_ml, (size_t)B * c.n_kv * ns * G * 2); A(part_acc, (size_t)B * c.n_kv * ns * G * c.hd);
+    const size_t nparts = solo && (size_t)PB_PREFILL_CHUNK * PB_WIN_SPLITS > (size_t)ns ? (size_t)PB_PREFILL_CHUNK * PB_WIN_SPLITS : (size_t)B * ns;   // a prefill chunk: its tokens x PB_WIN_SPLITS
+    A(part_ml, nparts * c.n_kv * G * 2); A(part_acc, nparts * c.n_kv * G * c.hd);
     s->conv.assign(m->n_lin, nullptr); s->ssm.assign(m->n_lin, nullptr); s->kv.assign(m->n_attn, PbKv());
     for (int i = 0; i < m->n_lin && rc == PB_OK; i++) {
         rc = dalloc(s, &s->conv[i], (size_t)B * c.conv_k * ch);
         if (rc == PB_OK) rc = dalloc(s, &s->ssm[i], (size_t)B * c.lin_nv * c.lin_dk * c.lin_dv);
     }
     const int64_t rowh = c.hd;
-    s->ring_cap = c.kv_bits == 4 ? (int64_t)c.kv_recent + 64 : (int64_t)c.max_ctx;
+    // 4-bit cache: the f32 ring holds the recent positions, the 64 that wait for the next packing step, and (batch-1 states)
+    // a whole prefill chunk appended before its packing step
+    s->ring_cap = c.kv_bits == 4 ? (int64_t)c.kv_recent + 64 + (solo ? PB_PREFILL_CHUNK : 0) : (int64_t)c.max_ctx;
     for (int i = 0; i < m->n_attn && rc == PB_OK; i++) {
         PbKv& k = s->kv[i];
         const size_t heads = (size_t)B * c.n_kv;
@@ -387,7 +394,7 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
         if (rc == PB_OK) rc = dalloc(s, &k.vs, heads * packed_pos * (rowh / 32));
     }
 #undef A
-    if (rc == PB_OK && cudaMallocHost(&s->pin_u32, (size_t)(s->trace_cap + 2) * B * 4) != cudaSuccess) { ctx->err = "pinned allocation failed"; rc = PB_ERR_OOM; }
+    if (rc == PB_OK && cudaMallocHost(&s->pin_u32, (size_t)(s->trace_cap + 2) * B * 4 + PB_PREFILL_CHUNK * 4) != cudaSuccess) { ctx->err = "pinned allocation failed"; rc = PB_ERR_OOM; }
     if (rc == PB_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) { ctx->err = "stream sync failed"; rc = PB_ERR_CUDA; }
     if (rc != PB_OK) { pb_state_destroy(s); return rc; }
     *out = s;
@@ -439,6 +446,18 @@ int pb_state_set_pos(pb_state* s, int64_t pos) {
     s->pos_host = pos;
     return PB_OK;
 }
+int pb_state_reset(pb_state* s) {
+    if (!s) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx;
+    PB_TRY(pb_state_set_pos(s, 0));
+    const pb_cfg& c = s->m->cfg;
+    for (int li = 0; li < s->m->n_lin; li++) {
+        PB_CUDA(ctx, cudaMemsetAsync(s->conv[li], 0, conv_elems(c, s->batch) * 4, ctx->stream));
+        PB_CUDA(ctx, cudaMemsetAsync(s->ssm[li], 0, ssm_elems(c, s->batch) * 4, ctx->stream));
+    }
+    s->verify_t = 0;
+    return PB_OK;
+}
 int pb_state_pos(const pb_state* s, int64_t* pos) { if (!s || !pos) return PB_ERR_ARG; *pos = s->pos_host; return PB_OK; }
 
 // ---- layer pieces -----------------------------------------------------------------------------
@@ -470,12 +489,17 @@ static int run_lin(pb_state* s, int il, const float* x_in, const float* norm_w, 
     seg(a, 0, M(m, il, PB_R_LIN_QKV), 0); seg(a, 1, M(m, il, PB_R_LIN_Z), ch); seg(a, 2, M(m, il, PB_R_LIN_BETA), ch + w); seg(a, 3, M(m, il, PB_R_LIN_ALPHA), ch + w + c.lin_nv);
     a.x = x_in; a.ldx = c.d; a.y = s->proj; a.ldy = s->ldproj; a.mode = norm_w ? PB_ACT_NORM : PB_ACT_PLAIN; a.norm_w = norm_w; a.eps = c.eps;
     const int ncol = s->win_t > 0 ? s->win_t : B;   // window mode: the columns are consecutive tokens of sequence 0
-    PB_TRY(gemv_cols(ctx, a, ncol));
+    const bool prefill = s->win_t >= 16 && !s->win_ckpt;
+    PB_TRY(gemv_cols(ctx, a, ncol, prefill));
     PbDeltaParams d; memset(&d, 0, sizeof d);
     d.proj = s->proj; d.ldp = s->ldproj; d.conv_w = V(m, il, PB_R_LIN_CONV); d.a = V(m, il, PB_R_LIN_A); d.dt = V(m, il, PB_R_LIN_DT);
     d.conv = s->conv[li]; d.ssm = s->ssm[li]; d.pos = s->pos; d.out = s->olin; d.ldo = w;
     d.nk = c.lin_nk; d.nv = c.lin_nv; d.dk = c.lin_dk; d.dv = c.lin_dv; d.conv_k = c.conv_k; d.batch = B;
-    if (s->win_t > 0) {
+    if (s->win_t > 0 && !s->win_ckpt && pb_deltanet_seq_supported(d)) {
+        // no rollback wanted: all tokens in one launch, the state slice stays in registers
+        d.pos = s->wpos; d.batch = 1;
+        PB_TRY(pb_launch_deltanet_seq(ctx, d, s->win_t));
+    } else if (s->win_t > 0) {
         // the recurrence is sequential: one launch per token, with a rollback checkpoint after each but the last
         for (int j = 0; j < s->win_t; j++) {
             d.proj = s->proj + (size_t)j * s->ldproj; d.out = s->olin + (size_t)j * w; d.pos = s->wpos + j; d.batch = 1;
@@ -490,7 +514,7 @@ static int run_lin(pb_state* s, int il, const float* x_in, const float* norm_w, 
     PbGemvQArgs o; memset(&o, 0, sizeof o);
     o.type = M(m, il, PB_R_LIN_OUT)->type; o.cols = w; o.nseg = 1; seg(o, 0, M(m, il, PB_R_LIN_OUT), 0);
     o.x = s->olin; o.ldx = w; o.y = y; o.ldy = ldy; o.mode = PB_ACT_GNORM; o.norm_w = V(m, il, PB_R_LIN_NORM); o.z = s->proj + ch; o.ldz = s->ldproj; o.head_dim = c.lin_dv; o.eps = c.eps; o.accumulate = accumulate;
-    return gemv_cols(ctx, o, ncol);
+    return gemv_cols(ctx, o, ncol, prefill);
 }
 
 static void attn_params(pb_state* s, int il, PbAttnParams& p) {
@@ -512,9 +536,19 @@ static int run_attn(pb_state* s, int il, const float* x_in, const float* norm_w,
     seg(a, 0, M(m, il, PB_R_ATTN_Q), 0); seg(a, 1, M(m, il, PB_R_ATTN_K), nq); seg(a, 2, M(m, il, PB_R_ATTN_V), nq + row);
     a.x = x_in; a.ldx = c.d; a.y = s->proj; a.ldy = s->ldproj; a.mode = norm_w ? PB_ACT_NORM : PB_ACT_PLAIN; a.norm_w = norm_w; a.eps = c.eps;
     const int ncol = s->win_t > 0 ? s->win_t : B;
-    PB_TRY(gemv_cols(ctx, a, ncol));
+    const bool prefill = s->win_t >= 16 && !s->win_ckpt;
+    PB_TRY(gemv_cols(ctx, a, ncol, prefill));
     PbAttnParams p; attn_params(s, il, p);
-    if (s->win_t > 0) {
+    if (s->win_t > 0 && !s->win_ckpt) {
+        // a prefill chunk: all tokens are appended, the packed boundary moves once, then every token attends to the
+        // positions <= its own in one launch (token j treats as packed what it would have found packed token by token)
+        p.window = 1; p.pos = s->wpos; p.batch = s->win_t;
+        const bool mma = s->nsplit_packed > 0;
+        p.nsplit = mma ? PB_WIN_SPLITS : 1; p.nsplit_packed = mma ? PB_WIN_SPLITS - 1 : 0;
+        PB_TRY(pb_launch_kv_append(ctx, p));
+        PB_TRY(pb_launch_kv_pack(ctx, p));
+        PB_TRY(pb_launch_attn(ctx, p));
+    } else if (s->win_t > 0) {
         // causal inside the window: token j is appended, then attends to positions <= its own
         for (int j = 0; j < s->win_t; j++) {
             p.proj = s->proj + (size_t)j * s->ldproj; p.pos = s->wpos + j; p.att = s->att + (size_t)j * p.lda; p.batch = 1;
@@ -528,7 +562,7 @@ static int run_attn(pb_state* s, int il, const float* x_in, const float* norm_w,
     PbGemvQArgs o; memset(&o, 0, sizeof o);
     o.type = M(m, il, PB_R_ATTN_O)->type; o.cols = c.n_head * c.hd; o.nseg = 1; seg(o, 0, M(m, il, PB_R_ATTN_O), 0);
     o.x = s->att; o.ldx = (int64_t)c.n_head * c.hd; o.y = y; o.ldy = ldy; o.mode = PB_ACT_PLAIN; o.accumulate = accumulate;
-    return gemv_cols(ctx, o, ncol);
+    return gemv_cols(ctx, o, ncol, prefill);
 }
 
 // MoE block on t tokens: x_in [t][d] (normalized when norm_w == null) -> y (stored or added)
@@ -814,8 +848,12 @@ static int run_window(pb_state* s, int t, bool ckpt, bool all_logits) {
 // second, replayed afterwards -- a window is ~1500 launches, whose host cost would otherwise dominate.
 static int window_once(pb_state* s, int t, bool ckpt, bool all_logits) {
     pb_ctx* ctx = s->m->ctx;
-    const int key = t * 4 + (ckpt ? 2 : 0) + (all_logits ? 1 : 0);
-    if (s->win_graph[key]) {
+    // graphs: windows of up to 8 tokens per (t, ckpt, all_logits), and the full prefill chunk; other lengths (the ragged
+    // ends of a prompt) run eagerly
+    const int key = t <= PB_MAX_WINDOW ? t * 4 + (ckpt ? 2 : 0) + (all_logits ? 1 : 0) : (t == PB_PREFILL_CHUNK && !ckpt && !all_logits ? PB_WIN_KEYS - 1 : -1);
+    if (key < 0) {
+        PB_TRY(run_window(s, t, ckpt, all_logits));
+    } else if (s->win_graph[key]) {
         PB_CUDA(ctx, cudaGraphLaunch(s->win_graph[key], ctx->stream));
     } else if (s->win_runs[key] == 0) {
         PB_TRY(run_window(s, t, ckpt, all_logits));
@@ -876,11 +914,14 @@ int pb_forward(pb_state* s, const uint32_t* ids_host, int t, float* logits_host)
     if (!ids_host || !logits_host || t < 1) PB_FAIL(ctx, PB_ERR_ARG, "pb_forward: bad argument");
     const int B = s->batch;
     if (B == 1 && !s->sharded && t >= 3) {
-        // a prompt of one sequence: windows of up to 8 tokens, each streaming the weights once
+        // a prompt of one sequence: batched passes of up to PB_PREFILL_CHUNK tokens, each streaming the weights once, cut on
+        // the absolute grid of that size -- the first piece runs up to the next multiple of the chunk, so a prompt resumed
+        // from a snapshot taken on the grid is split exactly like a prefill from position 0 (src/engine_qn.rs:117-128)
         if (s->pos_host + t > s->m->cfg.max_ctx) PB_FAIL(ctx, PB_ERR_STATE, "context is full (%d positions)", s->m->cfg.max_ctx);
         timing_begin(s);
-        for (int j0 = 0; j0 < t; j0 += PB_MAX_WINDOW) {
-            const int n = t - j0 < PB_MAX_WINDOW ? t - j0 : PB_MAX_WINDOW;
+        for (int j0 = 0, n = 0; j0 < t; j0 += n) {
+            const int64_t to_grid = PB_PREFILL_CHUNK - s->pos_host % PB_PREFILL_CHUNK;
+            n = t - j0 < to_grid ? t - j0 : (int)to_grid;
             for (int j = 0; j < n; j++) s->pin_u32[j] = ids_host[j0 + j];
             PB_CUDA(ctx, cudaMemcpyAsync(s->ids, s->pin_u32, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream));
             PB_TRY(window_once(s, n, false, false));

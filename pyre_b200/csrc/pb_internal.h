@@ -277,6 +277,8 @@ struct PbDeltaParams {
     unsigned long long* stamps;
 };
 int pb_launch_deltanet(pb_ctx* ctx, const PbDeltaParams& p);
+bool pb_deltanet_seq_supported(const PbDeltaParams& p);
+int pb_launch_deltanet_seq(pb_ctx* ctx, const PbDeltaParams& p, int T);   // T consecutive tokens of sequence 0, state kept in registers
 
 // ---------------------------------------------------------------- pb_attn.cu
 struct PbAttnParams {
@@ -292,9 +294,14 @@ struct PbAttnParams {
     int nsplit_packed;                                   // splits [0, nsplit_packed) walk the packed positions on the tensor cores
     float* att; int64_t lda;                             // [batch][n_head*hd]
     int batch;
+    // window: the `batch` entries are consecutive tokens of sequence 0 (a prefill chunk): they share its cache; the append
+    // kernel only writes the f32 ring, pb_launch_kv_pack then moves the packed boundary once for the whole window and
+    // keeps the previous boundary in q4n[1]; token j treats as packed what a token-by-token run would have packed by then
+    int window;
 };
 int pb_launch_kv_append(pb_ctx* ctx, const PbAttnParams& p);
 int pb_launch_attn(pb_ctx* ctx, const PbAttnParams& p);
+int pb_launch_kv_pack(pb_ctx* ctx, const PbAttnParams& p);   // window mode, after pb_launch_kv_append
 int pb_launch_kv4_pack(pb_ctx* ctx, const float* x, int64_t n, uint32_t* w, float* sc, int bias);   // bias 0: kv4.rs nibbles; 8: cache form
 int pb_launch_kv4_pack_vt(pb_ctx* ctx, const float* x, int64_t npos, int hd, uint32_t* w, float* sc, int bias);   // position-transposed V words
 int pb_launch_kv4_unpack(pb_ctx* ctx, const uint32_t* w, const float* sc, int64_t n, float* x);

@@ -108,10 +108,10 @@ __global__ void pb_window_pos_kernel(int64_t* pos, int64_t* wpos, int t, int adv
     pb_pdl_wait();
     pb_pdl_trigger();
     if (advance) { if (threadIdx.x == 0) pos[0] += t; }
-    else if ((int)threadIdx.x < t) wpos[threadIdx.x] = pos[0] + threadIdx.x;
+    else for (int j = threadIdx.x; j < t; j += blockDim.x) wpos[j] = pos[0] + j;
 }
 int pb_launch_window_pos(pb_ctx* ctx, int64_t* pos, int64_t* wpos, int t, int advance) {
-    pb_launch_k(ctx, pb_window_pos_kernel, dim3(1), dim3(32), (size_t)0, pos, wpos, t, advance);
+    pb_launch_k(ctx, pb_window_pos_kernel, dim3(1), dim3(256), (size_t)0, pos, wpos, t, advance);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;

@@ -104,6 +104,10 @@ class State:
     def set_pos(self, pos: int):
         self.ctx.check(lib().pb_state_set_pos(self.h, C.c_int64(pos)))
 
+    def reset(self):
+        """A fresh conversation: position 0, recurrent state and conv history zeroed (pb_state_reset)."""
+        self.ctx.check(lib().pb_state_reset(self.h))
+
     def pos(self) -> int:
         p = C.c_int64()
         self.ctx.check(lib().pb_state_pos(self.h, C.byref(p)))
