@@ -305,7 +305,8 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
     const int64_t wide = (int64_t)c.lin_nv * c.lin_dv > (int64_t)c.n_head * c.hd ? (int64_t)c.lin_nv * c.lin_dv : (int64_t)c.n_head * c.hd;
     int rc = PB_OK;
 #define A(p, n) if (rc == PB_OK) rc = dalloc(s, &s->p, (size_t)(n))
-    A(pos, B); A(ids, Ba); A(next, Ba); A(amax, Ba); A(ticket, 4); A(wpos, PB_PREFILL_CHUNK);
+    A(pos, B); A(ids, Ba); A(next, Ba); A(amax, Ba); A(wpos, PB_PREFILL_CHUNK);
+    A(ticket, 8 + (size_t)(Bm + 7) / 8);   // whole-launch counters, then one per group of 8 tokens of the router
     A(x, (size_t)Ba * c.d); A(xin, (size_t)Ba * (wide > c.d ? wide : c.d)); A(yout, (size_t)Ba * c.d);
     A(proj, (size_t)Ba * s->ldproj); A(olin, (size_t)Ba * wide); A(att, (size_t)Ba * wide);
     A(rlogits, (size_t)Bm * (c.n_exp + 1));

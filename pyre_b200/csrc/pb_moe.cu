@@ -6,9 +6,9 @@
 // (src/model/qn_cube.rs:3482-5419, 5210-5256).  Nothing leaves the device:
 //   1. pb_router_kernel   RMSNorm (optional) + f32 router GEMV + shared-gate logit; also emits
 //                         the normalized activations split into int8 levels for the experts
-//   2. pb_route_body      (last router CTA) per token top-k (descending logit, ties to the lower id, NaN -> -inf),
-//                         softmax over the selection, selection sorted by expert id; builds the
-//                         list of distinct local experts with their (token, slot) entries
+//   2. pb_route_tokens    (last router CTA of each group of 8 tokens) per token top-k (descending logit, ties to the
+//                         lower id, NaN -> -inf), softmax over the selection, selection sorted by expert id;
+//      pb_route_lists     (last of those CTAs) the list of distinct local experts with their (token, slot) entries
 //   3. pb_expert_gu_kernel   h = silu(gate_e x) * (up_e x) for every (expert, token) entry and the
 //                         shared expert; weights streamed once per expert
 //   4. pb_split_h_kernel  (several tokens) the hidden vectors of all entries split into int8 levels once
@@ -27,24 +27,31 @@
 
 // ------------------------------------------------------------------------------------ routing
 
-// Runs in ONE CTA of 256 threads (the last router CTA to finish); warp per token.  Everything stays in
-// registers: lane l holds experts l, l+32, ... of the token.  rsm = 2048 ints of shared memory.
-__device__ __forceinline__ void pb_route_body(const PbRouteParams& p, int* rsm) {
+// Tokens [b_lo, b_hi) by the 256 threads of one CTA (the last router CTA of the tokens' group), warp per token.
+// Everything stays in registers: lane l holds experts l, l+32, ... of the token.
+__device__ __forceinline__ void pb_route_tokens(const PbRouteParams& p, int b_lo, int b_hi) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int b = b_lo + warp; b < b_hi; b += 8) {
+        const float* lg = p.logits + (size_t)b * p.ldl;
+        // lane j keeps the j-th pick, its softmax weight and its rank by expert id (pb_topk.cuh)
+        int my_e, rank; float w;
+        pb_route_token(lg, p.n_exp, p.top_k, lane, my_e, w, rank);
+        if (lane < p.top_k) { p.sel_e[b * p.top_k + rank] = my_e; p.sel_w[b * p.top_k + rank] = w; }
+    }
+}
+
+// Runs in ONE CTA of 256 threads (the last router CTA to finish) once every token is routed: the list of distinct local
+// experts with their (token, slot) entries.  rsm = 2048 ints of shared memory.
+__device__ __forceinline__ void pb_route_lists(const PbRouteParams& p, int* rsm) {
     int* cnt = rsm;                 // [1024] entries per expert (local experts only)
     int* cursor = rsm + 1024;       // [1024] start offset of the expert's entries, then a fill cursor
     __shared__ int wsum[2][8];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     for (int e = tid; e < 1024; e += 256) { cnt[e] = 0; cursor[e] = 0; }
     __syncthreads();
-    for (int b = warp; b < p.t; b += 8) {
-        const float* lg = p.logits + (size_t)b * p.ldl;
-        // lane j keeps the j-th pick, its softmax weight and its rank by expert id (pb_topk.cuh)
-        int my_e, rank; float w;
-        pb_route_token(lg, p.n_exp, p.top_k, lane, my_e, w, rank);
-        if (lane < p.top_k) {
-            p.sel_e[b * p.top_k + rank] = my_e; p.sel_w[b * p.top_k + rank] = w;
-            if (my_e >= p.e_lo && my_e < p.e_hi) atomicAdd(&cnt[my_e], 1);
-        }
+    for (int i = tid; i < p.t * p.top_k; i += 256) {
+        const int e = __ldcg(p.sel_e + i);
+        if (e >= p.e_lo && e < p.e_hi) atomicAdd(&cnt[e], 1);
     }
     __syncthreads();
     // distinct local experts in ascending id with entry offsets: block-wide exclusive scans of
@@ -65,8 +72,8 @@ __device__ __forceinline__ void pb_route_body(const PbRouteParams& p, int* rsm) 
     if (tid == 255) { p.used_off[n] = off; *p.n_used = n; }
     __syncthreads();
     for (int i = tid; i < p.t * p.top_k; i += 256) {
-        const int e = p.sel_e[i];
-        if (e >= p.e_lo && e < p.e_hi) { const int pos = atomicAdd(&cursor[e], 1); p.ent_tok[pos] = i / p.top_k; p.ent_slot[pos] = i % p.top_k; p.ent_w[pos] = p.sel_w[i]; }
+        const int e = __ldcg(p.sel_e + i);
+        if (e >= p.e_lo && e < p.e_hi) { const int pos = atomicAdd(&cursor[e], 1); p.ent_tok[pos] = i / p.top_k; p.ent_slot[pos] = i % p.top_k; p.ent_w[pos] = __ldcg(p.sel_w + i); }
     }
 }
 
@@ -76,6 +83,7 @@ __device__ __forceinline__ void pb_route_body(const PbRouteParams& p, int* rsm) 
 // CTA j additionally splits groups 4j..4j+3 of every token's normalized activations into int8
 // levels for the expert kernels, so that work is spread over the grid.
 #define PB_ROUTER_TPG 8   // tokens per router CTA (one warp each for the RMS scales)
+#define PB_ROUTER_TICKETS 8   // ticket[0 .. 8): whole-launch counters (router, expert kernels); ticket[8 + g]: token group g of the router
 __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, const PbRouteParams rp, unsigned int* ticket) {
     extern __shared__ float rs[];   // 2048 ints for the routing pass, then scale[t]
     float* scale = rs + 2048;
@@ -152,19 +160,28 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
         if (tid < p.exch->world) pb_ep_handshake(*p.exch, tid, 0, *p.exch->seq_base + (unsigned long long)p.exch_idx + 1);
         return;
     }
-    // the last CTA to get here routes all tokens: its reads of the logits follow every other CTA's
-    // fence + ticket, the classic last-block pattern; the ticket is reset for the next launch
+    // two levels of the last-block pattern (fence, ticket, the last one reads what the others wrote): the last CTA of a
+    // token group (grid.y) routes the group's tokens, so the groups are routed in parallel; the last of those CTAs
+    // builds the expert lists from all selections.  The tickets are reset for the next launch.
     __shared__ int is_last;
     __threadfence();
     __syncthreads();
     pb_stamp(p.stamps, 5, st_first);   // this CTA's logits stored
-    if (tid == 0) is_last = atomicAdd(ticket, 1u) == gridDim.x * gridDim.y - 1;
+    if (tid == 0) is_last = atomicAdd(ticket + PB_ROUTER_TICKETS + blockIdx.y, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!is_last) return;
+    if (tid == 0) ticket[PB_ROUTER_TICKETS + blockIdx.y] = 0;
+    __threadfence();
+    pb_stamp(p.stamps, 6, tid == 0 && blockIdx.y == 0);   // the routing pass of the first group starts (its logits are in)
+    pb_route_tokens(rp, b_lo, b_hi);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) is_last = atomicAdd(ticket, 1u) == gridDim.y - 1;
     __syncthreads();
     if (!is_last) return;
     if (tid == 0) *ticket = 0;
     __threadfence();
-    pb_stamp(p.stamps, 6, tid == 0);   // the routing pass starts (all logits are in)
-    pb_route_body(rp, reinterpret_cast<int*>(rs));
+    pb_route_lists(rp, reinterpret_cast<int*>(rs));
     __syncthreads();
     pb_stamp(p.stamps, 7, tid == 0);
 }
