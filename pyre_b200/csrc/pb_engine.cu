@@ -61,6 +61,7 @@ struct pb_state {
     int win_t = 0; bool win_ckpt = false; int64_t* wpos = nullptr;
     int moe_cap = 0;   // rows of the MoE work buffers
     cudaGraphExec_t win_graph[PB_WIN_KEYS] = {}; unsigned char win_runs[PB_WIN_KEYS] = {};
+    float *hxn = nullptr, *hgate = nullptr, *hlo = nullptr, *hinj = nullptr, *hmix = nullptr;   // hyper-connection work rows (hc >= 1)
     float *xg = nullptr, *xs = nullptr, *part_rs = nullptr;   // gathered / local rows [token][d + logits], reduced partial rows
     int64_t ldg = 0;                                          // row stride of xg / xs
     // peer exchange (pb_ep.cu): xg and part_rs live in a block mapped into every rank; the kernels store into the peers' blocks
@@ -124,7 +125,7 @@ int pb_model_create(pb_ctx* ctx, const pb_cfg* cfg, pb_model** out) {
     if (!cfg) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_create: null config");
     const pb_cfg& c = *cfg;
     if (c.n_layers <= 0 || c.d <= 0 || c.vocab <= 0 || c.max_ctx <= 0) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_create: non-positive size in config");
-    if (c.hc != 0) PB_FAIL(ctx, PB_UNSUPPORTED, "pb_model_create: hyper-connection streams (hc=%d) are not built yet; use hc=0 (pre-norm residual)", c.hc);
+    if (c.hc < 0 || c.hc > 16 || (c.hc > 0 && c.hc_lr <= 0)) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_create: hc=%d streams with low rank %d", c.hc, c.hc_lr);
     if (c.top_k > PB_MAX_TOPK || c.top_k > c.n_exp) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_create: top_k=%d with %d experts", c.top_k, c.n_exp);
     if (c.kv_bits != 0 && c.kv_bits != 4) PB_FAIL(ctx, PB_UNSUPPORTED, "pb_model_create: kv_bits=%d (0 and 4 are built)", c.kv_bits);
     if (c.kv_bits == 4 && c.kv_recent < 64) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_create: kv_recent must be at least 64");
@@ -177,6 +178,18 @@ static int need_mat(pb_model* m, int il, int role, int64_t rows, int64_t cols, c
     if (quant_only && !pb_gemvq_supported(q->type, (int)q->cols)) PB_FAIL(ctx, PB_UNSUPPORTED, "layer %d: %s has ggml type %d / %lld columns, which the fused path does not cover", il, name, q->type, (long long)q->cols);
     return PB_OK;
 }
+static int need_vec(pb_model* m, int il, int role, int64_t n, const char* name);
+// the tensors of one hyper-connection mix (Hc, src/model/qwen4exp_gguf.rs:28, 492): f32 matrices only
+static int need_hc(pb_model* m, int il, int r_norm, int r_down, int r_up, int r_inj, const char* name) {
+    pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg; const int64_t w = (int64_t)c.hc * c.d;
+    PB_TRY(need_vec(m, il, r_norm, w, name));
+    PB_TRY(need_mat(m, il, r_down, c.hc_lr, w, name, false));
+    PB_TRY(need_mat(m, il, r_up, w, c.hc_lr, name, false));
+    if (r_inj >= 0) PB_TRY(need_mat(m, il, r_inj, c.hc, w, name, false));
+    const int roles[3] = {r_down, r_up, r_inj};
+    for (int i = 0; i < 3; i++) if (roles[i] >= 0 && M(m, il, roles[i])->type != PB_T_F32) PB_FAIL(ctx, PB_UNSUPPORTED, "layer %d: %s matrices must be f32 (ggml type %d given)", il, name, M(m, il, roles[i])->type);
+    return PB_OK;
+}
 static int need_vec(pb_model* m, int il, int role, int64_t n, const char* name) {
     pb_ctx* ctx = m->ctx;
     if (!V(m, il, role)) PB_FAIL(ctx, PB_ERR_STATE, "layer %d: vector %s is missing", il, name);
@@ -199,11 +212,17 @@ int pb_model_finalize(pb_model* m, int ep_rank, int ep_world) {
     if (!M(m, -1, PB_R_OUTPUT)) { /* falls back to token_embd (:511) */ }
     else PB_TRY(need_mat(m, -1, PB_R_OUTPUT, c.vocab, c.d, "output", true));
     if (!pb_gemvq_supported((M(m, -1, PB_R_OUTPUT) ? M(m, -1, PB_R_OUTPUT) : M(m, -1, PB_R_TOKEN_EMBD))->type, c.d)) PB_FAIL(ctx, PB_UNSUPPORTED, "lm-head type is not covered by the fused path");
-    PB_TRY(need_vec(m, -1, PB_R_OUT_NORM, c.d, "output_norm"));
+    if (c.hc == 0) PB_TRY(need_vec(m, -1, PB_R_OUT_NORM, c.d, "output_norm"));
+    else PB_TRY(need_hc(m, -1, PB_R_OUT_HC_NORM, PB_R_OUT_HC_DOWN, PB_R_OUT_HC_UP, -1, "output_hc"));
     wb += (M(m, -1, PB_R_OUTPUT) ? M(m, -1, PB_R_OUTPUT) : M(m, -1, PB_R_TOKEN_EMBD))->nbytes;
     for (int il = 0; il < c.n_layers; il++) {
-        PB_TRY(need_vec(m, il, PB_R_ATTN_NORM, c.d, "attn_norm"));
-        PB_TRY(need_vec(m, il, PB_R_FFN_NORM, c.d, "ffn_norm"));
+        if (c.hc == 0) {
+            PB_TRY(need_vec(m, il, PB_R_ATTN_NORM, c.d, "attn_norm"));
+            PB_TRY(need_vec(m, il, PB_R_FFN_NORM, c.d, "ffn_norm"));
+        } else {
+            PB_TRY(need_hc(m, il, PB_R_HCA_NORM, PB_R_HCA_DOWN, PB_R_HCA_UP, PB_R_HCA_INJECT, "hc_attn"));
+            PB_TRY(need_hc(m, il, PB_R_HCF_NORM, PB_R_HCF_DOWN, PB_R_HCF_UP, PB_R_HCF_INJECT, "hc_ffn"));
+        }
         if (m->kind[il]) {
             PB_TRY(need_mat(m, il, PB_R_ATTN_Q, (int64_t)c.n_head * 2 * c.hd, c.d, "attn_q", true));
             PB_TRY(need_mat(m, il, PB_R_ATTN_K, row, c.d, "attn_k", true));
@@ -307,7 +326,9 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
 #define A(p, n) if (rc == PB_OK) rc = dalloc(s, &s->p, (size_t)(n))
     A(pos, B); A(ids, Ba); A(next, Ba); A(amax, Ba); A(wpos, PB_PREFILL_CHUNK);
     A(ticket, 8 + (size_t)(Bm + 7) / 8);   // whole-launch counters, then one per group of 8 tokens of the router
-    A(x, (size_t)Ba * c.d); A(xin, (size_t)Ba * (wide > c.d ? wide : c.d)); A(yout, (size_t)Ba * c.d);
+    A(x, (size_t)Ba * c.d * (c.hc > 0 ? c.hc : 1));
+    if (c.hc > 0) { A(hxn, (size_t)Ba * c.hc * c.d); A(hgate, (size_t)Ba * c.hc * c.d); A(hlo, (size_t)Ba * c.hc_lr); A(hinj, (size_t)Ba * c.hc); A(hmix, (size_t)Ba * c.d); }
+    A(xin, (size_t)Ba * (wide > c.d ? wide : c.d)); A(yout, (size_t)Ba * c.d);
     A(proj, (size_t)Ba * s->ldproj); A(olin, (size_t)Ba * wide); A(att, (size_t)Ba * wide);
     A(rlogits, (size_t)Bm * (c.n_exp + 1));
     A(xq, (size_t)Bm * pb_xq_words(c.d));
@@ -798,6 +819,36 @@ static int run_step_fused(pb_state* s) {
     return pb_launch_advance(ctx, s->pos, 1, s->amax, s->next, s->ids, s->trace, s->trace_len, s->trace_cap);
 }
 
+// ---- hyper-connection residual (hc >= 1): forward_inner :2087-2157 with hc_mix / hc_combine around every block ----
+static void hc_params(pb_state* s, int il, int r_norm, int r_down, int r_up, int r_inj, PbHcParams& h) {
+    pb_model* m = s->m; const pb_cfg& c = m->cfg;
+    memset(&h, 0, sizeof h);
+    h.norm = V(m, il, r_norm); h.down = reinterpret_cast<const float*>(M(m, il, r_down)->data); h.up = reinterpret_cast<const float*>(M(m, il, r_up)->data);
+    h.inject = r_inj >= 0 ? reinterpret_cast<const float*>(M(m, il, r_inj)->data) : nullptr;
+    h.d = c.d; h.hc = c.hc; h.lr = c.hc_lr; h.eps = c.eps; h.xn = s->hxn; h.gate = s->hgate; h.lo = s->hlo; h.inj = s->hinj;
+}
+// all layers on t rows of the residual s->x [t][hc*d]; then the head's mix of rows [h0, h0 + hn) into s->hmix [hn][d]
+static int run_layers_hc(pb_state* s, int t, int h0, int hn) {
+    pb_model* m = s->m; pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg;
+    pb_qmat* embd = M(m, -1, PB_R_TOKEN_EMBD);
+    PB_TRY(pb_launch_embed(ctx, embd->type, embd->data, embd->rows, c.d, s->ids, t, s->yout, c.d));
+    PB_TRY(pb_launch_hc_spread(ctx, s->yout, s->x, t, c.d, c.hc));
+    PbHcParams h;
+    for (int il = 0; il < c.n_layers; il++) {
+        hc_params(s, il, PB_R_HCA_NORM, PB_R_HCA_DOWN, PB_R_HCA_UP, PB_R_HCA_INJECT, h);
+        PB_TRY(pb_launch_hc_mix(ctx, h, s->x, t, s->hmix));
+        if (m->kind[il]) PB_TRY(run_attn(s, il, s->hmix, nullptr, s->yout, c.d, 0));
+        else PB_TRY(run_lin(s, il, s->hmix, nullptr, s->yout, c.d, 0));
+        PB_TRY(pb_launch_hc_combine(ctx, h, s->x, s->yout, t));
+        hc_params(s, il, PB_R_HCF_NORM, PB_R_HCF_DOWN, PB_R_HCF_UP, PB_R_HCF_INJECT, h);
+        PB_TRY(pb_launch_hc_mix(ctx, h, s->x, t, s->hmix));
+        PB_TRY(run_moe(s, il, s->hmix, nullptr, t, s->yout, c.d, 0));
+        PB_TRY(pb_launch_hc_combine(ctx, h, s->x, s->yout, t));
+    }
+    hc_params(s, -1, PB_R_OUT_HC_NORM, PB_R_OUT_HC_DOWN, PB_R_OUT_HC_UP, -1, h);   // :2152
+    return pb_launch_hc_mix(ctx, h, s->x + (size_t)h0 * c.hc * c.d, hn, s->hmix);
+}
+
 // one decode step for every sequence of the batch, ids already in s->ids
 static int run_step(pb_state* s) {
     pb_model* m = s->m; pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg; const int B = s->batch;
@@ -805,16 +856,20 @@ static int run_step(pb_state* s) {
     if (s->fused == 1) return run_step_fused(s);
     struct Scope { pb_ctx* c; Scope(pb_ctx* x) : c(x) { c->pdl_scope++; c->pdl_chain = false; } ~Scope() { c->pdl_scope--; c->pdl_chain = false; } } scope(ctx);
     pb_qmat* embd = M(m, -1, PB_R_TOKEN_EMBD);
-    PB_TRY(pb_launch_embed(ctx, embd->type, embd->data, embd->rows, c.d, s->ids, B, s->x, c.d));
-    for (int il = 0; il < c.n_layers; il++) {
-        if (m->kind[il]) PB_TRY(run_attn(s, il, s->x, V(m, il, PB_R_ATTN_NORM), s->x, c.d, 1));
-        else PB_TRY(run_lin(s, il, s->x, V(m, il, PB_R_ATTN_NORM), s->x, c.d, 1));
-        PB_TRY(run_moe(s, il, s->x, V(m, il, PB_R_FFN_NORM), B, s->x, c.d, 1));
+    if (c.hc > 0) PB_TRY(run_layers_hc(s, B, 0, B));
+    else {
+        PB_TRY(pb_launch_embed(ctx, embd->type, embd->data, embd->rows, c.d, s->ids, B, s->x, c.d));
+        for (int il = 0; il < c.n_layers; il++) {
+            if (m->kind[il]) PB_TRY(run_attn(s, il, s->x, V(m, il, PB_R_ATTN_NORM), s->x, c.d, 1));
+            else PB_TRY(run_lin(s, il, s->x, V(m, il, PB_R_ATTN_NORM), s->x, c.d, 1));
+            PB_TRY(run_moe(s, il, s->x, V(m, il, PB_R_FFN_NORM), B, s->x, c.d, 1));
+        }
     }
     pb_qmat* out = M(m, -1, PB_R_OUTPUT) ? M(m, -1, PB_R_OUTPUT) : embd;
     PbGemvQArgs a; memset(&a, 0, sizeof a);
     a.type = out->type; a.cols = c.d; a.nseg = 1; seg(a, 0, out, 0);
     a.x = s->x; a.ldx = c.d; a.y = s->logits; a.ldy = c.vocab; a.mode = PB_ACT_NORM; a.norm_w = V(m, -1, PB_R_OUT_NORM); a.eps = c.eps;
+    if (c.hc > 0) { a.x = s->hmix; a.mode = PB_ACT_PLAIN; a.norm_w = nullptr; }   // the head's mix already normalized the streams
     PB_TRY(gemv_cols(ctx, a, B));
     PB_TRY(pb_launch_argmax(ctx, s->logits, c.vocab, c.vocab, B, s->amax));
     return pb_launch_advance(ctx, s->pos, B, s->amax, s->next, s->ids, s->trace, s->trace_len, s->trace_cap, s->p2p ? s->ep_seq : nullptr, 2ull * c.n_layers);
@@ -831,16 +886,20 @@ static int run_window(pb_state* s, int t, bool ckpt, bool all_logits) {
                    ~Scope() { c->pdl_scope--; c->pdl_chain = false; s->win_t = 0; s->win_ckpt = false; } } scope(ctx, s, t, ckpt);
     PB_TRY(pb_launch_window_pos(ctx, s->pos, s->wpos, t, 0));
     pb_qmat* embd = M(m, -1, PB_R_TOKEN_EMBD);
-    PB_TRY(pb_launch_embed(ctx, embd->type, embd->data, embd->rows, c.d, s->ids, t, s->x, c.d));
-    for (int il = 0; il < c.n_layers; il++) {
-        if (m->kind[il]) PB_TRY(run_attn(s, il, s->x, V(m, il, PB_R_ATTN_NORM), s->x, c.d, 1));
-        else PB_TRY(run_lin(s, il, s->x, V(m, il, PB_R_ATTN_NORM), s->x, c.d, 1));
-        PB_TRY(run_moe(s, il, s->x, V(m, il, PB_R_FFN_NORM), t, s->x, c.d, 1));
+    if (c.hc > 0) PB_TRY(run_layers_hc(s, t, all_logits ? 0 : t - 1, all_logits ? t : 1));
+    else {
+        PB_TRY(pb_launch_embed(ctx, embd->type, embd->data, embd->rows, c.d, s->ids, t, s->x, c.d));
+        for (int il = 0; il < c.n_layers; il++) {
+            if (m->kind[il]) PB_TRY(run_attn(s, il, s->x, V(m, il, PB_R_ATTN_NORM), s->x, c.d, 1));
+            else PB_TRY(run_lin(s, il, s->x, V(m, il, PB_R_ATTN_NORM), s->x, c.d, 1));
+            PB_TRY(run_moe(s, il, s->x, V(m, il, PB_R_FFN_NORM), t, s->x, c.d, 1));
+        }
     }
     pb_qmat* out = M(m, -1, PB_R_OUTPUT) ? M(m, -1, PB_R_OUTPUT) : embd;
     PbGemvQArgs a; memset(&a, 0, sizeof a);
     a.type = out->type; a.cols = c.d; a.nseg = 1; seg(a, 0, out, 0);
     a.x = all_logits ? s->x : s->x + (size_t)(t - 1) * c.d; a.ldx = c.d; a.y = s->logits; a.ldy = c.vocab; a.mode = PB_ACT_NORM; a.norm_w = V(m, -1, PB_R_OUT_NORM); a.eps = c.eps;
+    if (c.hc > 0) { a.x = s->hmix; a.mode = PB_ACT_PLAIN; a.norm_w = nullptr; }   // rows [0, hn) of the head's mix
     PB_TRY(gemv_cols(ctx, a, all_logits ? t : 1));
     return pb_launch_window_pos(ctx, s->pos, s->wpos, t, 1);   // position += t
 }

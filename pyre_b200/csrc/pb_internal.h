@@ -306,6 +306,16 @@ int pb_launch_kv4_pack(pb_ctx* ctx, const float* x, int64_t n, uint32_t* w, floa
 int pb_launch_kv4_pack_vt(pb_ctx* ctx, const float* x, int64_t npos, int hd, uint32_t* w, float* sc, int bias);   // position-transposed V words
 int pb_launch_kv4_unpack(pb_ctx* ctx, const uint32_t* w, const float* sc, int64_t n, float* x);
 
+// ---------------------------------------------------------------- pb_hc.cu
+struct PbHcParams {
+    const float *norm, *down, *up, *inject;   // [hc*d], [lr][hc*d], [hc*d][lr], [hc][hc*d] or null
+    int d, hc, lr; float eps;
+    float *xn, *gate, *lo, *inj;               // work rows per token: [hc*d], [hc*d], [lr], [hc]
+};
+int pb_launch_hc_mix(pb_ctx* ctx, const PbHcParams& p, const float* x, int t, float* mixed);      // x [t][hc*d] -> mixed [t][d], p.inj [t][hc]
+int pb_launch_hc_combine(pb_ctx* ctx, const PbHcParams& p, float* x, const float* out, int t);   // x [t][hc*d] += out [t][d] * 2 sigmoid(p.inj)
+int pb_launch_hc_spread(pb_ctx* ctx, const float* e, float* x, int t, int d, int hc);
+
 // ---------------------------------------------------------------- pb_misc.cu
 int pb_launch_embed(pb_ctx* ctx, int type, const uint8_t* w, int64_t rows, int cols, const uint32_t* ids, int t, float* out, int64_t ldo);
 int pb_launch_argmax(pb_ctx* ctx, const float* logits, int64_t ld, int n, int t, unsigned long long* keys);

@@ -41,12 +41,29 @@ def model_spec(cfg: Cfg, seed: int = 0, qtype: int = IQ3_S):
     def gamma(n):  # norm weights, stored pre-folded as (1 + w) like the reference's GGUF
         return 1.0 + 0.1 * rng.standard_normal(n)
 
+    hc, lr = cfg.hc, cfg.hc_lr
+
+    def hyper(layer, prefix, inject=True):
+        # one hyper-connection mix (Hc, src/model/qwen4exp_gguf.rs:28, 492): per-stream norm weights and small f32 matrices
+        vec(layer, f"{prefix}_NORM", gamma(hc * d))
+        mat(layer, f"{prefix}_DOWN", lr, hc * d, F32)
+        mat(layer, f"{prefix}_UP", hc * d, lr, F32)
+        if inject:
+            mat(layer, f"{prefix}_INJECT", hc, hc * d, F32)
+
     mat(-1, "TOKEN_EMBD", cfg.vocab, d)
     mat(-1, "OUTPUT", cfg.vocab, d)
-    vec(-1, "OUT_NORM", gamma(d))
+    if hc > 0:
+        hyper(-1, "OUT_HC", inject=False)
+    else:
+        vec(-1, "OUT_NORM", gamma(d))
     for il in range(cfg.n_layers):
-        vec(il, "ATTN_NORM", gamma(d))
-        vec(il, "FFN_NORM", gamma(d))
+        if hc > 0:
+            hyper(il, "HCA")
+            hyper(il, "HCF")
+        else:
+            vec(il, "ATTN_NORM", gamma(d))
+            vec(il, "FFN_NORM", gamma(d))
         if is_full(cfg, il):
             mat(il, "ATTN_Q", cfg.n_head * 2 * hd, d)
             mat(il, "ATTN_K", cfg.n_kv * hd, d)

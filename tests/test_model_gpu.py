@@ -292,3 +292,38 @@ def test_fused_step_greedy_identity_vs_oracle(ctx):
         assert tok == otok, (i, ost.margins())
     assert ctx.device_status() == 0
     st.destroy(); m.destroy()
+
+
+@pytest.mark.parametrize("hc", [1, 2])
+def test_hyper_connection_greedy_identity_vs_oracle(ctx, hc):
+    """The reference's own residual form: hc parallel streams mixed before every block and recombined after it
+    (hc_mix / hc_combine, src/model/qwen4exp_gguf.rs:1357-1388), low rank 32.  Prompt logits and 64 greedy tokens
+    against the CPU oracle; the verify window and the batched form agree with the token loop."""
+    cfg = small_cfg(pb, n_layers=8, kv_bits=4, kv_recent=64, max_ctx=256, hc=hc, hc_lr=32)
+    spec = synth.model_spec(cfg, 31)
+    m = synth.build_model(ctx, cfg, spec, 31)
+    om, _ = oracle_model(cfg, spec, 31)
+    st, ost = m.new_state(1), om.new_state()
+    prompt = [3, 999, 27, 500, 1]
+    lg, lo = st.forward(np.array(prompt, np.uint32))[0], ost.forward(prompt)
+    assert rel_err(lg, lo) < 1e-3
+    assert int(lg.argmax()) == oracle.argmax(lo)
+    a, b, margins = _greedy_pair(st, ost, int(lg.argmax()), 64)
+    assert a == b, f"diverged at step {next(i for i in range(64) if a[i] != b[i])}; oracle margins there {margins}"
+    # two sequences in one batch: each equals its own single-sequence run
+    s2 = m.new_state(2)
+    t2 = s2.decode_greedy([5, 600], 12)
+    for i, first in enumerate([5, 600]):
+        s1 = m.new_state(1)
+        assert s1.decode_greedy([first], 12)[0].tolist() == t2[i].tolist()
+        s1.destroy()
+    # a verify window: per-position logits against the oracle's token loop
+    w = m.new_state(1); ow = om.new_state()
+    win = np.array([7, 8, 9, 10, 11], np.uint32)
+    lw = w.forward_multi(win)
+    for j, tok in enumerate(win):
+        assert rel_err(lw[j], ow.forward([int(tok)])) < 1e-3
+    assert ctx.device_status() == 0
+    for x in (st, s2, w):
+        x.destroy()
+    m.destroy()
