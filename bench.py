@@ -325,7 +325,7 @@ def run_ours(args):
         step_bytes = stats.weight_bytes_per_step + stats.kv_bytes_per_step + stats.state_bytes_per_step
         peak, which = measured_peaks()
         line = {"metric": "decode_tok_per_s", "value": round(value, 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-                "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "weak" if (args.replicas or sharded or world == 1) else "strong", "vs_baseline": None, "dtype": "int8 (dp4a: decoded weights x int8-split activations) at batch 1, f16 mma.sync with f16 hi/lo activations for 3+ tokens and attention; f32 accumulate",
+                "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "weak" if (args.replicas or sharded or world == 1) else "strong", "vs_baseline": None, "dtype": "int8 (dp4a: decoded weights x int8-split activations) at batch 1, f16 tensor cores (mma.sync with f16 hi/lo activations for 3-15 tokens and attention, tcgen05 for prefill chunks); f32 accumulate",
                 "data": "synthetic", "config": workload_config(B, world, args.replicas, args.replicated_ep),
                 "e2e": {"value": round(e2e_v, 2), "unit": "tok/s", "h2d_bytes_per_step": 4 * B * mult, "d2h_bytes_per_step": 4 * B * cfg.vocab * mult, "ms_per_step": round(ms_e2e / args.steps, 4)},
                 "gpu_launches": int(stats.kernels_launched) * args.steps,
@@ -350,6 +350,34 @@ def run_ours(args):
         verify = {"window": 8, "ms": round(vms, 3), "ms_per_token": round(vms / 8, 3), "note": "pb_verify + pb_keep, host ids in, 8 x vocab logits out, wall clock"}
         if rank == 0:
             line["verify"] = verify
+    # ---- prompt prefill: a 4096-token prompt through pb_forward (256-token chunks on the absolute grid, tcgen05 GEMM for the
+    #      dense projections), from an empty context; host ids in, last-position logits out
+    if world == 1 and B == 1 and not args.no_bs32:
+        pst = model.new_state(1)
+        prompt = (np.arange(4096, dtype=np.uint32) * 7919 + 13) % cfg.vocab
+        pst.forward(prompt[:512])                       # warm-up: the eager chunk and the captured one
+        pst.reset()
+        torch.cuda.synchronize(); t0 = time.time()
+        pst.forward(prompt)
+        torch.cuda.synchronize()
+        pms = (time.time() - t0) * 1e3
+        pst.destroy()
+        if rank == 0:
+            line["prefill"] = {"prompt_tokens": 4096, "ms": round(pms, 1), "tok_per_s": round(4096 / (pms / 1e3), 1), "chunk": 256,
+                               "note": "pb_forward on a 4096-token prompt from an empty 4-bit KV cache, wall clock including the id upload and the logits read-back"}
+    # ---- mixed-quant GEMV sweep (the benchmark's config 1): four formats x four shapes x batch 1 / 4 / 16, device-resident operands
+    if world == 1 and B == 1 and not args.no_bs32 and rank == 0:
+        from pyre_b200 import sweep
+        peak, _ = measured_peaks()
+        flush = torch.zeros(64 << 20, device="cuda")
+        rows_out = []
+        for tname in ("Q8_0", "Q4_K", "IQ2_XS", "IQ3_S"):
+            for (r, c_) in sweep.SHAPES:
+                for tt in (1, 4, 16):
+                    us, nb = sweep.time_case(pb, torch, ctx, stream, tname, r, c_, tt, 5, flush)
+                    rows_out.append({"type": tname, "rows": r, "cols": c_, "tokens": tt, "us": round(us, 2), "weight_gbs": round(nb / us / 1e3, 1), "frac": round(nb / us / 1e3 / peak, 3)})
+        del flush
+        line["gemv_sweep"] = {"unit": "weight bytes / launch time, GB/s; frac = of the measured copy bandwidth; small shapes are evicted from L2 between launches", "cases": rows_out}
     # ---- the batch-32 half of the headline metric: 32 sequences in all (32 / N per GPU when sharded)
     if B == 1 and not args.no_bs32 and (world == 1 or (sharded and 32 % world == 0)):
         st.destroy()

@@ -391,6 +391,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) pb_gemmtc_iq3s_kernel(const TcP
 
 bool pb_gemmtc_supported(int type, int cols, int t) { return type == PB_T_IQ3_S && t >= 16 && cols % 256 == 0 && cols >= 256; }
 
+// Fewest tokens the dispatchers send here.  The kernel works from 16 tokens on, but a CTA walks the whole contraction on
+// its own (about 30 us for 2048 columns whatever the token count), so below ~32 tokens the warp-level kernel, which cuts
+// the tokens into tiles of 16 over all SMs, is faster: measured 17 vs 36 us at 16 tokens and 42 vs 40 us at 64 tokens on
+// a 4096 x 2048 matrix.  PYRE_B200_TC_MIN overrides (tests run the kernel at 16).
+int pb_gemmtc_min_tokens() {
+    const char* e = getenv("PYRE_B200_TC_MIN");
+    const int v = e ? atoi(e) : 32;
+    return v < 16 ? 16 : v;
+}
+
 int pb_gemmtc_max_tokens(int cols) {
     const size_t n = (PB_XH_BYTES - TC_XT_HEAD) / ((size_t)cols * 4) / TC_NBLK * TC_NBLK;
     return (int)(n < TC_XT_HEAD / 4 ? n : TC_XT_HEAD / 4);

@@ -278,11 +278,11 @@ int pb_launch_gemvq(pb_ctx* ctx, const PbGemvQArgs& a) {
     int el, bs;
     if (pb_geom(a.type, &el, &bs) || !pb_gemvq_supported(a.type, a.cols)) PB_FAIL(ctx, PB_UNSUPPORTED, "gemvq: type %d cols %d not supported by the integer kernel", a.type, a.cols);
     if (!a.exact && a.mode != PB_ACT_PREQ && pb_gemmtc_supported(a.type, a.cols, a.t) && a.t <= pb_gemmtc_max_tokens(a.cols)) {
-        // 16 tokens and more: tcgen05 (PYRE_B200_TC=0 keeps the warp-level kernel below)
+        // tcgen05 from pb_gemmtc_min_tokens() tokens on (PYRE_B200_TC=0 keeps the warp-level kernel below)
         static const bool use_tc = !(getenv("PYRE_B200_TC") && atoi(getenv("PYRE_B200_TC")) == 0);
         bool all = true;
         for (int s = 0; s < a.nseg && s < 4; s++) all = all && a.seg[s].wr != nullptr;
-        if (use_tc && all) return pb_launch_gemmtc(ctx, a);
+        if (use_tc && all && a.t >= pb_gemmtc_min_tokens()) return pb_launch_gemmtc(ctx, a);
     }
     if (a.mode != PB_ACT_PREQ && pb_gemmh_supported(a.type, a.cols, a.t)) {
         static const bool use_mma = !(getenv("PYRE_B200_MMA") && atoi(getenv("PYRE_B200_MMA")) == 0);

@@ -206,6 +206,7 @@ int pb_launch_gemmh(pb_ctx* ctx, const PbGemvQArgs& a);
 // pb_gemmtc.cu: tcgen05 path for 16 and more columns of IQ3_S weights that have a re-coded copy
 bool pb_gemmtc_supported(int type, int cols, int t);
 int pb_launch_gemmtc(pb_ctx* ctx, const PbGemvQArgs& a);
+int pb_gemmtc_min_tokens();            // tokens from which the dispatchers prefer this kernel (measured crossover)
 int pb_gemmtc_max_tokens(int cols);   // tokens one launch accepts (operand buffer), a multiple of 128
 
 // ---------------------------------------------------------------- pb_moe.cu

@@ -174,13 +174,15 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
     __threadfence();
     pb_stamp(p.stamps, 6, tid == 0 && blockIdx.y == 0);   // the routing pass of the first group starts (its logits are in)
     pb_route_tokens(rp, b_lo, b_hi);
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) is_last = atomicAdd(ticket, 1u) == gridDim.y - 1;
-    __syncthreads();
-    if (!is_last) return;
-    if (tid == 0) *ticket = 0;
-    __threadfence();
+    if (gridDim.y > 1) {
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) is_last = atomicAdd(ticket, 1u) == gridDim.y - 1;
+        __syncthreads();
+        if (!is_last) return;
+        if (tid == 0) *ticket = 0;
+        __threadfence();
+    } else __syncthreads();   // one group: this CTA routed every token itself
     pb_route_lists(rp, reinterpret_cast<int*>(rs));
     __syncthreads();
     pb_stamp(p.stamps, 7, tid == 0);
