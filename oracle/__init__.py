@@ -149,6 +149,29 @@ class QMat:
         return y
 
 
+def q8_quantize(x: np.ndarray):
+    """quantize, src/model/qdot.rs:15-30: int8 values and one f32 scale per 32 values."""
+    x = _f32(x).reshape(-1)
+    q = np.empty(x.size, dtype=np.int8)
+    d = np.empty(x.size // 32, dtype=np.float32)
+    lib().orc_q8_quantize(_p(x), C.c_int64(x.size), _p(q), _p(d))
+    return q, d
+
+
+def q8_dot_dequant(t: int, row: np.ndarray, q: np.ndarray, d: np.ndarray) -> float:
+    row = np.ascontiguousarray(row, dtype=np.uint8)
+    f = lib().orc_q8_dot_dequant
+    f.restype = C.c_float
+    return float(f(C.c_int(t), _p(row), C.c_int64(q.size), _p(q), _p(d)))
+
+
+def row_dot_q8_iq3s(row: np.ndarray, q: np.ndarray, d: np.ndarray) -> float:
+    row = np.ascontiguousarray(row, dtype=np.uint8)
+    f = lib().orc_row_dot_q8_iq3s
+    f.restype = C.c_float
+    return float(f(_p(row), C.c_int64(q.size), _p(q), _p(d)))
+
+
 def top_k(r: np.ndarray, k: int):
     r = _f32(r)
     idx = np.empty(k, dtype=np.int32)

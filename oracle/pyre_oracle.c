@@ -234,6 +234,56 @@ void orc_synth_normal(uint64_t seed, uint64_t tid, int64_t i0, int64_t n, float 
 
 /* ------------------------------------------------------------------ QMat */
 
+/* ---- the reference's int8 CPU fast path (src/model/qdot.rs): activations quantized to int8 per 32 values, the row's
+ * block integers dotted with them in integers.  The GPU path does not use it (it keeps three int8 levels, 21 bits);
+ * it is restated so that the oracle covers the approximation the reference's CPU decode really runs. ---- */
+/* quantize_into, qdot.rs:20-30: per 32 values d = amax / 127, q = round(x / d) (round half away from zero) */
+void orc_q8_quantize(const float* x, int64_t n, int8_t* q, float* d) {
+    for (int64_t b = 0; b < n / 32; b++) {
+        const float* xb = x + b * 32; float amax = 0.0f;
+        for (int j = 0; j < 32; j++) { float a = fabsf(xb[j]); if (a > amax) amax = a; }
+        float dd = amax / 127.0f, id = dd > 0.0f ? 1.0f / dd : 0.0f;
+        d[b] = dd;
+        for (int j = 0; j < 32; j++) q[b * 32 + j] = (int8_t)roundf(xb[j] * id);
+    }
+}
+/* the expected value of the reference's own test (q8_dot, qdot.rs:1046-1052): dequantized row times the int8
+ * activations, one f32 sum per 32 values scaled by the activation block scale; any block format */
+float orc_q8_dot_dequant(int type, const uint8_t* row, int64_t n, const int8_t* q, const float* d) {
+    float* y = (float*)malloc((size_t)n * 4); float acc = 0.0f;
+    orc_dequant(type, row, n, y);
+    for (int64_t b = 0; b < n / 32; b++) { float s = 0.0f; for (int j = 0; j < 32; j++) s += y[b * 32 + j] * (float)q[b * 32 + j]; acc += s * d[b]; }
+    free(y);
+    return acc;
+}
+/* row_dot for IQ3_S, scalar structure of qdot.rs:278-286 (the AVX2 kernel iq3s_avx2 :169 computes the same integers):
+ * per 32 values an exact integer sum of sign * grid byte * q, scaled by d * (1 + 2 * nibble) and the activation scale */
+float orc_row_dot_q8_iq3s(const uint8_t* row, int64_t n, const int8_t* q, const float* d) {
+    float acc = 0.0f;
+    for (int64_t i = 0; i < n / 256; i++) {
+        const uint8_t* b = row + i * 110; uint16_t hb; memcpy(&hb, b, 2); float dblk = h2f(hb);
+        const uint8_t* qs = b + 2; const uint8_t* qh = b + 66; const uint8_t* sg = b + 74; const uint8_t* scb = b + 106;
+        for (int ib = 0; ib < 8; ib++) {
+            int nib = (ib & 1) ? scb[ib / 2] >> 4 : scb[ib / 2] & 0xF;
+            float db = dblk * (float)(1 + 2 * nib);
+            int32_t isum = 0;
+            for (int l = 0; l < 4; l++) {
+                uint32_t g1 = PB_IQ3S_GRID[qs[8 * ib + 2 * l] | (((uint32_t)qh[ib] << (8 - 2 * l)) & 256)];
+                uint32_t g2 = PB_IQ3S_GRID[qs[8 * ib + 2 * l + 1] | (((uint32_t)qh[ib] << (7 - 2 * l)) & 256)];
+                uint8_t sb = sg[4 * ib + l];
+                for (int j = 0; j < 4; j++) {
+                    int w1 = (int)((g1 >> (8 * j)) & 0xFF), w2 = (int)((g2 >> (8 * j)) & 0xFF);
+                    if (sb & (1 << j)) w1 = -w1;
+                    if (sb & (1 << (4 + j))) w2 = -w2;
+                    isum += w1 * (int)q[i * 256 + ib * 32 + 8 * l + j] + w2 * (int)q[i * 256 + ib * 32 + 8 * l + 4 + j];
+                }
+            }
+            acc += (float)isum * db * d[i * 8 + ib];
+        }
+    }
+    return acc;
+}
+
 void orc_mat_row_raw(const orc_mat* m, int64_t r, uint8_t* out) {
     int64_t rb = orc_row_bytes(m->type, m->cols);
     if (m->data) memcpy(out, m->data + r * rb, (size_t)rb);

@@ -44,6 +44,10 @@ float orc_dot(const float* a, const float* b, int64_t n);      /* dot_avx2 :176-
 void orc_mat_row_raw(const orc_mat* m, int64_t r, uint8_t* out);
 void orc_mat_row(const orc_mat* m, int64_t r, float* y);       /* QMat::row :210 */
 void orc_matmul(const orc_mat* m, const float* x, int t, float* y);  /* QMat::matmul :217-242 (t<16 branch) */
+/* the reference's int8 CPU fast path, qdot.rs:15-30 (quantize), :278-286 (IQ3_S row_dot), :1046-1052 (its test's expected value) */
+void orc_q8_quantize(const float* x, int64_t n, int8_t* q, float* d);
+float orc_q8_dot_dequant(int type, const uint8_t* row, int64_t n, const int8_t* q, const float* d);
+float orc_row_dot_q8_iq3s(const uint8_t* row, int64_t n, const int8_t* q, const float* d);
 int orc_threads(void);
 void orc_set_threads(int n);   /* threads of the row-parallel loops from now on */
 

@@ -5,6 +5,7 @@ import numpy as np
 import pytest
 
 import oracle
+from conftest import rel_err
 
 GOLD = Path(__file__).resolve().parent / "golden"
 
@@ -116,3 +117,82 @@ def test_rope_inv():
     inv = oracle.rope_inv(64, 1e7)
     assert inv.shape == (32,) and inv[0] == 1.0
     assert np.allclose(inv, 1e7 ** (-(2.0 * np.arange(32)) / 64), rtol=1e-5)
+
+
+def _qdot_test_block(n: int) -> np.ndarray:
+    """The row the reference's own test builds (block, src/model/qdot.rs:1033-1045): bytes from a 64-bit LCG seeded with
+    0xC0FFEE ^ n, then a sane f16 scale written over the first two bytes of each of the two 110-byte rows."""
+    seed = 0xC0FFEE ^ n
+    nbytes = 110 * 2          # row_bytes(256) for IQ3_S, twice
+    v = np.zeros(nbytes, dtype=np.uint8)
+    s = seed
+    for i in range(nbytes):
+        s = (s * 6364136223846793005 + 1) % (1 << 64)
+        v[i] = (s >> 33) & 0xFF
+    d = np.float16(0.05 + (seed % 17) * 0.01)
+    v[0:2] = np.frombuffer(d.tobytes(), dtype=np.uint8)
+    v[110:112] = np.frombuffer(d.tobytes(), dtype=np.uint8)
+    return v
+
+
+def test_int8_row_dot_by_the_references_own_test_method():
+    """check(QType::IQ3S, 512), src/model/qdot.rs:1053-1070: the int8 row dot against the dequantized row times the same
+    int8 activations, relative error below 2e-3 -- same block generator, same activation pattern, same bound."""
+    n = 512
+    row = _qdot_test_block(n)
+    x = np.array([((i * 17 + 3) % 11) / 5.0 - 1.0 for i in range(n)], dtype=np.float32)
+    q, d = oracle.q8_quantize(x)
+    assert q.dtype == np.int8 and int(np.abs(q).max()) == 127 and d.shape == (16,)
+    got = oracle.row_dot_q8_iq3s(row, q, d)
+    exp = oracle.q8_dot_dequant(oracle.IQ3_S, row, q, d)
+    assert abs(got - exp) / max(abs(exp), 1e-3) < 2e-3
+    # the int8 activations reproduce x within half a step, and the approximation is close to the f32 product
+    assert np.abs(q.astype(np.float32) * np.repeat(d, 32) - x).max() <= d.max() * 0.5 + 1e-7
+    f32 = float(oracle.QMat(oracle.IQ3_S, 1, n, row).matmul(x[None])[0, 0])
+    assert abs(got - f32) / max(abs(f32), 1e-3) < 2e-2
+    # seeded synthetic rows of the benchmark's generator too
+    Wo = oracle.QMat.synth(oracle.IQ3_S, 4, 2048, 0, 42)
+    xx = np.random.default_rng(1).standard_normal(2048).astype(np.float32)
+    qq, dd = oracle.q8_quantize(xx)
+    raw = Wo.raw().reshape(4, -1)
+    for r in range(4):
+        a, b = oracle.row_dot_q8_iq3s(raw[r], qq, dd), oracle.q8_dot_dequant(oracle.IQ3_S, raw[r], qq, dd)
+        assert abs(a - b) / max(abs(b), 1e-3) < 2e-3
+
+
+def test_gated_deltanet_against_transformers_qwen3_next_vectors():
+    """The oracle's linear_core against vectors computed with Hugging Face transformers' Qwen3-Next code (conv + SiLU,
+    L2 norms, gates, torch_recurrent_gated_delta_rule); tests/golden/make_hf_deltanet_golden.py lines up the two places
+    where the reference's model family differs (head map, output gate).  Readout compared after the same weight-1 RMS
+    norm with the gate saturated to 1; the final recurrent state directly."""
+    g = np.load(Path(__file__).resolve().parent / "golden" / "hf_gated_deltanet.npz")
+    nk, nv, dk, dv, K, t = (int(g[k]) for k in ("nk", "nv", "dk", "dv", "conv_k", "t"))
+    cfg = oracle.Cfg()
+    cfg.lin_nk, cfg.lin_nv, cfg.lin_dk, cfg.lin_dv, cfg.conv_k, cfg.eps = nk, nv, dk, dv, K, 1e-6
+    ch = 2 * nk * dk + nv * dv
+    conv_state = np.zeros((K - 1, ch), np.float32)
+    ssm = np.zeros((nv, dk, dv), np.float32)
+    z = np.full((t, nv * dv), 30.0, np.float32)                      # sigmoid(30) == 1.0f
+    out = oracle.linear_core(cfg, g["qkv"], z, g["beta_raw"], g["alpha_raw"], g["ssm_a"], g["dt_bias"], g["conv_w"],
+                             np.ones(dv, np.float32), conv_state, ssm)
+    ref = g["readout"].astype(np.float64)                            # [t][nv][dv], before any norm
+    ref = ref / np.sqrt((ref ** 2).mean(axis=-1, keepdims=True) + 1e-6)
+    assert rel_err(out.reshape(t, nv, dv), ref) < 1e-5
+    assert rel_err(ssm, g["state"]) < 1e-5
+    assert np.array_equal(conv_state, g["qkv"][t - (K - 1):])        # the history holds the last K-1 raw inputs
+
+
+def test_gated_attention_against_transformers_qwen3_next_vectors():
+    """The oracle's attn_core (f32 KV) token by token against vectors computed with Hugging Face transformers' Qwen3-Next
+    code: zero-centred q / k RMS norms, partial rotary embedding, grouped-query causal softmax attention, sigmoid gate
+    (tests/golden/make_hf_attention_golden.py)."""
+    g = np.load(Path(__file__).resolve().parent / "golden" / "hf_gated_attention.npz")
+    cfg = oracle.Cfg()
+    cfg.n_head, cfg.n_kv, cfg.hd, cfg.n_rot, cfg.eps = int(g["n_head"]), int(g["n_kv"]), int(g["hd"]), int(g["n_rot"]), float(g["eps"])
+    cfg.kv_bits, cfg.kv_recent, cfg.max_ctx = 0, 1024, 64
+    t = int(g["t"]); row = cfg.n_kv * cfg.hd
+    inv = oracle.rope_inv(cfg.n_rot, float(g["rope_base"]))
+    kc = np.zeros((t, row), np.float32); vc = np.zeros((t, row), np.float32)
+    for pos in range(t):
+        att = oracle.attn_core(cfg, g["qf"][pos], g["kf"][pos], g["vf"][pos], g["q_norm"], g["k_norm"], inv, kc, vc, pos)
+        assert rel_err(att, g["att"][pos]) < 2e-5, pos
