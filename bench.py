@@ -437,7 +437,10 @@ def run_ours(args):
         full = synth.build_model(ctx, cfg, spec, SEED, 0, 1)
         ms_rep, _ = timed_decode(full, False, vsteps)
         full.destroy()
-        # greedy ids of sharded decoding against one GPU stepping the whole batch (8 layers of the same shapes, 32 tokens)
+        # greedy ids of sharded decoding against one GPU holding all experts (8 layers of the same shapes, 32 tokens).  The
+        # single-GPU run steps every sequence in a state of the same batch size as a rank's share (here 1): the dense
+        # kernels are chosen by batch size (dp4a for 1-2 tokens, tensor cores above; attention splits by sequences per GPU),
+        # and results are bit-identical only between runs that use the same ones.  What the flag checks is the exchange.
         cfg_s = full_cfg(pb, batch_room=64, n_layers=8)
         spec_s = synth.model_spec(cfg_s, SEED + 2)
         m_s = synth.build_model(ctx, cfg_s, spec_s, SEED + 2, rank, world)
@@ -448,9 +451,13 @@ def run_ours(args):
         dist.all_gather(got, mine)
         if rank == 0:
             m_1 = synth.build_model(ctx, cfg_s, spec_s, SEED + 2, 0, 1)
-            s_1 = m_1.new_state(world)
-            want = s_1.decode_greedy(np.arange(world, dtype=np.uint32) + 1, 32).astype(np.int64)
-            s_1.destroy(); m_1.destroy()
+            want = []
+            for r_ in range(world):
+                s_1 = m_1.new_state(1)
+                want.append(s_1.decode_greedy(np.array([1 + r_], np.uint32), 32).astype(np.int64))
+                s_1.destroy()
+            want = np.concatenate(want)
+            m_1.destroy()
             line["ep_tokens_identical"] = bool(np.array_equal(torch.cat(got).cpu().numpy(), want))
             per = lambda ms_: {"tok_per_s": round(B * world * vsteps / (ms_ / 1e3), 2), "ms_per_step": round(ms_ / vsteps, 4)}
             line["exchange"] = {"steps": vsteps, "p2p": {**per(ms_p2p), "handshake_ms_per_step": round(xns / 1e6 / (vsteps + 3), 4)}, "nccl": per(ms_nccl), "replicas": per(ms_rep),

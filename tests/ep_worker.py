@@ -129,9 +129,15 @@ def gpu_sharded_tokens(rank, world, port, out_dir):
     if rank == 0:
         ctx1 = pb.Ctx(0)
         m1 = synth.build_model(ctx1, cfg, spec, 3)
-        s1 = m1.new_state(2 * world)
-        np.save(Path(out_dir) / "single.npy", s1.decode_greedy(first, 40))
-        s1.destroy(); m1.destroy(); ctx1.close()
+        # the single-GPU run steps each rank's share in a state of the same batch size: kernels are chosen by batch size
+        # (dp4a / tensor cores, attention splits), and bit-identical results need the same ones on both sides
+        single = []
+        for r in range(world):
+            s1 = m1.new_state(2)
+            single.append(s1.decode_greedy(first[2 * r:2 * r + 2], 40))
+            s1.destroy()
+        np.save(Path(out_dir) / "single.npy", np.concatenate(single))
+        m1.destroy(); ctx1.close()
     dist.barrier(); ctx.close(); dist.destroy_process_group()
 
 
