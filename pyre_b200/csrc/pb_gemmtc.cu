@@ -5,15 +5,16 @@
 // This is the path of prefill chunks, wide verify windows and batched decode: the reference switches to its tensor-core
 // GEMM at 16 tokens as well (gmm, src/model/qwen4exp_gguf.rs:3264-3266; k_gemm_tc, src/model/qn_cube.rs:153, host side
 // gemm_pfx :6559-6587).  One CTA owns a tile of 128 weight rows x up to 128 tokens and walks the contraction in steps of
-// 64 columns through rings of shared memory (3 weight tiles, 4 activation tiles):
+// 64 columns through a ring of 6 stages (a weight tile in tensor memory + the activation tiles in shared memory):
 //
 //   producer warp       brings the activations of each step -- f16 high and low parts (x = hi + lo, 22 significant
 //                       bits), prepared once per GEMM by pb_xt_prep_kernel in exactly the operand layout -- with 1-D
 //                       bulk copies.
 //   decoder warps (8)   stream the re-coded IQ3_S rows of the tile (4-bit codes, PB_T_IQ3S_N4: 136 bytes per row and 256
 //                       columns) into a double buffer of raw bytes with 8-byte cp.async (all 256 threads share the
-//                       copies), then one thread = one row x 64 columns per step: f16 weights written into the stage as the canonical
-//                       K-major operand layout of tcgen05 (rows of 128 bytes, 128-byte swizzle).  (2c - 15) * (1 + 2s) is
+//                       copies), then one thread = one row x 64 columns per step: f16 weights stored with tcgen05.st
+//                       into the thread's own lane of a weight tile in tensor memory (the A operand is read from
+//                       there, behind the accumulator).  (2c - 15) * (1 + 2s) is
 //                       exact in f16; the block scale d is folded in with one rounding (relative 2^-11), after a
 //                       per-tile power-of-two shift that keeps d * 465 inside the f16 range and is undone at the end.
 //   MMA warp            one elected thread issues tcgen05.mma (kind::f16, M = 128, N = tokens, K = 16) for the high and
@@ -32,13 +33,15 @@
 #define TC_ROWS 128                 // weight rows per tile = MMA M
 #define TC_NBLK 128                 // tokens per CTA; the MMA's N is twice the (padded) token count: high and low parts side by side
 #define TC_KSTEP 64                 // contraction columns per step
-#define TC_A_STAGES 3               // ring of decoded weight tiles
-#define TC_B_STAGES 4               // ring of activation tiles (32 KB each at 128 tokens)
+#define TC_STAGES 6                 // ring depth: a stage = a decoded weight tile in tensor memory (32 columns behind the accumulator's
+                                    // 256) + the activation tiles of the same step in shared memory (32 KB at 128 tokens)
+#define TC_ACC_COLS (2 * TC_NBLK)   // accumulator columns: high and low parts of up to 128 tokens
+#define TC_A_COLS (TC_KSTEP / 2)    // a weight tile is 128 lanes x 32 columns: two f16 per 32-bit cell
+#define TC_TMEM_COLS 512            // 256 + 6 x 32 = 448, rounded to the power of two: the whole tensor memory of the SM (one CTA per SM)
 #define TC_RAW_STAGES 2             // raw double buffer: one block (256 columns = 4 steps) each
 #define TC_RAW_BYTES (TC_ROWS * 136)
 #define TC_DECODERS 8
 #define TC_THREADS ((TC_DECODERS + 2) * 32)
-#define TC_A_BYTES (TC_ROWS * TC_KSTEP * 2)                       // 16 KB
 #define TC_B_BYTES (2 * TC_NBLK * TC_KSTEP * 2)                   // high and low activation tiles: 32 KB
 #define TC_XT_HEAD 4096             // bytes of per-token prescale inverses in front of the activation tiles
 
@@ -54,11 +57,12 @@ __device__ __forceinline__ void tc_dealloc(uint32_t taddr, uint32_t ncols) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+// D (tensor memory) (+)= A (tensor memory: lane = row, two f16 per cell along K) x B (shared memory, by descriptor)
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // the mbarrier receives one arrival once every tcgen05.mma issued so far by this thread has completed
@@ -189,8 +193,21 @@ __device__ __forceinline__ void tc_cp_async8(uint32_t dst, const void* src) {
 __device__ __forceinline__ void tc_cp_async_arrive(uint64_t* bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(pb_smem_u32(bar)) : "memory");
 }
-// decode and store: row `row` of the A tile at `a_s` (shared-memory address), the 64 columns of step ks
-__device__ __forceinline__ void tc_decode_store(const TcRaw& r, int ks, uint32_t a_s, int row, float shift) {
+// 32 cells of this thread's lane, consecutive columns from taddr on (taddr carries the warp's first lane in bits 16+)
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+          "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+          "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// decode the 64 columns of step ks of this thread's row and store them as its lane of the weight tile at taddr
+// (tensor memory: lane = row, cell j = columns 2j, 2j + 1 of the step)
+__device__ __forceinline__ void tc_decode_store(const TcRaw& r, int ks, uint32_t taddr, float shift) {
     const int qt = ks & 3;
     const float d = pb_h2f((uint16_t)(r.head.x & 0xFFFF)) * shift;
     const uint32_t sc = (r.head.y >> (8 * qt)) & 0xFF;
@@ -198,7 +215,7 @@ __device__ __forceinline__ void tc_decode_store(const TcRaw& r, int ks, uint32_t
     const __half2 a0 = __float2half2_rn(2.0f * f0), b0 = __float2half2_rn(-15.0f * f0);
     const __half2 a1 = __float2half2_rn(2.0f * f1), b1 = __float2half2_rn(-15.0f * f1);
     const __half2 k1024 = __float2half2_rn(1024.0f), d2 = __float2half2_rn(d);
-    const uint32_t dst = a_s + (uint32_t)row * 128u;
+    uint32_t cells[32];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
 #pragma unroll
@@ -207,16 +224,15 @@ __device__ __forceinline__ void tc_decode_store(const TcRaw& r, int ks, uint32_t
             const uint32_t w = j ? r.c[i].y : r.c[i].x;
             const uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
             const uint32_t c4[4] = {pb_prmt(lo, 0x64006400u, 0x7150u), pb_prmt(lo, 0x64006400u, 0x7352u), pb_prmt(hi, 0x64006400u, 0x7150u), pb_prmt(hi, 0x64006400u, 0x7352u)};
-            uint32_t o[4];
 #pragma unroll
             for (int e = 0; e < 4; e++) {
                 // (1024 + c) - 1024 = c, c * 2m - 15m = (2c - 15) m: exact in f16; the product with d rounds once
                 const __half2 v = __hmul2(__hfma2(__hsub2(*reinterpret_cast<const __half2*>(&c4[e]), k1024), u < 4 ? a0 : a1, u < 4 ? b0 : b1), d2);
-                o[e] = *reinterpret_cast<const uint32_t*>(&v);
+                cells[4 * u + e] = *reinterpret_cast<const uint32_t*>(&v);
             }
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + (uint32_t)((u ^ (row & 7)) * 16)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
         }
     }
+    tc_st32(taddr, cells);
 }
 
 struct TcParams {
@@ -231,20 +247,17 @@ struct TcParams {
 
 __global__ void __launch_bounds__(TC_THREADS, 1) pb_gemmtc_iq3s_kernel(const TcParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint64_t* full_a = reinterpret_cast<uint64_t*>(smem);           // [TC_A_STAGES] 128 decoder arrivals
-    uint64_t* empty_a = full_a + TC_A_STAGES;                       // [TC_A_STAGES] tcgen05.commit
-    uint64_t* full_b = empty_a + TC_A_STAGES;                       // [TC_B_STAGES] bulk-copy bytes
-    uint64_t* empty_b = full_b + TC_B_STAGES;                       // [TC_B_STAGES] tcgen05.commit
-    uint64_t* raw_full = empty_b + TC_B_STAGES;                     // [TC_RAW_STAGES] 256 decoder threads (cp.async)
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);             // [TC_STAGES] 128 decoder arrivals + the producer's, and the bulk-copy bytes
+    uint64_t* empty = full + TC_STAGES;                             // [TC_STAGES] tcgen05.commit: the MMAs that read the stage are done
+    uint64_t* raw_full = empty + TC_STAGES;                         // [TC_RAW_STAGES] 256 decoder threads (cp.async)
     uint64_t* raw_empty = raw_full + TC_RAW_STAGES;                 // [TC_RAW_STAGES] 256 decoder threads
     uint64_t* acc_full = raw_empty + TC_RAW_STAGES;                 // accumulator complete
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 256);
-    float* red = reinterpret_cast<float*>(smem + 288);              // [8] per-warp maxima of d
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 384);
+    float* red = reinterpret_cast<float*>(smem + 416);              // [8] per-warp maxima of d
     float* xinv = reinterpret_cast<float*>(smem + 512);             // [TC_NBLK]
-    uint8_t* a_ring = smem + 1024;                                  // [TC_A_STAGES][128 rows][128 bytes], swizzled
-    uint8_t* b_ring = a_ring + TC_A_STAGES * TC_A_BYTES;            // [TC_B_STAGES][high tile | low tile]
-    uint8_t* raw = b_ring + TC_B_STAGES * TC_B_BYTES;               // [TC_RAW_STAGES][128 rows][136 bytes]
-    static_assert((TC_A_STAGES * 2 + TC_B_STAGES * 2 + TC_RAW_STAGES * 2 + 1) * 8 <= 256, "barriers fit in front of the TMEM slot");
+    uint8_t* b_ring = smem + 1024;                                  // [TC_STAGES][high tile | low tile], swizzled 128-byte rows
+    uint8_t* raw = b_ring + TC_STAGES * TC_B_BYTES;               // [TC_RAW_STAGES][128 rows][136 bytes]
+    static_assert((TC_STAGES * 2 + TC_RAW_STAGES * 2 + 1) * 8 <= 384 && TC_ACC_COLS + TC_STAGES * TC_A_COLS <= TC_TMEM_COLS, "barriers fit in front of the TMEM slot");
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     const int tile = (int)blockIdx.x, tb = (int)blockIdx.y;
@@ -258,13 +271,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) pb_gemmtc_iq3s_kernel(const TcP
     const uint32_t bbytes = 2u * (uint32_t)np * 128u;
 
     if (tid == 0) {
-        for (int i = 0; i < TC_A_STAGES; i++) { pb_mbar_init(&full_a[i], 128); pb_mbar_init(&empty_a[i], 1); }
-        for (int i = 0; i < TC_B_STAGES; i++) { pb_mbar_init(&full_b[i], 1); pb_mbar_init(&empty_b[i], 1); }
+        for (int i = 0; i < TC_STAGES; i++) { pb_mbar_init(&full[i], 128 + 1); pb_mbar_init(&empty[i], 1); }
         for (int i = 0; i < TC_RAW_STAGES; i++) { pb_mbar_init(&raw_full[i], TC_DECODERS * 32); pb_mbar_init(&raw_empty[i], TC_DECODERS * 32); }
         pb_mbar_init(acc_full, 1);
         pb_fence_barrier_init();
     }
-    if (warp == TC_DECODERS + 1) tc_alloc(tmem_slot, 2 * TC_NBLK);
+    if (warp == TC_DECODERS + 1) tc_alloc(tmem_slot, TC_TMEM_COLS);
     pb_pdl_trigger();
     tc_fence_before();
     __syncthreads();
@@ -273,18 +285,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) pb_gemmtc_iq3s_kernel(const TcP
     pb_pdl_wait();    // the activation tiles, and y when accumulating, come from earlier launches
 
     if (warp == TC_DECODERS) {
-        // ------------------------------------------------------------ producer: activation tiles, TC_B_STAGES steps ahead
+        // ------------------------------------------------------------ producer: activation tiles, TC_STAGES steps ahead
         if (lane == 0) {
             const uint8_t* src = p.xt + TC_XT_HEAD + (size_t)tb * (size_t)nk * (2 * (size_t)TC_NBLK * 128);
             int k = 0;
             for (; k < nk; k++) {
-                const int st = k % TC_B_STAGES;
-                if (k >= TC_B_STAGES && !pb_mbar_wait(&empty_b[st], ((k / TC_B_STAGES) - 1) & 1, p.status, PB_DEV_TC_TIMEOUT)) break;
-                pb_mbar_expect_tx(&full_b[st], bbytes);
-                pb_bulk_g2s(b_ring + (size_t)st * TC_B_BYTES, src + (size_t)k * bbytes, bbytes, &full_b[st]);
+                const int st = k % TC_STAGES;
+                if (k >= TC_STAGES && !pb_mbar_wait(&empty[st], ((k / TC_STAGES) - 1) & 1, p.status, PB_DEV_TC_TIMEOUT)) break;
+                pb_mbar_expect_tx(&full[st], bbytes);
+                pb_bulk_g2s(b_ring + (size_t)st * TC_B_BYTES, src + (size_t)k * bbytes, bbytes, &full[st]);
             }
             // error path: the copies in flight get a bounded chance to land before the CTA may exit
-            if (k < nk) for (int j = max(0, k - TC_B_STAGES); j < k; j++) pb_mbar_wait(&full_b[j % TC_B_STAGES], (j / TC_B_STAGES) & 1, nullptr, 0);
+            // (a stage's barrier also counts the decoders' arrivals: on the error path it may never complete; the wait is bounded)
+            if (k < nk) for (int j = max(0, k - TC_STAGES); j < k; j++) pb_mbar_wait(&full[j % TC_STAGES], (j / TC_STAGES) & 1, nullptr, 0);
         }
     } else if (warp == TC_DECODERS + 1) {
         // ------------------------------------------------------------ MMA issue
@@ -293,19 +306,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) pb_gemmtc_iq3s_kernel(const TcP
         const uint32_t idesc = tc_idesc(TC_ROWS, 2 * np);
         bool ok = true;
         for (int k = 0; k < nk && ok; k++) {
-            const int sa = k % TC_A_STAGES, sb = k % TC_B_STAGES;
-            ok = pb_mbar_wait(&full_b[sb], (k / TC_B_STAGES) & 1, p.status, PB_DEV_TC_TIMEOUT);
-            ok = ok && pb_mbar_wait(&full_a[sa], (k / TC_A_STAGES) & 1, p.status, PB_DEV_TC_TIMEOUT);
+            const int st = k % TC_STAGES;
+            ok = pb_mbar_wait(&full[st], (k / TC_STAGES) & 1, p.status, PB_DEV_TC_TIMEOUT);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             tc_fence_after();
             if (lane == 0) {
-                const uint32_t a_s = pb_smem_u32(a_ring + (size_t)sa * TC_A_BYTES);
-                const uint32_t b_s = pb_smem_u32(b_ring + (size_t)sb * TC_B_BYTES);
+                const uint32_t a_t = tmem + TC_ACC_COLS + (uint32_t)st * TC_A_COLS;
+                const uint32_t b_s = pb_smem_u32(b_ring + (size_t)st * TC_B_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < TC_KSTEP / 16; kk++) tc_mma_f16(tmem, tc_desc(a_s + kk * 32), tc_desc(b_s + kk * 32), idesc, (k | kk) ? 1u : 0u);
-                tc_commit(&empty_a[sa]);
-                tc_commit(&empty_b[sb]);
+                for (int kk = 0; kk < TC_KSTEP / 16; kk++) tc_mma_f16_ts(tmem, a_t + kk * 8, tc_desc(b_s + kk * 32), idesc, (k | kk) ? 1u : 0u);
+                tc_commit(&empty[st]);
             }
             __syncwarp();
         }
@@ -343,7 +354,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) pb_gemmtc_iq3s_kernel(const TcP
 
         bool ok = true;
         for (int k = grp; k < nk; k += 2) {
-            const int sa = k % TC_A_STAGES, kb = k >> 2, rs = kb % TC_RAW_STAGES;
+            const int st = k % TC_STAGES, kb = k >> 2, rs = kb % TC_RAW_STAGES;
             // this group's steps of a block are quarters grp and grp + 2: wait for the bytes at the first; after the second,
             // release the buffer and -- once all 256 threads have released it -- refill it with the block after next
             if ((k & 3) == grp && !pb_mbar_wait(&raw_full[rs], (kb / TC_RAW_STAGES) & 1, p.status, PB_DEV_TC_TIMEOUT)) { ok = false; break; }
@@ -356,10 +367,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) pb_gemmtc_iq3s_kernel(const TcP
                     issue_raw(kb + 2);
                 }
             }
-            if (k >= TC_A_STAGES && !pb_mbar_wait(&empty_a[sa], ((k / TC_A_STAGES) - 1) & 1, p.status, PB_DEV_TC_TIMEOUT)) { ok = false; break; }
-            tc_decode_store(cur, k, pb_smem_u32(a_ring + (size_t)sa * TC_A_BYTES), row, shift);
-            pb_fence_proxy_async();               // the tensor core reads shared memory through the async proxy
-            pb_mbar_arrive(&full_a[sa]);
+            if (k >= TC_STAGES && !pb_mbar_wait(&empty[st], ((k / TC_STAGES) - 1) & 1, p.status, PB_DEV_TC_TIMEOUT)) { ok = false; break; }
+            tc_decode_store(cur, k, tmem + ((uint32_t)((warp & 3) * 32) << 16) + TC_ACC_COLS + (uint32_t)st * TC_A_COLS, shift);
+            tc_fence_before();                    // the stores are complete (wait::st); order them before the MMA warp's instructions
+            pb_mbar_arrive(&full[st]);
         }
         // ---- epilogue: warp w reads lanes 32 (w % 4) .. + 31 (its rows); warps 0-3 take tokens below 64, 4-7 the rest; columns
         //      [0, np) hold the high parts' sums, [np, 2 np) the low parts'
@@ -386,7 +397,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) pb_gemmtc_iq3s_kernel(const TcP
     asm volatile("cp.async.wait_all;" ::: "memory");   // (error paths) no copy of this thread is still in flight when the CTA exits
     tc_fence_before();
     __syncthreads();
-    if (warp == TC_DECODERS + 1) { tc_fence_after(); tc_dealloc(tmem, 2 * TC_NBLK); }
+    if (warp == TC_DECODERS + 1) { tc_fence_after(); tc_dealloc(tmem, TC_TMEM_COLS); }
 }
 
 bool pb_gemmtc_supported(int type, int cols, int t) { return type == PB_T_IQ3_S && t >= 16 && cols % 256 == 0 && cols >= 256; }
@@ -434,7 +445,7 @@ int pb_launch_gemmtc(pb_ctx* ctx, const PbGemvQArgs& a) {
     }
     p.ntiles = ntiles;
     if (ntiles == 0) return PB_OK;
-    const size_t smem = 1024 + (size_t)TC_A_STAGES * TC_A_BYTES + (size_t)TC_B_STAGES * TC_B_BYTES + (size_t)TC_RAW_STAGES * TC_RAW_BYTES;
+    const size_t smem = 1024 + (size_t)TC_STAGES * TC_B_BYTES + (size_t)TC_RAW_STAGES * TC_RAW_BYTES;
     auto kern = pb_gemmtc_iq3s_kernel;
     PB_TRY(pb_ensure_smem(ctx, kern, smem));
     pb_launch_k(ctx, kern, dim3(ntiles, nblk), dim3(TC_THREADS), smem, p);
