@@ -294,7 +294,8 @@ int pb_gemv_dev(pb_ctx* ctx, const pb_qmat* m, const float* x, int t, float* y) 
     if (t < 0) PB_FAIL(ctx, PB_ERR_ARG, "pb_gemv: t=%d", t);
     PB_TRY(pb_enter(ctx));
     // many tokens of a re-coded IQ3_S matrix go to the tcgen05 GEMM in pieces as large as its operand buffer takes
-    const int piece = t >= pb_gemmtc_min_tokens() && m->rdata && pb_gemmtc_supported(m->type, (int)m->cols, t) ? pb_gemmtc_max_tokens((int)m->cols) : 16;
+    const bool tc = t >= pb_gemmtc_min_tokens() && m->rdata && pb_gemvq_supported(m->type, (int)m->cols) && pb_gemmtc_supported(m->type, (int)m->cols, t);   // what pb_launch_gemvq will pick
+    const int piece = tc ? pb_gemmtc_max_tokens((int)m->cols) : 16;
     for (int t0 = 0; t0 < t; t0 += piece) {
         PbGemvArgs a;
         a.w = m->data; a.wr = m->rdata; a.type = m->type; a.rows = m->rows; a.cols = (int)m->cols;

@@ -79,3 +79,13 @@ def test_gemm_extreme_scales_and_inputs(ctx):
         assert rel_err(y[b], ref[b]) < GEMM_TOL or np.abs(ref[b]).max() == 0
     assert np.all(y[9] == 0)
     W.free()
+
+
+def test_many_tokens_on_a_matrix_wider_than_the_streaming_kernels_take(ctx):
+    """8192 columns are outside the integer / tensor-core kernels (4096 at most): pb_gemv must cut 64 tokens into pieces
+    the generic kernel accepts instead of handing it all 64."""
+    W = pb.QMat.synth(ctx, pb.IQ3_S, 256, 8192, 0, 3)
+    Wo = oracle.QMat.synth(oracle.IQ3_S, 256, 8192, 0, 3)
+    x = np.random.default_rng(8).standard_normal((64, 8192)).astype(np.float32)
+    assert rel_err(W.matmul(x), Wo.matmul(x)) < GEMM_TOL
+    W.free()
