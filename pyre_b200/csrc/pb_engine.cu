@@ -71,6 +71,7 @@ struct pb_state {
     std::vector<PbKv> kv;
     uint32_t* trace = nullptr; int64_t* trace_len = nullptr; int64_t trace_cap = 0;
     uint32_t* pin_u32 = nullptr;   // pinned staging for ids / next tokens
+    float* pin_logits = nullptr; size_t pin_logits_n = 0;   // pinned staging for logits on their way to the caller's (pageable) buffer
     cudaGraphExec_t graph = nullptr;
     // speculative verify: DeltaNet (conv ring, ssm) after each of the first t-1 tokens of the last window
     std::vector<float*> ck_conv, ck_ssm;   // [n_lin * PB_MAX_WINDOW]
@@ -439,6 +440,7 @@ int pb_state_destroy(pb_state* s) {
     for (void* p : s->allocs) cudaFree(p);
     pb_ep_symm_free(s->m->ctx, &s->symm);
     if (s->pin_u32) cudaFreeHost(s->pin_u32);
+    if (s->pin_logits) cudaFreeHost(s->pin_logits);
     delete s;
     return PB_OK;
 }
@@ -967,6 +969,20 @@ static int step_once(pb_state* s) {
     return PB_OK;
 }
 
+// Logits leave through a pinned buffer of the state: a device -> pageable-host copy is staged by the driver in small pieces
+// (about 0.1 ms for one 608 KB row), a copy into pinned memory runs at link speed and the host copies it on.
+static int logits_stage(pb_state* s, size_t n) {
+    pb_ctx* ctx = s->m->ctx;
+    if (n > s->pin_logits_n) {
+        if (s->pin_logits) cudaFreeHost(s->pin_logits);
+        s->pin_logits = nullptr; s->pin_logits_n = 0;
+        if (cudaMallocHost(&s->pin_logits, n * 4) != cudaSuccess) PB_FAIL(ctx, PB_ERR_OOM, "pinned allocation of %zu bytes failed", n * 4);
+        s->pin_logits_n = n;
+    }
+    PB_CUDA(ctx, cudaMemcpyAsync(s->pin_logits, s->logits, n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return PB_OK;
+}
+
 int pb_forward(pb_state* s, const uint32_t* ids_host, int t, float* logits_host) {
     if (!s) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx;
@@ -989,9 +1005,10 @@ int pb_forward(pb_state* s, const uint32_t* ids_host, int t, float* logits_host)
         }
         s->verify_t = 0;
         timing_stop(s);
-        PB_CUDA(ctx, cudaMemcpyAsync(logits_host, s->logits, (size_t)s->m->cfg.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        PB_TRY(logits_stage(s, (size_t)s->m->cfg.vocab));
         const int rcw = pb_sync_check(ctx, "pb_forward");
         timing_collect(s);
+        if (rcw == PB_OK) memcpy(logits_host, s->pin_logits, (size_t)s->m->cfg.vocab * 4);
         return rcw;
     }
     timing_begin(s);
@@ -1002,9 +1019,10 @@ int pb_forward(pb_state* s, const uint32_t* ids_host, int t, float* logits_host)
         if (j + 1 < t) PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // the pinned id buffer is reused
     }
     timing_stop(s);
-    PB_CUDA(ctx, cudaMemcpyAsync(logits_host, s->logits, (size_t)B * s->m->cfg.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    PB_TRY(logits_stage(s, (size_t)B * s->m->cfg.vocab));
     const int rc = pb_sync_check(ctx, "pb_forward");
     timing_collect(s);
+    if (rc == PB_OK) memcpy(logits_host, s->pin_logits, (size_t)B * s->m->cfg.vocab * 4);
     return rc;
 }
 
@@ -1072,9 +1090,10 @@ int pb_verify(pb_state* s, const uint32_t* ids_host, int t, float* logits_host) 
     timing_begin(s);
     PB_TRY(window_once(s, t, true, true));
     timing_stop(s);
-    PB_CUDA(ctx, cudaMemcpyAsync(logits_host, s->logits, (size_t)t * c.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    PB_TRY(logits_stage(s, (size_t)t * c.vocab));
     PB_TRY(pb_sync_check(ctx, "pb_verify"));
     timing_collect(s);
+    memcpy(logits_host, s->pin_logits, (size_t)t * c.vocab * 4);
     s->verify_t = t;
     return PB_OK;
 }
