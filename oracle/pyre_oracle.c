@@ -89,6 +89,10 @@ int orc_type_geom(int type, int* el, int* by) {  /* gguf_q.rs:33-41 */
         case ORC_Q4_K: e = 256; b = 144; break;
         case ORC_IQ2_XS: e = 256; b = 74; break;
         case ORC_IQ3_S: e = 256; b = 110; break;
+        case ORC_IQ3_XXS: e = 256; b = 98; break;
+        case ORC_IQ2_S: e = 256; b = 82; break;
+        case ORC_IQ4_NL: e = 32; b = 18; break;
+        case ORC_IQ4_XS: e = 256; b = 136; break;
         default: return -1;
     }
     if (el) *el = e;
@@ -138,6 +142,50 @@ int orc_dequant(int type, const uint8_t* x, int64_t n, float* y) {  /* gguf_q.rs
                     uint16_t q = rd16(qs + 2 * (4 * ib + l));
                     uint64_t g = PB_IQ2XS_GRID[q & 511]; uint8_t gb[8]; for (int j = 0; j < 8; j++) gb[j] = (uint8_t)(g >> (8 * j));
                     put8(yy, db[l / 2], gb, PB_KSIGNS_IQ2XS[q >> 9]); yy += 8;
+                }
+            }
+        }
+        break;
+    case ORC_IQ4_NL:                                                                           /* :82-83 */
+        for (int64_t i = 0; i < nb; i++) {
+            const uint8_t* b = x + i * bs; float d = h2f(rd16(b)); float* yy = y + i * 32;
+            for (int j = 0; j < 16; j++) { yy[j] = d * (float)PB_KVALUES_IQ4NL[b[2 + j] & 0xF]; yy[16 + j] = d * (float)PB_KVALUES_IQ4NL[b[2 + j] >> 4]; }
+        }
+        break;
+    case ORC_IQ4_XS:                                                                           /* :84-89 */
+        for (int64_t i = 0; i < nb; i++) {
+            const uint8_t* b = x + i * bs; float d = h2f(rd16(b)); uint16_t sh = rd16(b + 2); const uint8_t* sl = b + 4; const uint8_t* qs = b + 8; float* yy = y + i * 256;
+            for (int ib = 0; ib < 8; ib++) {
+                int ls = (int)((sl[ib / 2] >> (4 * (ib % 2))) & 0xF) | (int)(((sh >> (2 * ib)) & 3) << 4); float dl = d * (float)(ls - 32);
+                for (int j = 0; j < 16; j++) { yy[j] = (float)PB_KVALUES_IQ4NL[qs[j] & 0xF] * dl; yy[16 + j] = (float)PB_KVALUES_IQ4NL[qs[j] >> 4] * dl; }
+                yy += 32; qs += 16;
+            }
+        }
+        break;
+    case ORC_IQ2_S:                                                                            /* :130-135 */
+        for (int64_t i = 0; i < nb; i++) {
+            const uint8_t* b = x + i * bs; float d = h2f(rd16(b)); const uint8_t* qs = b + 2; const uint8_t* signs = b + 34; const uint8_t* qh = b + 66; const uint8_t* sc = b + 74; float* yy = y + i * 256;
+            for (int ib = 0; ib < 8; ib++) {
+                float db[2]; db[0] = d * (0.5f + (float)(sc[ib] & 0xF)) * 0.25f; db[1] = d * (0.5f + (float)(sc[ib] >> 4)) * 0.25f;
+                for (int l = 0; l < 4; l++) {
+                    uint32_t idx = (uint32_t)qs[l] | ((((uint32_t)qh[ib]) << (8 - 2 * l)) & 0x300);
+                    uint64_t g = PB_IQ2S_GRID[idx]; uint8_t gb[8]; for (int j = 0; j < 8; j++) gb[j] = (uint8_t)(g >> (8 * j));
+                    put8(yy, db[l / 2], gb, signs[l]); yy += 8;
+                }
+                qs += 4; signs += 4;
+            }
+        }
+        break;
+    case ORC_IQ3_XXS:                                                                          /* :136-140 */
+        for (int64_t i = 0; i < nb; i++) {
+            const uint8_t* b = x + i * bs; float d = h2f(rd16(b)); const uint8_t* qs = b + 2; const uint8_t* ss = b + 66; float* yy = y + i * 256;
+            for (int ib = 0; ib < 8; ib++) {
+                uint32_t a = (uint32_t)ss[4 * ib] | ((uint32_t)ss[4 * ib + 1] << 8) | ((uint32_t)ss[4 * ib + 2] << 16) | ((uint32_t)ss[4 * ib + 3] << 24);
+                float db = d * (0.5f + (float)(a >> 28)) * 0.5f;
+                for (int l = 0; l < 4; l++) {
+                    uint32_t g1 = PB_IQ3XXS_GRID[qs[8 * ib + 2 * l]], g2 = PB_IQ3XXS_GRID[qs[8 * ib + 2 * l + 1]];
+                    uint8_t gb[8]; for (int j = 0; j < 4; j++) { gb[j] = (uint8_t)(g1 >> (8 * j)); gb[4 + j] = (uint8_t)(g2 >> (8 * j)); }
+                    put8(yy, db, gb, PB_KSIGNS_IQ2XS[(a >> (7 * l)) & 127]); yy += 8;
                 }
             }
         }

@@ -17,7 +17,7 @@ __global__ void __launch_bounds__(256) pb_dequant_kernel(const uint8_t* __restri
     if (step * 32 >= n_units) return;
     if (step * 32 + (FMT == PB_T_Q4_K ? 0 : lane) >= n_units) return;  // ragged tail (formats with 32-wide blocks)
     PbTables T;
-    T.iq3s = PB_IQ3S_GRID; T.iq2xs = PB_IQ2XS_GRID; T.ksigns = PB_KSIGNS_IQ2XS;
+    T.iq3s = PB_IQ3S_GRID; T.iq2xs = PB_IQ2XS_GRID; T.ksigns = PB_KSIGNS_IQ2XS; T.iq3xxs = PB_IQ3XXS_GRID; T.iq2s = PB_IQ2S_GRID; T.kvalues = PB_KVALUES_IQ4NL;
     PbUnit u;
     F::unit(w + step * F::STEP_BYTES, lane, T, u);
     float* o = out + step * 256;

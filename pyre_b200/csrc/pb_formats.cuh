@@ -12,7 +12,8 @@
 #define PB_TABLE_QUAL static __device__ const
 #include "pb_iq_tables.h"
 
-enum : int { PB_T_F32 = 0, PB_T_F16 = 1, PB_T_Q8_0 = 8, PB_T_Q4_K = 12, PB_T_IQ2_XS = 17, PB_T_IQ3_S = 21, PB_T_BF16 = 30,
+enum : int { PB_T_F32 = 0, PB_T_F16 = 1, PB_T_Q8_0 = 8, PB_T_Q4_K = 12, PB_T_IQ2_XS = 17, PB_T_IQ3_XXS = 18, PB_T_IQ4_NL = 20, PB_T_IQ3_S = 21, PB_T_IQ2_S = 22,
+             PB_T_IQ4_XS = 23, PB_T_BF16 = 30,
              // internal, never a ggml id: IQ3_S re-coded at upload into 4-bit codes (see pb_repack.cu).  Every IQ3_S
              // codebook value is odd (1..15), so a weight is one of the sixteen values -15, -13, .. 15 = 2 c - 15.
              // Block of 256 weights, 136 bytes: [d f16][2 pad][4 bytes of 4-bit sub-scales as in IQ3_S][32 words];
@@ -24,8 +25,11 @@ struct PbTables {
     const uint32_t* iq3s;   // 512 x 4 grid bytes
     const uint64_t* iq2xs;  // 512 x 8 grid bytes
     const uint8_t* ksigns;  // 128 sign bytes
+    const uint32_t* iq3xxs; // 256 x 4 grid bytes
+    const uint64_t* iq2s;   // 1024 x 8 grid bytes
+    const int8_t* kvalues;  // 16 values of the IQ4 non-linear code
 };
-#define PB_TABLE_BYTES (512 * 4 + 512 * 8 + 128)
+#define PB_TABLE_BYTES (512 * 8 + 512 * 4 + 128 + 256 * 4 + 1024 * 8 + 16)
 
 // Copy the codebooks a format needs into shared memory at `dst` (16-byte aligned,
 // PB_TABLE_BYTES long).  All threads of the CTA call it; the caller synchronises after.
@@ -41,7 +45,18 @@ __device__ __forceinline__ PbTables pb_load_tables(uint8_t* dst, int tid, int nt
         for (int i = tid; i < 512; i += nthreads) g2[i] = PB_IQ2XS_GRID[i];
         for (int i = tid; i < 128; i += nthreads) ks[i] = PB_KSIGNS_IQ2XS[i];
     }
-    t.iq2xs = g2; t.iq3s = g3; t.ksigns = ks;
+    uint32_t* g3x = reinterpret_cast<uint32_t*>(dst + 512 * 8 + 512 * 4 + 128);
+    uint64_t* g2s = reinterpret_cast<uint64_t*>(dst + 512 * 8 + 512 * 4 + 128 + 256 * 4);
+    int8_t* kv = reinterpret_cast<int8_t*>(dst + 512 * 8 + 512 * 4 + 128 + 256 * 4 + 1024 * 8);
+    if (FMT == PB_T_IQ3_XXS) {
+        for (int i = tid; i < 256; i += nthreads) g3x[i] = PB_IQ3XXS_GRID[i];
+        for (int i = tid; i < 128; i += nthreads) ks[i] = PB_KSIGNS_IQ2XS[i];
+    }
+    if (FMT == PB_T_IQ2_S)
+        for (int i = tid; i < 1024; i += nthreads) g2s[i] = PB_IQ2S_GRID[i];
+    if (FMT == PB_T_IQ4_NL || FMT == PB_T_IQ4_XS)
+        for (int i = tid; i < 16; i += nthreads) kv[i] = PB_KVALUES_IQ4NL[i];
+    t.iq2xs = g2; t.iq3s = g3; t.ksigns = ks; t.iq3xxs = g3x; t.iq2s = g2s; t.kvalues = kv;
     return t;
 }
 
@@ -105,6 +120,85 @@ template <> struct PbFmt<PB_T_IQ2_XS> : PbContig8 {
             o.w[j] = (sg >> j) & 1 ? -a : a;
             o.w[4 + j] = (sg >> (4 + j)) & 1 ? -b : b;
         }
+    }
+};
+
+// IQ3_XXS (gguf_q.rs:136-140): per 32 weights eight grid indices (two entries of four magnitudes per unit) and one u32 with
+// four 7-bit sign-pattern indices and a 4-bit scale
+template <> struct PbFmt<PB_T_IQ3_XXS> : PbContig8 {
+    static constexpr int STEP_BYTES = 98;   // [d f16][qs 64][scales and signs 8 x u32]
+    static constexpr bool HAS_MIN = false;
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables& T, PbUnit& o) {
+        const float d = pb_h2f(*reinterpret_cast<const uint16_t*>(p));
+        const int ib = u >> 2, l = u & 3;
+        const uint8_t* ss = p + 66 + 4 * ib;
+        const uint32_t a = (uint32_t)ss[0] | ((uint32_t)ss[1] << 8) | ((uint32_t)ss[2] << 16) | ((uint32_t)ss[3] << 24);
+        o.sa = o.sb = __fmul_rn(__fmul_rn(d, 0.5f + (float)(a >> 28)), 0.5f);
+        o.ma = o.mb = 0.0f;
+        const uint32_t g1 = T.iq3xxs[p[2 + 8 * ib + 2 * l]], g2 = T.iq3xxs[p[2 + 8 * ib + 2 * l + 1]];
+        const uint32_t sg = T.ksigns[(a >> (7 * l)) & 127];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float x = (float)((g1 >> (8 * j)) & 0xFF), y = (float)((g2 >> (8 * j)) & 0xFF);
+            o.w[j] = (sg >> j) & 1 ? -x : x;
+            o.w[4 + j] = (sg >> (4 + j)) & 1 ? -y : y;
+        }
+    }
+};
+
+// IQ2_S (gguf_q.rs:130-135): per unit one 10-bit grid index (8 bits in qs, 2 in qh) and one explicit sign byte
+template <> struct PbFmt<PB_T_IQ2_S> : PbContig8 {
+    static constexpr int STEP_BYTES = 82;   // [d f16][qs 32][signs 32][qh 8][scales 8]
+    static constexpr bool HAS_MIN = false;
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables& T, PbUnit& o) {
+        const float d = pb_h2f(*reinterpret_cast<const uint16_t*>(p));
+        const int ib = u >> 2, l = u & 3;
+        const uint32_t sc = p[74 + ib];
+        const uint32_t nib = (l & 2) ? (sc >> 4) : (sc & 0xF);
+        o.sa = o.sb = __fmul_rn(__fmul_rn(d, 0.5f + (float)nib), 0.25f);
+        o.ma = o.mb = 0.0f;
+        const uint32_t idx = (uint32_t)p[2 + 4 * ib + l] | ((((uint32_t)p[66 + ib]) << (8 - 2 * l)) & 0x300);
+        const uint64_t g = T.iq2s[idx];
+        const uint32_t sg = p[34 + 4 * ib + l];
+        const uint32_t lo = (uint32_t)g, hi = (uint32_t)(g >> 32);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float x = (float)((lo >> (8 * j)) & 0xFF), y = (float)((hi >> (8 * j)) & 0xFF);
+            o.w[j] = (sg >> j) & 1 ? -x : x;
+            o.w[4 + j] = (sg >> (4 + j)) & 1 ? -y : y;
+        }
+    }
+};
+
+// IQ4_NL (gguf_q.rs:82-83): blocks of 32 = [d f16][16 bytes]; weight j < 16 is the low nibble of byte j, weight 16 + j the high one
+template <> struct PbFmt<PB_T_IQ4_NL> : PbContig8 {
+    static constexpr int STEP_BYTES = 8 * 18;
+    static constexpr bool HAS_MIN = false;
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables& T, PbUnit& o) {
+        const uint8_t* b = p + 18 * (u >> 2);
+        const int part = u & 3;                       // weights 8 part .. 8 part + 7 of the block
+        o.sa = o.sb = pb_h2f((uint16_t)(b[0] | (b[1] << 8)));
+        o.ma = o.mb = 0.0f;
+        const uint8_t* q = b + 2 + 8 * (part & 1);
+#pragma unroll
+        for (int j = 0; j < 8; j++) o.w[j] = (float)T.kvalues[part < 2 ? (q[j] & 0xF) : (q[j] >> 4)];
+    }
+};
+
+// IQ4_XS (gguf_q.rs:84-89): super-block [d f16][scales_h u16][scales_l 4][qs 128]; per 32 weights a 6-bit scale ls, value = kvalue * (d * (ls - 32))
+template <> struct PbFmt<PB_T_IQ4_XS> : PbContig8 {
+    static constexpr int STEP_BYTES = 136;
+    static constexpr bool HAS_MIN = false;
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables& T, PbUnit& o) {
+        const float d = pb_h2f(*reinterpret_cast<const uint16_t*>(p));
+        const int ib = u >> 2, part = u & 3;
+        const uint32_t sh = (uint32_t)p[2] | ((uint32_t)p[3] << 8);
+        const int ls = (int)((p[4 + (ib >> 1)] >> (4 * (ib & 1))) & 0xF) | (int)(((sh >> (2 * ib)) & 3) << 4);
+        o.sa = o.sb = __fmul_rn(d, (float)(ls - 32));
+        o.ma = o.mb = 0.0f;
+        const uint8_t* q = p + 8 + 16 * ib + 8 * (part & 1);
+#pragma unroll
+        for (int j = 0; j < 8; j++) o.w[j] = (float)T.kvalues[part < 2 ? (q[j] & 0xF) : (q[j] >> 4)];
     }
 };
 
@@ -199,6 +293,10 @@ static inline int pb_geom(int type, int* elems, int* bytes) {
         case PB_T_Q4_K: e = 256; b = 144; break;
         case PB_T_IQ2_XS: e = 256; b = 74; break;
         case PB_T_IQ3_S: e = 256; b = 110; break;
+        case PB_T_IQ3_XXS: e = 256; b = 98; break;
+        case PB_T_IQ2_S: e = 256; b = 82; break;
+        case PB_T_IQ4_NL: e = 32; b = 18; break;
+        case PB_T_IQ4_XS: e = 256; b = 136; break;
         case PB_T_IQ3S_N4: e = 256; b = 136; break;
         default: return -1;
     }
@@ -212,6 +310,10 @@ static inline int pb_geom(int type, int* elems, int* bytes) {
     switch (type) {                                                    \
         case PB_T_IQ3_S: { constexpr int FMT = PB_T_IQ3_S; F(__VA_ARGS__); } break;  \
         case PB_T_IQ2_XS: { constexpr int FMT = PB_T_IQ2_XS; F(__VA_ARGS__); } break; \
+        case PB_T_IQ3_XXS: { constexpr int FMT = PB_T_IQ3_XXS; F(__VA_ARGS__); } break; \
+        case PB_T_IQ2_S: { constexpr int FMT = PB_T_IQ2_S; F(__VA_ARGS__); } break; \
+        case PB_T_IQ4_NL: { constexpr int FMT = PB_T_IQ4_NL; F(__VA_ARGS__); } break; \
+        case PB_T_IQ4_XS: { constexpr int FMT = PB_T_IQ4_XS; F(__VA_ARGS__); } break; \
         case PB_T_Q4_K: { constexpr int FMT = PB_T_Q4_K; F(__VA_ARGS__); } break;    \
         case PB_T_Q8_0: { constexpr int FMT = PB_T_Q8_0; F(__VA_ARGS__); } break;    \
         case PB_T_F32: { constexpr int FMT = PB_T_F32; F(__VA_ARGS__); } break;      \

@@ -21,7 +21,7 @@ import oracle  # noqa: E402
 from gguf import quants, GGMLQuantizationType as T  # noqa: E402
 
 HERE = Path(__file__).resolve().parent
-GG = {"Q8_0": T.Q8_0, "Q4_K": T.Q4_K, "IQ2_XS": T.IQ2_XS, "IQ3_S": T.IQ3_S}
+GG = {"Q8_0": T.Q8_0, "Q4_K": T.Q4_K, "IQ2_XS": T.IQ2_XS, "IQ3_S": T.IQ3_S, "IQ3_XXS": T.IQ3_XXS, "IQ2_S": T.IQ2_S, "IQ4_NL": T.IQ4_NL, "IQ4_XS": T.IQ4_XS}
 
 
 def main():
@@ -36,6 +36,17 @@ def main():
         if name == "Q4_K":
             b[:, 3] = rng.integers(0x20, 0x38, nb)
         raw = np.concatenate([a, b.reshape(-1)])
+        f32 = quants.dequantize(raw.reshape(-1, bs), GG[name]).reshape(rows, cols).astype(np.float32)
+        np.savez_compressed(HERE / f"dequant_{name}.npz", raw=raw, f32=f32, rows=rows, cols=cols, type=t)
+        print(name, raw.size, "bytes")
+    for name, t in oracle.EXTRA_TYPES.items():     # the loader's further formats: random bytes with a sane f16 scale only
+        el, bs = oracle.geom(t)
+        cols, rows = 512, 4
+        rng = np.random.default_rng(4321 + t)
+        nb = rows * cols // el
+        b = rng.integers(0, 256, size=(nb, bs), dtype=np.uint8)
+        b[:, 1] = rng.integers(0x20, 0x38, nb)
+        raw = b.reshape(-1)
         f32 = quants.dequantize(raw.reshape(-1, bs), GG[name]).reshape(rows, cols).astype(np.float32)
         np.savez_compressed(HERE / f"dequant_{name}.npz", raw=raw, f32=f32, rows=rows, cols=cols, type=t)
         print(name, raw.size, "bytes")

@@ -11,6 +11,7 @@ from conftest import rel_err
 pytestmark = pytest.mark.gpu
 GOLD = Path(__file__).resolve().parent / "golden"
 TYPES = {"Q8_0": pb.Q8_0, "Q4_K": pb.Q4_K, "IQ2_XS": pb.IQ2_XS, "IQ3_S": pb.IQ3_S}
+EXTRA = {"IQ3_XXS": pb.IQ3_XXS, "IQ2_S": pb.IQ2_S, "IQ4_NL": pb.IQ4_NL, "IQ4_XS": pb.IQ4_XS}   # the GGUF loader's further formats
 GEMV_TOL = 1e-3   # relative, f32 accumulate (north-star tolerance)
 
 
@@ -22,6 +23,20 @@ def test_dequant_golden_bit_exact(ctx, name):
     y = W.to_f32()
     assert np.array_equal(y.view(np.uint32), g["f32"].view(np.uint32))
     assert np.array_equal(W.raw_rows(1, 2), g["raw"].reshape(rows, -1)[1:3].reshape(-1))
+    W.free()
+
+
+@pytest.mark.parametrize("name", list(EXTRA))
+def test_extra_formats_dequant_golden_and_gemv(ctx, name):
+    """IQ3_XXS / IQ2_S / IQ4_NL / IQ4_XS: dequantization bit-for-bit against the gguf-py fixture, and the generic GEMV
+    against the oracle (these formats take the f32 kernel, not the streaming ones)."""
+    g = np.load(GOLD / f"dequant_{name}.npz")
+    rows, cols = int(g["rows"]), int(g["cols"])
+    W = pb.QMat.upload(ctx, EXTRA[name], rows, cols, g["raw"])
+    assert np.array_equal(W.to_f32().view(np.uint32), g["f32"].view(np.uint32))
+    x = np.random.default_rng(3).standard_normal((5, cols)).astype(np.float32)
+    ref = oracle.QMat(EXTRA[name], rows, cols, g["raw"]).matmul(x)
+    assert rel_err(W.matmul(x), ref) < GEMV_TOL
     W.free()
 
 
