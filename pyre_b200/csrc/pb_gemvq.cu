@@ -284,6 +284,11 @@ int pb_launch_gemvq(pb_ctx* ctx, const PbGemvQArgs& a) {
         for (int s = 0; s < a.nseg && s < 4; s++) all = all && a.seg[s].wr != nullptr;
         if (use_tc && all && a.t >= pb_gemmtc_min_tokens()) return pb_launch_gemmtc(ctx, a);
     }
+    if (a.mode != PB_ACT_PREQ && pb_gemvi_supported(a.type, a.cols, a.t)) {
+        bool all = true;
+        for (int s = 0; s < a.nseg && s < 4; s++) all = all && (a.type == PB_T_IQ3S_N4 ? a.seg[s].w : a.seg[s].wr) != nullptr;
+        if (all) return pb_launch_gemvi(ctx, a);
+    }
     if (a.mode != PB_ACT_PREQ && pb_gemmh_supported(a.type, a.cols, a.t)) {
         static const bool use_mma = !(getenv("PYRE_B200_MMA") && atoi(getenv("PYRE_B200_MMA")) == 0);
         if (use_mma) return pb_launch_gemmh(ctx, a);

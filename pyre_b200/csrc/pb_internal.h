@@ -203,6 +203,9 @@ int pb_launch_gemvq(pb_ctx* ctx, const PbGemvQArgs& a);
 // pb_gemmh.cu: tensor-core path for 3..16 columns of IQ3_S weights
 bool pb_gemmh_supported(int type, int cols, int t);
 int pb_launch_gemmh(pb_ctx* ctx, const PbGemvQArgs& a);
+// pb_gemvi.cu: int8 tensor-core path for one and two columns of IQ3_S weights that have a re-coded copy
+bool pb_gemvi_supported(int type, int cols, int t);
+int pb_launch_gemvi(pb_ctx* ctx, const PbGemvQArgs& a);
 // pb_gemmtc.cu: tcgen05 path for 16 and more columns of IQ3_S weights that have a re-coded copy
 bool pb_gemmtc_supported(int type, int cols, int t);
 int pb_launch_gemmtc(pb_ctx* ctx, const PbGemvQArgs& a);
