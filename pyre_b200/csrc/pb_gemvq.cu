@@ -289,7 +289,8 @@ int pb_launch_gemvq(pb_ctx* ctx, const PbGemvQArgs& a) {
         int64_t rows = 0;
         for (int s = 0; s < a.nseg && s < 4; s++) { all = all && (a.type == PB_T_IQ3S_N4 ? a.seg[s].w : a.seg[s].wr) != nullptr; rows += a.seg[s].rows; }
         // measured: from about ten million weights on it beats the dp4a kernel with two tokens, below that they tie
-        if (all && rows * a.cols >= ((int64_t)10 << 20)) return pb_launch_gemvi(ctx, a);
+        static const int64_t min_weights = getenv("PYRE_B200_IMMA_MIN_WEIGHTS") ? atoll(getenv("PYRE_B200_IMMA_MIN_WEIGHTS")) : ((int64_t)10 << 20);
+        if (all && rows * a.cols >= min_weights) return pb_launch_gemvi(ctx, a);
     }
     if (a.mode != PB_ACT_PREQ && pb_gemmh_supported(a.type, a.cols, a.t)) {
         static const bool use_mma = !(getenv("PYRE_B200_MMA") && atoi(getenv("PYRE_B200_MMA")) == 0);
