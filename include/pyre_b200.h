@@ -168,6 +168,10 @@ typedef enum pb_role {
 int pb_model_create(pb_ctx* ctx, const pb_cfg* cfg, pb_model** out);
 int pb_model_set_tensor(pb_model* m, int layer, int role, pb_qmat* mat);   /* the model takes ownership */
 int pb_model_set_vec(pb_model* m, int layer, int role, const float* v_host, int64_t n);
+/* Trained context of the checkpoint (`<arch>.context_length`).  When cfg.max_ctx exceeds it, the rope table is YaRN-scaled
+ * for the whole run as the reference does at load (src/model/qwen4exp_gguf.rs:490-517, table src/qn_ctx.rs:160-186, mscale on
+ * cos and sin :528-533); 0 (the default) or max_ctx <= ctx_train leave the plain table.  Before pb_model_finalize. */
+int pb_model_set_ctx_train(pb_model* m, int ctx_train);
 /* attach_gpu :555-657.  ep_rank/ep_world: this GPU holds routed experts
  * [ep_rank*n_exp/ep_world, (ep_rank+1)*n_exp/ep_world) of every layer; dense tensors are replicated. */
 int pb_model_finalize(pb_model* m, int ep_rank, int ep_world);

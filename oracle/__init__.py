@@ -209,6 +209,15 @@ def rope_inv(n_rot: int, base: float) -> np.ndarray:
     return inv
 
 
+def rope_inv_yarn(n_rot: int, base: float, ctx_train: int, ctx: int):
+    """(inverse frequencies, mscale) for a context of ctx positions of a model trained on ctx_train."""
+    inv = np.empty(n_rot // 2, dtype=np.float32)
+    f = lib().orc_rope_inv_yarn
+    f.restype = C.c_float
+    ms = f(C.c_int(n_rot), C.c_float(base), C.c_int64(ctx_train), C.c_int64(ctx), _p(inv))
+    return inv, float(ms)
+
+
 def make_cfg(**kw) -> Cfg:
     c = Cfg()
     defaults = dict(n_layers=4, d=2048, hc=0, hc_lr=0, n_head=16, n_kv=2, hd=256, n_rot=64, rope_base=1e7, eps=1e-6,
@@ -246,9 +255,10 @@ def linear_core(cfg: Cfg, qkv, z, beta, alpha, a, dt, conv_w, norm_w, conv_state
     return out
 
 
-def attn_core(cfg: Cfg, qf, kf, vf, qn, kn, inv, kc, vc, pos, packed=None, q4n=0):
+def attn_core(cfg: Cfg, qf, kf, vf, qn, kn, inv, kc, vc, pos, packed=None, q4n=0, mscale=1.0):
     """One new token at position pos.  kc/vc [>=pos+1][n_kv*hd] f32, updated in place at row pos."""
-    qf, kf, vf, qn, kn, inv = _f32(qf), _f32(kf), _f32(vf), _f32(qn), _f32(kn), _f32(inv)
+    qf, kf, vf, qn, kn = _f32(qf), _f32(kf), _f32(vf), _f32(qn), _f32(kn)
+    inv = np.concatenate([_f32(inv)[:cfg.n_rot // 2], np.array([mscale], np.float32)])   # the C side reads mscale behind the table
     att = np.empty(cfg.n_head * cfg.hd, dtype=np.float32)
     if packed is None:
         kw = ks = vw = vs = None
@@ -272,6 +282,10 @@ class Model:
     def set_vec(self, layer: int, role: str, v: np.ndarray):
         v = _f32(v).reshape(-1)
         assert lib().orc_model_set_vec(self.h, C.c_int(layer), C.c_int(ROLE[role]), _p(v), C.c_int64(v.size)) == 0
+
+    def set_ctx_train(self, ctx_train: int):
+        """YaRN rope scaling when cfg.max_ctx exceeds the trained context."""
+        lib().orc_model_set_ctx_train(self.h, C.c_int64(ctx_train))
 
     def new_state(self) -> "State":
         return State(self)

@@ -401,10 +401,38 @@ float orc_kv4_get(const uint32_t* w, const float* sc, int64_t i) {  /* kv4.rs:35
 void orc_rope_inv(int n_rot, float base, float* inv) {  /* qn_ctx.rs:168 */
     for (int i = 0; i < n_rot / 2; i++) inv[i] = powf(base, -(2.0f * (float)i) / (float)n_rot);
 }
-/* rope :1436-1439 with rope_cs :529-533 (mscale 1) */
+/* Inverse rope frequencies for a context of `ctx` positions of a model trained on `ctx_train` (qn_ctx.rs:160-186): plain
+ * base^(-2i/n_rot) at or under the trained length (or ctx_train = 0); above it YaRN with the llama.cpp / transformers
+ * defaults (beta_fast 32, beta_slow 1): low indices are interpolated (divided by scale = ctx / ctx_train), high indices
+ * keep the trained frequency, a linear ramp between the two correction dimensions.  Returns mscale = 1 + 0.1 ln(scale),
+ * which the caller applies to cos and sin (qwen4exp_gguf.rs:528-533). */
+float orc_rope_inv_yarn(int n_rot, float base, int64_t ctx_train, int64_t ctx, float* inv) {
+    int half = n_rot / 2;
+    float scale = ctx_train > 0 && ctx > ctx_train ? (float)ctx / (float)ctx_train : 1.0f;
+    if (scale <= 1.0f) { orc_rope_inv(n_rot, base, inv); return 1.0f; }
+    float dim = (float)n_rot;
+    float lo = floorf((dim * logf((float)ctx_train / (32.0f * 2.0f * 3.14159265358979323846f))) / (2.0f * logf(base)));
+    float hi = ceilf((dim * logf((float)ctx_train / (1.0f * 2.0f * 3.14159265358979323846f))) / (2.0f * logf(base)));
+    if (lo < 0.0f) lo = 0.0f;
+    float top = (float)(half > 0 ? half - 1 : 0);
+    if (hi > top) hi = top;
+    for (int i = 0; i < half; i++) {
+        float extrap = powf(base, -(2.0f * (float)i) / dim), interp = extrap / scale;
+        float ramp = fabsf(hi - lo) < 1e-6f ? 1.0f : ((float)i - lo) / (hi - lo);
+        ramp = ramp < 0.0f ? 0.0f : (ramp > 1.0f ? 1.0f : ramp);
+        inv[i] = interp * (1.0f - ramp) + extrap * ramp;
+    }
+    return 1.0f + 0.1f * logf(scale);
+}
+/* rope :1436-1439 with rope_cs :529-533; inv[n_rot / 2] holds mscale, applied only when it is not 1 */
 static void rope(float* v, int64_t pos, const float* inv, int n_rot) {
     int half = n_rot / 2;
-    for (int i = 0; i < half; i++) { float a = (float)pos * inv[i]; float s = sinf(a), co = cosf(a); float x0 = v[i], x1 = v[i + half]; v[i] = x0 * co - x1 * s; v[i + half] = x1 * co + x0 * s; }
+    float ms = inv[half];
+    for (int i = 0; i < half; i++) {
+        float a = (float)pos * inv[i]; float s = sinf(a), co = cosf(a);
+        if (ms != 1.0f) { co *= ms; s *= ms; }
+        float x0 = v[i], x1 = v[i + half]; v[i] = x0 * co - x1 * s; v[i + half] = x1 * co + x0 * s;
+    }
 }
 
 /* ------------------------------------------------------------------ MoE block */
@@ -553,12 +581,17 @@ orc_model* orc_model_new(const orc_cfg* cfg) {
     orc_model* m = (orc_model*)calloc(1, sizeof *m); m->cfg = *cfg;
     m->slots = (orc_slot*)calloc((size_t)(cfg->n_layers + 1) * ORC_R_COUNT, sizeof(orc_slot));
     m->rope_inv = (float*)malloc((size_t)(cfg->n_rot / 2 + 1) * 4); orc_rope_inv(cfg->n_rot, cfg->rope_base, m->rope_inv);
+    m->rope_inv[cfg->n_rot / 2] = 1.0f;
     return m;
 }
 void orc_model_free(orc_model* m) {
     if (!m) return;
     for (size_t i = 0; i < (size_t)(m->cfg.n_layers + 1) * ORC_R_COUNT; i++) free(m->slots[i].vec);
     free(m->slots); free(m->rope_inv); free(m);
+}
+/* Model::load :490-517: a context (cfg.max_ctx) past the trained length is YaRN-scaled for the whole run */
+void orc_model_set_ctx_train(orc_model* m, int64_t ctx_train) {
+    m->rope_inv[m->cfg.n_rot / 2] = orc_rope_inv_yarn(m->cfg.n_rot, m->cfg.rope_base, ctx_train, m->cfg.max_ctx, m->rope_inv);
 }
 int orc_model_set_mat(orc_model* m, int layer, int role, const orc_mat* mat) {
     if (layer < -1 || layer >= m->cfg.n_layers || role < 0 || role >= ORC_R_COUNT) return -1;

@@ -62,6 +62,7 @@ void orc_top_k(const float* r, int n, int k, int32_t* idx, float* w);
 void orc_kv4_pack(const float* x, int64_t n, uint32_t* w, float* sc);
 float orc_kv4_get(const uint32_t* w, const float* sc, int64_t i);
 void orc_rope_inv(int n_rot, float base, float* inv);          /* qn_ctx.rs:164-170, unscaled */
+float orc_rope_inv_yarn(int n_rot, float base, int64_t ctx_train, int64_t ctx, float* inv);   /* qn_ctx.rs:160-186; returns mscale */
 uint32_t orc_argmax(const float* v, int64_t n);                 /* sampler.rs:142-148 */
 
 /* ---- model ---- */
@@ -95,6 +96,7 @@ typedef struct orc_state orc_state;
 
 orc_model* orc_model_new(const orc_cfg* cfg);
 void orc_model_free(orc_model* m);
+void orc_model_set_ctx_train(orc_model* m, int64_t ctx_train);   /* YaRN when cfg.max_ctx > ctx_train (Model::load :490-517) */
 int orc_model_set_mat(orc_model* m, int layer, int role, const orc_mat* mat);   /* layer -1 = global */
 int orc_model_set_vec(orc_model* m, int layer, int role, const float* v, int64_t n);
 orc_state* orc_state_new(const orc_model* m);

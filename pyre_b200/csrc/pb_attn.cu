@@ -178,6 +178,8 @@ __global__ void __launch_bounds__(AT_THREADS) pb_kv_append_kernel(const PbAttnPa
                 const float other = kraw[h * hd + (i < half ? i + half : i - half)] * (s * p.kn[i < half ? i + half : i - half]);
                 float sn, co;
                 sincosf((float)pos * p.rope_inv[j], &sn, &co);
+                const float ms = p.rope_inv[half];     // YaRN mscale behind the table, applied only when it is not 1 (:528-533)
+                if (ms != 1.0f) { co *= ms; sn *= ms; }
                 x = i < half ? x * co - other * sn : x * co + other * sn;
             }
             kd[i] = x;
@@ -430,6 +432,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
                 const float other = qraw[oi] * (s * p.qn[oi]);
                 float sn, co;
                 sincosf((float)pos * p.rope_inv[j], &sn, &co);
+                const float ms = p.rope_inv[half];
+                if (ms != 1.0f) { co *= ms; sn *= ms; }
                 x = i < half ? x * co - other * sn : x * co + other * sn;
             }
             qs[g * hd + i] = x * scale;

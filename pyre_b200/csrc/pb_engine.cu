@@ -34,7 +34,8 @@ struct pb_model {
     int n_lin = 0, n_attn = 0;
     bool finalized = false;
     int ep_rank = 0, ep_world = 1, e_lo = 0, e_hi = 0;
-    float* rope_inv = nullptr;
+    float* rope_inv = nullptr;   // n_rot / 2 inverse frequencies, then mscale
+    int ctx_train = 0;           // trained context (0: unknown, no scaling)
     uint64_t weight_bytes_step = 0;
 };
 
@@ -155,6 +156,16 @@ int pb_model_set_tensor(pb_model* m, int layer, int role, pb_qmat* mat) {
     return PB_OK;
 }
 
+int pb_model_set_ctx_train(pb_model* m, int ctx_train) {
+    if (!m) return PB_ERR_ARG;
+    pb_ctx* ctx = m->ctx;
+    PB_TRY(pb_enter(ctx));
+    if (ctx_train < 0) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_set_ctx_train: %d", ctx_train);
+    if (m->finalized) PB_FAIL(ctx, PB_ERR_STATE, "pb_model_set_ctx_train: model already finalized");
+    m->ctx_train = ctx_train;
+    return PB_OK;
+}
+
 int pb_model_set_vec(pb_model* m, int layer, int role, const float* v, int64_t n) {
     if (!m) return PB_ERR_ARG;
     pb_ctx* ctx = m->ctx;
@@ -272,9 +283,29 @@ int pb_model_finalize(pb_model* m, int ep_rank, int ep_world) {
         PB_TRY(need_vec(m, il, PB_R_SH_GATE_INP, c.d, "ffn_gate_inp_shexp"));
         wb += M(m, il, PB_R_ROUTER)->nbytes + M(m, il, PB_R_SH_GATE)->nbytes + M(m, il, PB_R_SH_UP)->nbytes + M(m, il, PB_R_SH_DOWN)->nbytes;
     }
-    // rope_inv, qn_ctx.rs:168 (unscaled): base^(-2i/n_rot)
-    std::vector<float> inv((size_t)c.n_rot / 2 + 1);
-    for (int i = 0; i < c.n_rot / 2; i++) inv[i] = powf(c.rope_base, -(2.0f * (float)i) / (float)c.n_rot);
+    // rope_inv, qn_ctx.rs:160-186: base^(-2i/n_rot) at or under the trained context; above it YaRN (beta_fast 32, beta_slow 1:
+    // low indices divided by scale = max_ctx / ctx_train, high indices unchanged, a linear ramp between the correction
+    // dimensions).  The entry behind the table holds mscale = 1 + 0.1 ln(scale), which the kernels apply to cos and sin.
+    const int half = c.n_rot / 2;
+    std::vector<float> inv((size_t)half + 1);
+    const float scale = m->ctx_train > 0 && c.max_ctx > m->ctx_train ? (float)c.max_ctx / (float)m->ctx_train : 1.0f;
+    for (int i = 0; i < half; i++) inv[i] = powf(c.rope_base, -(2.0f * (float)i) / (float)c.n_rot);
+    inv[half] = 1.0f;
+    if (scale > 1.0f) {
+        const float dim = (float)c.n_rot, two_pi = 2.0f * 3.14159265358979323846f;
+        float lo = floorf((dim * logf((float)m->ctx_train / (32.0f * two_pi))) / (2.0f * logf(c.rope_base)));
+        float hi = ceilf((dim * logf((float)m->ctx_train / (1.0f * two_pi))) / (2.0f * logf(c.rope_base)));
+        if (lo < 0.0f) lo = 0.0f;
+        const float top = (float)(half > 0 ? half - 1 : 0);
+        if (hi > top) hi = top;
+        for (int i = 0; i < half; i++) {
+            const float extrap = inv[i], interp = extrap / scale;
+            float ramp = fabsf(hi - lo) < 1e-6f ? 1.0f : ((float)i - lo) / (hi - lo);
+            ramp = ramp < 0.0f ? 0.0f : (ramp > 1.0f ? 1.0f : ramp);
+            inv[i] = interp * (1.0f - ramp) + extrap * ramp;
+        }
+        inv[half] = 1.0f + 0.1f * logf(scale);
+    }
     PB_CUDA(ctx, cudaMalloc(&m->rope_inv, inv.size() * 4));
     PB_CUDA(ctx, cudaMemcpy(m->rope_inv, inv.data(), inv.size() * 4, cudaMemcpyHostToDevice));
     m->weight_bytes_step = wb;

@@ -173,6 +173,7 @@ def load_model(ctx: Ctx, path, max_ctx: int = 4096, kv_bits: int = 4, kv_recent:
                    lin_dk=int(k("ssm.state_size")), lin_dv=int(k("ssm.state_size")), conv_k=int(k("ssm.conv_kernel")), full_every=int(k("full_attention_interval", 4)),
                    vocab=int(g.shape("token_embd.weight")[1]), max_ctx=max_ctx, kv_bits=kv_bits, kv_recent=kv_recent)
     m = Model(ctx, cfg)
+    m.set_ctx_train(int(g.meta.get(f"{a}.context_length", 0)))   # a longer max_ctx is YaRN-scaled (Model::load :490-517)
 
     def mat(layer, role, name, expert_rows=False):
         ty, rows, cols, raw = g.mat(name)

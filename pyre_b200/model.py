@@ -30,6 +30,10 @@ class Model:
         v = _f32(v).reshape(-1)
         self.ctx.check(lib().pb_model_set_vec(self.h, C.c_int(layer), C.c_int(ROLE[role]), _p(v), C.c_int64(v.size)))
 
+    def set_ctx_train(self, ctx_train: int):
+        """Trained context; a larger cfg.max_ctx is YaRN-scaled (before finalize)."""
+        self.ctx.check(lib().pb_model_set_ctx_train(self.h, C.c_int(ctx_train)))
+
     def finalize(self, ep_rank: int = 0, ep_world: int = 1):
         self.ctx.check(lib().pb_model_finalize(self.h, C.c_int(ep_rank), C.c_int(ep_world)))
         self.ep_rank, self.ep_world = ep_rank, ep_world

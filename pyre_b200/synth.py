@@ -92,8 +92,10 @@ def model_spec(cfg: Cfg, seed: int = 0, qtype: int = IQ3_S):
     return spec
 
 
-def build_model(ctx: Ctx, cfg: Cfg, spec, seed: int = 0, ep_rank: int = 0, ep_world: int = 1) -> Model:
+def build_model(ctx: Ctx, cfg: Cfg, spec, seed: int = 0, ep_rank: int = 0, ep_world: int = 1, ctx_train: int = 0) -> Model:
     m = Model(ctx, cfg)
+    if ctx_train:
+        m.set_ctx_train(ctx_train)
     for item in spec:
         if item[0] == "mat":
             _, layer, role, t, rows, cols, tid = item

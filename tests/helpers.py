@@ -12,8 +12,10 @@ def oracle_cfg(cfg):
     return oc
 
 
-def oracle_model(cfg, spec, seed=0):
+def oracle_model(cfg, spec, seed=0, ctx_train=0):
     om = oracle.Model(oracle_cfg(cfg))
+    if ctx_train:
+        om.set_ctx_train(ctx_train)
     mats = {}
     for item in spec:
         if item[0] == "mat":

@@ -327,3 +327,29 @@ def test_hyper_connection_greedy_identity_vs_oracle(ctx, hc):
     for x in (st, s2, w):
         x.destroy()
     m.destroy()
+
+
+@pytest.mark.parametrize("kv_bits", [0, 4])
+def test_yarn_scaled_context_greedy_identity_vs_oracle(ctx, kv_bits):
+    """A context of 256 positions on a model trained on 64: the rope table is YaRN-scaled for the whole run (frequencies
+    and mscale on cos and sin, Model::load :490-517).  Prompt logits within 1e-3 and 48 greedy ids identical to the oracle;
+    and the scaling is really in effect (the logits differ from the same model without a trained-context limit)."""
+    cfg = small_cfg(pb, n_layers=8, kv_bits=kv_bits, kv_recent=64, max_ctx=256)
+    spec = synth.model_spec(cfg, 5)
+    m = synth.build_model(ctx, cfg, spec, 5, ctx_train=64)
+    om, _ = oracle_model(cfg, spec, 5, ctx_train=64)
+    st, ost = m.new_state(1), om.new_state()
+    prompt = list(range(40, 64))     # 24 tokens: below the size from which prompts take the f16 tensor-core GEMM
+    lg, lo = st.forward(np.array(prompt, np.uint32))[0], ost.forward(prompt)
+    assert rel_err(lg, lo) < 1e-3
+    assert int(lg.argmax()) == oracle.argmax(lo)
+    a, b, margins = _greedy_pair(st, ost, int(lg.argmax()), 48)
+    assert a == b, f"diverged at step {next(i for i in range(48) if a[i] != b[i])}; oracle margins there {margins}"
+    m0 = synth.build_model(ctx, cfg, spec, 5)
+    st0 = m0.new_state(1)
+    lg0 = st0.forward(np.array(prompt, np.uint32))[0]
+    assert rel_err(lg0, lg) > 1e-3
+    with pytest.raises(pb.PyreError):
+        m.set_ctx_train(128)          # after finalize
+    assert ctx.device_status() == 0
+    st.destroy(); st0.destroy(); m.destroy(); m0.destroy()

@@ -129,6 +129,26 @@ def test_rope_inv():
     assert np.allclose(inv, 1e7 ** (-(2.0 * np.arange(32)) / 64), rtol=1e-5)
 
 
+def test_yarn_rope_table_against_transformers():
+    """The YaRN table the reference builds past the trained context (src/qn_ctx.rs:160-186), held to vectors computed with
+    Hugging Face transformers (tests/golden/make_hf_yarn_golden.py).  The reference blends interpolated and trained
+    frequencies with the complementary ramp, so the two tables add up to extrap * (1 + 1 / scale) at every index; mscale
+    is the same number.  At or under the trained context the table is the plain one, bit for bit."""
+    g = np.load(GOLD / "hf_yarn.npz")
+    for i, (n_rot, base, tr, ctx) in enumerate(g["cases"]):
+        n_rot, tr, ctx = int(n_rot), int(tr), int(ctx)
+        inv, ms = oracle.rope_inv_yarn(n_rot, float(base), tr, ctx)
+        extrap = float(base) ** (-(2.0 * np.arange(n_rot // 2)) / n_rot)
+        total = extrap * (1.0 + tr / ctx)
+        assert np.max(np.abs((inv + g[f"inv{i}"]) - total) / total) < 1e-6, i
+        assert abs(ms - float(g[f"att{i}"])) < 1e-6, i
+        assert np.all(inv <= extrap * (1 + 1e-6)) and np.all(inv >= extrap * tr / ctx * (1 - 1e-6))
+    inv, ms = oracle.rope_inv_yarn(64, 1e7, 4096, 4096)
+    assert ms == 1.0 and np.array_equal(inv, oracle.rope_inv(64, 1e7))
+    inv, ms = oracle.rope_inv_yarn(64, 1e7, 0, 1 << 20)
+    assert ms == 1.0 and np.array_equal(inv, oracle.rope_inv(64, 1e7))
+
+
 def _qdot_test_block(n: int) -> np.ndarray:
     """The row the reference's own test builds (block, src/model/qdot.rs:1033-1045): bytes from a 64-bit LCG seeded with
     0xC0FFEE ^ n, then a sane f16 scale written over the first two bytes of each of the two 110-byte rows."""
