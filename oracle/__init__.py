@@ -28,6 +28,7 @@ ROLES = [
     "ROUTER", "EXP_GATE", "EXP_UP", "EXP_DOWN", "SH_GATE", "SH_UP", "SH_DOWN", "SH_GATE_INP",
     "HCA_NORM", "HCA_DOWN", "HCA_UP", "HCA_INJECT", "HCF_NORM", "HCF_DOWN", "HCF_UP", "HCF_INJECT",
     "OUT_HC_NORM", "OUT_HC_DOWN", "OUT_HC_UP",
+    "IDX_Q", "IDX_K", "IDX_Q_NORM", "IDX_K_NORM",
 ]
 ROLE = {n: i for i, n in enumerate(ROLES)}
 
@@ -68,6 +69,8 @@ def lib():
         L.orc_model_new.restype = C.c_void_p
         L.orc_state_new.restype = C.c_void_p
         L.orc_threads.restype = C.c_int
+        L.orc_last_qsa_margin.restype = C.c_float
+        L.orc_rope_inv_yarn.restype = C.c_float
         L.orc_set_threads.argtypes = [C.c_int]
         L.orc_set_threads.restype = None
         _lib = L
@@ -255,7 +258,29 @@ def linear_core(cfg: Cfg, qkv, z, beta, alpha, a, dt, conv_w, norm_w, conv_state
     return out
 
 
-def attn_core(cfg: Cfg, qf, kf, vf, qn, kn, inv, kc, vc, pos, packed=None, q4n=0, mscale=1.0):
+def qsa_pool(cfg: Cfg, ratio: int, ik, ikn, inv, b: int, mscale=1.0) -> np.ndarray:
+    """Pooled, normed and roped key of block b from the raw index keys ik [>= (b+1)*ratio][idx_hd]."""
+    ik, ikn = _f32(ik), _f32(ikn)
+    ihd = ik.shape[1]
+    inv = np.concatenate([_f32(inv)[:cfg.n_rot // 2], np.array([mscale], np.float32)])
+    out = np.empty(ihd, np.float32)
+    lib().orc_qsa_pool(C.byref(cfg), C.c_int(ratio), C.c_int(ihd), _p(ik), _p(ikn), _p(inv), C.c_int64(b), _p(out))
+    return out
+
+
+def qsa_select(cfg: Cfg, budget: int, ratio: int, iq_raw, iqn, inv, ib, pos: int, mscale=1.0):
+    """(selected blocks ascending, margin) for the query at pos; ([], inf) in the dense range.  iq_raw [idx_nh][idx_hd]."""
+    iq_raw, iqn, ib = _f32(iq_raw), _f32(iqn), _f32(ib)
+    inh, ihd = iq_raw.shape
+    inv = np.concatenate([_f32(inv)[:cfg.n_rot // 2], np.array([mscale], np.float32)])
+    blocks = np.zeros(budget // ratio + 1, np.int32)
+    mg = C.c_float(float("inf"))
+    k = lib().orc_qsa_select(C.byref(cfg), C.c_int(budget), C.c_int(ratio), C.c_int(inh), C.c_int(ihd), _p(iq_raw), _p(iqn), _p(inv), _p(ib),
+                             C.c_int64(pos), _p(blocks), C.byref(mg))
+    return blocks[:k].copy(), float(mg.value)
+
+
+def attn_core(cfg: Cfg, qf, kf, vf, qn, kn, inv, kc, vc, pos, packed=None, q4n=0, mscale=1.0, ps=None):
     """One new token at position pos.  kc/vc [>=pos+1][n_kv*hd] f32, updated in place at row pos."""
     qf, kf, vf, qn, kn = _f32(qf), _f32(kf), _f32(vf), _f32(qn), _f32(kn)
     inv = np.concatenate([_f32(inv)[:cfg.n_rot // 2], np.array([mscale], np.float32)])   # the C side reads mscale behind the table
@@ -264,8 +289,10 @@ def attn_core(cfg: Cfg, qf, kf, vf, qn, kn, inv, kc, vc, pos, packed=None, q4n=0
         kw = ks = vw = vs = None
     else:
         kw, ks, vw, vs = (_p(a) for a in packed)
-    lib().orc_attn_core(C.byref(cfg), _p(qf), _p(kf), _p(vf), _p(qn), _p(kn), _p(inv), _p(kc), _p(vc), C.c_int64(pos),
-                        kw, ks, vw, vs, C.c_int64(q4n), _p(att))
+    if ps is not None:
+        ps = np.ascontiguousarray(ps, dtype=np.int64)
+    lib().orc_attn_core_sel(C.byref(cfg), _p(qf), _p(kf), _p(vf), _p(qn), _p(kn), _p(inv), _p(kc), _p(vc), C.c_int64(pos),
+                            kw, ks, vw, vs, C.c_int64(q4n), _p(ps) if ps is not None else None, C.c_int64(0 if ps is None else ps.size), _p(att))
     return att
 
 
@@ -286,6 +313,10 @@ class Model:
     def set_ctx_train(self, ctx_train: int):
         """YaRN rope scaling when cfg.max_ctx exceeds the trained context."""
         lib().orc_model_set_ctx_train(self.h, C.c_int64(ctx_train))
+
+    def set_indexer(self, budget: int, ratio: int, n_head: int, head_dim: int):
+        """QSA block-sparse attention: layers that hold IDX_Q / IDX_K attend to budget / ratio blocks of ratio tokens."""
+        lib().orc_model_set_indexer(self.h, C.c_int(budget), C.c_int(ratio), C.c_int(n_head), C.c_int(head_dim))
 
     def new_state(self) -> "State":
         return State(self)
@@ -322,6 +353,11 @@ class State:
         a, b = C.c_float(), C.c_float()
         lib().orc_last_margins(self.h, C.byref(a), C.byref(b))
         return a.value, b.value
+
+    def qsa_margin(self) -> float:
+        """Smallest gap between the last block taken and the best block left out over the sparse queries of the last
+        forward call (inf when none was sparse): a tiny value marks a selection that rounding may turn."""
+        return float(lib().orc_last_qsa_margin(self.h))
 
     def __del__(self):
         try:

@@ -526,31 +526,74 @@ void orc_attn_core(const orc_cfg* c, const float* qf, const float* kf_in, const 
                    float* kc, float* vc, int64_t pos,
                    const uint32_t* kw, const float* ks, const uint32_t* vw, const float* vs, int64_t q4n,
                    float* att) {  /* attn_core :1558-1615, dense branch, one token */
+    orc_attn_core_sel(c, qf, kf_in, vf, qn, kn, inv, kc, vc, pos, kw, ks, vw, vs, q4n, NULL, 0, att);
+}
+/* The same with the key positions the query attends to (`ps`, ascending, `nps` of them; NULL = every position <= pos):
+ * the softmax runs over the listed positions only (:1605-1609, `sel`). */
+void orc_attn_core_sel(const orc_cfg* c, const float* qf, const float* kf_in, const float* vf,
+                       const float* qn, const float* kn, const float* inv,
+                       float* kc, float* vc, int64_t pos,
+                       const uint32_t* kw, const float* ks, const uint32_t* vw, const float* vs, int64_t q4n,
+                       const int64_t* ps, int64_t nps, float* att) {
     int nh = c->n_head, nkv = c->n_kv, hd = c->hd; int row = nkv * hd; int grp = nh / nkv;
     /* k: RMSNorm * kn, rope, append (:1563-1564) */
     float* kf = kc + pos * row; memcpy(kf, kf_in, (size_t)row * 4);
     for (int h = 0; h < nkv; h++) { rms_inplace(kf + h * hd, kn, c->eps, hd); rope(kf + h * hd, pos, inv, c->n_rot); }
     memcpy(vc + pos * row, vf, (size_t)row * 4);
-    float scale = 1.0f / sqrtf((float)hd); int64_t n = pos + 1;
+    float scale = 1.0f / sqrtf((float)hd); int64_t n = ps ? nps : pos + 1;
     #pragma omp parallel for schedule(static)
     for (int h = 0; h < nh; h++) {
         float* out = att + h * hd; for (int i = 0; i < hd; i++) out[i] = 0.0f;
         int base = h * 2 * hd; float qh[1024]; memcpy(qh, qf + base, (size_t)hd * 4); rms_inplace(qh, qn, c->eps, hd); rope(qh, pos, inv, c->n_rot);  /* :1603-1604 */
         int kvh = h / grp; float* sc = (float*)malloc((size_t)n * 4); float krow[1024];
-        for (int64_t p = 0; p < n; p++) {
+        for (int64_t j = 0; j < n; j++) {
+            const int64_t p = ps ? ps[j] : j;
             const float* kp;
             if (kw && p < q4n) { for (int i = 0; i < hd; i++) krow[i] = orc_kv4_get(kw, ks, p * row + kvh * hd + i); kp = krow; } else kp = kc + p * row + kvh * hd;
-            sc[p] = orc_dot(qh, kp, hd) * scale;
+            sc[j] = orc_dot(qh, kp, hd) * scale;
         }
-        float mx = -INFINITY; for (int64_t p = 0; p < n; p++) mx = fmaxf(mx, sc[p]);
-        float sum = 0.0f; for (int64_t p = 0; p < n; p++) { sc[p] = expf(sc[p] - mx); sum += sc[p]; }
+        float mx = -INFINITY; for (int64_t j = 0; j < n; j++) mx = fmaxf(mx, sc[j]);
+        float sum = 0.0f; for (int64_t j = 0; j < n; j++) { sc[j] = expf(sc[j] - mx); sum += sc[j]; }
         float invs = 1.0f / sum;
-        for (int64_t p = 0; p < n; p++) { float wgt = sc[p] * invs;
+        for (int64_t j = 0; j < n; j++) { const int64_t p = ps ? ps[j] : j; float wgt = sc[j] * invs;
             if (vw && p < q4n) { for (int i = 0; i < hd; i++) out[i] += wgt * orc_kv4_get(vw, vs, p * row + kvh * hd + i); }
             else { const float* vv = vc + p * row + kvh * hd; for (int i = 0; i < hd; i++) out[i] += wgt * vv[i]; } }
         const float* gate = qf + base + hd; for (int i = 0; i < hd; i++) out[i] *= sigm(gate[i]);  /* :1610 */
         free(sc);
     }
+}
+
+/* ------------------------------------------------------------------ QSA block-sparse selection (attn_core :1565-1599)
+ *
+ * Blocks of `ratio` tokens.  Every complete block has a pooled key: the mean of its tokens' raw index keys, RMS-normed
+ * with the index key norm, roped at the block's first position.  A query past the dense range (more than
+ * budget + ratio - 1 visible tokens, dense_n :1555) scores every complete block with
+ *     sum over index heads of relu(q_h . pooled_b) / sqrt(idx_hd),   q_h = rope(rms(raw q_h) * q_norm, pos)
+ * and attends to the budget / ratio best blocks plus the incomplete tail.  The reference picks them with
+ * select_nth_unstable_by, which leaves the order among equal scores open; here: higher score first, lower block first. */
+void orc_qsa_pool(const orc_cfg* c, int ratio, int ihd, const float* ik, const float* ikn, const float* inv, int64_t b, float* out) {
+    for (int i = 0; i < ihd; i++) out[i] = 0.0f;
+    for (int64_t p = b * ratio; p < (b + 1) * ratio; p++) for (int i = 0; i < ihd; i++) out[i] += ik[p * ihd + i];
+    for (int i = 0; i < ihd; i++) out[i] /= (float)ratio;
+    rms_inplace(out, ikn, c->eps, ihd); rope(out, b * ratio, inv, c->n_rot);
+}
+/* blocks[0 .. budget/ratio) <- the selected blocks, ascending; returns their number (0 when the query is in the dense
+ * range).  *margin (may be NULL) <- score of the last block taken minus score of the best block left out. */
+int orc_qsa_select(const orc_cfg* c, int budget, int ratio, int inh, int ihd, const float* iq_raw, const float* iqn, const float* inv,
+                   const float* ib, int64_t pos, int32_t* blocks, float* margin) {
+    int64_t n = pos + 1; if (n <= (int64_t)budget + ratio - 1) return 0;
+    int64_t nb = n / ratio; int kk = budget / ratio; float iscale = 1.0f / sqrtf((float)ihd);
+    float* q = (float*)malloc((size_t)inh * ihd * 4); memcpy(q, iq_raw, (size_t)inh * ihd * 4);
+    for (int h = 0; h < inh; h++) { rms_inplace(q + h * ihd, iqn, c->eps, ihd); rope(q + h * ihd, pos, inv, c->n_rot); }
+    float* sc = (float*)malloc((size_t)nb * 4); uint8_t* taken = (uint8_t*)calloc((size_t)nb, 1);
+    for (int64_t b = 0; b < nb; b++) { float s = 0.0f; for (int h = 0; h < inh; h++) { float d = orc_dot(q + h * ihd, ib + b * ihd, ihd); s += d > 0.0f ? d : 0.0f; } sc[b] = s * iscale; }
+    float last = INFINITY;
+    for (int j = 0; j < kk; j++) { int64_t best = -1; for (int64_t b = 0; b < nb; b++) if (!taken[b] && (best < 0 || sc[b] > sc[best])) best = b; taken[best] = 1; last = sc[best]; }
+    float nxt = -INFINITY; int k = 0;
+    for (int64_t b = 0; b < nb; b++) { if (taken[b]) blocks[k++] = (int32_t)b; else nxt = fmaxf(nxt, sc[b]); }
+    if (margin) *margin = last - nxt;
+    free(q); free(sc); free(taken);
+    return k;
 }
 
 /* ------------------------------------------------------------------ model / token loop */
@@ -561,6 +604,7 @@ struct orc_model {
     orc_cfg cfg;
     orc_slot* slots;   /* [(n_layers + 1)][ORC_R_COUNT], index 0 = global */
     float* rope_inv;
+    int idx_budget, idx_ratio, idx_nh, idx_hd;   /* QSA indexer (Cfg :24-25); idx_nh = 0: none */
 };
 struct orc_state {
     const orc_model* m;
@@ -569,7 +613,8 @@ struct orc_state {
     float** k; float** v;                /* per attention layer, f32 [max_ctx][row] (rows < q4n are stale) */
     uint32_t** kw; float** ks; uint32_t** vw; float** vs; int64_t* q4n;
     int n_lin, n_attn;
-    float logit_margin, router_margin;
+    float** ik; float** ib;              /* per attention layer: raw index keys [max_ctx][idx_hd], pooled block keys [max_ctx/ratio][idx_hd] (State :194) */
+    float logit_margin, router_margin, qsa_margin;
 };
 
 static orc_slot* slot(const orc_model* m, int layer, int role) { return &m->slots[(size_t)(layer + 1) * ORC_R_COUNT + role]; }
@@ -588,6 +633,10 @@ void orc_model_free(orc_model* m) {
     if (!m) return;
     for (size_t i = 0; i < (size_t)(m->cfg.n_layers + 1) * ORC_R_COUNT; i++) free(m->slots[i].vec);
     free(m->slots); free(m->rope_inv); free(m);
+}
+/* QSA indexer geometry (Cfg :24-25, keys attention.indexer.* :481-485); layers that have ORC_R_IDX_Q use it */
+void orc_model_set_indexer(orc_model* m, int budget, int ratio, int n_head, int head_dim) {
+    m->idx_budget = budget; m->idx_ratio = ratio < 1 ? 1 : ratio; m->idx_nh = n_head; m->idx_hd = head_dim;
 }
 /* Model::load :490-517: a context (cfg.max_ctx) past the trained length is YaRN-scaled for the whole run */
 void orc_model_set_ctx_train(orc_model* m, int64_t ctx_train) {
@@ -612,7 +661,9 @@ orc_state* orc_state_new(const orc_model* m) {  /* new_state :1345-1353 */
     s->k = (float**)calloc((size_t)na, sizeof(float*)); s->v = (float**)calloc((size_t)na, sizeof(float*));
     s->kw = (uint32_t**)calloc((size_t)na, sizeof(void*)); s->vw = (uint32_t**)calloc((size_t)na, sizeof(void*));
     s->ks = (float**)calloc((size_t)na, sizeof(void*)); s->vs = (float**)calloc((size_t)na, sizeof(void*)); s->q4n = (int64_t*)calloc((size_t)na, 8);
+    s->ik = (float**)calloc((size_t)na, sizeof(void*)); s->ib = (float**)calloc((size_t)na, sizeof(void*));
     for (int i = 0; i < s->n_attn; i++) {
+        if (m->idx_nh > 0) { s->ik[i] = (float*)calloc((size_t)c->max_ctx * m->idx_hd, 4); s->ib[i] = (float*)calloc((size_t)(c->max_ctx / m->idx_ratio + 1) * m->idx_hd, 4); }
         s->k[i] = (float*)calloc((size_t)c->max_ctx * row, 4); s->v[i] = (float*)calloc((size_t)c->max_ctx * row, 4);
         if (c->kv_bits == 4) { s->kw[i] = (uint32_t*)calloc((size_t)c->max_ctx * row / 8, 4); s->vw[i] = (uint32_t*)calloc((size_t)c->max_ctx * row / 8, 4);
             s->ks[i] = (float*)calloc((size_t)c->max_ctx * row / 32, 4); s->vs[i] = (float*)calloc((size_t)c->max_ctx * row / 32, 4); }
@@ -622,8 +673,8 @@ orc_state* orc_state_new(const orc_model* m) {  /* new_state :1345-1353 */
 void orc_state_free(orc_state* s) {
     if (!s) return;
     for (int i = 0; i < s->n_lin; i++) { free(s->conv[i]); free(s->ssm[i]); }
-    for (int i = 0; i < s->n_attn; i++) { free(s->k[i]); free(s->v[i]); free(s->kw[i]); free(s->vw[i]); free(s->ks[i]); free(s->vs[i]); }
-    free(s->conv); free(s->ssm); free(s->k); free(s->v); free(s->kw); free(s->vw); free(s->ks); free(s->vs); free(s->q4n); free(s);
+    for (int i = 0; i < s->n_attn; i++) { free(s->k[i]); free(s->v[i]); free(s->kw[i]); free(s->vw[i]); free(s->ks[i]); free(s->vs[i]); free(s->ik[i]); free(s->ib[i]); }
+    free(s->ik); free(s->ib); free(s->conv); free(s->ssm); free(s->k); free(s->v); free(s->kw); free(s->vw); free(s->ks); free(s->vs); free(s->q4n); free(s);
 }
 /* Layout rule of the packed region (kv_push :1517-1534): with len positions held, the first
  * q4n = ((len - recent) / 64) * 64 are 4-bit (whole multiples of 64 positions), the rest f32. */
@@ -642,6 +693,7 @@ int orc_state_fill_kv(orc_state* s, int ai, const float* k, const float* v, int6
 }
 int orc_state_set_pos(orc_state* s, int64_t pos) { s->pos = pos; return 0; }
 void orc_last_margins(const orc_state* s, float* a, float* b) { if (a) *a = s->logit_margin; if (b) *b = s->router_margin; }
+float orc_last_qsa_margin(const orc_state* s) { return s->qsa_margin; }   /* smallest selection margin of the last forward call (INFINITY: no sparse query) */
 
 /* hc_mix :1357-1382 (f32 branch).  x [t][hc*d] -> mixed [t][d], inj [t][hc] */
 static void hc_mix(const orc_model* m, int layer, int r_norm, int r_down, int r_up, int r_inj, const float* x, int t, float* mixed, float* inj) {
@@ -672,7 +724,7 @@ int orc_forward(const orc_model* m, orc_state* st, const uint32_t* ids, int t, f
     float* x = (float*)malloc((size_t)t * xw * 4); float* mx = (float*)malloc((size_t)t * d * 4); float* o = (float*)malloc((size_t)t * d * 4); float* inj = (float*)malloc((size_t)t * (hc > 0 ? hc : 1) * 4);
     const orc_mat* embd = M(m, -1, ORC_R_TOKEN_EMBD);
     for (int ti = 0; ti < t; ti++) { orc_mat_row(embd, ids[ti], o); for (int s = 0; s < (hc > 0 ? hc : 1); s++) memcpy(x + ((int64_t)ti * (hc > 0 ? hc : 1) + s) * d, o, (size_t)d * 4); }  /* :2092 */
-    int li = 0, ai = 0; st->router_margin = INFINITY;
+    int li = 0, ai = 0; st->router_margin = INFINITY; st->qsa_margin = INFINITY;
     int nk = c->lin_nk, nv = c->lin_nv, dk = c->lin_dk, dv = c->lin_dv; int ch = 2 * nk * dk + nv * dv; int row = c->n_kv * c->hd;
     for (int il = 0; il < c->n_layers; il++) {
         if (hc > 0) hc_mix(m, il, ORC_R_HCA_NORM, ORC_R_HCA_DOWN, ORC_R_HCA_UP, ORC_R_HCA_INJECT, x, t, mx, inj);
@@ -680,14 +732,29 @@ int orc_forward(const orc_model* m, orc_state* st, const uint32_t* ids, int t, f
         if (is_full(c, il)) {  /* attn :1441-1446 */
             int nq = c->n_head * 2 * c->hd; float* qf = (float*)malloc((size_t)t * nq * 4); float* kf = (float*)malloc((size_t)t * row * 4); float* vf = (float*)malloc((size_t)t * row * 4); float* att = (float*)malloc((size_t)t * c->n_head * c->hd * 4);
             orc_matmul(M(m, il, ORC_R_ATTN_Q), mx, t, qf); orc_matmul(M(m, il, ORC_R_ATTN_K), mx, t, kf); orc_matmul(M(m, il, ORC_R_ATTN_V), mx, t, vf);
+            /* QSA indexer: two more projections of the same input (:1567-1569) */
+            const int qsa = m->idx_nh > 0 && M(m, il, ORC_R_IDX_Q) != NULL; const int inh = m->idx_nh, ihd = m->idx_hd, ir = m->idx_ratio;
+            float* iqf = NULL; float* ikf = NULL; int32_t* blk = NULL; int64_t* ps = NULL;
+            if (qsa) { iqf = (float*)malloc((size_t)t * inh * ihd * 4); ikf = (float*)malloc((size_t)t * ihd * 4); blk = (int32_t*)malloc((size_t)(m->idx_budget / ir + 1) * 4); ps = (int64_t*)malloc((size_t)(m->idx_budget + 2 * ir) * 8);
+                orc_matmul(M(m, il, ORC_R_IDX_Q), mx, t, iqf); orc_matmul(M(m, il, ORC_R_IDX_K), mx, t, ikf); }
             for (int ti = 0; ti < t; ti++) {
                 int64_t pos = start + ti;
                 /* the packed boundary follows the row count after the append (pos + 1 rows); the rows it
                  * covers are all older than the recent window, so they are already normed and roped */
                 kv_repack(st, ai, pos + 1);
-                orc_attn_core(c, qf + (int64_t)ti * nq, kf + (int64_t)ti * row, vf + (int64_t)ti * row, V(m, il, ORC_R_ATTN_Q_NORM), V(m, il, ORC_R_ATTN_K_NORM), m->rope_inv,
-                              st->k[ai], st->v[ai], pos, st->kw[ai], st->ks[ai], st->vw[ai], st->vs[ai], st->q4n[ai], att + (int64_t)ti * c->n_head * c->hd);
+                int64_t nps = 0;
+                if (qsa) {
+                    memcpy(st->ik[ai] + pos * ihd, ikf + (int64_t)ti * ihd, (size_t)ihd * 4);
+                    if ((pos + 1) % ir == 0) orc_qsa_pool(c, ir, ihd, st->ik[ai], V(m, il, ORC_R_IDX_K_NORM), m->rope_inv, pos / ir, st->ib[ai] + (pos / ir) * ihd);
+                    float mg; int k = orc_qsa_select(c, m->idx_budget, ir, inh, ihd, iqf + (int64_t)ti * inh * ihd, V(m, il, ORC_R_IDX_Q_NORM), m->rope_inv, st->ib[ai], pos, blk, &mg);
+                    if (k > 0) { for (int j = 0; j < k; j++) for (int e = 0; e < ir; e++) ps[nps++] = (int64_t)blk[j] * ir + e;
+                        for (int64_t p = ((pos + 1) / ir) * ir; p <= pos; p++) ps[nps++] = p;
+                        st->qsa_margin = fminf(st->qsa_margin, mg); }
+                }
+                orc_attn_core_sel(c, qf + (int64_t)ti * nq, kf + (int64_t)ti * row, vf + (int64_t)ti * row, V(m, il, ORC_R_ATTN_Q_NORM), V(m, il, ORC_R_ATTN_K_NORM), m->rope_inv,
+                                  st->k[ai], st->v[ai], pos, st->kw[ai], st->ks[ai], st->vw[ai], st->vs[ai], st->q4n[ai], nps > 0 ? ps : NULL, nps, att + (int64_t)ti * c->n_head * c->hd);
             }
+            free(iqf); free(ikf); free(blk); free(ps);
             orc_matmul(M(m, il, ORC_R_ATTN_O), att, t, o); free(qf); free(kf); free(vf); free(att); ai++;
         } else {  /* linear :1617-1621 */
             float* qkv = (float*)malloc((size_t)t * ch * 4); float* z = (float*)malloc((size_t)t * nv * dv * 4); float* be = (float*)malloc((size_t)t * nv * 4); float* al = (float*)malloc((size_t)t * nv * 4); float* oa = (float*)malloc((size_t)t * nv * dv * 4);

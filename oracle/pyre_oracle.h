@@ -88,6 +88,7 @@ enum {
     ORC_R_HCA_NORM, ORC_R_HCA_DOWN, ORC_R_HCA_UP, ORC_R_HCA_INJECT,
     ORC_R_HCF_NORM, ORC_R_HCF_DOWN, ORC_R_HCF_UP, ORC_R_HCF_INJECT,
     ORC_R_OUT_HC_NORM, ORC_R_OUT_HC_DOWN, ORC_R_OUT_HC_UP,
+    ORC_R_IDX_Q, ORC_R_IDX_K, ORC_R_IDX_Q_NORM, ORC_R_IDX_K_NORM,   /* QSA indexer of an attention layer (Mixer::Attn idx, :501) */
     ORC_R_COUNT
 };
 
@@ -96,6 +97,7 @@ typedef struct orc_state orc_state;
 
 orc_model* orc_model_new(const orc_cfg* cfg);
 void orc_model_free(orc_model* m);
+void orc_model_set_indexer(orc_model* m, int budget, int ratio, int n_head, int head_dim);   /* QSA geometry, Cfg :24-25 */
 void orc_model_set_ctx_train(orc_model* m, int64_t ctx_train);   /* YaRN when cfg.max_ctx > ctx_train (Model::load :490-517) */
 int orc_model_set_mat(orc_model* m, int layer, int role, const orc_mat* mat);   /* layer -1 = global */
 int orc_model_set_vec(orc_model* m, int layer, int role, const float* v, int64_t n);
@@ -108,6 +110,7 @@ int orc_state_set_pos(orc_state* s, int64_t pos);
 int orc_forward(const orc_model* m, orc_state* s, const uint32_t* ids, int t, float* logits);
 /* per-step margins for near-tie classification: top-2 logit margin, min 10th/11th router margin */
 void orc_last_margins(const orc_state* s, float* logit_margin, float* router_margin);
+float orc_last_qsa_margin(const orc_state* s);
 
 /* ---- layer-level entry points (same arithmetic as inside orc_forward) ---- */
 /* MoE block: ffn :1675-1684 + routed (f32 branch) :1721-1793.  x [t][d] -> y [t][d].
@@ -128,6 +131,16 @@ void orc_attn_core(const orc_cfg* c, const float* qf, const float* kf, const flo
                    float* kc, float* vc, int64_t pos,
                    const uint32_t* kw, const float* ks, const uint32_t* vw, const float* vs, int64_t q4n,
                    float* att);
+/* the same over a list of key positions (ascending; NULL = all positions <= pos): the QSA sparse branch, :1605-1609 */
+void orc_attn_core_sel(const orc_cfg* c, const float* qf, const float* kf, const float* vf,
+                       const float* qn, const float* kn, const float* rope_inv,
+                       float* kc, float* vc, int64_t pos,
+                       const uint32_t* kw, const float* ks, const uint32_t* vw, const float* vs, int64_t q4n,
+                       const int64_t* ps, int64_t nps, float* att);
+/* QSA indexer pieces (attn_core :1565-1599): pooled key of block b; the blocks a query at `pos` attends to */
+void orc_qsa_pool(const orc_cfg* c, int ratio, int ihd, const float* ik, const float* ikn, const float* rope_inv, int64_t b, float* out);
+int orc_qsa_select(const orc_cfg* c, int budget, int ratio, int inh, int ihd, const float* iq_raw, const float* iqn, const float* rope_inv,
+                   const float* ib, int64_t pos, int32_t* blocks, float* margin);
 
 #ifdef __cplusplus
 }

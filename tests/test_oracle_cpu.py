@@ -226,3 +226,50 @@ def test_gated_attention_against_transformers_qwen3_next_vectors():
     for pos in range(t):
         att = oracle.attn_core(cfg, g["qf"][pos], g["kf"][pos], g["vf"][pos], g["q_norm"], g["k_norm"], inv, kc, vc, pos)
         assert rel_err(att, g["att"][pos]) < 2e-5, pos
+
+
+def test_qsa_selection_and_sparse_attention_properties():
+    """QSA (attn_core, src/model/qwen4exp_gguf.rs:1565-1609) as the oracle restates it: the pooled key is the normed, roped
+    mean of a block's raw keys; the dense range ends at budget + ratio - 1 tokens; a query past it takes exactly
+    budget / ratio complete blocks, the best-scoring ones by an independent numpy evaluation; attention over a position
+    list that holds every position equals dense attention, and dropping a position changes it."""
+    cfg = oracle.make_cfg(n_head=4, n_kv=2, hd=64, n_rot=32, max_ctx=128, kv_bits=0)
+    budget, ratio, inh, ihd = 16, 4, 3, 32
+    rng = np.random.default_rng(11)
+    inv = oracle.rope_inv(cfg.n_rot, 1e4)
+    ik = rng.standard_normal((80, ihd)).astype(np.float32)
+    ikn = (1 + 0.1 * rng.standard_normal(ihd)).astype(np.float32); iqn = (1 + 0.1 * rng.standard_normal(ihd)).astype(np.float32)
+
+    def rope(v, pos):
+        half = cfg.n_rot // 2; a = pos * inv.astype(np.float64); o = v.astype(np.float64).copy()
+        o[:half] = v[:half] * np.cos(a) - v[half:2 * half] * np.sin(a); o[half:2 * half] = v[half:2 * half] * np.cos(a) + v[:half] * np.sin(a)
+        return o
+
+    def norm(v, w):
+        v = v.astype(np.float64); return v / np.sqrt((v * v).mean() + cfg.eps) * w
+
+    ib = np.stack([oracle.qsa_pool(cfg, ratio, ik, ikn, inv, b) for b in range(20)])
+    for b in (0, 7, 19):
+        assert np.allclose(ib[b], rope(norm(ik[b * ratio:(b + 1) * ratio].astype(np.float64).mean(0), ikn), b * ratio), atol=2e-6)
+    iq = rng.standard_normal((inh, ihd)).astype(np.float32)
+    blocks, _ = oracle.qsa_select(cfg, budget, ratio, iq, iqn, inv, ib, budget + ratio - 2)
+    assert blocks.size == 0                                   # budget + ratio - 1 visible tokens: still dense
+    pos = 61
+    blocks, margin = oracle.qsa_select(cfg, budget, ratio, iq, iqn, inv, ib, pos)
+    nb = (pos + 1) // ratio
+    qh = np.stack([rope(norm(iq[h], iqn), pos) for h in range(inh)])
+    sc = np.maximum(qh @ ib[:nb].astype(np.float64).T, 0).sum(0) / np.sqrt(ihd)
+    want = np.sort(np.argsort(-sc, kind="stable")[:budget // ratio])
+    assert blocks.tolist() == want.tolist() and margin > 0 and np.all(np.diff(blocks) > 0)
+    srt = np.sort(sc)[::-1]
+    assert abs(margin - (srt[budget // ratio - 1] - srt[budget // ratio])) < 1e-5
+    # attention over a full list == dense; a shorter list differs
+    row = cfg.n_kv * cfg.hd; n = 40
+    kc = rng.standard_normal((n, row)).astype(np.float32); vc = rng.standard_normal((n, row)).astype(np.float32)
+    qf = rng.standard_normal(cfg.n_head * 2 * cfg.hd).astype(np.float32); kf = rng.standard_normal(row).astype(np.float32); vf = rng.standard_normal(row).astype(np.float32)
+    qn = np.ones(cfg.hd, np.float32); kn = np.ones(cfg.hd, np.float32)
+    dense = oracle.attn_core(cfg, qf, kf, vf, qn, kn, inv, kc.copy(), vc.copy(), n - 1)
+    full = oracle.attn_core(cfg, qf, kf, vf, qn, kn, inv, kc.copy(), vc.copy(), n - 1, ps=np.arange(n))
+    assert np.array_equal(dense, full)
+    part = oracle.attn_core(cfg, qf, kf, vf, qn, kn, inv, kc.copy(), vc.copy(), n - 1, ps=np.arange(1, n))
+    assert rel_err(part, dense) > 1e-4
