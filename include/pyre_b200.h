@@ -160,6 +160,8 @@ typedef enum pb_role {
     PB_R_HCA_NORM, PB_R_HCA_DOWN, PB_R_HCA_UP, PB_R_HCA_INJECT,
     PB_R_HCF_NORM, PB_R_HCF_DOWN, PB_R_HCF_UP, PB_R_HCF_INJECT,
     PB_R_OUT_HC_NORM, PB_R_OUT_HC_DOWN, PB_R_OUT_HC_UP,
+    /* QSA indexer of an attention layer (Mixer::Attn idx, :501): blk.N.indexer.q_proj / k_proj / q_norm / k_norm */
+    PB_R_IDX_Q, PB_R_IDX_K, PB_R_IDX_Q_NORM, PB_R_IDX_K_NORM,
     PB_R_COUNT
 } pb_role;
 
@@ -168,6 +170,11 @@ typedef enum pb_role {
 int pb_model_create(pb_ctx* ctx, const pb_cfg* cfg, pb_model** out);
 int pb_model_set_tensor(pb_model* m, int layer, int role, pb_qmat* mat);   /* the model takes ownership */
 int pb_model_set_vec(pb_model* m, int layer, int role, const float* v_host, int64_t n);
+/* QSA block-sparse attention (attn_core, src/model/qwen4exp_gguf.rs:1565-1599; Cfg :24-25, keys attention.indexer.* :481-485).
+ * `budget` tokens in blocks of `ratio`; the attention layers that hold PB_R_IDX_* tensors then attend, once a query sees
+ * more than budget + ratio - 1 tokens, to the budget / ratio best-scoring blocks plus the incomplete tail.  n_head = 0
+ * (the default) switches it off.  Before pb_model_finalize. */
+int pb_model_set_indexer(pb_model* m, int budget, int ratio, int n_head, int head_dim);
 /* Trained context of the checkpoint (`<arch>.context_length`).  When cfg.max_ctx exceeds it, the rope table is YaRN-scaled
  * for the whole run as the reference does at load (src/model/qwen4exp_gguf.rs:490-517, table src/qn_ctx.rs:160-186, mscale on
  * cos and sin :528-533); 0 (the default) or max_ctx <= ctx_train leave the plain table.  Before pb_model_finalize. */
@@ -191,8 +198,10 @@ int pb_state_destroy(pb_state* s);
  * roped K and V rows [n][n_kv*hd] (f32, host); packs per cfg.kv_bits.  Benchmark set-up for a
  * long context without running a prefill. */
 int pb_state_fill_kv(pb_state* s, int b, int attn_index, const float* k_host, const float* v_host, int64_t n);
-/* Same with seeded synthetic N(0,1) rows generated on the GPU. */
+/* Same with seeded synthetic N(0,1) rows generated on the GPU (and, for a model with an indexer, synthetic raw index keys). */
 int pb_state_fill_kv_synth(pb_state* s, int attn_index, int64_t n, uint64_t seed);
+/* Models with an indexer: the raw index keys [n][idx_hd] (f32, host) of the same n positions; the pooled block keys are derived. */
+int pb_state_fill_index_keys(pb_state* s, int b, int attn_index, const float* ik_host, int64_t n);
 int pb_state_set_pos(pb_state* s, int64_t pos);
 /* A fresh conversation in an existing state: position 0, the DeltaNet conv history and recurrent state zeroed, the packed
  * boundary of the 4-bit KV cache back to 0 (Model::new_state, src/model/qwen4exp_gguf.rs:3199-3213, without its allocations). */

@@ -33,6 +33,7 @@ ROLES = [
     "ROUTER", "EXP_GATE", "EXP_UP", "EXP_DOWN", "SH_GATE", "SH_UP", "SH_DOWN", "SH_GATE_INP",
     "HCA_NORM", "HCA_DOWN", "HCA_UP", "HCA_INJECT", "HCF_NORM", "HCF_DOWN", "HCF_UP", "HCF_INJECT",
     "OUT_HC_NORM", "OUT_HC_DOWN", "OUT_HC_UP",
+    "IDX_Q", "IDX_K", "IDX_Q_NORM", "IDX_K_NORM",
 ]
 ROLE = {n: i for i, n in enumerate(ROLES)}
 

@@ -250,7 +250,7 @@ __device__ __forceinline__ float pb_exp2i(int k) { k = k < -126 ? -126 : (k > 12
 //     and the rounding remainder in a second one.
 template <int G>
 __device__ __forceinline__ void pb_attn_mma_tiles(const float* qs, uint32_t* stage, int warp, int lane, int sp, int nsp, const uint32_t* kw,
-                                                  const uint32_t* vw, const float* ks, const float* vs, int64_t ntiles, float* mw) {
+                                                  const uint32_t* vw, const float* ks, const float* vs, int64_t ntiles, float* mw, const uint32_t* mk) {
     constexpr int HD = 256;
     const int g = lane >> 2, q = lane & 3, sh = 4 * q;
     // A fragments of the scores: rows 0..7 = the f16 of the heads' queries, rows 8..15 = what that rounding lost;
@@ -287,12 +287,18 @@ __device__ __forceinline__ void pb_attn_mma_tiles(const float* qs, uint32_t* sta
         pb_cp_async16(bs + 256 + 4 * lane, gvs + lane); pb_cp_async16(bs + 384 + 4 * lane, gvs + 32 + lane);
         pb_cp_async_commit();
     };
-    const int64_t t_first = (int64_t)warp * nsp + sp, t_step = (int64_t)AT_WARPS * nsp;
+    // with a position mask (mk: one word per tile), tiles without a set bit are skipped before they are fetched
+    const int64_t t_step = (int64_t)AT_WARPS * nsp;
+    int64_t t_first = (int64_t)warp * nsp + sp;
+    while (mk && t_first < ntiles && mk[t_first] == 0u) t_first += t_step;
     if (t_first < ntiles) fetch(t_first, 0);
     int buf = 0;
-    for (int64_t t = t_first; t < ntiles; t += t_step, buf ^= 1) {
+    for (int64_t t = t_first, t_next; t < ntiles; t = t_next, buf ^= 1) {
         {
-            if (t + t_step < ntiles) { fetch(t + t_step, buf ^ 1); pb_cp_async_wait<1>(); } else pb_cp_async_wait<0>();
+            t_next = t + t_step;
+            while (mk && t_next < ntiles && mk[t_next] == 0u) t_next += t_step;
+            const uint32_t mword = mk ? mk[t] : 0xFFFFFFFFu;
+            if (t_next < ntiles) { fetch(t_next, buf ^ 1); pb_cp_async_wait<1>(); } else pb_cp_async_wait<0>();
             __syncwarp();   // every lane's pieces of this tile have landed
             uint32_t* tk = stage + buf * AT_BUF_WORDS; uint32_t* tv = tk + 32 * AT_KSTRIDE;
             float* tks = reinterpret_cast<float*>(tv + 1024); float* tvs = tks + 256;
@@ -326,6 +332,9 @@ __device__ __forceinline__ void pb_attn_mma_tiles(const float* qs, uint32_t* sta
                     s0 = fmaf(sk[blk], c4[0] + c4[2], s0);
                     s1 = fmaf(sk[32 + blk], c4[1] + c4[3], s1);
                 }
+                // positions q and q + 4 of group nt; unselected ones leave the softmax
+                if (!((mword >> (8 * nt + q)) & 1u)) s0 = -INFINITY;
+                if (!((mword >> (8 * nt + q + 4)) & 1u)) s1 = -INFINITY;
                 sbuf[nt * 32 + lane] = make_float2(s0, s1);
             }
             // ---- online softmax: this thread holds 8 of the 32 scores of head g, its quad the rest
@@ -407,6 +416,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
         else q4n = p.q4n[b];
     }
     const float* proj = p.proj + (size_t)b * p.ldp;
+    const uint32_t* mk = p.qsa_on && p.qsa_on[b] ? p.qsa_mask + (size_t)b * p.qsa_ld : nullptr;   // block-sparse: the positions attended
 
     extern __shared__ float asm_[];
     float* qs = asm_;                         // [G][hd] normalized, roped, scaled queries
@@ -471,7 +481,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
     // tiles that are packed and entirely below the current length go to the tensor-core splits
     const int64_t tpk = nsp > 0 ? (q4n < n ? q4n : n) / AT_TILE : 0;
     if (sp < nsp) {
-        if (G <= 8) pb_attn_mma_tiles<(G <= 8 ? G : 8)>(qs, tkw, warp, lane, sp, nsp, kw, vw, ks, vs, tpk, mw);
+        if (G <= 8) pb_attn_mma_tiles<(G <= 8 ? G : 8)>(qs, tkw, warp, lane, sp, nsp, kw, vw, ks, vs, tpk, mw, mk);
     } else {
     // this lane's 8 query dims for every head of the group (hd = 256 -> one 8-dim slice per lane)
     float q[G][8];
@@ -497,6 +507,9 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
     const int64_t ntiles_s = (n + stile - 1) / stile;
     for (int64_t t = tpk * (AT_TILE / stile) + (int64_t)warp * nrs + (sp - nsp); t < ntiles_s; t += (int64_t)AT_WARPS * nrs) {
         const int64_t pbase = t * stile;
+        // block-sparse: the tile's bits of the position mask (tiles start at multiples of 8 and never straddle a word)
+        const uint32_t mbits = mk ? (mk[pbase >> 5] >> (pbase & 31)) & (stile == 32 ? 0xFFFFFFFFu : 0xFFu) : 0xFFFFFFFFu;
+        if (mbits == 0u) continue;
         // q4n is a multiple of 64 and tiles start at multiples of 32: a tile is entirely packed or entirely f32
         const bool packed = pbase < q4n;
         if (packed) {
@@ -563,7 +576,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
         }
         __syncwarp();
 #pragma unroll
-        for (int g = 0; g < G; g++) if (lane < stile && pbase + lane < n) sc[g] = pw[lane * G + g];
+        for (int g = 0; g < G; g++) if (lane < stile && pbase + lane < n && ((mbits >> lane) & 1u)) sc[g] = pw[lane * G + g];
         __syncwarp();
         // ---- online softmax over the tile (lane = position)
         float corr[G];

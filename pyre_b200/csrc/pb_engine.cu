@@ -36,10 +36,13 @@ struct pb_model {
     int ep_rank = 0, ep_world = 1, e_lo = 0, e_hi = 0;
     float* rope_inv = nullptr;   // n_rot / 2 inverse frequencies, then mscale
     int ctx_train = 0;           // trained context (0: unknown, no scaling)
+    int idx_budget = 0, idx_ratio = 1, idx_nh = 0, idx_hd = 0;   // QSA indexer geometry (Cfg :24-25); idx_nh = 0: none
+    bool qsa = false;            // the attention layers hold indexer tensors
     uint64_t weight_bytes_step = 0;
 };
 
-struct PbKv { uint32_t *kw = nullptr, *vw = nullptr; float *ks = nullptr, *vs = nullptr, *kr = nullptr, *vr = nullptr; int64_t* q4n = nullptr; };
+struct PbKv { uint32_t *kw = nullptr, *vw = nullptr; float *ks = nullptr, *vs = nullptr, *kr = nullptr, *vr = nullptr; int64_t* q4n = nullptr;
+              float *ik = nullptr, *ib = nullptr; };   // QSA: raw index keys [batch][max_ctx][idx_hd], pooled block keys [batch][nb_cap][idx_hd]
 
 struct pb_state {
     pb_model* m = nullptr;
@@ -68,6 +71,7 @@ struct pb_state {
     // peer exchange (pb_ep.cu): xg and part_rs live in a block mapped into every rank; the kernels store into the peers' blocks
     bool p2p = false; PbEpSymm symm; PbEpExch exch{}; PbEpExch* exch_dev = nullptr; float** part_tok = nullptr; unsigned long long* ep_seq = nullptr;
     int64_t ldproj = 0, ring_cap = 0;
+    float *iproj = nullptr, *qsa_scores = nullptr; uint32_t* qsa_mask = nullptr; int* qsa_on = nullptr; int64_t ldi = 0, nb_cap = 0, mask_ld = 0;   // QSA work buffers
     std::vector<float*> conv, ssm;
     std::vector<PbKv> kv;
     uint32_t* trace = nullptr; int64_t* trace_len = nullptr; int64_t trace_cap = 0;
@@ -156,6 +160,17 @@ int pb_model_set_tensor(pb_model* m, int layer, int role, pb_qmat* mat) {
     return PB_OK;
 }
 
+int pb_model_set_indexer(pb_model* m, int budget, int ratio, int n_head, int head_dim) {
+    if (!m) return PB_ERR_ARG;
+    pb_ctx* ctx = m->ctx;
+    PB_TRY(pb_enter(ctx));
+    if (m->finalized) PB_FAIL(ctx, PB_ERR_STATE, "pb_model_set_indexer: model already finalized");
+    if (n_head < 0 || (n_head > 0 && (ratio < 1 || budget < ratio || budget % ratio || head_dim < m->cfg.n_rot || head_dim % 8 || head_dim > 256)))
+        PB_FAIL(ctx, PB_ERR_ARG, "pb_model_set_indexer: budget %d ratio %d heads %d head dim %d (budget a multiple of ratio; head dim a multiple of 8 in [n_rot, 256])", budget, ratio, n_head, head_dim);
+    m->idx_budget = budget; m->idx_ratio = ratio; m->idx_nh = n_head; m->idx_hd = head_dim;
+    return PB_OK;
+}
+
 int pb_model_set_ctx_train(pb_model* m, int ctx_train) {
     if (!m) return PB_ERR_ARG;
     pb_ctx* ctx = m->ctx;
@@ -220,6 +235,7 @@ int pb_model_finalize(pb_model* m, int ep_rank, int ep_world) {
     m->e_lo = ep_rank * (c.n_exp / ep_world); m->e_hi = m->e_lo + c.n_exp / ep_world;
     const int ch = 2 * c.lin_nk * c.lin_dk + c.lin_nv * c.lin_dv, row = c.n_kv * c.hd;
     uint64_t wb = 0;
+    int n_attn_seen = 0;
     PB_TRY(need_mat(m, -1, PB_R_TOKEN_EMBD, c.vocab, c.d, "token_embd", false));
     if (!M(m, -1, PB_R_OUTPUT)) { /* falls back to token_embd (:511) */ }
     else PB_TRY(need_mat(m, -1, PB_R_OUTPUT, c.vocab, c.d, "output", true));
@@ -245,6 +261,18 @@ int pb_model_finalize(pb_model* m, int ep_rank, int ep_world) {
             if (M(m, il, PB_R_ATTN_Q)->type != M(m, il, PB_R_ATTN_K)->type || M(m, il, PB_R_ATTN_Q)->type != M(m, il, PB_R_ATTN_V)->type)
                 PB_FAIL(ctx, PB_UNSUPPORTED, "layer %d: attn_q/k/v must share one ggml type", il);
             wb += M(m, il, PB_R_ATTN_Q)->nbytes + M(m, il, PB_R_ATTN_K)->nbytes + M(m, il, PB_R_ATTN_V)->nbytes + M(m, il, PB_R_ATTN_O)->nbytes;
+            // QSA indexer (Mixer::Attn idx, :501): all attention layers or none
+            const bool has = m->idx_nh > 0 && M(m, il, PB_R_IDX_Q) != nullptr;
+            if (n_attn_seen > 0 && has != m->qsa) PB_FAIL(ctx, PB_UNSUPPORTED, "layer %d: indexer tensors on some attention layers only", il);
+            m->qsa = has; n_attn_seen++;
+            if (has) {
+                PB_TRY(need_mat(m, il, PB_R_IDX_Q, (int64_t)m->idx_nh * m->idx_hd, c.d, "indexer.q_proj", true));
+                PB_TRY(need_mat(m, il, PB_R_IDX_K, m->idx_hd, c.d, "indexer.k_proj", true));
+                PB_TRY(need_vec(m, il, PB_R_IDX_Q_NORM, m->idx_hd, "indexer.q_norm"));
+                PB_TRY(need_vec(m, il, PB_R_IDX_K_NORM, m->idx_hd, "indexer.k_norm"));
+                if (M(m, il, PB_R_IDX_Q)->type != M(m, il, PB_R_IDX_K)->type) PB_FAIL(ctx, PB_UNSUPPORTED, "layer %d: indexer q_proj / k_proj must share one ggml type", il);
+                wb += M(m, il, PB_R_IDX_Q)->nbytes + M(m, il, PB_R_IDX_K)->nbytes;
+            }
         } else {
             PB_TRY(need_mat(m, il, PB_R_LIN_QKV, ch, c.d, "attn_qkv", true));
             PB_TRY(need_mat(m, il, PB_R_LIN_Z, (int64_t)c.lin_nv * c.lin_dv, c.d, "attn_gate", true));
@@ -427,6 +455,7 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
     const size_t nparts = solo && (size_t)PB_PREFILL_CHUNK * PB_WIN_SPLITS > (size_t)ns ? (size_t)PB_PREFILL_CHUNK * PB_WIN_SPLITS : (size_t)B * ns;   // a prefill chunk: its tokens x PB_WIN_SPLITS
     A(part_ml, nparts * c.n_kv * G * 2); A(part_acc, nparts * c.n_kv * G * c.hd);
     s->conv.assign(m->n_lin, nullptr); s->ssm.assign(m->n_lin, nullptr); s->kv.assign(m->n_attn, PbKv());
+    s->ldi = (((int64_t)m->idx_nh + 1) * m->idx_hd + 3) & ~(int64_t)3; s->nb_cap = c.max_ctx / (m->idx_ratio > 0 ? m->idx_ratio : 1) + 1; s->mask_ld = c.max_ctx / 32 + 1;
     for (int i = 0; i < m->n_lin && rc == PB_OK; i++) {
         rc = dalloc(s, &s->conv[i], (size_t)B * c.conv_k * ch);
         if (rc == PB_OK) rc = dalloc(s, &s->ssm[i], (size_t)B * c.lin_nv * c.lin_dk * c.lin_dv);
@@ -446,6 +475,11 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
         if (rc == PB_OK) rc = dalloc(s, &k.vw, heads * packed_pos * (rowh / 8));
         if (rc == PB_OK) rc = dalloc(s, &k.ks, heads * packed_pos * (rowh / 32));
         if (rc == PB_OK) rc = dalloc(s, &k.vs, heads * packed_pos * (rowh / 32));
+        if (rc == PB_OK && m->qsa) rc = dalloc(s, &k.ik, (size_t)B * c.max_ctx * m->idx_hd);
+        if (rc == PB_OK && m->qsa) rc = dalloc(s, &k.ib, (size_t)B * s->nb_cap * m->idx_hd);
+    }
+    if (m->qsa) {
+        A(iproj, (size_t)Ba * s->ldi); A(qsa_scores, (size_t)B * s->nb_cap); A(qsa_mask, (size_t)B * s->mask_ld); A(qsa_on, (size_t)B);
     }
 #undef A
     if (rc == PB_OK && cudaMallocHost(&s->pin_u32, (size_t)(s->trace_cap + 2) * B * 4 + PB_PREFILL_CHUNK * 4) != cudaSuccess) { ctx->err = "pinned allocation failed"; rc = PB_ERR_OOM; }
@@ -594,7 +628,24 @@ static int run_attn(pb_state* s, int il, const float* x_in, const float* norm_w,
     const bool prefill = s->win_t >= 16 && !s->win_ckpt;
     PB_TRY(gemv_cols(ctx, a, ncol, prefill));
     PbAttnParams p; attn_params(s, il, p);
-    if (s->win_t > 0 && !s->win_ckpt) {
+    // QSA block-sparse attention (attn_core :1565-1599): two more projections of the same input give the raw index query
+    // heads and the raw index key; after the KV append the indexer stores the key, pools the block the token completes,
+    // and past the dense range writes the mask of positions this query attends to
+    PbQsaParams qp; memset(&qp, 0, sizeof qp);
+    if (m->qsa) {
+        PbGemvQArgs ia; memset(&ia, 0, sizeof ia);
+        ia.type = M(m, il, PB_R_IDX_Q)->type; ia.cols = c.d; ia.nseg = 2;
+        seg(ia, 0, M(m, il, PB_R_IDX_Q), 0); seg(ia, 1, M(m, il, PB_R_IDX_K), (int64_t)m->idx_nh * m->idx_hd);
+        ia.x = x_in; ia.ldx = c.d; ia.y = s->iproj; ia.ldy = s->ldi; ia.mode = a.mode; ia.norm_w = norm_w; ia.eps = c.eps;
+        PB_TRY(gemv_cols(ctx, ia, ncol, false));
+        const PbKv& k = s->kv[m->idx[il]];
+        qp.iproj = s->iproj; qp.ldi = s->ldi; qp.iqn = V(m, il, PB_R_IDX_Q_NORM); qp.ikn = V(m, il, PB_R_IDX_K_NORM); qp.rope_inv = m->rope_inv; qp.n_rot = c.n_rot; qp.eps = c.eps;
+        qp.inh = m->idx_nh; qp.ihd = m->idx_hd; qp.ratio = m->idx_ratio; qp.budget = m->idx_budget;
+        qp.ik = k.ik; qp.ib = k.ib; qp.max_ctx = c.max_ctx; qp.nb_cap = s->nb_cap; qp.pos = s->pos;
+        qp.scores = s->qsa_scores; qp.mask = s->qsa_mask; qp.mask_ld = s->mask_ld; qp.sparse = s->qsa_on; qp.batch = B;
+        p.qsa_mask = s->qsa_mask; p.qsa_ld = s->mask_ld; p.qsa_on = s->qsa_on;
+    }
+    if (s->win_t > 0 && !s->win_ckpt && !m->qsa) {
         // a prefill chunk: all tokens are appended, the packed boundary moves once, then every token attends to the
         // positions <= its own in one launch (token j treats as packed what it would have found packed token by token)
         p.window = 1; p.pos = s->wpos; p.batch = s->win_t;
@@ -605,13 +656,16 @@ static int run_attn(pb_state* s, int il, const float* x_in, const float* norm_w,
         PB_TRY(pb_launch_attn(ctx, p));
     } else if (s->win_t > 0) {
         // causal inside the window: token j is appended, then attends to positions <= its own
+        // (models with an indexer take this form for prefill chunks too: every token makes its own selection)
         for (int j = 0; j < s->win_t; j++) {
             p.proj = s->proj + (size_t)j * s->ldproj; p.pos = s->wpos + j; p.att = s->att + (size_t)j * p.lda; p.batch = 1;
             PB_TRY(pb_launch_kv_append(ctx, p));
+            if (m->qsa) { qp.iproj = s->iproj + (size_t)j * s->ldi; qp.pos = s->wpos + j; qp.batch = 1; PB_TRY(pb_launch_qsa_append(ctx, qp)); PB_TRY(pb_launch_qsa_select(ctx, qp)); }
             PB_TRY(pb_launch_attn(ctx, p));
         }
     } else {
         PB_TRY(pb_launch_kv_append(ctx, p));
+        if (m->qsa) { PB_TRY(pb_launch_qsa_append(ctx, qp)); PB_TRY(pb_launch_qsa_select(ctx, qp)); }
         PB_TRY(pb_launch_attn(ctx, p));
     }
     PbGemvQArgs o; memset(&o, 0, sizeof o);
@@ -694,6 +748,7 @@ static int run_moe(pb_state* s, int il, const float* x_in, const float* norm_w, 
 
 // ------------------------------------------------------------------------------------ fused step (pb_step.cu)
 
+static int qsa_pool_all(pb_state* s, int ai, int64_t n);
 static bool recoded(pb_qmat* q) { return q && q->type == PB_T_IQ3_S && q->rdata != nullptr; }
 
 // Decides whether the state can run its steps through the fused kernel and, if so, builds the operation list.
@@ -703,7 +758,7 @@ static int fused_build(pb_state* s) {
     pb_model* m = s->m; pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg;
     s->fused = 0;
     const bool on = !(getenv("PYRE_B200_FUSED") && atoi(getenv("PYRE_B200_FUSED")) == 0);   // read when a state takes its first step
-    if (!on || s->batch != 1 || s->sharded || m->ep_world != 1 || c.hc != 0) return PB_OK;
+    if (!on || s->batch != 1 || s->sharded || m->ep_world != 1 || c.hc != 0 || m->qsa) return PB_OK;
     const int d = c.d, ff = c.ff_exp, w_lin = c.lin_nv * c.lin_dv, w_att = c.n_head * c.hd;
     auto pow2 = [](int v) { return v > 0 && (v & (v - 1)) == 0; };
     if (d % 256 || d > 2048 || !pow2(d / 64) || ff % 512 || !pow2(ff / 64) || ff / 64 > 32 || c.ff_sh != ff) return PB_OK;
@@ -1170,6 +1225,7 @@ static size_t snap_size(const pb_state* s, const std::vector<int64_t>& q4) {
             const int64_t q4n = q4[(size_t)ai * B + b];
             n += (size_t)c.n_kv * (8 + 2 * ((size_t)q4n * (c.hd / 8) * 4 + (size_t)q4n * (c.hd / 32) * 4) + 2 * (size_t)(len - q4n) * c.hd * 4);
         }
+    if (s->m->qsa) n += (size_t)s->m->n_attn * B * (size_t)len * s->m->idx_hd * 4;   // raw index keys; the pooled block keys are rebuilt
     return n;
 }
 static int snap_read_q4(pb_state* s, std::vector<int64_t>& q4) {
@@ -1213,6 +1269,9 @@ static int snap_io(pb_state* s, uint8_t* buf, bool save, const std::vector<int64
                 }
             }
     }
+    if (s->m->qsa)
+        for (int ai = 0; ai < s->m->n_attn; ai++)
+            for (int b = 0; b < B; b++) PB_TRY(io(s->kv[ai].ik + (size_t)b * c.max_ctx * s->m->idx_hd, (size_t)len * s->m->idx_hd * 4));
     return PB_OK;
 }
 
@@ -1258,13 +1317,16 @@ int pb_state_restore(pb_state* s, const void* buf_host, size_t nbytes) {
                     q4[(size_t)ai * B + b] = q;
                     off += 8 + 2 * ((size_t)q * (c.hd / 8) * 4 + (size_t)q * (c.hd / 32) * 4) + 2 * (size_t)(h.pos - q) * c.hd * 4;
                 }
+        if (s->m->qsa) off += (size_t)s->m->n_attn * B * (size_t)h.pos * s->m->idx_hd * 4;
         if (off != nbytes) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_restore: size mismatch");
     }
     // position first (a fresh boundary of 0 so that any position is accepted), then the sections
     for (int ai = 0; ai < s->m->n_attn; ai++) PB_CUDA(ctx, cudaMemsetAsync(s->kv[ai].q4n, 0, (size_t)B * 8, ctx->stream));
     PB_TRY(pb_state_set_pos(s, h.pos));
     s->verify_t = 0;
-    return snap_io(s, (uint8_t*)const_cast<void*>(buf_host), false, q4);
+    PB_TRY(snap_io(s, (uint8_t*)const_cast<void*>(buf_host), false, q4));
+    if (s->m->qsa) for (int ai = 0; ai < s->m->n_attn; ai++) PB_TRY(qsa_pool_all(s, ai, h.pos));
+    return PB_OK;
 }
 
 int pb_stats_get(const pb_state* s, pb_stats* out) {
@@ -1383,6 +1445,32 @@ int pb_state_set_lin(pb_state* s, int layer, const float* conv_host, const float
 }
 
 // Pre-fill one sequence's KV of one attention layer from host rows [n][n_kv*hd] (already normed and roped).
+// pooled keys of the complete blocks among the first n positions of every sequence (after a fill or a restore)
+static int qsa_pool_all(pb_state* s, int ai, int64_t n) {
+    pb_model* m = s->m; const pb_cfg& c = m->cfg;
+    int il = 0;
+    for (int i = 0; i < c.n_layers; i++) if (m->kind[i] && m->idx[i] == ai) il = i;
+    PbQsaParams qp; memset(&qp, 0, sizeof qp);
+    qp.ikn = V(m, il, PB_R_IDX_K_NORM); qp.rope_inv = m->rope_inv; qp.n_rot = c.n_rot; qp.eps = c.eps;
+    qp.inh = m->idx_nh; qp.ihd = m->idx_hd; qp.ratio = m->idx_ratio; qp.budget = m->idx_budget;
+    qp.ik = s->kv[ai].ik; qp.ib = s->kv[ai].ib; qp.max_ctx = c.max_ctx; qp.nb_cap = s->nb_cap; qp.batch = s->batch;
+    return pb_launch_qsa_pool_all(m->ctx, qp, n / m->idx_ratio);
+}
+
+// Raw index keys of the first n positions of sequence b of attention layer ai, [n][idx_hd] (f32, host): the companion of
+// pb_state_fill_kv for models with an indexer.
+int pb_state_fill_index_keys(pb_state* s, int b, int ai, const float* ik_host, int64_t n) {
+    if (!s) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
+    PB_TRY(pb_enter(ctx));
+    if (!s->m->qsa) PB_FAIL(ctx, PB_ERR_STATE, "pb_state_fill_index_keys: the model has no indexer");
+    if (b < 0 || b >= s->batch || ai < 0 || ai >= s->m->n_attn || !ik_host || n < 0 || n > c.max_ctx) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_fill_index_keys: bad argument");
+    PB_CUDA(ctx, cudaMemcpyAsync(s->kv[ai].ik + (size_t)b * c.max_ctx * s->m->idx_hd, ik_host, (size_t)n * s->m->idx_hd * 4, cudaMemcpyHostToDevice, ctx->stream));
+    PB_TRY(qsa_pool_all(s, ai, n));
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return PB_OK;
+}
+
 int pb_state_fill_kv(pb_state* s, int b, int ai, const float* k_host, const float* v_host, int64_t n) {
     if (!s) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx; const pb_cfg& c = s->m->cfg;
@@ -1441,6 +1529,11 @@ int pb_state_fill_kv_synth(pb_state* s, int ai, int64_t n, uint64_t seed) {
                 }
                 PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
             }
+    if (s->m->qsa) {
+        // raw index keys of the n positions: normal(seed, tensor id 1000 + ai, index (b * max_ctx + p) * idx_hd + i); then every complete block is pooled
+        PB_TRY(pb_launch_synth_normal_at(ctx, kv.ik, (int64_t)s->batch * c.max_ctx * s->m->idx_hd, seed, 1000 + (uint64_t)ai, 0, 1.0f));
+        PB_TRY(qsa_pool_all(s, ai, n));
+    }
     std::vector<int64_t> q((size_t)s->batch, q4n);
     PB_CUDA(ctx, cudaMemcpy(kv.q4n, q.data(), q.size() * 8, cudaMemcpyHostToDevice));
     return PB_OK;

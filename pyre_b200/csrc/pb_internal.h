@@ -302,7 +302,26 @@ struct PbAttnParams {
     // kernel only writes the f32 ring, pb_launch_kv_pack then moves the packed boundary once for the whole window and
     // keeps the previous boundary in q4n[1]; token j treats as packed what a token-by-token run would have packed by then
     int window;
+    // QSA block-sparse attention (pb_qsa.cu): when qsa_on[b] is set, sequence b attends only to the positions whose bit is
+    // set in qsa_mask[b * qsa_ld + position / 32]; null = dense
+    const uint32_t* qsa_mask; int64_t qsa_ld; const int* qsa_on;
 };
+// pb_qsa.cu: the indexer of QSA block-sparse attention
+struct PbQsaParams {
+    const float* iproj; int64_t ldi;        // [batch][idx_nh * idx_hd raw query heads | idx_hd raw key]
+    const float* iqn; const float* ikn; const float* rope_inv; int n_rot; float eps;
+    int inh, ihd, ratio, budget;
+    float* ik; float* ib;                   // raw keys [batch][max_ctx][idx_hd], pooled block keys [batch][nb_cap][idx_hd]
+    int64_t max_ctx, nb_cap;
+    const int64_t* pos;                     // [batch]
+    float* scores;                          // [batch][nb_cap]
+    uint32_t* mask; int64_t mask_ld; int* sparse;   // out: see PbAttnParams
+    int batch;
+    int shared_seq;                         // the `batch` entries are tokens of sequence 0 (they share its keys)
+};
+int pb_launch_qsa_append(pb_ctx* ctx, const PbQsaParams& p);   // store the raw key, pool the block the token completes
+int pb_launch_qsa_select(pb_ctx* ctx, const PbQsaParams& p);   // block scores and the position mask (sparse[b] = 0 in the dense range)
+int pb_launch_qsa_pool_all(pb_ctx* ctx, const PbQsaParams& p, int64_t nblk);   // pooled keys of blocks [0, nblk) of every sequence
 int pb_launch_kv_append(pb_ctx* ctx, const PbAttnParams& p);
 int pb_launch_attn(pb_ctx* ctx, const PbAttnParams& p);
 int pb_launch_kv_pack(pb_ctx* ctx, const PbAttnParams& p);   // window mode, after pb_launch_kv_append

@@ -9,8 +9,9 @@ Tensor bytes are memory-mapped, never copied on the host.
 `load_model` restates the reference's loader (Model::load, src/model/qwen4exp_gguf.rs:462-512): the config from the
 `qwen4exp.*` metadata keys and the tensors by their `blk.N.*` names, uploaded in their GGUF block bytes
 (pb_qmat_upload) and bound to the library's roles.  Expert-parallel ranks upload only their rows of the three fused
-expert tensors.  Per-layer-input embeddings (PLE) and the sparse-attention indexer are not part of the built path and
-make the loader refuse the file instead of ignoring them.
+expert tensors.  The sparse-attention indexer (`attention.indexer.*` keys, `blk.N.indexer.*` tensors) and the trained context
+are handed to the library when the file has them.  Per-layer-input embeddings (PLE) are not part of the built path and make
+the loader refuse the file instead of ignoring them.
 """
 from __future__ import annotations
 
@@ -164,8 +165,6 @@ def load_model(ctx: Ctx, path, max_ctx: int = 4096, kv_bits: int = 4, kv_recent:
 
     if g.meta.get(f"{a}.ple.layers"):
         raise GgufError("per-layer-input embeddings (ple.layers) are not part of the built path")
-    if int(k("attention.indexer.head_count", 0)) > 0 and g.has("blk.3.indexer.q_proj.weight"):
-        raise GgufError("the sparse-attention indexer is not part of the built path")
     cfg = make_cfg(n_layers=int(k("block_count")), d=int(k("embedding_length")), hc=int(k("hyper_connection.count")), hc_lr=int(k("hyper_connection.low_rank")),
                    n_head=int(k("attention.head_count")), n_kv=int(k("attention.head_count_kv")), hd=int(k("attention.key_length")), n_rot=int(k("rope.dimension_count")),
                    rope_base=float(k("rope.freq_base")), eps=float(k("attention.layer_norm_rms_epsilon")), n_exp=int(k("expert_count")), top_k=int(k("expert_used_count")),
@@ -173,6 +172,13 @@ def load_model(ctx: Ctx, path, max_ctx: int = 4096, kv_bits: int = 4, kv_recent:
                    lin_dk=int(k("ssm.state_size")), lin_dv=int(k("ssm.state_size")), conv_k=int(k("ssm.conv_kernel")), full_every=int(k("full_attention_interval", 4)),
                    vocab=int(g.shape("token_embd.weight")[1]), max_ctx=max_ctx, kv_bits=kv_bits, kv_recent=kv_recent)
     m = Model(ctx, cfg)
+    # QSA indexer (Cfg :24-25, :481-489): budget = indexer.top_k, block size = the largest compress ratio
+    first_attn = cfg.full_every - 1
+    idx_nh = int(k("attention.indexer.head_count", 0))
+    has_idx = idx_nh > 0 and first_attn >= 0 and g.has(f"blk.{first_attn}.indexer.q_proj.weight")
+    if has_idx:
+        ratios = g.meta.get(f"{a}.attention.compress_ratios") or [4]
+        m.set_indexer(int(k("attention.indexer.top_k", 2048)), max(1, max(int(r) for r in ratios)), idx_nh, int(k("attention.indexer.key_length", 128)))
     m.set_ctx_train(int(g.meta.get(f"{a}.context_length", 0)))   # a longer max_ctx is YaRN-scaled (Model::load :490-517)
 
     def mat(layer, role, name, expert_rows=False):
@@ -223,6 +229,11 @@ def load_model(ctx: Ctx, path, max_ctx: int = 4096, kv_bits: int = 4, kv_recent:
                 mat(il, role, f"{p}.{n}.weight")
             vec(il, "ATTN_Q_NORM", f"{p}.attn_q_norm.weight")
             vec(il, "ATTN_K_NORM", f"{p}.attn_k_norm.weight")
+            if has_idx:
+                mat(il, "IDX_Q", f"{p}.indexer.q_proj.weight")
+                mat(il, "IDX_K", f"{p}.indexer.k_proj.weight")
+                vec(il, "IDX_Q_NORM", f"{p}.indexer.q_norm.weight")
+                vec(il, "IDX_K_NORM", f"{p}.indexer.k_norm.weight")
         else:
             for role, n in (("LIN_QKV", "attn_qkv"), ("LIN_Z", "attn_gate"), ("LIN_BETA", "ssm_beta"), ("LIN_ALPHA", "ssm_alpha"), ("LIN_OUT", "ssm_out")):
                 mat(il, role, f"{p}.{n}.weight")

@@ -30,6 +30,12 @@ class Model:
         v = _f32(v).reshape(-1)
         self.ctx.check(lib().pb_model_set_vec(self.h, C.c_int(layer), C.c_int(ROLE[role]), _p(v), C.c_int64(v.size)))
 
+    def set_indexer(self, budget: int, ratio: int, n_head: int, head_dim: int):
+        """QSA block-sparse attention: attention layers that hold IDX_Q / IDX_K / IDX_Q_NORM / IDX_K_NORM attend to the
+        budget / ratio best blocks of ratio tokens once a query sees more than budget + ratio - 1 tokens (before finalize)."""
+        self.ctx.check(lib().pb_model_set_indexer(self.h, C.c_int(budget), C.c_int(ratio), C.c_int(n_head), C.c_int(head_dim)))
+        self.indexer = (budget, ratio, n_head, head_dim)
+
     def set_ctx_train(self, ctx_train: int):
         """Trained context; a larger cfg.max_ctx is YaRN-scaled (before finalize)."""
         self.ctx.check(lib().pb_model_set_ctx_train(self.h, C.c_int(ctx_train)))
@@ -121,6 +127,11 @@ class State:
         k, v = _f32(k), _f32(v)
         row = self.model.cfg.n_kv * self.model.cfg.hd
         self.ctx.check(lib().pb_state_fill_kv(self.h, C.c_int(b), C.c_int(attn_index), _p(k), _p(v), C.c_int64(k.size // row)))
+
+    def fill_index_keys(self, b: int, attn_index: int, ik: np.ndarray):
+        """Raw index keys [n][idx_hd] of the positions given to fill_kv (models with an indexer)."""
+        ik = _f32(ik)
+        self.ctx.check(lib().pb_state_fill_index_keys(self.h, C.c_int(b), C.c_int(attn_index), _p(ik), C.c_int64(ik.shape[0])))
 
     def fill_kv_synth(self, attn_index: int, n: int, seed: int):
         self.ctx.check(lib().pb_state_fill_kv_synth(self.h, C.c_int(attn_index), C.c_int64(n), C.c_uint64(seed)))

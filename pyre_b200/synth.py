@@ -25,8 +25,9 @@ def is_full(cfg: Cfg, il: int) -> bool:
     return cfg.full_every > 0 and (il + 1) % cfg.full_every == 0
 
 
-def model_spec(cfg: Cfg, seed: int = 0, qtype: int = IQ3_S):
-    """List of ('mat', layer, role, type, rows, cols, tid) and ('vec', layer, role, array)."""
+def model_spec(cfg: Cfg, seed: int = 0, qtype: int = IQ3_S, indexer=None):
+    """List of ('mat', layer, role, type, rows, cols, tid) and ('vec', layer, role, array).  indexer = (budget, ratio, heads,
+    head dim) adds the QSA indexer tensors to every attention layer."""
     rng = np.random.default_rng(seed)
     d, hd = cfg.d, cfg.hd
     ch = 2 * cfg.lin_nk * cfg.lin_dk + cfg.lin_nv * cfg.lin_dv
@@ -71,6 +72,12 @@ def model_spec(cfg: Cfg, seed: int = 0, qtype: int = IQ3_S):
             mat(il, "ATTN_O", d, cfg.n_head * hd)
             vec(il, "ATTN_Q_NORM", gamma(hd))
             vec(il, "ATTN_K_NORM", gamma(hd))
+            if indexer:
+                _, _, inh, ihd = indexer
+                mat(il, "IDX_Q", inh * ihd, d)
+                mat(il, "IDX_K", ihd, d)
+                vec(il, "IDX_Q_NORM", gamma(ihd))
+                vec(il, "IDX_K_NORM", gamma(ihd))
         else:
             mat(il, "LIN_QKV", ch, d)
             mat(il, "LIN_Z", cfg.lin_nv * cfg.lin_dv, d)
@@ -92,10 +99,12 @@ def model_spec(cfg: Cfg, seed: int = 0, qtype: int = IQ3_S):
     return spec
 
 
-def build_model(ctx: Ctx, cfg: Cfg, spec, seed: int = 0, ep_rank: int = 0, ep_world: int = 1, ctx_train: int = 0) -> Model:
+def build_model(ctx: Ctx, cfg: Cfg, spec, seed: int = 0, ep_rank: int = 0, ep_world: int = 1, ctx_train: int = 0, indexer=None) -> Model:
     m = Model(ctx, cfg)
     if ctx_train:
         m.set_ctx_train(ctx_train)
+    if indexer:
+        m.set_indexer(*indexer)
     for item in spec:
         if item[0] == "mat":
             _, layer, role, t, rows, cols, tid = item

@@ -12,10 +12,12 @@ def oracle_cfg(cfg):
     return oc
 
 
-def oracle_model(cfg, spec, seed=0, ctx_train=0):
+def oracle_model(cfg, spec, seed=0, ctx_train=0, indexer=None):
     om = oracle.Model(oracle_cfg(cfg))
     if ctx_train:
         om.set_ctx_train(ctx_train)
+    if indexer:
+        om.set_indexer(*indexer)
     mats = {}
     for item in spec:
         if item[0] == "mat":
@@ -52,10 +54,11 @@ GGUF_NAMES = {
     "HCA_NORM": "hc_attn_norm.weight", "HCA_DOWN": "hc_attn_down.weight", "HCA_UP": "hc_attn_up.weight", "HCA_INJECT": "hc_attn_inject.weight",
     "HCF_NORM": "hc_ffn_norm.weight", "HCF_DOWN": "hc_ffn_down.weight", "HCF_UP": "hc_ffn_up.weight", "HCF_INJECT": "hc_ffn_inject.weight",
     "OUT_HC_NORM": "output_hc_norm.weight", "OUT_HC_DOWN": "output_hc_down.weight", "OUT_HC_UP": "output_hc_up.weight",
+    "IDX_Q": "indexer.q_proj.weight", "IDX_K": "indexer.k_proj.weight", "IDX_Q_NORM": "indexer.q_norm.weight", "IDX_K_NORM": "indexer.k_norm.weight",
 }
 
 
-def write_synth_gguf(path, cfg, spec, seed, split_after=None):
+def write_synth_gguf(path, cfg, spec, seed, split_after=None, indexer=None, ctx_train=0):
     """A synthetic model (pyre_b200.synth.model_spec) as a qwen4exp GGUF file written with gguf-py: metadata keys and tensor
     names as Model::load reads them, quantized tensors as their raw block bytes (the oracle's generator)."""
     import gguf
@@ -68,6 +71,12 @@ def write_synth_gguf(path, cfg, spec, seed, split_after=None):
                    ("expert_count", cfg.n_exp), ("expert_used_count", cfg.top_k), ("expert_feed_forward_length", cfg.ff_exp), ("ssm.group_count", cfg.lin_nk),
                    ("ssm.time_step_rank", cfg.lin_nv), ("ssm.state_size", cfg.lin_dk), ("ssm.conv_kernel", cfg.conv_k), ("full_attention_interval", cfg.full_every)):
         w.add_uint32(f"{a}.{key}", int(v))
+    if indexer:
+        budget, ratio, inh, ihd = indexer
+        w.add_uint32(f"{a}.attention.indexer.top_k", budget); w.add_uint32(f"{a}.attention.indexer.head_count", inh); w.add_uint32(f"{a}.attention.indexer.key_length", ihd)
+        w.add_array(f"{a}.attention.compress_ratios", [1, ratio])
+    if ctx_train:
+        w.add_uint32(f"{a}.context_length", ctx_train)
     w.add_float32(f"{a}.rope.freq_base", float(cfg.rope_base))
     w.add_float32(f"{a}.attention.layer_norm_rms_epsilon", float(cfg.eps))
     w.add_string("general.name", "synthetic")

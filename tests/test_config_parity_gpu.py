@@ -74,6 +74,59 @@ def test_attention_config4_context(ctx, batch):
     assert _attn_case(ctx, batch) < TOL
 
 
+def test_sparse_attention_config4_context(ctx):
+    """The same layer with the QSA indexer at the reference's defaults (budget 2048 tokens in blocks of 4, index heads of
+    128): 32740 pre-filled positions with their raw index keys, then decode steps of two sequences.  Every query scores
+    8185 pooled block keys, takes the best 512 plus the tail, and attends to them in the 4-bit region (tensor-core tiles
+    with masked positions, untouched tiles skipped) and in the f32 window; outputs within 1e-3 of the oracle, which makes
+    its own selection from its own keys; the smallest selection margin met is checked to be resolvable in f32."""
+    n0, steps, batch = 32740, 10, 2
+    indexer = (2048, 4, 4, 128)
+    budget, ratio, inh, ihd = indexer
+    cfg = pb.make_cfg(n_layers=4, full_every=4, vocab=1024, max_ctx=32768 + 64, kv_bits=4, kv_recent=1024, n_exp=16, top_k=2)
+    spec = synth.model_spec(cfg, 0, indexer=indexer)
+    m = synth.build_model(ctx, cfg, spec, 0, indexer=indexer)
+    _, mats = oracle_model(cfg, spec, 0, indexer=indexer)
+    ocfg = oracle_cfg(cfg)
+    layer, row = 3, cfg.n_kv * cfg.hd
+    st = m.new_state(batch)
+    rng = np.random.default_rng(77)
+    inv = oracle.rope_inv(cfg.n_rot, cfg.rope_base)
+    kc, vc, ik, ib, packed = [], [], [], [], []
+    q4n = ((n0 - cfg.kv_recent) // 64) * 64
+    for b in range(batch):
+        kc.append(np.zeros((cfg.max_ctx, row), np.float32)); vc.append(np.zeros((cfg.max_ctx, row), np.float32)); ik.append(np.zeros((cfg.max_ctx, ihd), np.float32))
+        kc[b][:n0] = rng.standard_normal((n0, row)); vc[b][:n0] = rng.standard_normal((n0, row)); ik[b][:n0] = rng.standard_normal((n0, ihd))
+        st.fill_kv(b, 0, kc[b][:n0], vc[b][:n0]); st.fill_index_keys(b, 0, ik[b][:n0])
+        ib.append(np.zeros((cfg.max_ctx // ratio + 1, ihd), np.float32))
+        for blk in range(n0 // ratio):
+            ib[b][blk] = oracle.qsa_pool(ocfg, ratio, ik[b], mats[(layer, "IDX_K_NORM")], inv, blk)
+        packed.append((*oracle.kv4_pack(kc[b][:q4n]), *oracle.kv4_pack(vc[b][:q4n])))
+    st.set_pos(n0)
+    worst, min_margin = 0.0, float("inf")
+    for step in range(steps):
+        pos = n0 + step
+        x = rng.standard_normal((batch, cfg.d)).astype(np.float32)
+        y = st.attn_step(layer, x)
+        st.set_pos(pos + 1)
+        assert ((pos + 1 - cfg.kv_recent) // 64) * 64 == q4n       # no packing step inside this run
+        for b in range(batch):
+            qf, kf, vf, iq, ikf = (mats[(layer, r)].matmul(x[b])[0] for r in ("ATTN_Q", "ATTN_K", "ATTN_V", "IDX_Q", "IDX_K"))
+            ik[b][pos] = ikf
+            if (pos + 1) % ratio == 0:
+                ib[b][pos // ratio] = oracle.qsa_pool(ocfg, ratio, ik[b], mats[(layer, "IDX_K_NORM")], inv, pos // ratio)
+            blocks, margin = oracle.qsa_select(ocfg, budget, ratio, iq.reshape(inh, ihd), mats[(layer, "IDX_Q_NORM")], inv, ib[b], pos)
+            assert blocks.size == budget // ratio
+            min_margin = min(min_margin, margin)
+            ps = np.concatenate([(blocks[:, None] * ratio + np.arange(ratio)[None]).reshape(-1), np.arange(((pos + 1) // ratio) * ratio, pos + 1)])
+            att = oracle.attn_core(ocfg, qf, kf, vf, mats[(layer, "ATTN_Q_NORM")], mats[(layer, "ATTN_K_NORM")], inv, kc[b], vc[b], pos, packed[b], q4n, ps=ps)
+            worst = max(worst, rel_err(y[b], mats[(layer, "ATTN_O")].matmul(att)[0]))
+    assert min_margin > 1e-6, min_margin
+    assert worst < TOL, (worst, min_margin)
+    assert ctx.device_status() == 0
+    st.destroy(); m.destroy()
+
+
 def test_deltanet_config2_batch64_256_steps(ctx):
     """Config 2 verbatim: 64 sequences, state N(0, 0.1), 256 sequential steps.  The sequences are independent, so the
     oracle follows a sample of them (first, last and two inside); their outputs are checked at every step and

@@ -106,3 +106,26 @@ def test_loaded_model_decodes_like_the_directly_built_one(ctx, tmp_path, hc):
     assert np.array_equal(la.view(np.uint32), lb.view(np.uint32))
     assert a.decode_greedy([int(la[0].argmax())], 24)[0].tolist() == b.decode_greedy([int(lb[0].argmax())], 24)[0].tolist()
     a.destroy(); b.destroy(); m.destroy(); ref.destroy()
+
+
+@pytest.mark.gpu
+def test_loaded_model_with_indexer_and_trained_context(ctx, tmp_path):
+    """A file that carries the sparse-attention indexer (attention.indexer.* keys, blk.N.indexer.* tensors) and a trained
+    context shorter than the requested one: the loader hands both to the library, and the loaded model decodes like the
+    same weights bound directly with the same indexer geometry and YaRN scaling -- 80 tokens, well past the dense range."""
+    pytest.importorskip("gguf")
+    indexer = (32, 4, 2, 64)
+    cfg = small_cfg(pb, n_layers=8, kv_bits=4, kv_recent=64, max_ctx=256)
+    spec = synth.model_spec(cfg, 43, indexer=indexer)
+    p = tmp_path / "model.gguf"
+    write_synth_gguf(p, cfg, spec, 43, indexer=indexer, ctx_train=128)
+    m = load_model(ctx, p, max_ctx=256, kv_bits=4, kv_recent=64)
+    assert m.indexer == indexer
+    ref = synth.build_model(ctx, cfg, spec, 43, ctx_train=128, indexer=indexer)
+    plain = synth.build_model(ctx, cfg, [it for it in spec if not it[2].startswith("IDX_")], 43)
+    a, b, c = m.new_state(1), ref.new_state(1), plain.new_state(1)
+    ta, tb, tc = (s.decode_greedy([17], 80)[0].tolist() for s in (a, b, c))
+    assert ta == tb and ta != tc
+    for s in (a, b, c):
+        s.destroy()
+    m.destroy(); ref.destroy(); plain.destroy()
