@@ -404,6 +404,34 @@ def run_ours(args):
         if rank == 0:
             line["batch32"] = {"value": round(32 * steps2 / (ms2 / 1e3), 2), "unit": "tok/s", "ms_per_step": round(ms2 / steps2, 4), "steps": steps2, "batch": 32, "per_gpu": B2, "context": CTX_PREFILL}
     st.destroy()
+    # ---- the same decode steps with the QSA indexer on the attention layers (the reference's long-context form: every query
+    #      attends to the 2048 / 4 best blocks of 4 tokens plus the tail instead of all 32768 positions); one GPU only
+    if world == 1 and B == 1 and not args.no_qsa:
+        model.destroy(); model = None
+        idx = (2048, 4, 8, 128)
+        spec_q = synth.model_spec(cfg, SEED, indexer=idx)
+        mq = synth.build_model(ctx, cfg, spec_q, SEED, indexer=idx)
+        res = {}
+        for Bq, steps_q in ((1, max(8, args.steps // 2)), (32, max(4, args.steps // 4))):
+            if Bq == 32 and args.no_bs32:
+                continue
+            sq = mq.new_state(Bq)
+            for ai in range(n_attn):
+                sq.fill_kv_synth(ai, CTX_PREFILL, SEED + 1)
+            sq.set_pos(CTX_PREFILL)
+            sq.decode_greedy(np.arange(Bq, dtype=np.uint32) + 1, 3)
+            q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.stream(stream):
+                q0.record(stream)
+                sq.decode_greedy(np.arange(Bq, dtype=np.uint32) + 7, steps_q)
+                q1.record(stream)
+            torch.cuda.synchronize()
+            msq = q0.elapsed_time(q1)
+            res[f"batch{Bq}"] = {"tok_per_s": round(Bq * steps_q / (msq / 1e3), 2), "ms_per_step": round(msq / steps_q, 4), "steps": steps_q}
+            sq.destroy()
+        mq.destroy()
+        line["sparse_attention"] = {"indexer": {"budget_tokens": idx[0], "block": idx[1], "heads": idx[2], "head_dim": idx[3]}, "context": CTX_PREFILL, **res,
+                                    "note": "same model and 4-bit cache with synthetic indexer tensors and index keys; the headline value above is dense attention"}
     if world > 1 and sharded and not args.no_variants:
         import torch.distributed as dist
 
@@ -481,6 +509,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-bs32", action="store_true", help="skip the batch-32 leg of the default run")
+    ap.add_argument("--no-qsa", action="store_true", help="skip the sparse-attention (QSA indexer) leg of the default run")
     ap.add_argument("--replicated-ep", action="store_true", help="N>1: expert parallelism with every GPU stepping all sequences (all-reduce) instead of sharded tokens")
     ap.add_argument("--no-variants", action="store_true", help="N>1: skip the NCCL / replicas comparison and the token-identity check")
     ap.add_argument("--replicas", action="store_true", help="N>1: independent replicas instead of expert parallelism")

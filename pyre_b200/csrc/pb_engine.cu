@@ -165,8 +165,8 @@ int pb_model_set_indexer(pb_model* m, int budget, int ratio, int n_head, int hea
     pb_ctx* ctx = m->ctx;
     PB_TRY(pb_enter(ctx));
     if (m->finalized) PB_FAIL(ctx, PB_ERR_STATE, "pb_model_set_indexer: model already finalized");
-    if (n_head < 0 || (n_head > 0 && (ratio < 1 || budget < ratio || budget % ratio || head_dim < m->cfg.n_rot || head_dim % 8 || head_dim > 256)))
-        PB_FAIL(ctx, PB_ERR_ARG, "pb_model_set_indexer: budget %d ratio %d heads %d head dim %d (budget a multiple of ratio; head dim a multiple of 8 in [n_rot, 256])", budget, ratio, n_head, head_dim);
+    if (n_head < 0 || (n_head > 0 && (ratio < 1 || budget < ratio || budget % ratio || head_dim < m->cfg.n_rot || head_dim % 32 || head_dim > 256)))
+        PB_FAIL(ctx, PB_ERR_ARG, "pb_model_set_indexer: budget %d ratio %d heads %d head dim %d (budget a multiple of ratio; head dim a multiple of 32 in [n_rot, 256])", budget, ratio, n_head, head_dim);
     m->idx_budget = budget; m->idx_ratio = ratio; m->idx_nh = n_head; m->idx_hd = head_dim;
     return PB_OK;
 }
@@ -617,6 +617,15 @@ static void attn_params(pb_state* s, int il, PbAttnParams& p) {
     p.att = s->att; p.lda = (int64_t)c.n_head * c.hd; p.batch = s->batch;
 }
 
+static void qsa_params(pb_state* s, int il, PbQsaParams& qp) {
+    pb_model* m = s->m; const pb_cfg& c = m->cfg; const PbKv& k = s->kv[m->idx[il]];
+    memset(&qp, 0, sizeof qp);
+    qp.iproj = s->iproj; qp.ldi = s->ldi; qp.iqn = V(m, il, PB_R_IDX_Q_NORM); qp.ikn = V(m, il, PB_R_IDX_K_NORM); qp.rope_inv = m->rope_inv; qp.n_rot = c.n_rot; qp.eps = c.eps;
+    qp.inh = m->idx_nh; qp.ihd = m->idx_hd; qp.ratio = m->idx_ratio; qp.budget = m->idx_budget;
+    qp.ik = k.ik; qp.ib = k.ib; qp.max_ctx = c.max_ctx; qp.nb_cap = s->nb_cap; qp.pos = s->pos;
+    qp.scores = s->qsa_scores; qp.mask = s->qsa_mask; qp.mask_ld = s->mask_ld; qp.sparse = s->qsa_on; qp.batch = s->batch;
+}
+
 static int run_attn(pb_state* s, int il, const float* x_in, const float* norm_w, float* y, int64_t ldy, int accumulate) {
     pb_model* m = s->m; pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg; const int B = s->batch;
     const int64_t nq = (int64_t)c.n_head * 2 * c.hd, row = (int64_t)c.n_kv * c.hd;
@@ -638,11 +647,7 @@ static int run_attn(pb_state* s, int il, const float* x_in, const float* norm_w,
         seg(ia, 0, M(m, il, PB_R_IDX_Q), 0); seg(ia, 1, M(m, il, PB_R_IDX_K), (int64_t)m->idx_nh * m->idx_hd);
         ia.x = x_in; ia.ldx = c.d; ia.y = s->iproj; ia.ldy = s->ldi; ia.mode = a.mode; ia.norm_w = norm_w; ia.eps = c.eps;
         PB_TRY(gemv_cols(ctx, ia, ncol, false));
-        const PbKv& k = s->kv[m->idx[il]];
-        qp.iproj = s->iproj; qp.ldi = s->ldi; qp.iqn = V(m, il, PB_R_IDX_Q_NORM); qp.ikn = V(m, il, PB_R_IDX_K_NORM); qp.rope_inv = m->rope_inv; qp.n_rot = c.n_rot; qp.eps = c.eps;
-        qp.inh = m->idx_nh; qp.ihd = m->idx_hd; qp.ratio = m->idx_ratio; qp.budget = m->idx_budget;
-        qp.ik = k.ik; qp.ib = k.ib; qp.max_ctx = c.max_ctx; qp.nb_cap = s->nb_cap; qp.pos = s->pos;
-        qp.scores = s->qsa_scores; qp.mask = s->qsa_mask; qp.mask_ld = s->mask_ld; qp.sparse = s->qsa_on; qp.batch = B;
+        qsa_params(s, il, qp);
         p.qsa_mask = s->qsa_mask; p.qsa_ld = s->mask_ld; p.qsa_on = s->qsa_on;
     }
     if (s->win_t > 0 && !s->win_ckpt && !m->qsa) {
@@ -758,7 +763,7 @@ static int fused_build(pb_state* s) {
     pb_model* m = s->m; pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg;
     s->fused = 0;
     const bool on = !(getenv("PYRE_B200_FUSED") && atoi(getenv("PYRE_B200_FUSED")) == 0);   // read when a state takes its first step
-    if (!on || s->batch != 1 || s->sharded || m->ep_world != 1 || c.hc != 0 || m->qsa) return PB_OK;
+    if (!on || s->batch != 1 || s->sharded || m->ep_world != 1 || c.hc != 0) return PB_OK;
     const int d = c.d, ff = c.ff_exp, w_lin = c.lin_nv * c.lin_dv, w_att = c.n_head * c.hd;
     auto pow2 = [](int v) { return v > 0 && (v & (v - 1)) == 0; };
     if (d % 256 || d > 2048 || !pow2(d / 64) || ff % 512 || !pow2(ff / 64) || ff / 64 > 32 || c.ff_sh != ff) return PB_OK;
@@ -769,6 +774,7 @@ static int fused_build(pb_state* s) {
     for (int il = 0; il < c.n_layers; il++) {
         if (m->kind[il]) {
             if (!recoded(M(m, il, PB_R_ATTN_Q)) || !recoded(M(m, il, PB_R_ATTN_K)) || !recoded(M(m, il, PB_R_ATTN_V)) || !recoded(M(m, il, PB_R_ATTN_O))) return PB_OK;
+            if (m->qsa && (!recoded(M(m, il, PB_R_IDX_Q)) || !recoded(M(m, il, PB_R_IDX_K)))) return PB_OK;
             if (w_att % 256 || w_att > 4096 || !pow2(w_att / 64)) return PB_OK;
             maxcols = w_att > maxcols ? w_att : maxcols;
         } else {
@@ -832,6 +838,8 @@ static int fused_build(pb_state* s) {
         if (m->kind[il]) {
             const int nq = c.n_head * 2 * c.hd, row = c.n_kv * c.hd;
             gemv(d, PB_ACT_NORM, s->x, V(m, il, PB_R_ATTN_NORM), nullptr, s->proj, 0, {{M(m, il, PB_R_ATTN_Q), 0}, {M(m, il, PB_R_ATTN_K), nq}, {M(m, il, PB_R_ATTN_V), nq + row}});
+            if (m->qsa)   // the indexer's raw query heads and raw key, from the same normalized input
+                gemv(d, PB_ACT_NORM, s->x, V(m, il, PB_R_ATTN_NORM), nullptr, s->iproj, 0, {{M(m, il, PB_R_IDX_Q), 0}, {M(m, il, PB_R_IDX_K), m->idx_nh * m->idx_hd}});
             s->fsegs.push_back({seg_begin, (int)ops.size(), il, 0});
             seg_begin = (int)ops.size();
             gemv(w_att, PB_ACT_PLAIN, s->att, nullptr, nullptr, s->x, 1, {{M(m, il, PB_R_ATTN_O), 0}});
@@ -900,6 +908,11 @@ static int run_step_fused(pb_state* s) {
         if (sg.attn_layer >= 0) {
             PbAttnParams p; attn_params(s, sg.attn_layer, p);
             PB_TRY(pb_launch_kv_append(ctx, p));
+            if (m->qsa) {
+                PbQsaParams qp; qsa_params(s, sg.attn_layer, qp);
+                p.qsa_mask = s->qsa_mask; p.qsa_ld = s->mask_ld; p.qsa_on = s->qsa_on;
+                PB_TRY(pb_launch_qsa_append(ctx, qp)); PB_TRY(pb_launch_qsa_select(ctx, qp));
+            }
             PB_TRY(pb_launch_attn(ctx, p));
         }
     }

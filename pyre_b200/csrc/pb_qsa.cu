@@ -11,8 +11,8 @@
 // get a score of minus infinity.
 //
 //   pb_qsa_append_kernel  one CTA per sequence: store the token's raw key, pool the block it completes
-//   pb_qsa_score_kernel   grid (blocks / 128, sequences): the block scores, dots accumulated in the order of the
-//                         reference's dot (32 partial sums, dot_avx2 in src/model/gguf_q.rs:176-197)
+//   pb_qsa_score_kernel   tiles of pooled keys in shared memory, a thread per block: the block scores, dots accumulated
+//                         in the order of the reference's dot (32 partial sums, dot_avx2 in src/model/gguf_q.rs:176-197)
 //   pb_qsa_pick_kernel    one CTA per sequence: the budget / ratio-th largest (score, lower block first) key by a
 //                         radix select over 64-bit keys, then the mask
 #include "pb_common.cuh"
@@ -79,57 +79,97 @@ __global__ void __launch_bounds__(32) pb_qsa_pool_kernel(const PbQsaParams p, in
         pb_qsa_pool_block(p, p.ik + (size_t)b * p.max_ctx * p.ihd, p.ib + (size_t)b * p.nb_cap * p.ihd, blk, tmp, lane);
 }
 
-// grid (ceil(nb_cap / 128), batch), 128 threads
-__global__ void __launch_bounds__(128) pb_qsa_score_kernel(const PbQsaParams p) {
+// grid (tiles, batch), 64 threads.  A CTA stages a tile of consecutive pooled keys in shared memory (coalesced loads, rows
+// padded by one word so that a column walk is conflict-free), then thread i scores block i of the tile against every
+// query head with the 32 running sums of the reference's dot (dot_avx2, src/model/gguf_q.rs:176-197: dims i, i + 32, ...
+// go to sum i mod 32), combined in its order: (s0 + s1) + (s2 + s3) per lane of eight, the eight added one after the other.
+#define QSA_TILE 64
+// IHD > 0: the head dim is known at compile time and the thread keeps its block's key in registers, so that only the
+// queries are read again for every head (as 128-bit broadcasts); IHD = 0: any head dim, everything from shared memory
+template <int IHD>
+__global__ void __launch_bounds__(QSA_TILE) pb_qsa_score_kernel(const PbQsaParams p, int tile_rows) {
     const int b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    extern __shared__ float qsm[];     // [inh][ihd] normed, roped index queries
+    extern __shared__ __align__(16) float qsm[];     // [inh][ihd] normed, roped index queries, then two tiles [tile_rows][ihd + 4]
     pb_pdl_wait();
     pb_pdl_trigger();
+    const int ihd = IHD > 0 ? IHD : p.ihd;
     const int64_t pos = p.pos[b], n = pos + 1;
     if (n <= (int64_t)p.budget + p.ratio - 1) return;       // dense range (dense_n, :1555)
     const int64_t nb = n / p.ratio;
-    if ((int64_t)blockIdx.x * 128 >= nb) return;
+    if ((int64_t)blockIdx.x * tile_rows >= nb) return;
     const float* iq = p.iproj + (size_t)b * p.ldi;
-    for (int i = tid; i < p.inh * p.ihd; i += 128) qsm[i] = iq[i];
+    for (int i = tid; i < p.inh * ihd; i += QSA_TILE) qsm[i] = iq[i];
     __syncthreads();
-    for (int h = warp; h < p.inh; h += 4) pb_qsa_norm_rope(qsm + h * p.ihd, p.iqn, p.rope_inv, p.ihd, p.n_rot, p.eps, pos, lane);
-    __syncthreads();
-    const int64_t blk = (int64_t)blockIdx.x * 128 + tid;
-    if (blk >= nb) return;
+    for (int h = warp; h < p.inh; h += QSA_TILE / 32) pb_qsa_norm_rope(qsm + h * ihd, p.iqn, p.rope_inv, ihd, p.n_rot, p.eps, pos, lane);
+    float* tile = qsm + p.inh * ihd;
+    const int ld = ihd + 4;                                 // rows stay 16-byte aligned; eight rows fall into eight groups of four banks
     const int sb = p.shared_seq ? 0 : b;
-    const float* kb = p.ib + ((size_t)sb * p.nb_cap + blk) * p.ihd;
-    const float iscale = 1.0f / sqrtf((float)p.ihd);
-    float s = 0.f;
-    for (int h = 0; h < p.inh; h++) {
-        const float* q = qsm + h * p.ihd;
-        // dot in the order of the reference: four groups of eight running sums over strides of 32, then
-        // (s0 + s1) + (s2 + s3) per lane, lanes added in order
-        float a[4][8];
-#pragma unroll
-        for (int k = 0; k < 4; k++)
-#pragma unroll
-            for (int l = 0; l < 8; l++) a[k][l] = 0.f;
-        int i = 0;
-        for (; i + 32 <= p.ihd; i += 32) {
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const float4 k0 = *reinterpret_cast<const float4*>(kb + i + 8 * k), k1 = *reinterpret_cast<const float4*>(kb + i + 8 * k + 4);
-                a[k][0] = fmaf(q[i + 8 * k + 0], k0.x, a[k][0]); a[k][1] = fmaf(q[i + 8 * k + 1], k0.y, a[k][1]);
-                a[k][2] = fmaf(q[i + 8 * k + 2], k0.z, a[k][2]); a[k][3] = fmaf(q[i + 8 * k + 3], k0.w, a[k][3]);
-                a[k][4] = fmaf(q[i + 8 * k + 4], k1.x, a[k][4]); a[k][5] = fmaf(q[i + 8 * k + 5], k1.y, a[k][5]);
-                a[k][6] = fmaf(q[i + 8 * k + 6], k1.z, a[k][6]); a[k][7] = fmaf(q[i + 8 * k + 7], k1.w, a[k][7]);
-            }
+    const float* ibase = p.ib + (size_t)sb * p.nb_cap * ihd;
+    const float iscale = 1.0f / sqrtf((float)ihd);
+    // two tile buffers: the next tile is on its way (cp.async) while this one is scored
+    const int64_t t_step = (int64_t)gridDim.x * tile_rows;
+    auto fetch = [&](int64_t t0, float* buf) {
+        const int rows = (int)(nb - t0 < tile_rows ? nb - t0 : tile_rows);
+        const float* src = ibase + t0 * ihd;
+        for (int e = tid; e < rows * ihd / 4; e += QSA_TILE) {
+            const int row = (4 * e) / ihd, col = 4 * e - row * ihd;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(pb_smem_u32(buf + row * ld + col)), "l"(src + 4 * e) : "memory");
         }
-        for (; i + 8 <= p.ihd; i += 8)
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float* bufs[2] = {tile, tile + (size_t)tile_rows * ld};
+    int cur = 0;
+    fetch((int64_t)blockIdx.x * tile_rows, bufs[0]);
+    for (int64_t t0 = (int64_t)blockIdx.x * tile_rows; t0 < nb; t0 += t_step, cur ^= 1) {
+        const int rows = (int)(nb - t0 < tile_rows ? nb - t0 : tile_rows);
+        if (t0 + t_step < nb) { fetch(t0 + t_step, bufs[cur ^ 1]); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                    // the tile (and, the first time, the queries) are ready
+        tile = bufs[cur];
+        if (tid < rows) {
+            const float* kb = tile + tid * ld;
+            float s = 0.f;
+            if (IHD > 0) {
+                float4 kr[IHD > 0 ? IHD / 4 : 1];
 #pragma unroll
-            for (int l = 0; l < 8; l++) a[0][l] = fmaf(q[i + l], kb[i + l], a[0][l]);
-        float r = 0.f;
+                for (int i = 0; i < IHD / 4; i++) kr[i] = *reinterpret_cast<const float4*>(kb + 4 * i);
+                for (int h = 0; h < p.inh; h++) {
+                    const float4* qh = reinterpret_cast<const float4*>(qsm + h * IHD);
+                    float acc[32];
 #pragma unroll
-        for (int l = 0; l < 8; l++) r += (a[0][l] + a[1][l]) + (a[2][l] + a[3][l]);
-        for (; i < p.ihd; i++) r += q[i] * kb[i];
-        s += r > 0.f ? r : 0.f;
+                    for (int j = 0; j < 32; j++) acc[j] = 0.f;
+#pragma unroll
+                    for (int i = 0; i < IHD / 4; i++) {
+                        const float4 qv = qh[i];
+                        const int j = (4 * i) & 31;
+                        acc[j] = fmaf(qv.x, kr[i].x, acc[j]); acc[j + 1] = fmaf(qv.y, kr[i].y, acc[j + 1]);
+                        acc[j + 2] = fmaf(qv.z, kr[i].z, acc[j + 2]); acc[j + 3] = fmaf(qv.w, kr[i].w, acc[j + 3]);
+                    }
+                    float r = 0.f;
+#pragma unroll
+                    for (int l = 0; l < 8; l++) r += (acc[l] + acc[8 + l]) + (acc[16 + l] + acc[24 + l]);
+                    s += r > 0.f ? r : 0.f;
+                }
+            } else {
+                for (int h = 0; h < p.inh; h++) {
+                    const float* qh = qsm + h * ihd;
+                    float acc[32];
+#pragma unroll
+                    for (int j = 0; j < 32; j++) acc[j] = 0.f;
+                    for (int i = 0; i < ihd; i += 32) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) acc[j] = fmaf(qh[i + j], kb[i + j], acc[j]);
+                    }
+                    float r = 0.f;
+#pragma unroll
+                    for (int l = 0; l < 8; l++) r += (acc[l] + acc[8 + l]) + (acc[16 + l] + acc[24 + l]);
+                    s += r > 0.f ? r : 0.f;
+                }
+            }
+            p.scores[(size_t)b * p.nb_cap + t0 + tid] = s * iscale;
+        }
+        __syncthreads();                                    // everyone has left this buffer before the next fetch refills it
     }
-    p.scores[(size_t)b * p.nb_cap + blk] = s * iscale;
 }
 
 // grid (batch), 1024 threads
@@ -137,7 +177,7 @@ __global__ void __launch_bounds__(1024) pb_qsa_pick_kernel(const PbQsaParams p) 
     const int b = blockIdx.x, tid = threadIdx.x;
     __shared__ unsigned int hist[256];
     __shared__ unsigned long long prefix_s;
-    __shared__ int want_s;
+    __shared__ int want_s, all_s;
     pb_pdl_wait();
     pb_pdl_trigger();
     const int64_t pos = p.pos[b], n = pos + 1;
@@ -161,15 +201,28 @@ __global__ void __launch_bounds__(1024) pb_qsa_pick_kernel(const PbQsaParams p) 
             if ((k & himask) == prefix) atomicAdd(&hist[(unsigned int)(k >> shift) & 255u], 1u);
         }
         __syncthreads();
-        if (tid == 0) {
-            int want = want_s, byte = 255;
-            for (; byte > 0; byte--) { if ((int)hist[byte] >= want) break; want -= (int)hist[byte]; }
-            prefix_s = prefix | ((unsigned long long)byte << shift);
-            want_s = want;
+        if (tid < 32) {
+            // the bin that holds the want-th largest: lane l owns bins 8 l .. 8 l + 7; `above` = keys in the bins of higher lanes
+            const int want = want_s;
+            unsigned int c[8], mine = 0u;
+#pragma unroll
+            for (int j = 0; j < 8; j++) { c[j] = hist[8 * tid + j]; mine += c[j]; }
+            unsigned int incl = mine;                    // inclusive suffix sum over lanes tid .. 31
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const unsigned int v = __shfl_down_sync(0xffffffffu, incl, o); if (tid + o < 32) incl += v; }
+            const unsigned int above = incl - mine;
+            if ((int)above < want && want <= (int)incl) {
+                int w = want - (int)above, j = 7;
+                for (; j > 0; j--) { if ((int)c[j] >= w) break; w -= (int)c[j]; }
+                prefix_s = prefix | ((unsigned long long)(8 * tid + j) << shift);
+                want_s = w;
+                all_s = (int)c[j] == w;                 // every key that shares the prefix so far is wanted
+            }
         }
         __syncthreads();
+        if (shift == 32 && all_s) break;                // no tie at the cut: the block index bits need not be searched
     }
-    const unsigned long long thr = prefix_s;            // the kk-th largest key: exactly kk keys are >= thr
+    const unsigned long long thr = prefix_s;            // the kk-th largest key (its low half zero when the search stopped early): exactly kk keys are >= thr
     uint32_t* mask = p.mask + (size_t)b * p.mask_ld;
     const int64_t nwords = (n + 31) / 32;
     for (int64_t w = tid; w < nwords; w += 1024) mask[w] = 0u;
@@ -191,9 +244,19 @@ int pb_launch_qsa_append(pb_ctx* ctx, const PbQsaParams& p) {
 }
 
 int pb_launch_qsa_select(pb_ctx* ctx, const PbQsaParams& p) {
-    const size_t smem = (size_t)p.inh * p.ihd * 4;
-    if (smem > 48 * 1024) PB_FAIL(ctx, PB_UNSUPPORTED, "indexer with %d heads of %d", p.inh, p.ihd);
-    pb_launch_k(ctx, pb_qsa_score_kernel, dim3((unsigned)((p.nb_cap + 127) / 128), p.batch), dim3(128), smem, p);
+    if (p.ihd % 32) PB_FAIL(ctx, PB_UNSUPPORTED, "indexer head dim %d (a multiple of 32)", p.ihd);
+    int tile_rows = QSA_TILE;
+    auto need = [&](int rows) { return ((size_t)p.inh * p.ihd + (size_t)2 * rows * (p.ihd + 4)) * 4; };
+    while (need(tile_rows) > 96 * 1024 && tile_rows > 8) tile_rows /= 2;
+    const size_t smem = need(tile_rows);
+    if (smem > 96 * 1024) PB_FAIL(ctx, PB_UNSUPPORTED, "indexer with %d heads of %d does not fit shared memory", p.inh, p.ihd);
+    int64_t gx = (p.nb_cap + tile_rows - 1) / tile_rows;
+    const int64_t cap = p.batch >= 4 ? 32 : 256;     // enough CTAs to fill the GPU
+    if (gx > cap) gx = cap;
+    const dim3 grid((unsigned)gx, p.batch);
+    if (p.ihd == 128) { PB_TRY(pb_ensure_smem(ctx, pb_qsa_score_kernel<128>, smem)); pb_launch_k(ctx, pb_qsa_score_kernel<128>, grid, dim3(QSA_TILE), smem, p, tile_rows); }
+    else if (p.ihd == 64) { PB_TRY(pb_ensure_smem(ctx, pb_qsa_score_kernel<64>, smem)); pb_launch_k(ctx, pb_qsa_score_kernel<64>, grid, dim3(QSA_TILE), smem, p, tile_rows); }
+    else { PB_TRY(pb_ensure_smem(ctx, pb_qsa_score_kernel<0>, smem)); pb_launch_k(ctx, pb_qsa_score_kernel<0>, grid, dim3(QSA_TILE), smem, p, tile_rows); }
     pb_launch_k(ctx, pb_qsa_pick_kernel, dim3(p.batch), dim3(1024), (size_t)0, p);
     ctx->kernels_launched += 2;
     PB_CUDA(ctx, cudaGetLastError());
