@@ -162,6 +162,8 @@ typedef enum pb_role {
     PB_R_OUT_HC_NORM, PB_R_OUT_HC_DOWN, PB_R_OUT_HC_UP,
     /* QSA indexer of an attention layer (Mixer::Attn idx, :501): blk.N.indexer.q_proj / k_proj / q_norm / k_norm */
     PB_R_IDX_Q, PB_R_IDX_K, PB_R_IDX_Q_NORM, PB_R_IDX_K_NORM,
+    /* input stage of an MTP drafter model (src/model/mtp.rs:104-123): fc_embedding, fc_hidden, pre_fc_norm_embedding, pre_fc_norm_hidden */
+    PB_R_MTP_FC_E, PB_R_MTP_FC_H, PB_R_MTP_PRE_E, PB_R_MTP_PRE_H,
     PB_R_COUNT
 } pb_role;
 
@@ -226,9 +228,27 @@ int pb_decode_greedy(pb_state* s, const uint32_t* tok_host, int n, uint32_t* out
 int pb_verify(pb_state* s, const uint32_t* ids_host, int t, float* logits_host);
 /* Model::spec_keep :2495-2515 (= Target::keep): keep the first `keep` of the last t verified tokens. */
 int pb_keep(pb_state* s, int t, int keep);
-/* Model::mtp_draft :2177 (= Target::draft).  Returns PB_UNSUPPORTED: the caller's n-gram drafter
- * then takes over (src/spec.rs:207). */
-int pb_draft(pb_state* s, int max_draft, uint32_t* ids_host, int* n);
+/* The model's own multi-token-prediction layer as a speculative drafter (src/model/mtp.rs; Mtp::load :104-123).
+ * The drafter is a pb_model of its own: cfg with n_layers = 1, full_every = 1 (one attention layer), the main model's
+ * d and hc, kv_bits = 0, max_ctx >= the main model's, vocab = the size of the draft vocabulary; tensors under the usual
+ * roles of an attention layer with hyper-connections and a MoE block (layer 0), PB_R_OUT_HC_* = the final mixer,
+ * PB_R_OUTPUT = the head rows of the draft vocabulary, PB_R_MTP_* = the input stage; norm vectors hold 1 + w as in
+ * the main model.  pb_model_set_mtp marks it (window = cells a draft step attends to, reference default 128) before
+ * pb_model_finalize. */
+int pb_model_set_mtp(pb_model* drafter, int window);
+/* Binds a finalized drafter to a batch-1 state of the main model (which must have hyper-connection streams: hc >= 1).
+ * vocab_ids[i] = the token whose head row is row i of the drafter's PB_R_OUTPUT.  From here on the state keeps the final
+ * residual row of every position it processes (mtp_keep_r :2279-2285) and the ids it is fed.  The drafter model must
+ * outlive the state. */
+int pb_state_attach_drafter(pb_state* s, pb_model* drafter, const uint32_t* vocab_ids_host, int n_ids);
+/* Model::mtp_draft :2177-2278 (= Target::draft): up to max_draft tokens that follow the tokens fed so far and `pending`,
+ * the token already chosen but not fed yet (the last element of spec.rs's history).  Cells of earlier positions the
+ * drafter has not seen are caught up first (K/V only).  Token j > 0 is kept only while the drafter's probability of it
+ * (softmax over the draft vocabulary) is at least min_p (draft_gate, src/spec.rs:326; reference default 0.9).
+ * probs_host may be NULL.  *n = 0 when the residual of the last position is not held (e.g. right after a restore).
+ * Every emitted token still comes from pb_verify, so greedy output is unchanged by drafting.
+ * Without an attached drafter: PB_UNSUPPORTED, and the caller's n-gram drafter takes over (src/spec.rs:207). */
+int pb_draft(pb_state* s, uint32_t pending, int max_draft, float min_p, uint32_t* ids_host, float* probs_host, int* n);
 
 /* Model::snapshot / restore, Snap :3277-3298.  size query: pass buf_host = NULL. */
 int pb_state_snapshot(pb_state* s, void* buf_host, size_t* nbytes);

@@ -29,6 +29,7 @@ ROLES = [
     "HCA_NORM", "HCA_DOWN", "HCA_UP", "HCA_INJECT", "HCF_NORM", "HCF_DOWN", "HCF_UP", "HCF_INJECT",
     "OUT_HC_NORM", "OUT_HC_DOWN", "OUT_HC_UP",
     "IDX_Q", "IDX_K", "IDX_Q_NORM", "IDX_K_NORM",
+    "MTP_FC_E", "MTP_FC_H", "MTP_PRE_E", "MTP_PRE_H",
 ]
 ROLE = {n: i for i, n in enumerate(ROLES)}
 
@@ -348,6 +349,22 @@ class State:
         if rc:
             raise RuntimeError(f"orc_forward failed: {rc}")
         return logits
+
+    def last_residual(self) -> np.ndarray:
+        """Final residual rows [t][max(hc, 1) * d] of the tokens of the last forward call."""
+        c = self.model.cfg
+        buf = np.empty(4096 * max(c.hc, 1) * c.d, np.float32)
+        n = lib().orc_last_residual(self.h, _p(buf), C.c_int64(buf.size))
+        assert n >= 0
+        return buf[:n].reshape(-1, max(c.hc, 1) * c.d).copy()
+
+    def mtp_cell(self, R, emb, pos: int, c0: int, window: int, full: bool):
+        """This state belongs to a drafter model (one attention layer + MTP tensors): one drafter cell.  Returns (s, rr) when full."""
+        c = self.model.cfg
+        R, emb = _f32(R).reshape(-1), _f32(emb).reshape(-1)
+        s = np.empty(c.d, np.float32); rr = np.empty(c.hc * c.d, np.float32)
+        lib().orc_mtp_cell(self.model.h, self.h, _p(R), _p(emb), C.c_int64(pos), C.c_int64(c0), C.c_int(window), C.c_int(1 if full else 0), _p(s), _p(rr))
+        return (s, rr) if full else None
 
     def margins(self):
         a, b = C.c_float(), C.c_float()

@@ -615,6 +615,7 @@ struct orc_state {
     int n_lin, n_attn;
     float** ik; float** ib;              /* per attention layer: raw index keys [max_ctx][idx_hd], pooled block keys [max_ctx/ratio][idx_hd] (State :194) */
     float logit_margin, router_margin, qsa_margin;
+    float* last_x; int64_t last_x_n;      /* final residual rows of the last forward call */
 };
 
 static orc_slot* slot(const orc_model* m, int layer, int role) { return &m->slots[(size_t)(layer + 1) * ORC_R_COUNT + role]; }
@@ -674,7 +675,7 @@ void orc_state_free(orc_state* s) {
     if (!s) return;
     for (int i = 0; i < s->n_lin; i++) { free(s->conv[i]); free(s->ssm[i]); }
     for (int i = 0; i < s->n_attn; i++) { free(s->k[i]); free(s->v[i]); free(s->kw[i]); free(s->vw[i]); free(s->ks[i]); free(s->vs[i]); free(s->ik[i]); free(s->ib[i]); }
-    free(s->ik); free(s->ib); free(s->conv); free(s->ssm); free(s->k); free(s->v); free(s->kw); free(s->vw); free(s->ks); free(s->vs); free(s->q4n); free(s);
+    free(s->ik); free(s->ib); free(s->last_x); free(s->conv); free(s->ssm); free(s->k); free(s->v); free(s->kw); free(s->vw); free(s->ks); free(s->vs); free(s->q4n); free(s);
 }
 /* Layout rule of the packed region (kv_push :1517-1534): with len positions held, the first
  * q4n = ((len - recent) / 64) * 64 are 4-bit (whole multiples of 64 positions), the rest f32. */
@@ -776,6 +777,7 @@ int orc_forward(const orc_model* m, orc_state* st, const uint32_t* ids, int t, f
         }
         if (hc > 0) hc_combine(c, x, o, inj, t); else for (int64_t i = 0; i < (int64_t)t * d; i++) x[i] += o[i];
     }
+    st->last_x = (float*)realloc(st->last_x, (size_t)t * xw * 4); memcpy(st->last_x, x, (size_t)t * xw * 4); st->last_x_n = (int64_t)t * xw;   /* mtp_keep_r :2150 */
     const float* last = x + (int64_t)(t - 1) * xw;
     if (hc > 0) hc_mix(m, -1, ORC_R_OUT_HC_NORM, ORC_R_OUT_HC_DOWN, ORC_R_OUT_HC_UP, -1, last, 1, mx, inj);  /* :2152 */
     else rms(last, V(m, -1, ORC_R_OUT_NORM), c->eps, mx, d);
@@ -785,4 +787,45 @@ int orc_forward(const orc_model* m, orc_state* st, const uint32_t* ids, int t, f
     st->pos = start + t;
     free(x); free(mx); free(o); free(inj);
     return 0;
+}
+
+int orc_last_residual(const orc_state* s, float* out, int64_t cap_floats) {
+    if (!s->last_x || s->last_x_n > cap_floats) return -1;
+    memcpy(out, s->last_x, (size_t)s->last_x_n * 4); return (int)s->last_x_n;
+}
+
+/* ------------------------------------------------------------------ MTP drafter (src/model/mtp.rs) */
+void orc_mtp_cell(const orc_model* dm, orc_state* ds, const float* R, const float* emb, int64_t pos, int64_t c0, int window, int full, float* s_out, float* rr_out) {
+    const orc_cfg* c = &dm->cfg; int d = c->d, hc = c->hc, w = hc * d; int row = c->n_kv * c->hd; int nq = c->n_head * 2 * c->hd;
+    float* en = (float*)malloc((size_t)d * 4); float* e2 = (float*)malloc((size_t)d * 4); float* hn = (float*)malloc((size_t)w * 4); float* rr = (float*)malloc((size_t)w * 4);
+    float* m = (float*)malloc((size_t)d * 4); float* inj = (float*)malloc((size_t)hc * 4); float* o = (float*)malloc((size_t)d * 4);
+    /* input :186-195: e = fc_embedding(rms(embed) * pre_e), h = fc_hidden per stream of rms over all hc*d values * pre_h, R' = h + e */
+    rms(emb, V(dm, -1, ORC_R_MTP_PRE_E), c->eps, en, d); orc_matmul(M(dm, -1, ORC_R_MTP_FC_E), en, 1, e2);
+    rms(R, V(dm, -1, ORC_R_MTP_PRE_H), c->eps, hn, w); orc_matmul(M(dm, -1, ORC_R_MTP_FC_H), hn, hc, rr);
+    for (int s = 0; s < hc; s++) for (int i = 0; i < d; i++) rr[s * d + i] += e2[i];
+    /* kv_append :156-170 */
+    hc_mix(dm, 0, ORC_R_HCA_NORM, ORC_R_HCA_DOWN, ORC_R_HCA_UP, ORC_R_HCA_INJECT, rr, 1, m, inj);
+    float* kf = (float*)malloc((size_t)row * 4); float* vf = (float*)malloc((size_t)row * 4);
+    orc_matmul(M(dm, 0, ORC_R_ATTN_K), m, 1, kf); orc_matmul(M(dm, 0, ORC_R_ATTN_V), m, 1, vf);
+    if (!full) {
+        float* kd = ds->k[0] + pos * row; memcpy(kd, kf, (size_t)row * 4);
+        for (int h = 0; h < c->n_kv; h++) { rms_inplace(kd + h * c->hd, V(dm, 0, ORC_R_ATTN_K_NORM), c->eps, c->hd); rope(kd + h * c->hd, pos, dm->rope_inv, c->n_rot); }
+        memcpy(ds->v[0] + pos * row, vf, (size_t)row * 4);
+    } else {
+        /* step :184-236: dense attention over the window of cells, MoE, final mixer */
+        float* qf = (float*)malloc((size_t)nq * 4); float* att = (float*)malloc((size_t)c->n_head * c->hd * 4);
+        orc_matmul(M(dm, 0, ORC_R_ATTN_Q), m, 1, qf);
+        int64_t lo = pos - window + 1; if (lo < c0) lo = c0; int64_t nps = pos - lo + 1; int64_t* ps = (int64_t*)malloc((size_t)nps * 8);
+        for (int64_t j = 0; j < nps; j++) ps[j] = lo + j;
+        orc_attn_core_sel(c, qf, kf, vf, V(dm, 0, ORC_R_ATTN_Q_NORM), V(dm, 0, ORC_R_ATTN_K_NORM), dm->rope_inv, ds->k[0], ds->v[0], pos, NULL, NULL, NULL, NULL, 0, ps, nps, att);
+        orc_matmul(M(dm, 0, ORC_R_ATTN_O), att, 1, o); hc_combine(c, rr, o, inj, 1);
+        hc_mix(dm, 0, ORC_R_HCF_NORM, ORC_R_HCF_DOWN, ORC_R_HCF_UP, ORC_R_HCF_INJECT, rr, 1, m, inj);
+        int32_t* sel = (int32_t*)malloc((size_t)c->top_k * 4);
+        orc_moe(c, M(dm, 0, ORC_R_ROUTER), M(dm, 0, ORC_R_EXP_GATE), M(dm, 0, ORC_R_EXP_UP), M(dm, 0, ORC_R_EXP_DOWN), M(dm, 0, ORC_R_SH_GATE), M(dm, 0, ORC_R_SH_UP), M(dm, 0, ORC_R_SH_DOWN), V(dm, 0, ORC_R_SH_GATE_INP), m, 1, o, sel, NULL);
+        hc_combine(c, rr, o, inj, 1);
+        hc_mix(dm, -1, ORC_R_OUT_HC_NORM, ORC_R_OUT_HC_DOWN, ORC_R_OUT_HC_UP, -1, rr, 1, s_out, inj);
+        memcpy(rr_out, rr, (size_t)w * 4);
+        free(qf); free(att); free(ps); free(sel);
+    }
+    free(en); free(e2); free(hn); free(rr); free(m); free(inj); free(o); free(kf); free(vf);
 }

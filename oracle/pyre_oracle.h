@@ -89,6 +89,7 @@ enum {
     ORC_R_HCF_NORM, ORC_R_HCF_DOWN, ORC_R_HCF_UP, ORC_R_HCF_INJECT,
     ORC_R_OUT_HC_NORM, ORC_R_OUT_HC_DOWN, ORC_R_OUT_HC_UP,
     ORC_R_IDX_Q, ORC_R_IDX_K, ORC_R_IDX_Q_NORM, ORC_R_IDX_K_NORM,   /* QSA indexer of an attention layer (Mixer::Attn idx, :501) */
+    ORC_R_MTP_FC_E, ORC_R_MTP_FC_H, ORC_R_MTP_PRE_E, ORC_R_MTP_PRE_H,   /* input stage of the MTP drafter (src/model/mtp.rs:186-195), global */
     ORC_R_COUNT
 };
 
@@ -111,6 +112,14 @@ int orc_forward(const orc_model* m, orc_state* s, const uint32_t* ids, int t, fl
 /* per-step margins for near-tie classification: top-2 logit margin, min 10th/11th router margin */
 void orc_last_margins(const orc_state* s, float* logit_margin, float* router_margin);
 float orc_last_qsa_margin(const orc_state* s);
+/* final multi-stream residual rows [t][max(hc,1) * d] of the tokens of the last orc_forward call (what the MTP drafter pairs with the next token) */
+int orc_last_residual(const orc_state* s, float* out, int64_t cap_floats);
+/* MTP drafter (src/model/mtp.rs): `dm` is a model of ONE attention layer with hyper-connections and a MoE block, whose global slots
+ * also hold ORC_R_MTP_*; its OUT_HC_* tensors are the final mixer and its OUTPUT the draft-vocabulary head.  One cell at rope position
+ * `pos`: R = the main model's residual row of position pos [hc*d], emb = the embedding row of token pos + 1.  The cell's K/V go into
+ * `ds` at row pos.  full = 0: K/V only (catch_up :172-175); full = 1: the whole step (step :184-236) attending to the cells
+ * max(c0, pos - window + 1) .. pos, s_out [d] = the final mixer's output for the head, rr_out [hc*d] = the drafter's residual. */
+void orc_mtp_cell(const orc_model* dm, orc_state* ds, const float* R, const float* emb, int64_t pos, int64_t c0, int window, int full, float* s_out, float* rr_out);
 
 /* ---- layer-level entry points (same arithmetic as inside orc_forward) ---- */
 /* MoE block: ffn :1675-1684 + routed (f32 branch) :1721-1793.  x [t][d] -> y [t][d].

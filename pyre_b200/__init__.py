@@ -34,6 +34,7 @@ ROLES = [
     "HCA_NORM", "HCA_DOWN", "HCA_UP", "HCA_INJECT", "HCF_NORM", "HCF_DOWN", "HCF_UP", "HCF_INJECT",
     "OUT_HC_NORM", "OUT_HC_DOWN", "OUT_HC_UP",
     "IDX_Q", "IDX_K", "IDX_Q_NORM", "IDX_K_NORM",
+    "MTP_FC_E", "MTP_FC_H", "MTP_PRE_E", "MTP_PRE_H",
 ]
 ROLE = {n: i for i, n in enumerate(ROLES)}
 

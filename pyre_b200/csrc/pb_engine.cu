@@ -38,11 +38,26 @@ struct pb_model {
     int ctx_train = 0;           // trained context (0: unknown, no scaling)
     int idx_budget = 0, idx_ratio = 1, idx_nh = 0, idx_hd = 0;   // QSA indexer geometry (Cfg :24-25); idx_nh = 0: none
     bool qsa = false;            // the attention layers hold indexer tensors
+    int mtp_window = 0;          // > 0: this model is an MTP drafter layer (pb_model_set_mtp)
     uint64_t weight_bytes_step = 0;
 };
 
 struct PbKv { uint32_t *kw = nullptr, *vw = nullptr; float *ks = nullptr, *vs = nullptr, *kr = nullptr, *vr = nullptr; int64_t* q4n = nullptr;
               float *ik = nullptr, *ib = nullptr; };   // QSA: raw index keys [batch][max_ctx][idx_hd], pooled block keys [batch][nb_cap][idx_hd]
+
+// MTP drafter attached to a state of the main model (src/model/mtp.rs; bookkeeping of mtp_draft_in, qwen4exp_gguf.rs:2179-2278)
+struct PbMtp {
+    pb_model* dm = nullptr; pb_state* ds = nullptr;     // the drafter layer and its own state (one sequence, f32 K/V by cell)
+    int window = 128;
+    float* ring = nullptr; int ring_cap = 0;            // the main model's final residual rows by position % ring_cap
+    std::vector<int64_t> ring_pos;                      // position held by each slot (-1: none)
+    std::vector<uint32_t> tokens; int64_t tok_base = 0; // ids the main state has been fed, tokens[i] at position tok_base + i
+    int64_t kv_c0 = 0, kv_end = 0;                      // the drafter holds cells [kv_c0, kv_end)
+    std::vector<uint32_t> ids; int n_ids = 0;           // draft vocabulary
+    float *e_raw = nullptr, *en = nullptr, *e2 = nullptr, *hn = nullptr, *h2 = nullptr, *lg = nullptr;
+    uint32_t *tok_dev = nullptr, *best = nullptr, *mask = nullptr; int* mask_on = nullptr;
+    uint32_t* pin = nullptr;                            // pinned: [1..2] (index, probability bits) of a draft step, read back
+};
 
 struct pb_state {
     pb_model* m = nullptr;
@@ -71,6 +86,8 @@ struct pb_state {
     // peer exchange (pb_ep.cu): xg and part_rs live in a block mapped into every rank; the kernels store into the peers' blocks
     bool p2p = false; PbEpSymm symm; PbEpExch exch{}; PbEpExch* exch_dev = nullptr; float** part_tok = nullptr; unsigned long long* ep_seq = nullptr;
     int64_t ldproj = 0, ring_cap = 0;
+    struct PbMtp* mtp = nullptr;   // drafter attached to this (main, batch-1) state
+    uint32_t* ext_mask = nullptr; int* ext_on = nullptr; int64_t ext_ld = 0;   // a position mask set from outside (the drafter's window of cells)
     float *iproj = nullptr, *qsa_scores = nullptr; uint32_t* qsa_mask = nullptr; int* qsa_on = nullptr; int64_t ldi = 0, nb_cap = 0, mask_ld = 0;   // QSA work buffers
     std::vector<float*> conv, ssm;
     std::vector<PbKv> kv;
@@ -92,6 +109,11 @@ struct pb_state {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;   // GPU time of the token-loop calls (pb_stats.device_ns)
     bool ev_open = false; uint64_t device_ns = 0;
 };
+extern "C" {
+static void mtp_moved(pb_state* s, int64_t pos);
+static void mtp_forget(PbMtp* t, int64_t pos);
+}
+
 // Brackets the GPU work of one token-loop call with two events; the elapsed time is added up once the call has synchronised.
 static void timing_begin(pb_state* s) {
     pb_ctx* ctx = s->m->ctx;
@@ -157,6 +179,16 @@ int pb_model_set_tensor(pb_model* m, int layer, int role, pb_qmat* mat) {
     PbSlot& s = slot(m, layer, role);
     if (s.mat) pb_qmat_free(s.mat);
     s.mat = mat;
+    return PB_OK;
+}
+
+int pb_model_set_mtp(pb_model* m, int window) {
+    if (!m) return PB_ERR_ARG;
+    pb_ctx* ctx = m->ctx;
+    PB_TRY(pb_enter(ctx));
+    if (m->finalized) PB_FAIL(ctx, PB_ERR_STATE, "pb_model_set_mtp: model already finalized");
+    if (window < 1) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_set_mtp: window %d", window);
+    m->mtp_window = window;
     return PB_OK;
 }
 
@@ -236,6 +268,16 @@ int pb_model_finalize(pb_model* m, int ep_rank, int ep_world) {
     const int ch = 2 * c.lin_nk * c.lin_dk + c.lin_nv * c.lin_dv, row = c.n_kv * c.hd;
     uint64_t wb = 0;
     int n_attn_seen = 0;
+    if (m->mtp_window > 0) {
+        // an MTP drafter layer (src/model/mtp.rs:104-123): one attention layer with hyper-connections, the input stage's tensors,
+        // its OUTPUT = the draft-vocabulary head; embeddings come from the main model
+        if (c.n_layers != 1 || c.full_every != 1 || c.hc < 1 || c.kv_bits != 0) PB_FAIL(ctx, PB_UNSUPPORTED, "an MTP drafter is one attention layer with hyper-connections and an f32 cache");
+        PB_TRY(need_mat(m, -1, PB_R_MTP_FC_E, c.d, c.d, "fc_embedding", false));
+        PB_TRY(need_mat(m, -1, PB_R_MTP_FC_H, c.d, c.d, "fc_hidden", false));
+        PB_TRY(need_vec(m, -1, PB_R_MTP_PRE_E, c.d, "pre_fc_norm_embedding"));
+        PB_TRY(need_vec(m, -1, PB_R_MTP_PRE_H, (int64_t)c.hc * c.d, "pre_fc_norm_hidden"));
+        if (!M(m, -1, PB_R_OUTPUT)) PB_FAIL(ctx, PB_ERR_STATE, "an MTP drafter needs its draft-vocabulary head (OUTPUT)");
+    } else
     PB_TRY(need_mat(m, -1, PB_R_TOKEN_EMBD, c.vocab, c.d, "token_embd", false));
     if (!M(m, -1, PB_R_OUTPUT)) { /* falls back to token_embd (:511) */ }
     else PB_TRY(need_mat(m, -1, PB_R_OUTPUT, c.vocab, c.d, "output", true));
@@ -503,6 +545,7 @@ int pb_state_destroy(pb_state* s) {
     if (s->ev1) cudaEventDestroy(s->ev1);
     for (cudaGraphExec_t g : s->win_graph) if (g) cudaGraphExecDestroy(g);
     for (void* p : s->allocs) cudaFree(p);
+    if (s->mtp) { if (s->mtp->ds) pb_state_destroy(s->mtp->ds); if (s->mtp->pin) cudaFreeHost(s->mtp->pin); delete s->mtp; }   // its device buffers are in s->allocs
     pb_ep_symm_free(s->m->ctx, &s->symm);
     if (s->pin_u32) cudaFreeHost(s->pin_u32);
     if (s->pin_logits) cudaFreeHost(s->pin_logits);
@@ -533,6 +576,7 @@ int pb_state_set_pos(pb_state* s, int64_t pos) {
     PB_CUDA(ctx, cudaMemcpyAsync(s->pos, v.data(), v.size() * 8, cudaMemcpyHostToDevice, ctx->stream));
     PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     s->pos_host = pos;
+    mtp_moved(s, pos);
     return PB_OK;
 }
 int pb_state_reset(pb_state* s) {
@@ -650,6 +694,7 @@ static int run_attn(pb_state* s, int il, const float* x_in, const float* norm_w,
         qsa_params(s, il, qp);
         p.qsa_mask = s->qsa_mask; p.qsa_ld = s->mask_ld; p.qsa_on = s->qsa_on;
     }
+    if (s->ext_mask) { p.qsa_mask = s->ext_mask; p.qsa_ld = s->ext_ld; p.qsa_on = s->ext_on; }
     if (s->win_t > 0 && !s->win_ckpt && !m->qsa) {
         // a prefill chunk: all tokens are appended, the packed boundary moves once, then every token attends to the
         // positions <= its own in one launch (token j treats as packed what it would have found packed token by token)
@@ -957,7 +1002,7 @@ static int run_step(pb_state* s) {
     if (s->fused == 1) return run_step_fused(s);
     struct Scope { pb_ctx* c; Scope(pb_ctx* x) : c(x) { c->pdl_scope++; c->pdl_chain = false; } ~Scope() { c->pdl_scope--; c->pdl_chain = false; } } scope(ctx);
     pb_qmat* embd = M(m, -1, PB_R_TOKEN_EMBD);
-    if (c.hc > 0) PB_TRY(run_layers_hc(s, B, 0, B));
+    if (c.hc > 0) { PB_TRY(run_layers_hc(s, B, 0, B)); if (s->mtp) PB_TRY(pb_launch_mtp_keep(ctx, s->x, (int64_t)c.hc * c.d, s->pos, 1, s->mtp->ring, s->mtp->ring_cap, c.hc * c.d)); }
     else {
         PB_TRY(pb_launch_embed(ctx, embd->type, embd->data, embd->rows, c.d, s->ids, B, s->x, c.d));
         for (int il = 0; il < c.n_layers; il++) {
@@ -987,7 +1032,7 @@ static int run_window(pb_state* s, int t, bool ckpt, bool all_logits) {
                    ~Scope() { c->pdl_scope--; c->pdl_chain = false; s->win_t = 0; s->win_ckpt = false; } } scope(ctx, s, t, ckpt);
     PB_TRY(pb_launch_window_pos(ctx, s->pos, s->wpos, t, 0));
     pb_qmat* embd = M(m, -1, PB_R_TOKEN_EMBD);
-    if (c.hc > 0) PB_TRY(run_layers_hc(s, t, all_logits ? 0 : t - 1, all_logits ? t : 1));
+    if (c.hc > 0) { PB_TRY(run_layers_hc(s, t, all_logits ? 0 : t - 1, all_logits ? t : 1)); if (s->mtp) PB_TRY(pb_launch_mtp_keep(ctx, s->x, (int64_t)c.hc * c.d, s->wpos, t, s->mtp->ring, s->mtp->ring_cap, c.hc * c.d)); }
     else {
         PB_TRY(pb_launch_embed(ctx, embd->type, embd->data, embd->rows, c.d, s->ids, t, s->x, c.d));
         for (int il = 0; il < c.n_layers; il++) {
@@ -1082,6 +1127,27 @@ static int logits_stage(pb_state* s, size_t n) {
     return PB_OK;
 }
 
+// ---- MTP drafter bookkeeping on the host: which tokens the main state was fed and which residual rows the ring holds ----
+static void mtp_forget(PbMtp* t, int64_t pos) { t->tokens.clear(); t->tok_base = pos; std::fill(t->ring_pos.begin(), t->ring_pos.end(), (int64_t)-1); t->kv_c0 = t->kv_end = pos; }
+// the state is about to process `n` tokens `ids` at positions [pos0, pos0 + n)
+static void mtp_note(pb_state* s, int64_t pos0, const uint32_t* ids, int n) {
+    PbMtp* t = s->mtp;
+    if (!t) return;
+    if (pos0 < t->tok_base || pos0 > t->tok_base + (int64_t)t->tokens.size()) mtp_forget(t, pos0);
+    t->tokens.resize((size_t)(pos0 - t->tok_base));
+    for (int j = 0; j < n; j++) { t->tokens.push_back(ids[j]); t->ring_pos[(size_t)((pos0 + j) % t->ring_cap)] = pos0 + j; }
+}
+// the position moved to `pos` by other means (rollback, restore, reset): keep what lies before it
+static void mtp_moved(pb_state* s, int64_t pos) {
+    PbMtp* t = s->mtp;
+    if (!t) return;
+    if (pos < t->tok_base || pos > t->tok_base + (int64_t)t->tokens.size()) { mtp_forget(t, pos); return; }
+    t->tokens.resize((size_t)(pos - t->tok_base));
+    for (int64_t& p : t->ring_pos) if (p >= pos) p = -1;
+    if (t->kv_end > pos) t->kv_end = pos;
+    if (t->kv_c0 > t->kv_end) t->kv_c0 = t->kv_end;
+}
+
 int pb_forward(pb_state* s, const uint32_t* ids_host, int t, float* logits_host) {
     if (!s) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx;
@@ -1093,6 +1159,7 @@ int pb_forward(pb_state* s, const uint32_t* ids_host, int t, float* logits_host)
         // the absolute grid of that size -- the first piece runs up to the next multiple of the chunk, so a prompt resumed
         // from a snapshot taken on the grid is split exactly like a prefill from position 0 (src/engine_qn.rs:117-128)
         if (s->pos_host + t > s->m->cfg.max_ctx) PB_FAIL(ctx, PB_ERR_STATE, "context is full (%d positions)", s->m->cfg.max_ctx);
+        mtp_note(s, s->pos_host, ids_host, t);
         timing_begin(s);
         for (int j0 = 0, n = 0; j0 < t; j0 += n) {
             const int64_t to_grid = PB_PREFILL_CHUNK - s->pos_host % PB_PREFILL_CHUNK;
@@ -1110,6 +1177,7 @@ int pb_forward(pb_state* s, const uint32_t* ids_host, int t, float* logits_host)
         if (rcw == PB_OK) memcpy(logits_host, s->pin_logits, (size_t)s->m->cfg.vocab * 4);
         return rcw;
     }
+    if (B == 1) mtp_note(s, s->pos_host, ids_host, t);
     timing_begin(s);
     for (int j = 0; j < t; j++) {
         for (int b = 0; b < B; b++) s->pin_u32[b] = ids_host[(size_t)b * t + j];
@@ -1131,6 +1199,7 @@ int pb_step_greedy(pb_state* s, const uint32_t* tok_host, uint32_t* next_host) {
     PB_TRY(pb_enter(ctx));
     if (!tok_host || !next_host) PB_FAIL(ctx, PB_ERR_ARG, "pb_step_greedy: null buffer");
     const int B = s->batch;
+    if (B == 1) mtp_note(s, s->pos_host, tok_host, 1);
     memcpy(s->pin_u32, tok_host, (size_t)B * 4);
     PB_CUDA(ctx, cudaMemcpyAsync(s->ids, s->pin_u32, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
     timing_begin(s);
@@ -1160,6 +1229,7 @@ int pb_decode_greedy(pb_state* s, const uint32_t* tok_host, int n, uint32_t* out
     PB_TRY(pb_sync_check(ctx, "pb_decode_greedy"));
     timing_collect(s);
     for (int j = 0; j < n; j++) for (int b = 0; b < B; b++) out_host[(size_t)b * n + j] = s->pin_u32[2 * B + (size_t)j * B + b];
+    if (B == 1 && s->mtp) { mtp_note(s, s->pos_host - n, tok_host, 1); if (n > 1) mtp_note(s, s->pos_host - n + 1, out_host, n - 1); }   // fed: the first token, then each output but the last
     return PB_OK;
 }
 
@@ -1184,6 +1254,7 @@ int pb_verify(pb_state* s, const uint32_t* ids_host, int t, float* logits_host) 
         for (size_t i = 0; i < s->ck_conv.size(); i++) { PB_TRY(dalloc(s, &s->ck_conv[i], conv_elems(c, 1))); PB_TRY(dalloc(s, &s->ck_ssm[i], ssm_elems(c, 1))); }
     }
     s->verify_pos0 = s->pos_host; s->verify_t = 0;
+    mtp_note(s, s->pos_host, ids_host, t);
     for (int j = 0; j < t; j++) s->pin_u32[j] = ids_host[j];
     PB_CUDA(ctx, cudaMemcpyAsync(s->ids, s->pin_u32, (size_t)t * 4, cudaMemcpyHostToDevice, ctx->stream));
     timing_begin(s);
@@ -1218,7 +1289,150 @@ int pb_keep(pb_state* s, int t, int keep) {
     return PB_OK;
 }
 
-int pb_draft(pb_state* s, int, uint32_t*, int* n) { if (!s) return PB_ERR_ARG; if (n) *n = 0; PB_FAIL(s->m->ctx, PB_UNSUPPORTED, "no drafter: use the caller's n-gram drafter"); }
+// ---------------------------------------------------------------- MTP drafter (src/model/mtp.rs, mtp_draft_in :2179-2278)
+int pb_state_attach_drafter(pb_state* s, pb_model* dm, const uint32_t* vocab_ids_host, int n_ids) {
+    if (!s || !dm) return PB_ERR_ARG;
+    pb_model* m = s->m; pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg; const pb_cfg& dc = dm->cfg;
+    PB_TRY(pb_enter(ctx));
+    if (s->mtp) PB_FAIL(ctx, PB_ERR_STATE, "pb_state_attach_drafter: the state already has a drafter");
+    if (dm->ctx != ctx || !dm->finalized || dm->mtp_window < 1) PB_FAIL(ctx, PB_ERR_STATE, "pb_state_attach_drafter: not a finalized drafter model of this context (pb_model_set_mtp)");
+    if (s->batch != 1 || s->sharded || c.hc < 1) PB_FAIL(ctx, PB_UNSUPPORTED, "pb_state_attach_drafter: the drafter follows one sequence of a model with hyper-connection streams");
+    if (dc.d != c.d || dc.hc != c.hc || dc.max_ctx < c.max_ctx) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_attach_drafter: drafter of width %d x %d streams and %d positions for a model of %d x %d and %d", dc.d, dc.hc, dc.max_ctx, c.d, c.hc, c.max_ctx);
+    if (!vocab_ids_host || n_ids != dc.vocab) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_attach_drafter: %d draft-vocabulary ids for a head of %d rows", n_ids, dc.vocab);
+    for (int i = 0; i < n_ids; i++) if (vocab_ids_host[i] >= (uint32_t)c.vocab) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_attach_drafter: id %u outside the vocabulary", vocab_ids_host[i]);
+    PbMtp* t = new PbMtp();
+    s->mtp = t;
+    t->dm = dm; t->window = dm->mtp_window; t->n_ids = n_ids; t->ids.assign(vocab_ids_host, vocab_ids_host + n_ids);
+    PB_TRY(pb_state_create(dm, 1, &t->ds));
+    const int w = c.hc * c.d;
+    t->ring_cap = t->window + 16 + PB_PREFILL_CHUNK;   // the reference keeps window + 16 rows; a whole prompt chunk arrives at once here
+    t->ring_pos.assign((size_t)t->ring_cap, (int64_t)-1);
+    PB_TRY(dalloc(s, &t->ring, (size_t)t->ring_cap * w));
+    PB_TRY(dalloc(s, &t->e_raw, (size_t)c.d)); PB_TRY(dalloc(s, &t->en, (size_t)c.d)); PB_TRY(dalloc(s, &t->e2, (size_t)c.d));
+    PB_TRY(dalloc(s, &t->hn, (size_t)w)); PB_TRY(dalloc(s, &t->h2, (size_t)w)); PB_TRY(dalloc(s, &t->lg, (size_t)n_ids));
+    PB_TRY(dalloc(s, &t->tok_dev, (size_t)4)); PB_TRY(dalloc(s, &t->best, (size_t)4));
+    PB_TRY(dalloc(s, &t->mask, (size_t)dc.max_ctx / 32 + 2)); PB_TRY(dalloc(s, &t->mask_on, (size_t)1));
+    if (cudaMallocHost(&t->pin, 64) != cudaSuccess) PB_FAIL(ctx, PB_ERR_OOM, "pinned allocation failed");
+    t->ds->ext_mask = t->mask; t->ds->ext_on = t->mask_on; t->ds->ext_ld = 0;
+    mtp_forget(t, s->pos_host);
+    // the step graphs of this state were captured without the copy of the residual rows: drop them
+    if (s->graph) { cudaGraphExecDestroy(s->graph); s->graph = nullptr; }
+    for (cudaGraphExec_t& g : s->win_graph) if (g) { cudaGraphExecDestroy(g); g = nullptr; }
+    PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return PB_OK;
+}
+
+// One drafter cell at rope position `pos`: R = the residual row it pairs (device, hc*d), tok = the token at pos + 1.
+// full = false: K/V only (catch_up, mtp.rs:172-175); full = true: the whole step (step, :184-236), leaving the final mixer's
+// output in ds->hmix, the drafter's residual in ds->x and (index, probability) of the best draft-vocabulary token in t->best.
+static int mtp_cell(pb_state* s, const float* R, uint32_t tok, int64_t pos, bool full) {
+    PbMtp* t = s->mtp; pb_model* m = s->m; pb_ctx* ctx = m->ctx; pb_model* dm = t->dm; pb_state* ds = t->ds; const pb_cfg& c = dm->cfg;
+    const int d = c.d, w = c.hc * c.d;
+    // (pageable sources: the driver stages them at the call, so the next cell may reuse the variables at once)
+    const uint32_t tk = tok; const int64_t p64 = pos;
+    PB_CUDA(ctx, cudaMemcpyAsync(t->tok_dev, &tk, 4, cudaMemcpyHostToDevice, ctx->stream));
+    PB_CUDA(ctx, cudaMemcpyAsync(ds->pos, &p64, 8, cudaMemcpyHostToDevice, ctx->stream));
+    ds->pos_host = pos;
+    pb_qmat* embd = M(m, -1, PB_R_TOKEN_EMBD);
+    PB_TRY(pb_launch_embed(ctx, embd->type, embd->data, embd->rows, d, t->tok_dev, 1, t->e_raw, d));
+    ctx->pdl_chain = false;
+    // input (mtp.rs:186-195): e = fc_embedding(rms(embed) * pre_e); h = fc_hidden per stream of rms over all hc*d values * pre_h; R' = h + e
+    PB_TRY(pb_launch_mtp_input(ctx, t->e_raw, V(dm, -1, PB_R_MTP_PRE_E), R, V(dm, -1, PB_R_MTP_PRE_H), t->en, t->hn, d, w, c.eps));
+    PbGemvArgs g;
+    pb_qmat* fe = M(dm, -1, PB_R_MTP_FC_E); pb_qmat* fh = M(dm, -1, PB_R_MTP_FC_H);
+    g.w = fe->data; g.wr = fe->rdata; g.type = fe->type; g.rows = fe->rows; g.cols = d; g.x = t->en; g.ldx = d; g.t = 1; g.y = t->e2; g.ldy = d;
+    PB_TRY(pb_launch_gemv(ctx, g));
+    g.w = fh->data; g.wr = fh->rdata; g.type = fh->type; g.rows = fh->rows; g.x = t->hn; g.t = c.hc; g.y = t->h2;
+    PB_TRY(pb_launch_gemv(ctx, g));
+    PB_TRY(pb_launch_mtp_join(ctx, t->h2, t->e2, ds->x, d, w));
+    PbHcParams h;
+    hc_params(ds, 0, PB_R_HCA_NORM, PB_R_HCA_DOWN, PB_R_HCA_UP, PB_R_HCA_INJECT, h);
+    PB_TRY(pb_launch_hc_mix(ctx, h, ds->x, 1, ds->hmix));
+    if (!full) {
+        // kv_append (:156-170): the cell's K and V
+        const int64_t nq = (int64_t)c.n_head * 2 * c.hd, row = (int64_t)c.n_kv * c.hd;
+        PbGemvQArgs a; memset(&a, 0, sizeof a);
+        a.type = M(dm, 0, PB_R_ATTN_Q)->type; a.cols = d; a.nseg = 2;
+        seg(a, 0, M(dm, 0, PB_R_ATTN_K), nq); seg(a, 1, M(dm, 0, PB_R_ATTN_V), nq + row);
+        a.x = ds->hmix; a.ldx = d; a.y = ds->proj; a.ldy = ds->ldproj; a.mode = PB_ACT_PLAIN; a.eps = c.eps;
+        PB_TRY(gemv_cols(ctx, a, 1, false));
+        PbAttnParams p; attn_params(ds, 0, p);
+        return pb_launch_kv_append(ctx, p);
+    }
+    int64_t lo = pos - t->window + 1;
+    if (lo < t->kv_c0) lo = t->kv_c0;
+    PB_TRY(pb_launch_mtp_mask(ctx, t->mask, t->mask_on, lo, pos));
+    PB_TRY(run_attn(ds, 0, ds->hmix, nullptr, ds->yout, d, 0));
+    PB_TRY(pb_launch_hc_combine(ctx, h, ds->x, ds->yout, 1));
+    hc_params(ds, 0, PB_R_HCF_NORM, PB_R_HCF_DOWN, PB_R_HCF_UP, PB_R_HCF_INJECT, h);
+    PB_TRY(pb_launch_hc_mix(ctx, h, ds->x, 1, ds->hmix));
+    PB_TRY(run_moe(ds, 0, ds->hmix, nullptr, 1, ds->yout, d, 0));
+    PB_TRY(pb_launch_hc_combine(ctx, h, ds->x, ds->yout, 1));
+    hc_params(ds, -1, PB_R_OUT_HC_NORM, PB_R_OUT_HC_DOWN, PB_R_OUT_HC_UP, -1, h);   // the final mixer
+    PB_TRY(pb_launch_hc_mix(ctx, h, ds->x, 1, ds->hmix));
+    pb_qmat* head = M(dm, -1, PB_R_OUTPUT);
+    g.w = head->data; g.wr = head->rdata; g.type = head->type; g.rows = head->rows; g.cols = d; g.x = ds->hmix; g.ldx = d; g.t = 1; g.y = t->lg; g.ldy = t->n_ids;
+    PB_TRY(pb_launch_gemv(ctx, g));
+    ctx->pdl_chain = false;
+    return pb_launch_mtp_best(ctx, t->lg, t->n_ids, t->best);
+}
+
+// Model::mtp_draft :2177 (= Target::draft): up to max_draft tokens that follow the fed tokens and `pending` (the token chosen
+// but not fed yet).  Token j > 0 is kept only while the drafter's probability of it is at least min_p (draft_gate, spec.rs:326).
+// *n = 0 when nothing can be drafted (no drafter state for the last position); PB_UNSUPPORTED without a drafter.
+int pb_draft(pb_state* s, uint32_t pending, int max_draft, float min_p, uint32_t* ids_host, float* probs_host, int* n) {
+    if (!s || !n) return PB_ERR_ARG;
+    pb_ctx* ctx = s->m->ctx;
+    PB_TRY(pb_enter(ctx));
+    *n = 0;
+    PbMtp* t = s->mtp;
+    if (!t) PB_FAIL(ctx, PB_UNSUPPORTED, "no drafter attached: use the caller's n-gram drafter");
+    if (max_draft < 0 || (max_draft > 0 && !ids_host)) PB_FAIL(ctx, PB_ERR_ARG, "pb_draft: bad argument");
+    if (pending >= (uint32_t)s->m->cfg.vocab) PB_FAIL(ctx, PB_ERR_ARG, "pb_draft: token %u outside the vocabulary", pending);
+    const int64_t np = s->pos_host;               // tokens fed so far: cells 0 .. np - 1 exist, cell i pairs R_i with token i + 1
+    if (np == 0 || max_draft == 0) return PB_OK;
+    const int w = s->m->cfg.hc * s->m->cfg.d;
+    auto have_r = [&](int64_t p) { return p >= 0 && t->ring_pos[(size_t)(p % t->ring_cap)] == p; };
+    auto r_of = [&](int64_t p) { return t->ring + (size_t)(p % t->ring_cap) * w; };
+    auto tok_at = [&](int64_t p, uint32_t& out) { if (p < t->tok_base || p >= t->tok_base + (int64_t)t->tokens.size()) return false; out = t->tokens[(size_t)(p - t->tok_base)]; return true; };
+    if (!have_r(np - 1)) return PB_OK;
+    if (np + max_draft > t->dm->cfg.max_ctx) return PB_OK;
+    if (t->kv_end > np - 1) t->kv_end = np - 1;   // kv.truncate(n - 1)
+    if (t->kv_c0 > t->kv_end) t->kv_c0 = t->kv_end;
+    // catch-up (:2191-2213): cells below np - 1 whose residual is known; a gap restarts the drafter's K/V
+    int64_t first = np - 1;
+    while (have_r(first - 1)) first--;
+    const bool cont = t->kv_end > t->kv_c0 && t->kv_end >= first;
+    int64_t lo = cont ? t->kv_end : (first > np - 1 - t->window ? first : np - 1 - t->window);
+    if (lo < 0) lo = 0;
+    bool ok = true;
+    for (int64_t i = lo; i < np - 1 && ok; i++) { uint32_t tk; ok = have_r(i) && tok_at(i + 1, tk); }
+    if (!ok) { lo = np - 1; t->kv_c0 = t->kv_end = lo; }
+    else if (!cont) { t->kv_c0 = t->kv_end = lo; }
+    for (int64_t i = lo; i < np - 1; i++) {
+        uint32_t tk = 0; tok_at(i + 1, tk);
+        PB_TRY(mtp_cell(s, r_of(i), tk, i, false));
+        t->kv_end = i + 1;
+    }
+    // the draft loop (:2214-2272)
+    const float* r = r_of(np - 1);
+    uint32_t tok = pending;
+    int made = 0;
+    for (int j = 0; j < max_draft; j++) {
+        PB_TRY(mtp_cell(s, r, tok, np - 1 + j, true));
+        PB_CUDA(ctx, cudaMemcpyAsync(t->pin + 1, t->best, 8, cudaMemcpyDeviceToHost, ctx->stream));
+        PB_TRY(pb_sync_check(ctx, "pb_draft"));
+        if (j == 0) t->kv_end = np;               // the cell of the last fed position stays (its token is `pending`)
+        const uint32_t bi = t->pin[1]; float p; memcpy(&p, t->pin + 2, 4);
+        if (j > 0 && p < min_p) break;            // draft_gate
+        const uint32_t id = t->ids[bi < (uint32_t)t->n_ids ? bi : (uint32_t)t->n_ids - 1];
+        ids_host[made] = id; if (probs_host) probs_host[made] = p;
+        made++;
+        r = t->ds->x; tok = id;                   // the drafter's own residual feeds its next step
+    }
+    *n = made;
+    return PB_OK;
+}
 
 // Model::snapshot / restore, Snap :3277-3298.  Layout: header, then per DeltaNet layer [conv ring][ssm],
 // then per attention layer and (sequence, KV head): q4n, packed K words/scales, packed V words/scales for
@@ -1338,6 +1552,7 @@ int pb_state_restore(pb_state* s, const void* buf_host, size_t nbytes) {
     PB_TRY(pb_state_set_pos(s, h.pos));
     s->verify_t = 0;
     PB_TRY(snap_io(s, (uint8_t*)const_cast<void*>(buf_host), false, q4));
+    if (s->mtp) mtp_forget(s->mtp, h.pos);   // the restored history is not the one the drafter followed
     if (s->m->qsa) for (int ai = 0; ai < s->m->n_attn; ai++) PB_TRY(qsa_pool_all(s, ai, h.pos));
     return PB_OK;
 }

@@ -322,6 +322,12 @@ struct PbQsaParams {
 int pb_launch_qsa_append(pb_ctx* ctx, const PbQsaParams& p);   // store the raw key, pool the block the token completes
 int pb_launch_qsa_select(pb_ctx* ctx, const PbQsaParams& p);   // block scores and the position mask (sparse[b] = 0 in the dense range)
 int pb_launch_qsa_pool_all(pb_ctx* ctx, const PbQsaParams& p, int64_t nblk);   // pooled keys of blocks [0, nblk) of every sequence
+// pb_mtp.cu: pieces of the MTP drafter around its layer
+int pb_launch_mtp_keep(pb_ctx* ctx, const float* x, int64_t ldx, const int64_t* pos, int t, float* ring, int cap, int w);
+int pb_launch_mtp_input(pb_ctx* ctx, const float* e, const float* pre_e, const float* R, const float* pre_h, float* en, float* hn, int d, int w, float eps);
+int pb_launch_mtp_join(pb_ctx* ctx, const float* h2, const float* e2, float* x, int d, int w);
+int pb_launch_mtp_mask(pb_ctx* ctx, uint32_t* mask, int* on, int64_t lo, int64_t pos);
+int pb_launch_mtp_best(pb_ctx* ctx, const float* lg, int n, uint32_t* out);
 int pb_launch_kv_append(pb_ctx* ctx, const PbAttnParams& p);
 int pb_launch_attn(pb_ctx* ctx, const PbAttnParams& p);
 int pb_launch_kv_pack(pb_ctx* ctx, const PbAttnParams& p);   // window mode, after pb_launch_kv_append

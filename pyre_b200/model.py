@@ -30,6 +30,10 @@ class Model:
         v = _f32(v).reshape(-1)
         self.ctx.check(lib().pb_model_set_vec(self.h, C.c_int(layer), C.c_int(ROLE[role]), _p(v), C.c_int64(v.size)))
 
+    def set_mtp(self, window: int = 128):
+        """Marks this model (one attention layer with hyper-connections + the MTP_* tensors) as an MTP drafter (before finalize)."""
+        self.ctx.check(lib().pb_model_set_mtp(self.h, C.c_int(window)))
+
     def set_indexer(self, budget: int, ratio: int, n_head: int, head_dim: int):
         """QSA block-sparse attention: attention layers that hold IDX_Q / IDX_K / IDX_Q_NORM / IDX_K_NORM attend to the
         budget / ratio best blocks of ratio tokens once a query sees more than budget + ratio - 1 tokens (before finalize)."""
@@ -95,6 +99,18 @@ class State:
         logits = np.empty((ids.size, self.model.cfg.vocab), dtype=np.float32)
         self.ctx.check(lib().pb_verify(self.h, _p(ids), C.c_int(ids.size), _p(logits)))
         return logits
+
+    def attach_drafter(self, drafter: "Model", vocab_ids):
+        """Binds an MTP drafter model to this batch-1 state; vocab_ids[i] = token of row i of the drafter's head."""
+        ids = np.ascontiguousarray(vocab_ids, dtype=np.uint32).reshape(-1)
+        self.ctx.check(lib().pb_state_attach_drafter(self.h, drafter.h, _p(ids), C.c_int(ids.size)))
+        self._drafter = drafter      # must outlive the state
+
+    def draft(self, pending: int, max_draft: int, min_p: float = 0.9):
+        """Target::draft: (token ids, their draft probabilities) that follow the fed tokens and `pending`."""
+        ids = np.zeros(max(max_draft, 1), np.uint32); probs = np.zeros(max(max_draft, 1), np.float32); n = C.c_int(0)
+        self.ctx.check(lib().pb_draft(self.h, C.c_uint32(pending), C.c_int(max_draft), C.c_float(min_p), _p(ids), _p(probs), C.byref(n)))
+        return ids[:n.value].copy(), probs[:n.value].copy()
 
     def spec_keep(self, t: int, keep: int):
         self.ctx.check(lib().pb_keep(self.h, C.c_int(t), C.c_int(keep)))
