@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(DN_THREADS) pb_deltanet_kernel(const PbDeltaPa
 // p.pos[0] is the position of token 0.  The conv history of in-window tokens comes from the earlier rows of proj, that
 // of the tokens before the window from the ring; the arithmetic per token is that of pb_deltanet_unit.
 template <int RPW>
-__global__ void __launch_bounds__(DN_THREADS) pb_deltanet_seq_kernel(const PbDeltaParams p, int T) {
+__global__ void __launch_bounds__(DN_THREADS) pb_deltanet_seq_kernel(const PbDeltaParams p, int T, const PbDeltaCk ck) {
     constexpr int K = 4;                                    // conv taps (checked by the launcher)
     const int nk = p.nk, nv = p.nv, dk = p.dk, dv = p.dv;
     const int splits = dv / DN_COLS;
@@ -161,6 +161,18 @@ __global__ void __launch_bounds__(DN_THREADS) pb_deltanet_seq_kernel(const PbDel
             p.out[(size_t)j * p.ldo + h * dv + j0 + lane] = o;
         }
         __syncthreads();   // red and the q / k / v vectors are rewritten by the next token
+        // rollback checkpoint after token j (k_delta_m writes them from registers too, src/model/qn_cube.rs:2839-2913): the
+        // state slice, and the K - 1 inputs the next token's conv reads, at their ring slots
+        if (j < 8 && j + 1 < T && ck.ssm[j]) {
+            float* C = ck.ssm[j] + ((size_t)h * dk) * dv + j0 + lane;
+#pragma unroll
+            for (int r = 0; r < RPW; r++) C[(size_t)(warp * RPW + r) * dv] = s[r];
+#pragma unroll
+            for (int e = 0; e < 2; e++)
+                if (own[e])
+#pragma unroll
+                    for (int k = 0; k < K - 1; k++) ck.conv[j][(size_t)((pos0 + j - (K - 2) + k + K) % K) * ch + cidx[e]] = hist[e][k];
+        }
         cur[0] = ncur[0]; cur[1] = ncur[1]; alpha = nalpha; beta = nbeta;
     }
 #pragma unroll
@@ -169,13 +181,15 @@ __global__ void __launch_bounds__(DN_THREADS) pb_deltanet_seq_kernel(const PbDel
 
 // T consecutive tokens of sequence 0 in one launch; false when the shape is outside what the kernel is built for
 bool pb_deltanet_seq_supported(const PbDeltaParams& p) { return p.conv_k == 4 && p.dv % DN_COLS == 0 && (p.dk == 128 || p.dk == 64 || p.dk == 32) && 2 * p.dk + DN_COLS <= 2 * DN_THREADS; }
-int pb_launch_deltanet_seq(pb_ctx* ctx, const PbDeltaParams& p, int T) {
+int pb_launch_deltanet_seq(pb_ctx* ctx, const PbDeltaParams& p, int T, const PbDeltaCk* ckp) {
     if (!pb_deltanet_seq_supported(p)) PB_FAIL(ctx, PB_UNSUPPORTED, "deltanet run: dk=%d dv=%d conv_k=%d not supported", p.dk, p.dv, p.conv_k);
+    PbDeltaCk ck; memset(&ck, 0, sizeof ck);
+    if (ckp) ck = *ckp;
     const dim3 grid(p.nv * (p.dv / DN_COLS));
     const size_t smem = (size_t)(2 * p.dk + DN_COLS + 8 * DN_COLS) * 4;
-    if (p.dk == 128) pb_launch_k(ctx, pb_deltanet_seq_kernel<16>, grid, dim3(DN_THREADS), smem, p, T);
-    else if (p.dk == 64) pb_launch_k(ctx, pb_deltanet_seq_kernel<8>, grid, dim3(DN_THREADS), smem, p, T);
-    else pb_launch_k(ctx, pb_deltanet_seq_kernel<4>, grid, dim3(DN_THREADS), smem, p, T);
+    if (p.dk == 128) pb_launch_k(ctx, pb_deltanet_seq_kernel<16>, grid, dim3(DN_THREADS), smem, p, T, ck);
+    else if (p.dk == 64) pb_launch_k(ctx, pb_deltanet_seq_kernel<8>, grid, dim3(DN_THREADS), smem, p, T, ck);
+    else pb_launch_k(ctx, pb_deltanet_seq_kernel<4>, grid, dim3(DN_THREADS), smem, p, T, ck);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
     return PB_OK;

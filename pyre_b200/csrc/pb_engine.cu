@@ -628,10 +628,13 @@ static int run_lin(pb_state* s, int il, const float* x_in, const float* norm_w, 
     d.proj = s->proj; d.ldp = s->ldproj; d.conv_w = V(m, il, PB_R_LIN_CONV); d.a = V(m, il, PB_R_LIN_A); d.dt = V(m, il, PB_R_LIN_DT);
     d.conv = s->conv[li]; d.ssm = s->ssm[li]; d.pos = s->pos; d.out = s->olin; d.ldo = w;
     d.nk = c.lin_nk; d.nv = c.lin_nv; d.dk = c.lin_dk; d.dv = c.lin_dv; d.conv_k = c.conv_k; d.batch = B;
-    if (s->win_t > 0 && !s->win_ckpt && pb_deltanet_seq_supported(d)) {
-        // no rollback wanted: all tokens in one launch, the state slice stays in registers
+    if (s->win_t > 0 && pb_deltanet_seq_supported(d) && (!s->win_ckpt || s->win_t <= 8)) {
+        // all tokens in one launch, the state slice stays in registers; a verify window also gets its rollback checkpoints
+        // (the state after each token but the last) written from there
         d.pos = s->wpos; d.batch = 1;
-        PB_TRY(pb_launch_deltanet_seq(ctx, d, s->win_t));
+        PbDeltaCk ck; memset(&ck, 0, sizeof ck);
+        if (s->win_ckpt) for (int j = 0; j + 1 < s->win_t; j++) { ck.conv[j] = s->ck_conv[(size_t)li * PB_MAX_WINDOW + j]; ck.ssm[j] = s->ck_ssm[(size_t)li * PB_MAX_WINDOW + j]; }
+        PB_TRY(pb_launch_deltanet_seq(ctx, d, s->win_t, s->win_ckpt ? &ck : nullptr));
     } else if (s->win_t > 0) {
         // the recurrence is sequential: one launch per token, with a rollback checkpoint after each but the last
         for (int j = 0; j < s->win_t; j++) {
@@ -695,12 +698,17 @@ static int run_attn(pb_state* s, int il, const float* x_in, const float* norm_w,
         p.qsa_mask = s->qsa_mask; p.qsa_ld = s->mask_ld; p.qsa_on = s->qsa_on;
     }
     if (s->ext_mask) { p.qsa_mask = s->ext_mask; p.qsa_ld = s->ext_ld; p.qsa_on = s->ext_on; }
-    if (s->win_t > 0 && !s->win_ckpt && !m->qsa) {
-        // a prefill chunk: all tokens are appended, the packed boundary moves once, then every token attends to the
-        // positions <= its own in one launch (token j treats as packed what it would have found packed token by token)
+    if (s->win_t > 0 && !m->qsa) {
+        // a prefill chunk or a verify window: all tokens are appended, the packed boundary moves once, then every token attends
+        // to the positions <= its own in one launch (token j treats as packed what it would have found packed token by
+        // token).  A verify window that is cut short afterwards gets its boundary back in pb_keep.
         p.window = 1; p.pos = s->wpos; p.batch = s->win_t;
         const bool mma = s->nsplit_packed > 0;
-        p.nsplit = mma ? PB_WIN_SPLITS : 1; p.nsplit_packed = mma ? PB_WIN_SPLITS - 1 : 0;
+        // splits per token: four for a chunk of hundreds of tokens, more for a window of a few, so that the grid fills the GPU
+        int ws = ctx->sm_count / (c.n_kv * s->win_t);
+        ws = ws < PB_WIN_SPLITS ? PB_WIN_SPLITS : (ws > 64 ? 64 : ws);
+        if ((size_t)ws * s->win_t > (size_t)PB_PREFILL_CHUNK * PB_WIN_SPLITS) ws = PB_WIN_SPLITS;
+        p.nsplit = mma ? ws : 1; p.nsplit_packed = mma ? ws - 1 : 0;
         PB_TRY(pb_launch_kv_append(ctx, p));
         PB_TRY(pb_launch_kv_pack(ctx, p));
         PB_TRY(pb_launch_attn(ctx, p));
@@ -1284,6 +1292,14 @@ int pb_keep(pb_state* s, int t, int keep) {
             PB_CUDA(ctx, cudaMemcpyAsync(s->ssm[li], s->ck_ssm[(size_t)li * PB_MAX_WINDOW + keep - 1], ssm_elems(c, 1) * 4, cudaMemcpyDeviceToDevice, ctx->stream));
         }
         PB_TRY(pb_state_set_pos(s, s->verify_pos0 + keep));
+        // the window moved the packed boundary to where its last token put it; the kept prefix may not have reached that far.
+        // Back to the rule for the kept length (kv_push :1520): the f32 rows of the positions in between are still in the
+        // ring (it holds kv_recent + 64 + a prompt chunk), and they are packed again, to the same bits, when their turn comes.
+        if (c.kv_bits == 4 && !s->m->qsa) {
+            const int64_t nk = s->verify_pos0 + keep, rule = nk > c.kv_recent ? ((nk - c.kv_recent) / 64) * 64 : 0;
+            for (int ai = 0; ai < s->m->n_attn; ai++) PB_CUDA(ctx, cudaMemcpyAsync(s->kv[ai].q4n, &rule, 8, cudaMemcpyHostToDevice, ctx->stream));
+            PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        }
     }
     s->verify_t = 0;
     return PB_OK;

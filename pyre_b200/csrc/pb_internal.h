@@ -282,7 +282,9 @@ struct PbDeltaParams {
 };
 int pb_launch_deltanet(pb_ctx* ctx, const PbDeltaParams& p);
 bool pb_deltanet_seq_supported(const PbDeltaParams& p);
-int pb_launch_deltanet_seq(pb_ctx* ctx, const PbDeltaParams& p, int T);   // T consecutive tokens of sequence 0, state kept in registers
+// rollback checkpoints of a window: the state as it is after token j (conv ring and ssm of one sequence), or null
+struct PbDeltaCk { float* conv[8]; float* ssm[8]; };
+int pb_launch_deltanet_seq(pb_ctx* ctx, const PbDeltaParams& p, int T, const PbDeltaCk* ck = nullptr);   // T consecutive tokens of sequence 0, state kept in registers
 
 // ---------------------------------------------------------------- pb_attn.cu
 struct PbAttnParams {
