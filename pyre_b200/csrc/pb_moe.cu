@@ -709,6 +709,12 @@ static int launch_expert(pb_ctx* ctx, PbExpertParams p, int cols, const PbCombin
         p.nx = 1;
         p.stage_bytes = (uint32_t)((((size_t)rpc * p.row_bytes * (DOWN ? 1 : 2)) + (size_t)pb_xq_words(cols) * 4 + 16 + 127) & ~(size_t)127);
     }
+    // wide rows (Q8_0 at 2048 columns: 2176 bytes): fewer rows per chunk than consumer warps, the other warps sit the chunk out
+    while (256 + p.tab_bytes + xbytes + (size_t)PB_STAGES * p.stage_bytes > (size_t)ctx->max_smem_optin && rpc > 32 / lpr && ((rpc / 2) * p.row_bytes) % 16 == 0) {
+        rpc /= 2;
+        p.rows_per_chunk = rpc;
+        p.stage_bytes = (uint32_t)((((size_t)rpc * p.row_bytes * (DOWN ? 1 : 2)) + (size_t)pb_xq_words(cols) * 4 + 16 + 127) & ~(size_t)127);
+    }
     const size_t smem = 256 + p.tab_bytes + xbytes + (size_t)PB_STAGES * p.stage_bytes;
     if (smem > (size_t)ctx->max_smem_optin) PB_FAIL(ctx, PB_UNSUPPORTED, "expert kernel needs %zu bytes of shared memory", smem);
     p.status = ctx->dev_status;

@@ -182,6 +182,25 @@ def test_moe_config3_128_tokens(ctx):
     st.destroy(); m.destroy()
 
 
+@pytest.mark.parametrize("name,t", [("Q8_0", 1), ("Q8_0", 8), ("Q4_K", 8), ("IQ2_XS", 8)])
+def test_moe_full_width_other_formats(ctx, name, t):
+    """The MoE block at full width (2048 x 512 experts of 512) in the other streaming formats; Q8_0 rows of 2048 columns are
+    2176 bytes, where a chunk of the gate / up kernel holds fewer rows than it has consumer warps."""
+    cfg = pb.make_cfg(n_layers=1, full_every=0, vocab=1024, max_ctx=64)
+    spec = synth.model_spec(cfg, 3, qtype=getattr(pb, name))
+    m = synth.build_model(ctx, cfg, spec, 3)
+    _, mats = oracle_model(cfg, spec, 3)
+    st = m.new_state(t)
+    x = np.random.default_rng(t).standard_normal((t, cfg.d)).astype(np.float32)
+    y, sel = st.moe_forward(0, x)
+    yo, selo, _ = oracle.moe(oracle_cfg(cfg), mats[(0, "ROUTER")], mats[(0, "EXP_GATE")], mats[(0, "EXP_UP")], mats[(0, "EXP_DOWN")],
+                             mats[(0, "SH_GATE")], mats[(0, "SH_UP")], mats[(0, "SH_DOWN")], mats[(0, "SH_GATE_INP")], x)
+    assert rel_err(y, yo) < TOL
+    assert np.array_equal(np.sort(sel, axis=1), np.sort(selo, axis=1))
+    assert ctx.device_status() == 0
+    st.destroy(); m.destroy()
+
+
 def test_full_model_greedy_identity_64_steps(ctx):
     """The whole 48-layer, 512-expert, 151936-token model: prompt, then 64 greedy tokens, against the oracle's
     recorded run.  A mismatch reports the oracle's margins at that step: a top-2 logit margin or a 10th/11th

@@ -108,6 +108,31 @@ def test_loaded_model_decodes_like_the_directly_built_one(ctx, tmp_path, hc):
     a.destroy(); b.destroy(); m.destroy(); ref.destroy()
 
 
+def test_drafter_file_reader_and_q8_0_quantizer(tmp_path):
+    """The MTP drafter's tensor file (safetensors of BF16, src/model/mtp.rs:27-44): names lose their `mtp.` / `layers.0.`
+    prefixes, values come back as the BF16 they were stored as; the Q8_0 quantizer gives the bytes gguf-py gives, and
+    the oracle decodes them to within half a step."""
+    gguf = pytest.importorskip("gguf")
+    from pyre_b200 import mtp_loader as ml
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((6, 64)).astype(np.float32); b = rng.standard_normal(64).astype(np.float32)
+    ml.write_safetensors(tmp_path / "d.safetensors", {"mtp.layers.0.self_attn.q_proj.weight": a, "mtp.pre_fc_norm_embedding.weight": b})
+    t = ml.read_safetensors(tmp_path / "d.safetensors")
+    assert set(t) == {"self_attn.q_proj.weight", "pre_fc_norm_embedding.weight"}
+    bf = lambda x: ((x.view(np.uint32) >> 16) << 16).view(np.float32)
+    assert np.array_equal(t["self_attn.q_proj.weight"], bf(a)) and np.array_equal(t["pre_fc_norm_embedding.weight"], bf(b))
+    x = (rng.standard_normal((5, 256)) * np.exp(rng.standard_normal((5, 1)))).astype(np.float32)
+    x[2, 32:64] = 0.0
+    raw = ml.quantize_q8_0(x)
+    want = gguf.quants.quantize(x, gguf.GGMLQuantizationType.Q8_0)
+    assert np.array_equal(raw, np.ascontiguousarray(want).view(np.uint8).reshape(-1))
+    back = oracle.dequant(oracle.Q8_0, raw, x.size).reshape(x.shape)
+    step = np.abs(x.reshape(5, 8, 32)).max(axis=2, keepdims=True) / 127.0
+    assert np.all(np.abs(back.reshape(5, 8, 32) - x.reshape(5, 8, 32)) <= 0.6 * step + 1e-7)       # half a step, plus what the f16 rounding of the scale moves the largest value
+    with pytest.raises(ml.MtpFileError):
+        ml.drafter_spec(t, type("C", (), dict(d=64, hc=2))())          # tensors missing
+
+
 @pytest.mark.gpu
 def test_loaded_model_with_indexer_and_trained_context(ctx, tmp_path):
     """A file that carries the sparse-attention indexer (attention.indexer.* keys, blk.N.indexer.* tensors) and a trained

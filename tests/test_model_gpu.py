@@ -353,3 +353,23 @@ def test_yarn_scaled_context_greedy_identity_vs_oracle(ctx, kv_bits):
         m.set_ctx_train(128)          # after finalize
     assert ctx.device_status() == 0
     st.destroy(); st0.destroy(); m.destroy(); m0.destroy()
+
+
+@pytest.mark.parametrize("name", ["Q8_0", "Q4_K", "IQ2_XS"])
+def test_other_quant_formats_greedy_identity_vs_oracle(ctx, name):
+    """The token loop with every matrix in one of the other streaming formats (the per-operation kernels; the fused step
+    kernel is for re-coded IQ3_S): prompt logits within 1e-3 and 32 greedy ids identical to the oracle.  Q8_0 rows are the
+    widest (34 bytes per 32 weights): the expert kernels then take fewer rows per chunk than they have consumer warps."""
+    qt = getattr(pb, name)
+    cfg = small_cfg(pb, n_layers=4, kv_bits=4, kv_recent=64, max_ctx=128)
+    spec = synth.model_spec(cfg, 7, qtype=qt)
+    m = synth.build_model(ctx, cfg, spec, 7)
+    om, _ = oracle_model(cfg, spec, 7)
+    st, ost = m.new_state(1), om.new_state()
+    prompt = [5, 900, 31, 77]
+    lg, lo = st.forward(np.array(prompt, np.uint32))[0], ost.forward(prompt)
+    assert rel_err(lg, lo) < 1e-3
+    a, b, margins = _greedy_pair(st, ost, int(lg.argmax()), 32)
+    assert a == b, (name, margins)
+    assert ctx.device_status() == 0
+    st.destroy(); m.destroy()

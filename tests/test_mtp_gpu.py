@@ -170,3 +170,63 @@ def test_speculative_decoding_with_the_drafter_equals_plain_greedy(ctx):
     assert out[:48] == want[:48], (passes, accepted)
     assert ctx.device_status() == 0
     plain.destroy(); st.destroy(); m.destroy(); dm.destroy()
+
+
+def test_drafter_loaded_from_its_tensor_file_matches_the_oracle(ctx, tmp_path):
+    """Mtp::load's host side (pyre_b200/mtp_loader.py): a synthetic drafter file in the reference's format (BF16
+    safetensors, `mtp.` names, fused gate_up_proj, norms stored without their 1) is read, quantized to Q8_0 and bound
+    under the library's roles, the head gathered from the main model's output matrix; the loaded drafter drafts what an
+    oracle drafter built from the same bytes drafts."""
+    from pyre_b200 import mtp_loader as ml
+    cfg = small_cfg(pb, n_layers=8, kv_bits=4, kv_recent=64, max_ctx=256, hc=2, hc_lr=32)
+    spec = synth.model_spec(cfg, 61)
+    m = synth.build_model(ctx, cfg, spec, 61)
+    om, mats = oracle_model(cfg, spec, 61)
+    d, hc, lr, ne, ff, nh, nkv, hd = cfg.d, cfg.hc, 16, 8, 256, cfg.n_head, cfg.n_kv, cfg.hd
+    rng = np.random.default_rng(62)
+    g = lambda *sh: (0.05 * rng.standard_normal(sh)).astype(np.float32)
+    tensors = {"mtp.pre_fc_norm_embedding.weight": g(d), "mtp.pre_fc_norm_hidden.weight": g(hc * d),
+               "mtp.fc_embedding.weight": g(d, d), "mtp.fc_hidden.weight": g(d, d),
+               "mtp.layers.0.self_attn.q_proj.weight": g(nh * 2 * hd, d), "mtp.layers.0.self_attn.k_proj.weight": g(nkv * hd, d),
+               "mtp.layers.0.self_attn.v_proj.weight": g(nkv * hd, d), "mtp.layers.0.self_attn.o_proj.weight": g(d, nh * hd),
+               "mtp.layers.0.self_attn.q_norm.weight": g(hd), "mtp.layers.0.self_attn.k_norm.weight": g(hd),
+               "mtp.layers.0.mlp.gate.weight": g(ne, d), "mtp.layers.0.mlp.experts.gate_up_proj": g(ne, 2 * ff, d), "mtp.layers.0.mlp.experts.down_proj": g(ne, d, ff),
+               "mtp.layers.0.mlp.shared_expert.gate_proj.weight": g(ff, d), "mtp.layers.0.mlp.shared_expert.up_proj.weight": g(ff, d),
+               "mtp.layers.0.mlp.shared_expert.down_proj.weight": g(d, ff), "mtp.layers.0.mlp.shared_expert_gate.weight": g(1, d)}
+    for pre, inj in (("mtp.layers.0.attn_hyper_connection", True), ("mtp.layers.0.mlp_hyper_connection", True), ("mtp.hyper_connection_mixer", False)):
+        tensors[f"{pre}.hc_norm.weight"] = g(hc * d); tensors[f"{pre}.input_mix_weight_down.weight"] = g(lr, hc * d); tensors[f"{pre}.input_mix_weight_up.weight"] = g(hc * d, lr)
+        if inj:
+            tensors[f"{pre}.block_inject_weight.weight"] = g(hc, hc * d)
+    path = tmp_path / "mtp.safetensors"
+    ml.write_safetensors(path, tensors)
+    ids = (np.arange(N_IDS, dtype=np.uint32) * 3 + 5) % cfg.vocab
+    head = pb.QMat.synth(ctx, pb.IQ3_S, cfg.vocab, d, 61, synth.tensor_id(-1, "OUTPUT"))        # the main model's output matrix again
+    dm = ml.load_drafter(ctx, path, cfg, head, ids, window=WINDOW)
+    assert dm.cfg.n_exp == ne and dm.cfg.ff_exp == ff and dm.cfg.hc_lr == lr and dm.cfg.vocab == N_IDS
+    # the oracle's drafter from the same bytes
+    cfgkw, items = ml.drafter_spec(ml.read_safetensors(path), cfg)
+    from helpers import oracle_cfg
+    ocfg = oracle_cfg(pb.make_cfg(vocab=N_IDS, **cfgkw))
+    odm = oracle.Model(ocfg); dmats = {}
+    for it in items:
+        if it[0] == "mat":
+            _, layer, role, ty, rows, cols, raw = it
+            q = oracle.QMat(ty, rows, cols, raw); odm.set_mat(layer, role, q); dmats[(layer, role)] = q
+        else:
+            odm.set_vec(it[1], it[2], it[3])
+    hq = oracle.QMat(oracle.IQ3_S, N_IDS, d, np.concatenate([head.raw_rows(int(i), 1) for i in ids]))
+    odm.set_mat(-1, "OUTPUT", hq); dmats[(-1, "OUTPUT")] = hq
+    st, ost = m.new_state(1), om.new_state()
+    st.attach_drafter(dm, ids)
+    od = OracleDrafter(om, mats, odm, dmats, ids, WINDOW)
+    prompt = list(range(100, 112))
+    st.forward(np.array(prompt, np.uint32)); lo = ost.forward(prompt); od.fed(ost, prompt)
+    pending = int(np.argmax(lo))
+    for rnd in range(4):
+        g_ids, g_p = st.draft(pending, 3, 0.0)
+        o_ids, o_p = od.draft(pending, 3, 0.0)
+        assert g_ids.tolist() == o_ids and np.allclose(g_p, o_p, rtol=2e-3, atol=1e-6), (rnd, g_ids, o_ids, g_p, o_p)
+        st.forward(np.array([pending], np.uint32)); lo = ost.forward([pending]); od.fed(ost, [pending])
+        pending = int(np.argmax(lo))
+    assert ctx.device_status() == 0
+    head.free(); st.destroy(); m.destroy(); dm.destroy()
