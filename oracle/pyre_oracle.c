@@ -265,6 +265,10 @@ static void synth_block(int type, uint64_t tkey, uint64_t b, uint8_t* out) {
     case ORC_Q4_K: { uint16_t m = synth_scale(k, 3); out[2] = (uint8_t)m; out[3] = (uint8_t)(m >> 8); synth_payload(k, 6, out + 4, 140); } break;
     case ORC_IQ2_XS: synth_payload(k, 3, out + 2, 72); break;
     case ORC_IQ3_S: synth_payload(k, 3, out + 2, 108); break;
+    case ORC_IQ3_XXS: synth_payload(k, 3, out + 2, 96); break;
+    case ORC_IQ2_S: synth_payload(k, 3, out + 2, 80); break;
+    case ORC_IQ4_NL: synth_payload(k, 3, out + 2, 16); break;
+    case ORC_IQ4_XS: synth_payload(k, 3, out + 2, 134); break;
     }
 }
 void orc_synth_rows(int type, uint64_t seed, uint64_t tid, int64_t cols, int64_t r0, int64_t nrows, uint8_t* out) {

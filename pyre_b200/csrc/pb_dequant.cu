@@ -76,7 +76,7 @@ __device__ static inline uint16_t pb_synth_scale(uint64_t bkey, int j0) {
 
 template <int FMT>
 __global__ void __launch_bounds__(256) pb_synth_kernel(uint8_t* __restrict__ w, int64_t nblocks, uint64_t tkey, int64_t block0) {
-    constexpr int BS = FMT == PB_T_Q8_0 ? 34 : PbFmt<FMT>::STEP_BYTES;
+    constexpr int BS = FMT == PB_T_Q8_0 ? 34 : (FMT == PB_T_IQ4_NL ? 18 : PbFmt<FMT>::STEP_BYTES);
     const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= nblocks) return;
     const uint64_t k = pb_sm64(tkey ^ ((uint64_t)(block0 + b) * 0xD1342543DE82EF95ull));
@@ -115,6 +115,10 @@ int pb_launch_synth(pb_ctx* ctx, int type, uint8_t* w, int64_t nblocks, uint64_t
         case PB_T_Q4_K: pb_synth_kernel<PB_T_Q4_K><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
         case PB_T_IQ2_XS: pb_synth_kernel<PB_T_IQ2_XS><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
         case PB_T_IQ3_S: pb_synth_kernel<PB_T_IQ3_S><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
+        case PB_T_IQ3_XXS: pb_synth_kernel<PB_T_IQ3_XXS><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
+        case PB_T_IQ2_S: pb_synth_kernel<PB_T_IQ2_S><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
+        case PB_T_IQ4_NL: pb_synth_kernel<PB_T_IQ4_NL><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
+        case PB_T_IQ4_XS: pb_synth_kernel<PB_T_IQ4_XS><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
         default: PB_FAIL(ctx, PB_ERR_ARG, "pb_qmat_synth: no generator for ggml type %d", type);
     }
     ctx->kernels_launched++;

@@ -215,7 +215,7 @@ static int launch_q(pb_ctx* ctx, const PbGemvQArgs& a, int row_bytes) {
     const size_t wbytes = (size_t)total_rows * row_bytes;
     // replicate the codebook per bank only when the matrix is large enough to amortise the fill
     constexpr int entry = pb_tab_entry_bytes<FMT>();
-    p.rep = entry && wbytes >= ((size_t)8 << 20) ? 128 / entry : 1;
+    p.rep = entry && wbytes >= ((size_t)8 << 20) ? pb_tab_rep_max<FMT>() : 1;
     p.tab_bytes = pb_tab_bytes<FMT>(p.rep);
     const size_t xbytes = ((size_t)NB * pb_xq_words(a.cols) * 4 + 127) & ~(size_t)127;
     const size_t fixed = 256 + p.tab_bytes + xbytes;
@@ -268,7 +268,8 @@ static int launch_q_fmt(pb_ctx* ctx, const PbGemvQArgs& a, int row_bytes) {
 }
 
 bool pb_gemvq_supported(int type, int cols) {
-    const bool quant = type == PB_T_IQ3_S || type == PB_T_IQ3S_N4 || type == PB_T_IQ2_XS || type == PB_T_Q4_K || type == PB_T_Q8_0;
+    const bool quant = type == PB_T_IQ3_S || type == PB_T_IQ3S_N4 || type == PB_T_IQ2_XS || type == PB_T_Q4_K || type == PB_T_Q8_0 ||
+                       type == PB_T_IQ3_XXS || type == PB_T_IQ2_S || type == PB_T_IQ4_NL || type == PB_T_IQ4_XS;
     const int bpr = cols / 256;
     return quant && cols % 256 == 0 && bpr > 0 && (bpr & (bpr - 1)) == 0 && cols <= 4096;
 }
@@ -326,6 +327,10 @@ static int launch_gemvq_dp4a(pb_ctx* ctx, const PbGemvQArgs& a, int el, int bs) 
             case PB_T_IQ3S_N4: rc = launch_q_fmt<PB_T_IQ3S_N4>(ctx, s, row_bytes); break;
             case PB_T_IQ2_XS: rc = launch_q_fmt<PB_T_IQ2_XS>(ctx, s, row_bytes); break;
             case PB_T_Q4_K: rc = launch_q_fmt<PB_T_Q4_K>(ctx, s, row_bytes); break;
+            case PB_T_IQ3_XXS: rc = launch_q_fmt<PB_T_IQ3_XXS>(ctx, s, row_bytes); break;
+            case PB_T_IQ2_S: rc = launch_q_fmt<PB_T_IQ2_S>(ctx, s, row_bytes); break;
+            case PB_T_IQ4_NL: rc = launch_q_fmt<PB_T_IQ4_NL>(ctx, s, row_bytes); break;
+            case PB_T_IQ4_XS: rc = launch_q_fmt<PB_T_IQ4_XS>(ctx, s, row_bytes); break;
             default: rc = launch_q_fmt<PB_T_Q8_0>(ctx, s, row_bytes); break;
         }
     }

@@ -693,7 +693,7 @@ static int launch_expert(pb_ctx* ctx, PbExpertParams p, int cols, const PbCombin
     // a few MB per launch at one or two tokens: the plain codebook; many tokens select most experts
     // (hundreds of MB), where the per-bank replicated form of pb_gemvq.cu pays for its fill
     constexpr int entry = pb_tab_entry_bytes<FMT>();
-    p.rep = entry && p.t >= 4 ? 128 / entry : 1;
+    p.rep = entry && p.t >= 4 ? pb_tab_rep_max<FMT>() : 1;
     p.tab_bytes = pb_tab_bytes<FMT>(p.rep);
     const int lpr = 4 * p.bpr < 32 ? 4 * p.bpr : 32;
     int rpc = PB_CONSUMERS * (32 / lpr);
@@ -761,6 +761,10 @@ static int launch_expert_type(pb_ctx* ctx, const PbExpertParams& p, int type, in
         case PB_T_IQ3S_N4: GO(PB_T_IQ3S_N4);
         case PB_T_IQ2_XS: GO(PB_T_IQ2_XS);
         case PB_T_Q4_K: GO(PB_T_Q4_K);
+        case PB_T_IQ3_XXS: GO(PB_T_IQ3_XXS);
+        case PB_T_IQ2_S: GO(PB_T_IQ2_S);
+        case PB_T_IQ4_NL: GO(PB_T_IQ4_NL);
+        case PB_T_IQ4_XS: GO(PB_T_IQ4_XS);
         default: GO(PB_T_Q8_0);
     }
 #undef GO

@@ -193,6 +193,119 @@ template <> struct PbQDec<PB_T_IQ3S_N4> {
     }
 };
 
+// ---- IQ3_XXS: per 32 weights eight 8-bit grid indices (entries of four magnitudes) and one u32 with four 7-bit sign
+// patterns and a 4-bit scale (gguf_q.rs:136-140).  Grid entries from shared memory (256 x 4 bytes), signs through the
+// 256-entry mask table after the parity bit is restored, as IQ2_XS.
+template <> struct PbQDec<PB_T_IQ3_XXS> {
+    static constexpr int STEP_BYTES = 98;
+    static constexpr bool HAS_MIN = false, SCALE16 = false, AFFINE = false;
+    __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs& T, PbQuarter& o) {
+        const float d = pb_h2f((uint16_t)pb_lds16(p));
+        uint32_t qs[4], aux[2];
+        pb_ld_u32x<4>(p + 2 + 16 * qt, qs);
+        pb_ld_u32x<2>(p + 66 + 8 * qt, aux);
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+            const float db = d * (0.5f + (float)(aux[b] >> 28)) * 0.5f;
+            o.sc[2 * b] = o.sc[2 * b + 1] = db;
+#pragma unroll
+            for (int l = 0; l < 4; l++) {
+                const uint32_t two = (qs[2 * b + (l >> 1)] >> (16 * (l & 1))) & 0xFFFF;
+                const uint32_t g1 = pb_lds32(T.grid + (two & 0xFF) * T.stride), g2 = pb_lds32(T.grid + (two >> 8) * T.stride);
+                const uint32_t s7 = (aux[b] >> (7 * l)) & 127;
+                const uint32_t s8 = s7 | ((__popc(s7) & 1) << 7);
+                const uint4 m = pb_lds128(T.sign256 + s8 * 16);
+                o.w[8 * b + 2 * l] = pb_apply_sign(g1, m.x, m.y);
+                o.w[8 * b + 2 * l + 1] = pb_apply_sign(g2, m.z, m.w);
+            }
+        }
+    }
+};
+
+// ---- IQ2_S: per 8 weights a 10-bit grid index (8 bits in qs, 2 in qh) and an explicit sign byte; a 4-bit scale per 16
+// weights (gguf_q.rs:130-135).  Grid entries from shared memory (1024 x 8 bytes).
+template <> struct PbQDec<PB_T_IQ2_S> {
+    static constexpr int STEP_BYTES = 82;
+    static constexpr bool HAS_MIN = false, SCALE16 = true, AFFINE = false;
+    __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs& T, PbQuarter& o) {
+        const float d = pb_h2f((uint16_t)pb_lds16(p));
+        uint32_t qs[2], sg[2];
+        pb_ld_u32x<2>(p + 2 + 8 * qt, qs);
+        pb_ld_u32x<2>(p + 34 + 8 * qt, sg);
+        const uint32_t qh = pb_lds16(p + 66 + 2 * qt), sc = pb_lds16(p + 74 + 2 * qt);
+#pragma unroll
+        for (int h = 0; h < 4; h++) o.sc[h] = d * (0.5f + (float)((sc >> (4 * h)) & 0xF)) * 0.25f;
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+            const uint32_t hb = (qh >> (8 * b)) & 0xFF;
+#pragma unroll
+            for (int l = 0; l < 4; l++) {
+                const uint32_t idx = ((qs[b] >> (8 * l)) & 0xFF) | ((hb << (8 - 2 * l)) & 0x300);
+                const uint2 g = pb_lds64(T.grid + idx * T.stride);
+                const uint4 m = pb_lds128(T.sign256 + ((sg[b] >> (8 * l)) & 0xFF) * 16);
+                o.w[8 * b + 2 * l] = pb_apply_sign(g.x, m.x, m.y);
+                o.w[8 * b + 2 * l + 1] = pb_apply_sign(g.y, m.z, m.w);
+            }
+        }
+    }
+};
+
+// ---- IQ4_NL / IQ4_XS: 4-bit codes into a table of 16 signed values (kvalues_iq4nl).  Sixteen bytes hold 32 weights:
+// weight j < 16 is the low nibble of byte j, weight 16 + j the high one.  The table lives in four registers; prmt looks four
+// codes up at once: its selector takes one nibble per output byte, and a 16-bit piece of the data IS four nibbles (low and
+// high nibble of two bytes), so  prmt(table 0..7, piece & 0x7777)  and  prmt(table 8..15, piece & 0x7777)  give the
+// values for both halves of the table, bit 3 of every nibble picks between them, and two more prmt put the low-nibble
+// and the high-nibble weights of four bytes into their words.
+__device__ __forceinline__ uint32_t pb_iq4_lut4(uint32_t piece) {
+    constexpr uint32_t K0 = 0xBFAD9881u, K1 = 0xF6EADDCFu, K2 = 0x26190D01u, K3 = 0x71594535u;   // -127 -104 -83 -65 | -49 -35 -22 -10 | 1 13 25 38 | 53 69 89 113
+    const uint32_t sel = piece & 0x7777u;
+    const uint32_t v0 = pb_prmt(K0, K1, sel), v1 = pb_prmt(K2, K3, sel);
+    const uint32_t mask = pb_prmt(0x0000FF00u, 0u, (piece >> 3) & 0x1111u);
+    return (v0 & ~mask) | (v1 & mask);
+}
+// 16 bytes of codes (four words) -> weights 0..15 in lo[0..3], weights 16..31 in hi[0..3]
+__device__ __forceinline__ void pb_iq4_block(const uint32_t (&q)[4], int* lo, int* hi) {
+#pragma unroll
+    for (int m = 0; m < 4; m++) {
+        const uint32_t ra = pb_iq4_lut4(q[m] & 0xFFFFu), rb = pb_iq4_lut4(q[m] >> 16);   // [w j, w j+16, w j+1, w j+17] for bytes (4m, 4m+1) and (4m+2, 4m+3)
+        lo[m] = (int)pb_prmt(ra, rb, 0x6420u);
+        hi[m] = (int)pb_prmt(ra, rb, 0x7531u);
+    }
+}
+template <> struct PbQDec<PB_T_IQ4_NL> {
+    static constexpr int STEP_BYTES = 8 * 18;
+    static constexpr bool HAS_MIN = false, SCALE16 = false, AFFINE = false;
+    __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs&, PbQuarter& o) {
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+            const uint32_t blk = p + 18 * (2 * qt + b);
+            o.sc[2 * b] = o.sc[2 * b + 1] = pb_h2f((uint16_t)pb_lds16(blk));
+            uint32_t q[4];
+            pb_ld_u32x<4>(blk + 2, q);
+            pb_iq4_block(q, o.w + 8 * b, o.w + 8 * b + 4);
+        }
+    }
+};
+template <> struct PbQDec<PB_T_IQ4_XS> {
+    static constexpr int STEP_BYTES = 136;   // [d f16][scales_h u16][scales_l 4][qs 128] (gguf_q.rs:84-89)
+    static constexpr bool HAS_MIN = false, SCALE16 = false, AFFINE = false;
+    __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs&, PbQuarter& o) {
+        const uint2 hdr = pb_lds64(p);
+        const float d = pb_h2f((uint16_t)(hdr.x & 0xFFFF));
+        const uint32_t sh = hdr.x >> 16, sl = hdr.y;
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+            const int ib = 2 * qt + b;
+            const int ls = (int)((sl >> (4 * ib)) & 0xF) | (int)(((sh >> (2 * ib)) & 3) << 4);
+            o.sc[2 * b] = o.sc[2 * b + 1] = d * (float)(ls - 32);
+            // blocks are 136 bytes: the codes of a sub-block start on an 8-byte boundary, on a 16-byte one only in every other block
+            const uint2 v0 = pb_lds64(p + 8 + 16 * ib), v1 = pb_lds64(p + 16 + 16 * ib);
+            const uint32_t q[4] = {v0.x, v0.y, v1.x, v1.y};
+            pb_iq4_block(q, o.w + 8 * b, o.w + 8 * b + 4);
+        }
+    }
+};
+
 // unsigned bytes of a times signed bytes of b
 __device__ __forceinline__ int pb_dp4a_us(int a, int b, int c) {
     int d; asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;

@@ -28,8 +28,8 @@ def test_dequant_golden_bit_exact(ctx, name):
 
 @pytest.mark.parametrize("name", list(EXTRA))
 def test_extra_formats_dequant_golden_and_gemv(ctx, name):
-    """IQ3_XXS / IQ2_S / IQ4_NL / IQ4_XS: dequantization bit-for-bit against the gguf-py fixture, and the generic GEMV
-    against the oracle (these formats take the f32 kernel, not the streaming ones)."""
+    """IQ3_XXS / IQ2_S / IQ4_NL / IQ4_XS: dequantization bit-for-bit against the gguf-py fixture, and the GEMV over the
+    fixture's bytes against the oracle."""
     g = np.load(GOLD / f"dequant_{name}.npz")
     rows, cols = int(g["rows"]), int(g["cols"])
     W = pb.QMat.upload(ctx, EXTRA[name], rows, cols, g["raw"])
@@ -71,11 +71,11 @@ def test_config0_iq3s_gemv(ctx):
     W.free()
 
 
-@pytest.mark.parametrize("name", list(TYPES) + ["F32"])
+@pytest.mark.parametrize("name", list(TYPES) + list(EXTRA) + ["F32"])
 @pytest.mark.parametrize("shape", [(2048, 512), (1024, 2048), (4096, 2048), (515, 2048), (200, 4096), (300, 256), (40, 768)])
 def test_gemv_sweep(ctx, name, shape):
     """Config 1 shapes (lm-head covered separately) and ragged row counts, batch 1 / 4 / 16 and odd batches."""
-    t = pb.F32 if name == "F32" else TYPES[name]
+    t = pb.F32 if name == "F32" else (TYPES[name] if name in TYPES else EXTRA[name])
     rows, cols = shape
     W = pb.QMat.synth(ctx, t, rows, cols, 0, 42)
     Wo = oracle.QMat.synth(t, rows, cols, 0, 42)

@@ -154,3 +154,42 @@ def test_loaded_model_with_indexer_and_trained_context(ctx, tmp_path):
     for s in (a, b, c):
         s.destroy()
     m.destroy(); ref.destroy(); plain.destroy()
+
+
+@pytest.mark.gpu
+def test_mixed_type_file_decodes_like_the_oracle(ctx, tmp_path):
+    """A file whose tensors mix the block formats the way the reference's own checkpoint does (routed and shared gate / up in
+    IQ3_XXS or IQ2_S by layer, down in IQ4_NL, projections in IQ4_XS and IQ3_S, Q8_0 head, Q4_K embeddings): every tensor
+    runs through the streaming kernels in its own format, and the loaded model gives the oracle's greedy tokens."""
+    pytest.importorskip("gguf")
+    from helpers import oracle_model
+    cfg = small_cfg(pb, n_layers=8, kv_bits=4, kv_recent=64, max_ctx=128)
+    spec = []
+    for it in synth.model_spec(cfg, 45):
+        if it[0] == "mat" and it[3] == pb.IQ3_S:
+            _, layer, role, ty, rows, cols, tid = it
+            if role in ("EXP_GATE", "EXP_UP", "SH_GATE", "SH_UP"):
+                ty = pb.IQ3_XXS if layer % 2 == 0 else pb.IQ2_S
+            elif role in ("EXP_DOWN", "SH_DOWN"):
+                ty = pb.IQ4_NL
+            elif role.startswith("ATTN_") or role == "LIN_OUT":
+                ty = pb.IQ4_XS
+            elif role == "OUTPUT":
+                ty = pb.Q8_0
+            elif role == "TOKEN_EMBD":
+                ty = pb.Q4_K
+            it = ("mat", layer, role, ty, rows, cols, tid)
+        spec.append(it)
+    p = tmp_path / "mixed.gguf"
+    write_synth_gguf(p, cfg, spec, 45)
+    m = load_model(ctx, p, max_ctx=128, kv_bits=4, kv_recent=64)
+    om, _ = oracle_model(cfg, spec, 45)
+    st, ost = m.new_state(1), om.new_state()
+    prompt = [3, 999, 27, 500, 1]
+    lg, lo = st.forward(np.array(prompt, np.uint32))[0], ost.forward(prompt)
+    assert np.max(np.abs(lg - lo)) < 1e-3 * np.max(np.abs(lo))
+    tok = otok = int(lg.argmax())
+    for i in range(32):
+        tok = int(st.step_greedy([tok])[0]); otok = oracle.argmax(ost.forward([otok]))
+        assert tok == otok, (i, ost.margins())
+    st.destroy(); m.destroy()
