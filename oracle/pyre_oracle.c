@@ -93,6 +93,9 @@ int orc_type_geom(int type, int* el, int* by) {  /* gguf_q.rs:33-41 */
         case ORC_IQ2_S: e = 256; b = 82; break;
         case ORC_IQ4_NL: e = 32; b = 18; break;
         case ORC_IQ4_XS: e = 256; b = 136; break;
+        case ORC_Q2_0: e = 64; b = 18; break;
+        case ORC_IQ2_XXS: e = 256; b = 66; break;
+        case ORC_Q6_K: e = 256; b = 210; break;
         default: return -1;
     }
     if (el) *el = e;
@@ -159,6 +162,38 @@ int orc_dequant(int type, const uint8_t* x, int64_t n, float* y) {  /* gguf_q.rs
                 int ls = (int)((sl[ib / 2] >> (4 * (ib % 2))) & 0xF) | (int)(((sh >> (2 * ib)) & 3) << 4); float dl = d * (float)(ls - 32);
                 for (int j = 0; j < 16; j++) { yy[j] = (float)PB_KVALUES_IQ4NL[qs[j] & 0xF] * dl; yy[16 + j] = (float)PB_KVALUES_IQ4NL[qs[j] >> 4] * dl; }
                 yy += 32; qs += 16;
+            }
+        }
+        break;
+    case ORC_Q2_0:                                                                             /* :80-81: 64 weights, two bits each, value (code - 1) * d */
+        for (int64_t i = 0; i < nb; i++) {
+            const uint8_t* b = x + i * bs; float d = h2f(rd16(b)); float* yy = y + i * 64;
+            for (int k = 0; k < 16; k++) for (int j = 0; j < 4; j++) yy[4 * k + j] = (float)((int)((b[2 + k] >> (2 * j)) & 3) - 1) * d;
+        }
+        break;
+    case ORC_Q6_K:                                                                             /* :114-121 */
+        for (int64_t i = 0; i < nb; i++) {
+            const uint8_t* b = x + i * bs; const uint8_t* ql = b; const uint8_t* qh = b + 128; const int8_t* sc = (const int8_t*)(b + 192); float d = h2f(rd16(b + 208)); float* yy = y + i * 256;
+            for (int n = 0; n < 2; n++) {
+                for (int l = 0; l < 32; l++) { int is = l / 16;
+                    int q1 = (int)((ql[l] & 0xF) | ((qh[l] & 3) << 4)) - 32, q2 = (int)((ql[l + 32] & 0xF) | (((qh[l] >> 2) & 3) << 4)) - 32;
+                    int q3 = (int)((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32, q4 = (int)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32;
+                    yy[l] = d * (float)sc[is] * (float)q1; yy[l + 32] = d * (float)sc[is + 2] * (float)q2;
+                    yy[l + 64] = d * (float)sc[is + 4] * (float)q3; yy[l + 96] = d * (float)sc[is + 6] * (float)q4; }
+                yy += 128; ql += 64; qh += 32; sc += 8;
+            }
+        }
+        break;
+    case ORC_IQ2_XXS:                                                                          /* :122-125 */
+        for (int64_t i = 0; i < nb; i++) {
+            const uint8_t* b = x + i * bs; float d = h2f(rd16(b)); const uint8_t* qs = b + 2; float* yy = y + i * 256;
+            for (int ib = 0; ib < 8; ib++) {
+                const uint8_t* a0 = qs + 8 * ib; uint32_t a1 = (uint32_t)qs[8 * ib + 4] | ((uint32_t)qs[8 * ib + 5] << 8) | ((uint32_t)qs[8 * ib + 6] << 16) | ((uint32_t)qs[8 * ib + 7] << 24);
+                float db = d * (0.5f + (float)(a1 >> 28)) * 0.25f;
+                for (int l = 0; l < 4; l++) {
+                    uint64_t g = PB_IQ2XXS_GRID[a0[l]]; uint8_t gb[8]; for (int j = 0; j < 8; j++) gb[j] = (uint8_t)(g >> (8 * j));
+                    put8(yy, db, gb, PB_KSIGNS_IQ2XS[(a1 >> (7 * l)) & 127]); yy += 8;
+                }
             }
         }
         break;
@@ -269,6 +304,12 @@ static void synth_block(int type, uint64_t tkey, uint64_t b, uint8_t* out) {
     case ORC_IQ2_S: synth_payload(k, 3, out + 2, 80); break;
     case ORC_IQ4_NL: synth_payload(k, 3, out + 2, 16); break;
     case ORC_IQ4_XS: synth_payload(k, 3, out + 2, 134); break;
+    case ORC_Q2_0: synth_payload(k, 3, out + 2, 16); break;
+    case ORC_Q6_K:   /* the f16 scale closes the block; sub-block scales kept to -8..7 so that weights stay in the range of the other generators */
+        synth_payload(k, 3, out, 208);
+        for (int i = 192; i < 208; i++) out[i] = (uint8_t)(int8_t)((int)(out[i] & 15) - 8);
+        out[208] = (uint8_t)d; out[209] = (uint8_t)(d >> 8); break;
+    case ORC_IQ2_XXS: synth_payload(k, 3, out + 2, 64); break;
     }
 }
 void orc_synth_rows(int type, uint64_t seed, uint64_t tid, int64_t cols, int64_t r0, int64_t nrows, uint8_t* out) {

@@ -12,7 +12,7 @@
 #define PB_TABLE_QUAL static __device__ const
 #include "pb_iq_tables.h"
 
-enum : int { PB_T_F32 = 0, PB_T_F16 = 1, PB_T_Q8_0 = 8, PB_T_Q4_K = 12, PB_T_IQ2_XS = 17, PB_T_IQ3_XXS = 18, PB_T_IQ4_NL = 20, PB_T_IQ3_S = 21, PB_T_IQ2_S = 22,
+enum : int { PB_T_F32 = 0, PB_T_F16 = 1, PB_T_Q8_0 = 8, PB_T_Q4_K = 12, PB_T_Q6_K = 14, PB_T_IQ2_XXS = 16, PB_T_Q2_0 = 42, PB_T_IQ2_XS = 17, PB_T_IQ3_XXS = 18, PB_T_IQ4_NL = 20, PB_T_IQ3_S = 21, PB_T_IQ2_S = 22,
              PB_T_IQ4_XS = 23, PB_T_BF16 = 30,
              // internal, never a ggml id: IQ3_S re-coded at upload into 4-bit codes (see pb_repack.cu).  Every IQ3_S
              // codebook value is odd (1..15), so a weight is one of the sixteen values -15, -13, .. 15 = 2 c - 15.
@@ -28,8 +28,9 @@ struct PbTables {
     const uint32_t* iq3xxs; // 256 x 4 grid bytes
     const uint64_t* iq2s;   // 1024 x 8 grid bytes
     const int8_t* kvalues;  // 16 values of the IQ4 non-linear code
+    const uint64_t* iq2xxs; // 256 x 8 grid bytes
 };
-#define PB_TABLE_BYTES (512 * 8 + 512 * 4 + 128 + 256 * 4 + 1024 * 8 + 16)
+#define PB_TABLE_BYTES (512 * 8 + 512 * 4 + 128 + 256 * 4 + 1024 * 8 + 16 + 256 * 8)
 
 // Copy the codebooks a format needs into shared memory at `dst` (16-byte aligned,
 // PB_TABLE_BYTES long).  All threads of the CTA call it; the caller synchronises after.
@@ -56,7 +57,12 @@ __device__ __forceinline__ PbTables pb_load_tables(uint8_t* dst, int tid, int nt
         for (int i = tid; i < 1024; i += nthreads) g2s[i] = PB_IQ2S_GRID[i];
     if (FMT == PB_T_IQ4_NL || FMT == PB_T_IQ4_XS)
         for (int i = tid; i < 16; i += nthreads) kv[i] = PB_KVALUES_IQ4NL[i];
-    t.iq2xs = g2; t.iq3s = g3; t.ksigns = ks; t.iq3xxs = g3x; t.iq2s = g2s; t.kvalues = kv;
+    uint64_t* g2x = reinterpret_cast<uint64_t*>(dst + 512 * 8 + 512 * 4 + 128 + 256 * 4 + 1024 * 8 + 16);
+    if (FMT == PB_T_IQ2_XXS) {
+        for (int i = tid; i < 256; i += nthreads) g2x[i] = PB_IQ2XXS_GRID[i];
+        for (int i = tid; i < 128; i += nthreads) ks[i] = PB_KSIGNS_IQ2XS[i];
+    }
+    t.iq2xs = g2; t.iq3s = g3; t.ksigns = ks; t.iq3xxs = g3x; t.iq2s = g2s; t.kvalues = kv; t.iq2xxs = g2x;
     return t;
 }
 
@@ -202,6 +208,63 @@ template <> struct PbFmt<PB_T_IQ4_XS> : PbContig8 {
     }
 };
 
+// Q2_0 (gguf_q.rs:80-81, ggml id 42): blocks of 64 = [d f16][16 bytes]; weight 4k + j is field j (two bits) of byte k, value (field - 1) * d
+template <> struct PbFmt<PB_T_Q2_0> : PbContig8 {
+    static constexpr int STEP_BYTES = 4 * 18;
+    static constexpr bool HAS_MIN = false;
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables&, PbUnit& o) {
+        const uint8_t* b = p + 18 * (u >> 3);
+        o.sa = o.sb = pb_h2f((uint16_t)(b[0] | (b[1] << 8)));
+        o.ma = o.mb = 0.0f;
+        const uint32_t two = (uint32_t)b[2 + 2 * (u & 7)] | ((uint32_t)b[3 + 2 * (u & 7)] << 8);
+#pragma unroll
+        for (int j = 0; j < 8; j++) o.w[j] = (float)((int)((two >> (2 * j)) & 3) - 1);
+    }
+};
+
+// IQ2_XXS (gguf_q.rs:122-125): per 32 weights four 8-bit grid indices (entries of eight magnitudes) and one u32 with four
+// 7-bit sign patterns and a 4-bit scale
+template <> struct PbFmt<PB_T_IQ2_XXS> : PbContig8 {
+    static constexpr int STEP_BYTES = 66;   // [d f16][8 x (4 index bytes, u32 signs and scale)]
+    static constexpr bool HAS_MIN = false;
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables& T, PbUnit& o) {
+        const float d = pb_h2f(*reinterpret_cast<const uint16_t*>(p));
+        const int ib = u >> 2, l = u & 3;
+        const uint8_t* q = p + 2 + 8 * ib;
+        const uint32_t a = (uint32_t)q[4] | ((uint32_t)q[5] << 8) | ((uint32_t)q[6] << 16) | ((uint32_t)q[7] << 24);
+        o.sa = o.sb = __fmul_rn(__fmul_rn(d, 0.5f + (float)(a >> 28)), 0.25f);
+        o.ma = o.mb = 0.0f;
+        const uint64_t g = T.iq2xxs[q[l]];
+        const uint32_t sg = T.ksigns[(a >> (7 * l)) & 127];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float x = (float)((uint32_t)(g >> (8 * j)) & 0xFF);
+            o.w[j] = (sg >> j) & 1 ? -x : x;
+        }
+    }
+};
+
+// Q6_K (gguf_q.rs:114-121): [ql 128][qh 64][scales 16 x i8][d f16]; per half of 128 weights, weight l + 32 g (g = 0..3) takes its
+// low four bits from ql[l + 32 (g & 1)] (low nibble for g < 2, high nibble else), bits 4-5 from field g of qh[l], scale 2 g + l / 16
+template <> struct PbFmt<PB_T_Q6_K> : PbContig8 {
+    static constexpr int STEP_BYTES = 210;
+    static constexpr bool HAS_MIN = false;
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables&, PbUnit& o) {
+        const float d = pb_h2f((uint16_t)(p[208] | (p[209] << 8)));
+        const int n = u >> 4, g = (u >> 2) & 3, l0 = 8 * (u & 3);
+        const float sc = (float)(int8_t)p[192 + 8 * n + 2 * g + (l0 >> 4)];
+        o.sa = o.sb = __fmul_rn(d, sc);
+        o.ma = o.mb = 0.0f;
+        const uint8_t* ql = p + 64 * n + 32 * (g & 1) + l0;
+        const uint8_t* qh = p + 128 + 32 * n + l0;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int lo = g < 2 ? (ql[j] & 0xF) : (ql[j] >> 4);
+            o.w[j] = (float)((lo | (((qh[j] >> (2 * g)) & 3) << 4)) - 32);
+        }
+    }
+};
+
 template <> struct PbFmt<PB_T_Q8_0> : PbContig8 {
     static constexpr int STEP_BYTES = 8 * 34;  // eight [d f16][32 x i8] blocks
     static constexpr bool HAS_MIN = false;
@@ -297,6 +360,9 @@ static inline int pb_geom(int type, int* elems, int* bytes) {
         case PB_T_IQ2_S: e = 256; b = 82; break;
         case PB_T_IQ4_NL: e = 32; b = 18; break;
         case PB_T_IQ4_XS: e = 256; b = 136; break;
+        case PB_T_Q2_0: e = 64; b = 18; break;
+        case PB_T_IQ2_XXS: e = 256; b = 66; break;
+        case PB_T_Q6_K: e = 256; b = 210; break;
         case PB_T_IQ3S_N4: e = 256; b = 136; break;
         default: return -1;
     }
@@ -314,6 +380,9 @@ static inline int pb_geom(int type, int* elems, int* bytes) {
         case PB_T_IQ2_S: { constexpr int FMT = PB_T_IQ2_S; F(__VA_ARGS__); } break; \
         case PB_T_IQ4_NL: { constexpr int FMT = PB_T_IQ4_NL; F(__VA_ARGS__); } break; \
         case PB_T_IQ4_XS: { constexpr int FMT = PB_T_IQ4_XS; F(__VA_ARGS__); } break; \
+        case PB_T_Q2_0: { constexpr int FMT = PB_T_Q2_0; F(__VA_ARGS__); } break; \
+        case PB_T_IQ2_XXS: { constexpr int FMT = PB_T_IQ2_XXS; F(__VA_ARGS__); } break; \
+        case PB_T_Q6_K: { constexpr int FMT = PB_T_Q6_K; F(__VA_ARGS__); } break; \
         case PB_T_Q4_K: { constexpr int FMT = PB_T_Q4_K; F(__VA_ARGS__); } break;    \
         case PB_T_Q8_0: { constexpr int FMT = PB_T_Q8_0; F(__VA_ARGS__); } break;    \
         case PB_T_F32: { constexpr int FMT = PB_T_F32; F(__VA_ARGS__); } break;      \

@@ -765,6 +765,9 @@ static int launch_expert_type(pb_ctx* ctx, const PbExpertParams& p, int type, in
         case PB_T_IQ2_S: GO(PB_T_IQ2_S);
         case PB_T_IQ4_NL: GO(PB_T_IQ4_NL);
         case PB_T_IQ4_XS: GO(PB_T_IQ4_XS);
+        case PB_T_Q2_0: GO(PB_T_Q2_0);
+        case PB_T_IQ2_XXS: GO(PB_T_IQ2_XXS);
+        case PB_T_Q6_K: GO(PB_T_Q6_K);
         default: GO(PB_T_Q8_0);
     }
 #undef GO

@@ -306,6 +306,84 @@ template <> struct PbQDec<PB_T_IQ4_XS> {
     }
 };
 
+// ---- IQ2_XXS: per 32 weights four 8-bit grid indices (entries of eight magnitudes) and one u32 with four 7-bit sign patterns and
+// a 4-bit scale (gguf_q.rs:122-125).  Grid entries from shared memory (256 x 8 bytes), signs as IQ3_XXS.
+template <> struct PbQDec<PB_T_IQ2_XXS> {
+    static constexpr int STEP_BYTES = 66;
+    static constexpr bool HAS_MIN = false, SCALE16 = false, AFFINE = false;
+    __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs& T, PbQuarter& o) {
+        const float d = pb_h2f((uint16_t)pb_lds16(p));
+        uint32_t q[4];                               // [indices, signs and scale] of the quarter's two sub-blocks
+        pb_ld_u32x<4>(p + 2 + 16 * qt, q);
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+            const uint32_t idx = q[2 * b], aux = q[2 * b + 1];
+            const float db = d * (0.5f + (float)(aux >> 28)) * 0.25f;
+            o.sc[2 * b] = o.sc[2 * b + 1] = db;
+#pragma unroll
+            for (int l = 0; l < 4; l++) {
+                const uint2 g = pb_lds64(T.grid + ((idx >> (8 * l)) & 0xFF) * T.stride);
+                const uint32_t s7 = (aux >> (7 * l)) & 127;
+                const uint32_t s8 = s7 | ((__popc(s7) & 1) << 7);
+                const uint4 m = pb_lds128(T.sign256 + s8 * 16);
+                o.w[8 * b + 2 * l] = pb_apply_sign(g.x, m.x, m.y);
+                o.w[8 * b + 2 * l + 1] = pb_apply_sign(g.y, m.z, m.w);
+            }
+        }
+    }
+};
+
+// ---- Q2_0: blocks of 64 weights = [d f16][16 bytes], weight 4k + j in field j (two bits) of byte k, value field - 1.  A quarter is
+// one block.  x * 0x1001 puts fields 0 and 2 of a byte at bits 0 and 16, (x >> 2) * 0x100100 fields 1 and 3 at bits 8 and 24
+// (the partial products of an 8-bit x do not meet); the subtraction of 1 per byte runs with bit 7 set so that no borrow crosses.
+template <> struct PbQDec<PB_T_Q2_0> {
+    static constexpr int STEP_BYTES = 4 * 18;
+    static constexpr bool HAS_MIN = false, SCALE16 = false, AFFINE = false;
+    __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs&, PbQuarter& o) {
+        const uint32_t blk = p + 18 * qt;
+        const float d = pb_h2f((uint16_t)pb_lds16(blk));
+        o.sc[0] = o.sc[1] = o.sc[2] = o.sc[3] = d;
+        uint32_t q[4];
+        pb_ld_u32x<4>(blk + 2, q);
+#pragma unroll
+        for (int m = 0; m < 4; m++) {
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                const uint32_t x = (q[m] >> (8 * b)) & 0xFF;
+                const uint32_t f = ((x * 0x1001u) & 0x00030003u) | (((x >> 2) * 0x100100u) & 0x03000300u);
+                o.w[4 * m + b] = (int)((((f | 0x80808080u) - 0x01010101u)) ^ 0x80808080u);
+            }
+        }
+    }
+};
+
+// ---- Q6_K: [ql 128][qh 64][16 x i8 scales][d f16] (gguf_q.rs:114-121).  Per half of 128 weights, weight l + 32 g takes four bits
+// from ql[l + 32 (g & 1)] (low nibbles for g < 2) and two from field g of qh[l]; a quarter is groups g = 2 (qt & 1) and the next of half
+// qt / 2, so both groups read the same nibble side of 64 ql bytes and two fields of the same 32 qh bytes.  value = six bits - 32.
+template <> struct PbQDec<PB_T_Q6_K> {
+    static constexpr int STEP_BYTES = 210;
+    static constexpr bool HAS_MIN = false, SCALE16 = true, AFFINE = false;
+    __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs&, PbQuarter& o) {
+        const float d = pb_h2f((uint16_t)pb_lds16(p + 208));
+        const int n = qt >> 1, side = qt & 1;
+        uint32_t ql[16], qh[8], sc[1];
+        pb_ld_u32x<16>(p + 64 * n, ql);
+        pb_ld_u32x<8>(p + 128 + 32 * n, qh);
+        pb_ld_u32x<1>(p + 192 + 8 * n + 4 * side, sc);
+#pragma unroll
+        for (int h = 0; h < 4; h++) o.sc[h] = d * (float)(int)(int8_t)((sc[0] >> (8 * h)) & 0xFF);
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const uint32_t lo = (side ? ql[8 * b + k] >> 4 : ql[8 * b + k]) & 0x0F0F0F0Fu;
+                const uint32_t hi = ((qh[k] >> (4 * side + 2 * b)) & 0x03030303u) << 4;
+                o.w[8 * b + k] = (int)((((lo | hi) | 0x80808080u) - 0x20202020u) ^ 0x80808080u);
+            }
+        }
+    }
+};
+
 // unsigned bytes of a times signed bytes of b
 __device__ __forceinline__ int pb_dp4a_us(int a, int b, int c) {
     int d; asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;

@@ -11,7 +11,8 @@ from conftest import rel_err
 pytestmark = pytest.mark.gpu
 GOLD = Path(__file__).resolve().parent / "golden"
 TYPES = {"Q8_0": pb.Q8_0, "Q4_K": pb.Q4_K, "IQ2_XS": pb.IQ2_XS, "IQ3_S": pb.IQ3_S}
-EXTRA = {"IQ3_XXS": pb.IQ3_XXS, "IQ2_S": pb.IQ2_S, "IQ4_NL": pb.IQ4_NL, "IQ4_XS": pb.IQ4_XS}   # the GGUF loader's further formats
+EXTRA = {"IQ3_XXS": pb.IQ3_XXS, "IQ2_S": pb.IQ2_S, "IQ4_NL": pb.IQ4_NL, "IQ4_XS": pb.IQ4_XS,   # the GGUF loader's further formats
+         "Q2_0": pb.Q2_0, "IQ2_XXS": pb.IQ2_XXS, "Q6_K": pb.Q6_K}
 GEMV_TOL = 1e-3   # relative, f32 accumulate (north-star tolerance)
 
 
@@ -28,7 +29,7 @@ def test_dequant_golden_bit_exact(ctx, name):
 
 @pytest.mark.parametrize("name", list(EXTRA))
 def test_extra_formats_dequant_golden_and_gemv(ctx, name):
-    """IQ3_XXS / IQ2_S / IQ4_NL / IQ4_XS: dequantization bit-for-bit against the gguf-py fixture, and the GEMV over the
+    """The further formats: dequantization bit-for-bit against the gguf-py fixture, and the GEMV over the
     fixture's bytes against the oracle."""
     g = np.load(GOLD / f"dequant_{name}.npz")
     rows, cols = int(g["rows"]), int(g["cols"])
