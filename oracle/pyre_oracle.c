@@ -96,6 +96,7 @@ int orc_type_geom(int type, int* el, int* by) {  /* gguf_q.rs:33-41 */
         case ORC_Q2_0: e = 64; b = 18; break;
         case ORC_IQ2_XXS: e = 256; b = 66; break;
         case ORC_Q6_K: e = 256; b = 210; break;
+        case ORC_IQ1_M: e = 256; b = 56; break;
         default: return -1;
     }
     if (el) *el = e;
@@ -181,6 +182,24 @@ int orc_dequant(int type, const uint8_t* x, int64_t n, float* y) {  /* gguf_q.rs
                     yy[l] = d * (float)sc[is] * (float)q1; yy[l + 32] = d * (float)sc[is + 2] * (float)q2;
                     yy[l + 64] = d * (float)sc[is + 4] * (float)q3; yy[l + 96] = d * (float)sc[is + 6] * (float)q4; }
                 yy += 128; ql += 64; qh += 32; sc += 8;
+            }
+        }
+        break;
+    case ORC_IQ1_M:                                                                            /* :152-164: [qs 32][qh 16][scales 4 x u16]; the f16 scale sits in the top nibbles of the scale words */
+        for (int64_t i = 0; i < nb; i++) {
+            const uint8_t* b = x + i * bs; const uint8_t* qs = b; const uint8_t* qh = b + 32; float* yy = y + i * 256;
+            uint16_t sc[4]; for (int k = 0; k < 4; k++) sc[k] = rd16(b + 48 + 2 * k);
+            float d = h2f((uint16_t)((sc[0] >> 12) | ((sc[1] >> 8) & 0x00f0) | ((sc[2] >> 4) & 0x0f00) | (sc[3] & 0xf000)));
+            for (int ib = 0; ib < 8; ib++) {
+                float dl1 = d * (float)(2 * ((sc[ib / 2] >> (6 * (ib % 2))) & 7) + 1), dl2 = d * (float)(2 * ((sc[ib / 2] >> (6 * (ib % 2) + 3)) & 7) + 1);
+                for (int l = 0; l < 4; l++) {
+                    uint8_t h = qh[l / 2]; int sh = 4 * (l & 1);
+                    uint64_t g = PB_IQ1S_GRID[(size_t)qs[l] | ((((size_t)h >> sh) << 8) & 0x700)];
+                    float delta = (h >> sh) & 0x08 ? -0.125f : 0.125f, sl = l < 2 ? dl1 : dl2;
+                    for (int j = 0; j < 8; j++) yy[j] = sl * ((float)(int8_t)(uint8_t)(g >> (8 * j)) + delta);
+                    yy += 8;
+                }
+                qs += 4; qh += 2;
             }
         }
         break;
@@ -310,6 +329,10 @@ static void synth_block(int type, uint64_t tkey, uint64_t b, uint8_t* out) {
         for (int i = 192; i < 208; i++) out[i] = (uint8_t)(int8_t)((int)(out[i] & 15) - 8);
         out[208] = (uint8_t)d; out[209] = (uint8_t)(d >> 8); break;
     case ORC_IQ2_XXS: synth_payload(k, 3, out + 2, 64); break;
+    case ORC_IQ1_M:   /* the f16 scale goes, a nibble each, into the top of the four scale words */
+        synth_payload(k, 3, out, 56);
+        for (int i = 0; i < 4; i++) out[49 + 2 * i] = (uint8_t)((out[49 + 2 * i] & 0x0F) | (((d >> (4 * i)) & 0xF) << 4));
+        break;
     }
 }
 void orc_synth_rows(int type, uint64_t seed, uint64_t tid, int64_t cols, int64_t r0, int64_t nrows, uint8_t* out) {

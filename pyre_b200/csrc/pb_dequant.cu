@@ -17,7 +17,7 @@ __global__ void __launch_bounds__(256) pb_dequant_kernel(const uint8_t* __restri
     if (step * 32 >= n_units) return;
     if (step * 32 + (FMT == PB_T_Q4_K ? 0 : lane) >= n_units) return;  // ragged tail (formats with 32-wide blocks)
     PbTables T;
-    T.iq3s = PB_IQ3S_GRID; T.iq2xs = PB_IQ2XS_GRID; T.ksigns = PB_KSIGNS_IQ2XS; T.iq3xxs = PB_IQ3XXS_GRID; T.iq2s = PB_IQ2S_GRID; T.kvalues = PB_KVALUES_IQ4NL; T.iq2xxs = PB_IQ2XXS_GRID;
+    T.iq3s = PB_IQ3S_GRID; T.iq2xs = PB_IQ2XS_GRID; T.ksigns = PB_KSIGNS_IQ2XS; T.iq3xxs = PB_IQ3XXS_GRID; T.iq2s = PB_IQ2S_GRID; T.kvalues = PB_KVALUES_IQ4NL; T.iq2xxs = PB_IQ2XXS_GRID; T.iq1s = PB_IQ1S_GRID;
     PbUnit u;
     F::unit(w + step * F::STEP_BYTES, lane, T, u);
     float* o = out + step * 256;
@@ -85,6 +85,7 @@ __global__ void __launch_bounds__(256) pb_synth_kernel(uint8_t* __restrict__ w, 
     int j0 = 3, off = 1, payload = BS - 2;
     if (FMT == PB_T_Q4_K) { o[1] = pb_synth_scale(k, 3); j0 = 6; off = 2; payload = 140; }
     if (FMT == PB_T_Q6_K) { off = 0; payload = 208; }   // the f16 scale closes the block
+    if (FMT == PB_T_IQ1_M) { off = 0; payload = 56; }   // no scale of its own at the front
     for (int i = 0; i < payload; i += 8) {
         const uint64_t v = pb_sm64(k + (uint64_t)(j0 + i / 8));
 #pragma unroll
@@ -98,6 +99,10 @@ __global__ void __launch_bounds__(256) pb_synth_kernel(uint8_t* __restrict__ w, 
             }
             o[off + i / 2 + h] = (uint16_t)two;
         }
+    }
+    if (FMT == PB_T_IQ1_M) {   // the f16 scale goes, a nibble each, into the top of the four scale words
+        const uint32_t d = pb_synth_scale(k, 0);
+        for (int i = 0; i < 4; i++) o[24 + i] = (uint16_t)((o[24 + i] & 0x0FFF) | (((d >> (4 * i)) & 0xF) << 12));
     }
     if (FMT == PB_T_Q6_K) {   // sub-block scales kept to -8..7
         for (int i = 96; i < 104; i++) {
@@ -130,6 +135,7 @@ int pb_launch_synth(pb_ctx* ctx, int type, uint8_t* w, int64_t nblocks, uint64_t
         case PB_T_Q2_0: pb_synth_kernel<PB_T_Q2_0><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
         case PB_T_IQ2_XXS: pb_synth_kernel<PB_T_IQ2_XXS><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
         case PB_T_Q6_K: pb_synth_kernel<PB_T_Q6_K><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
+        case PB_T_IQ1_M: pb_synth_kernel<PB_T_IQ1_M><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
         default: PB_FAIL(ctx, PB_ERR_ARG, "pb_qmat_synth: no generator for ggml type %d", type);
     }
     ctx->kernels_launched++;

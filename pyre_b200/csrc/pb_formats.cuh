@@ -12,7 +12,7 @@
 #define PB_TABLE_QUAL static __device__ const
 #include "pb_iq_tables.h"
 
-enum : int { PB_T_F32 = 0, PB_T_F16 = 1, PB_T_Q8_0 = 8, PB_T_Q4_K = 12, PB_T_Q6_K = 14, PB_T_IQ2_XXS = 16, PB_T_Q2_0 = 42, PB_T_IQ2_XS = 17, PB_T_IQ3_XXS = 18, PB_T_IQ4_NL = 20, PB_T_IQ3_S = 21, PB_T_IQ2_S = 22,
+enum : int { PB_T_F32 = 0, PB_T_F16 = 1, PB_T_Q8_0 = 8, PB_T_Q4_K = 12, PB_T_Q6_K = 14, PB_T_IQ2_XXS = 16, PB_T_Q2_0 = 42, PB_T_IQ1_M = 29, PB_T_IQ2_XS = 17, PB_T_IQ3_XXS = 18, PB_T_IQ4_NL = 20, PB_T_IQ3_S = 21, PB_T_IQ2_S = 22,
              PB_T_IQ4_XS = 23, PB_T_BF16 = 30,
              // internal, never a ggml id: IQ3_S re-coded at upload into 4-bit codes (see pb_repack.cu).  Every IQ3_S
              // codebook value is odd (1..15), so a weight is one of the sixteen values -15, -13, .. 15 = 2 c - 15.
@@ -29,6 +29,7 @@ struct PbTables {
     const uint64_t* iq2s;   // 1024 x 8 grid bytes
     const int8_t* kvalues;  // 16 values of the IQ4 non-linear code
     const uint64_t* iq2xxs; // 256 x 8 grid bytes
+    const uint64_t* iq1s;   // 2048 x 8 signed grid bytes (-1, 0, 1): read where it lies in global memory, never copied to shared memory
 };
 #define PB_TABLE_BYTES (512 * 8 + 512 * 4 + 128 + 256 * 4 + 1024 * 8 + 16 + 256 * 8)
 
@@ -62,7 +63,7 @@ __device__ __forceinline__ PbTables pb_load_tables(uint8_t* dst, int tid, int nt
         for (int i = tid; i < 256; i += nthreads) g2x[i] = PB_IQ2XXS_GRID[i];
         for (int i = tid; i < 128; i += nthreads) ks[i] = PB_KSIGNS_IQ2XS[i];
     }
-    t.iq2xs = g2; t.iq3s = g3; t.ksigns = ks; t.iq3xxs = g3x; t.iq2s = g2s; t.kvalues = kv; t.iq2xxs = g2x;
+    t.iq2xs = g2; t.iq3s = g3; t.ksigns = ks; t.iq3xxs = g3x; t.iq2s = g2s; t.kvalues = kv; t.iq2xxs = g2x; t.iq1s = PB_IQ1S_GRID;
     return t;
 }
 
@@ -244,6 +245,28 @@ template <> struct PbFmt<PB_T_IQ2_XXS> : PbContig8 {
     }
 };
 
+// IQ1_M (gguf_q.rs:152-164): [qs 32][qh 16][scales 4 x u16]; per 8 weights an 11-bit grid index (8 bits in qs, 3 in a nibble of qh) into
+// entries of eight values -1 / 0 / 1, the nibble's top bit the sign of a shift of 1/8; two 3-bit scales per 32 weights in the low twelve
+// bits of the scale words, the block's f16 scale in their top nibbles.
+template <> struct PbFmt<PB_T_IQ1_M> : PbContig8 {
+    static constexpr int STEP_BYTES = 56;
+    static constexpr bool HAS_MIN = false;
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables& T, PbUnit& o) {
+        const uint16_t* scw = reinterpret_cast<const uint16_t*>(p + 48);
+        const uint32_t s0 = scw[0], s1 = scw[1], s2 = scw[2], s3 = scw[3];
+        const float d = pb_h2f((uint16_t)((s0 >> 12) | ((s1 >> 8) & 0x00f0) | ((s2 >> 4) & 0x0f00) | (s3 & 0xf000)));
+        const int ib = u >> 2, l = u & 3;
+        const uint32_t sw = scw[ib >> 1];
+        o.sa = o.sb = __fmul_rn(d, (float)(2 * ((sw >> (6 * (ib & 1) + 3 * (l >> 1))) & 7) + 1));
+        const uint32_t h = (uint32_t)p[32 + 2 * ib + (l >> 1)] >> (4 * (l & 1));
+        const uint64_t g = T.iq1s[p[4 * ib + l] | ((h << 8) & 0x700)];
+        const float delta = h & 8 ? -0.125f : 0.125f;
+        o.ma = o.mb = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) o.w[j] = __fadd_rn((float)(int8_t)(uint8_t)(g >> (8 * j)), delta);
+    }
+};
+
 // Q6_K (gguf_q.rs:114-121): [ql 128][qh 64][scales 16 x i8][d f16]; per half of 128 weights, weight l + 32 g (g = 0..3) takes its
 // low four bits from ql[l + 32 (g & 1)] (low nibble for g < 2, high nibble else), bits 4-5 from field g of qh[l], scale 2 g + l / 16
 template <> struct PbFmt<PB_T_Q6_K> : PbContig8 {
@@ -363,6 +386,7 @@ static inline int pb_geom(int type, int* elems, int* bytes) {
         case PB_T_Q2_0: e = 64; b = 18; break;
         case PB_T_IQ2_XXS: e = 256; b = 66; break;
         case PB_T_Q6_K: e = 256; b = 210; break;
+        case PB_T_IQ1_M: e = 256; b = 56; break;
         case PB_T_IQ3S_N4: e = 256; b = 136; break;
         default: return -1;
     }
@@ -383,6 +407,7 @@ static inline int pb_geom(int type, int* elems, int* bytes) {
         case PB_T_Q2_0: { constexpr int FMT = PB_T_Q2_0; F(__VA_ARGS__); } break; \
         case PB_T_IQ2_XXS: { constexpr int FMT = PB_T_IQ2_XXS; F(__VA_ARGS__); } break; \
         case PB_T_Q6_K: { constexpr int FMT = PB_T_Q6_K; F(__VA_ARGS__); } break; \
+        case PB_T_IQ1_M: { constexpr int FMT = PB_T_IQ1_M; F(__VA_ARGS__); } break; \
         case PB_T_Q4_K: { constexpr int FMT = PB_T_Q4_K; F(__VA_ARGS__); } break;    \
         case PB_T_Q8_0: { constexpr int FMT = PB_T_Q8_0; F(__VA_ARGS__); } break;    \
         case PB_T_F32: { constexpr int FMT = PB_T_F32; F(__VA_ARGS__); } break;      \

@@ -15,7 +15,7 @@ __global__ void __launch_bounds__(32) pb_embed_kernel(const uint8_t* __restrict_
     if (id >= rows) id = 0;   // out-of-range token ids read row 0 instead of faulting
     PbTables T;
     T.iq3s = PB_IQ3S_GRID; T.iq2xs = PB_IQ2XS_GRID; T.ksigns = PB_KSIGNS_IQ2XS;
-    T.iq3xxs = PB_IQ3XXS_GRID; T.iq2s = PB_IQ2S_GRID; T.kvalues = PB_KVALUES_IQ4NL; T.iq2xxs = PB_IQ2XXS_GRID;
+    T.iq3xxs = PB_IQ3XXS_GRID; T.iq2s = PB_IQ2S_GRID; T.kvalues = PB_KVALUES_IQ4NL; T.iq2xxs = PB_IQ2XXS_GRID; T.iq1s = PB_IQ1S_GRID;
     PbUnit u;
     F::unit(w + (size_t)id * row_bytes + (size_t)step * F::STEP_BYTES, lane, T, u);
     float* o = out + (size_t)b * ldo + step * 256;

@@ -768,6 +768,7 @@ static int launch_expert_type(pb_ctx* ctx, const PbExpertParams& p, int type, in
         case PB_T_Q2_0: GO(PB_T_Q2_0);
         case PB_T_IQ2_XXS: GO(PB_T_IQ2_XXS);
         case PB_T_Q6_K: GO(PB_T_Q6_K);
+        case PB_T_IQ1_M: GO(PB_T_IQ1_M);
         default: GO(PB_T_Q8_0);
     }
 #undef GO

@@ -333,6 +333,30 @@ template <> struct PbQDec<PB_T_IQ2_XXS> {
     }
 };
 
+// ---- IQ1_M: weights are s * (g + delta) with g in -1 / 0 / 1 and delta = +-1/8, i.e. (s / 8) * (8 g +- 1) with an int8 in the bracket.
+// The shared-memory table holds those eight int8 per (sign, 11-bit index), so a look-up is the whole decode; scales per 16 weights.
+template <> struct PbQDec<PB_T_IQ1_M> {
+    static constexpr int STEP_BYTES = 56;    // blocks of 56 bytes keep every field below 8-byte aligned
+    static constexpr bool HAS_MIN = false, SCALE16 = true, AFFINE = false;
+    __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs& T, PbQuarter& o) {
+        const uint2 scw = pb_lds64(p + 48);
+        const uint32_t su = ((scw.x >> 12) & 0xF) | ((scw.x >> 24) & 0xF0) | ((scw.y >> 4) & 0xF00) | ((scw.y >> 16) & 0xF000);
+        const float d8 = pb_h2f((uint16_t)su) * 0.125f;
+        const uint32_t sw = (qt & 2 ? scw.y : scw.x) >> (16 * (qt & 1));      // scale word qt: sub-blocks 2 qt and 2 qt + 1
+#pragma unroll
+        for (int h = 0; h < 4; h++) o.sc[h] = d8 * (float)(2 * ((sw >> (3 * h)) & 7) + 1);
+        const uint2 qs = pb_lds64(p + 8 * qt);
+        const uint32_t qh = pb_lds32(p + 32 + 4 * qt);
+#pragma unroll
+        for (int l = 0; l < 8; l++) {
+            const uint32_t b = ((l < 4 ? qs.x : qs.y) >> (8 * (l & 3))) & 0xFF;
+            const uint32_t h = (qh >> (4 * l)) & 0xF;                          // three index bits and the sign, together the table's high bits
+            const uint2 g = pb_lds64(T.grid + (b | (h << 8)) * T.stride);
+            o.w[2 * l] = (int)g.x; o.w[2 * l + 1] = (int)g.y;
+        }
+    }
+};
+
 // ---- Q2_0: blocks of 64 weights = [d f16][16 bytes], weight 4k + j in field j (two bits) of byte k, value field - 1.  A quarter is
 // one block.  x * 0x1001 puts fields 0 and 2 of a byte at bits 0 and 16, (x >> 2) * 0x100100 fields 1 and 3 at bits 8 and 24
 // (the partial products of an 8-bit x do not meet); the subtraction of 1 per byte runs with bit 7 set so that no borrow crosses.

@@ -150,8 +150,8 @@ __device__ __forceinline__ void pb_load_xquarter(const uint32_t* xcol, int cols,
 // Fill the shared-memory tables a format needs at `tab` (16-byte aligned, pb_tab_bytes<FMT>(rep) long):
 // the sign look-up table first, then the codebook with `rep` copies of every entry (rep = 1, or one
 // copy per bank so that random look-ups of a warp never conflict).  The caller synchronises after.
-template <int FMT> __host__ __device__ constexpr int pb_tab_entry_bytes() { return FMT == PB_T_IQ3_S || FMT == PB_T_IQ3_XXS ? 4 : (FMT == PB_T_IQ2_XS || FMT == PB_T_IQ2_S || FMT == PB_T_IQ2_XXS ? 8 : 0); }
-template <int FMT> __host__ __device__ constexpr int pb_tab_entries() { return FMT == PB_T_IQ3_XXS || FMT == PB_T_IQ2_XXS ? 256 : (FMT == PB_T_IQ2_S ? 1024 : 512); }
+template <int FMT> __host__ __device__ constexpr int pb_tab_entry_bytes() { return FMT == PB_T_IQ3_S || FMT == PB_T_IQ3_XXS ? 4 : (FMT == PB_T_IQ2_XS || FMT == PB_T_IQ2_S || FMT == PB_T_IQ2_XXS || FMT == PB_T_IQ1_M ? 8 : 0); }
+template <int FMT> __host__ __device__ constexpr int pb_tab_entries() { return FMT == PB_T_IQ3_XXS || FMT == PB_T_IQ2_XXS ? 256 : (FMT == PB_T_IQ2_S ? 1024 : (FMT == PB_T_IQ1_M ? 4096 : 512)); }
 template <int FMT> __host__ __device__ constexpr uint32_t pb_tab_bytes(int rep) { return pb_tab_entry_bytes<FMT>() ? PB_SIGN_LUT_BYTES + pb_tab_entries<FMT>() * pb_tab_entry_bytes<FMT>() * rep : 0; }
 // copies of every entry when the codebook is replicated: one per shared-memory bank, but no more than 64 KB in all
 template <int FMT> __host__ __device__ constexpr int pb_tab_rep_max() {
@@ -192,6 +192,17 @@ __device__ __forceinline__ PbQTabs pb_fill_qtabs(uint8_t* tab, int rep, int tid,
     if (FMT == PB_T_IQ2_S) {
         uint64_t* g = reinterpret_cast<uint64_t*>(tab + PB_SIGN_LUT_BYTES);
         for (int i = tid; i < 1024 * rep; i += nthreads) g[i] = PB_IQ2S_GRID[i / rep];
+    }
+    if (FMT == PB_T_IQ1_M) {   // entry (sign << 11 | index) = 8 * grid value + (sign ? -1 : 1) per byte: the weights in eighths, as int8
+        uint64_t* g = reinterpret_cast<uint64_t*>(tab + PB_SIGN_LUT_BYTES);
+        for (int i = tid; i < 4096 * rep; i += nthreads) {
+            const int e = i / rep;
+            const uint64_t v = PB_IQ1S_GRID[e & 2047];
+            const int dl = e >> 11 ? -1 : 1;
+            uint64_t r = 0;
+            for (int j = 0; j < 8; j++) r |= (uint64_t)(uint8_t)(8 * (int)(int8_t)(uint8_t)(v >> (8 * j)) + dl) << (8 * j);
+            g[i] = r;
+        }
     }
     if (FMT == PB_T_IQ2_XXS) {
         uint64_t* g = reinterpret_cast<uint64_t*>(tab + PB_SIGN_LUT_BYTES);

@@ -159,7 +159,7 @@ def test_loaded_model_with_indexer_and_trained_context(ctx, tmp_path):
 @pytest.mark.gpu
 def test_mixed_type_file_decodes_like_the_oracle(ctx, tmp_path):
     """A file whose tensors mix the block formats the way the reference's own checkpoint does (routed and shared gate / up in
-    IQ3_XXS, IQ2_XXS or IQ2_S by layer, down in IQ4_NL, projections in IQ4_XS and IQ3_S, Q6_K head, Q4_K embeddings): every tensor
+    IQ3_XXS, IQ2_S, IQ2_XXS or IQ1_M by layer, down in IQ4_NL, projections in IQ4_XS and IQ3_S, Q6_K head, Q4_K embeddings): every tensor
     runs through the streaming kernels in its own format, and the loaded model gives the oracle's greedy tokens."""
     pytest.importorskip("gguf")
     from helpers import oracle_model
@@ -169,7 +169,7 @@ def test_mixed_type_file_decodes_like_the_oracle(ctx, tmp_path):
         if it[0] == "mat" and it[3] == pb.IQ3_S:
             _, layer, role, ty, rows, cols, tid = it
             if role in ("EXP_GATE", "EXP_UP", "SH_GATE", "SH_UP"):
-                ty = (pb.IQ3_XXS if layer % 4 == 0 else pb.IQ2_XXS) if layer % 2 == 0 else pb.IQ2_S
+                ty = (pb.IQ3_XXS, pb.IQ2_S, pb.IQ2_XXS, pb.IQ1_M)[layer % 4]
             elif role in ("EXP_DOWN", "SH_DOWN"):
                 ty = pb.IQ4_NL
             elif role.startswith("ATTN_") or role == "LIN_OUT":
