@@ -164,6 +164,10 @@ typedef enum pb_role {
     PB_R_IDX_Q, PB_R_IDX_K, PB_R_IDX_Q_NORM, PB_R_IDX_K_NORM,
     /* input stage of an MTP drafter model (src/model/mtp.rs:104-123): fc_embedding, fc_hidden, pre_fc_norm_embedding, pre_fc_norm_hidden */
     PB_R_MTP_FC_E, PB_R_MTP_FC_H, PB_R_MTP_PRE_E, PB_R_MTP_PRE_H,
+    /* per-layer n-gram embeddings (Ple, src/model/qwen4exp_gguf.rs:33, tensors :505, 512): per_layer_token_embd (global); per layer
+     * ple_key [streams * d][heads * dim], ple_value [d][heads * dim], ple_norm_key / ple_norm_query / ple_norm_conv [streams * d],
+     * ple_conv1d [streams * d][conv_kernel] */
+    PB_R_PLE_TAB, PB_R_PLE_KEY, PB_R_PLE_VALUE, PB_R_PLE_NORM_KEY, PB_R_PLE_NORM_QUERY, PB_R_PLE_NORM_CONV, PB_R_PLE_CONV,
     PB_R_COUNT
 } pb_role;
 
@@ -177,6 +181,15 @@ int pb_model_set_vec(pb_model* m, int layer, int role, const float* v_host, int6
  * more than budget + ratio - 1 tokens, to the budget / ratio best-scoring blocks plus the incomplete tail.  n_head = 0
  * (the default) switches it off.  Before pb_model_finalize. */
 int pb_model_set_indexer(pb_model* m, int budget, int ratio, int n_head, int head_dim);
+/* Per-layer n-gram embeddings (ple_rows / ple, src/model/qwen4exp_gguf.rs:1390-1434; Cfg ple_* :477-480, metadata keys `ple.ngram_size`,
+ * `ple.heads_per_ngram`, `ple.conv_kernel`, `ple.eos_token_id`, `embedding_length_per_layer_input`, `ple.layer_multipliers`,
+ * `ple.head_offsets`, `ple.head_vocab_sizes`).  Every fed token is hashed, together with its ngram - 1 predecessors (cut at a missing or
+ * end-of-sequence one), into heads = (ngram - 1) * heads_per_ngram rows of the PB_R_PLE_TAB table; the layers that hold PB_R_PLE_KEY add a
+ * gated projection of those rows, and a causal depthwise convolution of its normalized form over earlier positions, to the residual
+ * streams at their start.  multipliers[ngram], head_offsets[heads], head_vocab_sizes[heads]; 2 <= ngram <= 8, heads <= 32, dim a
+ * multiple of 256.  Before pb_model_finalize. */
+int pb_model_set_ple(pb_model* m, int ngram, int heads_per_ngram, int conv_kernel, uint32_t eos, int dim,
+                     const uint64_t* multipliers, const uint64_t* head_offsets, const uint64_t* head_vocab_sizes);
 /* Trained context of the checkpoint (`<arch>.context_length`).  When cfg.max_ctx exceeds it, the rope table is YaRN-scaled
  * for the whole run as the reference does at load (src/model/qwen4exp_gguf.rs:490-517, table src/qn_ctx.rs:160-186, mscale on
  * cos and sin :528-533); 0 (the default) or max_ctx <= ctx_train leave the plain table.  Before pb_model_finalize. */

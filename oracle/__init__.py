@@ -31,6 +31,7 @@ ROLES = [
     "OUT_HC_NORM", "OUT_HC_DOWN", "OUT_HC_UP",
     "IDX_Q", "IDX_K", "IDX_Q_NORM", "IDX_K_NORM",
     "MTP_FC_E", "MTP_FC_H", "MTP_PRE_E", "MTP_PRE_H",
+    "PLE_TAB", "PLE_KEY", "PLE_VALUE", "PLE_NORM_KEY", "PLE_NORM_QUERY", "PLE_NORM_CONV", "PLE_CONV",
 ]
 ROLE = {n: i for i, n in enumerate(ROLES)}
 
@@ -319,6 +320,23 @@ class Model:
     def set_indexer(self, budget: int, ratio: int, n_head: int, head_dim: int):
         """QSA block-sparse attention: layers that hold IDX_Q / IDX_K attend to budget / ratio blocks of ratio tokens."""
         lib().orc_model_set_indexer(self.h, C.c_int(budget), C.c_int(ratio), C.c_int(n_head), C.c_int(head_dim))
+
+    def set_ple(self, ngram: int, per_gram: int, conv_k: int, eos: int, dim: int, mult, off, vocab):
+        """Per-layer n-gram embeddings: layers that hold PLE_KEY add them at their start (ple, qwen4exp_gguf.rs:1409-1434)."""
+        a = lambda v: np.ascontiguousarray(v, dtype=np.uint64)
+        mult, off, vocab = a(mult), a(off), a(vocab)
+        assert mult.size == ngram and off.size == vocab.size == (ngram - 1) * per_gram
+        self.ple = (ngram, per_gram)
+        lib().orc_model_set_ple(self.h, C.c_int(ngram), C.c_int(per_gram), C.c_int(conv_k), C.c_uint32(eos), C.c_int(dim),
+                                mult.ctypes.data_as(C.c_void_p), off.ctypes.data_as(C.c_void_p), vocab.ctypes.data_as(C.c_void_p))
+
+    def ple_hash(self, ctx):
+        """Table rows of a token with context `ctx` (the token, then its predecessors; -1 = none)."""
+        ngram, per = self.ple
+        c = np.ascontiguousarray(ctx, dtype=np.int64); assert c.size == ngram
+        rows = np.zeros((ngram - 1) * per, dtype=np.int64)
+        lib().orc_ple_hash(self.h, c.ctypes.data_as(C.c_void_p), rows.ctypes.data_as(C.c_void_p))
+        return rows
 
     def new_state(self) -> "State":
         return State(self)

@@ -672,7 +672,7 @@ struct orc_model {
     orc_cfg cfg;
     orc_slot* slots;   /* [(n_layers + 1)][ORC_R_COUNT], index 0 = global */
     float* rope_inv;
-    int idx_budget, idx_ratio, idx_nh, idx_hd;   /* QSA indexer (Cfg :24-25); idx_nh = 0: none */
+    int idx_budget, idx_ratio, idx_nh, idx_hd;   /* QSA indexer (Cfg :24-25); idx_nh = 0: none */    int ple_ngram, ple_per_gram, ple_conv_k, ple_dim; uint32_t ple_eos; uint64_t ple_mult[8], ple_off[32], ple_vocab[32];   /* Cfg :477-480; ple_ngram = 0: none */
 };
 struct orc_state {
     const orc_model* m;
@@ -683,7 +683,11 @@ struct orc_state {
     int n_lin, n_attn;
     float** ik; float** ib;              /* per attention layer: raw index keys [max_ctx][idx_hd], pooled block keys [max_ctx/ratio][idx_hd] (State :194) */
     float logit_margin, router_margin, qsa_margin;
-    float* last_x; int64_t last_x_n;      /* final residual rows of the last forward call */
+    float* last_x; int64_t last_x_n;      /* final residual rows of the last forward call */    /* n-gram embeddings: the ids fed so far by position (State.tokens), and per layer that has them the normalized rows by
+     * position.  The reference keeps the last (conv_k - 1) * ngram rows in a ring (ple_hist :196, drained and extended per token
+     * :1432); row (hl - back) of that ring is the row of position p - back (zeros before the sequence starts), which is what
+     * the by-position array gives, and a position set back (spec_keep :2508) needs no checkpoint. */
+    uint32_t* tokens; float** ple_nrm;
 };
 
 static orc_slot* slot(const orc_model* m, int layer, int role) { return &m->slots[(size_t)(layer + 1) * ORC_R_COUNT + role]; }
@@ -706,6 +710,22 @@ void orc_model_free(orc_model* m) {
 /* QSA indexer geometry (Cfg :24-25, keys attention.indexer.* :481-485); layers that have ORC_R_IDX_Q use it */
 void orc_model_set_indexer(orc_model* m, int budget, int ratio, int n_head, int head_dim) {
     m->idx_budget = budget; m->idx_ratio = ratio < 1 ? 1 : ratio; m->idx_nh = n_head; m->idx_hd = head_dim;
+}
+void orc_model_set_ple(orc_model* m, int ngram, int per_gram, int conv_k, uint32_t eos, int dim, const uint64_t* mult, const uint64_t* off, const uint64_t* vocab) {
+    m->ple_ngram = ngram; m->ple_per_gram = per_gram; m->ple_conv_k = conv_k; m->ple_eos = eos; m->ple_dim = dim;
+    for (int i = 0; i < ngram && i < 8; i++) m->ple_mult[i] = mult[i];
+    for (int i = 0; i < (ngram - 1) * per_gram && i < 32; i++) { m->ple_off[i] = off[i]; m->ple_vocab[i] = vocab[i]; }
+}
+/* ple_rows :1394-1403: a context is cut at the first missing or end-of-sequence predecessor (everything older reads as eos); n-gram size n
+ * mixes the first n context ids, each times its multiplier (wrapping), by xor; head h of that size takes the mix modulo its own vocabulary */
+void orc_ple_hash(const orc_model* m, const int64_t* ctx_in, int64_t* rows) {
+    uint64_t ctx[8]; int cut = 0; ctx[0] = (uint64_t)ctx_in[0];
+    for (int s = 1; s < m->ple_ngram; s++) { int none = cut || ctx_in[s] < 0; cut = cut || none || (uint32_t)ctx_in[s] == m->ple_eos; ctx[s] = cut ? (uint64_t)m->ple_eos : (uint64_t)ctx_in[s]; }
+    for (int n = 2; n <= m->ple_ngram; n++) {
+        uint64_t mixed = ctx[0] * m->ple_mult[0];
+        for (int j = 1; j < n; j++) mixed ^= ctx[j] * m->ple_mult[j];
+        for (int gi = 0; gi < m->ple_per_gram; gi++) { int h = (n - 2) * m->ple_per_gram + gi; rows[h] = (int64_t)(mixed % m->ple_vocab[h] + m->ple_off[h]); }
+    }
 }
 /* Model::load :490-517: a context (cfg.max_ctx) past the trained length is YaRN-scaled for the whole run */
 void orc_model_set_ctx_train(orc_model* m, int64_t ctx_train) {
@@ -731,6 +751,10 @@ orc_state* orc_state_new(const orc_model* m) {  /* new_state :1345-1353 */
     s->kw = (uint32_t**)calloc((size_t)na, sizeof(void*)); s->vw = (uint32_t**)calloc((size_t)na, sizeof(void*));
     s->ks = (float**)calloc((size_t)na, sizeof(void*)); s->vs = (float**)calloc((size_t)na, sizeof(void*)); s->q4n = (int64_t*)calloc((size_t)na, 8);
     s->ik = (float**)calloc((size_t)na, sizeof(void*)); s->ib = (float**)calloc((size_t)na, sizeof(void*));
+    if (m->ple_ngram > 0) {
+        s->tokens = (uint32_t*)calloc((size_t)c->max_ctx, 4); s->ple_nrm = (float**)calloc((size_t)c->n_layers, sizeof(float*));
+        for (int il = 0; il < c->n_layers; il++) if (M(m, il, ORC_R_PLE_KEY)) s->ple_nrm[il] = (float*)calloc((size_t)c->max_ctx * (c->hc > 0 ? c->hc : 1) * c->d, 4);
+    }
     for (int i = 0; i < s->n_attn; i++) {
         if (m->idx_nh > 0) { s->ik[i] = (float*)calloc((size_t)c->max_ctx * m->idx_hd, 4); s->ib[i] = (float*)calloc((size_t)(c->max_ctx / m->idx_ratio + 1) * m->idx_hd, 4); }
         s->k[i] = (float*)calloc((size_t)c->max_ctx * row, 4); s->v[i] = (float*)calloc((size_t)c->max_ctx * row, 4);
@@ -743,6 +767,7 @@ void orc_state_free(orc_state* s) {
     if (!s) return;
     for (int i = 0; i < s->n_lin; i++) { free(s->conv[i]); free(s->ssm[i]); }
     for (int i = 0; i < s->n_attn; i++) { free(s->k[i]); free(s->v[i]); free(s->kw[i]); free(s->vw[i]); free(s->ks[i]); free(s->vs[i]); free(s->ik[i]); free(s->ib[i]); }
+    if (s->ple_nrm) { for (int il = 0; il < s->m->cfg.n_layers; il++) free(s->ple_nrm[il]); free(s->ple_nrm); } free(s->tokens);
     free(s->ik); free(s->ib); free(s->last_x); free(s->conv); free(s->ssm); free(s->k); free(s->v); free(s->kw); free(s->vw); free(s->ks); free(s->vs); free(s->q4n); free(s);
 }
 /* Layout rule of the packed region (kv_push :1517-1534): with len positions held, the first
@@ -787,15 +812,58 @@ static void hc_combine(const orc_cfg* c, float* x, const float* out, const float
 /* forward_inner :2087-2157 (pure-CPU branch :2134-2142).  hc == 0 selects the plain pre-norm
  * residual form (x += mixer(rms(x)*attn_norm); x += ffn(rms(x)*ffn_norm); head on rms(x)*out_norm),
  * which the reference does not have; hc >= 1 is the reference's hyper-connection plumbing. */
+/* ple :1409-1434 for one token at position pos: the table rows `emb` projected to a key per stream and one value; per stream a
+ * gate from the normalized key and the normalized stream, value times gate, normalized again; x += gated + silu(depthwise conv over
+ * the normalized rows of this and of earlier positions, conv_k taps ngram positions apart) */
+static void ple_token(const orc_model* m, int il, float* nrm_all, const float* key, const float* val, float* xt, int64_t pos) {
+    const orc_cfg* c = &m->cfg; int d = c->d, hcn = c->hc > 0 ? c->hc : 1, w = hcn * d, kk = m->ple_conv_k, dil = m->ple_ngram;
+    const float* nk = V(m, il, ORC_R_PLE_NORM_KEY); const float* nq = V(m, il, ORC_R_PLE_NORM_QUERY); const float* nc = V(m, il, ORC_R_PLE_NORM_CONV); const float* cv = V(m, il, ORC_R_PLE_CONV);
+    float* gated = (float*)malloc((size_t)w * 4); float* kn = (float*)malloc((size_t)d * 4); float* q = (float*)malloc((size_t)d * 4);
+    float* nrm = nrm_all + pos * w;
+    for (int s = 0; s < hcn; s++) {
+        memcpy(kn, key + (int64_t)s * d, (size_t)d * 4); rms_inplace(kn, nk + (int64_t)s * d, c->eps, d);
+        rms(xt + (int64_t)s * d, nq + (int64_t)s * d, c->eps, q, d);
+        float sc = orc_dot(kn, q, d) / sqrtf((float)d);
+        float g = sigm((signbit(sc) ? -1.0f : 1.0f) * sqrtf(fmaxf(fabsf(sc), 1e-6f)));
+        for (int i = 0; i < d; i++) gated[s * d + i] = val[i] * g;
+    }
+    memcpy(nrm, gated, (size_t)w * 4);
+    for (int s = 0; s < hcn; s++) rms_inplace(nrm + (int64_t)s * d, nc + (int64_t)s * d, c->eps, d);
+    for (int ch = 0; ch < w; ch++) {
+        float o = cv[ch * kk + kk - 1] * nrm[ch];
+        for (int k = 0; k < kk - 1; k++) { int64_t p = pos - (int64_t)(kk - 1 - k) * dil; o += cv[ch * kk + k] * (p >= 0 ? nrm_all[p * w + ch] : 0.0f); }
+        xt[ch] += gated[ch] + silu(o);
+    }
+    free(gated); free(kn); free(q);
+}
+
 int orc_forward(const orc_model* m, orc_state* st, const uint32_t* ids, int t, float* logits) {
     const orc_cfg* c = &m->cfg; int d = c->d, hc = c->hc; int xw = (hc > 0 ? hc : 1) * d; int64_t start = st->pos;
     if (start + t > c->max_ctx) return -2;
     float* x = (float*)malloc((size_t)t * xw * 4); float* mx = (float*)malloc((size_t)t * d * 4); float* o = (float*)malloc((size_t)t * d * 4); float* inj = (float*)malloc((size_t)t * (hc > 0 ? hc : 1) * 4);
     const orc_mat* embd = M(m, -1, ORC_R_TOKEN_EMBD);
     for (int ti = 0; ti < t; ti++) { orc_mat_row(embd, ids[ti], o); for (int s = 0; s < (hc > 0 ? hc : 1); s++) memcpy(x + ((int64_t)ti * (hc > 0 ? hc : 1) + s) * d, o, (size_t)d * 4); }  /* :2092 */
+    /* :2089, 2093: the ids join the history, then the table rows of every fed position (shared by all layers that use them) */
+    float* pemb = NULL; const int pnh = m->ple_ngram > 0 ? (m->ple_ngram - 1) * m->ple_per_gram : 0; const orc_mat* ptab = M(m, -1, ORC_R_PLE_TAB);
+    if (pnh > 0 && ptab) {
+        pemb = (float*)malloc((size_t)t * pnh * m->ple_dim * 4);
+        for (int ti = 0; ti < t; ti++) st->tokens[start + ti] = ids[ti];
+        for (int ti = 0; ti < t; ti++) {
+            int64_t ctx[8], rows[32]; int64_t p = start + ti;
+            for (int s = 0; s < m->ple_ngram; s++) ctx[s] = p >= s ? (int64_t)st->tokens[p - s] : -1;
+            orc_ple_hash(m, ctx, rows);
+            for (int h = 0; h < pnh; h++) orc_mat_row(ptab, rows[h], pemb + ((int64_t)ti * pnh + h) * m->ple_dim);
+        }
+    }
     int li = 0, ai = 0; st->router_margin = INFINITY; st->qsa_margin = INFINITY;
     int nk = c->lin_nk, nv = c->lin_nv, dk = c->lin_dk, dv = c->lin_dv; int ch = 2 * nk * dk + nv * dv; int row = c->n_kv * c->hd;
     for (int il = 0; il < c->n_layers; il++) {
+        if (pemb && M(m, il, ORC_R_PLE_KEY)) {   /* :2112 */
+            float* key = (float*)malloc((size_t)t * xw * 4); float* val = (float*)malloc((size_t)t * d * 4);
+            orc_matmul(M(m, il, ORC_R_PLE_KEY), pemb, t, key); orc_matmul(M(m, il, ORC_R_PLE_VALUE), pemb, t, val);
+            for (int ti = 0; ti < t; ti++) ple_token(m, il, st->ple_nrm[il], key + (int64_t)ti * xw, val + (int64_t)ti * d, x + (int64_t)ti * xw, start + ti);
+            free(key); free(val);
+        }
         if (hc > 0) hc_mix(m, il, ORC_R_HCA_NORM, ORC_R_HCA_DOWN, ORC_R_HCA_UP, ORC_R_HCA_INJECT, x, t, mx, inj);
         else for (int ti = 0; ti < t; ti++) rms(x + (int64_t)ti * d, V(m, il, ORC_R_ATTN_NORM), c->eps, mx + (int64_t)ti * d, d);
         if (is_full(c, il)) {  /* attn :1441-1446 */
@@ -853,7 +921,7 @@ int orc_forward(const orc_model* m, orc_state* st, const uint32_t* ids, int t, f
     orc_matmul(out, mx, 1, logits);                                                                              /* head_logits :2361-2364 */
     { uint32_t b = orc_argmax(logits, c->vocab); float second = -INFINITY; for (int i = 0; i < c->vocab; i++) if ((uint32_t)i != b) second = fmaxf(second, logits[i]); st->logit_margin = logits[b] - second; }
     st->pos = start + t;
-    free(x); free(mx); free(o); free(inj);
+    free(x); free(mx); free(o); free(inj); free(pemb);
     return 0;
 }
 

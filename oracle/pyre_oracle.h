@@ -90,6 +90,8 @@ enum {
     ORC_R_OUT_HC_NORM, ORC_R_OUT_HC_DOWN, ORC_R_OUT_HC_UP,
     ORC_R_IDX_Q, ORC_R_IDX_K, ORC_R_IDX_Q_NORM, ORC_R_IDX_K_NORM,   /* QSA indexer of an attention layer (Mixer::Attn idx, :501) */
     ORC_R_MTP_FC_E, ORC_R_MTP_FC_H, ORC_R_MTP_PRE_E, ORC_R_MTP_PRE_H,   /* input stage of the MTP drafter (src/model/mtp.rs:186-195), global */
+    /* per-layer n-gram embeddings (Ple :33, tensors :505, 512): the table (global), per layer key / value projections, three norm vectors, the conv taps */
+    ORC_R_PLE_TAB, ORC_R_PLE_KEY, ORC_R_PLE_VALUE, ORC_R_PLE_NORM_KEY, ORC_R_PLE_NORM_QUERY, ORC_R_PLE_NORM_CONV, ORC_R_PLE_CONV,
     ORC_R_COUNT
 };
 
@@ -98,6 +100,11 @@ typedef struct orc_state orc_state;
 
 orc_model* orc_model_new(const orc_cfg* cfg);
 void orc_model_free(orc_model* m);
+/* n-gram embedding geometry (Cfg ple_* :477-480): ngram, heads per n-gram size, conv taps, the end-of-sequence id that cuts a context,
+ * the width of a table row; mult[ngram], off[nh], vocab[nh] with nh = (ngram - 1) * per_gram.  Layers that hold ORC_R_PLE_KEY use it. */
+void orc_model_set_ple(orc_model* m, int ngram, int per_gram, int conv_k, uint32_t eos, int dim, const uint64_t* mult, const uint64_t* off, const uint64_t* vocab);
+/* table rows of a token whose context (the token first, then its predecessors, -1 = none) is ctx[ngram]: rows[nh] (ple_rows :1390-1407) */
+void orc_ple_hash(const orc_model* m, const int64_t* ctx, int64_t* rows);
 void orc_model_set_indexer(orc_model* m, int budget, int ratio, int n_head, int head_dim);   /* QSA geometry, Cfg :24-25 */
 void orc_model_set_ctx_train(orc_model* m, int64_t ctx_train);   /* YaRN when cfg.max_ctx > ctx_train (Model::load :490-517) */
 int orc_model_set_mat(orc_model* m, int layer, int role, const orc_mat* mat);   /* layer -1 = global */

@@ -37,6 +37,7 @@ ROLES = [
     "OUT_HC_NORM", "OUT_HC_DOWN", "OUT_HC_UP",
     "IDX_Q", "IDX_K", "IDX_Q_NORM", "IDX_K_NORM",
     "MTP_FC_E", "MTP_FC_H", "MTP_PRE_E", "MTP_PRE_H",
+    "PLE_TAB", "PLE_KEY", "PLE_VALUE", "PLE_NORM_KEY", "PLE_NORM_QUERY", "PLE_NORM_CONV", "PLE_CONV",
 ]
 ROLE = {n: i for i, n in enumerate(ROLES)}
 

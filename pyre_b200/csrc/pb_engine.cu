@@ -39,6 +39,8 @@ struct pb_model {
     int idx_budget = 0, idx_ratio = 1, idx_nh = 0, idx_hd = 0;   // QSA indexer geometry (Cfg :24-25); idx_nh = 0: none
     bool qsa = false;            // the attention layers hold indexer tensors
     int mtp_window = 0;          // > 0: this model is an MTP drafter layer (pb_model_set_mtp)
+    PbPleHash ple{}; int ple_conv_k = 0, ple_dim = 0, n_ple = 0;   // n-gram embeddings (pb_model_set_ple); ple.ngram = 0: none
+    std::vector<int> ple_idx;    // per layer: index among the layers that hold PLE tensors, or -1
     uint64_t weight_bytes_step = 0;
 };
 
@@ -89,6 +91,11 @@ struct pb_state {
     struct PbMtp* mtp = nullptr;   // drafter attached to this (main, batch-1) state
     uint32_t* ext_mask = nullptr; int* ext_on = nullptr; int64_t ext_ld = 0;   // a position mask set from outside (the drafter's window of cells)
     float *iproj = nullptr, *qsa_scores = nullptr; uint32_t* qsa_mask = nullptr; int* qsa_on = nullptr; int64_t ldi = 0, nb_cap = 0, mask_ld = 0;   // QSA work buffers
+    // n-gram embeddings: ids by position [batch][max_ctx], first position with a history per sequence, table rows / gathered rows /
+    // key and value / gated values of the rows in flight, per PLE layer the normalized rows by position % ple_R [batch][ple_R][streams * d]
+    uint32_t *tok_hist = nullptr, *ple_rows = nullptr; int64_t* ple_base = nullptr; int64_t ple_base_host = 0;
+    float *ple_emb = nullptr, *ple_key = nullptr, *ple_val = nullptr, *ple_gated = nullptr; int ple_R = 0;
+    std::vector<float*> ple_ring;
     std::vector<float*> conv, ssm;
     std::vector<PbKv> kv;
     uint32_t* trace = nullptr; int64_t* trace_len = nullptr; int64_t trace_cap = 0;
@@ -203,6 +210,26 @@ int pb_model_set_indexer(pb_model* m, int budget, int ratio, int n_head, int hea
     return PB_OK;
 }
 
+int pb_model_set_ple(pb_model* m, int ngram, int per_gram, int conv_k, uint32_t eos, int dim, const uint64_t* mult, const uint64_t* off, const uint64_t* vocab) {
+    if (!m) return PB_ERR_ARG;
+    pb_ctx* ctx = m->ctx;
+    PB_TRY(pb_enter(ctx));
+    if (m->finalized) PB_FAIL(ctx, PB_ERR_STATE, "pb_model_set_ple: the model is finalized");
+    if (!mult || !off || !vocab) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_set_ple: null array");
+    const int nh = (ngram - 1) * per_gram;
+    if (ngram < 2 || ngram > 8 || per_gram < 1 || nh > 32 || conv_k < 1 || conv_k > 16 || dim < 256 || dim % 256)
+        PB_FAIL(ctx, PB_ERR_ARG, "pb_model_set_ple: ngram %d (2..8), %d heads per n-gram (at most 32 heads in all), %d conv taps (1..16), dim %d (a multiple of 256)", ngram, per_gram, conv_k, dim);
+    PbPleHash& h = m->ple;
+    memset(&h, 0, sizeof h);
+    h.ngram = ngram; h.per_gram = per_gram; h.nh = nh; h.eos = eos;
+    for (int i = 0; i < ngram; i++) h.mult[i] = mult[i];
+    for (int i = 0; i < nh; i++) {
+        if (vocab[i] == 0 || off[i] + vocab[i] > 0xFFFFFFFFull) PB_FAIL(ctx, PB_ERR_ARG, "pb_model_set_ple: head %d has vocabulary %llu at offset %llu", i, (unsigned long long)vocab[i], (unsigned long long)off[i]);
+        h.off[i] = off[i]; h.vocab[i] = vocab[i];
+    }
+    m->ple_conv_k = conv_k; m->ple_dim = dim;
+    return PB_OK;
+}
 int pb_model_set_ctx_train(pb_model* m, int ctx_train) {
     if (!m) return PB_ERR_ARG;
     pb_ctx* ctx = m->ctx;
@@ -285,7 +312,26 @@ int pb_model_finalize(pb_model* m, int ep_rank, int ep_world) {
     if (c.hc == 0) PB_TRY(need_vec(m, -1, PB_R_OUT_NORM, c.d, "output_norm"));
     else PB_TRY(need_hc(m, -1, PB_R_OUT_HC_NORM, PB_R_OUT_HC_DOWN, PB_R_OUT_HC_UP, -1, "output_hc"));
     wb += (M(m, -1, PB_R_OUTPUT) ? M(m, -1, PB_R_OUTPUT) : M(m, -1, PB_R_TOKEN_EMBD))->nbytes;
+    m->ple_idx.assign((size_t)c.n_layers, -1); m->n_ple = 0;
+    if (m->ple.ngram > 0) {
+        if (m->mtp_window > 0) PB_FAIL(ctx, PB_UNSUPPORTED, "an MTP drafter has no n-gram embeddings");
+        pb_qmat* tab = M(m, -1, PB_R_PLE_TAB);
+        if (!tab || tab->cols != m->ple_dim) PB_FAIL(ctx, PB_ERR_STATE, "per_layer_token_embd: missing, or not %d columns wide", m->ple_dim);
+        for (int i = 0; i < m->ple.nh; i++)
+            if ((int64_t)(m->ple.off[i] + m->ple.vocab[i]) > tab->rows) PB_FAIL(ctx, PB_ERR_ARG, "n-gram head %d reaches row %llu of a table of %lld rows", i, (unsigned long long)(m->ple.off[i] + m->ple.vocab[i]), (long long)tab->rows);
+    }
     for (int il = 0; il < c.n_layers; il++) {
+        if (M(m, il, PB_R_PLE_KEY)) {
+            if (m->ple.ngram == 0) PB_FAIL(ctx, PB_ERR_STATE, "layer %d holds n-gram embedding tensors, but pb_model_set_ple was not called", il);
+            const int64_t w = (int64_t)(c.hc > 0 ? c.hc : 1) * c.d, ein = (int64_t)m->ple.nh * m->ple_dim;
+            PB_TRY(need_mat(m, il, PB_R_PLE_KEY, w, ein, "ple_key", false));
+            PB_TRY(need_mat(m, il, PB_R_PLE_VALUE, c.d, ein, "ple_value", false));
+            PB_TRY(need_vec(m, il, PB_R_PLE_NORM_KEY, w, "ple_norm_key"));
+            PB_TRY(need_vec(m, il, PB_R_PLE_NORM_QUERY, w, "ple_norm_query"));
+            PB_TRY(need_vec(m, il, PB_R_PLE_NORM_CONV, w, "ple_norm_conv"));
+            PB_TRY(need_vec(m, il, PB_R_PLE_CONV, w * m->ple_conv_k, "ple_conv1d"));
+            m->ple_idx[il] = m->n_ple++;
+        }
         if (c.hc == 0) {
             PB_TRY(need_vec(m, il, PB_R_ATTN_NORM, c.d, "attn_norm"));
             PB_TRY(need_vec(m, il, PB_R_FFN_NORM, c.d, "ffn_norm"));
@@ -429,6 +475,14 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
     A(pos, B); A(ids, Ba); A(next, Ba); A(amax, Ba); A(wpos, PB_PREFILL_CHUNK);
     A(ticket, 8 + (size_t)(Bm + 7) / 8);   // whole-launch counters, then one per group of 8 tokens of the router
     A(x, (size_t)Ba * c.d * (c.hc > 0 ? c.hc : 1));
+    if (m->n_ple > 0) {
+        const size_t w = (size_t)c.d * (c.hc > 0 ? c.hc : 1);
+        s->ple_R = (m->ple_conv_k - 1) * m->ple.ngram + (solo ? PB_PREFILL_CHUNK : 1);
+        A(tok_hist, (size_t)B * c.max_ctx); A(ple_base, B); A(ple_rows, (size_t)Ba * m->ple.nh); A(ple_emb, (size_t)Ba * m->ple.nh * m->ple_dim);
+        A(ple_key, (size_t)Ba * w); A(ple_val, (size_t)Ba * c.d); A(ple_gated, (size_t)Ba * w);
+        s->ple_ring.assign((size_t)m->n_ple, nullptr);
+        for (int i = 0; i < m->n_ple; i++) { if (rc == PB_OK) rc = dalloc(s, &s->ple_ring[(size_t)i], (size_t)B * s->ple_R * w); }
+    }
     if (c.hc > 0) { A(hxn, (size_t)Ba * c.hc * c.d); A(hgate, (size_t)Ba * c.hc * c.d); A(hlo, (size_t)Ba * c.hc_lr); A(hinj, (size_t)Ba * c.hc); A(hmix, (size_t)Ba * c.d); }
     A(xin, (size_t)Ba * (wide > c.d ? wide : c.d)); A(yout, (size_t)Ba * c.d);
     A(proj, (size_t)Ba * s->ldproj); A(olin, (size_t)Ba * wide); A(att, (size_t)Ba * wide);
@@ -575,6 +629,12 @@ int pb_state_set_pos(pb_state* s, int64_t pos) {
     std::vector<int64_t> v((size_t)s->batch, pos);
     PB_CUDA(ctx, cudaMemcpyAsync(s->pos, v.data(), v.size() * 8, cudaMemcpyHostToDevice, ctx->stream));
     PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    // n-gram embeddings: a position set ahead of the sequence (or back to 0) starts a history there; a position set back keeps what is below it
+    if (s->ple_base && (pos == 0 || pos > s->pos_host || pos < s->ple_base_host)) {
+        std::vector<int64_t> b((size_t)s->batch, pos);
+        PB_CUDA(ctx, cudaMemcpy(s->ple_base, b.data(), b.size() * 8, cudaMemcpyHostToDevice));
+        s->ple_base_host = pos;
+    }
     s->pos_host = pos;
     mtp_moved(s, pos);
     return PB_OK;
@@ -816,7 +876,7 @@ static int fused_build(pb_state* s) {
     pb_model* m = s->m; pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg;
     s->fused = 0;
     const bool on = !(getenv("PYRE_B200_FUSED") && atoi(getenv("PYRE_B200_FUSED")) == 0);   // read when a state takes its first step
-    if (!on || s->batch != 1 || s->sharded || m->ep_world != 1 || c.hc != 0) return PB_OK;
+    if (!on || s->batch != 1 || s->sharded || m->ep_world != 1 || c.hc != 0 || m->n_ple > 0) return PB_OK;
     const int d = c.d, ff = c.ff_exp, w_lin = c.lin_nv * c.lin_dv, w_att = c.n_head * c.hd;
     auto pow2 = [](int v) { return v > 0 && (v & (v - 1)) == 0; };
     if (d % 256 || d > 2048 || !pow2(d / 64) || ff % 512 || !pow2(ff / 64) || ff / 64 > 32 || c.ff_sh != ff) return PB_OK;
@@ -974,6 +1034,43 @@ static int run_step_fused(pb_state* s) {
 }
 
 // ---- hyper-connection residual (hc >= 1): forward_inner :2087-2157 with hc_mix / hc_combine around every block ----
+// ---- per-layer n-gram embeddings (ple_rows :1390-1407, ple :1409-1434) ----
+// y[t][ldy] = W . x[t][ldx] for a matrix of any type, 16 columns a launch
+static int gemv_any(pb_ctx* ctx, pb_qmat* q, const float* x, int64_t ldx, int t, float* y, int64_t ldy) {
+    for (int t0 = 0; t0 < t; t0 += 16) {
+        PbGemvArgs g; memset(&g, 0, sizeof g);
+        g.w = q->data; g.wr = q->rdata; g.type = q->type; g.rows = q->rows; g.cols = (int)q->cols;
+        g.x = x + (int64_t)t0 * ldx; g.ldx = ldx; g.t = t - t0 < 16 ? t - t0 : 16; g.y = y + (int64_t)t0 * ldy; g.ldy = ldy;
+        PB_TRY(pb_launch_gemv(ctx, g));
+    }
+    return PB_OK;
+}
+// the table rows of the t rows in flight (ids in s->ids; positions s->wpos inside a window, else one sequence per row at s->pos)
+static int ple_gather(pb_state* s, int t) {
+    pb_model* m = s->m; pb_ctx* ctx = m->ctx;
+    if (m->n_ple == 0) return PB_OK;
+    const int window = s->win_t > 0;
+    PB_TRY(pb_launch_ple_rows(ctx, m->ple, s->ids, window ? s->wpos : s->pos, t, window, s->tok_hist, m->cfg.max_ctx, s->ple_base, s->ple_rows));
+    pb_qmat* tab = M(m, -1, PB_R_PLE_TAB);
+    PB_TRY(pb_launch_embed(ctx, tab->type, tab->data, tab->rows, m->ple_dim, s->ple_rows, t * m->ple.nh, s->ple_emb, m->ple_dim));
+    ctx->pdl_chain = false;
+    return PB_OK;
+}
+// layer il's injection into the residual rows x [t][w]
+static int run_ple(pb_state* s, int il, float* x, int t) {
+    pb_model* m = s->m; pb_ctx* ctx = m->ctx; const pb_cfg& c = m->cfg;
+    const int pi = m->ple_idx[il];
+    if (pi < 0) return PB_OK;
+    const int streams = c.hc > 0 ? c.hc : 1, w = streams * c.d, window = s->win_t > 0;
+    const int64_t ein = (int64_t)m->ple.nh * m->ple_dim;
+    const int64_t* posv = window ? s->wpos : s->pos;
+    PB_TRY(gemv_any(ctx, M(m, il, PB_R_PLE_KEY), s->ple_emb, ein, t, s->ple_key, w));
+    PB_TRY(gemv_any(ctx, M(m, il, PB_R_PLE_VALUE), s->ple_emb, ein, t, s->ple_val, c.d));
+    PB_TRY(pb_launch_ple_gate(ctx, s->ple_key, w, s->ple_val, c.d, x, w, V(m, il, PB_R_PLE_NORM_KEY), V(m, il, PB_R_PLE_NORM_QUERY), V(m, il, PB_R_PLE_NORM_CONV),
+                              s->ple_gated, s->ple_ring[(size_t)pi], s->ple_R, posv, t, window, c.d, streams, c.eps));
+    return pb_launch_ple_conv(ctx, s->ple_gated, s->ple_ring[(size_t)pi], s->ple_R, V(m, il, PB_R_PLE_CONV), m->ple_conv_k, m->ple.ngram, posv, t, window, s->ple_base, x, w, w);
+}
+
 static void hc_params(pb_state* s, int il, int r_norm, int r_down, int r_up, int r_inj, PbHcParams& h) {
     pb_model* m = s->m; const pb_cfg& c = m->cfg;
     memset(&h, 0, sizeof h);
@@ -987,8 +1084,10 @@ static int run_layers_hc(pb_state* s, int t, int h0, int hn) {
     pb_qmat* embd = M(m, -1, PB_R_TOKEN_EMBD);
     PB_TRY(pb_launch_embed(ctx, embd->type, embd->data, embd->rows, c.d, s->ids, t, s->yout, c.d));
     PB_TRY(pb_launch_hc_spread(ctx, s->yout, s->x, t, c.d, c.hc));
+    PB_TRY(ple_gather(s, t));
     PbHcParams h;
     for (int il = 0; il < c.n_layers; il++) {
+        PB_TRY(run_ple(s, il, s->x, t));
         hc_params(s, il, PB_R_HCA_NORM, PB_R_HCA_DOWN, PB_R_HCA_UP, PB_R_HCA_INJECT, h);
         PB_TRY(pb_launch_hc_mix(ctx, h, s->x, t, s->hmix));
         if (m->kind[il]) PB_TRY(run_attn(s, il, s->hmix, nullptr, s->yout, c.d, 0));
@@ -1013,7 +1112,9 @@ static int run_step(pb_state* s) {
     if (c.hc > 0) { PB_TRY(run_layers_hc(s, B, 0, B)); if (s->mtp) PB_TRY(pb_launch_mtp_keep(ctx, s->x, (int64_t)c.hc * c.d, s->pos, 1, s->mtp->ring, s->mtp->ring_cap, c.hc * c.d)); }
     else {
         PB_TRY(pb_launch_embed(ctx, embd->type, embd->data, embd->rows, c.d, s->ids, B, s->x, c.d));
+        PB_TRY(ple_gather(s, B));
         for (int il = 0; il < c.n_layers; il++) {
+            PB_TRY(run_ple(s, il, s->x, B));
             if (m->kind[il]) PB_TRY(run_attn(s, il, s->x, V(m, il, PB_R_ATTN_NORM), s->x, c.d, 1));
             else PB_TRY(run_lin(s, il, s->x, V(m, il, PB_R_ATTN_NORM), s->x, c.d, 1));
             PB_TRY(run_moe(s, il, s->x, V(m, il, PB_R_FFN_NORM), B, s->x, c.d, 1));
@@ -1043,7 +1144,9 @@ static int run_window(pb_state* s, int t, bool ckpt, bool all_logits) {
     if (c.hc > 0) { PB_TRY(run_layers_hc(s, t, all_logits ? 0 : t - 1, all_logits ? t : 1)); if (s->mtp) PB_TRY(pb_launch_mtp_keep(ctx, s->x, (int64_t)c.hc * c.d, s->wpos, t, s->mtp->ring, s->mtp->ring_cap, c.hc * c.d)); }
     else {
         PB_TRY(pb_launch_embed(ctx, embd->type, embd->data, embd->rows, c.d, s->ids, t, s->x, c.d));
+        PB_TRY(ple_gather(s, t));
         for (int il = 0; il < c.n_layers; il++) {
+            PB_TRY(run_ple(s, il, s->x, t));
             if (m->kind[il]) PB_TRY(run_attn(s, il, s->x, V(m, il, PB_R_ATTN_NORM), s->x, c.d, 1));
             else PB_TRY(run_lin(s, il, s->x, V(m, il, PB_R_ATTN_NORM), s->x, c.d, 1));
             PB_TRY(run_moe(s, il, s->x, V(m, il, PB_R_FFN_NORM), t, s->x, c.d, 1));
@@ -1459,6 +1562,14 @@ static const uint64_t kSnapMagic = 0x3150414e53425050ull;   // "PPBSNAP1"
 // q4[ai * B + b] = packed boundary of sequence b in attention layer ai.  The boundary is what the device holds
 // (after a rollback it is ahead of the value the current length alone would give), so a snapshot reads it back
 // and stores it; a restore takes it from the snapshot.
+// n-gram embeddings in a snapshot: the first position with a history, then per sequence the last ngram - 1 ids and per PLE layer the
+// normalized rows of the last (conv_k - 1) * ngram positions (what a later token can still read), newest first
+static size_t ple_snap_bytes(const pb_state* s) {
+    const pb_model* m = s->m;
+    if (m->n_ple == 0) return 0;
+    const size_t w = (size_t)m->cfg.d * (m->cfg.hc > 0 ? m->cfg.hc : 1), hl = (size_t)(m->ple_conv_k - 1) * m->ple.ngram;
+    return 8 + (size_t)s->batch * (m->ple.ngram - 1) * 4 + (size_t)m->n_ple * s->batch * hl * w * 4;
+}
 static size_t snap_size(const pb_state* s, const std::vector<int64_t>& q4) {
     const pb_cfg& c = s->m->cfg; const int B = s->batch;
     const int64_t len = s->pos_host;
@@ -1469,7 +1580,7 @@ static size_t snap_size(const pb_state* s, const std::vector<int64_t>& q4) {
             n += (size_t)c.n_kv * (8 + 2 * ((size_t)q4n * (c.hd / 8) * 4 + (size_t)q4n * (c.hd / 32) * 4) + 2 * (size_t)(len - q4n) * c.hd * 4);
         }
     if (s->m->qsa) n += (size_t)s->m->n_attn * B * (size_t)len * s->m->idx_hd * 4;   // raw index keys; the pooled block keys are rebuilt
-    return n;
+    return n + ple_snap_bytes(s);
 }
 static int snap_read_q4(pb_state* s, std::vector<int64_t>& q4) {
     pb_ctx* ctx = s->m->ctx; const int B = s->batch;
@@ -1515,6 +1626,29 @@ static int snap_io(pb_state* s, uint8_t* buf, bool save, const std::vector<int64
     if (s->m->qsa)
         for (int ai = 0; ai < s->m->n_attn; ai++)
             for (int b = 0; b < B; b++) PB_TRY(io(s->kv[ai].ik + (size_t)b * c.max_ctx * s->m->idx_hd, (size_t)len * s->m->idx_hd * 4));
+    if (s->m->n_ple > 0) {
+        const pb_model* m = s->m;
+        const size_t w = (size_t)c.d * (c.hc > 0 ? c.hc : 1); const int hl = (m->ple_conv_k - 1) * m->ple.ngram;
+        if (save) memcpy(p, &s->ple_base_host, 8);
+        else {
+            int64_t base; memcpy(&base, p, 8);
+            if (base < 0 || base > len) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_restore: corrupt snapshot (history base %lld at position %lld)", (long long)base, (long long)len);
+            std::vector<int64_t> bv((size_t)B, base);
+            PB_CUDA(ctx, cudaMemcpy(s->ple_base, bv.data(), bv.size() * 8, cudaMemcpyHostToDevice));
+            s->ple_base_host = base;
+        }
+        p += 8;
+        auto io_or_skip = [&](void* dev, size_t bytes, bool have) -> int {
+            if (have) return io(dev, bytes);
+            if (save) memset(p, 0, bytes);
+            p += bytes; return PB_OK;
+        };
+        for (int b = 0; b < B; b++)
+            for (int j = 1; j < m->ple.ngram; j++) { const int64_t q = len - j; PB_TRY(io_or_skip(s->tok_hist + (size_t)b * c.max_ctx + (q >= 0 ? q : 0), 4, q >= 0)); }
+        for (int pi = 0; pi < m->n_ple; pi++)
+            for (int b = 0; b < B; b++)
+                for (int j = 1; j <= hl; j++) { const int64_t q = len - j; PB_TRY(io_or_skip(s->ple_ring[(size_t)pi] + ((size_t)b * s->ple_R + (size_t)((q >= 0 ? q : 0) % s->ple_R)) * w, w * 4, q >= 0)); }
+    }
     return PB_OK;
 }
 
@@ -1561,6 +1695,7 @@ int pb_state_restore(pb_state* s, const void* buf_host, size_t nbytes) {
                     off += 8 + 2 * ((size_t)q * (c.hd / 8) * 4 + (size_t)q * (c.hd / 32) * 4) + 2 * (size_t)(h.pos - q) * c.hd * 4;
                 }
         if (s->m->qsa) off += (size_t)s->m->n_attn * B * (size_t)h.pos * s->m->idx_hd * 4;
+        off += ple_snap_bytes(s);
         if (off != nbytes) PB_FAIL(ctx, PB_ERR_ARG, "pb_state_restore: size mismatch");
     }
     // position first (a fresh boundary of 0 so that any position is accepted), then the sections

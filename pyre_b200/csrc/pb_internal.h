@@ -149,6 +149,13 @@ int pb_launch_synth_normal(pb_ctx* ctx, float* out, int64_t n, uint64_t seed, ui
 int pb_launch_synth_normal_at(pb_ctx* ctx, float* out, int64_t n, uint64_t seed, uint64_t tid, int64_t i0, float sigma);
 
 // pb_gemv.cu
+// n-gram embedding hash (Cfg ple_*, src/model/qwen4exp_gguf.rs:477-480): nh = (ngram - 1) * per_gram heads
+struct PbPleHash { int ngram, per_gram, nh; uint32_t eos; uint64_t mult[8], off[32], vocab[32]; };
+int pb_launch_ple_rows(pb_ctx* ctx, const PbPleHash& hp, const uint32_t* ids, const int64_t* posv, int t, int window, uint32_t* tok_hist, int64_t max_ctx, const int64_t* base, uint32_t* rows_out);
+int pb_launch_ple_gate(pb_ctx* ctx, const float* key, int64_t ldk, const float* val, int64_t ldv, const float* x, int64_t ldx, const float* nk, const float* nq, const float* nc,
+                       float* gated, float* ring, int R, const int64_t* posv, int t, int window, int d, int streams, float eps);
+int pb_launch_ple_conv(pb_ctx* ctx, const float* gated, const float* ring, int R, const float* conv, int K, int dil, const int64_t* posv, int t, int window, const int64_t* base, float* x, int64_t ldx, int w);
+
 struct PbGemvArgs {
     const uint8_t* w;   // first row of the matrix (16-byte aligned)
     const uint8_t* wr = nullptr;   // the same rows in the re-coded form (pb_qmat::rdata), or null

@@ -163,8 +163,6 @@ def load_model(ctx: Ctx, path, max_ctx: int = 4096, kv_bits: int = 4, kv_recent:
             raise GgufError(f"gguf key {a}.{s}")
         return v
 
-    if g.meta.get(f"{a}.ple.layers"):
-        raise GgufError("per-layer-input embeddings (ple.layers) are not part of the built path")
     cfg = make_cfg(n_layers=int(k("block_count")), d=int(k("embedding_length")), hc=int(k("hyper_connection.count")), hc_lr=int(k("hyper_connection.low_rank")),
                    n_head=int(k("attention.head_count")), n_kv=int(k("attention.head_count_kv")), hd=int(k("attention.key_length")), n_rot=int(k("rope.dimension_count")),
                    rope_base=float(k("rope.freq_base")), eps=float(k("attention.layer_norm_rms_epsilon")), n_exp=int(k("expert_count")), top_k=int(k("expert_used_count")),
@@ -180,6 +178,12 @@ def load_model(ctx: Ctx, path, max_ctx: int = 4096, kv_bits: int = 4, kv_recent:
         ratios = g.meta.get(f"{a}.attention.compress_ratios") or [4]
         m.set_indexer(int(k("attention.indexer.top_k", 2048)), max(1, max(int(r) for r in ratios)), idx_nh, int(k("attention.indexer.key_length", 128)))
     m.set_ctx_train(int(g.meta.get(f"{a}.context_length", 0)))   # a longer max_ctx is YaRN-scaled (Model::load :490-517)
+    # per-layer n-gram embeddings (Cfg ple_* :468, 477-480): the layers named by ple.layers hold the tensors
+    ple_layers = [int(v) for v in (g.meta.get(f"{a}.ple.layers") or [])]
+    if ple_layers:
+        u64 = lambda key: [int(v) for v in (g.meta.get(f"{a}.{key}") or [])]
+        m.set_ple(int(k("ple.ngram_size")), int(k("ple.heads_per_ngram")), int(k("ple.conv_kernel")), int(k("ple.eos_token_id", 0)), int(k("embedding_length_per_layer_input")),
+                  u64("ple.layer_multipliers"), u64("ple.head_offsets"), u64("ple.head_vocab_sizes"))
 
     def mat(layer, role, name, expert_rows=False):
         ty, rows, cols, raw = g.mat(name)
@@ -210,6 +214,8 @@ def load_model(ctx: Ctx, path, max_ctx: int = 4096, kv_bits: int = 4, kv_recent:
             (vec if suffix == "norm" else mat)(layer, f"{role}_{r}", name)
 
     mat(-1, "TOKEN_EMBD", "token_embd.weight")
+    if ple_layers:
+        mat(-1, "PLE_TAB", "per_layer_token_embd.weight")
     if g.has("output.weight"):
         mat(-1, "OUTPUT", "output.weight")
     if cfg.hc > 0:
@@ -218,6 +224,11 @@ def load_model(ctx: Ctx, path, max_ctx: int = 4096, kv_bits: int = 4, kv_recent:
         vec(-1, "OUT_NORM", "output_norm.weight")
     for il in range(cfg.n_layers):
         p = f"blk.{il}"
+        if il in ple_layers:                       # Ple :505
+            mat(il, "PLE_KEY", f"{p}.ple_key.weight")
+            mat(il, "PLE_VALUE", f"{p}.ple_value.weight")
+            for role, n in (("PLE_NORM_KEY", "ple_norm_key"), ("PLE_NORM_QUERY", "ple_norm_query"), ("PLE_NORM_CONV", "ple_norm_conv"), ("PLE_CONV", "ple_conv1d")):
+                vec(il, role, f"{p}.{n}.weight")
         if cfg.hc > 0:
             hyper(il, f"{p}.hc_attn", "HCA", True)
             hyper(il, f"{p}.hc_ffn", "HCF", True)

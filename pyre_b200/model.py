@@ -40,6 +40,16 @@ class Model:
         self.ctx.check(lib().pb_model_set_indexer(self.h, C.c_int(budget), C.c_int(ratio), C.c_int(n_head), C.c_int(head_dim)))
         self.indexer = (budget, ratio, n_head, head_dim)
 
+    def set_ple(self, ngram: int, per_gram: int, conv_k: int, eos: int, dim: int, mult, off, vocab):
+        """Per-layer n-gram embeddings (the metadata keys `ple.*` of a qwen4exp file): layers that hold PLE_KEY inject a gated
+        projection of hashed table rows at their start (before finalize)."""
+        a = lambda v: np.ascontiguousarray(v, dtype=np.uint64)
+        mult, off, vocab = a(mult), a(off), a(vocab)
+        if mult.size != ngram or off.size != (ngram - 1) * per_gram or vocab.size != off.size:
+            raise ValueError("set_ple: multipliers[ngram], offsets / vocabulary sizes [(ngram - 1) * per_gram]")
+        self.ctx.check(lib().pb_model_set_ple(self.h, C.c_int(ngram), C.c_int(per_gram), C.c_int(conv_k), C.c_uint32(eos), C.c_int(dim),
+                                              mult.ctypes.data_as(C.c_void_p), off.ctypes.data_as(C.c_void_p), vocab.ctypes.data_as(C.c_void_p)))
+
     def set_ctx_train(self, ctx_train: int):
         """Trained context; a larger cfg.max_ctx is YaRN-scaled (before finalize)."""
         self.ctx.check(lib().pb_model_set_ctx_train(self.h, C.c_int(ctx_train)))

@@ -25,9 +25,20 @@ def is_full(cfg: Cfg, il: int) -> bool:
     return cfg.full_every > 0 and (il + 1) % cfg.full_every == 0
 
 
-def model_spec(cfg: Cfg, seed: int = 0, qtype: int = IQ3_S, indexer=None):
+def ple_geometry(layers, ngram: int = 3, per_gram: int = 2, conv_k: int = 4, eos: int = 2, dim: int = 256, head_vocab: int = 997):
+    """Geometry of per-layer n-gram embeddings for a synthetic model (the reference's metadata keys `ple.*`,
+    src/model/qwen4exp_gguf.rs:468-480): odd 64-bit multipliers, heads of slightly different vocabulary sizes laid end to end."""
+    nh = (ngram - 1) * per_gram
+    vocab = [head_vocab + 2 * i for i in range(nh)]
+    off = [int(sum(vocab[:i])) for i in range(nh)]
+    mult = [(0x9E3779B97F4A7C15 * (2 * i + 1) + 0x632BE59BD9B4E019 * i) % (1 << 64) | 1 for i in range(ngram)]
+    return dict(layers=list(layers), ngram=ngram, per_gram=per_gram, conv_k=conv_k, eos=eos, dim=dim, mult=mult, off=off, vocab=vocab)
+
+
+def model_spec(cfg: Cfg, seed: int = 0, qtype: int = IQ3_S, indexer=None, ple=None):
     """List of ('mat', layer, role, type, rows, cols, tid) and ('vec', layer, role, array).  indexer = (budget, ratio, heads,
-    head dim) adds the QSA indexer tensors to every attention layer."""
+    head dim) adds the QSA indexer tensors to every attention layer; ple = ple_geometry(...) adds the n-gram embedding table and
+    the tensors of the layers it names."""
     rng = np.random.default_rng(seed)
     d, hd = cfg.d, cfg.hd
     ch = 2 * cfg.lin_nk * cfg.lin_dk + cfg.lin_nv * cfg.lin_dv
@@ -58,7 +69,17 @@ def model_spec(cfg: Cfg, seed: int = 0, qtype: int = IQ3_S, indexer=None):
         hyper(-1, "OUT_HC", inject=False)
     else:
         vec(-1, "OUT_NORM", gamma(d))
+    if ple:
+        mat(-1, "PLE_TAB", int(sum(ple["vocab"])), ple["dim"])
     for il in range(cfg.n_layers):
+        if ple and il in ple["layers"]:
+            w, ein = max(hc, 1) * d, (ple["ngram"] - 1) * ple["per_gram"] * ple["dim"]
+            mat(il, "PLE_KEY", w, ein)
+            mat(il, "PLE_VALUE", d, ein)
+            vec(il, "PLE_NORM_KEY", gamma(w))
+            vec(il, "PLE_NORM_QUERY", gamma(w))
+            vec(il, "PLE_NORM_CONV", gamma(w))
+            vec(il, "PLE_CONV", 0.5 * rng.standard_normal((w, ple["conv_k"])))
         if hc > 0:
             hyper(il, "HCA")
             hyper(il, "HCF")
@@ -99,8 +120,10 @@ def model_spec(cfg: Cfg, seed: int = 0, qtype: int = IQ3_S, indexer=None):
     return spec
 
 
-def build_model(ctx: Ctx, cfg: Cfg, spec, seed: int = 0, ep_rank: int = 0, ep_world: int = 1, ctx_train: int = 0, indexer=None) -> Model:
+def build_model(ctx: Ctx, cfg: Cfg, spec, seed: int = 0, ep_rank: int = 0, ep_world: int = 1, ctx_train: int = 0, indexer=None, ple=None) -> Model:
     m = Model(ctx, cfg)
+    if ple:
+        m.set_ple(ple["ngram"], ple["per_gram"], ple["conv_k"], ple["eos"], ple["dim"], ple["mult"], ple["off"], ple["vocab"])
     if ctx_train:
         m.set_ctx_train(ctx_train)
     if indexer:

@@ -12,8 +12,10 @@ def oracle_cfg(cfg):
     return oc
 
 
-def oracle_model(cfg, spec, seed=0, ctx_train=0, indexer=None):
+def oracle_model(cfg, spec, seed=0, ctx_train=0, indexer=None, ple=None):
     om = oracle.Model(oracle_cfg(cfg))
+    if ple:
+        om.set_ple(ple["ngram"], ple["per_gram"], ple["conv_k"], ple["eos"], ple["dim"], ple["mult"], ple["off"], ple["vocab"])
     if ctx_train:
         om.set_ctx_train(ctx_train)
     if indexer:
@@ -51,6 +53,8 @@ GGUF_NAMES = {
     "LIN_A": "ssm_a", "LIN_DT": "ssm_dt.bias", "LIN_CONV": "ssm_conv1d.weight", "LIN_NORM": "ssm_norm.weight",
     "ROUTER": "ffn_gate_inp.weight", "EXP_GATE": "ffn_gate_exps.weight", "EXP_UP": "ffn_up_exps.weight", "EXP_DOWN": "ffn_down_exps.weight",
     "SH_GATE_INP": "ffn_gate_inp_shexp.weight", "SH_GATE": "ffn_gate_shexp.weight", "SH_UP": "ffn_up_shexp.weight", "SH_DOWN": "ffn_down_shexp.weight",
+    "PLE_TAB": "per_layer_token_embd.weight", "PLE_KEY": "ple_key.weight", "PLE_VALUE": "ple_value.weight", "PLE_NORM_KEY": "ple_norm_key.weight",
+    "PLE_NORM_QUERY": "ple_norm_query.weight", "PLE_NORM_CONV": "ple_norm_conv.weight", "PLE_CONV": "ple_conv1d.weight",
     "HCA_NORM": "hc_attn_norm.weight", "HCA_DOWN": "hc_attn_down.weight", "HCA_UP": "hc_attn_up.weight", "HCA_INJECT": "hc_attn_inject.weight",
     "HCF_NORM": "hc_ffn_norm.weight", "HCF_DOWN": "hc_ffn_down.weight", "HCF_UP": "hc_ffn_up.weight", "HCF_INJECT": "hc_ffn_inject.weight",
     "OUT_HC_NORM": "output_hc_norm.weight", "OUT_HC_DOWN": "output_hc_down.weight", "OUT_HC_UP": "output_hc_up.weight",
@@ -58,7 +62,7 @@ GGUF_NAMES = {
 }
 
 
-def write_synth_gguf(path, cfg, spec, seed, split_after=None, indexer=None, ctx_train=0):
+def write_synth_gguf(path, cfg, spec, seed, split_after=None, indexer=None, ctx_train=0, ple=None):
     """A synthetic model (pyre_b200.synth.model_spec) as a qwen4exp GGUF file written with gguf-py: metadata keys and tensor
     names as Model::load reads them, quantized tensors as their raw block bytes (the oracle's generator)."""
     import gguf
@@ -77,6 +81,13 @@ def write_synth_gguf(path, cfg, spec, seed, split_after=None, indexer=None, ctx_
         w.add_array(f"{a}.attention.compress_ratios", [1, ratio])
     if ctx_train:
         w.add_uint32(f"{a}.context_length", ctx_train)
+    if ple:
+        w.add_array(f"{a}.ple.layers", [int(v) for v in ple["layers"]])
+        for key, name in (("ngram", "ple.ngram_size"), ("per_gram", "ple.heads_per_ngram"), ("conv_k", "ple.conv_kernel"), ("eos", "ple.eos_token_id"), ("dim", "embedding_length_per_layer_input")):
+            w.add_uint32(f"{a}.{name}", int(ple[key]))
+        # gguf-py stores a Python int array as int32 unless told otherwise; the multipliers need all 64 bits
+        for key, name in (("mult", "ple.layer_multipliers"), ("off", "ple.head_offsets"), ("vocab", "ple.head_vocab_sizes")):
+            w.add_key_value(f"{a}.{name}", [int(v) for v in ple[key]], gguf.GGUFValueType.ARRAY, sub_type=gguf.GGUFValueType.UINT64)
     w.add_float32(f"{a}.rope.freq_base", float(cfg.rope_base))
     w.add_float32(f"{a}.attention.layer_norm_rms_epsilon", float(cfg.eps))
     w.add_string("general.name", "synthetic")
@@ -88,6 +99,8 @@ def write_synth_gguf(path, cfg, spec, seed, split_after=None, indexer=None, ctx_
             arr = np.ascontiguousarray(item[3], dtype=np.float32)
             if role == "LIN_CONV":
                 arr = arr.reshape(-1, cfg.conv_k)
+            if role == "PLE_CONV":
+                arr = arr.reshape(-1, ple["conv_k"])
             w.add_tensor(name, arr)
         else:
             _, _, _, t, rows, cols, tid = item

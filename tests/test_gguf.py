@@ -156,6 +156,47 @@ def test_loaded_model_with_indexer_and_trained_context(ctx, tmp_path):
     m.destroy(); ref.destroy(); plain.destroy()
 
 
+def test_ple_keys_and_tensors_are_read_back(tmp_path):
+    """The n-gram embedding keys (64-bit multipliers among them) and tensor names of a written file, through the reader."""
+    pytest.importorskip("gguf")
+    cfg = small_cfg(pb, n_layers=4, max_ctx=64, hc=1, hc_lr=32)
+    ple = synth.ple_geometry([1, 3])
+    spec = synth.model_spec(cfg, 47, ple=ple)
+    p = tmp_path / "ple.gguf"
+    write_synth_gguf(p, cfg, spec, 47, ple=ple)
+    g = Gguf.open(p)
+    assert [int(v) for v in g.meta["qwen4exp.ple.layers"]] == [1, 3]
+    assert [int(v) for v in g.meta["qwen4exp.ple.layer_multipliers"]] == ple["mult"] and max(ple["mult"]) > 1 << 63
+    assert [int(v) for v in g.meta["qwen4exp.ple.head_vocab_sizes"]] == ple["vocab"]
+    assert int(g.meta["qwen4exp.embedding_length_per_layer_input"]) == 256
+    ty, rows, cols, raw = g.mat("per_layer_token_embd.weight")
+    assert (rows, cols) == (sum(ple["vocab"]), 256)
+    assert g.has("blk.1.ple_key.weight") and g.has("blk.3.ple_conv1d.weight") and not g.has("blk.0.ple_key.weight")
+    assert g.mat("blk.1.ple_key.weight")[1:3] == (cfg.d, 4 * 256)
+    g.close()
+
+
+@pytest.mark.gpu
+def test_loaded_model_with_ngram_embeddings(ctx, tmp_path):
+    """A file with per-layer n-gram embeddings (ple.* keys, per_layer_token_embd and blk.N.ple_* tensors) loads into a model that decodes
+    like the same weights bound directly, and unlike the model without them."""
+    pytest.importorskip("gguf")
+    cfg = small_cfg(pb, n_layers=8, kv_bits=4, kv_recent=64, max_ctx=256, hc=2, hc_lr=32)
+    ple = synth.ple_geometry([2, 5])
+    spec = synth.model_spec(cfg, 48, ple=ple)
+    p = tmp_path / "ple.gguf"
+    write_synth_gguf(p, cfg, spec, 48, ple=ple)
+    m = load_model(ctx, p, max_ctx=256, kv_bits=4, kv_recent=64)
+    ref = synth.build_model(ctx, cfg, spec, 48, ple=ple)
+    plain = synth.build_model(ctx, cfg, [it for it in spec if not it[2].startswith("PLE_")], 48)
+    a, b, c = m.new_state(1), ref.new_state(1), plain.new_state(1)
+    ta, tb, tc = (s.decode_greedy([17], 40)[0].tolist() for s in (a, b, c))
+    assert ta == tb and ta != tc
+    for s in (a, b, c):
+        s.destroy()
+    m.destroy(); ref.destroy(); plain.destroy()
+
+
 @pytest.mark.gpu
 def test_mixed_type_file_decodes_like_the_oracle(ctx, tmp_path):
     """A file whose tensors mix the block formats the way the reference's own checkpoint does (routed and shared gate / up in

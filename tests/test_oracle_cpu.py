@@ -279,3 +279,28 @@ def test_qsa_selection_and_sparse_attention_properties():
     assert np.array_equal(dense, full)
     part = oracle.attn_core(cfg, qf, kf, vf, qn, kn, inv, kc.copy(), vc.copy(), n - 1, ps=np.arange(1, n))
     assert rel_err(part, dense) > 1e-4
+
+
+def test_ple_hash_rows_follow_the_reference_rule():
+    """ple_rows (qwen4exp_gguf.rs:1394-1403) in Python integers: contexts cut at a missing or end-of-sequence predecessor, n-gram size n
+    mixes the first n ids times their multipliers by xor (wrapping 64-bit), each head takes the mix modulo its vocabulary plus its offset."""
+    from pyre_b200.synth import ple_geometry
+    g = ple_geometry([0], ngram=4, per_gram=2, eos=2)
+    om = oracle.Model(oracle.make_cfg(n_layers=1, d=256, vocab=64, max_ctx=16))
+    om.set_ple(g["ngram"], g["per_gram"], g["conv_k"], g["eos"], g["dim"], g["mult"], g["off"], g["vocab"])
+    M64 = (1 << 64) - 1
+    for ctx in ([5, 9, 11, 13], [5, -1, 11, 13], [5, 9, 2, 13], [5, 2, 7, 8], [2, 9, 11, 13], [(1 << 32) - 1, 70000, 3, 4]):
+        c, cut = [ctx[0]], False
+        for s in range(1, 4):
+            none = cut or ctx[s] < 0
+            cut = cut or none or ctx[s] == 2
+            c.append(2 if cut else ctx[s])
+        want = []
+        for n in range(2, 5):
+            mixed = (c[0] * g["mult"][0]) & M64
+            for j in range(1, n):
+                mixed ^= (c[j] * g["mult"][j]) & M64
+            for gi in range(2):
+                h = (n - 2) * 2 + gi
+                want.append(mixed % g["vocab"][h] + g["off"][h])
+        assert om.ple_hash(ctx).tolist() == want, ctx
