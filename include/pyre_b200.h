@@ -43,7 +43,7 @@ typedef struct pb_model pb_model;
 typedef struct pb_state pb_state;
 
 /* ggml type ids accepted for matrices (QType::from_id, src/model/gguf_q.rs:23-29) */
-enum { PB_TYPE_F32 = 0, PB_TYPE_F16 = 1, PB_TYPE_Q8_0 = 8, PB_TYPE_Q4_K = 12, PB_TYPE_Q6_K = 14, PB_TYPE_IQ2_XXS = 16, PB_TYPE_IQ2_XS = 17, PB_TYPE_IQ3_XXS = 18,
+enum { PB_TYPE_F32 = 0, PB_TYPE_F16 = 1, PB_TYPE_Q4_0 = 2, PB_TYPE_Q5_0 = 6, PB_TYPE_Q8_0 = 8, PB_TYPE_Q3_K = 11, PB_TYPE_Q4_K = 12, PB_TYPE_Q5_K = 13, PB_TYPE_Q6_K = 14, PB_TYPE_IQ2_XXS = 16, PB_TYPE_IQ2_XS = 17, PB_TYPE_IQ3_XXS = 18,
        PB_TYPE_IQ4_NL = 20, PB_TYPE_IQ3_S = 21, PB_TYPE_IQ2_S = 22, PB_TYPE_IQ4_XS = 23, PB_TYPE_IQ1_M = 29, PB_TYPE_BF16 = 30, PB_TYPE_Q2_0 = 42 };
 
 /* ---------------------------------------------------------------- context */

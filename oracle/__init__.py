@@ -18,9 +18,10 @@ _SO = _HERE / "_ref" / "libpyre_oracle.so"
 F32, F16, Q8_0, Q4_K, IQ2_XS, IQ3_S, BF16 = 0, 1, 8, 12, 17, 21, 30
 IQ3_XXS, IQ4_NL, IQ2_S, IQ4_XS = 18, 20, 22, 23
 Q6_K, IQ2_XXS, Q2_0, IQ1_M = 14, 16, 42, 29
+Q4_0, Q5_0, Q3_K, Q5_K = 2, 6, 11, 13
 QUANT_TYPES = {"Q8_0": Q8_0, "Q4_K": Q4_K, "IQ2_XS": IQ2_XS, "IQ3_S": IQ3_S}
 # formats of the GGUF loader beyond the four of the hot path: dequantization only (no synthetic generator)
-EXTRA_TYPES = {"IQ3_XXS": IQ3_XXS, "IQ2_S": IQ2_S, "IQ4_NL": IQ4_NL, "IQ4_XS": IQ4_XS, "Q2_0": Q2_0, "IQ2_XXS": IQ2_XXS, "Q6_K": Q6_K, "IQ1_M": IQ1_M}
+EXTRA_TYPES = {"IQ3_XXS": IQ3_XXS, "IQ2_S": IQ2_S, "IQ4_NL": IQ4_NL, "IQ4_XS": IQ4_XS, "Q2_0": Q2_0, "IQ2_XXS": IQ2_XXS, "Q6_K": Q6_K, "IQ1_M": IQ1_M, "Q4_0": Q4_0, "Q5_0": Q5_0, "Q3_K": Q3_K, "Q5_K": Q5_K}
 
 ROLES = [
     "TOKEN_EMBD", "OUTPUT", "OUT_NORM", "ATTN_NORM", "FFN_NORM",

@@ -97,6 +97,10 @@ int orc_type_geom(int type, int* el, int* by) {  /* gguf_q.rs:33-41 */
         case ORC_IQ2_XXS: e = 256; b = 66; break;
         case ORC_Q6_K: e = 256; b = 210; break;
         case ORC_IQ1_M: e = 256; b = 56; break;
+        case ORC_Q4_0: e = 32; b = 18; break;
+        case ORC_Q5_0: e = 32; b = 22; break;
+        case ORC_Q3_K: e = 256; b = 110; break;
+        case ORC_Q5_K: e = 256; b = 176; break;
         default: return -1;
     }
     if (el) *el = e;
@@ -183,6 +187,45 @@ int orc_dequant(int type, const uint8_t* x, int64_t n, float* y) {  /* gguf_q.rs
                     yy[l + 64] = d * (float)sc[is + 4] * (float)q3; yy[l + 96] = d * (float)sc[is + 6] * (float)q4; }
                 yy += 128; ql += 64; qh += 32; sc += 8;
             }
+        }
+        break;
+    case ORC_Q4_0:                                                                             /* :74-75 */
+        for (int64_t i = 0; i < nb; i++) {
+            const uint8_t* b = x + i * bs; float d = h2f(rd16(b)); float* yy = y + i * 32;
+            for (int j = 0; j < 16; j++) { yy[j] = (float)((int)(b[2 + j] & 0xF) - 8) * d; yy[j + 16] = (float)((int)(b[2 + j] >> 4) - 8) * d; }
+        }
+        break;
+    case ORC_Q5_0:                                                                             /* :76-78 */
+        for (int64_t i = 0; i < nb; i++) {
+            const uint8_t* b = x + i * bs; float d = h2f(rd16(b)); uint32_t qh = (uint32_t)b[2] | ((uint32_t)b[3] << 8) | ((uint32_t)b[4] << 16) | ((uint32_t)b[5] << 24); const uint8_t* qs = b + 6; float* yy = y + i * 32;
+            for (int j = 0; j < 16; j++) { uint32_t h0 = ((qh >> j) << 4) & 0x10, h1 = (qh >> (j + 12)) & 0x10;
+                yy[j] = (float)((int)((qs[j] & 0xF) | h0) - 16) * d; yy[j + 16] = (float)((int)((qs[j] >> 4) | h1) - 16) * d; }
+        }
+        break;
+    case ORC_Q3_K:                                                                             /* :90-102: [hmask 32][qs 64][scales 12][d f16] */
+        for (int64_t i = 0; i < nb; i++) {
+            const uint8_t* b = x + i * bs; const uint8_t* hm = b; const uint8_t* q = b + 32; const uint8_t* sc = b + 96; float d_all = h2f(rd16(b + 108)); float* yy = y + i * 256;
+            uint32_t a[3]; for (int k = 0; k < 3; k++) a[k] = (uint32_t)sc[4 * k] | ((uint32_t)sc[4 * k + 1] << 8) | ((uint32_t)sc[4 * k + 2] << 16) | ((uint32_t)sc[4 * k + 3] << 24);
+            const uint32_t k1 = 0x03030303u, k2 = 0x0f0f0f0fu;
+            uint32_t aux[4] = { (a[0] & k2) | ((a[2] & k1) << 4), (a[1] & k2) | (((a[2] >> 2) & k1) << 4), ((a[0] >> 4) & k2) | (((a[2] >> 4) & k1) << 4), ((a[1] >> 4) & k2) | (((a[2] >> 6) & k1) << 4) };
+            int is = 0; uint8_t m = 1;
+            for (int n = 0; n < 2; n++) { int shift = 0;
+                for (int j = 0; j < 4; j++) {
+                    for (int half = 0; half < 2; half++) { float dl = d_all * (float)((int)(int8_t)(uint8_t)(aux[is / 4] >> (8 * (is % 4))) - 32); is++;
+                        for (int l = 0; l < 16; l++) { int oo = l + 16 * half; yy[l] = dl * (float)((int)((q[oo] >> shift) & 3) - (hm[oo] & m ? 0 : 4)); }
+                        yy += 16; }
+                    shift += 2; m = (uint8_t)(m << 1); }
+                q += 32; }
+        }
+        break;
+    case ORC_Q5_K:                                                                             /* :108-113: [d][dmin][scales 12][qh 32][ql 128] */
+        for (int64_t i = 0; i < nb; i++) {
+            const uint8_t* b = x + i * bs; float d = h2f(rd16(b)), mn = h2f(rd16(b + 2)); const uint8_t* sc = b + 4; const uint8_t* qh = b + 16; const uint8_t* ql = b + 48; float* yy = y + i * 256;
+            uint8_t u1 = 1, u2 = 2;
+            for (int j = 0; j < 4; j++) { uint8_t s1, m1, s2, m2; scale_min_k4(2 * j, sc, &s1, &m1); scale_min_k4(2 * j + 1, sc, &s2, &m2);
+                float d1 = d * (float)s1, mm1 = mn * (float)m1, d2 = d * (float)s2, mm2 = mn * (float)m2;
+                for (int l = 0; l < 32; l++) { yy[l] = d1 * (float)((ql[l] & 0xF) + (qh[l] & u1 ? 16 : 0)) - mm1; yy[l + 32] = d2 * (float)((ql[l] >> 4) + (qh[l] & u2 ? 16 : 0)) - mm2; }
+                yy += 64; ql += 32; u1 = (uint8_t)(u1 << 2); u2 = (uint8_t)(u2 << 2); }
         }
         break;
     case ORC_IQ1_M:                                                                            /* :152-164: [qs 32][qh 16][scales 4 x u16]; the f16 scale sits in the top nibbles of the scale words */
@@ -329,6 +372,10 @@ static void synth_block(int type, uint64_t tkey, uint64_t b, uint8_t* out) {
         for (int i = 192; i < 208; i++) out[i] = (uint8_t)(int8_t)((int)(out[i] & 15) - 8);
         out[208] = (uint8_t)d; out[209] = (uint8_t)(d >> 8); break;
     case ORC_IQ2_XXS: synth_payload(k, 3, out + 2, 64); break;
+    case ORC_Q4_0: synth_payload(k, 3, out + 2, 16); break;
+    case ORC_Q5_0: synth_payload(k, 3, out + 2, 20); break;
+    case ORC_Q3_K: synth_payload(k, 3, out, 108); out[108] = (uint8_t)d; out[109] = (uint8_t)(d >> 8); break;   /* the f16 scale closes the block */
+    case ORC_Q5_K: { uint16_t dm = synth_scale(k, 3); out[2] = (uint8_t)dm; out[3] = (uint8_t)(dm >> 8); synth_payload(k, 6, out + 4, 172); } break;
     case ORC_IQ1_M:   /* the f16 scale goes, a nibble each, into the top of the four scale words */
         synth_payload(k, 3, out, 56);
         for (int i = 0; i < 4; i++) out[49 + 2 * i] = (uint8_t)((out[49 + 2 * i] & 0x0F) | (((d >> (4 * i)) & 0xF) << 4));

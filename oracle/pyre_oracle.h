@@ -26,7 +26,7 @@ extern "C" {
 #endif
 
 /* ggml type ids, gguf_q.rs:23-29 */
-enum { ORC_F32 = 0, ORC_F16 = 1, ORC_Q8_0 = 8, ORC_Q4_K = 12, ORC_Q6_K = 14, ORC_IQ2_XXS = 16, ORC_Q2_0 = 42, ORC_IQ2_XS = 17, ORC_IQ3_XXS = 18, ORC_IQ4_NL = 20, ORC_IQ3_S = 21, ORC_IQ2_S = 22, ORC_IQ4_XS = 23, ORC_IQ1_M = 29, ORC_BF16 = 30 };
+enum { ORC_F32 = 0, ORC_F16 = 1, ORC_Q4_0 = 2, ORC_Q5_0 = 6, ORC_Q3_K = 11, ORC_Q5_K = 13, ORC_Q8_0 = 8, ORC_Q4_K = 12, ORC_Q6_K = 14, ORC_IQ2_XXS = 16, ORC_Q2_0 = 42, ORC_IQ2_XS = 17, ORC_IQ3_XXS = 18, ORC_IQ4_NL = 20, ORC_IQ3_S = 21, ORC_IQ2_S = 22, ORC_IQ4_XS = 23, ORC_IQ1_M = 29, ORC_BF16 = 30 };
 
 /* A quantized row-major matrix (QMat, gguf_q.rs:199-215).  data == NULL means the
  * matrix is synthetic: row bytes are generated on demand from (seed, tid). */

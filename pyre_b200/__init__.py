@@ -21,9 +21,10 @@ LIB_PATH = _PKG / "libpyre_b200.so"
 F32, F16, Q8_0, Q4_K, IQ2_XS, IQ3_S, BF16 = 0, 1, 8, 12, 17, 21, 30
 IQ3_XXS, IQ4_NL, IQ2_S, IQ4_XS = 18, 20, 22, 23          # the further formats of mixed-type files
 Q6_K, IQ2_XXS, Q2_0, IQ1_M = 14, 16, 42, 29
+Q4_0, Q5_0, Q3_K, Q5_K = 2, 6, 11, 13
 TYPE_NAMES = {"F32": F32, "F16": F16, "Q8_0": Q8_0, "Q4_K": Q4_K, "IQ2_XS": IQ2_XS, "IQ3_S": IQ3_S, "BF16": BF16,
               "IQ3_XXS": IQ3_XXS, "IQ4_NL": IQ4_NL, "IQ2_S": IQ2_S, "IQ4_XS": IQ4_XS,
-              "Q6_K": Q6_K, "IQ2_XXS": IQ2_XXS, "Q2_0": Q2_0, "IQ1_M": IQ1_M}
+              "Q6_K": Q6_K, "IQ2_XXS": IQ2_XXS, "Q2_0": Q2_0, "IQ1_M": IQ1_M, "Q4_0": Q4_0, "Q5_0": Q5_0, "Q3_K": Q3_K, "Q5_K": Q5_K}
 
 PB_OK, PB_ERR_ARG, PB_ERR_CUDA, PB_ERR_OOM, PB_UNSUPPORTED, PB_ERR_DEVICE, PB_ERR_STATE = range(7)
 _STATUS = {1: "PB_ERR_ARG", 2: "PB_ERR_CUDA", 3: "PB_ERR_OOM", 4: "PB_UNSUPPORTED", 5: "PB_ERR_DEVICE", 6: "PB_ERR_STATE"}

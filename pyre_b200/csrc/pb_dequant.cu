@@ -76,14 +76,15 @@ __device__ static inline uint16_t pb_synth_scale(uint64_t bkey, int j0) {
 
 template <int FMT>
 __global__ void __launch_bounds__(256) pb_synth_kernel(uint8_t* __restrict__ w, int64_t nblocks, uint64_t tkey, int64_t block0) {
-    constexpr int BS = FMT == PB_T_Q8_0 ? 34 : (FMT == PB_T_IQ4_NL || FMT == PB_T_Q2_0 ? 18 : PbFmt<FMT>::STEP_BYTES);
+    constexpr int BS = FMT == PB_T_Q8_0 ? 34 : (FMT == PB_T_IQ4_NL || FMT == PB_T_Q2_0 || FMT == PB_T_Q4_0 ? 18 : (FMT == PB_T_Q5_0 ? 22 : PbFmt<FMT>::STEP_BYTES));
     const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= nblocks) return;
     const uint64_t k = pb_sm64(tkey ^ ((uint64_t)(block0 + b) * 0xD1342543DE82EF95ull));
     uint16_t* o = reinterpret_cast<uint16_t*>(w + b * BS);  // every block size is even
     o[0] = pb_synth_scale(k, 0);
     int j0 = 3, off = 1, payload = BS - 2;
-    if (FMT == PB_T_Q4_K) { o[1] = pb_synth_scale(k, 3); j0 = 6; off = 2; payload = 140; }
+    if (FMT == PB_T_Q4_K || FMT == PB_T_Q5_K) { o[1] = pb_synth_scale(k, 3); j0 = 6; off = 2; payload = FMT == PB_T_Q4_K ? 140 : 172; }
+    if (FMT == PB_T_Q3_K) { off = 0; payload = 108; }   // the f16 scale closes the block
     if (FMT == PB_T_Q6_K) { off = 0; payload = 208; }   // the f16 scale closes the block
     if (FMT == PB_T_IQ1_M) { off = 0; payload = 56; }   // no scale of its own at the front
     for (int i = 0; i < payload; i += 8) {
@@ -100,6 +101,7 @@ __global__ void __launch_bounds__(256) pb_synth_kernel(uint8_t* __restrict__ w, 
             o[off + i / 2 + h] = (uint16_t)two;
         }
     }
+    if (FMT == PB_T_Q3_K) o[54] = pb_synth_scale(k, 0);
     if (FMT == PB_T_IQ1_M) {   // the f16 scale goes, a nibble each, into the top of the four scale words
         const uint32_t d = pb_synth_scale(k, 0);
         for (int i = 0; i < 4; i++) o[24 + i] = (uint16_t)((o[24 + i] & 0x0FFF) | (((d >> (4 * i)) & 0xF) << 12));
@@ -136,6 +138,10 @@ int pb_launch_synth(pb_ctx* ctx, int type, uint8_t* w, int64_t nblocks, uint64_t
         case PB_T_IQ2_XXS: pb_synth_kernel<PB_T_IQ2_XXS><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
         case PB_T_Q6_K: pb_synth_kernel<PB_T_Q6_K><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
         case PB_T_IQ1_M: pb_synth_kernel<PB_T_IQ1_M><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
+        case PB_T_Q4_0: pb_synth_kernel<PB_T_Q4_0><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
+        case PB_T_Q5_0: pb_synth_kernel<PB_T_Q5_0><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
+        case PB_T_Q3_K: pb_synth_kernel<PB_T_Q3_K><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
+        case PB_T_Q5_K: pb_synth_kernel<PB_T_Q5_K><<<grid, 256, 0, ctx->stream>>>(w, nblocks, tkey, block0); break;
         default: PB_FAIL(ctx, PB_ERR_ARG, "pb_qmat_synth: no generator for ggml type %d", type);
     }
     ctx->kernels_launched++;

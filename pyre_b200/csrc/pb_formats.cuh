@@ -12,7 +12,7 @@
 #define PB_TABLE_QUAL static __device__ const
 #include "pb_iq_tables.h"
 
-enum : int { PB_T_F32 = 0, PB_T_F16 = 1, PB_T_Q8_0 = 8, PB_T_Q4_K = 12, PB_T_Q6_K = 14, PB_T_IQ2_XXS = 16, PB_T_Q2_0 = 42, PB_T_IQ1_M = 29, PB_T_IQ2_XS = 17, PB_T_IQ3_XXS = 18, PB_T_IQ4_NL = 20, PB_T_IQ3_S = 21, PB_T_IQ2_S = 22,
+enum : int { PB_T_F32 = 0, PB_T_F16 = 1, PB_T_Q4_0 = 2, PB_T_Q5_0 = 6, PB_T_Q3_K = 11, PB_T_Q5_K = 13, PB_T_Q8_0 = 8, PB_T_Q4_K = 12, PB_T_Q6_K = 14, PB_T_IQ2_XXS = 16, PB_T_Q2_0 = 42, PB_T_IQ1_M = 29, PB_T_IQ2_XS = 17, PB_T_IQ3_XXS = 18, PB_T_IQ4_NL = 20, PB_T_IQ3_S = 21, PB_T_IQ2_S = 22,
              PB_T_IQ4_XS = 23, PB_T_BF16 = 30,
              // internal, never a ggml id: IQ3_S re-coded at upload into 4-bit codes (see pb_repack.cu).  Every IQ3_S
              // codebook value is odd (1..15), so a weight is one of the sixteen values -15, -13, .. 15 = 2 c - 15.
@@ -245,6 +245,77 @@ template <> struct PbFmt<PB_T_IQ2_XXS> : PbContig8 {
     }
 };
 
+// Q4_0 (gguf_q.rs:74-75): blocks of 32 = [d f16][16 bytes]; weight j < 16 is the low nibble of byte j, weight 16 + j the high one, value nibble - 8
+template <> struct PbFmt<PB_T_Q4_0> : PbContig8 {
+    static constexpr int STEP_BYTES = 8 * 18;
+    static constexpr bool HAS_MIN = false;
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables&, PbUnit& o) {
+        const uint8_t* b = p + 18 * (u >> 2);
+        const int part = u & 3;
+        o.sa = o.sb = pb_h2f((uint16_t)(b[0] | (b[1] << 8)));
+        o.ma = o.mb = 0.0f;
+        const uint8_t* q = b + 2 + 8 * (part & 1);
+#pragma unroll
+        for (int j = 0; j < 8; j++) o.w[j] = (float)((int)(part < 2 ? (q[j] & 0xF) : (q[j] >> 4)) - 8);
+    }
+};
+
+// Q5_0 (gguf_q.rs:76-78): blocks of 32 = [d f16][qh u32][16 bytes]; as Q4_0 with bit i of qh as the fifth bit of weight i, value - 16
+template <> struct PbFmt<PB_T_Q5_0> : PbContig8 {
+    static constexpr int STEP_BYTES = 8 * 22;
+    static constexpr bool HAS_MIN = false;
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables&, PbUnit& o) {
+        const uint8_t* b = p + 22 * (u >> 2);
+        const int part = u & 3;
+        o.sa = o.sb = pb_h2f((uint16_t)(b[0] | (b[1] << 8)));
+        o.ma = o.mb = 0.0f;
+        const uint32_t qh = ((uint32_t)b[2] | ((uint32_t)b[3] << 8) | ((uint32_t)b[4] << 16) | ((uint32_t)b[5] << 24)) >> (8 * part);
+        const uint8_t* q = b + 6 + 8 * (part & 1);
+#pragma unroll
+        for (int j = 0; j < 8; j++) o.w[j] = (float)((int)((part < 2 ? (q[j] & 0xF) : (q[j] >> 4)) | (((qh >> j) & 1) << 4)) - 16);
+    }
+};
+
+// Q3_K (gguf_q.rs:90-102): [hmask 32][qs 64][scales 12][d f16]; weight 128 n + 32 j + o takes two bits (shift 2 j) of qs[32 n + o] and, as
+// "not minus four", bit 4 n + j of hmask[o]; sixteen 6-bit scales (minus 32), one per 16 weights, spread over the twelve scale bytes
+template <> struct PbFmt<PB_T_Q3_K> : PbContig8 {
+    static constexpr int STEP_BYTES = 110;
+    static constexpr bool HAS_MIN = false;
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables&, PbUnit& o) {
+        const float d = pb_h2f((uint16_t)(p[108] | (p[109] << 8)));
+        const int n = u >> 4, j = (u >> 2) & 3, o0 = 8 * (u & 3), is = 8 * n + 2 * j + (o0 >> 4);
+        const uint8_t* sc = p + 96;
+        const int lo = is < 8 ? (sc[is] & 0xF) : (sc[is - 8] >> 4), hi = (sc[8 + (is & 3)] >> (2 * (is >> 2))) & 3;
+        o.sa = o.sb = __fmul_rn(d, (float)((lo | (hi << 4)) - 32));
+        o.ma = o.mb = 0.0f;
+        const uint8_t* q = p + 32 + 32 * n + o0;
+        const uint8_t* hm = p + o0;
+#pragma unroll
+        for (int k = 0; k < 8; k++) o.w[k] = (float)((int)((q[k] >> (2 * j)) & 3) - ((hm[k] >> (4 * n + j)) & 1 ? 0 : 4));
+    }
+};
+
+// Q5_K (gguf_q.rs:108-113): [d f16][dmin f16][scales 12][qh 32][ql 128]; as Q4_K (64 weights per group: low nibbles, then high nibbles of 32
+// bytes) with bits 2 g and 2 g + 1 of qh[l] as the fifth bit
+template <> struct PbFmt<PB_T_Q5_K> : PbContig8 {
+    static constexpr int STEP_BYTES = 176;
+    static constexpr bool HAS_MIN = true;
+    __device__ static __forceinline__ void unit(const uint8_t* p, int u, const PbTables&, PbUnit& o) {
+        const float d = pb_h2f(*reinterpret_cast<const uint16_t*>(p));
+        const float mn = pb_h2f(*reinterpret_cast<const uint16_t*>(p + 2));
+        const int g = u >> 3, r = u & 7, hi = r >> 2, l0 = 8 * (r & 3);
+        uint32_t s, m;
+        { const uint8_t* q = p + 4; const int j = 2 * g + hi;      // scale_min_k4, gguf_q.rs:62-64
+          if (j < 4) { s = q[j] & 63; m = q[j + 4] & 63; }
+          else { s = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4); m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4); } }
+        o.sa = o.sb = __fmul_rn(d, (float)s); o.ma = o.mb = __fmul_rn(mn, (float)m);
+        const uint8_t* ql = p + 48 + 32 * g + l0;
+        const uint8_t* qh = p + 16 + l0;
+#pragma unroll
+        for (int k = 0; k < 8; k++) o.w[k] = (float)((hi ? (ql[k] >> 4) : (ql[k] & 0xF)) + (((qh[k] >> (2 * g + hi)) & 1) << 4));
+    }
+};
+
 // IQ1_M (gguf_q.rs:152-164): [qs 32][qh 16][scales 4 x u16]; per 8 weights an 11-bit grid index (8 bits in qs, 3 in a nibble of qh) into
 // entries of eight values -1 / 0 / 1, the nibble's top bit the sign of a shift of 1/8; two 3-bit scales per 32 weights in the low twelve
 // bits of the scale words, the block's f16 scale in their top nibbles.
@@ -387,6 +458,10 @@ static inline int pb_geom(int type, int* elems, int* bytes) {
         case PB_T_IQ2_XXS: e = 256; b = 66; break;
         case PB_T_Q6_K: e = 256; b = 210; break;
         case PB_T_IQ1_M: e = 256; b = 56; break;
+        case PB_T_Q4_0: e = 32; b = 18; break;
+        case PB_T_Q5_0: e = 32; b = 22; break;
+        case PB_T_Q3_K: e = 256; b = 110; break;
+        case PB_T_Q5_K: e = 256; b = 176; break;
         case PB_T_IQ3S_N4: e = 256; b = 136; break;
         default: return -1;
     }
@@ -408,6 +483,10 @@ static inline int pb_geom(int type, int* elems, int* bytes) {
         case PB_T_IQ2_XXS: { constexpr int FMT = PB_T_IQ2_XXS; F(__VA_ARGS__); } break; \
         case PB_T_Q6_K: { constexpr int FMT = PB_T_Q6_K; F(__VA_ARGS__); } break; \
         case PB_T_IQ1_M: { constexpr int FMT = PB_T_IQ1_M; F(__VA_ARGS__); } break; \
+        case PB_T_Q4_0: { constexpr int FMT = PB_T_Q4_0; F(__VA_ARGS__); } break; \
+        case PB_T_Q5_0: { constexpr int FMT = PB_T_Q5_0; F(__VA_ARGS__); } break; \
+        case PB_T_Q3_K: { constexpr int FMT = PB_T_Q3_K; F(__VA_ARGS__); } break; \
+        case PB_T_Q5_K: { constexpr int FMT = PB_T_Q5_K; F(__VA_ARGS__); } break; \
         case PB_T_Q4_K: { constexpr int FMT = PB_T_Q4_K; F(__VA_ARGS__); } break;    \
         case PB_T_Q8_0: { constexpr int FMT = PB_T_Q8_0; F(__VA_ARGS__); } break;    \
         case PB_T_F32: { constexpr int FMT = PB_T_F32; F(__VA_ARGS__); } break;      \

@@ -270,7 +270,8 @@ static int launch_q_fmt(pb_ctx* ctx, const PbGemvQArgs& a, int row_bytes) {
 bool pb_gemvq_supported(int type, int cols) {
     const bool quant = type == PB_T_IQ3_S || type == PB_T_IQ3S_N4 || type == PB_T_IQ2_XS || type == PB_T_Q4_K || type == PB_T_Q8_0 ||
                        type == PB_T_IQ3_XXS || type == PB_T_IQ2_S || type == PB_T_IQ4_NL || type == PB_T_IQ4_XS ||
-                       type == PB_T_Q2_0 || type == PB_T_IQ2_XXS || type == PB_T_Q6_K || type == PB_T_IQ1_M;
+                       type == PB_T_Q2_0 || type == PB_T_IQ2_XXS || type == PB_T_Q6_K || type == PB_T_IQ1_M ||
+                       type == PB_T_Q4_0 || type == PB_T_Q5_0 || type == PB_T_Q3_K || type == PB_T_Q5_K;
     const int bpr = cols / 256;
     return quant && cols % 256 == 0 && bpr > 0 && (bpr & (bpr - 1)) == 0 && cols <= 4096;
 }
@@ -336,6 +337,10 @@ static int launch_gemvq_dp4a(pb_ctx* ctx, const PbGemvQArgs& a, int el, int bs) 
             case PB_T_IQ2_XXS: rc = launch_q_fmt<PB_T_IQ2_XXS>(ctx, s, row_bytes); break;
             case PB_T_Q6_K: rc = launch_q_fmt<PB_T_Q6_K>(ctx, s, row_bytes); break;
             case PB_T_IQ1_M: rc = launch_q_fmt<PB_T_IQ1_M>(ctx, s, row_bytes); break;
+            case PB_T_Q4_0: rc = launch_q_fmt<PB_T_Q4_0>(ctx, s, row_bytes); break;
+            case PB_T_Q5_0: rc = launch_q_fmt<PB_T_Q5_0>(ctx, s, row_bytes); break;
+            case PB_T_Q3_K: rc = launch_q_fmt<PB_T_Q3_K>(ctx, s, row_bytes); break;
+            case PB_T_Q5_K: rc = launch_q_fmt<PB_T_Q5_K>(ctx, s, row_bytes); break;
             default: rc = launch_q_fmt<PB_T_Q8_0>(ctx, s, row_bytes); break;
         }
     }

@@ -769,6 +769,10 @@ static int launch_expert_type(pb_ctx* ctx, const PbExpertParams& p, int type, in
         case PB_T_IQ2_XXS: GO(PB_T_IQ2_XXS);
         case PB_T_Q6_K: GO(PB_T_Q6_K);
         case PB_T_IQ1_M: GO(PB_T_IQ1_M);
+        case PB_T_Q4_0: GO(PB_T_Q4_0);
+        case PB_T_Q5_0: GO(PB_T_Q5_0);
+        case PB_T_Q3_K: GO(PB_T_Q3_K);
+        case PB_T_Q5_K: GO(PB_T_Q5_K);
         default: GO(PB_T_Q8_0);
     }
 #undef GO

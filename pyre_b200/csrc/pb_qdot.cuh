@@ -333,6 +333,103 @@ template <> struct PbQDec<PB_T_IQ2_XXS> {
     }
 };
 
+// ---- Q4_0 / Q5_0: sixteen bytes hold 32 weights (low nibbles, then high nibbles), Q5_0 with a fifth bit per weight from a 32-bit word;
+// the offset (8 or 16) is taken off per byte with bit 7 set so that no borrow crosses.
+template <> struct PbQDec<PB_T_Q4_0> {
+    static constexpr int STEP_BYTES = 8 * 18;
+    static constexpr bool HAS_MIN = false, SCALE16 = false, AFFINE = false;
+    __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs&, PbQuarter& o) {
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+            const uint32_t blk = p + 18 * (2 * qt + b);
+            o.sc[2 * b] = o.sc[2 * b + 1] = pb_h2f((uint16_t)pb_lds16(blk));
+            uint32_t q[4];
+            pb_ld_u32x<4>(blk + 2, q);
+#pragma unroll
+            for (int m = 0; m < 4; m++) {
+                o.w[8 * b + m] = (int)((((q[m] & 0x0F0F0F0Fu) | 0x80808080u) - 0x08080808u) ^ 0x80808080u);
+                o.w[8 * b + 4 + m] = (int)(((((q[m] >> 4) & 0x0F0F0F0Fu) | 0x80808080u) - 0x08080808u) ^ 0x80808080u);
+            }
+        }
+    }
+};
+template <> struct PbQDec<PB_T_Q5_0> {
+    static constexpr int STEP_BYTES = 8 * 22;
+    static constexpr bool HAS_MIN = false, SCALE16 = false, AFFINE = false;
+    __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs&, PbQuarter& o) {
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+            const uint32_t blk = p + 22 * (2 * qt + b);
+            o.sc[2 * b] = o.sc[2 * b + 1] = pb_h2f((uint16_t)pb_lds16(blk));
+            uint32_t q[5];                              // [qh, 16 bytes of nibbles]
+            pb_ld_u32x<5>(blk + 2, q);
+#pragma unroll
+            for (int m = 0; m < 4; m++) {
+                const uint32_t lo = (q[1 + m] & 0x0F0F0F0Fu) | (pb_spread4((q[0] >> (4 * m)) & 0xFu) << 4);
+                const uint32_t hi = ((q[1 + m] >> 4) & 0x0F0F0F0Fu) | (pb_spread4((q[0] >> (16 + 4 * m)) & 0xFu) << 4);
+                o.w[8 * b + m] = (int)(((lo | 0x80808080u) - 0x10101010u) ^ 0x80808080u);
+                o.w[8 * b + 4 + m] = (int)(((hi | 0x80808080u) - 0x10101010u) ^ 0x80808080u);
+            }
+        }
+    }
+};
+
+// ---- Q3_K: a quarter is the two-bit planes j = 2 (qt & 1) and the next of half n = qt / 2: both read the 32 qs bytes of the half and the
+// 32 hmask bytes; value = two bits + 4 * mask bit - 4.  The four scales of the quarter are the bytes of one word of the unpacked scales.
+template <> struct PbQDec<PB_T_Q3_K> {
+    static constexpr int STEP_BYTES = 110;
+    static constexpr bool HAS_MIN = false, SCALE16 = true, AFFINE = false;
+    __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs&, PbQuarter& o) {
+        const float d = pb_h2f((uint16_t)pb_lds16(p + 108));
+        const int n = qt >> 1, side = qt & 1;
+        uint32_t hm[8], qs[8], a[3];
+        pb_ld_u32x<8>(p, hm);
+        pb_ld_u32x<8>(p + 32 + 32 * n, qs);
+        pb_ld_u32x<3>(p + 96, a);
+        const uint32_t aux = (((side ? a[1] : a[0]) >> (4 * n)) & 0x0F0F0F0Fu) | (((a[2] >> (2 * qt)) & 0x03030303u) << 4);
+#pragma unroll
+        for (int h = 0; h < 4; h++) o.sc[h] = d * (float)((int)((aux >> (8 * h)) & 0xFF) - 32);
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+            const int j = 2 * side + b;
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const uint32_t v = ((qs[k] >> (2 * j)) & 0x03030303u) | (((hm[k] >> (4 * n + j)) & 0x01010101u) << 2);
+                o.w[8 * b + k] = (int)(((v | 0x80808080u) - 0x04040404u) ^ 0x80808080u);
+            }
+        }
+    }
+};
+
+// ---- Q5_K: Q4_K's nibbles (at byte 48) with bits 2 qt and 2 qt + 1 of the 32 qh bytes (at byte 16) as the fifth bit; blocks of 176 bytes
+// keep every field 16-byte aligned.
+template <> struct PbQDec<PB_T_Q5_K> {
+    static constexpr int STEP_BYTES = 176;
+    static constexpr bool HAS_MIN = true, SCALE16 = false, AFFINE = false;
+    __device__ static __forceinline__ void quarter(uint32_t p, int qt, const PbQTabs&, PbQuarter& o) {
+        const uint4 hdr = pb_lds128(p);            // d, dmin, 12 scale bytes
+        const float d = pb_h2f((uint16_t)(hdr.x & 0xFFFF)), mn = pb_h2f((uint16_t)(hdr.x >> 16));
+        const uint32_t scw[3] = {hdr.y, hdr.z, hdr.w};
+        auto sb = [&](int i) -> uint32_t { return (scw[i >> 2] >> (8 * (i & 3))) & 0xFF; };
+        uint32_t s[2], m[2];
+#pragma unroll
+        for (int e = 0; e < 2; e++) {              // scale_min_k4, gguf_q.rs:62-64
+            const int j = 2 * qt + e;
+            if (j < 4) { s[e] = sb(j) & 63; m[e] = sb(j + 4) & 63; }
+            else { s[e] = (sb(j + 4) & 0xF) | ((sb(j - 4) >> 6) << 4); m[e] = (sb(j + 4) >> 4) | ((sb(j) >> 6) << 4); }
+        }
+        o.sc[0] = o.sc[1] = d * (float)s[0]; o.sc[2] = o.sc[3] = d * (float)s[1];
+        o.mn[0] = mn * (float)m[0]; o.mn[1] = mn * (float)m[1];
+        const uint4 a = pb_lds128(p + 48 + 32 * qt), b = pb_lds128(p + 64 + 32 * qt), ha = pb_lds128(p + 16), hb = pb_lds128(p + 32);
+        const uint32_t q[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w}, h[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            o.w[k] = (int)((q[k] & 0x0F0F0F0Fu) | (((h[k] >> (2 * qt)) & 0x01010101u) << 4));
+            o.w[8 + k] = (int)(((q[k] >> 4) & 0x0F0F0F0Fu) | (((h[k] >> (2 * qt + 1)) & 0x01010101u) << 4));
+        }
+    }
+};
+
 // ---- IQ1_M: weights are s * (g + delta) with g in -1 / 0 / 1 and delta = +-1/8, i.e. (s / 8) * (8 g +- 1) with an int8 in the bracket.
 // The shared-memory table holds those eight int8 per (sign, 11-bit index), so a look-up is the whole decode; scales per 16 weights.
 template <> struct PbQDec<PB_T_IQ1_M> {

@@ -22,7 +22,7 @@ from gguf import quants, GGMLQuantizationType as T  # noqa: E402
 
 HERE = Path(__file__).resolve().parent
 # Q2_0 (ggml id 42 of the reference, src/model/gguf_q.rs:80-81) is not a gguf-py type: its fixture is the two-line rule of that file written in numpy
-GG = {"IQ2_XXS": T.IQ2_XXS, "Q6_K": T.Q6_K, "IQ1_M": T.IQ1_M, "Q8_0": T.Q8_0, "Q4_K": T.Q4_K, "IQ2_XS": T.IQ2_XS, "IQ3_S": T.IQ3_S, "IQ3_XXS": T.IQ3_XXS, "IQ2_S": T.IQ2_S, "IQ4_NL": T.IQ4_NL, "IQ4_XS": T.IQ4_XS}
+GG = {"IQ2_XXS": T.IQ2_XXS, "Q6_K": T.Q6_K, "IQ1_M": T.IQ1_M, "Q4_0": T.Q4_0, "Q5_0": T.Q5_0, "Q3_K": T.Q3_K, "Q5_K": T.Q5_K, "Q8_0": T.Q8_0, "Q4_K": T.Q4_K, "IQ2_XS": T.IQ2_XS, "IQ3_S": T.IQ3_S, "IQ3_XXS": T.IQ3_XXS, "IQ2_S": T.IQ2_S, "IQ4_NL": T.IQ4_NL, "IQ4_XS": T.IQ4_XS}
 
 
 def q2_0_numpy(blocks):
@@ -58,7 +58,9 @@ def main():
         rng = np.random.default_rng(4321 + t)
         nb = rows * cols // el
         b = rng.integers(0, 256, size=(nb, bs), dtype=np.uint8)
-        b[:, 209 if name == "Q6_K" else 1] = rng.integers(0x20, 0x38, nb)      # Q6_K keeps its f16 scale in the last two bytes
+        b[:, {"Q6_K": 209, "Q3_K": 109}.get(name, 1)] = rng.integers(0x20, 0x38, nb)      # Q6_K and Q3_K keep their f16 scale in the last two bytes
+        if name == "Q5_K":
+            b[:, 3] = rng.integers(0x20, 0x38, nb)
         if name == "IQ1_M":            # its f16 scale is spread over the top nibbles of the four scale words (bytes 49, 51, 53, 55)
             hi = rng.integers(0x20, 0x38, nb)
             b[:, 53] = (b[:, 53] & 0x0F) | ((hi & 0xF) << 4).astype(np.uint8)

@@ -183,7 +183,7 @@ def test_moe_config3_128_tokens(ctx):
 
 
 @pytest.mark.parametrize("name,t", [("Q8_0", 1), ("Q8_0", 8), ("Q4_K", 8), ("IQ2_XS", 8), ("IQ3_XXS", 1), ("IQ3_XXS", 8), ("IQ2_S", 8), ("IQ4_NL", 8), ("IQ4_XS", 1), ("IQ4_XS", 8),
-                                    ("IQ2_XXS", 1), ("IQ2_XXS", 8), ("Q6_K", 8), ("Q2_0", 1), ("Q2_0", 8), ("IQ1_M", 1), ("IQ1_M", 8)])
+                                    ("IQ2_XXS", 1), ("IQ2_XXS", 8), ("Q6_K", 8), ("Q2_0", 1), ("Q2_0", 8), ("IQ1_M", 1), ("IQ1_M", 8), ("Q4_0", 8), ("Q5_0", 1), ("Q5_0", 8), ("Q3_K", 1), ("Q3_K", 8), ("Q5_K", 1), ("Q5_K", 8)])
 def test_moe_full_width_other_formats(ctx, name, t):
     """The MoE block at full width (2048 x 512 experts of 512) in the other streaming formats; Q8_0 rows of 2048 columns are
     2176 bytes, where a chunk of the gate / up kernel holds fewer rows than it has consumer warps."""

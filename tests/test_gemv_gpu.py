@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 GOLD = Path(__file__).resolve().parent / "golden"
 TYPES = {"Q8_0": pb.Q8_0, "Q4_K": pb.Q4_K, "IQ2_XS": pb.IQ2_XS, "IQ3_S": pb.IQ3_S}
 EXTRA = {"IQ3_XXS": pb.IQ3_XXS, "IQ2_S": pb.IQ2_S, "IQ4_NL": pb.IQ4_NL, "IQ4_XS": pb.IQ4_XS,   # the GGUF loader's further formats
-         "Q2_0": pb.Q2_0, "IQ2_XXS": pb.IQ2_XXS, "Q6_K": pb.Q6_K, "IQ1_M": pb.IQ1_M}
+         "Q2_0": pb.Q2_0, "IQ2_XXS": pb.IQ2_XXS, "Q6_K": pb.Q6_K, "IQ1_M": pb.IQ1_M, "Q4_0": pb.Q4_0, "Q5_0": pb.Q5_0, "Q3_K": pb.Q3_K, "Q5_K": pb.Q5_K}
 GEMV_TOL = 1e-3   # relative, f32 accumulate (north-star tolerance)
 
 

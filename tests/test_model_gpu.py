@@ -355,7 +355,7 @@ def test_yarn_scaled_context_greedy_identity_vs_oracle(ctx, kv_bits):
     st.destroy(); st0.destroy(); m.destroy(); m0.destroy()
 
 
-@pytest.mark.parametrize("name", ["Q8_0", "Q4_K", "IQ2_XS", "IQ3_XXS", "IQ2_S", "IQ4_NL", "IQ4_XS", "IQ2_XXS", "Q6_K", "Q2_0", "IQ1_M"])
+@pytest.mark.parametrize("name", ["Q8_0", "Q4_K", "IQ2_XS", "IQ3_XXS", "IQ2_S", "IQ4_NL", "IQ4_XS", "IQ2_XXS", "Q6_K", "Q2_0", "IQ1_M", "Q4_0", "Q5_0", "Q3_K", "Q5_K"])
 def test_other_quant_formats_greedy_identity_vs_oracle(ctx, name):
     """The token loop with every matrix in one of the other streaming formats (the per-operation kernels; the fused step
     kernel is for re-coded IQ3_S): prompt logits within 1e-3 and 32 greedy ids identical to the oracle.  Q8_0 rows are the

@@ -10,7 +10,7 @@ from conftest import rel_err
 GOLD = Path(__file__).resolve().parent / "golden"
 
 
-@pytest.mark.parametrize("name", ["Q8_0", "Q4_K", "IQ2_XS", "IQ3_S", "IQ3_XXS", "IQ2_S", "IQ4_NL", "IQ4_XS", "IQ2_XXS", "Q6_K", "Q2_0", "IQ1_M"])
+@pytest.mark.parametrize("name", ["Q8_0", "Q4_K", "IQ2_XS", "IQ3_S", "IQ3_XXS", "IQ2_S", "IQ4_NL", "IQ4_XS", "IQ2_XXS", "Q6_K", "Q2_0", "IQ1_M", "Q4_0", "Q5_0", "Q3_K", "Q5_K"])
 def test_dequant_matches_gguf_py_golden(name):
     """Bit-for-bit against gguf-py 0.19 output committed as a fixture (tests/golden/make_golden.py; Q2_0, which gguf-py does not
     know, against the reference's two-line rule written in numpy there)."""
@@ -31,14 +31,16 @@ def test_dequant_matches_gguf_py_live():
         y = oracle.dequant(t, raw, 32 * 1024)
         ref = quants.dequantize(raw.reshape(-1, bs), m[name]).reshape(-1)
         assert np.array_equal(y.view(np.uint32), ref.view(np.uint32)), name
-    m2 = {"IQ3_XXS": T.IQ3_XXS, "IQ2_S": T.IQ2_S, "IQ4_NL": T.IQ4_NL, "IQ4_XS": T.IQ4_XS, "IQ2_XXS": T.IQ2_XXS, "Q6_K": T.Q6_K, "IQ1_M": T.IQ1_M}
+    m2 = {"IQ3_XXS": T.IQ3_XXS, "IQ2_S": T.IQ2_S, "IQ4_NL": T.IQ4_NL, "IQ4_XS": T.IQ4_XS, "IQ2_XXS": T.IQ2_XXS, "Q6_K": T.Q6_K, "IQ1_M": T.IQ1_M, "Q4_0": T.Q4_0, "Q5_0": T.Q5_0, "Q3_K": T.Q3_K, "Q5_K": T.Q5_K}
     rng = np.random.default_rng(99)
     for name, t in oracle.EXTRA_TYPES.items():
         if name not in m2:
             continue
         el, bs = oracle.geom(t)
         b = rng.integers(0, 256, size=(2048 // el * 8, bs), dtype=np.uint8)
-        b[:, 209 if name == "Q6_K" else 1] = rng.integers(0x20, 0x38, b.shape[0])
+        b[:, {"Q6_K": 209, "Q3_K": 109}.get(name, 1)] = rng.integers(0x20, 0x38, b.shape[0])
+        if name == "Q5_K":
+            b[:, 3] = rng.integers(0x20, 0x38, b.shape[0])
         if name == "IQ1_M":          # exponent nibbles of the scattered f16 scale
             b[:, 55] = (b[:, 55] & 0x0F) | 0x20
         y = oracle.dequant(t, b.reshape(-1), 8 * 2048)
@@ -54,7 +56,7 @@ def test_geometry():
     assert oracle.geom(oracle.IQ3_S) == (256, 110)
     assert [oracle.row_bytes(t, 2048) for t in (oracle.Q8_0, oracle.Q4_K, oracle.IQ2_XS, oracle.IQ3_S)] == [2176, 1152, 592, 880]
     assert [oracle.geom(t) for t in (oracle.IQ3_XXS, oracle.IQ2_S, oracle.IQ4_NL, oracle.IQ4_XS)] == [(256, 98), (256, 82), (32, 18), (256, 136)]
-    assert [oracle.geom(t) for t in (oracle.Q2_0, oracle.IQ2_XXS, oracle.Q6_K, oracle.IQ1_M)] == [(64, 18), (256, 66), (256, 210), (256, 56)]
+    assert [oracle.geom(t) for t in (oracle.Q2_0, oracle.IQ2_XXS, oracle.Q6_K, oracle.IQ1_M, oracle.Q4_0, oracle.Q5_0, oracle.Q3_K, oracle.Q5_K)] == [(64, 18), (256, 66), (256, 210), (256, 56), (32, 18), (32, 22), (256, 110), (256, 176)]
     with pytest.raises(ValueError):
         oracle.geom(99)
 
