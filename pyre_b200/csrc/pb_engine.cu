@@ -104,6 +104,8 @@ struct pb_state {
     cudaGraphExec_t graph = nullptr;
     // speculative verify: DeltaNet (conv ring, ssm) after each of the first t-1 tokens of the last window
     std::vector<float*> ck_conv, ck_ssm;   // [n_lin * PB_MAX_WINDOW]
+    float** ck_tab = nullptr; float** ck_live = nullptr;   // the same pointers and the live buffers as device tables (pb_launch_ck_restore)
+    int64_t* q4n_all = nullptr;   // packed boundaries of all attention layers [n_attn][batch]; PbKv::q4n points into it
     int verify_t = 0; int64_t verify_pos0 = 0;
     uint64_t steps = 0, kernels_per_step = 0;
     // fused step (pb_step.cu), one sequence on one GPU: operation list on the device, launch segments (runs of operations
@@ -560,12 +562,13 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
     // 4-bit cache: the f32 ring holds the recent positions, the 64 that wait for the next packing step, and (batch-1 states)
     // a whole prefill chunk appended before its packing step
     s->ring_cap = c.kv_bits == 4 ? (int64_t)c.kv_recent + 64 + (solo ? PB_PREFILL_CHUNK : 0) : (int64_t)c.max_ctx;
+    if (rc == PB_OK) rc = dalloc(s, &s->q4n_all, (size_t)(m->n_attn > 0 ? m->n_attn : 1) * B);
     for (int i = 0; i < m->n_attn && rc == PB_OK; i++) {
         PbKv& k = s->kv[i];
         const size_t heads = (size_t)B * c.n_kv;
         rc = dalloc(s, &k.kr, heads * s->ring_cap * rowh);
         if (rc == PB_OK) rc = dalloc(s, &k.vr, heads * s->ring_cap * rowh);
-        if (rc == PB_OK) rc = dalloc(s, &k.q4n, (size_t)B);
+        if (rc == PB_OK) k.q4n = s->q4n_all + (size_t)i * B;
         const size_t packed_pos = c.kv_bits == 4 ? (size_t)c.max_ctx : 1;
         if (rc == PB_OK) rc = dalloc(s, &k.kw, heads * packed_pos * (rowh / 8));
         if (rc == PB_OK) rc = dalloc(s, &k.vw, heads * packed_pos * (rowh / 8));
@@ -618,12 +621,13 @@ int pb_state_set_pos(pb_state* s, int64_t pos) {
     // position below the boundary cannot be served (the reference's spec_keep drops packed rows in that
     // case, kv8_drop :2507; here the f32 rows are gone) and is refused.
     if (s->m->cfg.kv_bits == 4 && s->m->n_attn > 0) {
-        std::vector<int64_t> q((size_t)s->batch);
-        for (int ai = 0; ai < s->m->n_attn; ai++) {
-            if (pos == 0) { PB_CUDA(ctx, cudaMemsetAsync(s->kv[ai].q4n, 0, (size_t)s->batch * 8, ctx->stream)); continue; }
-            PB_CUDA(ctx, cudaMemcpy(q.data(), s->kv[ai].q4n, q.size() * 8, cudaMemcpyDeviceToHost));
-            for (int b = 0; b < s->batch; b++)
-                if (pos < q[b]) PB_FAIL(ctx, PB_ERR_STATE, "pb_state_set_pos: position %lld is below the packed KV boundary %lld of sequence %d", (long long)pos, (long long)q[b], b);
+        const size_t nq = (size_t)s->m->n_attn * s->batch;
+        if (pos == 0) PB_CUDA(ctx, cudaMemsetAsync(s->q4n_all, 0, nq * 8, ctx->stream));
+        else {
+            std::vector<int64_t> q(nq);
+            PB_CUDA(ctx, cudaMemcpy(q.data(), s->q4n_all, nq * 8, cudaMemcpyDeviceToHost));
+            for (size_t i = 0; i < nq; i++)
+                if (pos < q[i]) PB_FAIL(ctx, PB_ERR_STATE, "pb_state_set_pos: position %lld is below the packed KV boundary %lld of sequence %d", (long long)pos, (long long)q[i], (int)(i % s->batch));
         }
     }
     std::vector<int64_t> v((size_t)s->batch, pos);
@@ -1363,6 +1367,12 @@ int pb_verify(pb_state* s, const uint32_t* ids_host, int t, float* logits_host) 
     if (s->ck_conv.empty() && nl > 0) {
         s->ck_conv.assign((size_t)nl * PB_MAX_WINDOW, nullptr); s->ck_ssm.assign((size_t)nl * PB_MAX_WINDOW, nullptr);
         for (size_t i = 0; i < s->ck_conv.size(); i++) { PB_TRY(dalloc(s, &s->ck_conv[i], conv_elems(c, 1))); PB_TRY(dalloc(s, &s->ck_ssm[i], ssm_elems(c, 1))); }
+        std::vector<float*> tab(s->ck_conv.size() * 2), live((size_t)nl * 2);
+        for (size_t i = 0; i < s->ck_conv.size(); i++) { tab[2 * i] = s->ck_conv[i]; tab[2 * i + 1] = s->ck_ssm[i]; }
+        for (int li = 0; li < nl; li++) { live[(size_t)li * 2] = s->conv[li]; live[(size_t)li * 2 + 1] = s->ssm[li]; }
+        PB_TRY(dalloc(s, &s->ck_tab, tab.size())); PB_TRY(dalloc(s, &s->ck_live, live.size()));
+        PB_CUDA(ctx, cudaMemcpy(s->ck_tab, tab.data(), tab.size() * sizeof(float*), cudaMemcpyHostToDevice));
+        PB_CUDA(ctx, cudaMemcpy(s->ck_live, live.data(), live.size() * sizeof(float*), cudaMemcpyHostToDevice));
     }
     s->verify_pos0 = s->pos_host; s->verify_t = 0;
     mtp_note(s, s->pos_host, ids_host, t);
@@ -1390,18 +1400,15 @@ int pb_keep(pb_state* s, int t, int keep) {
     if (s->verify_t == 0 || t != s->verify_t) PB_FAIL(ctx, PB_ERR_STATE, "pb_keep: t=%d does not match the last verify window (%d)", t, s->verify_t);
     if (keep < 1 || keep > t) PB_FAIL(ctx, PB_ERR_ARG, "pb_keep: keep=%d outside 1..%d", keep, t);
     if (keep < t) {
-        for (int li = 0; li < s->m->n_lin; li++) {
-            PB_CUDA(ctx, cudaMemcpyAsync(s->conv[li], s->ck_conv[(size_t)li * PB_MAX_WINDOW + keep - 1], conv_elems(c, 1) * 4, cudaMemcpyDeviceToDevice, ctx->stream));
-            PB_CUDA(ctx, cudaMemcpyAsync(s->ssm[li], s->ck_ssm[(size_t)li * PB_MAX_WINDOW + keep - 1], ssm_elems(c, 1) * 4, cudaMemcpyDeviceToDevice, ctx->stream));
-        }
+        if (s->m->n_lin > 0) PB_TRY(pb_launch_ck_restore(ctx, s->ck_tab, s->ck_live, s->m->n_lin, PB_MAX_WINDOW, keep - 1, (int64_t)conv_elems(c, 1), (int64_t)ssm_elems(c, 1)));
         PB_TRY(pb_state_set_pos(s, s->verify_pos0 + keep));
         // the window moved the packed boundary to where its last token put it; the kept prefix may not have reached that far.
         // Back to the rule for the kept length (kv_push :1520): the f32 rows of the positions in between are still in the
         // ring (it holds kv_recent + 64 + a prompt chunk), and they are packed again, to the same bits, when their turn comes.
         if (c.kv_bits == 4 && !s->m->qsa) {
             const int64_t nk = s->verify_pos0 + keep, rule = nk > c.kv_recent ? ((nk - c.kv_recent) / 64) * 64 : 0;
-            for (int ai = 0; ai < s->m->n_attn; ai++) PB_CUDA(ctx, cudaMemcpyAsync(s->kv[ai].q4n, &rule, 8, cudaMemcpyHostToDevice, ctx->stream));
-            PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            std::vector<int64_t> rv((size_t)s->m->n_attn * s->batch, rule);
+            if (!rv.empty()) PB_CUDA(ctx, cudaMemcpy(s->q4n_all, rv.data(), rv.size() * 8, cudaMemcpyHostToDevice));
         }
     }
     s->verify_t = 0;
@@ -1586,7 +1593,7 @@ static int snap_read_q4(pb_state* s, std::vector<int64_t>& q4) {
     pb_ctx* ctx = s->m->ctx; const int B = s->batch;
     q4.assign((size_t)s->m->n_attn * B, 0);
     PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    for (int ai = 0; ai < s->m->n_attn; ai++) PB_CUDA(ctx, cudaMemcpy(q4.data() + (size_t)ai * B, s->kv[ai].q4n, (size_t)B * 8, cudaMemcpyDeviceToHost));
+    if (!q4.empty()) PB_CUDA(ctx, cudaMemcpy(q4.data(), s->q4n_all, q4.size() * 8, cudaMemcpyDeviceToHost));
     for (int64_t v : q4) if (v < 0 || v > s->pos_host || v % 64) PB_FAIL(ctx, PB_ERR_STATE, "packed KV boundary %lld does not fit the position %lld", (long long)v, (long long)s->pos_host);
     return PB_OK;
 }

@@ -156,6 +156,7 @@ int pb_launch_ple_gate(pb_ctx* ctx, const float* key, int64_t ldk, const float* 
                        float* gated, float* ring, int R, const int64_t* posv, int t, int window, int d, int streams, float eps);
 int pb_launch_ple_conv(pb_ctx* ctx, const float* gated, const float* ring, int R, const float* conv, int K, int dil, const int64_t* posv, int t, int window, const int64_t* base, float* x, int64_t ldx, int w);
 
+int pb_launch_ck_restore(pb_ctx* ctx, const float* const* tab, float* const* live, int n_lin, int stride, int idx, int64_t conv_n, int64_t ssm_n);
 struct PbGemvArgs {
     const uint8_t* w;   // first row of the matrix (16-byte aligned)
     const uint8_t* wr = nullptr;   // the same rows in the re-coded form (pb_qmat::rdata), or null

@@ -104,6 +104,27 @@ int pb_launch_advance(pb_ctx* ctx, int64_t* pos, int t, unsigned long long* keys
     return PB_OK;
 }
 
+// Rollback of a verify window: every DeltaNet layer's conv ring and recurrent state go back to the checkpoint taken after token
+// `idx` of the window.  tab[(li * stride + idx) * 2 + {0, 1}] = checkpoint of layer li (conv, ssm), live[li * 2 + {0, 1}] = the live
+// buffers.  grid (n_lin, 32), 256 threads; one launch instead of two copies per layer.
+__global__ void __launch_bounds__(256) pb_ck_restore_kernel(const float* const* __restrict__ tab, float* const* __restrict__ live, int stride, int idx, int64_t conv_n, int64_t ssm_n) {
+    const int li = blockIdx.x;
+    const float4* cs = reinterpret_cast<const float4*>(tab[((size_t)li * stride + idx) * 2]);
+    const float4* ss = reinterpret_cast<const float4*>(tab[((size_t)li * stride + idx) * 2 + 1]);
+    float4* cd = reinterpret_cast<float4*>(live[li * 2]);
+    float4* sd = reinterpret_cast<float4*>(live[li * 2 + 1]);
+    const int64_t step = (int64_t)gridDim.y * 256, i0 = (int64_t)blockIdx.y * 256 + threadIdx.x;
+    for (int64_t i = i0; i < conv_n / 4; i += step) cd[i] = cs[i];
+    for (int64_t i = i0; i < ssm_n / 4; i += step) sd[i] = ss[i];
+}
+int pb_launch_ck_restore(pb_ctx* ctx, const float* const* tab, float* const* live, int n_lin, int stride, int idx, int64_t conv_n, int64_t ssm_n) {
+    if (conv_n % 4 || ssm_n % 4) PB_FAIL(ctx, PB_UNSUPPORTED, "checkpoint restore: state sizes %lld / %lld are not multiples of four", (long long)conv_n, (long long)ssm_n);
+    pb_ck_restore_kernel<<<dim3(n_lin, 32), 256, 0, ctx->stream>>>(tab, live, stride, idx, conv_n, ssm_n);
+    ctx->kernels_launched++; ctx->pdl_chain = false;
+    PB_CUDA(ctx, cudaGetLastError());
+    return PB_OK;
+}
+
 // Window bookkeeping of a batch-1 state: advance == 0: wpos[j] = pos[0] + j for j < t; advance == 1: pos[0] += t.
 __global__ void pb_window_pos_kernel(int64_t* pos, int64_t* wpos, int t, int advance) {
     pb_pdl_wait();
