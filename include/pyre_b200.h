@@ -262,6 +262,13 @@ int pb_state_attach_drafter(pb_state* s, pb_model* drafter, const uint32_t* voca
  * Every emitted token still comes from pb_verify, so greedy output is unchanged by drafting.
  * Without an attached drafter: PB_UNSUPPORTED, and the caller's n-gram drafter takes over (src/spec.rs:207). */
 int pb_draft(pb_state* s, uint32_t pending, int max_draft, float min_p, uint32_t* ids_host, float* probs_host, int* n);
+/* Drafts drawn from the drafter's distribution (the reference's sampled drafts, mtp_qsample :3321-3331, used when the request's
+ * temperature is above 0, :2229-2246): after the min_p gate on the most probable token, `pick` -- the caller's sampler -- is handed the
+ * drafter's logits over the draft vocabulary (host memory, valid during the call) with the token of every row, and returns the token to
+ * draft; that token feeds the next step.  The caller keeps whatever it needs of the distribution for its acceptance test.  probs_host
+ * holds the probability of the most probable token of each step, as with pb_draft.  pick = NULL is pb_draft. */
+typedef uint32_t (*pb_draft_pick)(void* user, const float* logits, const uint32_t* vocab_ids, int n_ids);
+int pb_draft_sampled(pb_state* s, uint32_t pending, int max_draft, float min_p, pb_draft_pick pick, void* user, uint32_t* ids_host, float* probs_host, int* n);
 
 /* Model::snapshot / restore, Snap :3277-3298.  size query: pass buf_host = NULL. */
 int pb_state_snapshot(pb_state* s, void* buf_host, size_t* nbytes);

@@ -56,6 +56,7 @@ struct PbMtp {
     std::vector<uint32_t> tokens; int64_t tok_base = 0; // ids the main state has been fed, tokens[i] at position tok_base + i
     int64_t kv_c0 = 0, kv_end = 0;                      // the drafter holds cells [kv_c0, kv_end)
     std::vector<uint32_t> ids; int n_ids = 0;           // draft vocabulary
+    std::vector<float> lg_host;                         // the drafter's logits on their way to the caller's sampler (pb_draft_sampled)
     float *e_raw = nullptr, *en = nullptr, *e2 = nullptr, *hn = nullptr, *h2 = nullptr, *lg = nullptr;
     uint32_t *tok_dev = nullptr, *best = nullptr, *mask = nullptr; int* mask_on = nullptr;
     uint32_t* pin = nullptr;                            // pinned: [1..2] (index, probability bits) of a draft step, read back
@@ -1507,6 +1508,9 @@ static int mtp_cell(pb_state* s, const float* R, uint32_t tok, int64_t pos, bool
 // but not fed yet).  Token j > 0 is kept only while the drafter's probability of it is at least min_p (draft_gate, spec.rs:326).
 // *n = 0 when nothing can be drafted (no drafter state for the last position); PB_UNSUPPORTED without a drafter.
 int pb_draft(pb_state* s, uint32_t pending, int max_draft, float min_p, uint32_t* ids_host, float* probs_host, int* n) {
+    return pb_draft_sampled(s, pending, max_draft, min_p, nullptr, nullptr, ids_host, probs_host, n);
+}
+int pb_draft_sampled(pb_state* s, uint32_t pending, int max_draft, float min_p, pb_draft_pick pick, void* user, uint32_t* ids_host, float* probs_host, int* n) {
     if (!s || !n) return PB_ERR_ARG;
     pb_ctx* ctx = s->m->ctx;
     PB_TRY(pb_enter(ctx));
@@ -1551,7 +1555,14 @@ int pb_draft(pb_state* s, uint32_t pending, int max_draft, float min_p, uint32_t
         if (j == 0) t->kv_end = np;               // the cell of the last fed position stays (its token is `pending`)
         const uint32_t bi = t->pin[1]; float p; memcpy(&p, t->pin + 2, 4);
         if (j > 0 && p < min_p) break;            // draft_gate
-        const uint32_t id = t->ids[bi < (uint32_t)t->n_ids ? bi : (uint32_t)t->n_ids - 1];
+        uint32_t id = t->ids[bi < (uint32_t)t->n_ids ? bi : (uint32_t)t->n_ids - 1];
+        if (pick) {   // :2246: the caller's sampler draws from the drafter's distribution
+            if ((size_t)t->n_ids > t->lg_host.size()) t->lg_host.resize((size_t)t->n_ids);
+            PB_CUDA(ctx, cudaMemcpyAsync(t->lg_host.data(), t->lg, (size_t)t->n_ids * 4, cudaMemcpyDeviceToHost, ctx->stream));
+            PB_TRY(pb_sync_check(ctx, "pb_draft_sampled"));
+            id = pick(user, t->lg_host.data(), t->ids.data(), t->n_ids);
+            if (id >= (uint32_t)s->m->cfg.vocab) PB_FAIL(ctx, PB_ERR_ARG, "pb_draft_sampled: the sampler returned token %u, outside the vocabulary", id);
+        }
         ids_host[made] = id; if (probs_host) probs_host[made] = p;
         made++;
         r = t->ds->x; tok = id;                   // the drafter's own residual feeds its next step

@@ -137,10 +137,10 @@ __global__ void __launch_bounds__(256) pb_xh_prep_kernel(const PbGemvQParams p, 
     const float* z = p.z ? p.z + (size_t)(ti * tile + b) * p.ldz : nullptr;
     uint8_t* xh = xbuf + (size_t)ti * tile_stride + 256;
     float* xinv = reinterpret_cast<float*>(xbuf + (size_t)ti * tile_stride);
-    if (tid == 0) xinv[b] = 1.0f;
+    if (tid == 0 && blockIdx.y == 0) xinv[b] = 1.0f;
     if (p.mode == PB_ACT_GNORM) {
-        const int nheads = cols / p.head_dim;   // head_dim == 128 (checked on the host)
-        for (int h = warp; h < nheads; h += 8) {
+        const int nheads = cols / p.head_dim;   // head_dim == 128 (checked on the host); the heads are spread over grid.y
+        for (int h = warp + 8 * (int)blockIdx.y; h < nheads; h += 8 * (int)gridDim.y) {
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (live) {
                 v = *reinterpret_cast<const float4*>(x + h * p.head_dim + 4 * lane);
@@ -383,7 +383,7 @@ int pb_launch_gemmh(pb_ctx* ctx, const PbGemvQArgs& a) {
         PbGemvQParams p;
         memset(&p, 0, sizeof p);
         p.bpr = a.cols / 256; p.x = a.x; p.ldx = a.ldx; p.t = a.t; p.mode = a.mode; p.norm_w = a.norm_w; p.z = a.z; p.ldz = a.ldz; p.head_dim = a.head_dim; p.eps = a.eps;
-        pb_launch_k(ctx, pb_xh_prep_kernel, dim3(ntiles * tile), dim3(256), (size_t)0, p, ctx->xh_buf, tile, tile_stride);
+        pb_launch_k(ctx, pb_xh_prep_kernel, dim3(ntiles * tile, p.mode == PB_ACT_GNORM ? 4 : 1), dim3(256), (size_t)0, p, ctx->xh_buf, tile, tile_stride);
         ctx->kernels_launched++;
         PB_CUDA(ctx, cudaGetLastError());
     }

@@ -122,6 +122,19 @@ class State:
         self.ctx.check(lib().pb_draft(self.h, C.c_uint32(pending), C.c_int(max_draft), C.c_float(min_p), _p(ids), _p(probs), C.byref(n)))
         return ids[:n.value].copy(), probs[:n.value].copy()
 
+    def draft_sampled(self, pending: int, max_draft: int, min_p: float, pick):
+        """As draft(), with every drafted token chosen by `pick(logits, vocab_ids) -> token id` from the drafter's logits over
+        the draft vocabulary (the reference's sampled drafts, mtp_qsample, qwen4exp_gguf.rs:3321-3331)."""
+        ids = np.zeros(max(max_draft, 1), np.uint32); probs = np.zeros(max(max_draft, 1), np.float32); n = C.c_int(0)
+        PICK = C.CFUNCTYPE(C.c_uint32, C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_uint32), C.c_int)
+
+        def tramp(_user, lg, vid, n_ids):
+            return int(pick(np.ctypeslib.as_array(lg, shape=(n_ids,)).copy(), np.ctypeslib.as_array(vid, shape=(n_ids,)).copy()))
+
+        cb = PICK(tramp)
+        self.ctx.check(lib().pb_draft_sampled(self.h, C.c_uint32(pending), C.c_int(max_draft), C.c_float(min_p), cb, None, _p(ids), _p(probs), C.byref(n)))
+        return ids[:n.value].copy(), probs[:n.value].copy()
+
     def spec_keep(self, t: int, keep: int):
         self.ctx.check(lib().pb_keep(self.h, C.c_int(t), C.c_int(keep)))
 

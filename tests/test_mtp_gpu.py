@@ -70,7 +70,7 @@ class OracleDrafter:
         self.R = {p: r for p, r in self.R.items() if p < n}
         self.end = min(self.end, n); self.c0 = min(self.c0, self.end)
 
-    def draft(self, pending, k, min_p):
+    def draft(self, pending, k, min_p, pick=None):
         n = len(self.tokens)
         if n == 0 or (n - 1) not in self.R:
             return [], []
@@ -95,8 +95,9 @@ class OracleDrafter:
             bi = int(np.argmax(lg)); p = float(1.0 / np.exp(lg.astype(np.float64) - lg[bi]).sum())
             if j > 0 and p < min_p:
                 break
-            out.append(int(self.ids[bi])); probs.append(p)
-            r, tok = rr, int(self.ids[bi])
+            tid = int(self.ids[bi]) if pick is None else int(pick(lg, self.ids))
+            out.append(tid); probs.append(p)
+            r, tok = rr, tid
         return out, probs
 
 
@@ -230,3 +231,57 @@ def test_drafter_loaded_from_its_tensor_file_matches_the_oracle(ctx, tmp_path):
         pending = int(np.argmax(lo))
     assert ctx.device_status() == 0
     head.free(); st.destroy(); m.destroy(); dm.destroy()
+
+
+def _qsample(temperature, rng):
+    """mtp_qsample (qwen4exp_gguf.rs:3321-3331): softmax at the temperature over the 64 largest logits, one uniform draw."""
+    def pick(lg, ids):
+        n = min(len(lg), len(ids)); kk = min(64, n)
+        ix = np.argsort(-lg[:n], kind="stable")[:kk]
+        w = np.exp((lg[ix] - lg[ix].max()) / max(temperature, 1e-3)); q = w / w.sum()
+        u, choice = rng.random(), int(ids[ix[0]])
+        for i, pr in zip(ix, q):
+            choice = int(ids[i])
+            if u < pr:
+                break
+            u -= pr
+        return choice
+    return pick
+
+
+def test_sampled_drafts_follow_the_callers_sampler(ctx):
+    """pb_draft_sampled hands the drafter's logits to the caller's sampler after the gate; with the same sampler and the same random
+    draws the engine and the oracle's drafter produce the same drafts, and they differ from the greedy drafts."""
+    cfg, m, om, mats, cfg_d, dm, odm, dmats, ids = _build(ctx)
+    st, ost = m.new_state(1), om.new_state()
+    st.attach_drafter(dm, ids)
+    od = OracleDrafter(om, mats, odm, dmats, ids, WINDOW)
+    prompt = list(range(300, 312))
+    st.forward(np.array(prompt, np.uint32))
+    lo = ost.forward(prompt); od.fed(ost, prompt)
+    pending = int(np.argmax(lo))
+    greedy, _ = st.draft(pending, 4, 0.0)
+    seen = []
+
+    def spy(lg, vid):
+        seen.append((lg.copy(), vid.copy()))
+        return _qsample(1.5, np.random.default_rng(100 + len(seen)))(lg, vid)
+
+    g_ids, g_p = st.draft_sampled(pending, 4, 0.0, spy)
+    calls = [0]
+
+    def opick(lg, vid):
+        calls[0] += 1
+        return _qsample(1.5, np.random.default_rng(100 + calls[0]))(seen[calls[0] - 1][0], vid)   # the engine's logits: same draw, same token
+
+    o_ids, o_p = od.draft(pending, 4, 0.0, opick)
+    assert g_ids.tolist() == o_ids and len(o_ids) == 4
+    assert np.allclose(g_p, o_p, rtol=2e-3, atol=1e-6)
+    assert np.array_equal(seen[0][1], ids) and seen[0][0].shape == (N_IDS,)
+    # the oracle's own logits of the first step agree with the ones the sampler was handed
+    s0, _ = od.ds.mtp_cell(od.R[len(prompt) - 1], od.embd[pending], len(prompt) - 1, od.c0, WINDOW, True)
+    assert rel_err(seen[0][0], dmats[(-1, "OUTPUT")].matmul(s0)[0]) < 2e-3
+    assert g_ids.tolist() != greedy.tolist()
+    with pytest.raises(pb.PyreError):
+        st.draft_sampled(pending, 2, 0.0, lambda lg, vid: cfg.vocab + 5)      # a sampler that answers outside the vocabulary
+    assert ctx.device_status() == 0
