@@ -90,6 +90,12 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool st_first = tid == 0 && blockIdx.x == 0 && blockIdx.y == 0;
     pb_stamp(p.stamps, 0, st_first);
+    // the warp's router row (times the norm weight) is model data: it is fetched before the wait for the previous kernel, so its
+    // trip to DRAM overlaps that kernel's tail
+    const int row = blockIdx.x * 8 + warp;
+    const float* wrow = p.phase != 2 && row <= p.n_exp ? (row < p.n_exp ? p.router + (size_t)row * p.cols : p.sh_gate_inp) : nullptr;
+    PbRouterRow2048 rr;
+    if (p.cols == 2048 && wrow) rr.load(wrow, p.norm_w, lane);
     pb_pdl_wait();
     pb_pdl_trigger();
     pb_stamp(p.stamps, 2, st_first);
@@ -126,13 +132,9 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
         }
     }
     pb_stamp(p.stamps, 3, st_first);   // activations split
-    const int row = blockIdx.x * 8 + warp;
     if (p.phase != 2 && row <= p.n_exp) {
-        const float* wrow = row < p.n_exp ? p.router + (size_t)row * p.cols : p.sh_gate_inp;
         if (p.cols == 2048 && wrow) {
             // the row, times the norm weight, stays in registers for all tokens
-            PbRouterRow2048 rr;
-            rr.load(wrow, p.norm_w, lane);
 #pragma unroll 2
             for (int b = b_lo; b < b_hi; b++) {
                 const float acc = rr.dot(p.x + b * p.ldx, scale[b], lane);
