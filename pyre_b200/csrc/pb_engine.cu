@@ -1362,6 +1362,7 @@ int pb_verify(pb_state* s, const uint32_t* ids_host, int t, float* logits_host) 
     PB_TRY(pb_enter(ctx));
     if (!ids_host || !logits_host) PB_FAIL(ctx, PB_ERR_ARG, "pb_verify: null buffer");
     if (s->batch != 1) PB_FAIL(ctx, PB_ERR_STATE, "pb_verify: the state must have batch 1 (it has %d)", s->batch);
+    if (s->sharded) PB_FAIL(ctx, PB_UNSUPPORTED, "pb_verify: a sharded state holds the rows of one token per sequence; windows run on a plain batch-1 state");
     if (t < 1 || t > PB_MAX_WINDOW) PB_FAIL(ctx, PB_ERR_ARG, "pb_verify: window of %d tokens (1..%d)", t, PB_MAX_WINDOW);
     if (s->pos_host + t > c.max_ctx) PB_FAIL(ctx, PB_ERR_STATE, "context is full (%d positions)", c.max_ctx);
     const int nl = s->m->n_lin;
