@@ -80,7 +80,8 @@ int pb_ctx_create(int device, pb_ctx** out) {
     *c->host_status = 0;
     c->owner_thread = (unsigned long)pthread_self();
     { const char* e = getenv("PYRE_B200_CHECK_THREAD"); c->check_thread = e && e[0] == '1'; }
-    { const char* e = getenv("PYRE_B200_PDL"); if (e && e[0] == '0') c->use_pdl = false; }   // PYRE_B200_PDL=0: plain stream order inside the token step
+    { const char* e = getenv("PYRE_B200_PDL"); if (e && e[0] == '0') c->use_pdl = false; }
+    { const char* e = getenv("PYRE_B200_STEP_PDL"); c->step_pdl = c->use_pdl && !(e && e[0] == '0'); }   // PYRE_B200_STEP_PDL=0: the fused step kernel stays outside the chain   // PYRE_B200_PDL=0: plain stream order inside the token step
     *out = c;
     return PB_OK;
 }

@@ -27,6 +27,7 @@ struct pb_ctx {
     // expert-parallel group (pb_ep.cu); ep_comm is an ncclComm_t
     // programmatic dependent launch is used only inside the token step, where every stream op is ours
     bool use_pdl = true;
+    bool step_pdl = true;    // the fused step kernel takes part in the dependent-launch chain (PYRE_B200_STEP_PDL=0: it does not)
     int pdl_scope = 0;       // > 0 while run_step is issuing launches
     bool pdl_chain = false;  // the previous op on the stream was one of our kernels
     void* ep_comm = nullptr;

@@ -633,6 +633,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) pb_step_kernel(const PsParams P
         c.m->abort = 0; c.m->route_seq = 0;
         pb_fence_barrier_init();
     }
+    pb_pdl_trigger();   // the kernel after this one may become resident; it waits for this grid to complete before it reads anything of it
     uint8_t* opslot = smem + PS_OPBUF_OFF + c.warp * 256;
     PsOpFetch fetch;
     fetch.request(P.ops, P.op_begin, P.op_end, c.lane);
@@ -697,6 +698,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) pb_step_kernel(const PsParams P
     }
 
     // ---- consumers
+    pb_pdl_wait();   // the activations come from the kernel before this one (the weights, streamed by the producer warp, do not)
     bool ok = true;
     for (int i = P.op_begin; i < P.op_end && ok; i++) {
         const PbStepOp& op = fetch.take(opslot, c.lane);
@@ -722,11 +724,17 @@ int pb_launch_step(pb_ctx* ctx, const PsParams& p) {
     memset(&cfg, 0, sizeof cfg);
     cfg.gridDim = dim3(ctx->sm_count); cfg.blockDim = dim3(PS_THREADS); cfg.dynamicSmemBytes = p.lay.total; cfg.stream = ctx->stream;
     // the CTAs wait on one another: a cooperative launch guarantees that all of them are resident
-    cudaLaunchAttribute at[1];
+    cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeCooperative;
     at[0].val.cooperative = 1;
-    cfg.attrs = at; cfg.numAttrs = 1;
-    ctx->pdl_chain = false;   // a cooperative launch is not chained with programmatic stream serialization
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    // With step_pdl the kernel joins the dependent-launch chain on both sides: its set-up and the first weight copies (model data)
+    // overlap the tail of the kernel before it, and the kernel after it is resident by the time this one ends.  Without, a
+    // cooperative launch waits for the stream to drain and the next kernel for this one.
+    const bool chain = ctx->step_pdl && ctx->pdl_scope > 0;
+    cfg.attrs = at; cfg.numAttrs = chain && ctx->pdl_chain ? 2 : 1;
+    ctx->pdl_chain = chain;
     cudaError_t e = cudaLaunchKernelEx(&cfg, pb_step_kernel, p);
     if (e != cudaSuccess) PB_FAIL(ctx, PB_ERR_CUDA, "fused step launch: %s", cudaGetErrorString(e));
     ctx->kernels_launched++;
