@@ -197,6 +197,7 @@ int pb_model_set_ctx_train(pb_model* m, int ctx_train);
 /* attach_gpu :555-657.  ep_rank/ep_world: this GPU holds routed experts
  * [ep_rank*n_exp/ep_world, (ep_rank+1)*n_exp/ep_world) of every layer; dense tensors are replicated. */
 int pb_model_finalize(pb_model* m, int ep_rank, int ep_world);
+int pb_model_cfg(const pb_model* m, pb_cfg* out);   /* the configuration the model was created with (Model.cfg) */
 int pb_model_destroy(pb_model* m);
 
 /* new_state :1345-1353; `batch` independent sequences decode together. */

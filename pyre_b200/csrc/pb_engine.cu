@@ -432,6 +432,7 @@ int pb_model_finalize(pb_model* m, int ep_rank, int ep_world) {
     return PB_OK;
 }
 
+int pb_model_cfg(const pb_model* m, pb_cfg* out) { if (!m || !out) return PB_ERR_ARG; *out = m->cfg; return PB_OK; }
 int pb_model_destroy(pb_model* m) {
     if (!m) return PB_OK;
     cudaSetDevice(m->ctx->device);
