@@ -161,6 +161,34 @@ __global__ void __launch_bounds__(AT_THREADS) pb_kv_append_kernel(const PbAttnPa
     const float* vraw = kraw + (size_t)nkv * hd;
     const int64_t slot = pos % p.ring_cap;
     __shared__ float sc[8];
+    if (hd == 256 && p.n_rot == 64) {
+        // the model's head shape: a lane owns dims lane + 32 k of the head.  All of its loads are issued before anything is
+        // computed (the loop below pays a trip to L2 per iteration), the rope partner of dim i < 32 is the same lane's
+        // dim i + 32, and both use the same angle: one sincosf per lane.  Same arithmetic as the general loop.
+        for (int h = warp; h < nkv; h += AT_WARPS) {
+            float kv[8], wn[8], vv[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) { kv[k] = kraw[h * hd + lane + 32 * k]; wn[k] = p.kn[lane + 32 * k]; vv[k] = vraw[h * hd + lane + 32 * k]; }
+            const float ang = (float)pos * p.rope_inv[lane], ms = p.rope_inv[half];
+            float ss = 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; k++) ss += kv[k] * kv[k];
+            ss = pb_warp_sum(ss);
+            const float s = 1.0f / sqrtf(ss / (float)hd + p.eps);
+            float sn, co;
+            sincosf(ang, &sn, &co);
+            if (ms != 1.0f) { co *= ms; sn *= ms; }
+            float* kd = p.kr + (((size_t)cb * nkv + h) * p.ring_cap + slot) * hd;
+            float* vd = p.vr + (((size_t)cb * nkv + h) * p.ring_cap + slot) * hd;
+            const float x0 = kv[0] * (s * wn[0]), x1 = kv[1] * (s * wn[1]);
+            kd[lane] = x0 * co - x1 * sn;
+            kd[lane + 32] = x1 * co + x0 * sn;
+#pragma unroll
+            for (int k = 2; k < 8; k++) kd[lane + 32 * k] = kv[k] * (s * wn[k]);
+#pragma unroll
+            for (int k = 0; k < 8; k++) vd[lane + 32 * k] = vv[k];
+        }
+    } else
     for (int h = warp; h < nkv; h += AT_WARPS) {
         float ss = 0.f;
         for (int i = lane; i < hd; i += 32) { const float v = kraw[h * hd + i]; ss += v * v; }
@@ -426,6 +454,30 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
     float* mrg = reinterpret_cast<float*>(stage_base);
 
     // queries of this GQA group: rms_inplace(q, qn), rope, times 1/sqrt(hd)  (:1603-1606)
+    if (hd == 256 && p.n_rot == 64) {
+        // as in pb_kv_append_kernel: the loads of a head up front, one sincosf per lane
+        for (int g = warp; g < G; g += AT_WARPS) {
+            const float* qraw = proj + (size_t)(kvh * G + g) * 2 * hd;
+            float qv[8], wn[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) { qv[k] = qraw[lane + 32 * k]; wn[k] = p.qn[lane + 32 * k]; }
+            const float ang = (float)pos * p.rope_inv[lane], ms = p.rope_inv[half];
+            float ss = 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; k++) ss += qv[k] * qv[k];
+            ss = pb_warp_sum(ss);
+            const float s = 1.0f / sqrtf(ss / (float)hd + p.eps);
+            const float scale = 1.0f / sqrtf((float)hd);
+            float sn, co;
+            sincosf(ang, &sn, &co);
+            if (ms != 1.0f) { co *= ms; sn *= ms; }
+            const float x0 = qv[0] * (s * wn[0]), x1 = qv[1] * (s * wn[1]);
+            qs[g * hd + lane] = (x0 * co - x1 * sn) * scale;
+            qs[g * hd + lane + 32] = (x1 * co + x0 * sn) * scale;
+#pragma unroll
+            for (int k = 2; k < 8; k++) qs[g * hd + lane + 32 * k] = (qv[k] * (s * wn[k])) * scale;
+        }
+    } else
     for (int g = warp; g < G; g += AT_WARPS) {
         const int h = kvh * G + g;
         const float* qraw = proj + (size_t)h * 2 * hd;
@@ -661,23 +713,36 @@ __global__ void __launch_bounds__(1024) pb_attn_combine_kernel(const PbAttnParam
     const size_t base = ((size_t)b * p.n_kv + kvh) * p.nsplit;
     if (threadIdx.x < 32) {
         const int l = threadIdx.x;
-        float M = -INFINITY;
-        for (int s = l; s < p.nsplit; s += 32) M = fmaxf(M, p.part_ml[((base + s) * G + g) * 2]);
+        // a lane's (up to four: nsplit <= 128) splits, maximum and sum of each, fetched in one go
+        float2 ml[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int s = l + 32 * k;
+            ml[k] = s < p.nsplit ? *reinterpret_cast<const float2*>(p.part_ml + ((base + s) * G + g) * 2) : make_float2(-INFINITY, 0.f);
+        }
+        float M = fmaxf(fmaxf(ml[0].x, ml[1].x), fmaxf(ml[2].x, ml[3].x));
         M = pb_warp_max(M);
         float L = 0.f;
-        for (int s = l; s < p.nsplit; s += 32) {
-            const float m = p.part_ml[((base + s) * G + g) * 2];
-            const float f = m == -INFINITY ? 0.f : expf(m - M);
-            fs[s] = f;
-            L += p.part_ml[((base + s) * G + g) * 2 + 1] * f;
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int s = l + 32 * k;
+            if (s < p.nsplit) {
+                const float f = ml[k].x == -INFINITY ? 0.f : expf(ml[k].x - M);
+                fs[s] = f;
+                L += ml[k].y * f;
+            }
         }
         L = pb_warp_sum(L);
         if (l == 0) { ML[0] = M; ML[1] = L; }
     }
+    // this thread's rows of the splits' accumulators are requested before the factors are awaited
+    float pa[32];
+#pragma unroll
+    for (int k = 0; k < 32; k++) { const int s = q + 4 * k; pa[k] = s < p.nsplit ? p.part_acc[((base + s) * G + g) * p.hd + d] : 0.f; }
     __syncthreads();
     float o = 0.f;
-#pragma unroll 4
-    for (int s = q; s < p.nsplit; s += 4) o = fmaf(p.part_acc[((base + s) * G + g) * p.hd + d], fs[s], o);
+#pragma unroll
+    for (int k = 0; k < 32; k++) { const int s = q + 4 * k; if (s < p.nsplit) o = fmaf(pa[k], fs[s], o); }
     if (q > 0) part[q - 1][d] = o;
     __syncthreads();
     if (q == 0) {
