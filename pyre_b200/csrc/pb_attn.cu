@@ -519,12 +519,12 @@ __global__ void __launch_bounds__(AT_THREADS, 1) pb_attn_partial_kernel(const Pb
     uint32_t* tkw = stage_base + (size_t)warp * AT_STAGE_WORDS;
     // Share of the splits that walk the packed positions on the tensor cores (p.nsplit_packed > 0 enables that
     // path), by estimated work at the sequence's current length: an f32 tile of 8 positions costs about two
-    // packed tiles of 32.  Computed here, from the position and the packed boundary the device holds, so that a
+    // and a half packed tiles of 32 (p.ring_weight).  Computed here, from the position and the packed boundary the device holds, so that a
     // captured graph keeps the right share however far the context has grown since its capture.
     int nsp = 0;
     if (p.nsplit_packed > 0) {
         const int64_t q4 = q4n < n ? q4n : n;
-        const float wp = (float)(q4 / 32), wr = 2.0f * (float)((n - q4 + 7) / 8);
+        const float wp = (float)(q4 / 32), wr = p.ring_weight * (float)((n - q4 + 7) / 8);
         int nr = (int)((float)gridDim.x * wr / (wr + wp) + 0.5f);
         nr = nr < 1 ? 1 : (nr > (int)gridDim.x - 1 ? (int)gridDim.x - 1 : nr);
         nsp = (int)gridDim.x - nr;

@@ -727,6 +727,7 @@ static void attn_params(pb_state* s, int il, PbAttnParams& p) {
     p.kw = k.kw; p.ks = k.ks; p.vw = k.vw; p.vs = k.vs; p.kr = k.kr; p.vr = k.vr;
     p.max_ctx = c.kv_bits == 4 ? c.max_ctx : 1; p.ring_cap = s->ring_cap; p.kv_bits = c.kv_bits; p.kv_recent = c.kv_recent;
     p.pos = s->pos; p.q4n = k.q4n; p.part_ml = s->part_ml; p.part_acc = s->part_acc; p.nsplit = s->nsplit; p.nsplit_packed = s->nsplit_packed;
+    { static const float rw = getenv("PYRE_B200_ATTN_RINGW") ? (float)atof(getenv("PYRE_B200_ATTN_RINGW")) : 2.5f; p.ring_weight = rw > 0.f ? rw : 2.5f; }   // measured: 2.5 .. 3.5 give the shortest batch-1 step, 2 .. 2.5 the shortest batch-32 step
     p.att = s->att; p.lda = (int64_t)c.n_head * c.hd; p.batch = s->batch;
 }
 

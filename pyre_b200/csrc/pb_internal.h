@@ -307,6 +307,7 @@ struct PbAttnParams {
     const int64_t* pos; int64_t* q4n;                    // [batch]
     float* part_ml; float* part_acc; int nsplit;
     int nsplit_packed;                                   // splits [0, nsplit_packed) walk the packed positions on the tensor cores
+    float ring_weight;                                   // cost of a scalar tile of 8 f32 positions in packed tiles of 32 (split shares)
     float* att; int64_t lda;                             // [batch][n_head*hd]
     int batch;
     // window: the `batch` entries are consecutive tokens of sequence 0 (a prefill chunk): they share its cache; the append
