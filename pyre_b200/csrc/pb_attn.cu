@@ -735,7 +735,8 @@ __global__ void __launch_bounds__(1024) pb_attn_combine_kernel(const PbAttnParam
         L = pb_warp_sum(L);
         if (l == 0) { ML[0] = M; ML[1] = L; }
     }
-    // this thread's rows of the splits' accumulators are requested before the factors are awaited
+    // this thread's rows of the splits' accumulators (and its gate value) are requested before the factors are awaited
+    const float gate_raw = q == 0 ? p.proj[(size_t)b * p.ldp + (size_t)h * 2 * p.hd + p.hd + d] : 0.f;
     float pa[32];
 #pragma unroll
     for (int k = 0; k < 32; k++) { const int s = q + 4 * k; pa[k] = s < p.nsplit ? p.part_acc[((base + s) * G + g) * p.hd + d] : 0.f; }
@@ -747,8 +748,7 @@ __global__ void __launch_bounds__(1024) pb_attn_combine_kernel(const PbAttnParam
     __syncthreads();
     if (q == 0) {
         o = ((o + part[0][d]) + part[1][d]) + part[2][d];
-        const float gate = p.proj[(size_t)b * p.ldp + (size_t)h * 2 * p.hd + p.hd + d];
-        p.att[(size_t)b * p.lda + (size_t)h * p.hd + d] = (o * (1.0f / ML[1])) * pb_sigm(gate);
+        p.att[(size_t)b * p.lda + (size_t)h * p.hd + d] = (o * (1.0f / ML[1])) * pb_sigm(gate_raw);
     }
 }
 
