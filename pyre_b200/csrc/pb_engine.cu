@@ -546,7 +546,8 @@ static int state_create(pb_model* m, int batch, bool sharded, pb_state** out) {
         else {
             // many (sequence, KV head) pairs: several CTAs per SM's worth of work, so that the tail wave stays short
             int fine = 8 * ctx->sm_count / (c.n_kv * B);
-            if (fine > 16) fine = 16;
+            static const int fine_cap = getenv("PYRE_B200_ATTN_FINE") ? atoi(getenv("PYRE_B200_ATTN_FINE")) : 16;
+            if (fine > fine_cap) fine = fine_cap;
             s->nsplit_packed = fine > ns ? fine : ns;
             ns = s->nsplit_packed + 1;
         }
