@@ -22,8 +22,26 @@
 
 #define QSA_MAX_HD 256
 
-// rms_inplace(x, w) then rope at `pos` over the first n_rot dims, for a vector held by a warp (lane l: dims l, l + 32, ...)
-__device__ __forceinline__ void pb_qsa_norm_rope(float* v, const float* w, const float* rope_inv, int n, int n_rot, float eps, int64_t pos, int lane) {
+// sine and cosine (times the YaRN mscale) of this lane's rope angles at `pos`: dims lane and lane + 32 (rotary halves of up to 64)
+struct PbQsaAngles { float sn[2], co[2]; };
+__device__ __forceinline__ PbQsaAngles pb_qsa_angles(const float* rope_inv, int n_rot, int64_t pos, int lane) {
+    PbQsaAngles a;
+    const int half = n_rot / 2;
+    const float ms = rope_inv[half];
+#pragma unroll
+    for (int k = 0; k < 2; k++) {
+        a.sn[k] = 0.f; a.co[k] = 1.f;
+        const int i = lane + 32 * k;
+        if (i < half) {
+            sincosf((float)pos * rope_inv[i], &a.sn[k], &a.co[k]);
+            if (ms != 1.0f) { a.co[k] *= ms; a.sn[k] *= ms; }
+        }
+    }
+    return a;
+}
+// rms_inplace(x, w) then rope over the first n_rot dims (n_rot <= 128) with the lane's angles, for a vector held by a warp
+// (lane l: dims l, l + 32, ...)
+__device__ __forceinline__ void pb_qsa_norm_rope_a(float* v, const float* w, int n, int n_rot, float eps, const PbQsaAngles& a, int lane) {
     float ss = 0.f;
     for (int i = lane; i < n; i += 32) ss += v[i] * v[i];
     ss = pb_warp_sum(ss);
@@ -32,15 +50,18 @@ __device__ __forceinline__ void pb_qsa_norm_rope(float* v, const float* w, const
     for (int i = lane; i < n; i += 32) v[i] *= s * w[i];
     __syncwarp();
     const int half = n_rot / 2;
-    const float ms = rope_inv[half];
-    for (int i = lane; i < half; i += 32) {
-        float sn, co;
-        sincosf((float)pos * rope_inv[i], &sn, &co);
-        if (ms != 1.0f) { co *= ms; sn *= ms; }
-        const float x0 = v[i], x1 = v[i + half];
-        v[i] = x0 * co - x1 * sn; v[i + half] = x1 * co + x0 * sn;
+#pragma unroll
+    for (int k = 0; k < 2; k++) {
+        const int i = lane + 32 * k;
+        if (i < half) {
+            const float x0 = v[i], x1 = v[i + half];
+            v[i] = x0 * a.co[k] - x1 * a.sn[k]; v[i + half] = x1 * a.co[k] + x0 * a.sn[k];
+        }
     }
     __syncwarp();
+}
+__device__ __forceinline__ void pb_qsa_norm_rope(float* v, const float* w, const float* rope_inv, int n, int n_rot, float eps, int64_t pos, int lane) {
+    pb_qsa_norm_rope_a(v, w, n, n_rot, eps, pb_qsa_angles(rope_inv, n_rot, pos, lane), lane);
 }
 
 // pooled key of block `blk` of one sequence from its raw keys (one warp)
@@ -100,7 +121,10 @@ __global__ void __launch_bounds__(QSA_TILE) pb_qsa_score_kernel(const PbQsaParam
     const float* iq = p.iproj + (size_t)b * p.ldi;
     for (int i = tid; i < p.inh * ihd; i += QSA_TILE) qsm[i] = iq[i];
     __syncthreads();
-    for (int h = warp; h < p.inh; h += QSA_TILE / 32) pb_qsa_norm_rope(qsm + h * ihd, p.iqn, p.rope_inv, ihd, p.n_rot, p.eps, pos, lane);
+    {   // the heads share the position: one pair of sincosf per lane for all of them
+        const PbQsaAngles ang = pb_qsa_angles(p.rope_inv, p.n_rot, pos, lane);
+        for (int h = warp; h < p.inh; h += QSA_TILE / 32) pb_qsa_norm_rope_a(qsm + h * ihd, p.iqn, ihd, p.n_rot, p.eps, ang, lane);
+    }
     float* tile = qsm + p.inh * ihd;
     const int ld = ihd + 4;                                 // rows stay 16-byte aligned; eight rows fall into eight groups of four banks
     const int sb = p.shared_seq ? 0 : b;
@@ -236,7 +260,7 @@ __global__ void __launch_bounds__(1024) pb_qsa_pick_kernel(const PbQsaParams p) 
 }
 
 int pb_launch_qsa_append(pb_ctx* ctx, const PbQsaParams& p) {
-    if (p.ihd > QSA_MAX_HD || p.ihd % 8 || p.n_rot > p.ihd) PB_FAIL(ctx, PB_UNSUPPORTED, "indexer head dim %d (a multiple of 8, at least the rope width %d, at most %d)", p.ihd, p.n_rot, QSA_MAX_HD);
+    if (p.ihd > QSA_MAX_HD || p.ihd % 8 || p.n_rot > p.ihd || p.n_rot > 128) PB_FAIL(ctx, PB_UNSUPPORTED, "indexer head dim %d (a multiple of 8, at least the rope width %d <= 128, at most %d)", p.ihd, p.n_rot, QSA_MAX_HD);
     pb_launch_k(ctx, pb_qsa_append_kernel, dim3(p.batch), dim3(32), (size_t)0, p);
     ctx->kernels_launched++;
     PB_CUDA(ctx, cudaGetLastError());
@@ -244,7 +268,7 @@ int pb_launch_qsa_append(pb_ctx* ctx, const PbQsaParams& p) {
 }
 
 int pb_launch_qsa_select(pb_ctx* ctx, const PbQsaParams& p) {
-    if (p.ihd % 32) PB_FAIL(ctx, PB_UNSUPPORTED, "indexer head dim %d (a multiple of 32)", p.ihd);
+    if (p.ihd % 32 || p.n_rot > 128) PB_FAIL(ctx, PB_UNSUPPORTED, "indexer head dim %d (a multiple of 32), rope width %d (at most 128)", p.ihd, p.n_rot);
     int tile_rows = QSA_TILE;
     auto need = [&](int rows) { return ((size_t)p.inh * p.ihd + (size_t)2 * rows * (p.ihd + 4)) * 4; };
     while (need(tile_rows) > 96 * 1024 && tile_rows > 8) tile_rows /= 2;
@@ -265,6 +289,7 @@ int pb_launch_qsa_select(pb_ctx* ctx, const PbQsaParams& p) {
 
 int pb_launch_qsa_pool_all(pb_ctx* ctx, const PbQsaParams& p, int64_t nblk) {
     if (nblk <= 0) return PB_OK;
+    if (p.ihd > QSA_MAX_HD || p.n_rot > p.ihd || p.n_rot > 128) PB_FAIL(ctx, PB_UNSUPPORTED, "indexer head dim %d, rope width %d (at most 128)", p.ihd, p.n_rot);
     const unsigned gx = (unsigned)(nblk < 1024 ? nblk : 1024);
     pb_qsa_pool_kernel<<<dim3(gx, p.batch), 32, 0, ctx->stream>>>(p, nblk);
     ctx->kernels_launched++;
