@@ -40,6 +40,61 @@ __device__ __forceinline__ void pb_route_tokens(const PbRouteParams& p, int b_lo
     }
 }
 
+// One token routed by all 256 threads of the CTA (the last router CTA), the scheme of the fused step kernel's routing: every logit
+// becomes a 64-bit key (pb_topk.cuh); pass 1: each warp ranks its own keys (n_exp / 8 of them) by counting the greater ones and
+// passes on its top_k; pass 2: the 8 * top_k candidates are ranked the same way, the counting of each cut over several threads;
+// rank j < top_k is the j-th pick, and warp 0 finishes as pb_route_token does (same picks, same weights, same order).  One warp
+// alone spends top_k rounds of a warp-wide maximum on this.  sm = 2048 ints of shared memory; n_exp <= 512, top_k <= 16.
+__device__ __forceinline__ void pb_route_token_cta(const PbRouteParams& p, int b, int* sm) {
+    unsigned long long* keys = reinterpret_cast<unsigned long long*>(sm);      // [8 warps][32 * kpt]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kpt = (p.n_exp + 255) / 256, gsz = 32 * kpt, top_k = p.top_k;   // kpt <= 2
+    unsigned long long* cand = keys + 8 * gsz;                                  // [8][top_k]
+    unsigned long long* pick = cand + 8 * 16;                                   // [top_k]
+    int* crank = reinterpret_cast<int*>(pick + 16);                             // [8 * top_k]
+    const float* lg = p.logits + (size_t)b * p.ldl;
+    if (tid < 8 * 16) crank[tid] = 0;
+    unsigned long long mine[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        mine[j] = 0;
+        if (j < kpt) {
+            const int e = tid + 256 * j;
+            mine[j] = e < p.n_exp ? pb_topk_key(__ldcg(lg + e), e) : (unsigned long long)(0xFFFFFFFFu - (unsigned)e);   // slots past n_exp: distinct keys below every real one
+            keys[warp * gsz + j * 32 + lane] = mine[j];
+        }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        if (j < kpt) {
+            int rk = 0;
+            for (int i = 0; i < gsz; i++) rk += keys[warp * gsz + i] > mine[j] ? 1 : 0;
+            if (rk < top_k) cand[warp * top_k + rk] = mine[j];
+        }
+    }
+    __syncthreads();
+    const int ncand = 8 * top_k, parts = 256 / ncand;   // parts >= 2: ncand <= 128
+    if (tid < ncand * parts) {
+        const int ci = tid % ncand, part = tid / ncand;
+        const int i0 = part * ncand / parts, i1 = (part + 1) * ncand / parts;
+        const unsigned long long key = cand[ci];
+        int rk = 0;
+#pragma unroll 4
+        for (int i = i0; i < i1; i++) rk += cand[i] > key ? 1 : 0;
+        if (rk) atomicAdd(&crank[ci], rk);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        for (int i = lane; i < ncand; i += 32) { const int rk = crank[i]; if (rk < top_k) pick[rk] = cand[i]; }
+        __syncwarp();
+        int my_e, rank; float w;
+        pb_route_finish(lane < top_k ? pick[lane] : 0ull, top_k, lane, my_e, w, rank);
+        if (lane < top_k) { p.sel_e[b * top_k + rank] = my_e; p.sel_w[b * top_k + rank] = w; }
+    }
+    __syncthreads();
+}
+
 // Runs in ONE CTA of 256 threads (the last router CTA to finish) once every token is routed: the list of distinct local
 // experts with their (token, slot) entries.  rsm = 2048 ints of shared memory.
 __device__ __forceinline__ void pb_route_lists(const PbRouteParams& p, int* rsm) {
@@ -175,7 +230,8 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
     if (tid == 0) ticket[PB_ROUTER_TICKETS + blockIdx.y] = 0;
     __threadfence();
     pb_stamp(p.stamps, 6, tid == 0 && blockIdx.y == 0);   // the routing pass of the first group starts (its logits are in)
-    pb_route_tokens(rp, b_lo, b_hi);
+    if (b_hi - b_lo == 1 && rp.top_k <= 16 && rp.n_exp >= rp.top_k && rp.n_exp <= 512) pb_route_token_cta(rp, b_lo, reinterpret_cast<int*>(rs));   // 512 experts: its keys and candidates fit the 8 KB
+    else pb_route_tokens(rp, b_lo, b_hi);
     if (gridDim.y > 1) {
         __threadfence();
         __syncthreads();
@@ -185,7 +241,18 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
         if (tid == 0) *ticket = 0;
         __threadfence();
     } else __syncthreads();   // one group: this CTA routed every token itself
-    pb_route_lists(rp, reinterpret_cast<int*>(rs));
+    if (rp.t == 1 && rp.top_k <= 32) {
+        // one token: its selection, already in ascending expert id, IS the list of distinct experts, one entry each (what
+        // pb_route_lists would build with its counting pass over all expert ids)
+        if (warp == 0) {
+            const int e = lane < rp.top_k ? __ldcg(rp.sel_e + lane) : -1;
+            const bool local = e >= rp.e_lo && e < rp.e_hi;
+            const unsigned m = __ballot_sync(0xffffffffu, local);
+            const int n = __popc(m & ((1u << lane) - 1u));
+            if (local) { rp.used_e[n] = e; rp.used_off[n] = n; rp.ent_tok[n] = 0; rp.ent_slot[n] = lane; rp.ent_w[n] = __ldcg(rp.sel_w + lane); }
+            if (lane == 0) { const int tot = __popc(m); rp.used_off[tot] = tot; *rp.n_used = tot; }
+        }
+    } else pb_route_lists(rp, reinterpret_cast<int*>(rs));
     __syncthreads();
     pb_stamp(p.stamps, 7, tid == 0);
 }

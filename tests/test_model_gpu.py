@@ -247,7 +247,7 @@ def test_contexts_on_two_devices_in_one_process():
 
 def _fused_cfg(**kw):
     """A scaled-down hybrid model whose every matrix has a re-coded copy, so that a batch-1 state takes its steps
-    through the fused step kernel (expert width 512; hidden 512)."""
+    through the fused step kernel when PYRE_B200_FUSED=1 asks for it (expert width 512; hidden 512)."""
     base = dict(n_layers=8, ff_exp=512, ff_sh=512, kv_bits=4, kv_recent=64, max_ctx=256)
     base.update(kw)
     return small_cfg(pb, **base)
@@ -255,16 +255,15 @@ def _fused_cfg(**kw):
 
 def test_fused_step_matches_per_operation_kernels_bit_for_bit(ctx, monkeypatch):
     """The fused step kernel runs the arithmetic of the per-operation kernels: logits and tokens must be identical,
-    not merely close.  PYRE_B200_FUSED=0 (read at a state's first step) keeps a state on the per-operation path."""
+    not merely close.  PYRE_B200_FUSED=1 (read at a state's first step) puts a state on the fused path."""
     cfg = _fused_cfg()
     spec = synth.model_spec(cfg, 11)
     m = synth.build_model(ctx, cfg, spec, 11)
-    fused = m.new_state(1)
-    monkeypatch.setenv("PYRE_B200_FUSED", "0")
-    plain = m.new_state(1)
-    lp = plain.forward([5])[0]                                   # first step decides the path of `plain`
+    fused, plain = m.new_state(1), m.new_state(1)
+    monkeypatch.setenv("PYRE_B200_FUSED", "1")
+    lf = fused.forward([5])[0]                                   # first step decides the path of `fused`
     monkeypatch.delenv("PYRE_B200_FUSED")
-    lf = fused.forward([5])[0]
+    lp = plain.forward([5])[0]
     assert fused.stats().kernels_launched < plain.stats().kernels_launched   # the fused path really ran
     assert np.array_equal(lf.view(np.uint32), lp.view(np.uint32))
     tok = int(lf.argmax())
@@ -277,7 +276,8 @@ def test_fused_step_matches_per_operation_kernels_bit_for_bit(ctx, monkeypatch):
     fused.destroy(); plain.destroy(); m.destroy()
 
 
-def test_fused_step_greedy_identity_vs_oracle(ctx):
+def test_fused_step_greedy_identity_vs_oracle(ctx, monkeypatch):
+    monkeypatch.setenv("PYRE_B200_FUSED", "1")
     cfg = _fused_cfg()
     spec = synth.model_spec(cfg, 12)
     m = synth.build_model(ctx, cfg, spec, 12)
