@@ -93,15 +93,23 @@ __global__ void __launch_bounds__(PB_KTHREADS, 1) pb_gemvq_kernel(const PbGemvQP
         }
     } else {
         for (int b = 0; b < NB; b++) {
+            // the values this warp splits (its first two passes: rows of up to 4096 columns) are requested before the sum of
+            // squares is formed, so that the two walks over the row share one trip to L2
+            float4 vp0 = make_float4(0.f, 0.f, 0.f, 0.f), vp1 = vp0;
+            if (b < p.t) {
+                if (warp * 4 < ng) vp0 = *reinterpret_cast<const float4*>(p.x + b * p.ldx + 32 * (warp * 4) + 4 * lane);
+                if ((warp + PB_CONSUMERS) * 4 < ng) vp1 = *reinterpret_cast<const float4*>(p.x + b * p.ldx + 32 * ((warp + PB_CONSUMERS) * 4) + 4 * lane);
+            }
             float s = 1.0f;
             if (p.mode == PB_ACT_NORM && b < p.t) {  // rms(): x * s * w  (qwen4exp_gguf.rs:209)
                 float ss = pb_strided_ss(p.x + b * p.ldx, cols, tid, CT);
                 ss = pb_consumer_sum(ss, red, warp, lane);
                 s = 1.0f / sqrtf(ss / (float)cols + p.eps);
             }
-            for (int g0 = warp * 4; g0 < ng; g0 += PB_CONSUMERS * 4) {
+            int pass = 0;
+            for (int g0 = warp * 4; g0 < ng; g0 += PB_CONSUMERS * 4, pass++) {
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (b < p.t) v = *reinterpret_cast<const float4*>(p.x + b * p.ldx + 32 * g0 + 4 * lane);
+                if (b < p.t) v = pass == 0 ? vp0 : (pass == 1 ? vp1 : *reinterpret_cast<const float4*>(p.x + b * p.ldx + 32 * g0 + 4 * lane));
                 if (p.mode == PB_ACT_NORM) v = pb_norm_vec(v, s, *reinterpret_cast<const float4*>(p.norm_w + 32 * g0 + 4 * lane));
                 pb_split_groups4(v, lane, g0, cols, xq + (size_t)b * xw);
             }

@@ -163,6 +163,36 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
     }
     // grid.y cuts the tokens into groups of PB_ROUTER_TPG: this CTA handles tokens [b_lo, b_hi)
     const int b_lo = (int)blockIdx.y * PB_ROUTER_TPG, b_hi = min(p.t, b_lo + PB_ROUTER_TPG);
+    if (p.t == 1 && p.cols == 2048 && p.phase == 0 && p.norm_w && !p.exch) {
+        // One token on one GPU: every warp fetches the activation row once, in the layout that the RMS scale, the row product and
+        // (for the CTAs that split a piece of it) the split all use, instead of one trip to L2 for each of the three.  Same arithmetic
+        // as pb_row_rms_scale, PbRouterRow2048::dot and the general loops below.
+        float4 xv[16];
+#pragma unroll
+        for (int k = 0; k < 16; k++) xv[k] = *reinterpret_cast<const float4*>(p.x + lane * 4 + 128 * k);
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < 16; k++) ss += fmaf(xv[k].x, xv[k].x, fmaf(xv[k].y, xv[k].y, fmaf(xv[k].z, xv[k].z, __fmul_rn(xv[k].w, xv[k].w))));
+        ss = pb_warp_sum(ss);
+        const float s = 1.0f / sqrtf(ss / (float)p.cols + p.eps);
+        if (warp == 0 && (int)blockIdx.x < 16) {   // groups 4 j .. 4 j + 3 of CTA j are elements 128 j + 4 lane ..: the lane's xv[j]
+            float4 v = xv[0];
+#pragma unroll
+            for (int k = 1; k < 16; k++) if (k == (int)blockIdx.x) v = xv[k];
+            const int g0 = (int)blockIdx.x * 4;
+            const float4 n = *reinterpret_cast<const float4*>(p.norm_w + 32 * g0 + 4 * lane);
+            v.x = v.x * s * n.x; v.y = v.y * s * n.y; v.z = v.z * s * n.z; v.w = v.w * s * n.w;
+            pb_split_groups4(v, lane, g0, p.cols, p.xq_out);
+        }
+        pb_stamp(p.stamps, 3, st_first);
+        if (wrow) {
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+            for (int k = 0; k < 16; k++) { a0 = fmaf(rr.wr[k].x, xv[k].x, a0); a1 = fmaf(rr.wr[k].y, xv[k].y, a1); a2 = fmaf(rr.wr[k].z, xv[k].z, a2); a3 = fmaf(rr.wr[k].w, xv[k].w, a3); }
+            const float acc = pb_warp_sum((a0 + a1) + (a2 + a3)) * s;
+            if (lane == 0) p.logits[row] = acc;
+        }
+    } else {
     // per-token RMS scale (rms(): 1 / sqrt(mean(x^2) + eps), qwen4exp_gguf.rs:209); one warp per token
     for (int b = b_lo + warp; b < b_hi; b += 8) {
         const float s = p.norm_w ? pb_row_rms_scale(p.x + b * p.ldx, p.cols, p.eps, lane) : 1.0f;
@@ -202,6 +232,7 @@ __global__ void __launch_bounds__(256) pb_router_kernel(const PbRouterParams p, 
             if (lane == 0) p.logits[b * p.ldl + row] = acc;
             if (p.exch && lane < p.exch->world) p.exch->peer_xg[lane][p.peer_off + b * p.ldl + p.cols + row] = acc;
         }
+    }
     }
     if (p.phase == 1) {
         if (!p.exch) return;
