@@ -331,6 +331,13 @@ class Model:
         lib().orc_model_set_ple(self.h, C.c_int(ngram), C.c_int(per_gram), C.c_int(conv_k), C.c_uint32(eos), C.c_int(dim),
                                 mult.ctypes.data_as(C.c_void_p), off.ctypes.data_as(C.c_void_p), vocab.ctypes.data_as(C.c_void_p))
 
+    def ple_token(self, layer: int, nrm_all: np.ndarray, key: np.ndarray, val: np.ndarray, x: np.ndarray, pos: int):
+        """One token's injection (ple, qwen4exp_gguf.rs:1409-1434): x and nrm_all[pos] are updated in place."""
+        assert nrm_all.dtype == np.float32 and x.dtype == np.float32 and nrm_all.flags.c_contiguous and x.flags.c_contiguous
+        k = np.ascontiguousarray(key, dtype=np.float32); v = np.ascontiguousarray(val, dtype=np.float32)
+        lib().orc_ple_token(self.h, C.c_int(layer), nrm_all.ctypes.data_as(C.c_void_p), k.ctypes.data_as(C.c_void_p), v.ctypes.data_as(C.c_void_p),
+                            x.ctypes.data_as(C.c_void_p), C.c_int64(pos))
+
     def ple_hash(self, ctx):
         """Table rows of a token with context `ctx` (the token, then its predecessors; -1 = none)."""
         ngram, per = self.ple

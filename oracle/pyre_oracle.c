@@ -884,6 +884,9 @@ static void ple_token(const orc_model* m, int il, float* nrm_all, const float* k
     free(gated); free(kn); free(q);
 }
 
+/* ple_token for callers outside the forward pass (tests): nrm_all = rows by position [max positions][streams * d] */
+void orc_ple_token(const orc_model* m, int il, float* nrm_all, const float* key, const float* val, float* xt, int64_t pos) { ple_token(m, il, nrm_all, key, val, xt, pos); }
+
 int orc_forward(const orc_model* m, orc_state* st, const uint32_t* ids, int t, float* logits) {
     const orc_cfg* c = &m->cfg; int d = c->d, hc = c->hc; int xw = (hc > 0 ? hc : 1) * d; int64_t start = st->pos;
     if (start + t > c->max_ctx) return -2;

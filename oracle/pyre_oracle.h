@@ -105,6 +105,9 @@ void orc_model_free(orc_model* m);
 void orc_model_set_ple(orc_model* m, int ngram, int per_gram, int conv_k, uint32_t eos, int dim, const uint64_t* mult, const uint64_t* off, const uint64_t* vocab);
 /* table rows of a token whose context (the token first, then its predecessors, -1 = none) is ctx[ngram]: rows[nh] (ple_rows :1390-1407) */
 void orc_ple_hash(const orc_model* m, const int64_t* ctx, int64_t* rows);
+/* ple :1409-1434 for one token at position pos, given its projected key [streams * d] and value [d]: updates xt [streams * d] and stores the
+ * token's normalized row at nrm_all[pos] (rows of earlier positions are read from the same array) */
+void orc_ple_token(const orc_model* m, int il, float* nrm_all, const float* key, const float* val, float* xt, int64_t pos);
 void orc_model_set_indexer(orc_model* m, int budget, int ratio, int n_head, int head_dim);   /* QSA geometry, Cfg :24-25 */
 void orc_model_set_ctx_train(orc_model* m, int64_t ctx_train);   /* YaRN when cfg.max_ctx > ctx_train (Model::load :490-517) */
 int orc_model_set_mat(orc_model* m, int layer, int role, const orc_mat* mat);   /* layer -1 = global */

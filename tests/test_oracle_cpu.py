@@ -306,3 +306,52 @@ def test_ple_hash_rows_follow_the_reference_rule():
                 h = (n - 2) * 2 + gi
                 want.append(mixed % g["vocab"][h] + g["off"][h])
         assert om.ple_hash(ctx).tolist() == want, ctx
+
+
+def test_ple_by_position_rows_equal_the_reference_ring():
+    """The oracle keeps the normalized rows by position; the reference drains and extends a ring of the last (conv_k - 1) * ngram rows
+    (ple, qwen4exp_gguf.rs:1409-1434, hist :1432).  The reference's loop, written here in numpy with its ring, gives the same streams."""
+    from pyre_b200.synth import ple_geometry
+    rng = np.random.default_rng(8)
+    d, hc, K, ngram, T = 64, 2, 3, 3, 11
+    w = hc * d
+    g = ple_geometry([0], ngram=ngram, per_gram=1, conv_k=K, dim=256)
+    om = oracle.Model(oracle.make_cfg(n_layers=1, d=d, hc=hc, hc_lr=8, vocab=64, max_ctx=32, eps=1e-6))
+    om.set_ple(g["ngram"], g["per_gram"], g["conv_k"], g["eos"], g["dim"], g["mult"], g["off"], g["vocab"])
+    nk, nq, nc = (1.0 + 0.1 * rng.standard_normal(w)).astype(np.float32), (1.0 + 0.1 * rng.standard_normal(w)).astype(np.float32), (1.0 + 0.1 * rng.standard_normal(w)).astype(np.float32)
+    conv = (0.5 * rng.standard_normal((w, K))).astype(np.float32)
+    for role, a in (("PLE_NORM_KEY", nk), ("PLE_NORM_QUERY", nq), ("PLE_NORM_CONV", nc), ("PLE_CONV", conv.reshape(-1))):
+        om.set_vec(0, role, a)
+    keys = rng.standard_normal((T, w)).astype(np.float32); vals = rng.standard_normal((T, d)).astype(np.float32)
+    xs = rng.standard_normal((T, w)).astype(np.float32)
+    # the oracle, by position
+    nrm_all = np.zeros((32, w), np.float32); xo = xs.copy()
+    for t in range(T):
+        om.ple_token(0, nrm_all, keys[t], vals[t], xo[t], t)
+    # the reference's loop with its ring (float64 accumulation is avoided: same f32 operations, numpy order)
+    f32 = np.float32
+    def rms(v, wt):
+        s = f32(1.0) / np.sqrt(f32(np.sum(v * v, dtype=np.float32)) / f32(len(v)) + f32(1e-6))
+        return v * s * wt
+    dil, hl = ngram, (K - 1) * ngram
+    hist = np.zeros((hl, w), np.float32); xr = xs.copy()
+    for t in range(T):
+        gated = np.zeros(w, np.float32)
+        for s_ in range(hc):
+            sl = slice(s_ * d, (s_ + 1) * d)
+            kk, q = rms(keys[t, sl], nk[sl]), rms(xr[t, sl], nq[sl])
+            sc = f32(np.dot(kk, q)) / f32(np.sqrt(f32(d)))
+            gte = f32(1.0) / (f32(1.0) + np.exp(-(np.sign(sc) if sc != 0 else f32(1.0)) * np.sqrt(max(abs(sc), f32(1e-6)))))
+            gated[sl] = vals[t] * f32(gte)
+        nrm = gated.copy()
+        for s_ in range(hc):
+            sl = slice(s_ * d, (s_ + 1) * d)
+            nrm[sl] = rms(nrm[sl], nc[sl])
+        o = conv[:, K - 1] * nrm
+        for k in range(K - 1):
+            back = (K - 1 - k) * dil
+            o = o + conv[:, k] * hist[hl - back]
+        xr[t] += gated + o / (1.0 + np.exp(-o))
+        hist = np.concatenate([hist[1:], nrm[None]])
+    assert np.max(np.abs(xo - xr)) < 2e-5 * max(1.0, float(np.max(np.abs(xr))))
+    assert np.max(np.abs(nrm_all[T - hl:T] - hist)) < 2e-5
