@@ -1044,7 +1044,6 @@ static int run_step_fused(pb_state* s) {
     return pb_launch_advance(ctx, s->pos, 1, s->amax, s->next, s->ids, s->trace, s->trace_len, s->trace_cap);
 }
 
-// ---- hyper-connection residual (hc >= 1): forward_inner :2087-2157 with hc_mix / hc_combine around every block ----
 // ---- per-layer n-gram embeddings (ple_rows :1390-1407, ple :1409-1434) ----
 // y[t][ldy] = W . x[t][ldx] for a matrix of any type, 16 columns a launch
 static int gemv_any(pb_ctx* ctx, pb_qmat* q, const float* x, int64_t ldx, int t, float* y, int64_t ldy) {
@@ -1082,6 +1081,7 @@ static int run_ple(pb_state* s, int il, float* x, int t) {
     return pb_launch_ple_conv(ctx, s->ple_gated, s->ple_ring[(size_t)pi], s->ple_R, V(m, il, PB_R_PLE_CONV), m->ple_conv_k, m->ple.ngram, posv, t, window, s->ple_base, x, w, w);
 }
 
+// ---- hyper-connection residual (hc >= 1): forward_inner :2087-2157 with hc_mix / hc_combine around every block ----
 static void hc_params(pb_state* s, int il, int r_norm, int r_down, int r_up, int r_inj, PbHcParams& h) {
     pb_model* m = s->m; const pb_cfg& c = m->cfg;
     memset(&h, 0, sizeof h);
