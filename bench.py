@@ -280,8 +280,9 @@ def run_ours(args):
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         e2.record(stream)
+        lg_host = ctx.pinned_empty((B, cfg.vocab))           # the caller's reused, page-locked logits buffer
         for _ in range(args.steps):
-            lg = st.forward(ids.reshape(B, 1))
+            lg = st.forward(ids.reshape(B, 1), out=lg_host)
             ids = lg.argmax(axis=1).astype(np.uint32)
         e3.record(stream)
     barrier()

@@ -58,6 +58,12 @@ const char* pb_last_error(const pb_ctx* ctx);
 int pb_ctx_set_stream(pb_ctx* ctx, void* cuda_stream);
 int pb_ctx_own_stream(pb_ctx* ctx);
 int pb_ctx_sync(pb_ctx* ctx);
+/* Page-locked host memory for the caller's logits buffers: pb_forward / pb_verify copy straight into such a destination (one DMA),
+ * where a pageable one costs a staging copy in the library and a second copy on the host (the reference reads logits into a fresh Vec
+ * per step, Model::forward src/model/qwen4exp_gguf.rs:2050; a caller that reuses one buffer allocates it here).  Memory the caller
+ * page-locked itself (cudaHostRegister) is recognised the same way. */
+int pb_host_alloc(pb_ctx* ctx, size_t nbytes, void** out);
+int pb_host_free(pb_ctx* ctx, void* p);   /* ctx may be NULL (the buffer outlived its context) */
 /* Reads and clears the device status word (0 = no kernel reported a failure). */
 int pb_ctx_device_status(pb_ctx* ctx, int* status);
 /* Non-blocking check for the host's idle / step hooks (Model::idle_hook and step_hook,

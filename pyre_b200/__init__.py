@@ -126,6 +126,20 @@ class Ctx:
     def own_stream(self):
         self.check(lib().pb_ctx_own_stream(self.h))
 
+    def pinned_empty(self, shape, dtype=np.float32) -> np.ndarray:
+        """An array in page-locked host memory (pb_host_alloc): logits read into it take one DMA instead of a staging copy and a
+        host copy.  The memory is released when the array (and every view of it) is gone."""
+        shape = tuple(int(x) for x in (shape if isinstance(shape, (tuple, list)) else (shape,)))
+        n = int(np.prod(shape, dtype=np.int64)) * np.dtype(dtype).itemsize
+        ptr = C.c_void_p()
+        self.check(lib().pb_host_alloc(self.h, C.c_size_t(n), C.byref(ptr)))
+        buf = (C.c_uint8 * max(n, 1)).from_address(ptr.value)
+        arr = np.frombuffer(buf, dtype=np.uint8, count=n).view(dtype).reshape(shape)
+        free = lib().pb_host_free
+        import weakref
+        weakref.finalize(buf, lambda a=ptr.value: free(None, C.c_void_p(a)))     # without the context: the array may outlive it
+        return arr
+
     def sync(self):
         self.check(lib().pb_ctx_sync(self.h))
 

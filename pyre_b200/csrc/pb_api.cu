@@ -120,6 +120,20 @@ int pb_ctx_own_stream(pb_ctx* ctx) {
     return PB_OK;
 }
 
+int pb_host_alloc(pb_ctx* ctx, size_t nbytes, void** out) {
+    if (!ctx || !out) return PB_ERR_ARG;
+    *out = nullptr;
+    PB_TRY(pb_enter(ctx));
+    if (cudaMallocHost(out, nbytes ? nbytes : 1) != cudaSuccess) { cudaGetLastError(); *out = nullptr; PB_FAIL(ctx, PB_ERR_OOM, "page-locked allocation of %zu bytes failed", nbytes); }
+    return PB_OK;
+}
+int pb_host_free(pb_ctx* ctx, void* p) {
+    if (!p) return PB_OK;
+    if (!ctx) { if (cudaFreeHost(p) != cudaSuccess) { cudaGetLastError(); return PB_ERR_CUDA; } return PB_OK; }   // a buffer may outlive the context that made it
+    PB_TRY(pb_enter(ctx));
+    PB_CUDA(ctx, cudaFreeHost(p));
+    return PB_OK;
+}
 int pb_ctx_sync(pb_ctx* ctx) {
     if (!ctx) return PB_ERR_ARG;
     PB_TRY(pb_enter(ctx));

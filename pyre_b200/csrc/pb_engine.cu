@@ -1237,8 +1237,20 @@ static int step_once(pb_state* s) {
 
 // Logits leave through a pinned buffer of the state: a device -> pageable-host copy is staged by the driver in small pieces
 // (about 0.1 ms for one 608 KB row), a copy into pinned memory runs at link speed and the host copies it on.
-static int logits_stage(pb_state* s, size_t n) {
+// A destination in page-locked host memory (pb_host_alloc, or the caller's own registered buffer) takes the copy directly.
+static bool host_pinned(const void* p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+    return a.type == cudaMemoryTypeHost;
+}
+static int logits_stage(pb_state* s, size_t n, float* dst = nullptr, bool* direct = nullptr) {
     pb_ctx* ctx = s->m->ctx;
+    if (direct) *direct = false;
+    if (dst && direct && host_pinned(dst)) {
+        PB_CUDA(ctx, cudaMemcpyAsync(dst, s->logits, n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        *direct = true;
+        return PB_OK;
+    }
     if (n > s->pin_logits_n) {
         if (s->pin_logits) cudaFreeHost(s->pin_logits);
         s->pin_logits = nullptr; s->pin_logits_n = 0;
@@ -1293,10 +1305,11 @@ int pb_forward(pb_state* s, const uint32_t* ids_host, int t, float* logits_host)
         }
         s->verify_t = 0;
         timing_stop(s);
-        PB_TRY(logits_stage(s, (size_t)s->m->cfg.vocab));
+        bool direct = false;
+        PB_TRY(logits_stage(s, (size_t)s->m->cfg.vocab, logits_host, &direct));
         const int rcw = pb_sync_check(ctx, "pb_forward");
         timing_collect(s);
-        if (rcw == PB_OK) memcpy(logits_host, s->pin_logits, (size_t)s->m->cfg.vocab * 4);
+        if (rcw == PB_OK && !direct) memcpy(logits_host, s->pin_logits, (size_t)s->m->cfg.vocab * 4);
         return rcw;
     }
     if (B == 1) mtp_note(s, s->pos_host, ids_host, t);
@@ -1308,10 +1321,11 @@ int pb_forward(pb_state* s, const uint32_t* ids_host, int t, float* logits_host)
         if (j + 1 < t) PB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // the pinned id buffer is reused
     }
     timing_stop(s);
-    PB_TRY(logits_stage(s, (size_t)B * s->m->cfg.vocab));
+    bool direct = false;
+    PB_TRY(logits_stage(s, (size_t)B * s->m->cfg.vocab, logits_host, &direct));
     const int rc = pb_sync_check(ctx, "pb_forward");
     timing_collect(s);
-    if (rc == PB_OK) memcpy(logits_host, s->pin_logits, (size_t)B * s->m->cfg.vocab * 4);
+    if (rc == PB_OK && !direct) memcpy(logits_host, s->pin_logits, (size_t)B * s->m->cfg.vocab * 4);
     return rc;
 }
 
@@ -1389,10 +1403,11 @@ int pb_verify(pb_state* s, const uint32_t* ids_host, int t, float* logits_host) 
     timing_begin(s);
     PB_TRY(window_once(s, t, true, true));
     timing_stop(s);
-    PB_TRY(logits_stage(s, (size_t)t * c.vocab));
+    bool direct = false;
+    PB_TRY(logits_stage(s, (size_t)t * c.vocab, logits_host, &direct));
     PB_TRY(pb_sync_check(ctx, "pb_verify"));
     timing_collect(s);
-    memcpy(logits_host, s->pin_logits, (size_t)t * c.vocab * 4);
+    if (!direct) memcpy(logits_host, s->pin_logits, (size_t)t * c.vocab * 4);
     s->verify_t = t;
     return PB_OK;
 }

@@ -84,10 +84,16 @@ class State:
         self.ctx.check(create(model.h, C.c_int(batch), C.byref(self.h)))
 
     # ---- token loop -------------------------------------------------------------------
-    def forward(self, ids) -> np.ndarray:
-        """Feed ids [batch][t] (or [t] when batch == 1); logits of the last position, [batch][vocab]."""
+    def forward(self, ids, out: np.ndarray = None) -> np.ndarray:
+        """Feed ids [batch][t] (or [t] when batch == 1); logits of the last position, [batch][vocab].  out = a float32 array of
+        that shape to reuse (Ctx.pinned_empty gives one the device writes into directly)."""
         ids = np.ascontiguousarray(ids, dtype=np.uint32).reshape(self.batch, -1)
-        logits = np.empty((self.batch, self.model.cfg.vocab), dtype=np.float32)
+        if out is not None:
+            if out.dtype != np.float32 or out.shape != (self.batch, self.model.cfg.vocab) or not out.flags.c_contiguous:
+                raise ValueError("forward: out must be a C-contiguous float32 array [batch][vocab]")
+            logits = out
+        else:
+            logits = np.empty((self.batch, self.model.cfg.vocab), dtype=np.float32)
         self.ctx.check(lib().pb_forward(self.h, _p(ids), C.c_int(ids.shape[1]), _p(logits)))
         return logits
 

@@ -373,3 +373,21 @@ def test_other_quant_formats_greedy_identity_vs_oracle(ctx, name):
     assert a == b, (name, margins)
     assert ctx.device_status() == 0
     st.destroy(); m.destroy()
+
+
+def test_forward_into_page_locked_buffer(ctx):
+    """pb_forward / pb_verify write straight into a destination from pb_host_alloc: same logits as through a pageable array."""
+    cfg = small_cfg(pb, n_layers=4, kv_bits=4, kv_recent=64, max_ctx=128)
+    spec = synth.model_spec(cfg, 5)
+    m = synth.build_model(ctx, cfg, spec, 5)
+    a, b = m.new_state(1), m.new_state(1)
+    out = ctx.pinned_empty((1, cfg.vocab))
+    for tok in (3, 400, 9):
+        la = a.forward([tok], out=out)
+        assert la is out
+        assert np.array_equal(la, b.forward([tok]))
+    with pytest.raises(ValueError):
+        a.forward([1], out=np.empty((2, cfg.vocab), np.float32))
+    del out, la
+    assert ctx.device_status() == 0
+    a.destroy(); b.destroy(); m.destroy()
